@@ -1,0 +1,115 @@
+"""In-tree build of the native libraries.
+
+* ``lib/libneox_b200.so``  – every CUDA kernel, compiled by nvcc for sm_100a only
+  (``-gencode arch=compute_100a,code=sm_100a``), exposing a plain C ABI that
+  ``gpt_neox_b200.ops`` binds with ctypes.
+* ``lib/libneox_data.so`` – the CPU dataset-index builders (g++), the counterpart of the
+  reference's ``megatron/data/helpers.cpp`` built by ``megatron/data/Makefile``.
+
+Objects are cached under ``build/`` and rebuilt when a source or any header is newer.
+Run ``python -m gpt_neox_b200.build`` (``--force`` to rebuild everything).
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIB = PKG / "lib"
+OBJ = PKG.parent / "build" / "obj"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+    "--use_fast_math",
+    "-Xptxas", "-v",
+    "--expt-relaxed-constexpr",
+]
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-shared", "-Wall", "-pthread"]
+
+
+def _nvcc() -> str:
+    for c in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if c and os.path.exists(c):
+            return c
+    raise RuntimeError("nvcc not found")
+
+
+def _stale(target: Path, deps) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(Path(d).stat().st_mtime > t for d in deps)
+
+
+def _compile_one(src: Path, headers, force: bool, verbose: bool):
+    obj = OBJ / (src.stem + ".o")
+    if not force and not _stale(obj, [src, *headers]):
+        return obj, ""
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
+    log = r.stderr
+    (OBJ / (src.stem + ".ptxas.log")).write_text(log)
+    if verbose:
+        print(log)
+    return obj, log
+
+
+def build_cuda(force: bool = False, verbose: bool = False) -> Path:
+    OBJ.mkdir(parents=True, exist_ok=True)
+    LIB.mkdir(parents=True, exist_ok=True)
+    srcs = sorted(CSRC.glob("*.cu"))
+    headers = sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")))
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
+        objs = [o for o, _ in ex.map(lambda s: _compile_one(s, headers, force, verbose), srcs)]
+    out = LIB / "libneox_b200.so"
+    if force or _stale(out, objs):
+        cmd = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
+               "-Xcompiler", "-fPIC", "-o", str(out), *map(str, objs), "-lcudart"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
+def build_data_helpers(force: bool = False) -> Path:
+    LIB.mkdir(parents=True, exist_ok=True)
+    src = CSRC / "data_helpers.cpp"
+    out = LIB / "libneox_data.so"
+    if src.exists() and (force or _stale(out, [src])):
+        cmd = [os.environ.get("CXX", "g++"), *CXX_FLAGS, str(src), "-o", str(out)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"g++ failed:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
+def build_all(force: bool = False, verbose: bool = False):
+    a = build_data_helpers(force)
+    b = build_cuda(force, verbose)
+    return a, b
+
+
+def ptxas_report() -> str:
+    """Registers / spills / shared memory of every kernel, from the cached ptxas logs."""
+    out = []
+    for f in sorted(OBJ.glob("*.ptxas.log")):
+        out.append(f"== {f.stem}")
+        out.append(f.read_text())
+    return "\n".join(out)
+
+
+if __name__ == "__main__":
+    force = "--force" in sys.argv
+    verbose = "--verbose" in sys.argv
+    a, b = build_all(force, verbose)
+    print("built", a)
+    print("built", b)

@@ -1,0 +1,457 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory),
+// operands staged by TMA into a 128-byte-swizzled shared-memory ring.
+//
+// Replaces the cuBLAS calls behind every dense projection of the reference
+// (megatron/mpu/layers.py:576,773 and megatron/model/transformer.py:1240-1242) and fuses the
+// element-wise work the reference runs as separate torch.jit kernels
+// (megatron/model/activations.py:78-112, megatron/model/fused_bias_dropout.py:44-55) into the
+// epilogue.
+//
+// Kernel shape: persistent, one CTA per SM, 192 threads:
+//   warp 0      TMA producer  (one elected lane)
+//   warp 1      TMEM allocator + tcgen05.mma issuer (one elected lane)
+//   warps 2..5  epilogue: tcgen05.ld from TMEM -> registers -> fused math -> global stores
+// Tile 128 x BN x 64 with a STAGES-deep operand ring and two TMEM accumulators, so the
+// epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Operand layouts (all row-major in memory):
+//   transA = 0: A is [M, K]  (K contiguous)      transA = 1: A is [K, M]  (M contiguous)
+//   transB = 0: B is [N, K]  (K contiguous, the nn.Linear weight layout)
+//   transB = 1: B is [K, N]  (N contiguous)
+// so that  forward = (0,0),  input-gradient = (0,1),  weight-gradient = (1,1).
+#include "common.h"
+#include "ptx.cuh"
+
+namespace nx {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+enum EpiFlags : int {
+  EPI_BIAS = 1,         // + bias[n]
+  EPI_GELU_ERF = 2,     // exact GeLU
+  EPI_GELU_TANH = 4,    // tanh-approximated GeLU
+  EPI_AUX_OUT = 8,      // store the pre-activation (after bias) as bf16 into aux_out
+  EPI_DGELU_ERF = 16,   // multiply by gelu_erf'(aux_in)
+  EPI_DGELU_TANH = 32,  // multiply by gelu_tanh'(aux_in)
+  EPI_RESIDUAL = 64,    // + residual (bf16, same shape / leading dimension as aux ld)
+  EPI_ACCUM = 128,      // C += result (read-modify-write)
+  EPI_OUT_F32 = 256,    // C is fp32 instead of bf16
+  EPI_SCALE = 512,      // result *= alpha (applied first)
+};
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* aux_in;
+  __nv_bfloat16* aux_out;
+  const __nv_bfloat16* residual;
+  long long ld_aux;
+  int flags;
+  float alpha;
+  int tiles_m, tiles_n;
+  int* err;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem base word
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  // Group 8 row-tiles together so that concurrently running CTAs share B panels in L2.
+  constexpr int GROUP = 8;
+  const int per_group = GROUP * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP;
+  const int gsize = min(GROUP, tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + (r % gsize);
+  tn = r / gsize;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const GemmParams p) {
+  using L = SmemLayout<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const uint32_t bar_base = smem_base + L::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  volatile uint32_t* tmem_slot_gen =
+      reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFFSET + 8 * (2 * STAGES + 4));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  bool aborted = false;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !aborted; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, p.err, 1)) {
+            aborted = true;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + L::A_BYTES;
+          mbar_expect_tx(full_bar(stage), L::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_2d(a_dst, &tmA, full_bar(stage), k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(a_dst + j * (BK * 128), &tmA, full_bar(stage), m0 + j * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(b_dst, &tmB, full_bar(stage), k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * (BK * 128), &tmB, full_bar(stage), n0 + j * 64, k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      // K-major: 8-row groups are 1024 B apart (SBO), 16 K-elements advance 32 B.
+      // MN-major: 64-element column blocks are BK*128 B apart (LBO), 8-row K groups 1024 B
+      // apart (SBO), 16 K-rows advance 2048 B.
+      constexpr uint32_t A_LBO = A_MN ? BK * 128 : 0, B_LBO = B_MN ? BK * 128 : 0;
+      constexpr uint32_t A_KADV = A_MN ? UMMA_K * 128 : UMMA_K * 2;
+      constexpr uint32_t B_KADV = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !aborted; tile += gridDim.x) {
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, p.err, 2)) {
+          aborted = true;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, p.err, 3)) {
+            aborted = true;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + stage * L::STAGE_BYTES;
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = umma_smem_desc_sw128(a_addr + k * A_KADV, A_LBO, 1024);
+            const uint64_t bdesc = umma_smem_desc_sw128(b_addr + k * B_KADV, B_LBO, 1024);
+            umma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // frees the smem slot once these MMAs retire
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (aborted) break;
+        umma_commit(tmem_full_bar(acc));  // accumulator complete -> epilogue
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const int flags = p.flags;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, p.err, 4)) {
+        aborted = true;
+        break;
+      }
+      tc_fence_after_sync();
+      const long long row = m0 + row_in_tile;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(quad * 32) << 16), r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (flags & EPI_SCALE) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+        }
+        if (flags & EPI_BIAS) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + j < p.N) {
+              const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + j));
+              const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y),
+                           b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+              v[j + 0] += b0.x; v[j + 1] += b0.y; v[j + 2] += b1.x; v[j + 3] += b1.y;
+              v[j + 4] += b2.x; v[j + 5] += b2.y; v[j + 6] += b3.x; v[j + 7] += b3.y;
+            }
+          }
+        }
+        if (row_ok) {
+          if (flags & EPI_AUX_OUT) {
+            __nv_bfloat16* ap = p.aux_out + row * p.ld_aux + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < p.N) {
+                uint4 o;
+                o.x = pack_bf16x2(v[j], v[j + 1]);
+                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(ap + j) = o;
+              }
+            }
+          }
+          if (flags & (EPI_DGELU_ERF | EPI_DGELU_TANH)) {
+            const __nv_bfloat16* ap = p.aux_in + row * p.ld_aux + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < p.N) {
+                const uint4 a = *reinterpret_cast<const uint4*>(ap + j);
+                const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const float2 x = unpack_bf16x2(aw[q]);
+                  if (flags & EPI_DGELU_ERF) {
+                    v[j + 2 * q] *= gelu_erf_grad(x.x);
+                    v[j + 2 * q + 1] *= gelu_erf_grad(x.y);
+                  } else {
+                    v[j + 2 * q] *= gelu_tanh_grad(x.x);
+                    v[j + 2 * q + 1] *= gelu_tanh_grad(x.y);
+                  }
+                }
+              }
+            }
+          }
+          if (flags & EPI_GELU_ERF) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+          } else if (flags & EPI_GELU_TANH) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+          }
+          if (flags & EPI_RESIDUAL) {
+            const __nv_bfloat16* rp = p.residual + row * p.ld_aux + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < p.N) {
+                const uint4 a = *reinterpret_cast<const uint4*>(rp + j);
+                const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y),
+                             x2 = unpack_bf16x2(a.z), x3 = unpack_bf16x2(a.w);
+                v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
+                v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
+              }
+            }
+          }
+          if (flags & EPI_OUT_F32) {
+            float* cp = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col0 + j < p.N) {
+                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (flags & EPI_ACCUM) {
+                  const float4 old = *reinterpret_cast<const float4*>(cp + j);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(cp + j) = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < p.N) {
+                if (flags & EPI_ACCUM) {
+                  const uint4 a = *reinterpret_cast<const uint4*>(cp + j);
+                  const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y),
+                               x2 = unpack_bf16x2(a.z), x3 = unpack_bf16x2(a.w);
+                  v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
+                  v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[j], v[j + 1]);
+                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(cp + j) = o;
+              }
+            }
+          }
+        }
+      }
+      // This warp is done reading the accumulator: hand it back to the MMA issuer.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (aborted) {
+    // A bounded wait ran out: give copies already in flight time to land before the CTA's
+    // shared memory is released.
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                       cudaStream_t stream) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    NX_CUDA_CHECK(
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    configured = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, GEMM_THREADS, L::DYN_BYTES, stream>>>(tmA, tmB, p);
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+
+template <int BN, int STAGES>
+static int dispatch_layout(int transA, int transB, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                           const GemmParams& p, cudaStream_t stream) {
+  if (!transA && !transB) return launch_gemm<BN, STAGES, false, false>(tmA, tmB, p, stream);
+  if (!transA && transB) return launch_gemm<BN, STAGES, false, true>(tmA, tmB, p, stream);
+  if (transA && !transB) return launch_gemm<BN, STAGES, true, false>(tmA, tmB, p, stream);
+  return launch_gemm<BN, STAGES, true, true>(tmA, tmB, p, stream);
+}
+
+}  // namespace nx
+
+// C[M,N] = epilogue(op(A) * op(B)).  Leading dimensions in elements.  bias/aux/residual may be
+// null when their flag is clear.  ld_aux is the leading dimension shared by aux_in, aux_out
+// and residual.  Returns an NxStatus.
+NX_API int nx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                        long long ldb, long long ldc, int transA, int transB, const void* bias,
+                        const void* aux_in, void* aux_out, const void* residual, long long ld_aux,
+                        int flags, float alpha, void* stream_) {
+  using namespace nx;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return NX_OK;
+  NX_REQUIRE(K > 0, "gemm: K must be positive");
+  NX_REQUIRE(N % 8 == 0, "gemm: N (%d) must be a multiple of 8", N);
+  NX_REQUIRE(lda % 8 == 0 && ldb % 8 == 0, "gemm: lda/ldb must be multiples of 8 elements");
+  NX_REQUIRE(ldc % ((flags & EPI_OUT_F32) ? 4 : 8) == 0, "gemm: ldc alignment");
+  NX_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0, "gemm: C must be 16-byte aligned");
+  if (flags & EPI_BIAS) NX_REQUIRE(bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15) == 0, "gemm: bias null/unaligned");
+  if (flags & (EPI_DGELU_ERF | EPI_DGELU_TANH)) NX_REQUIRE(aux_in != nullptr && ld_aux % 8 == 0, "gemm: aux_in");
+  if (flags & EPI_AUX_OUT) NX_REQUIRE(aux_out != nullptr && ld_aux % 8 == 0, "gemm: aux_out");
+  if (flags & EPI_RESIDUAL) NX_REQUIRE(residual != nullptr && ld_aux % 8 == 0, "gemm: residual");
+
+  const int BN = (N <= 128) ? 128 : 256;
+  CUtensorMap tmA, tmB;
+  bool ok;
+  if (!transA) ok = make_tma_2d(&tmA, A, M, K, lda * 2, BM, BK, 2);
+  else         ok = make_tma_2d(&tmA, A, K, M, lda * 2, BK, 64, 2);
+  if (!ok) return NX_ERR_ARG;
+  if (!transB) ok = make_tma_2d(&tmB, B, N, K, ldb * 2, BN, BK, 2);
+  else         ok = make_tma_2d(&tmB, B, K, N, ldb * 2, BK, 64, 2);
+  if (!ok) return NX_ERR_ARG;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.aux_in = static_cast<const __nv_bfloat16*>(aux_in);
+  p.aux_out = static_cast<__nv_bfloat16*>(aux_out);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.ld_aux = ld_aux;
+  p.flags = flags;
+  p.alpha = alpha;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.err = device_error_word();
+  if (BN == 128) return dispatch_layout<128, 6>(transA, transB, tmA, tmB, p, stream);
+  return dispatch_layout<256, 4>(transA, transB, tmA, tmB, p, stream);
+}

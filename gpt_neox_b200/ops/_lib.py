@@ -1,0 +1,111 @@
+"""ctypes binding of ``lib/libneox_b200.so`` (the sm_100a kernel library).
+
+The library is loaded lazily on first use.  On a machine with a CUDA device a missing
+or unloadable library is a hard error: the CUDA ops never fall back silently to
+PyTorch kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libneox_b200.so"
+
+c_void_p, c_int, c_ll, c_float = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+
+
+class KernelError(RuntimeError):
+    """A native kernel launcher returned a non-zero status."""
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """The device error word was set: a bounded wait inside a kernel ran out."""
+
+
+def _declare(lib):
+    def sig(name, argtypes, restype=c_int):
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.argtypes = argtypes
+            fn.restype = restype
+
+    P, I, L, F = c_void_p, c_int, c_ll, c_float
+    sig("nx_last_error", [], C.c_char_p)
+    sig("nx_read_device_error", [I])
+    sig("nx_poison_device_error", [I])
+    sig("nx_sm_count", [])
+    sig("nx_abi_version", [])
+    sig("nx_gemm_bf16", [P, P, P, I, I, I, L, L, L, I, I, P, P, P, P, L, I, F, P])
+    sig("nx_grouped_gemm_bf16", [P, P, P, P, I, I, I, I, I, I, P])
+    sig("nx_layernorm_fwd", [P, P, P, P, P, P, P, L, I, F, I, P])
+    sig("nx_layernorm_bwd", [P, P, P, P, P, P, P, P, P, L, I, I, P])
+    sig("nx_rmsnorm_fwd", [P, P, P, P, P, L, I, F, I, P])
+    sig("nx_rmsnorm_bwd", [P, P, P, P, P, P, P, L, I, I, P])
+    sig("nx_bias_act_fwd", [P, P, P, L, I, I, P])
+    sig("nx_bias_act_bwd", [P, P, P, P, L, I, I, P])
+    sig("nx_gated_act_fwd", [P, P, P, L, I, I, P])
+    sig("nx_gated_act_bwd", [P, P, P, P, L, I, I, P])
+    sig("nx_bias_dropout_add_fwd", [P, P, P, P, P, L, I, F, C.c_ulonglong, C.c_ulonglong, P])
+    sig("nx_colsum_bf16", [P, P, L, I, I, P])
+    sig("nx_rope_fwd", [P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, L, L, I, P])
+    sig("nx_softmax_causal_fwd", [P, P, L, I, I, F, P])
+    sig("nx_softmax_causal_bwd", [P, P, P, L, I, I, F, P])
+    sig("nx_softmax_masked_fwd", [P, P, P, I, I, I, I, I, F, P])
+    sig("nx_softmax_masked_bwd", [P, P, P, L, I, F, P])
+    sig("nx_cross_entropy_fwd", [P, P, P, P, P, L, I, L, I, I, P])
+    sig("nx_cross_entropy_bwd", [P, P, P, P, P, P, L, I, L, I, I, P])
+    sig("nx_adamw_step", [P, P, P, P, P, L, F, F, F, F, F, F, F, P, I, P])
+    sig("nx_sumsq", [P, P, L, I, P])
+    sig("nx_embedding_fwd", [P, P, P, L, I, L, L, P])
+    sig("nx_embedding_bwd", [P, P, P, L, I, L, L, P])
+    sig("nx_flash_attn_fwd", [P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P])
+    sig("nx_flash_attn_bwd", [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P])
+    return lib
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        if not _LIB_PATH.exists():
+            raise KernelError(
+                f"{_LIB_PATH} is missing: build it with `python -m gpt_neox_b200.build` "
+                "(the CUDA ops have no PyTorch fallback on a GPU)"
+            )
+        _LIB = _declare(C.CDLL(str(_LIB_PATH), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL") else 0))
+    return _LIB
+
+
+def check(status: int, what: str = "kernel"):
+    if status != 0:
+        msg = lib().nx_last_error().decode(errors="replace")
+        raise KernelError(f"{what} failed with status {status}: {msg}")
+
+
+def ptr(t):
+    """Device pointer of a tensor (or None) as a ctypes void pointer."""
+    if t is None:
+        return None
+    return c_void_p(t.data_ptr())
+
+
+def stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def read_device_error(clear: bool = True) -> int:
+    return int(lib().nx_read_device_error(1 if clear else 0))
+
+
+def raise_on_device_error():
+    """Synchronising check of the device error word; raises DeviceWaitTimeout if set."""
+    v = read_device_error(clear=True)
+    if v != 0:
+        raise DeviceWaitTimeout(f"device error word = 0x{v:x} (code {v & 0xff}, site {v >> 8})")

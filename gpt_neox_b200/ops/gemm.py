@@ -1,0 +1,152 @@
+"""Dense bf16 GEMM on tcgen05 tensor cores, with fused epilogues, and the autograd
+``linear`` built on it.
+
+Counterpart of the cuBLAS ``F.linear`` calls of the reference
+(megatron/mpu/layers.py:576,773; megatron/model/transformer.py:1240-1242) and of its
+torch.jit bias+GeLU fusion (megatron/model/activations.py:78-112).
+
+On CPU tensors (tests, the gloo plumbing runs) the same functions compute with plain
+PyTorch in the tensor's dtype; that path is the numerical oracle of the CUDA kernels.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+EPI_BIAS = 1
+EPI_GELU_ERF = 2
+EPI_GELU_TANH = 4
+EPI_AUX_OUT = 8
+EPI_DGELU_ERF = 16
+EPI_DGELU_TANH = 32
+EPI_RESIDUAL = 64
+EPI_ACCUM = 128
+EPI_OUT_F32 = 256
+EPI_SCALE = 512
+
+#: counts launches of this library's kernels (read by bench.py for its ``gpu_launches`` claim)
+LAUNCHES = {"n": 0}
+
+
+def _as_2d(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or (x2.stride(0) % 8) != 0 or (x2.data_ptr() % 16) != 0:
+        x2 = x2.contiguous()
+    return x2
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
+         bias: torch.Tensor | None = None, gelu: str | None = None,
+         aux_out: torch.Tensor | None = None, dgelu_aux: torch.Tensor | None = None,
+         dgelu: str | None = None, residual: torch.Tensor | None = None,
+         out: torch.Tensor | None = None, accumulate: bool = False,
+         out_dtype: torch.dtype = torch.bfloat16, alpha: float | None = None) -> torch.Tensor:
+    """``C = epilogue(op(a) @ op(b))`` with 2-D row-major bf16 operands.
+
+    ``trans_a=False``: a is [M,K]; ``True``: a is [K,M].
+    ``trans_b=False``: b is [N,K] (weight layout); ``True``: b is [K,N].
+    Epilogue order: scale, +bias, store ``aux_out``, ×gelu'(``dgelu_aux``), GeLU, +residual,
+    (+= out if ``accumulate``).
+    """
+    assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    if trans_a:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if trans_b:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"inner dimensions differ: {K} vs {Kb}"
+    assert a.stride(1) == 1 and b.stride(1) == 1
+    if out is None:
+        assert not accumulate
+        out = torch.empty((M, N), device=a.device, dtype=out_dtype)
+    else:
+        assert out.shape == (M, N) and out.stride(1) == 1
+    flags = 0
+    if out.dtype == torch.float32:
+        flags |= EPI_OUT_F32
+    else:
+        assert out.dtype == torch.bfloat16
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N
+        flags |= EPI_BIAS
+    if gelu is not None:
+        flags |= EPI_GELU_TANH if gelu == "tanh" else EPI_GELU_ERF
+    ld_aux = 0
+    for t in (aux_out, dgelu_aux, residual):
+        if t is not None:
+            assert t.shape == (M, N) and t.stride(1) == 1 and t.dtype == torch.bfloat16
+            assert ld_aux in (0, t.stride(0)), "aux tensors must share one leading dimension"
+            ld_aux = t.stride(0)
+    if aux_out is not None:
+        flags |= EPI_AUX_OUT
+    if dgelu_aux is not None:
+        flags |= EPI_DGELU_TANH if dgelu == "tanh" else EPI_DGELU_ERF
+    if residual is not None:
+        flags |= EPI_RESIDUAL
+    if accumulate:
+        flags |= EPI_ACCUM
+    if alpha is not None:
+        flags |= EPI_SCALE
+    L = _lib.lib()
+    LAUNCHES["n"] += 1
+    _lib.check(L.nx_gemm_bf16(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+        int(trans_a), int(trans_b), _lib.ptr(bias), _lib.ptr(dgelu_aux), _lib.ptr(aux_out),
+        _lib.ptr(residual), ld_aux, flags, float(alpha if alpha is not None else 1.0),
+        _lib.stream()), "nx_gemm_bf16")
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x @ W^T (+ b) with the three GEMMs (forward, dgrad, wgrad) on tcgen05.
+
+    ``W.main_grad`` (fp32, optional): when present the weight gradient is accumulated into it
+    by the wgrad epilogue and ``None`` is returned for W — the fused gradient-accumulation
+    path used by the ZeRO engine.
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = _as_2d(x)
+        y = gemm(x2, weight, bias=bias)
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, weight = ctx.saved_tensors
+        gy2 = _as_2d(gy)
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = gemm(gy2, weight, trans_b=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            gw = wgrad(gy2, x2, weight)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            from .elementwise import colsum
+            gb = colsum(gy2)
+        return gx, gw, gb
+
+
+def wgrad(gy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor):
+    """dW[N,K] = gy2[M,N]^T @ x2[M,K]; accumulates into ``weight.main_grad`` when it exists."""
+    mg = getattr(weight, "main_grad", None)
+    if mg is not None:
+        gemm(gy2, x2, trans_a=True, trans_b=True, out=mg, accumulate=True)
+        return None
+    return gemm(gy2, x2, trans_a=True, trans_b=True)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``F.linear`` on the tcgen05 GEMM for CUDA bf16 tensors; PyTorch on CPU (oracle path)."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _LinearFn.apply(x, weight, bias)
+    if x.is_cuda:
+        raise _lib.KernelError(f"linear: CUDA path needs bf16 activations, got {x.dtype}")
+    return F.linear(x, weight, bias)
