@@ -1,0 +1,585 @@
+// Flash attention backward on tcgen05 (causal / sliding window / ALiBi / GQA).
+//
+// Three launches, no atomics, no fp32 scratch for dQ, deterministic:
+//   1. attn_delta_kernel    delta[b,h,q] = sum_d O * dO
+//   2. attn_bwd_dq_kernel   one CTA per 128 query rows: loops over key blocks, recomputes
+//                           S = Q K^T and dP = dO V^T on the tensor cores, forms
+//                           dS = P o (dP - delta) * scale per row (thread == query row), writes it
+//                           as bf16 into TMEM and accumulates dQ += dS K  (A operand from TMEM).
+//   3. attn_bwd_dkv_kernel  one CTA per 128 keys (per kv head; loops over the query heads of the
+//                           GQA group and over query blocks): computes the transposed tiles
+//                           S^T = K Q^T and dP^T = V dO^T so that thread == key row, writes P^T and
+//                           dS^T (bf16) over the same TMEM columns and accumulates
+//                           dV += P^T dO,  dK += dS^T Q.
+// Recomputing S and dP in both kernels costs 7 tile GEMMs instead of 5 but keeps every
+// accumulator in TMEM from first to last block.  Counterpart of the flash-attn 2 backward the
+// reference calls through autograd (megatron/model/transformer.py:573-690).
+#include "common.h"
+#include "ptx.cuh"
+#include "reduce.cuh"
+
+namespace nx {
+
+constexpr int AB = 128;  // rows per tile in every role
+constexpr int AB_THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnBwdParams {
+  const float* lse;    // [B,H,Sq_pad] base-2 log-sum-exp, +inf in the padding
+  const float* delta;  // [B,H,Sq_pad], 0 in the padding
+  const float* alibi;
+  __nv_bfloat16 *dq, *dk, *dv;
+  long long dq_sb, dq_sh, dq_ss, dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss;
+  int B, H, Hk, Sq, Sk, D, Sq_pad;
+  float scale, scale_log2;
+  int causal, window;
+  int* err;
+};
+
+// delta = rowsum(O * dO); one warp per (b, h, q) row.
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
+                                  const __nv_bfloat16* __restrict__ dO, float* __restrict__ delta,
+                                  int B, int H, int Sq, int Sq_pad, int D, long long o_sb, long long o_sh,
+                                  long long o_ss, long long d_sb, long long d_sh, long long d_ss) {
+  const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = static_cast<long long>(B) * H * Sq;
+  if (row >= total) return;
+  const int lane = threadIdx.x & 31;
+  const int q = static_cast<int>(row % Sq);
+  const int h = static_cast<int>((row / Sq) % H);
+  const int b = static_cast<int>(row / (static_cast<long long>(Sq) * H));
+  const __nv_bfloat16* op = o + b * o_sb + h * o_sh + q * o_ss;
+  const __nv_bfloat16* dp = dO + b * d_sb + h * d_sh + q * d_ss;
+  float s = 0.f;
+  for (int d = lane * 2; d < D; d += 64) {
+    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(op + d));
+    const float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dp + d));
+    s += a.x * g.x + a.y * g.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) delta[(static_cast<long long>(b) * H + h) * Sq_pad + q] = s;
+}
+
+template <int DP>
+struct BwdSmem {
+  static constexpr int TILE = AB * DP * 2;
+  static constexpr int BAR_OFF = 6 * TILE;  // two resident tiles + 2 x 2 streamed tiles
+  static constexpr int NBAR = 24;
+  static constexpr int VEC_OFF = BAR_OFF + NBAR * 8;  // lse / delta staging: 2 stages x 2 x 128 floats
+  static constexpr int TOTAL = VEC_OFF + 4 * AB * 4 + 16;
+  static constexpr int DYN = TOTAL + 1024;
+};
+
+// Loads one [128 x DP] tile (rows contiguous in d) as DP/64 swizzled boxes.
+template <int DP>
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* m, uint32_t bar, int row0,
+                                          int head, int batch) {
+#pragma unroll
+  for (int c = 0; c < DP / 64; ++c) tma_load_4d(dst + c * (AB * 128), m, bar, c * 64, row0, head, batch);
+}
+// D[128 x 128] = A[128 x DP] * B[128 x DP]^T, both K-major (head dim contiguous).
+template <int DP>
+__device__ __forceinline__ void mma_nt(uint32_t d_tmem, uint32_t a, uint32_t b) {
+  constexpr uint32_t idesc = umma_idesc_bf16(AB, AB, 0, 0);
+#pragma unroll
+  for (int k = 0; k < DP / 16; ++k) {
+    const uint32_t o = (k >> 2) * (AB * 128) + (k & 3) * 32;
+    umma_bf16_ss(d_tmem, umma_smem_desc_sw128(a + o, 0, 1024), umma_smem_desc_sw128(b + o, 0, 1024),
+                 idesc, k != 0 ? 1u : 0u);
+  }
+}
+// D[128 x DP] (+)= A_tmem[128 x 128 (bf16, 64 columns)] * B[128 x DP] with B's head dim contiguous
+// (MN-major B operand).
+template <int DP>
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b, bool accumulate) {
+  constexpr uint32_t idesc = umma_idesc_bf16(AB, DP, 0, 1);
+#pragma unroll
+  for (int k = 0; k < AB / 16; ++k) {
+    umma_bf16_ts(d_tmem, a_tmem + k * 8, umma_smem_desc_sw128(b + k * 2048, AB * 128, 1024), idesc,
+                 (accumulate || k != 0) ? 1u : 0u);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dQ kernel.  smem tiles: 0 = Q, 1 = dO, 2..3 = K ring, 4..5 = V ring.
+// TMEM: S [0,128) dP [128,256) dQ [256,256+DP) dS0 [384,448) dS1 [448,512)
+// ------------------------------------------------------------------------------------------------
+template <int DP>
+__global__ void __launch_bounds__(AB_THREADS, 1)
+    attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                       const AttnBwdParams p) {
+  using L = BwdSmem<DP>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  const uint32_t bar0 = sbase + L::BAR_OFF;
+  enum { QDO_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, SDP_FULL = 9, SDP_EMPTY = 10,
+         DS_FULL = 11, DQ_DONE = 13, NUSED = 15 };
+  auto bar = [&](int which, int idx) { return bar0 + 8u * (which + idx); };
+  const uint32_t tmem_slot = bar0 + 8u * 23;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(sgen + L::BAR_OFF + 8 * 23);
+  auto tile = [&](int i) { return sbase + i * L::TILE; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int kv_head = head / (p.H / p.Hk);
+  const int q0 = qt * AB;
+  const int off = p.Sk - p.Sq;
+  int kv_end = p.Sk;
+  if (p.causal) kv_end = min(p.Sk, q0 + AB + off);
+  int kv_begin = 0;
+  if (p.window >= 0) kv_begin = max(0, q0 + off - p.window);
+  const int jb = kv_begin / AB;
+  const int nblk = max((kv_end + AB - 1) / AB - jb, 0);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NUSED; ++i) {
+      const bool by_softmax = (i == SDP_EMPTY) || (i >= DS_FULL && i < DS_FULL + 2);
+      mbar_init(bar0 + 8u * i, by_softmax ? 4 : 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot_gen;
+  const uint32_t T_S = tmem, T_DP = tmem + 128, T_DQ = tmem + 256, T_DS = tmem + 384;
+  bool aborted = false;
+
+  if (warp == 0) {
+    if (elect_one() && nblk > 0) {
+      mbar_expect_tx(bar(QDO_FULL, 0), 2 * L::TILE);
+      load_tile<DP>(tile(0), &tmQ, bar(QDO_FULL, 0), q0, head, batch);
+      load_tile<DP>(tile(1), &tmDO, bar(QDO_FULL, 0), q0, head, batch);
+      for (int i = 0; i < nblk; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        const int k0 = (jb + i) * AB;
+        if (!mbar_wait(bar(K_EMPTY, st), ph ^ 1, p.err, 31)) { aborted = true; break; }
+        mbar_expect_tx(bar(K_FULL, st), L::TILE);
+        load_tile<DP>(tile(2 + st), &tmK, bar(K_FULL, st), k0, kv_head, batch);
+        if (!mbar_wait(bar(V_EMPTY, st), ph ^ 1, p.err, 32)) { aborted = true; break; }
+        mbar_expect_tx(bar(V_FULL, st), L::TILE);
+        load_tile<DP>(tile(4 + st), &tmV, bar(V_FULL, st), k0, kv_head, batch);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one() && nblk > 0) {
+      auto issue_dq = [&](int i) -> bool {
+        const int st = i & 1;
+        if (!mbar_wait(bar(DS_FULL, st), (i >> 1) & 1, p.err, 33)) return false;
+        tc_fence_after_sync();
+        mma_ts<DP>(T_DQ, T_DS + st * 64, tile(2 + st), i != 0);
+        umma_commit(bar(DQ_DONE, st));
+        umma_commit(bar(K_EMPTY, st));
+        return true;
+      };
+      if (!mbar_wait(bar(QDO_FULL, 0), 0, p.err, 34)) aborted = true;
+      for (int i = 0; i < nblk && !aborted; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        if (!mbar_wait(bar(K_FULL, st), ph, p.err, 35)) { aborted = true; break; }
+        if (!mbar_wait(bar(V_FULL, st), ph, p.err, 36)) { aborted = true; break; }
+        if (!mbar_wait(bar(SDP_EMPTY, 0), (i & 1) ^ 1, p.err, 37)) { aborted = true; break; }
+        tc_fence_after_sync();
+        mma_nt<DP>(T_S, tile(0), tile(2 + st));
+        mma_nt<DP>(T_DP, tile(1), tile(4 + st));
+        umma_commit(bar(SDP_FULL, 0));
+        umma_commit(bar(V_EMPTY, st));
+        if (i > 0 && !issue_dq(i - 1)) { aborted = true; break; }
+      }
+      if (!aborted && !issue_dq(nblk - 1)) aborted = true;
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const int qi = q0 + r;
+    const int qpos = qi + off;
+    const bool row_ok = qi < p.Sq;
+    const long long stat_idx = (static_cast<long long>(batch) * p.H + head) * p.Sq_pad + qi;
+    const float lse2 = p.lse[stat_idx];     // +inf for rows past Sq -> P = 0
+    const float delta = p.delta[stat_idx];
+    const float slope2 = p.alibi != nullptr ? p.alibi[head] * LOG2E : 0.f;
+    for (int i = 0; i < nblk; ++i) {
+      const int st = i & 1;
+      const int k0 = (jb + i) * AB;
+      if (!mbar_wait(bar(SDP_FULL, 0), i & 1, p.err, 38)) { aborted = true; break; }
+      if (i >= 2 && !mbar_wait(bar(DQ_DONE, st), ((i - 2) >> 1) & 1, p.err, 39)) { aborted = true; break; }
+      tc_fence_after_sync();
+      const bool need_mask = (k0 + AB > p.Sk) || (p.causal && k0 + AB - 1 > q0 + quad * 32 + off) ||
+                             (p.window >= 0 && k0 < q0 + quad * 32 + 31 + off - p.window);
+      const int rel0 = k0 - qpos;
+      int hi = p.Sk - k0 - 1;
+      if (p.causal) hi = min(hi, -rel0);
+      const int lo = p.window >= 0 ? -rel0 - p.window : -(1 << 30);
+      const float bias0 = slope2 * static_cast<float>(rel0) - lse2;  // folded into the exponent
+#pragma unroll 1
+      for (int c = 0; c < AB / 32; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(T_S + c * 32 + lane_off, sv);
+        tmem_ld_32x32b_x32(T_DP + c * 32 + lane_off, dv);
+        tmem_ld_wait();
+        uint32_t pk[16];
+        if (!need_mask && p.alibi == nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(sv[j]), p.scale_log2, -lse2)) * p.scale;
+            const float p1 = exp2f(fmaf(__uint_as_float(sv[j + 1]), p.scale_log2, -lse2)) * p.scale;
+            pk[j >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[j]) - delta),
+                                     p1 * (__uint_as_float(dv[j + 1]) - delta));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float ds[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int idx = c * 32 + j + e;
+              float x = fmaf(__uint_as_float(sv[j + e]), p.scale_log2,
+                             fmaf(slope2, static_cast<float>(idx), bias0));
+              float pr = exp2f(x) * p.scale;
+              if (idx < lo || idx > hi) pr = 0.f;
+              ds[e] = pr * (__uint_as_float(dv[j + e]) - delta);
+            }
+            pk[j >> 1] = pack_bf16x2(ds[0], ds[1]);
+          }
+        }
+        tmem_st_32x32b_x16(T_DS + st * 64 + c * 16 + lane_off, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(SDP_EMPTY, 0));
+        mbar_arrive(bar(DS_FULL, st));
+      }
+    }
+    if (!aborted && nblk > 0) {
+      if (!mbar_wait(bar(DQ_DONE, (nblk - 1) & 1), ((nblk - 1) >> 1) & 1, p.err, 40)) aborted = true;
+      tc_fence_after_sync();
+    }
+    if (!aborted) {
+      __nv_bfloat16* orow = p.dq + batch * p.dq_sb + head * p.dq_sh + static_cast<long long>(qi) * p.dq_ss;
+#pragma unroll 1
+      for (int c = 0; c < DP / 32; ++c) {
+        uint32_t ov[32];
+        if (nblk > 0) {  // warp-uniform: every lane takes part in the collective TMEM load
+          tmem_ld_32x32b_x32(T_DQ + c * 32 + lane_off, ov);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) ov[j] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (c * 32 + j < p.D) {
+              uint4 o4;
+              o4.x = pack_bf16x2(__uint_as_float(ov[j]), __uint_as_float(ov[j + 1]));
+              o4.y = pack_bf16x2(__uint_as_float(ov[j + 2]), __uint_as_float(ov[j + 3]));
+              o4.z = pack_bf16x2(__uint_as_float(ov[j + 4]), __uint_as_float(ov[j + 5]));
+              o4.w = pack_bf16x2(__uint_as_float(ov[j + 6]), __uint_as_float(ov[j + 7]));
+              *reinterpret_cast<uint4*>(orow + c * 32 + j) = o4;
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  if (aborted) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dK / dV kernel.  smem tiles: 0 = K, 1 = V, 2..3 = Q ring, 4..5 = dO ring.
+// TMEM: S^T [0,128) (P^T bf16 overwrites cols [0,64)), dP^T [128,256) (dS^T bf16 over [128,192)),
+//       dK [256,256+DP), dV [384,384+DP)
+// ------------------------------------------------------------------------------------------------
+template <int DP>
+__global__ void __launch_bounds__(AB_THREADS, 1)
+    attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                        const AttnBwdParams p) {
+  using L = BwdSmem<DP>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  const uint32_t bar0 = sbase + L::BAR_OFF;
+  enum { KV_FULL = 0, Q_FULL = 1, Q_EMPTY = 3, ST_FULL = 5, PT_FULL = 6, ACC_DONE = 7, NUSED = 8 };
+  auto bar = [&](int which, int idx) { return bar0 + 8u * (which + idx); };
+  const uint32_t tmem_slot = bar0 + 8u * 23;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(sgen + L::BAR_OFF + 8 * 23);
+  auto tile = [&](int i) { return sbase + i * L::TILE; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x;
+  const int kv_head = blockIdx.y, batch = blockIdx.z;
+  const int group = p.H / p.Hk;
+  const int k0 = kt * AB;
+  const int off = p.Sk - p.Sq;
+  // query rows that can see this key block: qpos >= k0 (causal), qpos <= k_last + window
+  int q_begin = 0, q_end = p.Sq;
+  if (p.causal) q_begin = max(0, k0 - off);
+  if (p.window >= 0) q_end = min(p.Sq, k0 + AB - 1 + p.window - off + 1);
+  const int ib = q_begin / AB;
+  const int nq = max((q_end + AB - 1) / AB - ib, 0);
+  const int nsteps = nq * group;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NUSED; ++i) mbar_init(bar0 + 8u * i, i == PT_FULL ? 4 : 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot_gen;
+  const uint32_t T_ST = tmem, T_DPT = tmem + 128, T_DK = tmem + 256, T_DV = tmem + 384;
+  bool aborted = false;
+
+  if (warp == 0) {
+    if (elect_one() && nsteps > 0) {
+      mbar_expect_tx(bar(KV_FULL, 0), 2 * L::TILE);
+      load_tile<DP>(tile(0), &tmK, bar(KV_FULL, 0), k0, kv_head, batch);
+      load_tile<DP>(tile(1), &tmV, bar(KV_FULL, 0), k0, kv_head, batch);
+      for (int t = 0; t < nsteps; ++t) {
+        const int st = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        const int head = kv_head * group + t / nq;
+        const int q0 = (ib + t % nq) * AB;
+        if (!mbar_wait(bar(Q_EMPTY, st), ph ^ 1, p.err, 51)) { aborted = true; break; }
+        mbar_expect_tx(bar(Q_FULL, st), 2 * L::TILE + 2 * AB * 4);
+        load_tile<DP>(tile(2 + st), &tmQ, bar(Q_FULL, st), q0, head, batch);
+        load_tile<DP>(tile(4 + st), &tmDO, bar(Q_FULL, st), q0, head, batch);
+        const long long stat0 = (static_cast<long long>(batch) * p.H + head) * p.Sq_pad + q0;
+        bulk_load_1d(sbase + L::VEC_OFF + st * (2 * AB * 4), p.lse + stat0, AB * 4, bar(Q_FULL, st));
+        bulk_load_1d(sbase + L::VEC_OFF + st * (2 * AB * 4) + AB * 4, p.delta + stat0, AB * 4,
+                     bar(Q_FULL, st));
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one() && nsteps > 0) {
+      if (!mbar_wait(bar(KV_FULL, 0), 0, p.err, 52)) aborted = true;
+      for (int t = 0; t < nsteps && !aborted; ++t) {
+        const int st = t & 1;
+        if (!mbar_wait(bar(Q_FULL, st), (t >> 1) & 1, p.err, 53)) { aborted = true; break; }
+        tc_fence_after_sync();
+        mma_nt<DP>(T_ST, tile(0), tile(2 + st));   // S^T  = K Q^T
+        mma_nt<DP>(T_DPT, tile(1), tile(4 + st));  // dP^T = V dO^T
+        umma_commit(bar(ST_FULL, 0));
+        if (!mbar_wait(bar(PT_FULL, 0), t & 1, p.err, 54)) { aborted = true; break; }
+        tc_fence_after_sync();
+        mma_ts<DP>(T_DV, T_ST, tile(4 + st), t != 0);   // dV += P^T dO
+        mma_ts<DP>(T_DK, T_DPT, tile(2 + st), t != 0);  // dK += dS^T Q
+        umma_commit(bar(Q_EMPTY, st));
+      }
+      if (!aborted) umma_commit(bar(ACC_DONE, 0));
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;  // key row in tile
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const int kcol = k0 + r;
+    const bool key_ok = kcol < p.Sk;
+    for (int t = 0; t < nsteps; ++t) {
+      const int head = kv_head * group + t / nq;
+      const int q0 = (ib + t % nq) * AB;
+      const float slope2 = p.alibi != nullptr ? p.alibi[head] * LOG2E : 0.f;
+      const int st = t & 1;
+      // lse / delta of this query block were bulk-copied next to the Q / dO tiles
+      if (!mbar_wait(bar(Q_FULL, st), (t >> 1) & 1, p.err, 57)) { aborted = true; break; }
+      const float4* v_lse = reinterpret_cast<const float4*>(sgen + L::VEC_OFF + st * (2 * AB * 4));
+      const float4* v_del = v_lse + AB / 4;
+      if (!mbar_wait(bar(ST_FULL, 0), t & 1, p.err, 55)) { aborted = true; break; }
+      tc_fence_after_sync();
+      // query columns qq (0..127) of this block are alive for lo <= qq <= hi
+      const int rel0 = kcol - q0 - off;  // key position minus position of query column 0
+      int lo = p.causal ? rel0 : -(1 << 30);
+      int hi = p.window >= 0 ? rel0 + p.window : (1 << 30);
+      if (!key_ok) hi = -(1 << 30);
+      const bool need_mask = __any_sync(0xffffffffu, lo > 0 || hi < AB - 1);
+      const float bias0 = slope2 * static_cast<float>(rel0);
+#pragma unroll 1
+      for (int c = 0; c < AB / 32; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(T_ST + c * 32 + lane_off, sv);
+        tmem_ld_32x32b_x32(T_DPT + c * 32 + lane_off, dv);
+        tmem_ld_wait();
+        uint32_t pp[16], pd[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 l4 = v_lse[(c * 32 + j) >> 2];
+          const float4 d4 = v_del[(c * 32 + j) >> 2];
+          const float lq[4] = {l4.x, l4.y, l4.z, l4.w}, dq_[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pr[4], ds[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int idx = c * 32 + j + e;
+            float x = fmaf(__uint_as_float(sv[j + e]), p.scale_log2, -lq[e]);
+            if (p.alibi != nullptr) x += fmaf(-slope2, static_cast<float>(idx), bias0);
+            pr[e] = exp2f(x);
+            if (need_mask && (idx < lo || idx > hi)) pr[e] = 0.f;
+            ds[e] = pr[e] * p.scale * (__uint_as_float(dv[j + e]) - dq_[e]);
+          }
+          pp[j >> 1] = pack_bf16x2(pr[0], pr[1]);
+          pp[(j >> 1) + 1] = pack_bf16x2(pr[2], pr[3]);
+          pd[j >> 1] = pack_bf16x2(ds[0], ds[1]);
+          pd[(j >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
+        }
+        tmem_st_32x32b_x16(T_ST + c * 16 + lane_off, pp);
+        tmem_st_32x32b_x16(T_DPT + c * 16 + lane_off, pd);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(PT_FULL, 0));
+    }
+    if (!aborted && nsteps > 0) {
+      if (!mbar_wait(bar(ACC_DONE, 0), 0, p.err, 56)) aborted = true;
+      tc_fence_after_sync();
+    }
+    if (!aborted) {
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t T = which == 0 ? T_DK : T_DV;
+        __nv_bfloat16* base = which == 0 ? p.dk : p.dv;
+        const long long sb = which == 0 ? p.dk_sb : p.dv_sb, sh = which == 0 ? p.dk_sh : p.dv_sh,
+                        ss = which == 0 ? p.dk_ss : p.dv_ss;
+        __nv_bfloat16* orow = base + batch * sb + kv_head * sh + static_cast<long long>(kcol) * ss;
+#pragma unroll 1
+        for (int c = 0; c < DP / 32; ++c) {
+          uint32_t ov[32];
+          if (nsteps > 0) {
+            tmem_ld_32x32b_x32(T + c * 32 + lane_off, ov);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ov[j] = 0u;
+          }
+          if (key_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (c * 32 + j < p.D) {
+                uint4 o4;
+                o4.x = pack_bf16x2(__uint_as_float(ov[j]), __uint_as_float(ov[j + 1]));
+                o4.y = pack_bf16x2(__uint_as_float(ov[j + 2]), __uint_as_float(ov[j + 3]));
+                o4.z = pack_bf16x2(__uint_as_float(ov[j + 4]), __uint_as_float(ov[j + 5]));
+                o4.w = pack_bf16x2(__uint_as_float(ov[j + 6]), __uint_as_float(ov[j + 7]));
+                *reinterpret_cast<uint4*>(orow + c * 32 + j) = o4;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  if (aborted) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+static bool bwd_map(CUtensorMap* m, const void* base, int B, int Hh, int S, int D, long long sb,
+                    long long sh, long long ss) {
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)S, (uint64_t)Hh, (uint64_t)B};
+  const uint64_t strides[3] = {(uint64_t)ss * 2, (uint64_t)sh * 2, (uint64_t)sb * 2};
+  const uint32_t box[4] = {64, AB, 1, 1};
+  return make_tma_4d(m, base, dims, strides, box, 2, true);
+}
+
+template <int DP>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                      const CUtensorMap& tdo, const AttnBwdParams& p, cudaStream_t s) {
+  static bool cfg = false;
+  if (!cfg) {
+    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       BwdSmem<DP>::DYN));
+    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       BwdSmem<DP>::DYN));
+    cfg = true;
+  }
+  dim3 gq((p.Sq + AB - 1) / AB, p.H, p.B);
+  attn_bwd_dq_kernel<DP><<<gq, AB_THREADS, BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
+  NX_LAUNCH_CHECK();
+  dim3 gk((p.Sk + AB - 1) / AB, p.Hk, p.B);
+  attn_bwd_dkv_kernel<DP><<<gk, AB_THREADS, BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+
+}  // namespace nx
+
+// Views as in nx_flash_attn_fwd (element strides batch, head, seq).  delta: fp32 scratch [B,H,Sq]
+// provided by the caller.  dq/dk/dv: bf16 strided outputs, fully overwritten.
+NX_API int nx_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO,
+                             const void* lse, void* delta, void* dq, void* dk, void* dv,
+                             const void* alibi, int B, int H, int Hk, int Sq, int Sk, int D,
+                             long long q_sb, long long q_sh, long long q_ss, long long k_sb,
+                             long long k_sh, long long k_ss, long long v_sb, long long v_sh,
+                             long long v_ss, long long o_sb, long long o_sh, long long o_ss,
+                             long long do_sb, long long do_sh, long long do_ss, long long dq_sb,
+                             long long dq_sh, long long dq_ss, long long dk_sb, long long dk_sh,
+                             long long dk_ss, long long dv_sb, long long dv_sh, long long dv_ss,
+                             float scale, int causal, int window, void* stream_) {
+  using namespace nx;
+  if (B == 0 || H == 0 || Sq == 0 || Sk == 0) return NX_OK;
+  NX_REQUIRE(D % 8 == 0 && D <= 128 && D > 0, "flash_attn_bwd: head dim %d unsupported", D);
+  NX_REQUIRE(Hk > 0 && H % Hk == 0, "flash_attn_bwd: H=%d not a multiple of Hk=%d", H, Hk);
+  auto aligned = [](const void* ptr, long long a, long long b, long long c) {
+    return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && a % 8 == 0 && b % 8 == 0 && c % 8 == 0;
+  };
+  NX_REQUIRE(aligned(dq, dq_sb, dq_sh, dq_ss) && aligned(dk, dk_sb, dk_sh, dk_ss) &&
+                 aligned(dv, dv_sb, dv_sh, dv_ss),
+             "flash_attn_bwd: gradient views must be 16-byte aligned");
+  auto s = (cudaStream_t)stream_;
+  {
+    const long long rows = static_cast<long long>(B) * H * Sq;
+    const int wpb = 8;
+    attn_delta_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, s>>>(
+        (const __nv_bfloat16*)o, (const __nv_bfloat16*)dO, (float*)delta, B, H, Sq, (Sq + AB - 1) / AB * AB, D, o_sb, o_sh, o_ss,
+        do_sb, do_sh, do_ss);
+    NX_LAUNCH_CHECK();
+  }
+  CUtensorMap tq, tk, tv, tdo;
+  if (!bwd_map(&tq, q, B, H, Sq, D, q_sb, q_sh, q_ss)) return NX_ERR_ARG;
+  if (!bwd_map(&tk, k, B, Hk, Sk, D, k_sb, k_sh, k_ss)) return NX_ERR_ARG;
+  if (!bwd_map(&tv, v, B, Hk, Sk, D, v_sb, v_sh, v_ss)) return NX_ERR_ARG;
+  if (!bwd_map(&tdo, dO, B, H, Sq, D, do_sb, do_sh, do_ss)) return NX_ERR_ARG;
+  AttnBwdParams p;
+  p.lse = (const float*)lse; p.delta = (const float*)delta; p.alibi = (const float*)alibi;
+  p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.dq_sb = dq_sb; p.dq_sh = dq_sh; p.dq_ss = dq_ss;
+  p.dk_sb = dk_sb; p.dk_sh = dk_sh; p.dk_ss = dk_ss;
+  p.dv_sb = dv_sb; p.dv_sh = dv_sh; p.dv_ss = dv_ss;
+  p.B = B; p.H = H; p.Hk = Hk; p.Sq = Sq; p.Sk = Sk; p.D = D;
+  p.Sq_pad = (Sq + AB - 1) / AB * AB;
+  p.scale = scale; p.scale_log2 = scale * LOG2E;
+  p.causal = causal; p.window = window;
+  p.err = device_error_word();
+  if (D <= 64) return launch_bwd<64>(tq, tk, tv, tdo, p, s);
+  return launch_bwd<128>(tq, tk, tv, tdo, p, s);
+}

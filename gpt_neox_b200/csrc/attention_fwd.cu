@@ -1,0 +1,424 @@
+// Flash attention forward on tcgen05: causal / sliding-window / ALiBi / GQA, bf16 in, bf16 out,
+// fp32 log-sum-exp saved for the backward.
+//
+// Replaces the flash-attn 2 calls of the reference (megatron/model/transformer.py:573-690;
+// flash_attn_func with causal=True, window_size, alibi_slopes) and, for the "global" path, the
+// baddbmm -> fused softmax -> bmm chain (megatron/model/transformer.py:473-571).
+//
+// One CTA per (128 query rows, head, batch); 192 threads:
+//   warp 0      TMA producer: Q once, then K_j / V_j blocks of 128 keys through a 2-deep ring
+//   warp 1      tcgen05.mma issuer:  S_j = Q K_j^T  (two S buffers in TMEM, so S_{j+1} is computed
+//               while the softmax warps work on S_j),  O += P_j V_j  with P_j read from TMEM
+//   warps 2..5  softmax: thread t owns query row t; reads S from TMEM, applies scale / masks /
+//               ALiBi, online max and sum in base 2, writes P (bf16) back to TMEM, rescales the O
+//               accumulator only when the running max moved by more than 2^8 (lazy rescale),
+//               and finally normalises and stores O.
+// TMEM columns: S0 [0,128) S1 [128,256) O [256,256+DP) P0 [384,448) P1 [448,512).
+// Head dims up to 128 are zero-padded to DP in {64,128} by TMA out-of-bounds fill.
+#include "common.h"
+#include "ptx.cuh"
+
+namespace nx {
+
+constexpr int ATT_BM = 128;  // query rows per CTA
+constexpr int ATT_BN = 128;  // keys per block
+constexpr int ATT_THREADS = 192;
+
+struct AttnFwdParams {
+  __nv_bfloat16* o;
+  float* lse;
+  const float* alibi;  // per query head, or null
+  int B, H, Hk, Sq, Sk, D, Sq_pad;
+  long long o_sb, o_sh, o_ss;
+  float scale_log2;  // softmax scale * log2(e)
+  int causal;
+  int window;  // < 0: unlimited look-back
+  int* err;
+};
+
+template <int DP>
+struct AttnSmem {
+  static constexpr int TILE = ATT_BN * DP * 2;  // one Q / K / V tile
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = TILE;
+  static constexpr int V_OFF = 3 * TILE;
+  static constexpr int BAR_OFF = 5 * TILE;
+  // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2],
+  // pv_done[2]  = 17 barriers, then the TMEM base word in slot 17
+  static constexpr int NBAR = 18;
+  static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
+  static constexpr int DYN = TOTAL + 1024;
+};
+
+// Row maximum of raw scores (no mask, no ALiBi), four independent chains for ILP.
+__device__ __forceinline__ float row_max_plain(const uint32_t (&sv)[4][32]) {
+  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      m0 = fmaxf(m0, __uint_as_float(sv[c][j]));
+      m1 = fmaxf(m1, __uint_as_float(sv[c][j + 1]));
+      m2 = fmaxf(m2, __uint_as_float(sv[c][j + 2]));
+      m3 = fmaxf(m3, __uint_as_float(sv[c][j + 3]));
+    }
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+// Rewrites raw scores in place as base-2 logits: x = s * scale_log2 (+ slope2 * (col - qpos)),
+// -inf outside the live column range [lo, hi] of this block; returns the row maximum.
+// rel0 = (first column of the block) - (query position).
+template <bool ALIBI>
+__device__ __forceinline__ float prep_scores(uint32_t (&sv)[4][32], float scale_log2, float slope2,
+                                             int rel0, int lo, int hi) {
+  float m0 = -INFINITY, m1 = -INFINITY;
+  const float bias0 = ALIBI ? slope2 * static_cast<float>(rel0) : 0.f;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int idx = c * 32 + j;
+      float x = __uint_as_float(sv[c][j]) * scale_log2;
+      if (ALIBI) x += fmaf(slope2, static_cast<float>(idx), bias0);
+      if (idx < lo || idx > hi) x = -INFINITY;
+      sv[c][j] = __float_as_uint(x);
+      if (j & 1) m1 = fmaxf(m1, x); else m0 = fmaxf(m0, x);
+    }
+  }
+  return fmaxf(m0, m1);
+}
+
+template <int DP>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+    attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
+  using L = AttnSmem<DP>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  const uint32_t bar0 = sbase + L::BAR_OFF;
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11,
+         P_FULL = 13, PV_DONE = 15 };
+  auto bar = [&](int which, int idx) { return bar0 + 8u * (which + idx); };
+  const uint32_t tmem_slot = bar0 + 8u * 17;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(sgen + L::BAR_OFF + 8 * 17);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) query tiles first
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int kv_head = head / (p.H / p.Hk);
+  const int q0 = qt * ATT_BM;
+  const int off = p.Sk - p.Sq;  // query i sits at absolute position i + off
+
+  // key range this query tile can see
+  int kv_end = p.Sk;
+  if (p.causal) kv_end = min(p.Sk, q0 + ATT_BM + off);
+  int kv_begin = 0;
+  if (p.window >= 0) kv_begin = max(0, q0 + off - p.window);
+  const int jb = kv_begin / ATT_BN;
+  const int je = (kv_end + ATT_BN - 1) / ATT_BN;  // exclusive
+  const int nblk = max(je - jb, 0);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 17; ++i) {
+      const bool softmax_arrives = (i >= S_EMPTY && i < S_EMPTY + 2) || (i >= P_FULL && i < P_FULL + 2);
+      mbar_init(bar0 + 8u * i, softmax_arrives ? 4 : 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot_gen;
+  const uint32_t T_S = tmem, T_O = tmem + 256, T_P = tmem + 384;
+  bool aborted = false;
+
+  if (warp == 0) {
+    if (elect_one() && nblk > 0) {
+      // ---------------------------------------------------------------- producer
+      mbar_expect_tx(bar(Q_FULL, 0), L::TILE);
+#pragma unroll
+      for (int c = 0; c < DP / 64; ++c)
+        tma_load_4d(sbase + L::Q_OFF + c * (ATT_BM * 128), &tmQ, bar(Q_FULL, 0), c * 64, q0, head, batch);
+      for (int i = 0; i < nblk; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        const int k0 = (jb + i) * ATT_BN;
+        if (!mbar_wait(bar(K_EMPTY, st), ph ^ 1, p.err, 11)) { aborted = true; break; }
+        mbar_expect_tx(bar(K_FULL, st), L::TILE);
+#pragma unroll
+        for (int c = 0; c < DP / 64; ++c)
+          tma_load_4d(sbase + L::K_OFF + st * L::TILE + c * (ATT_BN * 128), &tmK, bar(K_FULL, st),
+                      c * 64, k0, kv_head, batch);
+        if (!mbar_wait(bar(V_EMPTY, st), ph ^ 1, p.err, 12)) { aborted = true; break; }
+        mbar_expect_tx(bar(V_FULL, st), L::TILE);
+#pragma unroll
+        for (int c = 0; c < DP / 64; ++c)
+          tma_load_4d(sbase + L::V_OFF + st * L::TILE + c * (ATT_BN * 128), &tmV, bar(V_FULL, st),
+                      c * 64, k0, kv_head, batch);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one() && nblk > 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc_s = umma_idesc_bf16(ATT_BM, ATT_BN, 0, 0);
+      constexpr uint32_t idesc_o = umma_idesc_bf16(ATT_BM, DP, 0, 1);
+      auto issue_pv = [&](int i) -> bool {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        if (!mbar_wait(bar(P_FULL, st), ph, p.err, 13)) return false;
+        if (!mbar_wait(bar(V_FULL, st), ph, p.err, 14)) return false;
+        tc_fence_after_sync();
+        const uint32_t vb = sbase + L::V_OFF + st * L::TILE;
+#pragma unroll
+        for (int k = 0; k < ATT_BN / 16; ++k) {
+          // V tile is [128 keys][DP] with the head dim contiguous: MN-major B operand.
+          const uint64_t bdesc = umma_smem_desc_sw128(vb + k * 2048, ATT_BN * 128, 1024);
+          umma_bf16_ts(T_O, T_P + st * 64 + k * 8, bdesc, idesc_o, (i | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(bar(PV_DONE, st));
+        umma_commit(bar(V_EMPTY, st));
+        return true;
+      };
+      if (!mbar_wait(bar(Q_FULL, 0), 0, p.err, 15)) aborted = true;
+      for (int i = 0; i < nblk && !aborted; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        if (!mbar_wait(bar(K_FULL, st), ph, p.err, 16)) { aborted = true; break; }
+        if (!mbar_wait(bar(S_EMPTY, st), ph ^ 1, p.err, 17)) { aborted = true; break; }
+        tc_fence_after_sync();
+        const uint32_t qb = sbase + L::Q_OFF, kb = sbase + L::K_OFF + st * L::TILE;
+#pragma unroll
+        for (int k = 0; k < DP / 16; ++k) {
+          const uint32_t o = (k >> 2) * (ATT_BM * 128) + (k & 3) * 32;
+          umma_bf16_ss(T_S + st * 128, umma_smem_desc_sw128(qb + o, 0, 1024),
+                       umma_smem_desc_sw128(kb + o, 0, 1024), idesc_s, k != 0 ? 1u : 0u);
+        }
+        umma_commit(bar(S_FULL, st));
+        umma_commit(bar(K_EMPTY, st));
+        if (i > 0 && !issue_pv(i - 1)) { aborted = true; break; }
+      }
+      if (!aborted && !issue_pv(nblk - 1)) aborted = true;
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / epilogue
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;  // row in tile == TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const int qi = q0 + r;
+    const int qpos = qi + off;
+    float m_used = -INFINITY, l = 0.f;
+    const float slope2 = p.alibi != nullptr ? p.alibi[head] * 1.4426950408889634f : 0.f;
+    for (int i = 0; i < nblk; ++i) {
+      const int st = i & 1;
+      const uint32_t ph = (i >> 1) & 1;
+      const int k0 = (jb + i) * ATT_BN;
+      if (!mbar_wait(bar(S_FULL, st), ph, p.err, 18)) { aborted = true; break; }
+      tc_fence_after_sync();
+      // One read of the whole score row into registers.
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(T_S + st * 128 + c * 32 + lane_off, sv[c]);
+      tmem_ld_wait();
+      // Does this block need per-element masking?  (warp-uniform decision)
+      const bool need_mask = (k0 + ATT_BN > p.Sk) || (p.causal && k0 + ATT_BN - 1 > q0 + quad * 32 + off) ||
+                             (p.window >= 0 && k0 < q0 + quad * 32 + 31 + off - p.window);
+      const bool plain = !need_mask && p.alibi == nullptr;
+      float mx;
+      if (plain) {
+        mx = row_max_plain(sv) * p.scale_log2;
+      } else {
+        // columns idx (0..127) of this block are alive for lo <= idx <= hi
+        const int rel0 = k0 - qpos;
+        int hi = p.Sk - k0 - 1;
+        if (p.causal) hi = min(hi, -rel0);
+        const int lo = p.window >= 0 ? -rel0 - p.window : -(1 << 30);
+        mx = p.alibi != nullptr ? prep_scores<true>(sv, p.scale_log2, slope2, rel0, lo, hi)
+                                : prep_scores<false>(sv, p.scale_log2, slope2, rel0, lo, hi);
+      }
+      float alpha = 1.f;
+      bool rescale = false;
+      if (mx > m_used + 8.f || m_used == -INFINITY) {
+        const float m_new = fmaxf(m_used, mx);
+        if (m_used != -INFINITY) {
+          alpha = exp2f(m_used - m_new);
+          rescale = true;
+        }
+        m_used = m_new;
+        l *= alpha;
+      }
+      if (i > 0 && __any_sync(0xffffffffu, rescale)) {
+        // O must be complete up to block i-1 before it is rescaled.
+        if (!mbar_wait(bar(PV_DONE, (i - 1) & 1), ((i - 1) >> 1) & 1, p.err, 19)) { aborted = true; break; }
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < DP / 32; ++c) {
+          uint32_t ov[32];
+          tmem_ld_32x32b_x32(T_O + c * 32 + lane_off, ov);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha);
+          tmem_st_32x32b_x32(T_O + c * 32 + lane_off, ov);
+        }
+        tmem_st_wait();
+      }
+      // P buffer `st` was last read by PV_{i-2}.
+      if (i >= 2) {
+        if (!mbar_wait(bar(PV_DONE, st), ((i - 2) >> 1) & 1, p.err, 20)) { aborted = true; break; }
+      }
+      // probabilities (base 2), packed to bf16 and written to TMEM as the A operand of P V
+      const float msub = m_used == -INFINITY ? 0.f : m_used;
+      float rs[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float p0, p1;
+          if (plain) {
+            p0 = exp2f(fmaf(__uint_as_float(sv[c][j]), p.scale_log2, -msub));
+            p1 = exp2f(fmaf(__uint_as_float(sv[c][j + 1]), p.scale_log2, -msub));
+          } else {
+            p0 = exp2f(__uint_as_float(sv[c][j]) - msub);
+            p1 = exp2f(__uint_as_float(sv[c][j + 1]) - msub);
+          }
+          rs[(j >> 1) & 3] += p0 + p1;
+          pk[j >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x32b_x16(T_P + st * 64 + c * 16 + lane_off, pk);
+      }
+      const float rowsum = (rs[0] + rs[1]) + (rs[2] + rs[3]);
+      l += rowsum;
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(S_EMPTY, st));
+        mbar_arrive(bar(P_FULL, st));
+      }
+    }
+    // ---- epilogue: O / l -> global, lse
+    if (!aborted && nblk > 0) {
+      if (!mbar_wait(bar(PV_DONE, (nblk - 1) & 1), ((nblk - 1) >> 1) & 1, p.err, 21)) aborted = true;
+      tc_fence_after_sync();
+    }
+    if (!aborted) {
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      const bool row_ok = qi < p.Sq;
+      __nv_bfloat16* orow = p.o + batch * p.o_sb + head * p.o_sh + static_cast<long long>(qi) * p.o_ss;
+#pragma unroll 1
+      for (int c = 0; c < DP / 32; ++c) {
+        uint32_t ov[32];
+        if (nblk > 0) {
+          tmem_ld_32x32b_x32(T_O + c * 32 + lane_off, ov);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) ov[j] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (c * 32 + j < p.D) {
+              uint4 o4;
+              o4.x = pack_bf16x2(__uint_as_float(ov[j]) * inv_l, __uint_as_float(ov[j + 1]) * inv_l);
+              o4.y = pack_bf16x2(__uint_as_float(ov[j + 2]) * inv_l, __uint_as_float(ov[j + 3]) * inv_l);
+              o4.z = pack_bf16x2(__uint_as_float(ov[j + 4]) * inv_l, __uint_as_float(ov[j + 5]) * inv_l);
+              o4.w = pack_bf16x2(__uint_as_float(ov[j + 6]) * inv_l, __uint_as_float(ov[j + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + c * 32 + j) = o4;
+            }
+          }
+        }
+      }
+      if (row_ok) {
+        // base-2 log-sum-exp of the scaled scores; rows are padded to a multiple of 128
+        const float lse2 = l > 0.f ? m_used + log2f(l) : -INFINITY;
+        p.lse[(static_cast<long long>(batch) * p.H + head) * p.Sq_pad + qi] = lse2;
+      }
+    }
+  }
+
+  __syncwarp();
+  if (aborted) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// Builds the 4-D (d, s, head, batch) tensor map of a [B, heads, S, D] view given element strides.
+static bool attn_map(CUtensorMap* m, const void* base, int B, int Hh, int S, int D, long long sb,
+                     long long sh, long long ss, int box_rows) {
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)S, (uint64_t)Hh, (uint64_t)B};
+  const uint64_t strides[3] = {(uint64_t)ss * 2, (uint64_t)sh * 2, (uint64_t)sb * 2};
+  const uint32_t box[4] = {64, (uint32_t)box_rows, 1, 1};
+  return make_tma_4d(m, base, dims, strides, box, 2, true);
+}
+
+}  // namespace nx
+
+// q [B,H,Sq,D], k/v [B,Hk,Sk,D], o [B,H,Sq,D] as strided views (element strides for batch, head,
+// sequence; head dim contiguous); lse: fp32 [B,H,Sq_pad] (Sq rounded up to 128), receives the
+// base-2 log-sum-exp of the scaled scores for rows < Sq (the caller pre-fills it with +inf).  alibi: fp32 [H] or null.
+// window < 0: no sliding window.  D % 8 == 0, D <= 128.
+NX_API int nx_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, void* lse,
+                             const void* alibi, int B, int H, int Hk, int Sq, int Sk, int D,
+                             long long q_sb, long long q_sh, long long q_ss, long long k_sb,
+                             long long k_sh, long long k_ss, long long v_sb, long long v_sh,
+                             long long v_ss, long long o_sb, long long o_sh, long long o_ss,
+                             float scale, int causal, int window, void* stream_) {
+  using namespace nx;
+  if (B == 0 || H == 0 || Sq == 0) return NX_OK;
+  NX_REQUIRE(D % 8 == 0 && D <= 128 && D > 0, "flash_attn: head dim %d unsupported (need %%8, <=128)", D);
+  NX_REQUIRE(Hk > 0 && H % Hk == 0, "flash_attn: H=%d not a multiple of Hk=%d", H, Hk);
+  NX_REQUIRE(Sk >= 1, "flash_attn: empty key sequence");
+  NX_REQUIRE((o_ss % 8) == 0 && (o_sh % 8) == 0 && (o_sb % 8) == 0 &&
+                 (reinterpret_cast<uintptr_t>(o) & 15) == 0,
+             "flash_attn: output view must be 16-byte aligned");
+  CUtensorMap tq, tk, tv;
+  if (!attn_map(&tq, q, B, H, Sq, D, q_sb, q_sh, q_ss, ATT_BM)) return NX_ERR_ARG;
+  if (!attn_map(&tk, k, B, Hk, Sk, D, k_sb, k_sh, k_ss, ATT_BN)) return NX_ERR_ARG;
+  if (!attn_map(&tv, v, B, Hk, Sk, D, v_sb, v_sh, v_ss, ATT_BN)) return NX_ERR_ARG;
+  AttnFwdParams p;
+  p.o = (__nv_bfloat16*)o; p.lse = (float*)lse; p.alibi = (const float*)alibi;
+  p.B = B; p.H = H; p.Hk = Hk; p.Sq = Sq; p.Sk = Sk; p.D = D;
+  p.Sq_pad = (Sq + ATT_BM - 1) / ATT_BM * ATT_BM;
+  p.o_sb = o_sb; p.o_sh = o_sh; p.o_ss = o_ss;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal; p.window = window;
+  p.err = device_error_word();
+  dim3 grid((Sq + ATT_BM - 1) / ATT_BM, H, B);
+  auto s = (cudaStream_t)stream_;
+  if (D <= 64) {
+    static bool cfg = false;
+    if (!cfg) {
+      NX_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         AttnSmem<64>::DYN));
+      cfg = true;
+    }
+    attn_fwd_kernel<64><<<grid, ATT_THREADS, AttnSmem<64>::DYN, s>>>(tq, tk, tv, p);
+  } else {
+    static bool cfg = false;
+    if (!cfg) {
+      NX_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         AttnSmem<128>::DYN));
+      cfg = true;
+    }
+    attn_fwd_kernel<128><<<grid, ATT_THREADS, AttnSmem<128>::DYN, s>>>(tq, tk, tv, p);
+  }
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}

@@ -131,6 +131,38 @@ bool make_tma_3d(CUtensorMap* map, const void* base, uint64_t d2, uint64_t d1, u
   return true;
 }
 
+bool make_tma_4d(CUtensorMap* map, const void* base, const uint64_t dims[4],
+                 const uint64_t strides_bytes[3], const uint32_t box[4], int elem_bytes,
+                 bool swizzle128) {
+  auto fn = get_encode_fn();
+  if (fn == nullptr) {
+    set_last_error("cuTensorMapEncodeTiled entry point not available");
+    return false;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (strides_bytes[0] & 15) != 0 ||
+      (strides_bytes[1] & 15) != 0 || (strides_bytes[2] & 15) != 0) {
+    set_last_error("TMA operand needs 16-byte aligned base and strides (base=%p strides=%llu,%llu,%llu)",
+                   base, (unsigned long long)strides_bytes[0], (unsigned long long)strides_bytes[1],
+                   (unsigned long long)strides_bytes[2]);
+    return false;
+  }
+  cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t gstride[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
+  cuuint32_t estride[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, dtype_of(elem_bytes), 4, const_cast<void*>(base), gdim, gstride, b, estride,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled(4d) failed (%d): dims=%llu,%llu,%llu,%llu", (int)r,
+                   (unsigned long long)dims[0], (unsigned long long)dims[1],
+                   (unsigned long long)dims[2], (unsigned long long)dims[3]);
+    return false;
+  }
+  return true;
+}
+
 }  // namespace nx
 
 NX_API const char* nx_last_error() { return nx::g_last_error; }

@@ -34,6 +34,11 @@ bool make_tma_3d(CUtensorMap* map, const void* base, uint64_t d2, uint64_t d1, u
                  uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box2, uint32_t box1,
                  uint32_t box0, int elem_bytes, bool swizzle128 = true);
 
+// 4-D variant: dims / box given innermost first; strides (bytes) for dims 1..3.
+bool make_tma_4d(CUtensorMap* map, const void* base, const uint64_t dims[4],
+                 const uint64_t strides_bytes[3], const uint32_t box[4], int elem_bytes,
+                 bool swizzle128 = true);
+
 }  // namespace nx
 
 #define NX_CUDA_CHECK(expr)                                                              \

@@ -1,0 +1,178 @@
+// Fused optimizer kernels over flat (ZeRO-partitioned) buffers.
+//
+// Counterpart of apex / DeepSpeed FusedAdam (megatron/training.py:1069-1083) and of the
+// DeepSpeed engine's clip / unscale / overflow logic the reference delegates to
+// (megatron/training.py:1357,1380).  One launch updates a whole flat shard:
+// fp32 master weights + Adam moments, gradient read as bf16 or fp32, multiplied by a scale that
+// lives in device memory (loss-scale reciprocal x clip coefficient, so no host sync is needed
+// between the norm reduction and the update), new bf16 model weights written in the same pass.
+// If the device-side "skip" word is non-zero (non-finite gradients) nothing is modified.
+#include "common.h"
+#include "ptx.cuh"
+#include "reduce.cuh"
+
+namespace nx {
+
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2;
+  int adam_w_mode;  // 1 = decoupled weight decay (AdamW), 0 = L2 added to the gradient
+};
+
+template <typename G>
+__device__ __forceinline__ float4 load_grad4(const G* g, long long i);
+template <>
+__device__ __forceinline__ float4 load_grad4<float>(const float* g, long long i) {
+  return *reinterpret_cast<const float4*>(g + i);
+}
+template <>
+__device__ __forceinline__ float4 load_grad4<__nv_bfloat16>(const __nv_bfloat16* g, long long i) {
+  const uint2 u = *reinterpret_cast<const uint2*>(g + i);
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename G>
+__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                             const G* __restrict__ g, __nv_bfloat16* __restrict__ p_bf16,
+                             long long n, AdamArgs a, const float* __restrict__ grad_scale,
+                             const int* __restrict__ skip) {
+  if (skip != nullptr && *skip != 0) return;
+  const float gs = grad_scale != nullptr ? *grad_scale : 1.f;
+  const float step = a.lr / a.bias_corr1;
+  const float inv_bc2_sqrt = rsqrtf(a.bias_corr2);
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < n;
+       i += (long long)gridDim.x * blockDim.x * 4) {
+    if (i + 4 <= n) {
+      float4 pv = *reinterpret_cast<float4*>(p + i);
+      float4 mv = *reinterpret_cast<float4*>(m + i);
+      float4 vv = *reinterpret_cast<float4*>(v + i);
+      const float4 gv = load_grad4<G>(g, i);
+      float pp[4] = {pv.x, pv.y, pv.z, pv.w}, mm[4] = {mv.x, mv.y, mv.z, mv.w},
+            vvv[4] = {vv.x, vv.y, vv.z, vv.w}, gg[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float gr = gg[j] * gs;
+        if (!a.adam_w_mode) gr += a.weight_decay * pp[j];
+        mm[j] = a.beta1 * mm[j] + (1.f - a.beta1) * gr;
+        vvv[j] = a.beta2 * vvv[j] + (1.f - a.beta2) * gr * gr;
+        const float denom = sqrtf(vvv[j]) * inv_bc2_sqrt + a.eps;
+        float upd = mm[j] / denom;
+        if (a.adam_w_mode) pp[j] -= a.lr * a.weight_decay * pp[j];
+        pp[j] -= step * upd;
+      }
+      *reinterpret_cast<float4*>(p + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+      *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+      *reinterpret_cast<float4*>(v + i) = make_float4(vvv[0], vvv[1], vvv[2], vvv[3]);
+      if (p_bf16 != nullptr) {
+        uint2 o;
+        o.x = pack_bf16x2(pp[0], pp[1]);
+        o.y = pack_bf16x2(pp[2], pp[3]);
+        *reinterpret_cast<uint2*>(p_bf16 + i) = o;
+      }
+    } else {
+      for (long long j = i; j < n; ++j) {
+        float gr;
+        if (sizeof(G) == 2) gr = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g)[j]);
+        else gr = reinterpret_cast<const float*>(g)[j];
+        gr *= gs;
+        float pj = p[j];
+        if (!a.adam_w_mode) gr += a.weight_decay * pj;
+        const float mj = a.beta1 * m[j] + (1.f - a.beta1) * gr;
+        const float vj = a.beta2 * v[j] + (1.f - a.beta2) * gr * gr;
+        const float denom = sqrtf(vj) * inv_bc2_sqrt + a.eps;
+        if (a.adam_w_mode) pj -= a.lr * a.weight_decay * pj;
+        pj -= step * (mj / denom);
+        p[j] = pj; m[j] = mj; v[j] = vj;
+        if (p_bf16 != nullptr) p_bf16[j] = __float2bfloat16(pj);
+      }
+    }
+  }
+}
+
+// acc[0] += sum(x^2) ; acc[1] = max(acc[1], any non-finite ? 1 : 0)   (acc: float[2])
+template <typename G>
+__global__ void sumsq_kernel(const G* __restrict__ x, long long n, float* __restrict__ acc) {
+  __shared__ float sh[64];
+  float s = 0.f;
+  float bad = 0.f;
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < n;
+       i += (long long)gridDim.x * blockDim.x * 4) {
+    if (i + 4 <= n) {
+      const float4 v = load_grad4<G>(x, i);
+      s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    } else {
+      for (long long j = i; j < n; ++j) {
+        float f;
+        if (sizeof(G) == 2) f = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[j]);
+        else f = reinterpret_cast<const float*>(x)[j];
+        s += f * f;
+      }
+    }
+  }
+  if (!isfinite(s)) bad = 1.f;
+  const float2 r = block_sum2(s, bad, sh);
+  if (threadIdx.x == 0) {
+    atomicAdd(acc, r.x);
+    if (r.y > 0.f || !isfinite(r.x)) atomicExch(acc + 1, 1.f);
+  }
+}
+
+// out[0] = min(1, max_norm / (sqrt(acc[0]) * inv_scale + 1e-6)) * inv_scale ; skip = acc[1] != 0
+// (the gradient multiplier for the update), out[1] = unscaled global norm.
+__global__ void clip_coef_kernel(const float* __restrict__ acc, float max_norm, float inv_scale,
+                                 float* __restrict__ out, int* __restrict__ skip) {
+  const float norm = sqrtf(acc[0]) * inv_scale;
+  float coef = 1.f;
+  if (max_norm > 0.f) coef = fminf(1.f, max_norm / (norm + 1e-6f));
+  out[0] = coef * inv_scale;
+  out[1] = norm;
+  if (skip != nullptr) *skip = (acc[1] != 0.f || !isfinite(norm)) ? 1 : 0;
+}
+
+}  // namespace nx
+
+// grad_dtype: 0 = bf16, 1 = fp32.  grad_scale (device float*, nullable) multiplies every gradient;
+// skip (device int*, nullable) non-zero turns the launch into a no-op.
+NX_API int nx_adamw_step(void* p, void* m, void* v, const void* g, void* p_bf16, long long n,
+                         float lr, float beta1, float beta2, float eps, float weight_decay,
+                         float bias_corr1, float bias_corr2, int adam_w_mode,
+                         const void* grad_scale, const void* skip, int grad_dtype, void* stream_) {
+  using namespace nx;
+  if (n == 0) return NX_OK;
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, adam_w_mode};
+  const long long nvec = (n + 3) / 4;
+  long long g_ = (nvec + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  const int grid = static_cast<int>(g_ < cap ? g_ : cap);
+  auto s = (cudaStream_t)stream_;
+  if (grad_dtype == 0)
+    adamw_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((float*)p, (float*)m, (float*)v,
+                                                     (const __nv_bfloat16*)g, (__nv_bfloat16*)p_bf16,
+                                                     n, a, (const float*)grad_scale, (const int*)skip);
+  else
+    adamw_kernel<float><<<grid, 256, 0, s>>>((float*)p, (float*)m, (float*)v, (const float*)g,
+                                             (__nv_bfloat16*)p_bf16, n, a, (const float*)grad_scale,
+                                             (const int*)skip);
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+NX_API int nx_sumsq(const void* x, long long n, void* acc, int dtype, void* stream_) {
+  using namespace nx;
+  if (n == 0) return NX_OK;
+  const long long nvec = (n + 3) / 4;
+  long long g_ = (nvec + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 8;
+  const int grid = static_cast<int>(g_ < cap ? g_ : cap);
+  auto s = (cudaStream_t)stream_;
+  if (dtype == 0) sumsq_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, n, (float*)acc);
+  else sumsq_kernel<float><<<grid, 256, 0, s>>>((const float*)x, n, (float*)acc);
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+NX_API int nx_clip_coef(const void* acc, float max_norm, float inv_scale, void* out, void* skip,
+                        void* stream_) {
+  nx::clip_coef_kernel<<<1, 1, 0, (cudaStream_t)stream_>>>((const float*)acc, max_norm, inv_scale,
+                                                           (float*)out, (int*)skip);
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}

@@ -33,37 +33,39 @@ def _declare(lib):
             fn.argtypes = argtypes
             fn.restype = restype
 
-    P, I, L, F = c_void_p, c_int, c_ll, c_float
+    P, I, L, F, U = c_void_p, c_int, c_ll, c_float, C.c_ulonglong
     sig("nx_last_error", [], C.c_char_p)
     sig("nx_read_device_error", [I])
     sig("nx_poison_device_error", [I])
     sig("nx_sm_count", [])
     sig("nx_abi_version", [])
     sig("nx_gemm_bf16", [P, P, P, I, I, I, L, L, L, I, I, P, P, P, P, L, I, F, P])
-    sig("nx_grouped_gemm_bf16", [P, P, P, P, I, I, I, I, I, I, P])
-    sig("nx_layernorm_fwd", [P, P, P, P, P, P, P, L, I, F, I, P])
-    sig("nx_layernorm_bwd", [P, P, P, P, P, P, P, P, P, L, I, I, P])
-    sig("nx_rmsnorm_fwd", [P, P, P, P, P, L, I, F, I, P])
-    sig("nx_rmsnorm_bwd", [P, P, P, P, P, P, P, L, I, I, P])
+    sig("nx_norm_fwd", [I, P, P, P, P, P, P, P, P, P, L, I, F, P])
+    sig("nx_norm_bwd_blocks", [L])
+    sig("nx_norm_bwd", [I, P, P, P, P, P, P, P, P, P, P, L, I, I, P])
     sig("nx_bias_act_fwd", [P, P, P, L, I, I, P])
     sig("nx_bias_act_bwd", [P, P, P, P, L, I, I, P])
-    sig("nx_gated_act_fwd", [P, P, P, L, I, I, P])
-    sig("nx_gated_act_bwd", [P, P, P, P, L, I, I, P])
-    sig("nx_bias_dropout_add_fwd", [P, P, P, P, P, L, I, F, C.c_ulonglong, C.c_ulonglong, P])
-    sig("nx_colsum_bf16", [P, P, L, I, I, P])
-    sig("nx_rope_fwd", [P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, L, L, I, P])
+    sig("nx_gated_act_fwd", [P, P, L, I, I, P])
+    sig("nx_gated_act_bwd", [P, P, P, L, I, I, P])
+    sig("nx_bias_dropout_add", [P, P, P, P, P, L, I, F, U, U, P])
+    sig("nx_dropout_bwd", [P, P, P, L, F, P])
+    sig("nx_colsum_slabs", [L])
+    sig("nx_colsum_bf16", [P, P, P, P, L, I, L, I, P])
+    sig("nx_cast_f32_to_bf16", [P, P, L, F, P])
     sig("nx_softmax_causal_fwd", [P, P, L, I, I, F, P])
-    sig("nx_softmax_causal_bwd", [P, P, P, L, I, I, F, P])
     sig("nx_softmax_masked_fwd", [P, P, P, I, I, I, I, I, F, P])
-    sig("nx_softmax_masked_bwd", [P, P, P, L, I, F, P])
-    sig("nx_cross_entropy_fwd", [P, P, P, P, P, L, I, L, I, I, P])
-    sig("nx_cross_entropy_bwd", [P, P, P, P, P, P, L, I, L, I, I, P])
-    sig("nx_adamw_step", [P, P, P, P, P, L, F, F, F, F, F, F, F, P, I, P])
-    sig("nx_sumsq", [P, P, L, I, P])
+    sig("nx_softmax_bwd", [P, P, P, L, I, F, P])
+    sig("nx_softmax_batch_per_block", [I, I, I, I])
+    sig("nx_ce_fwd", [P, P, P, L, I, L, I, I, P])
+    sig("nx_ce_bwd", [P, P, P, P, P, L, I, L, L, I, I, P])
+    sig("nx_adamw_step", [P, P, P, P, P, L, F, F, F, F, F, F, F, I, P, P, I, P])
+    sig("nx_sumsq", [P, L, P, I, P])
+    sig("nx_clip_coef", [P, F, F, P, P, P])
+    sig("nx_rope", [P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, I, I, P])
     sig("nx_embedding_fwd", [P, P, P, L, I, L, L, P])
     sig("nx_embedding_bwd", [P, P, P, L, I, L, L, P])
-    sig("nx_flash_attn_fwd", [P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P])
-    sig("nx_flash_attn_bwd", [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P])
+    sig("nx_flash_attn_fwd", [P] * 6 + [I] * 6 + [L] * 12 + [F, I, I, P])
+    sig("nx_flash_attn_bwd", [P] * 11 + [I] * 6 + [L] * 24 + [F, I, I, P])
     return lib
 
 
