@@ -1,0 +1,418 @@
+"""Training engine: what the reference obtains from ``deepspeed.initialize`` (megatron/training.py:1188-1198):
+mixed precision with fp32 master weights, gradient accumulation, ZeRO-1/2 optimizer-state
+partitioning over the data-parallel group, global-norm clipping, fp16 dynamic loss scaling, the
+optimizer step and the learning-rate schedule.
+
+Layout (designed for 180 GB of HBM per GPU and NVSwitch collectives, not ported from DeepSpeed):
+every parameter of a data-parallel group lives in ONE flat low-precision buffer, ordered
+[decay | no-decay] x [tensor-parallel-sharded | replicated]; a flat fp32 ``main_grad`` buffer of the
+same shape receives gradients (GEMM weight gradients are accumulated straight into it by the wgrad
+epilogue).  At the accumulation boundary the flat gradient is reduce-scattered once, each rank runs
+the fused AdamW kernel on its contiguous shard (fp32 master + moments, clip / unscale factor read
+from device memory, bf16 weights written in the same pass) and the flat weight buffer is
+all-gathered once.  No per-parameter launches, no host synchronisation in bf16 mode.
+"""
+from __future__ import annotations
+
+import math
+from contextlib import contextmanager
+
+import torch
+import torch.distributed as dist
+
+from .. import parallel as mpu
+from ..ops import optim as optim_ops
+from .loss_scaler import LossScaler, build_loss_scaler
+
+_ALIGN = 64  # elements: keeps every parameter 128-byte aligned inside the flat buffer (TMA needs 16)
+
+
+def _is_replicated(p) -> bool:
+    """True for parameters that hold the same values on every tensor-parallel rank."""
+    return not getattr(p, "model_parallel", False)
+
+
+class FlatGroup:
+    """One flat parameter space reduced over one data-parallel process group."""
+
+    def __init__(self, entries, dp_group, dp_size, dp_rank, zero_stage, grad_dtype):
+        # entries: list of (param, weight_decay)
+        self.dp_group, self.dp_size, self.dp_rank = dp_group, dp_size, dp_rank
+        self.zero_stage = zero_stage
+        order = sorted(range(len(entries)), key=lambda i: (0 if entries[i][1] > 0 else 1,
+                                                            1 if _is_replicated(entries[i][0]) else 0))
+        self.params = [entries[i][0] for i in order]
+        self.wds = [entries[i][1] for i in order]
+        self.device = self.params[0].device
+        self.lp_dtype = self.params[0].dtype
+        offs, off = [], 0
+        for p in self.params:
+            offs.append(off)
+            off += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
+        unit = dp_size * 256
+        self.total = (off + unit - 1) // unit * unit
+        self.offsets = offs
+        self.flat_lp = torch.zeros(self.total, dtype=self.lp_dtype, device=self.device)
+        self.main_grad = torch.zeros(self.total, dtype=grad_dtype, device=self.device)
+        for p, o in zip(self.params, offs):
+            n = p.numel()
+            self.flat_lp[o:o + n].copy_(p.data.reshape(-1))
+            p.data = self.flat_lp[o:o + n].view(p.shape)
+            p.main_grad = self.main_grad[o:o + n].view(p.shape)
+            p.grad = None
+        # regions of constant (weight decay, replicated)
+        self.regions = []
+        for p, o, wd in zip(self.params, offs, self.wds):
+            key = (wd, _is_replicated(p))
+            end = o + (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
+            if self.regions and self.regions[-1][2:] == key and self.regions[-1][1] == o:
+                self.regions[-1] = (self.regions[-1][0], end) + key
+            else:
+                self.regions.append((o, end) + key)
+        sharded = zero_stage >= 1 and dp_size > 1
+        self.shard_size = self.total // dp_size if sharded else self.total
+        self.shard_start = dp_rank * self.shard_size if sharded else 0
+        self.sharded = sharded
+        s, e = self.shard_start, self.shard_start + self.shard_size
+        if self.lp_dtype == torch.float32:
+            self.master = self.flat_lp[s:e]
+        else:
+            self.master = self.flat_lp[s:e].float()
+        self.exp_avg = torch.zeros(self.shard_size, dtype=torch.float32, device=self.device)
+        self.exp_avg_sq = torch.zeros(self.shard_size, dtype=torch.float32, device=self.device)
+        # my shard's intersections with the regions: (lo, hi, wd, replicated), shard-relative
+        self.segments = []
+        for (a, b, wd, rep) in self.regions:
+            lo, hi = max(a, s), min(b, e)
+            if hi > lo:
+                self.segments.append((lo - s, hi - s, wd, rep))
+
+    def numel(self):
+        return sum(p.numel() for p in self.params)
+
+    def fold_autograd_grads(self):
+        """Parameters whose gradient came through plain autograd (``.grad``) are added into
+        ``main_grad``; GEMM weights were accumulated there directly by the wgrad epilogue."""
+        for p in self.params:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.view_as(p.main_grad).to(p.main_grad.dtype))
+                p.grad = None
+
+    def grad_shard(self):
+        return self.main_grad[self.shard_start:self.shard_start + self.shard_size]
+
+    def reduce_gradients(self):
+        if self.dp_size == 1:
+            return
+        if self.sharded:
+            out = self.grad_shard()
+            if self.main_grad.is_cuda:
+                dist.reduce_scatter_tensor(out, self.main_grad, group=self.dp_group)
+            else:
+                dist.all_reduce(self.main_grad, group=self.dp_group)
+        else:
+            dist.all_reduce(self.main_grad, group=self.dp_group)
+
+    def gather_params(self):
+        if self.sharded:
+            lp_shard = self.flat_lp[self.shard_start:self.shard_start + self.shard_size]
+            if self.flat_lp.is_cuda:
+                dist.all_gather_into_tensor(self.flat_lp, lp_shard, group=self.dp_group)
+            else:
+                parts = [torch.empty_like(lp_shard) for _ in range(self.dp_size)]
+                dist.all_gather(parts, lp_shard.clone(), group=self.dp_group)
+                self.flat_lp.copy_(torch.cat(parts))
+
+    def zero_grad(self):
+        self.main_grad.zero_()
+        for p in self.params:
+            p.grad = None
+
+    # ------------------------------------------------------------------ checkpoint support
+    def shard_state(self):
+        return {"master": self.master.detach().clone().cpu() if self.lp_dtype != torch.float32 else
+                self.master.detach().clone().cpu(),
+                "exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu(),
+                "shard_start": self.shard_start, "shard_size": self.shard_size, "total": self.total}
+
+    def load_shard_state(self, sd):
+        if sd["shard_size"] == self.shard_size and sd["shard_start"] == self.shard_start:
+            self.exp_avg.copy_(sd["exp_avg"])
+            self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+            if self.lp_dtype != torch.float32:
+                self.master.copy_(sd["master"])
+            return True
+        return False
+
+    def refresh_master_from_lp(self):
+        if self.lp_dtype != torch.float32:
+            self.master.copy_(self.flat_lp[self.shard_start:self.shard_start + self.shard_size].float())
+
+
+class FlatAdam:
+    """Optimizer facade over the flat groups: ``param_groups`` (for the LR schedule and logging),
+    ``step``, ``state_dict`` / ``load_state_dict``, ``overflow`` and ``cur_scale`` as the reference
+    reads them from its engine's optimizer (megatron/training.py:1380,1518)."""
+
+    def __init__(self, groups, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, adam_w_mode=True,
+                 generic_cls=None, generic_kwargs=None):
+        self.groups = groups
+        self.defaults = {"lr": lr, "betas": tuple(betas), "eps": eps, "weight_decay": weight_decay}
+        self.adam_w_mode = adam_w_mode
+        self.param_groups = [
+            {"params": [p for g in groups for p, wd in zip(g.params, g.wds) if wd > 0], "lr": lr,
+             "betas": tuple(betas), "eps": eps, "weight_decay": weight_decay, "name": "weight_decay_params"},
+            {"params": [p for g in groups for p, wd in zip(g.params, g.wds) if wd == 0], "lr": lr,
+             "betas": tuple(betas), "eps": eps, "weight_decay": 0.0, "name": "no_weight_decay_params"},
+        ]
+        self.step_count = 0
+        self.overflow = False
+        self.cur_scale = 1.0
+        self.generic = None
+        if generic_cls is not None:
+            self._seg_params = []
+            pgs = []
+            for g in groups:
+                for (lo, hi, wd, _rep) in g.segments:
+                    sp = torch.nn.Parameter(g.master[lo:hi], requires_grad=True)
+                    self._seg_params.append((g, lo, hi, sp))
+                    pgs.append({"params": [sp], "weight_decay": wd})
+            self.generic = generic_cls(pgs, lr=lr, **(generic_kwargs or {}))
+
+    @property
+    def lr(self):
+        return self.param_groups[0]["lr"]
+
+    def step(self, grad_scale, skip):
+        self.step_count += 1
+        lr = self.param_groups[0]["lr"]
+        b1, b2 = self.param_groups[0]["betas"]
+        eps = self.param_groups[0]["eps"]
+        if self.generic is not None:
+            if skip is not None and int(skip[0]) != 0:
+                self.step_count -= 1
+                return
+            for pg in self.generic.param_groups:
+                pg["lr"] = lr
+            for (g, lo, hi, sp) in self._seg_params:
+                sp.grad = g.grad_shard()[lo:hi].float() * grad_scale[0]
+            self.generic.step()
+            for g in self.groups:
+                if g.lp_dtype != torch.float32:
+                    g.flat_lp[g.shard_start:g.shard_start + g.shard_size].copy_(g.master)
+            return
+        for g in self.groups:
+            gs = g.grad_shard()
+            lp_shard = g.flat_lp[g.shard_start:g.shard_start + g.shard_size] if g.lp_dtype != torch.float32 else None
+            for (lo, hi, wd, _rep) in g.segments:
+                optim_ops.adamw_step_(g.master[lo:hi], g.exp_avg[lo:hi], g.exp_avg_sq[lo:hi], gs[lo:hi],
+                                      lp_shard[lo:hi] if lp_shard is not None else None,
+                                      lr=lr, beta1=b1, beta2=b2, eps=eps, weight_decay=wd, step=self.step_count,
+                                      adam_w_mode=self.adam_w_mode, grad_scale=grad_scale, skip=skip)
+
+    def zero_grad(self, set_to_none=True):
+        for g in self.groups:
+            g.zero_grad()
+
+    def state_dict(self):
+        return {"step": self.step_count, "param_groups": [{k: v for k, v in pg.items() if k != "params"}
+                                                           for pg in self.param_groups],
+                "shards": [g.shard_state() for g in self.groups], "cur_scale": self.cur_scale}
+
+    def load_state_dict(self, sd):
+        self.step_count = sd.get("step", 0)
+        for pg, spg in zip(self.param_groups, sd.get("param_groups", [])):
+            pg.update({k: v for k, v in spg.items() if k != "params"})
+        ok = True
+        for g, s in zip(self.groups, sd.get("shards", [])):
+            ok = g.load_shard_state(s) and ok
+        self.cur_scale = sd.get("cur_scale", self.cur_scale)
+        return ok
+
+
+class Engine(torch.nn.Module):
+    """forward / backward / step with gradient accumulation over the flat groups above."""
+
+    def __init__(self, module, neox_args, param_groups, optimizer_cfg=None, lr_scheduler=None,
+                 generic_optimizer=None):
+        super().__init__()
+        self.module = module
+        self.neox_args = neox_args
+        a = neox_args
+        self.gradient_accumulation_steps = a.gradient_accumulation_steps
+        self.micro_steps = 0
+        self.global_steps = 0
+        self.skipped_steps = 0
+        self.global_samples = 0
+        self.zero_stage = a.zero_stage if isinstance(a.zero_stage, int) else 0
+        if self.zero_stage >= 3:
+            raise NotImplementedError("ZeRO stage 3 (parameter partitioning) is not built; use stage 0, 1 or 2")
+        self.gradient_clipping = a.gradient_clipping or 0.0
+        self.fp16_enabled = a.precision == "fp16"
+        self.bfloat16_enabled = a.precision == "bfloat16"
+        self.loss_scaler = build_loss_scaler(a.fp16) if self.fp16_enabled else LossScaler(1.0)
+        grad_dtype = torch.float32 if (a.fp32_grad_accum or a.precision == "fp32") else a.params_dtype
+        dense, expert = [], []
+        for pg in param_groups:
+            wd = pg.get("weight_decay", a.weight_decay)
+            for p in pg["params"]:
+                (expert if getattr(p, "expert_parallel", False) else dense).append((p, wd))
+        self.groups = []
+        if dense:
+            self.groups.append(FlatGroup(dense, mpu.get_data_parallel_group(), mpu.get_data_parallel_world_size(),
+                                         mpu.get_data_parallel_rank(), self.zero_stage, grad_dtype))
+        if expert:
+            ep = mpu.get_expert_parallel_world_size()
+            self.groups.append(FlatGroup(expert, mpu.get_expert_data_parallel_group(),
+                                         mpu.get_data_parallel_world_size() // ep,
+                                         mpu.get_data_parallel_rank() // ep, self.zero_stage, grad_dtype))
+        self.optimizer = None
+        if optimizer_cfg is not None and self.groups:
+            self.optimizer = FlatAdam(self.groups, **optimizer_cfg, **(generic_optimizer or {}))
+            self.optimizer.cur_scale = self.loss_scaler.cur_scale
+        self.lr_scheduler = lr_scheduler
+        dev = self.groups[0].device if self.groups else torch.device("cpu")
+        self._acc = torch.zeros(2, dtype=torch.float32, device=dev)
+        self._scale = torch.ones(2, dtype=torch.float32, device=dev)
+        self._skip = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._last_grad_norm = None
+        self.store_gradients = False
+        self.stored_gradients = None
+        self.timer_values = None
+        self.training_dataloader = None
+
+    # ------------------------------------------------------------------ reference-engine surface
+    def train(self, mode=True):
+        super().train(mode)
+        return self
+
+    def forward(self, *inputs, **kwargs):
+        return self.module(*inputs, **kwargs)
+
+    def is_gradient_accumulation_boundary(self):
+        return (self.micro_steps + 1) % self.gradient_accumulation_steps == 0
+
+    @property
+    def cur_scale(self):
+        return self.loss_scaler.cur_scale
+
+    def get_global_grad_norm(self):
+        return None if self._last_grad_norm is None else float(self._last_grad_norm)
+
+    def backward(self, loss, retain_graph=False):
+        """Scale by 1/GAS (and the fp16 loss scale) and back-propagate."""
+        scaled = loss / self.gradient_accumulation_steps
+        if self.fp16_enabled:
+            scaled = scaled * self.loss_scaler.cur_scale
+        scaled.backward(retain_graph=retain_graph)
+        return loss
+
+    def _sync_sequence_parallel_grads(self):
+        """Norm parameters see only their sequence shard under sequence parallelism: sum their
+        gradients over the tensor-parallel group with ONE flat all-reduce."""
+        if mpu.get_model_parallel_world_size() == 1:
+            return
+        ps = [p for g in self.groups for p in g.params if getattr(p, "sequence_parallel_grad_sync", False)]
+        if not ps:
+            return
+        flat = torch.cat([p.main_grad.reshape(-1) for p in ps])
+        dist.all_reduce(flat, group=mpu.get_model_parallel_group())
+        off = 0
+        for p in ps:
+            n = p.numel()
+            p.main_grad.copy_(flat[off:off + n].view_as(p.main_grad))
+            off += n
+
+    def step(self):
+        """Optimizer step at the accumulation boundary, otherwise just count the micro-step."""
+        boundary = self.is_gradient_accumulation_boundary()
+        self.micro_steps += 1
+        self.global_samples += self.neox_args.train_micro_batch_size_per_gpu * mpu.get_data_parallel_world_size()
+        if not boundary:
+            return
+        self._take_model_step()
+
+    def _take_model_step(self):
+        for g in self.groups:
+            g.fold_autograd_grads()
+        self._sync_sequence_parallel_grads()
+        if self.store_gradients:
+            self.stored_gradients = [p.main_grad.detach().clone() for g in self.groups for p in g.params]
+        for g in self.groups:
+            g.reduce_gradients()
+        # global gradient norm: every element is owned (counted) by exactly one rank of the world
+        self._acc.zero_()
+        tp_rank0 = mpu.get_model_parallel_rank() == 0
+        for g in self.groups:
+            gs = g.grad_shard()
+            for (lo, hi, _wd, rep) in g.segments:
+                if rep and not tp_rank0:
+                    continue
+                optim_ops.sumsq_(gs[lo:hi], self._acc)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(self._acc[0:1])
+            dist.all_reduce(self._acc[1:2], op=dist.ReduceOp.MAX)
+        dp_avg = 1.0 / max(g.dp_size for g in self.groups) if self.groups else 1.0
+        inv_scale = dp_avg / (self.loss_scaler.cur_scale if self.fp16_enabled else 1.0)
+        optim_ops.clip_coef_(self._acc, self.gradient_clipping, inv_scale, self._scale, self._skip)
+        self._last_grad_norm = self._scale[1]
+        overflow = False
+        if self.fp16_enabled:
+            overflow = bool(self._skip.item() != 0)     # fp16 only: the scaler needs the answer on the host
+            self.loss_scaler.update_scale(overflow)
+        if self.optimizer is not None:
+            self.optimizer.overflow = overflow
+            self.optimizer.cur_scale = self.loss_scaler.cur_scale
+            self.optimizer.step(self._scale, self._skip)
+        for g in self.groups:
+            g.gather_params()
+            g.zero_grad()
+        if overflow:
+            self.skipped_steps += 1
+        elif self.lr_scheduler is not None:
+            self.lr_scheduler.step()
+        self.global_steps += 1
+
+    def zero_grad(self):
+        for g in self.groups:
+            g.zero_grad()
+
+    def set_batch_fn(self, fn):
+        self.batch_fn = fn
+        if hasattr(self.module, "set_batch_fn"):
+            self.module.set_batch_fn(fn)
+
+    def set_has_attention_mask(self, value):
+        self.has_attention_mask = value
+
+    @property
+    def total_params(self):
+        return sum(g.numel() for g in self.groups)
+
+    # checkpoint IO is implemented in ckpt/ and bound here
+    def save_checkpoint(self, save_dir, tag=None, client_state=None):
+        from ..ckpt.io import save_engine_checkpoint
+        return save_engine_checkpoint(self, save_dir, tag, client_state or {})
+
+    def load_checkpoint(self, load_dir, tag=None, load_optimizer_states=True, load_lr_scheduler_states=True,
+                        load_module_only=False, load_module_strict=True):
+        from ..ckpt.io import load_engine_checkpoint
+        return load_engine_checkpoint(self, load_dir, tag, load_optimizer_states, load_lr_scheduler_states,
+                                      load_module_only, load_module_strict)
+
+
+def initialize(model, neox_args, param_groups=None, optimizer_cfg=None, lr_scheduler=None, generic_optimizer=None):
+    """Counterpart of ``deepspeed.initialize``: returns ``(engine, optimizer, None, lr_scheduler)``.
+    A pipeline-parallel model gets the pipeline engine."""
+    if param_groups is None:
+        from ..models.utils import get_params_for_weight_decay_optimization
+        param_groups = get_params_for_weight_decay_optimization(model, neox_args)
+    if neox_args.is_pipe_parallel:
+        from .pipeline import PipelineEngine
+        engine = PipelineEngine(model, neox_args, param_groups, optimizer_cfg, lr_scheduler, generic_optimizer)
+    else:
+        engine = Engine(model, neox_args, param_groups, optimizer_cfg, lr_scheduler, generic_optimizer)
+    if lr_scheduler is not None and engine.optimizer is not None:
+        lr_scheduler.optimizer = engine.optimizer
+        lr_scheduler.step(lr_scheduler.num_iters)
+    return engine, engine.optimizer, None, lr_scheduler

@@ -1,0 +1,235 @@
+"""Tensor-parallel layers: VocabParallelEmbedding, ColumnParallelLinear, RowParallelLinear,
+ParallelRelativePositionBias.
+
+Same constructor / forward contracts as megatron/mpu/layers.py:98-790 (weights ``[out/p, in]`` for
+column, ``[out, in/p]`` for row; forward returns ``(output, bias_if_skipped)``).  The matmuls run
+on this library's tcgen05 GEMM; under tensor parallelism the collective next to each GEMM is
+issued through ``comm`` (NCCL in baseline mode, in-kernel NVLink paths in fused mode).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch.nn.parameter import Parameter
+
+from ..ops.embedding import embedding as embedding_op
+from ..ops.gemm import linear as linear_op
+from . import state as mpu
+from .mappings import (copy_to_model_parallel_region, gather_from_model_parallel_region,
+                       gather_from_sequence_parallel_region, reduce_from_model_parallel_region,
+                       reduce_scatter_to_sequence_parallel_region, scatter_to_model_parallel_region)
+from .random import get_cuda_rng_tracker
+from .utils import VocabUtility, divide
+
+
+def _device(neox_args):
+    if getattr(neox_args, "use_cpu_initialization", False) or not torch.cuda.is_available():
+        return torch.device("cpu")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+def _set_tp_attrs(p, is_parallel, dim, stride):
+    p.model_parallel = is_parallel
+    p.partition_dim = dim
+    p.partition_stride = stride
+
+
+def _init_partitioned(weight, full_shape, partition_dim, init_method, neox_args, stride=1):
+    """Initialise this rank's shard. With ``use_cpu_initialization`` the full matrix is drawn once
+    (identical on all ranks) and sliced, so a tensor-parallel model starts from exactly the
+    weights of the unsharded one; otherwise the shard is drawn directly from the per-rank
+    model-parallel RNG stream (megatron/mpu/layers.py:44-95)."""
+    ws = mpu.get_model_parallel_world_size()
+    _set_tp_attrs(weight, True, partition_dim, stride)
+    if ws == 1 or not getattr(neox_args, "use_cpu_initialization", False):
+        with get_cuda_rng_tracker().fork():
+            init_method(weight)
+        return
+    master = torch.empty(full_shape, dtype=torch.float32)
+    init_method(master)
+    per = full_shape[partition_dim] // ws
+    shard = master.narrow(partition_dim, mpu.get_model_parallel_rank() * per, per)
+    with torch.no_grad():
+        weight.copy_(shard.to(weight.dtype))
+
+
+class VocabParallelEmbedding(nn.Module):
+    """Embedding with the vocabulary dimension sharded over the tensor-parallel group."""
+
+    def __init__(self, neox_args, num_embeddings, embedding_dim, init_method=nn.init.xavier_normal_):
+        super().__init__()
+        self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
+        self.model_parallel_size = mpu.get_model_parallel_world_size()
+        self.vocab_start_index, self.vocab_end_index = VocabUtility.vocab_range_from_global_vocab_size(
+            num_embeddings, mpu.get_model_parallel_rank(), self.model_parallel_size)
+        self.num_embeddings_per_partition = self.vocab_end_index - self.vocab_start_index
+        self.init_method = init_method
+        self.use_mup = getattr(neox_args, "use_mup", False)
+        self.mup_embedding_mult = getattr(neox_args, "mup_embedding_mult", 1.0)
+        self.weight = Parameter(torch.empty(self.num_embeddings_per_partition, embedding_dim,
+                                            device=_device(neox_args), dtype=neox_args.params_dtype))
+        _init_partitioned(self.weight, (num_embeddings, embedding_dim), 0, init_method, neox_args)
+
+    def forward(self, input_):
+        out = embedding_op(input_, self.weight, self.vocab_start_index)
+        if self.use_mup:
+            out = out * self.mup_embedding_mult
+        if self.model_parallel_size > 1:
+            out = reduce_from_model_parallel_region(out)
+        return out
+
+
+class ParallelRelativePositionBias(nn.Module):
+    """T5 relative-position bias with heads sharded over the tensor-parallel group
+    (megatron/mpu/layers.py:215-380)."""
+
+    def __init__(self, neox_args, scale, causal=True, num_buckets=32, max_distance=128, heads=8,
+                 init_method=nn.init.xavier_normal_):
+        super().__init__()
+        self.scale, self.causal, self.num_buckets, self.max_distance, self.heads = \
+            scale, causal, num_buckets, max_distance, heads
+        ws = mpu.get_model_parallel_world_size()
+        self.head_start_index, self.head_end_index = VocabUtility.vocab_range_from_global_vocab_size(
+            heads, mpu.get_model_parallel_rank(), ws)
+        self.num_heads_per_partition = self.head_end_index - self.head_start_index
+        self.weight = Parameter(torch.empty(num_buckets, self.num_heads_per_partition,
+                                            device=_device(neox_args), dtype=neox_args.params_dtype))
+        _init_partitioned(self.weight, (num_buckets, heads), 1, init_method, neox_args)
+        self._q_len_cached = self._k_len_cached = self._rel_pos_bucket_cached = None
+
+    @staticmethod
+    def get_heads_range(global_n_heads, rank, world_size):
+        per = divide(global_n_heads, world_size)
+        return rank * per, (rank + 1) * per
+
+    def _relative_position_bucket(self, relative_position, num_buckets=32, max_distance=128):
+        ret = 0
+        n = -relative_position
+        if not self.causal:
+            num_buckets //= 2
+            ret += (n < 0).long() * num_buckets
+            n = torch.abs(n)
+        else:
+            n = torch.max(n, torch.zeros_like(n))
+        max_exact = num_buckets // 2
+        is_small = n < max_exact
+        val_if_large = max_exact + (torch.log(n.float().clamp(min=1) / max_exact) /
+                                    math.log(max_distance / max_exact) * (num_buckets - max_exact)).long()
+        val_if_large = torch.min(val_if_large, torch.full_like(val_if_large, num_buckets - 1))
+        return ret + torch.where(is_small, n, val_if_large)
+
+    def compute_bias(self, q_len, k_len):
+        dev = self.weight.device
+        q_pos = torch.arange(q_len, dtype=torch.long, device=dev)
+        k_pos = torch.arange(k_len, dtype=torch.long, device=dev)
+        rel = k_pos[None, :] - q_pos[:, None]
+        bucket = self._relative_position_bucket(rel, self.num_buckets, self.max_distance)
+        values = F.embedding(bucket, self.weight)          # [q, k, heads/p]
+        return values.permute(2, 0, 1).unsqueeze(0) * self.scale
+
+    def forward(self, q_len, k_len):
+        return self.compute_bias(q_len, k_len)
+
+
+class ColumnParallelLinear(nn.Module):
+    """Y = X A^T + b with A sharded along its output dimension: A_i is ``[out/p, in]``.
+
+    Forward: (sequence-parallel: all-gather X along ``seq_dim`` | else identity with an all-reduce
+    in backward) -> GEMM -> optional all-gather of the output."""
+
+    def __init__(self, neox_args, input_size, output_size, bias=True, gather_output=True,
+                 init_method=nn.init.xavier_normal_, stride=1, keep_master_weight_for_test=False,
+                 skip_bias_add=False, mup_rescale_parameters=False, seq_dim=0):
+        super().__init__()
+        self.input_size, self.output_size = input_size, output_size
+        self.gather_output, self.skip_bias_add = gather_output, skip_bias_add
+        ws = mpu.get_model_parallel_world_size()
+        self.output_size_per_partition = divide(output_size, ws)
+        self.sequence_parallel = bool(neox_args.sequence_parallel) and ws > 1
+        self.seq_dim = seq_dim
+        self.init_method, self.stride = init_method, stride
+        self.mup_rescale_parameters = mup_rescale_parameters
+        self.use_mup = getattr(neox_args, "use_mup", False)
+        self.width_mult_value = 1.0
+        dev, dt = _device(neox_args), neox_args.params_dtype
+        self.weight = Parameter(torch.empty(self.output_size_per_partition, input_size, device=dev, dtype=dt))
+        _init_partitioned(self.weight, (output_size, input_size), 0, init_method, neox_args, stride)
+        if bias:
+            self.bias = Parameter(torch.zeros(self.output_size_per_partition, device=dev, dtype=dt))
+            _set_tp_attrs(self.bias, True, 0, stride)
+        else:
+            self.register_parameter("bias", None)
+
+    def width_mult(self):
+        return self.width_mult_value
+
+    def set_parallel_output(self, value: bool):
+        assert isinstance(value, bool)
+        self.gather_output = not value
+
+    def forward(self, input_):
+        if self.use_mup and self.mup_rescale_parameters:
+            input_ = input_ / self.width_mult()
+        if self.sequence_parallel:
+            input_parallel = gather_from_sequence_parallel_region(input_, seq_dim=self.seq_dim)
+        else:
+            input_parallel = copy_to_model_parallel_region(input_)
+        bias = self.bias if not self.skip_bias_add else None
+        output_parallel = linear_op(input_parallel, self.weight, bias)
+        output = gather_from_model_parallel_region(output_parallel) if self.gather_output else output_parallel
+        return output, (self.bias if self.skip_bias_add else None)
+
+
+class RowParallelLinear(nn.Module):
+    """Y = X A^T + b with A sharded along its input dimension: A_i is ``[out, in/p]``.
+
+    Forward: (optional scatter of X) -> GEMM -> sequence-parallel reduce-scatter | all-reduce |
+    nothing when ``parallel_output`` (the caller reduces, e.g. once per GPT-J block) -> + bias."""
+
+    def __init__(self, neox_args, input_size, output_size, bias=True, input_is_parallel=False,
+                 init_method=nn.init.xavier_normal_, stride=1, keep_master_weight_for_test=False,
+                 skip_bias_add=False, parallel_output=False, mup_rescale_parameters=False, seq_dim=0):
+        super().__init__()
+        self.input_size, self.output_size = input_size, output_size
+        self.input_is_parallel, self.skip_bias_add = input_is_parallel, skip_bias_add
+        self.parallel_output = parallel_output
+        ws = mpu.get_model_parallel_world_size()
+        self.input_size_per_partition = divide(input_size, ws)
+        self.sequence_parallel = bool(neox_args.sequence_parallel) and ws > 1
+        self.seq_dim = seq_dim
+        self.init_method, self.stride = init_method, stride
+        self.mup_rescale_parameters = mup_rescale_parameters
+        self.use_mup = getattr(neox_args, "use_mup", False)
+        self.width_mult_value = 1.0
+        dev, dt = _device(neox_args), neox_args.params_dtype
+        self.weight = Parameter(torch.empty(output_size, self.input_size_per_partition, device=dev, dtype=dt))
+        _init_partitioned(self.weight, (output_size, input_size), 1, init_method, neox_args, stride)
+        if bias:
+            self.bias = Parameter(torch.zeros(output_size, device=dev, dtype=dt))
+        else:
+            self.register_parameter("bias", None)
+
+    def width_mult(self):
+        return self.width_mult_value
+
+    def set_parallel_output(self, parallel_output: bool):
+        assert isinstance(parallel_output, bool)
+        self.parallel_output = parallel_output
+
+    def forward(self, input_):
+        if self.use_mup and self.mup_rescale_parameters:
+            input_ = input_ / self.width_mult()
+        input_parallel = input_ if self.input_is_parallel else scatter_to_model_parallel_region(input_)
+        output_parallel = linear_op(input_parallel, self.weight, None)
+        if self.sequence_parallel and not self.parallel_output:
+            output_ = reduce_scatter_to_sequence_parallel_region(output_parallel, seq_dim=self.seq_dim)
+        elif not self.parallel_output:
+            output_ = reduce_from_model_parallel_region(output_parallel)
+        else:
+            output_ = output_parallel
+        if not self.skip_bias_add:
+            return (output_ + self.bias if self.bias is not None else output_), None
+        return output_, self.bias

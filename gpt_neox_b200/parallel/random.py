@@ -1,0 +1,153 @@
+"""Model-parallel RNG streams and activation checkpointing.
+
+The reference re-exports DeepSpeed's tracker and ``checkpoint`` (megatron/mpu/random.py:18-37);
+this is a self-contained equivalent: a named-stream RNG tracker (dropout inside tensor-parallel
+regions draws from a per-tensor-rank stream, everything else from the default stream shared by
+the tensor-parallel group) and a recompute-in-backward ``checkpoint`` that replays both the default
+and the tracked RNG states.  Works on CPU (gloo tests) and CUDA.
+"""
+from __future__ import annotations
+
+import contextlib
+
+import torch
+
+from . import state as mpu
+
+_MODEL_PARALLEL_RNG = "model-parallel-rng"
+
+
+def _get_state(device_cuda: bool):
+    return torch.cuda.get_rng_state() if device_cuda else torch.get_rng_state()
+
+
+def _set_state(state, device_cuda: bool):
+    if device_cuda:
+        torch.cuda.set_rng_state(state)
+    else:
+        torch.set_rng_state(state)
+
+
+class RNGStatesTracker:
+    """Named RNG states; ``fork(name)`` runs a block under that state and saves it back."""
+
+    def __init__(self):
+        self.states_ = {}
+        self.seeds_ = set()
+
+    def reset(self):
+        self.states_ = {}
+        self.seeds_ = set()
+
+    def get_states(self):
+        return {k: v.clone() for k, v in self.states_.items()}
+
+    def set_states(self, states):
+        self.states_ = states
+
+    def add(self, name, seed):
+        if seed in self.seeds_:
+            raise Exception(f"seed {seed} already exists")
+        if name in self.states_:
+            raise Exception(f"rng state {name} already exists")
+        self.seeds_.add(seed)
+        cuda = torch.cuda.is_available()
+        orig = _get_state(cuda)
+        if cuda:
+            torch.cuda.manual_seed(seed)
+        else:
+            torch.manual_seed(seed)
+        self.states_[name] = _get_state(cuda)
+        _set_state(orig, cuda)
+
+    @contextlib.contextmanager
+    def fork(self, name=_MODEL_PARALLEL_RNG):
+        if name not in self.states_:
+            # single-process / uninitialised use: behave like the default stream
+            yield
+            return
+        cuda = torch.cuda.is_available()
+        orig = _get_state(cuda)
+        _set_state(self.states_[name], cuda)
+        try:
+            yield
+        finally:
+            self.states_[name] = _get_state(cuda)
+            _set_state(orig, cuda)
+
+
+_TRACKER = RNGStatesTracker()
+
+
+def get_cuda_rng_tracker():
+    return _TRACKER
+
+
+def model_parallel_cuda_manual_seed(seed: int):
+    """Default stream: ``seed`` on every rank of a tensor-parallel group (so non-parallel regions
+    agree); tracked model-parallel stream: ``seed + 2718 + tensor_rank``."""
+    offset = seed + 2718
+    mp_seed = offset + mpu.get_model_parallel_rank()
+    _TRACKER.reset()
+    torch.manual_seed(seed)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed(seed)
+    _TRACKER.add(_MODEL_PARALLEL_RNG, mp_seed)
+
+
+class _CheckpointFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, run_function, n_tensor, *args):
+        ctx.run_function = run_function
+        ctx.cuda = any(isinstance(a, torch.Tensor) and a.is_cuda for a in args)
+        ctx.cpu_state = torch.get_rng_state()
+        ctx.cuda_state = torch.cuda.get_rng_state() if ctx.cuda else None
+        ctx.tracker_states = _TRACKER.get_states()
+        with torch.no_grad():
+            outputs = run_function(*args)
+        ctx.inputs = args
+        return outputs
+
+    @staticmethod
+    def backward(ctx, *grads):
+        bwd_cpu = torch.get_rng_state()
+        bwd_cuda = torch.cuda.get_rng_state() if ctx.cuda else None
+        bwd_tracker = _TRACKER.get_states()
+        torch.set_rng_state(ctx.cpu_state)
+        if ctx.cuda:
+            torch.cuda.set_rng_state(ctx.cuda_state)
+        _TRACKER.set_states(ctx.tracker_states)
+        detached = tuple(a.detach().requires_grad_(a.requires_grad) if isinstance(a, torch.Tensor) else a
+                         for a in ctx.inputs)
+        with torch.enable_grad():
+            outputs = ctx.run_function(*detached)
+        torch.set_rng_state(bwd_cpu)
+        if ctx.cuda:
+            torch.cuda.set_rng_state(bwd_cuda)
+        _TRACKER.set_states(bwd_tracker)
+        if isinstance(outputs, torch.Tensor):
+            outputs = (outputs,)
+        pairs = [(o, g) for o, g in zip(outputs, grads) if isinstance(o, torch.Tensor) and o.requires_grad and g is not None]
+        if pairs:
+            torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        in_grads = tuple(a.grad if isinstance(a, torch.Tensor) else None for a in detached)
+        return (None, None) + in_grads
+
+
+_CKPT_CONFIG = {"partition_activations": False, "contiguous": False, "cpu": False, "num_layers": None,
+                "synchronize": False, "profile": False}
+
+
+def configure_checkpointing(partition_activations=False, contiguous_checkpointing=False, num_checkpoints=None,
+                            checkpoint_in_cpu=False, synchronize=False, profile=False):
+    """Counterpart of ``deepspeed.checkpointing.configure`` (megatron/initialize.py:103-118). Under
+    sequence parallelism the layer inputs are already sharded over the tensor-parallel group, which
+    is what ``partition_activations`` buys in the reference."""
+    _CKPT_CONFIG.update(partition_activations=partition_activations, contiguous=contiguous_checkpointing,
+                        num_layers=num_checkpoints, cpu=checkpoint_in_cpu, synchronize=synchronize,
+                        profile=profile)
+
+
+def checkpoint(function, *args):
+    """Run ``function(*args)`` without storing its intermediates; recompute them in backward."""
+    return _CheckpointFunction.apply(function, len(args), *args)
