@@ -95,6 +95,10 @@ def ptr(t):
     """Device pointer of a tensor (or None) as a ctypes void pointer."""
     if t is None:
         return None
+    if not t.is_cuda:
+        # every kernel dereferences its pointers on the device: refuse a host tensor here instead
+        # of letting the GPU fault on it
+        raise KernelError(f"host tensor (shape {tuple(t.shape)}, {t.dtype}) passed to a CUDA kernel")
     return c_void_p(t.data_ptr())
 
 

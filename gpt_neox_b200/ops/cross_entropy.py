@@ -69,6 +69,9 @@ def vocab_parallel_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, voc
     """Per-token loss; ``logits`` [..., V_local] holds vocabulary ids
     [vocab_start, vocab_start + V_local) of the full vocabulary."""
     if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32):
+        if labels.device != logits.device or labels.dtype != torch.int64:
+            raise _lib.KernelError(f"cross_entropy: labels must be int64 on {logits.device}, got {labels.dtype} "
+                                   f"on {labels.device}")
         return _VocabParallelCE.apply(logits, labels, vocab_start, group)
     if logits.is_cuda:
         raise _lib.KernelError(f"cross_entropy: unsupported CUDA dtype {logits.dtype}")

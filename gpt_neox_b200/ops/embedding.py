@@ -38,6 +38,8 @@ class _EmbeddingFn(torch.autograd.Function):
 
 def embedding(ids: torch.Tensor, table: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
     if table.is_cuda and table.dtype == torch.bfloat16 and table.shape[1] % 8 == 0:
+        if ids.device != table.device or ids.dtype != torch.int64:
+            raise _lib.KernelError(f"embedding: ids must be int64 on {table.device}, got {ids.dtype} on {ids.device}")
         return _EmbeddingFn.apply(ids, table, vocab_start)
     if table.is_cuda:
         raise _lib.KernelError("embedding: CUDA path needs a bf16 table with H % 8 == 0")

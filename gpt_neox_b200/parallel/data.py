@@ -11,8 +11,10 @@ _MAX_DATA_DIM = 5
 
 
 def _device():
-    return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() and dist.is_initialized() \
-        and dist.get_backend() == "nccl" else torch.device("cpu")
+    # GPU unless this is a CPU (gloo) run
+    if torch.cuda.is_available() and (not dist.is_initialized() or dist.get_backend() == "nccl"):
+        return torch.device("cuda", torch.cuda.current_device())
+    return torch.device("cpu")
 
 
 def broadcast_data(keys, data, datatype):
