@@ -1,0 +1,55 @@
+"""The fused bf16 CUDA model against the fp32 PyTorch statement of the same model (same weights)."""
+import pytest
+import torch
+
+from common import tiny_config
+
+pytestmark = pytest.mark.gpu
+
+
+def _build(cfg):
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    from gpt_neox_b200.initialize import initialize_megatron
+    a = NeoXArgs.from_dict(cfg)
+    a.configure_distributed_args()
+    a.build_tokenizer()
+    mpu.destroy_model_parallel()
+    initialize_megatron(a)
+    return a, training.get_model(a)
+
+
+@pytest.mark.parametrize("variant", [
+    dict(), dict(gpt_j_residual=False), dict(norm="rmsnorm", activation="swiglu", use_bias_in_mlp=False,
+                                             use_bias_in_attn_linear=False, mlp_multiple_of=64),
+    dict(num_kv_heads=2), dict(pos_emb="alibi"), dict(sliding_window_width=64), dict(bias_gelu_fusion=True)])
+def test_fused_model_matches_fp32_oracle(variant):
+    from gpt_neox_b200.models.gpt2_model import cross_entropy
+    base = dict(num_layers=2, hidden_size=256, num_attention_heads=4, seq_length=256, max_position_embeddings=256,
+                synthetic_vocab_size=1000, attention_config=[[["flash"], 2]], distributed_backend="nccl")
+    base.update(variant)
+    a_gpu, m_gpu = _build(tiny_config(precision="bfloat16", **base))
+    sd = {k: v.detach().float().cpu() for k, v in m_gpu.state_dict().items()}
+    a_cpu, m_cpu = _build(tiny_config(precision="fp32", use_cpu_initialization=True, **base))
+    m_cpu = m_cpu.cpu().float()
+    m_cpu.load_state_dict(sd, strict=False)
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 1000, (2, 257))
+    x, y = tokens[:, :-1].contiguous(), tokens[:, 1:].contiguous()
+    pos = torch.arange(256)[None].expand(2, -1)
+    mask = torch.ones(2, 256)
+    out_g = m_gpu((x.cuda(), pos.cuda(), None))
+    loss_g = cross_entropy(out_g, (y.cuda(), mask.cuda()))
+    loss_g.backward()
+    out_c = m_cpu((x, pos, None))
+    loss_c = cross_entropy(out_c, (y, mask))
+    loss_c.backward()
+    assert abs(loss_g.item() - loss_c.item()) < 3e-2, (loss_g.item(), loss_c.item())
+    gg = {n: p.grad for n, p in m_gpu.named_parameters() if p.grad is not None}
+    worst = 0.0
+    for n, p in m_cpu.named_parameters():
+        if n in gg and p.grad is not None and p.grad.abs().max() > 1e-6:
+            r = ((gg[n].float().cpu() - p.grad).norm() / (p.grad.norm() + 1e-8)).item()
+            worst = max(worst, r)
+    assert worst < 8e-2, f"worst relative gradient error {worst}"
