@@ -19,8 +19,9 @@ def _combine_stats(stats: torch.Tensor, group) -> tuple[torch.Tensor, torch.Tens
     Returns (lse, target) after combining across ``group``."""
     if group is not None and dist.get_world_size(group) > 1:
         ws = dist.get_world_size(group)
-        gathered = torch.empty((ws,) + tuple(stats.shape), device=stats.device, dtype=stats.dtype)
-        dist.all_gather_into_tensor(gathered, stats.contiguous(), group=group)
+        flat = torch.empty((ws * stats.shape[0], stats.shape[1]), device=stats.device, dtype=stats.dtype)
+        dist.all_gather_into_tensor(flat, stats.contiguous(), group=group)
+        gathered = flat.view((ws,) + tuple(stats.shape))
         m = gathered[..., 0]
         gm = m.max(dim=0).values
         s = (gathered[..., 1] * torch.exp(m - gm)).sum(0)

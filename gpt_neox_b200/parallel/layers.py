@@ -44,7 +44,7 @@ def _init_partitioned(weight, full_shape, partition_dim, init_method, neox_args,
     model-parallel RNG stream (megatron/mpu/layers.py:44-95)."""
     ws = mpu.get_model_parallel_world_size()
     _set_tp_attrs(weight, True, partition_dim, stride)
-    if ws == 1 or not getattr(neox_args, "use_cpu_initialization", False):
+    if not getattr(neox_args, "use_cpu_initialization", False):
         with get_cuda_rng_tracker().fork():
             init_method(weight)
         return
@@ -209,6 +209,10 @@ class RowParallelLinear(nn.Module):
         _init_partitioned(self.weight, (output_size, input_size), 1, init_method, neox_args, stride)
         if bias:
             self.bias = Parameter(torch.zeros(output_size, device=dev, dtype=dt))
+            if self.sequence_parallel and not parallel_output:
+                # added after the reduce-scatter: each rank sees only its sequence shard, so the
+                # gradient of this replicated bias is summed over the tensor-parallel group
+                self.bias.sequence_parallel_grad_sync = True
         else:
             self.register_parameter("bias", None)
 
