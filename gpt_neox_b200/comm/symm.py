@@ -1,0 +1,225 @@
+"""Symmetric-memory workspaces and the collectives / fused GEMM+collective kernels that run on them.
+
+One workspace per process group: the same number of bytes allocated on every rank and mapped into
+every peer (handle exchange and mapping are done by ``torch.distributed._symmetric_memory``; the
+kernels that use the peer pointers are this library's own, csrc/comm.cu and csrc/gemm_tcgen05.cu).
+Layout: 64 KiB of epoch flags, then payload.  Epochs are monotone counters advanced identically on
+every rank, so flags are never reset.  When the platform offers an NVLS multicast mapping its
+address is passed to the kernels, which then use ``multimem`` reductions / stores through the switch;
+``NEOX_NVLS=0`` forces plain peer loads and stores (used by the failure-detection tests).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops.gemm import LAUNCHES
+
+_BACKENDS: dict = {}
+DEFAULT_BYTES = int(os.environ.get("NEOX_SYMM_BYTES", 768 * 1024 * 1024))
+
+
+def _declare():
+    L = _lib.lib()
+    if getattr(L, "_comm_declared", False):
+        return L
+    P, I, LL, U, ULL = C.c_void_p, C.c_int, C.c_longlong, C.c_uint, C.c_ulonglong
+    PP = C.POINTER(C.c_ulonglong)
+    L.nx_comm_flag_bytes.restype = I
+    L.nx_comm_allreduce.argtypes = [PP, ULL, I, I, LL, LL, I, U, P]
+    L.nx_comm_reduce_scatter.argtypes = [PP, ULL, I, I, LL, LL, P, I, U, P]
+    L.nx_comm_allgather.argtypes = [PP, ULL, I, I, LL, LL, P, U, P]
+    L.nx_gemm_bf16_comm.argtypes = [P, P, P, I, I, I, LL, LL, LL, I, P, P, P, P, LL, I, I, I, I, U, PP, PP, P, LL,
+                                    P, LL, P]
+    L.nx_gemm_grid.argtypes = [I, I]
+    for n in ("nx_comm_allreduce", "nx_comm_reduce_scatter", "nx_comm_allgather", "nx_gemm_bf16_comm",
+              "nx_gemm_grid"):
+        getattr(L, n).restype = I
+    L._comm_declared = True
+    return L
+
+
+class SymmBackend:
+    def __init__(self, group, nbytes: int = DEFAULT_BYTES):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group
+        self.ws = dist.get_world_size(group)
+        self.me = dist.get_rank(group)
+        L = _declare()
+        self.flag_bytes = L.nx_comm_flag_bytes()
+        self.nbytes = nbytes
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.buf.zero_()
+        torch.cuda.synchronize()
+        self.hdl = symm_mem.rendezvous(self.buf, group)
+        self.ptrs = (C.c_ulonglong * 8)(*([int(p) for p in self.hdl.buffer_ptrs] + [0] * (8 - self.ws)))
+        use_nvls = os.environ.get("NEOX_NVLS", "1") != "0"
+        mc = 0
+        try:
+            if use_nvls and self.hdl.has_multicast_support(dev.type, dev.index):
+                mc = int(self.hdl.multicast_ptr)
+        except Exception:
+            mc = 0
+        self.mc = mc
+        self.epoch = 1
+        # regions: [barrier flags 64K][RS flags 1M][AG flags 16K][collective payload][gather x2][stage x2]
+        self.rs_flag_off = self.flag_bytes
+        self.ag_flag_off = self.rs_flag_off + (1 << 20)
+        data0 = self.ag_flag_off + (16 << 10)
+        unit = ((nbytes - data0) // 5) // 4096 * 4096
+        self.unit = unit
+        self.payload_bytes = unit
+        self.payload = self.buf[self.flag_bytes:]          # collectives address their payload from here
+        self.coll_off = data0
+        self.gather_off = [data0 + unit, data0 + 2 * unit]
+        self.stage_off = [data0 + 3 * unit, data0 + 4 * unit]
+        self.ag_calls = 0
+        self.rs_calls = 0
+        dist.barrier(group)
+
+    def _table(self, off):
+        return (C.c_ulonglong * 8)(*([int(p) + off for p in self.hdl.buffer_ptrs] + [0] * (8 - self.ws)))
+
+    # ------------------------------------------------------------------ fused GEMM + collective
+    def can_fuse(self, m_full: int, k: int, n: int) -> bool:
+        """Row count divisible into ws chunks of whole 128-row tiles, operands fit the regions."""
+        return (m_full % (self.ws * 128) == 0 and k % 8 == 0 and n % 8 == 0 and m_full * k * 2 <= self.unit
+                and m_full * n * 2 <= self.unit and (m_full // self.ws // 128) * ((n + 255) // 256) * self.ws * 16
+                <= (1 << 20))
+
+    def ag_gemm(self, x_shard, w, *, trans_b=False, bias=None, gelu=None, aux_out=None, dgelu_aux=None,
+                dgelu=None):
+        """``y = all_gather_rows(x_shard) @ op(w) (+ epilogue)``. Returns (y [M, N], gathered x [M, K]): the
+        gathered matrix is a view of the symmetric gather buffer, valid until the second next call."""
+        from ..ops import gemm as G
+        ms, k = x_shard.shape
+        m = ms * self.ws
+        n = w.shape[1] if trans_b else w.shape[0]
+        par = self.ag_calls & 1
+        self.ag_calls += 1
+        goff = self.gather_off[par]
+        gathered = self.buf[goff:goff + m * k * 2].view(torch.bfloat16).view(m, k)
+        out = torch.empty((m, n), device=x_shard.device, dtype=torch.bfloat16)
+        flags = 0
+        ld_aux = 0
+        if bias is not None:
+            flags |= G.EPI_BIAS
+        if gelu is not None:
+            flags |= G.EPI_GELU_TANH if gelu == "tanh" else G.EPI_GELU_ERF
+        if aux_out is not None:
+            flags |= G.EPI_AUX_OUT
+            ld_aux = aux_out.stride(0)
+        if dgelu_aux is not None:
+            flags |= G.EPI_DGELU_TANH if dgelu == "tanh" else G.EPI_DGELU_ERF
+            ld_aux = dgelu_aux.stride(0)
+        epoch = self._next_epoch(1)
+        LAUNCHES["n"] += 1
+        _lib.check(_lib.lib().nx_gemm_bf16_comm(
+            _lib.ptr(gathered), _lib.ptr(w), _lib.ptr(out), m, n, k, k, w.stride(0), out.stride(0), int(trans_b),
+            _lib.ptr(bias), _lib.ptr(dgelu_aux), _lib.ptr(aux_out), None, ld_aux, flags, 2, self.me, self.ws, epoch,
+            self._table(goff), self._table(self.ag_flag_off), None, 0, _lib.ptr(x_shard), x_shard.stride(0),
+            _lib.stream()), "nx_gemm_bf16_comm(all-gather)")
+        return out, gathered
+
+    def gemm_rs(self, a, w, *, trans_b=False, residual=None, bias=None, residual2=None, dgelu_aux=None, dgelu=None):
+        """``out = reduce_scatter_rows(a @ op(w) + residual) + bias + residual2`` -> [M / ws, N]."""
+        from ..ops import gemm as G
+        m, k = a.shape
+        n = w.shape[1] if trans_b else w.shape[0]
+        par = self.rs_calls & 1
+        self.rs_calls += 1
+        out = torch.empty((m // self.ws, n), device=a.device, dtype=torch.bfloat16)
+        flags = 0
+        ld_aux = 0
+        if bias is not None:
+            flags |= G.EPI_BIAS
+        if residual is not None:
+            flags |= G.EPI_RESIDUAL
+            ld_aux = residual.stride(0)
+        if dgelu_aux is not None:
+            flags |= G.EPI_DGELU_TANH if dgelu == "tanh" else G.EPI_DGELU_ERF
+            assert ld_aux in (0, dgelu_aux.stride(0))
+            ld_aux = dgelu_aux.stride(0)
+        epoch = self._next_epoch(1)
+        LAUNCHES["n"] += 1
+        _lib.check(_lib.lib().nx_gemm_bf16_comm(
+            _lib.ptr(a), _lib.ptr(w), _lib.ptr(out), m, n, k, a.stride(0), w.stride(0), out.stride(0), int(trans_b),
+            _lib.ptr(bias), _lib.ptr(dgelu_aux), None, _lib.ptr(residual), ld_aux, flags, 1, self.me, self.ws, epoch,
+            self._table(self.stage_off[par]), self._table(self.rs_flag_off), _lib.ptr(residual2),
+            residual2.stride(0) if residual2 is not None else 0, None, 0, _lib.stream()),
+            "nx_gemm_bf16_comm(reduce-scatter)")
+        return out
+
+    def supports(self, x: torch.Tensor) -> bool:
+        return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and x.is_contiguous()
+                and (x.numel() * x.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0)
+
+    def _next_epoch(self, n=2):
+        e = self.epoch
+        self.epoch += n
+        return e
+
+    def _view(self, nbytes, dtype, shape):
+        return self.buf[self.coll_off:self.coll_off + nbytes].view(dtype).view(shape)
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        nb = x.numel() * x.element_size()
+        if nb > self.payload_bytes:
+            dist.all_reduce(x, group=self.group)
+            return x
+        stage = self._view(nb, x.dtype, x.shape)
+        stage.copy_(x)
+        LAUNCHES["n"] += 1
+        _lib.check(_lib.lib().nx_comm_allreduce(self.ptrs, self.mc, self.me, self.ws, self.coll_off, nb,
+                                                0 if x.dtype == torch.bfloat16 else 1, self._next_epoch(),
+                                                _lib.stream()), "nx_comm_allreduce")
+        x.copy_(stage)
+        return x
+
+    def reduce_scatter0(self, x: torch.Tensor) -> torch.Tensor:
+        nb = x.numel() * x.element_size()
+        shard = nb // self.ws
+        if nb > self.payload_bytes or shard % 16 or x.shape[0] % self.ws:
+            out = torch.empty((x.shape[0] // self.ws,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+            dist.reduce_scatter_tensor(out, x, group=self.group)
+            return out
+        self._view(nb, x.dtype, x.shape).copy_(x)
+        out = torch.empty((x.shape[0] // self.ws,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        LAUNCHES["n"] += 1
+        _lib.check(_lib.lib().nx_comm_reduce_scatter(self.ptrs, self.mc, self.me, self.ws, self.coll_off, shard, _lib.ptr(out),
+                                                     0 if x.dtype == torch.bfloat16 else 1, self._next_epoch(),
+                                                     _lib.stream()), "nx_comm_reduce_scatter")
+        return out
+
+    def all_gather0(self, x: torch.Tensor) -> torch.Tensor:
+        shard = x.numel() * x.element_size()
+        nb = shard * self.ws
+        if nb > self.payload_bytes:
+            out = torch.empty((self.ws * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+            dist.all_gather_into_tensor(out, x, group=self.group)
+            return out
+        LAUNCHES["n"] += 1
+        _lib.check(_lib.lib().nx_comm_allgather(self.ptrs, self.mc, self.me, self.ws, self.coll_off, shard, _lib.ptr(x),
+                                                self._next_epoch(), _lib.stream()), "nx_comm_allgather")
+        return self._view(nb, x.dtype, (self.ws * x.shape[0],) + tuple(x.shape[1:])).clone()
+
+
+def init_group(group, nbytes: int = DEFAULT_BYTES):
+    """Create (once) the symmetric workspace of ``group``. Collective: every rank of the group calls it."""
+    key = id(group) if group is not None else 0
+    if key not in _BACKENDS:
+        _BACKENDS[key] = SymmBackend(group, nbytes)
+    return _BACKENDS[key]
+
+
+def backend_for(group):
+    return _BACKENDS.get(id(group) if group is not None else 0)
+
+
+def reset():
+    _BACKENDS.clear()

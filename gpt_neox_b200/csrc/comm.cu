@@ -1,0 +1,194 @@
+// Collectives over NVLink peer memory: all-reduce, all-gather and reduce-scatter kernels that read and
+// write other GPUs' symmetric buffers directly (plain P2P ld/st, or NVLS multimem when a multicast
+// address is given).  They replace the NCCL calls the reference issues from Python at
+// megatron/mpu/mappings.py:44,210,248 in this framework's "fused" communication mode.
+//
+// Symmetric workspace layout (same on every rank; allocated and exchanged by comm/symm.py):
+//   [0, FLAG_BYTES)        uint32 flags: flags[block][src_rank], monotone epoch counters, never reset
+//   [FLAG_BYTES, ...)      payload
+// Cross-rank barrier = every block b of every rank writes its epoch into flags[b][me] of every peer,
+// then waits until its own flags[b][*] have reached that epoch.  All waits are bounded: on expiry
+// the kernel records an error word and returns (outputs are then invalid; the host raises).
+#include "common.h"
+#include "ptx.cuh"
+
+namespace nx {
+
+constexpr int COMM_MAX_RANKS = 8;
+constexpr int COMM_BLOCKS = 64;
+constexpr int COMM_THREADS = 512;
+constexpr int COMM_FLAG_BYTES = 64 * 1024;
+
+struct PeerTable {
+  void* ptr[COMM_MAX_RANKS];  // base of every rank's symmetric workspace, as mapped on this rank
+};
+
+// Block-level barrier across ranks.  phase distinguishes the barriers of one launch.
+__device__ __forceinline__ bool rank_barrier(const PeerTable& t, int me, int ws, uint32_t epoch,
+                                             int* err, int where) {
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x < ws) {
+    const int peer = threadIdx.x;
+    uint32_t* remote = reinterpret_cast<uint32_t*>(t.ptr[peer]) + blockIdx.x * COMM_MAX_RANKS + me;
+    __threadfence_system();
+    st_release_sys(remote, epoch);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(t.ptr[me]) + blockIdx.x * COMM_MAX_RANKS + peer;
+    ok = wait_flag_ge(mine, epoch, err, where);
+  }
+  ok = __syncthreads_and(ok ? 1 : 0) != 0;
+  return ok;
+}
+
+__device__ __forceinline__ float4 add4(float4 a, float4 b) {
+  return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+__device__ __forceinline__ void acc_bf16x8(float (&acc)[8], uint4 u) {
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+  acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+}
+__device__ __forceinline__ uint4 pack_acc(const float (&acc)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+  o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+  return o;
+}
+
+// Sum of the 16-byte vector at payload offset `off` over all ranks (fp32 accumulation).
+template <bool BF16>
+__device__ __forceinline__ uint4 reduce_vec(const PeerTable& t, int ws, const void* mc, long long pay, long long off) {
+  if (mc != nullptr) {
+    const char* p = reinterpret_cast<const char*>(mc) + pay + off;
+    if (BF16) return multimem_ld_reduce_bf16x8(p);
+    const float4 f = multimem_ld_reduce_f32x4(p);
+    return make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z), __float_as_uint(f.w));
+  }
+  if (BF16) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int r = 0; r < ws; ++r)
+      acc_bf16x8(acc, *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(t.ptr[r]) + pay + off));
+    return pack_acc(acc);
+  }
+  float4 s = make_float4(0, 0, 0, 0);
+  for (int r = 0; r < ws; ++r)
+    s = add4(s, *reinterpret_cast<const float4*>(reinterpret_cast<const char*>(t.ptr[r]) + pay + off));
+  return make_uint4(__float_as_uint(s.x), __float_as_uint(s.y), __float_as_uint(s.z), __float_as_uint(s.w));
+}
+
+// Two-shot all-reduce of `bytes` of payload that every rank has placed at payload offset 0 of its
+// own workspace: rank r reduces slice r and writes the result into every rank's workspace.
+template <bool BF16>
+__global__ void __launch_bounds__(COMM_THREADS) allreduce_kernel(PeerTable t, const void* mc, int me, int ws,
+                                                                 long long pay, long long bytes, uint32_t epoch, int* err) {
+  if (!rank_barrier(t, me, ws, epoch, err, 101)) return;
+  const long long nvec = bytes / 16;
+  const long long per = (nvec + ws - 1) / ws;
+  const long long v0 = me * per, v1 = min(nvec, v0 + per);
+  for (long long v = v0 + blockIdx.x * (long long)blockDim.x + threadIdx.x; v < v1;
+       v += (long long)gridDim.x * blockDim.x) {
+    const uint4 s = reduce_vec<BF16>(t, ws, mc, pay, v * 16);
+    if (mc != nullptr) {
+      multimem_st_b128(reinterpret_cast<char*>(const_cast<void*>(mc)) + pay + v * 16, s);
+    } else {
+      for (int r = 0; r < ws; ++r)
+        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.ptr[r]) + pay + v * 16) = s;
+    }
+  }
+  rank_barrier(t, me, ws, epoch + 1, err, 102);
+}
+
+// Reduce-scatter along dim 0: every rank has its full [ws * shard] payload at offset 0; rank r writes
+// the sum of chunk r to `out` (its own memory).
+template <bool BF16>
+__global__ void __launch_bounds__(COMM_THREADS) reduce_scatter_kernel(PeerTable t, const void* mc, int me, int ws,
+                                                                      long long pay, long long shard_bytes, void* out,
+                                                                      uint32_t epoch, int* err) {
+  if (!rank_barrier(t, me, ws, epoch, err, 103)) return;
+  const long long nvec = shard_bytes / 16;
+  const long long base = me * shard_bytes;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec;
+       v += (long long)gridDim.x * blockDim.x) {
+    reinterpret_cast<uint4*>(out)[v] = reduce_vec<BF16>(t, ws, mc, pay, base + v * 16);
+  }
+  rank_barrier(t, me, ws, epoch + 1, err, 104);  // peers may overwrite their payload only after all reads
+}
+
+// All-gather along dim 0: rank r pushes its shard (`in`, own memory) to payload offset r * shard of
+// every rank's workspace.
+__global__ void __launch_bounds__(COMM_THREADS) allgather_kernel(PeerTable t, const void* mc, int me, int ws,
+                                                                 long long pay, long long shard_bytes, const void* in,
+                                                                 uint32_t epoch, int* err) {
+  // the previous user of the workspace must be done on every rank before it is overwritten
+  if (!rank_barrier(t, me, ws, epoch, err, 105)) return;
+  const long long nvec = shard_bytes / 16;
+  const long long base = pay + me * shard_bytes;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec;
+       v += (long long)gridDim.x * blockDim.x) {
+    const uint4 x = reinterpret_cast<const uint4*>(in)[v];
+    if (mc != nullptr) {
+      multimem_st_b128(reinterpret_cast<char*>(const_cast<void*>(mc)) + base + v * 16, x);
+    } else {
+      for (int r = 0; r < ws; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.ptr[r]) + base + v * 16) = x;
+    }
+  }
+  rank_barrier(t, me, ws, epoch + 1, err, 106);
+}
+
+static bool fill_table(PeerTable& t, const unsigned long long* ptrs, int ws) {
+  if (ws < 1 || ws > COMM_MAX_RANKS) return false;
+  for (int i = 0; i < COMM_MAX_RANKS; ++i) t.ptr[i] = i < ws ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+  return true;
+}
+
+}  // namespace nx
+
+NX_API int nx_comm_flag_bytes() { return nx::COMM_FLAG_BYTES; }
+NX_API int nx_comm_epochs_per_call() { return 2; }
+
+// dtype: 0 = bf16, 1 = fp32.  peer_ptrs: host array of ws workspace base addresses (as mapped here).
+// mc_ptr: NVLS multicast address of the workspace or 0.  epoch: first of the two epochs this call
+// consumes (the caller advances its counter by nx_comm_epochs_per_call()).
+NX_API int nx_comm_allreduce(const unsigned long long* peer_ptrs, unsigned long long mc_ptr, int me, int ws,
+                             long long payload_off, long long bytes, int dtype, unsigned int epoch, void* stream_) {
+  using namespace nx;
+  PeerTable t;
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws), "comm: world size %d out of range", ws);
+  NX_REQUIRE(bytes % 16 == 0, "comm: payload must be a multiple of 16 bytes");
+  auto s = (cudaStream_t)stream_;
+  if (dtype == 0)
+    allreduce_kernel<true><<<COMM_BLOCKS, COMM_THREADS, 0, s>>>(t, (const void*)mc_ptr, me, ws, payload_off, bytes, epoch,
+                                                                device_error_word());
+  else
+    allreduce_kernel<false><<<COMM_BLOCKS, COMM_THREADS, 0, s>>>(t, (const void*)mc_ptr, me, ws, payload_off, bytes, epoch,
+                                                                 device_error_word());
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+NX_API int nx_comm_reduce_scatter(const unsigned long long* peer_ptrs, unsigned long long mc_ptr, int me, int ws,
+                                  long long payload_off, long long shard_bytes, void* out, int dtype, unsigned int epoch, void* stream_) {
+  using namespace nx;
+  PeerTable t;
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws), "comm: world size %d out of range", ws);
+  NX_REQUIRE(shard_bytes % 16 == 0, "comm: shard must be a multiple of 16 bytes");
+  auto s = (cudaStream_t)stream_;
+  if (dtype == 0)
+    reduce_scatter_kernel<true><<<COMM_BLOCKS, COMM_THREADS, 0, s>>>(t, (const void*)mc_ptr, me, ws, payload_off, shard_bytes,
+                                                                     out, epoch, device_error_word());
+  else
+    reduce_scatter_kernel<false><<<COMM_BLOCKS, COMM_THREADS, 0, s>>>(t, (const void*)mc_ptr, me, ws, payload_off, shard_bytes,
+                                                                      out, epoch, device_error_word());
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+NX_API int nx_comm_allgather(const unsigned long long* peer_ptrs, unsigned long long mc_ptr, int me, int ws,
+                             long long payload_off, long long shard_bytes, const void* in, unsigned int epoch, void* stream_) {
+  using namespace nx;
+  PeerTable t;
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws), "comm: world size %d out of range", ws);
+  NX_REQUIRE(shard_bytes % 16 == 0, "comm: shard must be a multiple of 16 bytes");
+  allgather_kernel<<<COMM_BLOCKS, COMM_THREADS, 0, (cudaStream_t)stream_>>>(
+      t, (const void*)mc_ptr, me, ws, payload_off, shard_bytes, in, epoch, device_error_word());
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}

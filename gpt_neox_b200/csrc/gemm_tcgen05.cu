@@ -19,6 +19,8 @@
 //   transB = 0: B is [N, K]  (K contiguous, the nn.Linear weight layout)
 //   transB = 1: B is [K, N]  (N contiguous)
 // so that  forward = (0,0),  input-gradient = (0,1),  weight-gradient = (1,1).
+#include <string.h>
+
 #include "common.h"
 #include "ptx.cuh"
 
@@ -55,7 +57,24 @@ struct GemmParams {
   float alpha;
   int tiles_m, tiles_n;
   int* err;
+  // ---- fused collective (tensor-parallel group of `ws` ranks, this rank = `rank`); comm == COMM_NONE
+  //      leaves everything below unused
+  int comm, rank, ws;
+  int tiles_m_chunk;            // row tiles per rank chunk: (M / ws) / BM
+  uint32_t epoch;               // value written to / expected in the flags of this call
+  // COMM_RS (GEMM -> reduce-scatter over rows): C points to this rank's [M/ws, N] output.
+  __nv_bfloat16* rs_stage[8];   // on rank q: staging area [ws][M/ws, N]; slot = source rank
+  uint32_t* rs_flags[8];        // on rank q: flags[tile_in_chunk][src][4 epilogue warps]
+  const __nv_bfloat16* residual2;  // [M/ws, N] added on the owner after the reduction (may be null)
+  long long ld_res2;
+  // COMM_AG (all-gather over rows -> GEMM): A's shard is pushed to every rank's gather buffer first
+  const __nv_bfloat16* ag_src;  // this rank's shard [M/ws, K], leading dimension ag_ld
+  long long ag_ld;
+  __nv_bfloat16* ag_dst[8];     // on rank q: gather buffer [M, K] (dense, leading dimension K)
+  uint32_t* ag_flags[8];        // on rank q: flags[src][cta]
 };
+
+enum CommMode : int { COMM_NONE = 0, COMM_RS = 1, COMM_AG = 2 };
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -80,10 +99,27 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / gsize;
 }
 
+// Tile order under a fused collective: whole rank-chunks of rows at a time.  Reduce-scatter computes the
+// peers' chunks first (so they can finish early) and its own last; all-gather computes its own
+// chunk first (its operand is already local) and the peers' as their shards arrive.
+__device__ __forceinline__ void tile_coords_p(int tile, const GemmParams& p, int& tm, int& tn, int& chunk) {
+  if (p.comm == COMM_NONE) {
+    tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+    chunk = 0;
+    return;
+  }
+  const int per_chunk = p.tiles_m_chunk * p.tiles_n;
+  const int order = tile / per_chunk;
+  chunk = p.comm == COMM_RS ? (p.rank + 1 + order) % p.ws : (p.rank + order) % p.ws;
+  int tl;
+  tile_coords(tile - order * per_chunk, p.tiles_m_chunk, p.tiles_n, tl, tn);
+  tm = chunk * p.tiles_m_chunk + tl;
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const GemmParams p) {
+                     const __grid_constant__ CUtensorMap tmA2, const GemmParams p) {
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -135,10 +171,32 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
+      int ag_ready_chunk = -1;
       for (int tile = blockIdx.x; tile < num_tiles && !aborted; tile += gridDim.x) {
-        int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
+        int tm, tn, chunk;
+        tile_coords_p(tile, p, tm, tn, chunk);
+        int m0 = tm * BM;
+        const int n0 = tn * BN;
+        const CUtensorMap* mapA = &tmA;
+        if (p.comm == COMM_AG) {
+          if (chunk == p.rank) {
+            // own shard: read it where it already is
+            mapA = &tmA2;
+            m0 -= chunk * p.tiles_m_chunk * BM;
+          } else if (chunk != ag_ready_chunk) {
+            // peer shard: wait until every CTA of that peer has pushed its part into this GPU's
+            // gather buffer, then make those generic-proxy writes visible to TMA
+            bool ok = true;
+            for (int c = 0; c < static_cast<int>(gridDim.x) && ok; ++c)
+              ok = wait_flag_ge(p.ag_flags[p.rank] + chunk * 256 + c, p.epoch, p.err, 7);
+            if (!ok) {
+              aborted = true;
+              break;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
+            ag_ready_chunk = chunk;
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, p.err, 1)) {
             aborted = true;
@@ -149,7 +207,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           mbar_expect_tx(full_bar(stage), L::STAGE_BYTES);
           const int k0 = kb * BK;
           if constexpr (!A_MN) {
-            tma_load_2d(a_dst, &tmA, full_bar(stage), k0, m0);
+            tma_load_2d(a_dst, mapA, full_bar(stage), k0, m0);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
@@ -225,9 +283,28 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     int acc = 0;
     uint32_t acc_phase = 0;
     const int flags = p.flags;
+    const long long chunk_rows = static_cast<long long>(p.tiles_m_chunk) * BM;
+    if (p.comm == COMM_AG) {
+      // Push this rank's shard of A into every rank's gather buffer (peer stores over NVLink) while
+      // the main loop already works on the local chunk; then publish "CTA b of rank r is done".
+      const int kv = p.K >> 3;
+      const long long total = chunk_rows * kv;
+      const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+      for (long long v = static_cast<long long>(blockIdx.x) * 128 + et; v < total;
+           v += static_cast<long long>(gridDim.x) * 128) {
+        const long long r = v / kv;
+        const int c = static_cast<int>(v - r * kv) * 8;
+        const uint4 x = *reinterpret_cast<const uint4*>(p.ag_src + r * p.ag_ld + c);
+        for (int q = 0; q < p.ws; ++q)
+          *reinterpret_cast<uint4*>(p.ag_dst[q] + (p.rank * chunk_rows + r) * p.K + c) = x;
+      }
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et < p.ws && et != p.rank) st_release_sys(p.ag_flags[et] + p.rank * 256 + blockIdx.x, p.epoch);
+    }
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      int tm, tn, chunk;
+      tile_coords_p(tile, p, tm, tn, chunk);
       const int m0 = tm * BM, n0 = tn * BN;
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, p.err, 4)) {
         aborted = true;
@@ -236,6 +313,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       tc_fence_after_sync();
       const long long row = m0 + row_in_tile;
       const bool row_ok = row < p.M;
+      const int tile_in_chunk = (tm - chunk * p.tiles_m_chunk) * p.tiles_n + tn;
+      if (p.comm == COMM_RS && chunk == p.rank) {
+        // own rows: every peer's four epilogue warps must have delivered this tile
+        bool ok = true;
+        if (lane < p.ws * 4 && (lane >> 2) != p.rank)
+          ok = wait_flag_ge(p.rs_flags[p.rank] + (static_cast<long long>(tile_in_chunk) * p.ws) * 4 + lane, p.epoch,
+                            p.err, 8);
+        if (!__all_sync(0xffffffffu, ok)) {
+          aborted = true;
+          break;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n0 + c * 32;
@@ -250,7 +339,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
         }
-        if (flags & EPI_BIAS) {
+        if ((flags & EPI_BIAS) && p.comm != COMM_RS) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             if (col0 + j < p.N) {
@@ -318,7 +407,64 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
               }
             }
           }
-          if (flags & EPI_OUT_F32) {
+          if (p.comm == COMM_RS) {
+            const long long crow = row - chunk * chunk_rows;
+            if (chunk != p.rank) {
+              // partial tile of a peer's rows: store it into that peer's staging slot for this rank
+              __nv_bfloat16* dp = p.rs_stage[chunk] + (p.rank * chunk_rows + crow) * p.N + col0;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (col0 + j < p.N) {
+                  uint4 o;
+                  o.x = pack_bf16x2(v[j], v[j + 1]);
+                  o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                  o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                  o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                  *reinterpret_cast<uint4*>(dp + j) = o;
+                }
+              }
+            } else {
+              for (int sr = 0; sr < p.ws; ++sr) {
+                if (sr == p.rank) continue;
+                const __nv_bfloat16* sp = p.rs_stage[p.rank] + (sr * chunk_rows + crow) * p.N + col0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  if (col0 + j < p.N) {
+                    const uint4 a = *reinterpret_cast<const uint4*>(sp + j);
+                    const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y),
+                                 x2 = unpack_bf16x2(a.z), x3 = unpack_bf16x2(a.w);
+                    v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
+                    v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
+                  }
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (col0 + j < p.N) {
+                  if (flags & EPI_BIAS) {
+                    const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + j));
+                    const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y),
+                                 b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+                    v[j + 0] += b0.x; v[j + 1] += b0.y; v[j + 2] += b1.x; v[j + 3] += b1.y;
+                    v[j + 4] += b2.x; v[j + 5] += b2.y; v[j + 6] += b3.x; v[j + 7] += b3.y;
+                  }
+                  if (p.residual2 != nullptr) {
+                    const uint4 a = *reinterpret_cast<const uint4*>(p.residual2 + crow * p.ld_res2 + col0 + j);
+                    const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y),
+                                 x2 = unpack_bf16x2(a.z), x3 = unpack_bf16x2(a.w);
+                    v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
+                    v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
+                  }
+                  uint4 o;
+                  o.x = pack_bf16x2(v[j], v[j + 1]);
+                  o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                  o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                  o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + crow * p.ldc + col0 + j) = o;
+                }
+              }
+            }
+          } else if (flags & EPI_OUT_F32) {
             float* cp = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
@@ -354,6 +500,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           }
         }
       }
+      if (p.comm == COMM_RS && chunk != p.rank) {
+        // this warp's 32 rows of the tile are in the peer's memory: publish them
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0)
+          st_release_sys(p.rs_flags[chunk] + (static_cast<long long>(tile_in_chunk) * p.ws + p.rank) * 4 + quad,
+                         p.epoch);
+      }
       // This warp is done reading the accumulator: hand it back to the MMA issuer.
       tc_fence_before_sync();
       __syncwarp();
@@ -381,8 +535,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                       cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2,
+                       const GemmParams& p, cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
   static bool configured = false;
@@ -393,31 +547,38 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, GEMM_THREADS, L::DYN_BYTES, stream>>>(tmA, tmB, p);
+  kern<<<grid, GEMM_THREADS, L::DYN_BYTES, stream>>>(tmA, tmB, tmA2, p);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
 
 template <int BN, int STAGES>
 static int dispatch_layout(int transA, int transB, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                           const GemmParams& p, cudaStream_t stream) {
-  if (!transA && !transB) return launch_gemm<BN, STAGES, false, false>(tmA, tmB, p, stream);
-  if (!transA && transB) return launch_gemm<BN, STAGES, false, true>(tmA, tmB, p, stream);
-  if (transA && !transB) return launch_gemm<BN, STAGES, true, false>(tmA, tmB, p, stream);
-  return launch_gemm<BN, STAGES, true, true>(tmA, tmB, p, stream);
+                           const CUtensorMap& tmA2, const GemmParams& p, cudaStream_t stream) {
+  if (!transA && !transB) return launch_gemm<BN, STAGES, false, false>(tmA, tmB, tmA2, p, stream);
+  if (!transA && transB) return launch_gemm<BN, STAGES, false, true>(tmA, tmB, tmA2, p, stream);
+  if (transA && !transB) return launch_gemm<BN, STAGES, true, false>(tmA, tmB, tmA2, p, stream);
+  return launch_gemm<BN, STAGES, true, true>(tmA, tmB, tmA2, p, stream);
 }
 
 }  // namespace nx
 
-// C[M,N] = epilogue(op(A) * op(B)).  Leading dimensions in elements.  bias/aux/residual may be
-// null when their flag is clear.  ld_aux is the leading dimension shared by aux_in, aux_out
-// and residual.  Returns an NxStatus.
-NX_API int nx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
-                        long long ldb, long long ldc, int transA, int transB, const void* bias,
-                        const void* aux_in, void* aux_out, const void* residual, long long ld_aux,
-                        int flags, float alpha, void* stream_) {
+struct CommArgs {
+  int mode = 0, rank = 0, ws = 1;
+  unsigned int epoch = 0;
+  const unsigned long long* data_ptrs = nullptr;  // per rank: RS staging area / AG gather buffer
+  const unsigned long long* flag_ptrs = nullptr;  // per rank: flag array of that mode
+  const void* residual2 = nullptr;
+  long long ld_res2 = 0;
+  const void* ag_src = nullptr;
+  long long ag_ld = 0;
+};
+
+static int gemm_common(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                       long long ldc, int transA, int transB, const void* bias, const void* aux_in, void* aux_out,
+                       const void* residual, long long ld_aux, int flags, float alpha, const CommArgs& ca,
+                       cudaStream_t stream) {
   using namespace nx;
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return NX_OK;
   NX_REQUIRE(K > 0, "gemm: K must be positive");
   NX_REQUIRE(N % 8 == 0, "gemm: N (%d) must be a multiple of 8", N);
@@ -430,7 +591,38 @@ NX_API int nx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   if (flags & EPI_RESIDUAL) NX_REQUIRE(residual != nullptr && ld_aux % 8 == 0, "gemm: residual");
 
   const int BN = (N <= 128) ? 128 : 256;
-  CUtensorMap tmA, tmB;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.comm = ca.mode;
+  if (ca.mode != COMM_NONE) {
+    NX_REQUIRE(ca.ws >= 2 && ca.ws <= 8 && ca.rank >= 0 && ca.rank < ca.ws, "gemm_comm: bad rank/world %d/%d", ca.rank, ca.ws);
+    NX_REQUIRE(!transA, "gemm_comm: A must be row-major [M, K]");
+    NX_REQUIRE(M % (ca.ws * BM) == 0, "gemm_comm: M (%d) must be a multiple of ws * %d", M, BM);
+    NX_REQUIRE(!(flags & (EPI_OUT_F32 | EPI_ACCUM)), "gemm_comm: fp32 / accumulate outputs are not supported");
+    NX_REQUIRE(ca.data_ptrs != nullptr && ca.flag_ptrs != nullptr, "gemm_comm: null peer tables");
+    p.rank = ca.rank; p.ws = ca.ws; p.epoch = ca.epoch;
+    p.tiles_m_chunk = (M / ca.ws) / BM;
+    for (int i = 0; i < ca.ws; ++i) {
+      if (ca.mode == COMM_RS) {
+        p.rs_stage[i] = reinterpret_cast<__nv_bfloat16*>(ca.data_ptrs[i]);
+        p.rs_flags[i] = reinterpret_cast<uint32_t*>(ca.flag_ptrs[i]);
+      } else {
+        p.ag_dst[i] = reinterpret_cast<__nv_bfloat16*>(ca.data_ptrs[i]);
+        p.ag_flags[i] = reinterpret_cast<uint32_t*>(ca.flag_ptrs[i]);
+      }
+    }
+    p.residual2 = static_cast<const __nv_bfloat16*>(ca.residual2);
+    p.ld_res2 = ca.ld_res2;
+    p.ag_src = static_cast<const __nv_bfloat16*>(ca.ag_src);
+    p.ag_ld = ca.ag_ld;
+    if (ca.mode == COMM_RS && ca.residual2 != nullptr) NX_REQUIRE(ca.ld_res2 % 8 == 0, "gemm_comm: residual2 ld");
+    if (ca.mode == COMM_AG) {
+      NX_REQUIRE(ca.ag_src != nullptr && ca.ag_ld % 8 == 0 && K % 8 == 0 && lda == K,
+                 "gemm_comm: all-gather mode needs a dense [M, K] gather buffer and an aligned shard");
+      NX_REQUIRE(sm_count() <= 256, "gemm_comm: flag table holds 256 CTAs per rank");
+    }
+  }
+  CUtensorMap tmA, tmB, tmA2;
   bool ok;
   if (!transA) ok = make_tma_2d(&tmA, A, M, K, lda * 2, BM, BK, 2);
   else         ok = make_tma_2d(&tmA, A, K, M, lda * 2, BK, 64, 2);
@@ -438,8 +630,10 @@ NX_API int nx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   if (!transB) ok = make_tma_2d(&tmB, B, N, K, ldb * 2, BN, BK, 2);
   else         ok = make_tma_2d(&tmB, B, K, N, ldb * 2, BK, 64, 2);
   if (!ok) return NX_ERR_ARG;
-
-  GemmParams p;
+  tmA2 = tmA;
+  if (ca.mode == COMM_AG) {
+    if (!make_tma_2d(&tmA2, ca.ag_src, M / ca.ws, K, ca.ag_ld * 2, BM, BK, 2)) return NX_ERR_ARG;
+  }
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -452,6 +646,44 @@ NX_API int nx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;
   p.err = device_error_word();
-  if (BN == 128) return dispatch_layout<128, 6>(transA, transB, tmA, tmB, p, stream);
-  return dispatch_layout<256, 4>(transA, transB, tmA, tmB, p, stream);
+  if (BN == 128) return dispatch_layout<128, 6>(transA, transB, tmA, tmB, tmA2, p, stream);
+  return dispatch_layout<256, 4>(transA, transB, tmA, tmB, tmA2, p, stream);
+}
+
+// C[M,N] = epilogue(op(A) * op(B)).  Leading dimensions in elements.  bias/aux/residual may be
+// null when their flag is clear.  ld_aux is the leading dimension shared by aux_in, aux_out
+// and residual.  Returns an NxStatus.
+NX_API int nx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                        long long ldb, long long ldc, int transA, int transB, const void* bias,
+                        const void* aux_in, void* aux_out, const void* residual, long long ld_aux,
+                        int flags, float alpha, void* stream_) {
+  CommArgs ca;
+  return gemm_common(A, B, C, M, N, K, lda, ldb, ldc, transA, transB, bias, aux_in, aux_out, residual, ld_aux,
+                     flags, alpha, ca, static_cast<cudaStream_t>(stream_));
+}
+
+// Number of CTAs the GEMM of this shape launches (the all-gather mode's flag count per source rank).
+NX_API int nx_gemm_grid(int M, int N) {
+  const int BN = (N <= 128) ? 128 : 256;
+  const long long tiles = static_cast<long long>((M + nx::BM - 1) / nx::BM) * ((N + BN - 1) / BN);
+  return static_cast<int>(tiles < nx::sm_count() ? tiles : nx::sm_count());
+}
+
+// GEMM fused with its tensor-parallel collective over peer memory (mode 1: GEMM -> reduce-scatter of
+// the rows, C = this rank's [M/ws, N] slice, bias / residual2 applied after the reduction;
+// mode 2: all-gather of the rows of A -> GEMM, A = this rank's dense [M, K] gather buffer, ag_src =
+// this rank's [M/ws, K] shard).  data_ptrs / flag_ptrs: per-rank addresses (as mapped on this
+// rank) of the staging / gather area and of its flag array; epoch: this call's flag value.
+NX_API int nx_gemm_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                             long long ldb, long long ldc, int transB, const void* bias, const void* aux_in,
+                             void* aux_out, const void* residual, long long ld_aux, int flags, int mode,
+                             int rank, int ws, unsigned int epoch, const unsigned long long* data_ptrs,
+                             const unsigned long long* flag_ptrs, const void* residual2, long long ld_res2,
+                             const void* ag_src, long long ag_ld, void* stream_) {
+  CommArgs ca;
+  ca.mode = mode; ca.rank = rank; ca.ws = ws; ca.epoch = epoch;
+  ca.data_ptrs = data_ptrs; ca.flag_ptrs = flag_ptrs;
+  ca.residual2 = residual2; ca.ld_res2 = ld_res2; ca.ag_src = ag_src; ca.ag_ld = ag_ld;
+  return gemm_common(A, B, C, M, N, K, lda, ldb, ldc, 0, transB, bias, aux_in, aux_out, residual, ld_aux, flags,
+                     1.0f, ca, static_cast<cudaStream_t>(stream_));
 }

@@ -100,6 +100,10 @@ def _initialize_distributed(neox_args):
     else:
         mpu.initialize_model_parallel(mp, topology=topo, fp32_allreduce=neox_args.fp32_allreduce,
                                       expert_parallel_size=neox_args.moe_expert_parallel_size)
+    if collectives.get_mode() == "fused" and mp > 1 and torch.cuda.is_available():
+        # symmetric workspace + peer mappings of the tensor-parallel group (collective call)
+        from .comm import symm
+        symm.init_group(mpu.get_model_parallel_group())
     if neox_args.rank in (0, None):
         print(f"> topology: pipe {pp} x data {dp} x model {mp} (expert-parallel "
               f"{mpu.get_expert_parallel_world_size()})", flush=True)
