@@ -415,8 +415,27 @@ class ParallelTransformerLayer(nn.Module):
                                          self.post_attention_layernorm.bias, self.input_layernorm.eps)
             else:
                 x1, x2 = self.input_layernorm(x), self.post_attention_layernorm(x)
-            fast = (p == 0.0 and ws == 1 and x.is_cuda and self.num_experts <= 1 and not self.use_cache
-                    and isinstance(self.mlp, ParallelMLP) and self.mlp._fusable(x2))
+            fusable = (p == 0.0 and x.is_cuda and self.num_experts <= 1 and not self.use_cache
+                       and isinstance(self.mlp, ParallelMLP) and self.mlp._fusable(x2))
+            fast = fusable and ws == 1
+            if fusable and self.sequence_parallel:
+                from ..ops import fused_tp
+                be = fused_tp.backend(x, mpu.get_model_parallel_group())
+                m_full = x.shape[0] * x.shape[1] * ws
+                if be is not None and be.can_fuse(m_full, x.shape[-1], x.shape[-1]) and \
+                        be.can_fuse(m_full, x.shape[-1], self.mlp.linear1.output_size_per_partition):
+                    # Tensor + sequence parallel block with every collective inside a GEMM kernel:
+                    # QKV and MLP-up gather their input shards in front of the GEMM; the attention
+                    # output stays a partial sum and rides as a residual of the MLP-down GEMM, whose
+                    # epilogue does the block's single reduce-scatter, then adds biases and x.
+                    attn_partial, b_attn = self.attention(x1, attention_mask, layer_past=layer_past)
+                    b_mlp = self.mlp.linear2.bias
+                    bias_total = _sum_bias(b_attn, b_mlp)
+                    if bias_total is not None:
+                        bias_total = bias_total * ws      # added on every rank before the reduction
+                    kind = "tanh" if self.mlp.bias_gelu_fusion else "erf"
+                    return fused_tp.mlp_gelu_sp(x2, self.mlp.linear1.weight, self.mlp.linear1.bias,
+                                                self.mlp.linear2.weight, attn_partial, bias_total, residual, kind, be)
             if fast:
                 # x + attn + b_attn + mlp + b_mlp with both adds of matrices inside GEMM epilogues:
                 #   t = dense(ctx) + x ;  out = linear2(h) + t ; the two bias vectors are added once.

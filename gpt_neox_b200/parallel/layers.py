@@ -25,6 +25,13 @@ from .random import get_cuda_rng_tracker
 from .utils import VocabUtility, divide
 
 
+def _fused_backend(x):
+    """Symmetric-memory backend of the tensor-parallel group when the fused communication mode
+    applies to ``x`` (CUDA bf16), else None."""
+    from ..ops.fused_tp import backend
+    return backend(x, mpu.get_model_parallel_group())
+
+
 def _device(neox_args):
     if getattr(neox_args, "use_cpu_initialization", False) or not torch.cuda.is_available():
         return torch.device("cpu")
@@ -173,12 +180,19 @@ class ColumnParallelLinear(nn.Module):
     def forward(self, input_):
         if self.use_mup and self.mup_rescale_parameters:
             input_ = input_ / self.width_mult()
-        if self.sequence_parallel:
-            input_parallel = gather_from_sequence_parallel_region(input_, seq_dim=self.seq_dim)
-        else:
-            input_parallel = copy_to_model_parallel_region(input_)
         bias = self.bias if not self.skip_bias_add else None
-        output_parallel = linear_op(input_parallel, self.weight, bias)
+        be = _fused_backend(input_) if (self.sequence_parallel and self.seq_dim == 0) else None
+        if be is not None and be.can_fuse(input_.numel() // input_.shape[-1] * be.ws, self.input_size,
+                                          self.output_size_per_partition):
+            # all-gather of the sequence shards fused into the GEMM (peer stores over NVLink)
+            from ..ops.fused_tp import ag_linear
+            output_parallel = ag_linear(input_, self.weight, bias, be)
+        else:
+            if self.sequence_parallel:
+                input_parallel = gather_from_sequence_parallel_region(input_, seq_dim=self.seq_dim)
+            else:
+                input_parallel = copy_to_model_parallel_region(input_)
+            output_parallel = linear_op(input_parallel, self.weight, bias)
         output = gather_from_model_parallel_region(output_parallel) if self.gather_output else output_parallel
         return output, (self.bias if self.skip_bias_add else None)
 
@@ -227,6 +241,15 @@ class RowParallelLinear(nn.Module):
         if self.use_mup and self.mup_rescale_parameters:
             input_ = input_ / self.width_mult()
         input_parallel = input_ if self.input_is_parallel else scatter_to_model_parallel_region(input_)
+        be = _fused_backend(input_parallel) if (self.sequence_parallel and not self.parallel_output
+                                                and self.seq_dim == 0) else None
+        if be is not None and be.can_fuse(input_parallel.numel() // input_parallel.shape[-1],
+                                          self.input_size_per_partition, self.output_size):
+            # reduce-scatter fused into the GEMM epilogue; a bias that is not skipped is added after it
+            from ..ops.fused_tp import linear_rs
+            b = self.bias if not self.skip_bias_add else None
+            out = linear_rs(input_parallel, self.weight, b, None, be)
+            return out, (self.bias if self.skip_bias_add else None)
         output_parallel = linear_op(input_parallel, self.weight, None)
         if self.sequence_parallel and not self.parallel_output:
             output_ = reduce_scatter_to_sequence_parallel_region(output_parallel, seq_dim=self.seq_dim)

@@ -1,0 +1,41 @@
+"""Multi-GPU checks (need >= 2 GPUs; each case is a torchrun child job): the fused NVLink
+communication mode must reproduce the NCCL baseline's loss curve."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from common import free_port
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(nproc, *args, timeout=600):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+           os.path.join(HERE, "mgpu", "train_losses.py"), *map(str, args)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("LOSSES ")][-1]
+    return json.loads(line[len("LOSSES "):])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tp2_sp_matches_nccl_baseline():
+    base = _run(2, "nccl_baseline", 2, 1, 6)
+    fused = _run(2, "fused", 2, 1, 6)
+    assert base["device_error"] == 0 and fused["device_error"] == 0
+    assert fused["losses"] == pytest.approx(base["losses"], rel=2e-2)
+    assert fused["losses"][-1] < fused["losses"][0]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_dp2_zero1_trains():
+    opt = {"optimizer": {"type": "Adam", "params": {"lr": 3e-4, "betas": [0.9, 0.95], "eps": 1e-8}}}
+    two = _run(2, "fused", 1, 0, 10, json.dumps(opt))
+    assert two["device_error"] == 0
+    assert min(two["losses"][4:]) < two["losses"][0]
