@@ -40,7 +40,8 @@ class FlatGroup:
         self.dp_group, self.dp_size, self.dp_rank = dp_group, dp_size, dp_rank
         self.zero_stage = zero_stage
         order = sorted(range(len(entries)), key=lambda i: (0 if entries[i][1] > 0 else 1,
-                                                            1 if _is_replicated(entries[i][0]) else 0))
+                                                            1 if _is_replicated(entries[i][0]) else 0,
+                                                            1 if getattr(entries[i][0], "_norm_skip", False) else 0))
         self.params = [entries[i][0] for i in order]
         self.wds = [entries[i][1] for i in order]
         self.device = self.params[0].device
@@ -63,7 +64,7 @@ class FlatGroup:
         # regions of constant (weight decay, replicated)
         self.regions = []
         for p, o, wd in zip(self.params, offs, self.wds):
-            key = (wd, _is_replicated(p))
+            key = (wd, _is_replicated(p), bool(getattr(p, "_norm_skip", False)))
             end = o + (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
             if self.regions and self.regions[-1][2:] == key and self.regions[-1][1] == o:
                 self.regions[-1] = (self.regions[-1][0], end) + key
@@ -80,12 +81,12 @@ class FlatGroup:
             self.master = self.flat_lp[s:e].float()
         self.exp_avg = torch.zeros(self.shard_size, dtype=torch.float32, device=self.device)
         self.exp_avg_sq = torch.zeros(self.shard_size, dtype=torch.float32, device=self.device)
-        # my shard's intersections with the regions: (lo, hi, wd, replicated), shard-relative
+        # my shard's intersections with the regions: (lo, hi, wd, replicated, norm_skip), shard-relative
         self.segments = []
-        for (a, b, wd, rep) in self.regions:
+        for (a, b, wd, rep, skip) in self.regions:
             lo, hi = max(a, s), min(b, e)
             if hi > lo:
-                self.segments.append((lo - s, hi - s, wd, rep))
+                self.segments.append((lo - s, hi - s, wd, rep, skip))
 
     def numel(self):
         return sum(p.numel() for p in self.params)
@@ -173,7 +174,7 @@ class FlatAdam:
             self._seg_params = []
             pgs = []
             for g in groups:
-                for (lo, hi, wd, _rep) in g.segments:
+                for (lo, hi, wd, _rep, _skip) in g.segments:
                     sp = torch.nn.Parameter(g.master[lo:hi], requires_grad=True)
                     self._seg_params.append((g, lo, hi, sp))
                     pgs.append({"params": [sp], "weight_decay": wd})
@@ -204,7 +205,7 @@ class FlatAdam:
         for g in self.groups:
             gs = g.grad_shard()
             lp_shard = g.flat_lp[g.shard_start:g.shard_start + g.shard_size] if g.lp_dtype != torch.float32 else None
-            for (lo, hi, wd, _rep) in g.segments:
+            for (lo, hi, wd, _rep, _skip) in g.segments:
                 optim_ops.adamw_step_(g.master[lo:hi], g.exp_avg[lo:hi], g.exp_avg_sq[lo:hi], gs[lo:hi],
                                       lp_shard[lo:hi] if lp_shard is not None else None,
                                       lr=lr, beta1=b1, beta2=b2, eps=eps, weight_decay=wd, step=self.step_count,
@@ -345,9 +346,9 @@ class Engine(torch.nn.Module):
         tp_rank0 = mpu.get_model_parallel_rank() == 0
         for g in self.groups:
             gs = g.grad_shard()
-            for (lo, hi, _wd, rep) in g.segments:
-                if rep and not tp_rank0:
-                    continue
+            for (lo, hi, _wd, rep, skip) in g.segments:
+                if skip or (rep and not tp_rank0):
+                    continue   # counted by another owner (tensor-parallel replica / tied pipeline copy)
                 optim_ops.sumsq_(gs[lo:hi], self._acc)
         if dist.is_initialized() and dist.get_world_size() > 1:
             dist.all_reduce(self._acc[0:1])

@@ -160,12 +160,26 @@ class GPT2ModelPipe(nn.Module):
                                         parallel_output=self.parallel_output, is_last_layer=True))
 
     # ------------------------------------------------------------------ building
+    def _seed_layer(self, idx):
+        """With ``use_cpu_initialization`` every layer is drawn from its own seed, so the weights do
+        not depend on how the layer list is cut into pipeline stages."""
+        if getattr(self.neox_args, "use_cpu_initialization", False):
+            torch.manual_seed(self.neox_args.seed * 1000 + idx)
+
     def _build_one(self, spec, idx):
         """-> (callable, module-or-None) for spec ``idx``."""
+        self._seed_layer(idx)
         if isinstance(spec, TiedLayerSpec):
+            # every owner of a tied module must start from the same weights: seed by its first occurrence
+            first = next(i for i, sp in enumerate(self.specs) if getattr(sp, "key", None) == spec.key)
+            self._seed_layer(first)
             if spec.key not in self.tied_modules:
                 self.tied_modules[spec.key] = spec.build()
                 self.tied_specs[spec.key] = spec
+                if idx != first:
+                    # a later pipeline stage's copy: the first owner counts it in the gradient norm
+                    for p_ in self.tied_modules[spec.key].parameters():
+                        p_._norm_skip = True
             mod = self.tied_modules[spec.key]
             if spec.forward_fn is not None:
                 return partial(spec.forward_fn, mod), None
@@ -265,7 +279,8 @@ class GPT2ModelPipe(nn.Module):
         """Flatten into a ``SequentialWrapper`` (used when ``pipe_parallel_size == 0``)."""
         layers = []
         tied_layers = {}
-        for spec in self.specs:
+        for idx, spec in enumerate(self.specs):
+            self._seed_layer(idx)
             if isinstance(spec, TiedLayerSpec):
                 if spec.key in tied_layers:
                     layers.append(Lambda(partial(spec.forward_fn, tied_layers[spec.key][0])))

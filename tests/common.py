@@ -59,9 +59,13 @@ def run_distributed(fn, world_size, *args, timeout=240):
     for p in hung:
         p.kill()
     assert not hung, f"{len(hung)} rank(s) hung for more than {timeout}s"
-    out = []
+    out, errors = [], []
     for r in range(world_size):
         status, val = ret.get(r, ("err", "no result (process died)"))
-        assert status == "ok", f"rank {r} failed:\n{val}"
+        if status != "ok":
+            errors.append(f"--- rank {r} failed:\n{val}")
         out.append(val)
+    # a rank that dies takes its peers' connections down: show the failure that is not a lost connection first
+    errors.sort(key=lambda e: "Connection closed by peer" in e or "Connection reset" in e)
+    assert not errors, "\n".join(errors)
     return out

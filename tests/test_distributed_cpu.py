@@ -75,3 +75,23 @@ def test_tp2_x_dp2_world4():
     out = run_distributed(_train, 4, dict(cfg, model_parallel_size=2, sequence_parallel=True,
                                           make_vocab_size_divisible_by=128), 3)
     assert out[0] == pytest.approx(ref, rel=5e-5)
+
+
+def test_pipeline_parallel_2_matches_sequential():
+    """1F1B over two stages (4 micro-batches) reproduces the unpipelined loss curve."""
+    cfg = tiny_config(use_cpu_initialization=True, num_layers=4, train_micro_batch_size_per_gpu=2,
+                      gradient_accumulation_steps=4)
+    ref = _single(cfg, 4)
+    out = run_distributed(_train, 2, dict(cfg, pipe_parallel_size=2), 4)
+    assert out[0] == pytest.approx(out[1], rel=1e-6)
+    assert out[0] == pytest.approx(ref, rel=5e-5)
+
+
+def test_pipeline_2_x_tensor_2_with_tied_embeddings():
+    cfg = tiny_config(use_cpu_initialization=True, num_layers=4, train_micro_batch_size_per_gpu=2,
+                      gradient_accumulation_steps=2, no_weight_tying=False, make_vocab_size_divisible_by=256,
+                      use_bias_in_attn_linear=False, use_bias_in_mlp=False)
+    ref = _single(cfg, 3)
+    out = run_distributed(_train, 4, dict(cfg, pipe_parallel_size=2, model_parallel_size=2,
+                                          make_vocab_size_divisible_by=128), 3)
+    assert out[0] == pytest.approx(ref, rel=5e-5)
