@@ -95,3 +95,13 @@ def test_pipeline_2_x_tensor_2_with_tied_embeddings():
     out = run_distributed(_train, 4, dict(cfg, pipe_parallel_size=2, model_parallel_size=2,
                                           make_vocab_size_divisible_by=128), 3)
     assert out[0] == pytest.approx(ref, rel=5e-5)
+
+
+def test_moe_expert_parallel_2_matches_single_rank():
+    """Dropless MoE with all-to-all dispatch over 2 expert-parallel ranks == the single-rank MoE."""
+    cfg = tiny_config(use_cpu_initialization=True, gpt_j_residual=False, moe_num_experts=4, moe_top_k=2,
+                      moe_router_type="topk", moe_expert_interval=1, train_micro_batch_size_per_gpu=2)
+    ref = _single(dict(cfg, train_micro_batch_size_per_gpu=4), 3)
+    out = run_distributed(_train, 2, dict(cfg, moe_expert_parallel_size=2), 3)
+    assert out[0] == pytest.approx(out[1], rel=1e-6)
+    assert out[0] == pytest.approx(ref, rel=1e-4)
