@@ -259,14 +259,24 @@ class Engine(torch.nn.Module):
             for p in pg["params"]:
                 (expert if getattr(p, "expert_parallel", False) else dense).append((p, wd))
         self.groups = []
-        if dense:
-            self.groups.append(FlatGroup(dense, mpu.get_data_parallel_group(), mpu.get_data_parallel_world_size(),
-                                         mpu.get_data_parallel_rank(), self.zero_stage, grad_dtype))
-        if expert:
+        # one flat space per (reduction group, parameter dtype): parameters deliberately kept in fp32
+        # inside a bf16 model (Mamba's A_log / D) keep their precision
+        def by_dtype(entries):
+            out = {}
+            for e in entries:
+                out.setdefault(e[0].dtype, []).append(e)
+            return [out[k] for k in sorted(out, key=lambda d: (d != a.params_dtype, str(d)))]
+
+        for ents in by_dtype(dense):
+            gd = torch.float32 if ents[0][0].dtype == torch.float32 else grad_dtype
+            self.groups.append(FlatGroup(ents, mpu.get_data_parallel_group(), mpu.get_data_parallel_world_size(),
+                                         mpu.get_data_parallel_rank(), self.zero_stage, gd))
+        for ents in by_dtype(expert):
             ep = mpu.get_expert_parallel_world_size()
-            self.groups.append(FlatGroup(expert, mpu.get_expert_data_parallel_group(),
+            gd = torch.float32 if ents[0][0].dtype == torch.float32 else grad_dtype
+            self.groups.append(FlatGroup(ents, mpu.get_expert_data_parallel_group(),
                                          mpu.get_data_parallel_world_size() // ep,
-                                         mpu.get_data_parallel_rank() // ep, self.zero_stage, grad_dtype))
+                                         mpu.get_data_parallel_rank() // ep, self.zero_stage, gd))
         self.optimizer = None
         if optimizer_cfg is not None and self.groups:
             self.optimizer = FlatAdam(self.groups, **optimizer_cfg, **(generic_optimizer or {}))

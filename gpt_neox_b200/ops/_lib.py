@@ -61,6 +61,15 @@ def _declare(lib):
     sig("nx_adamw_step", [P, P, P, P, P, L, F, F, F, F, F, F, F, I, P, P, I, P])
     sig("nx_sumsq", [P, L, P, I, P])
     sig("nx_clip_coef", [P, F, F, P, P, P])
+    sig("nx_conv1d_silu_fwd", [P, L, L, P, P, P, L, L, I, I, I, I, P])
+    sig("nx_conv1d_silu_bwd", [P, L, L, P, P, P, L, L, P, L, L, P, P, I, I, I, I, P])
+    sig("nx_scan_chunks", [I])
+    sig("nx_scan_channel_blocks", [I])
+    sig("nx_selective_scan_fwd", [P, L, L, P, L, L, P, L, L, P, L, L, P, L, L, P, P, P, P, L, L, P, P, P, I, I, I, P])
+    sig("nx_selective_scan_bwd", [P, L, L, P, L, L, P, L, L, P, L, L, P, L, L, P, P, P, P, L, L, P, P, P, L, L, P, P,
+                                  P, P, P, P, P, I, I, I, P])
+    sig("nx_wkv6_chunks", [I])
+    sig("nx_wkv6_pass", [I, P, P, P, P, L, L, P, P, L, L, I, P, P, P, I, I, I, I, P])
     sig("nx_rope", [P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, I, I, P])
     sig("nx_embedding_fwd", [P, P, P, L, I, L, L, P])
     sig("nx_embedding_bwd", [P, P, P, L, I, L, L, P])
