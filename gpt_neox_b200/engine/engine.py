@@ -174,6 +174,15 @@ class FlatAdam:
             self._seg_params = []
             pgs = []
             for g in groups:
+                if not g.sharded:
+                    # whole parameters are local: give the optimizer their true shapes (SM3's covers
+                    # depend on them); under ZeRO sharding it sees flat 1-D segments, as a flattened
+                    # ZeRO partition would present them
+                    for p, o, wd in zip(g.params, g.offsets, g.wds):
+                        sp = torch.nn.Parameter(g.master[o:o + p.numel()].view(p.shape), requires_grad=True)
+                        self._seg_params.append((g, o, o + p.numel(), sp))
+                        pgs.append({"params": [sp], "weight_decay": wd})
+                    continue
                 for (lo, hi, wd, _rep, _skip) in g.segments:
                     sp = torch.nn.Parameter(g.master[lo:hi], requires_grad=True)
                     self._seg_params.append((g, lo, hi, sp))
@@ -196,7 +205,7 @@ class FlatAdam:
             for pg in self.generic.param_groups:
                 pg["lr"] = lr
             for (g, lo, hi, sp) in self._seg_params:
-                sp.grad = g.grad_shard()[lo:hi].float() * grad_scale[0]
+                sp.grad = (g.grad_shard()[lo:hi].float() * grad_scale[0]).view(sp.shape)
             self.generic.step()
             for g in self.groups:
                 if g.lp_dtype != torch.float32:

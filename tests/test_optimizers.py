@@ -1,0 +1,70 @@
+"""SM3 / MADGRAD-WD / Lion: closed-form single steps and a convex problem (reference: megatron/optimizers.py)."""
+import pytest
+import torch
+
+from gpt_neox_b200.optimizers import SM3, Lion, madgrad_wd
+
+
+def _quad(opt_cls, steps=200, **kw):
+    torch.manual_seed(0)
+    w = torch.nn.Parameter(torch.randn(6, 5))
+    tgt = torch.randn(6, 5)
+    opt = opt_cls([w], **kw)
+    first = None
+    for _ in range(steps):
+        opt.zero_grad()
+        loss = ((w - tgt) ** 2).sum()
+        loss.backward()
+        opt.step()
+        first = first if first is not None else loss.item()
+    return first, loss.item()
+
+
+@pytest.mark.parametrize("cls,kw", [(SM3, dict(lr=0.1)), (SM3, dict(lr=0.1, momentum=0.9, beta=0.5)),
+                                    (madgrad_wd, dict(lr=0.05)), (madgrad_wd, dict(lr=0.05, momentum=0.0)),
+                                    (Lion, dict(lr=0.01))])
+def test_optimizers_minimise_a_quadratic(cls, kw):
+    first, last = _quad(cls, **kw)
+    assert last < 0.05 * first
+
+
+def test_lion_single_step_closed_form():
+    w = torch.nn.Parameter(torch.tensor([1.0, -2.0, 3.0]))
+    w.grad = torch.tensor([0.5, -0.5, 0.0])
+    Lion([w], lr=0.1, betas=(0.9, 0.99), weight_decay=0.1).step()
+    exp = torch.tensor([1.0, -2.0, 3.0]) * (1 - 0.01) - 0.1 * torch.tensor([1.0, -1.0, 0.0])
+    torch.testing.assert_close(w.data, exp)
+
+
+def test_sm3_first_step_is_sign_like_and_covers_are_row_col_max():
+    w = torch.nn.Parameter(torch.zeros(2, 3))
+    g = torch.tensor([[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]])
+    w.grad = g.clone()
+    opt = SM3([w], lr=1.0)
+    opt.step()
+    torch.testing.assert_close(w.data, -torch.ones(2, 3))          # g / sqrt(g^2)
+    rows, cols = opt.state[w]["covers"]
+    torch.testing.assert_close(rows.flatten(), torch.tensor([9.0, 36.0]))
+    torch.testing.assert_close(cols.flatten(), torch.tensor([16.0, 25.0, 36.0]))
+
+
+def test_madgrad_first_step_closed_form():
+    w = torch.nn.Parameter(torch.tensor([1.0, 2.0]))
+    g = torch.tensor([0.5, -1.0])
+    w.grad = g.clone()
+    lr, eps, mom = 0.1, 1e-6, 0.9
+    madgrad_wd([w], lr=lr, momentum=mom, eps=eps).step()
+    lam = (lr + eps) * 1.0
+    z = torch.tensor([1.0, 2.0]) - lam * g / ((lam * g * g).pow(1 / 3) + eps)
+    exp = torch.tensor([1.0, 2.0]) * mom + (1 - mom) * z
+    torch.testing.assert_close(w.data, exp)
+
+
+@pytest.mark.parametrize("name,params", [("sm3", {"lr": 0.01}), ("lion", {"lr": 1e-4, "betas": [0.9, 0.99]}),
+                                          ("madgrad_wd", {"lr": 0.01, "momentum": 0.9}), ("sgd", {"lr": 0.01})])
+def test_engine_runs_with_in_tree_optimizers(name, params):
+    from common import run_distributed, tiny_config
+    from test_mamba import _train
+    cfg = tiny_config(use_cpu_initialization=True, optimizer={"type": name, "params": params})
+    losses = run_distributed(_train, 1, cfg, 4)[0]
+    assert all(l == l for l in losses)
