@@ -251,6 +251,8 @@ class ParallelSelfAttention(nn.Module):
             if self.pos_emb == "alibi":
                 s4 = self.alibi_embed(s4)
             mask = attention_mask
+            if mask is not None and (mask.shape[-2] != sq or mask.shape[-1] != sk):
+                mask = mask[..., sk - sq:sk, :sk]        # decoding with a KV cache: rows of the new positions
             if mask is None:
                 qpos = torch.arange(sq, device=q.device)[:, None] + (sk - sq)
                 kpos = torch.arange(sk, device=q.device)[None, :]

@@ -312,7 +312,8 @@ def get_model(neox_args, use_cache=False):
     dev = _device()
     model = model.to(device=dev)
     for p in model.parameters():
-        if p.dtype != neox_args.params_dtype and p.is_floating_point():
+        if p.dtype != neox_args.params_dtype and p.is_floating_point() and \
+                not getattr(p, "_deepspeed_no_cast", False):
             p.data = p.data.to(neox_args.params_dtype)
     for b in model.buffers():
         if b.is_floating_point() and b.dtype != torch.float32:

@@ -1,0 +1,79 @@
+"""Text generation on CPU: sampling filters, stop sequences, and KV-cache decoding == full recompute."""
+import pytest
+import torch
+
+from common import tiny_config
+
+
+def _model(**over):
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    from gpt_neox_b200.initialize import initialize_megatron
+    cfg = tiny_config(use_cpu_initialization=True, attention_config=[[["global"], 2]], **over)
+    a = NeoXArgs.from_dict(cfg)
+    a.configure_distributed_args()
+    a.build_tokenizer()
+    mpu.destroy_model_parallel()
+    initialize_megatron(a)
+    m = training.get_model(a, use_cache=True)
+    return a, m
+
+
+def test_filter_logits_topk_topp():
+    from gpt_neox_b200.text_generation_utils import filter_logits
+    logits = torch.tensor([[1.0, 2.0, 3.0, 4.0], [4.0, 3.0, 2.0, 1.0]])
+    out = filter_logits(logits.clone(), top_k=2)
+    assert torch.isinf(out[0, :2]).all() and torch.isfinite(out[0, 2:]).all()
+    assert torch.isinf(out[1, 2:]).all() and torch.isfinite(out[1, :2]).all()
+    p = torch.tensor([[0.5, 0.3, 0.15, 0.05]]).log()
+    out = filter_logits(p.clone(), top_p=0.7)
+    assert torch.isfinite(out[0, :2]).all() and torch.isinf(out[0, 2:]).all()
+
+
+def test_pad_batch_and_stop_tokens():
+    from gpt_neox_b200.text_generation_utils import pad_batch, stop_tokens_in_completion
+    toks, lens = pad_batch([[1, 2, 3], [4]], pad_id=0, pad_len=5)
+    assert toks == [[1, 2, 3, 0, 0], [4, 0, 0, 0, 0]] and lens == [3, 1]
+    with pytest.raises(ValueError):
+        pad_batch([[1] * 6], pad_id=0, pad_len=5)
+    ctx = torch.tensor([[5, 6, 7, 8, 0]])
+    assert stop_tokens_in_completion([torch.tensor([7, 8])], ctx, 0, 3)
+    assert not stop_tokens_in_completion([torch.tensor([6, 8])], ctx, 0, 3)
+
+
+@pytest.mark.parametrize("over", [dict(), dict(pos_emb="learned"), dict(gpt_j_residual=False, num_kv_heads=2)])
+def test_kv_cache_decoding_matches_recompute(over):
+    from gpt_neox_b200.text_generation_utils import stream_tokens
+    a, m = _model(**over)
+    prompts = [[5, 9, 11, 3], [7, 2]]
+    outs = []
+    for recompute in (True, False):
+        m.inference_mode(use_cache=not recompute)
+        m.clear_cache()
+        last = None
+        for last in stream_tokens(a, m, prompts, maximum_tokens=6, recompute=recompute, eos_token_id=10 ** 6):
+            pass
+        outs.append(last[0][:, :10].clone())
+    assert torch.equal(outs[0], outs[1]), (outs[0], outs[1])
+    assert torch.equal(outs[0][0, :4], torch.tensor([5, 9, 11, 3]))
+
+
+def test_generate_samples_from_prompt_returns_records():
+    from gpt_neox_b200.text_generation_utils import generate_samples_from_prompt
+    a, m = _model()
+    m.inference_mode(use_cache=True)
+
+    class _Tok:
+        eod = 0
+
+        def tokenize(self, s):
+            return [min(ord(c), 99) for c in s] or [0]
+
+        def detokenize(self, ids):
+            return "".join(chr(33 + (i % 60)) for i in ids)
+    a.tokenizer = _Tok()
+    m.clear_cache()
+    out = generate_samples_from_prompt(a, m, ["ab", ""], maximum_tokens=4, temperature=0.8, top_k=5)
+    assert len(out) == 2 and all(set(r) >= {"context", "text", "length", "finished", "message"} for r in out)
+    assert out[0]["length"] <= 4
