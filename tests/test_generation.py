@@ -77,3 +77,36 @@ def test_generate_samples_from_prompt_returns_records():
     out = generate_samples_from_prompt(a, m, ["ab", ""], maximum_tokens=4, temperature=0.8, top_k=5)
     assert len(out) == 2 and all(set(r) >= {"context", "text", "length", "finished", "message"} for r in out)
     assert out[0]["length"] <= 4
+
+
+def test_eval_adapter_loglikelihood_matches_direct_computation():
+    from gpt_neox_b200.eval_tasks import EvalHarnessAdapter
+    a, m = _model()
+
+    class _Tok:
+        eod = 0
+        eod_id = 0
+
+        def tokenize(self, s):
+            return [3 + (ord(c) % 90) for c in s]
+
+        def detokenize(self, ids):
+            return "".join(chr(40 + (i % 50)) for i in ids)
+    a.tokenizer = _Tok()
+    ad = EvalHarnessAdapter(m, None, a, batch_size=2)
+    reqs = [("hello wor", "ld"), ("", "abc"), ("a much longer context string", " x")]
+    got = ad.loglikelihood(reqs)
+    m.inference_mode(use_cache=False)
+    for (ctx, cont), (ll, greedy) in zip(reqs, got):
+        c = [0] if ctx == "" else a.tokenizer.tokenize(ctx)
+        t = a.tokenizer.tokenize(cont)
+        full = torch.tensor([c + t])
+        pos = torch.arange(full.shape[1] - 1)[None]
+        from gpt_neox_b200.utils.common import get_attn_mask
+        with torch.no_grad():
+            logits = m((full[:, :-1], pos, get_attn_mask(full.shape[1] - 1, "cpu", None)))
+        lp = torch.log_softmax(logits.float(), -1)[0, -len(t):]
+        want = lp.gather(1, torch.tensor(t)[:, None]).sum().item()
+        assert ll == pytest.approx(want, rel=1e-4, abs=1e-4)
+        assert greedy == bool((lp.argmax(-1) == torch.tensor(t)).all())
+    assert len(ad.loglikelihood_rolling([("some document text " * 5,)])) == 1
