@@ -1,0 +1,124 @@
+"""Curriculum scheduler, gradient noise scale, weight server, pairwise / online datasets."""
+import pickle
+import socket
+import threading
+
+import numpy as np
+import pytest
+import torch
+
+from common import free_port
+
+
+def test_curriculum_schedules():
+    from gpt_neox_b200.engine.curriculum import CurriculumScheduler
+    lin = CurriculumScheduler({"min_difficulty": 64, "max_difficulty": 1024, "schedule_type": "fixed_linear",
+                               "schedule_config": {"total_curriculum_step": 100, "difficulty_step": 8}})
+    assert lin.update_difficulty(0) == 64
+    mid = lin.update_difficulty(50)
+    assert 64 < mid < 1024 and mid % 8 == 0
+    assert lin.update_difficulty(100) == 1024 and lin.update_difficulty(500) == 1024
+    root = CurriculumScheduler({"min_difficulty": 64, "max_difficulty": 1024, "schedule_type": "fixed_root",
+                                "schedule_config": {"total_curriculum_step": 100, "difficulty_step": 8,
+                                                    "root_degree": 2}})
+    assert root.get_difficulty(25) > lin.get_difficulty(25)
+    disc = CurriculumScheduler({"min_difficulty": 1, "max_difficulty": 3, "schedule_type": "fixed_discrete",
+                                "schedule_config": {"difficulty": [1, 2, 3], "max_step": [5, 10]}})
+    assert [disc.get_difficulty(s) for s in (1, 5, 6, 10, 11)] == [1, 1, 2, 2, 3]
+
+
+def test_gradient_noise_scale_recovers_known_ratio():
+    """Gradients g = G + noise with known |G|^2 and tr(Sigma): the estimate approaches tr(Sigma)/|G|^2."""
+    from gpt_neox_b200.gradient_noise_scale import GradientNoiseScale
+
+    class _M:
+        stored_gradients = None
+    m = _M()
+    torch.manual_seed(0)
+    dim, bs, sigma = 4000, 8, 2.0
+    G = torch.randn(dim) * 0.5
+    gns = GradientNoiseScale(m, batch_size_small=bs, n_batches=5, beta=0.9)
+    for _ in range(300):
+        m.stored_gradients = [G + torch.randn(dim) * sigma / bs ** 0.5]
+        gns.update()
+    want = dim * sigma ** 2 / float(G.pow(2).sum())
+    assert gns.noise_scale == pytest.approx(want, rel=0.15)
+
+
+def test_weight_server_roundtrip_cpu():
+    from gpt_neox_b200.models import weight_server
+    model = torch.nn.Linear(4, 3)
+    port = free_port()
+    th = threading.Thread(target=weight_server.start_server, args=(model, [port]), kwargs={"accept_timeout_s": 20})
+    th.start()
+    import time
+    got = None
+    for _ in range(100):
+        try:
+            got = weight_server.receive_state_dict(port)
+            break
+        except ConnectionRefusedError:
+            time.sleep(0.05)
+    th.join(20)
+    assert got is not None and set(got) == {"weight", "bias"}
+    torch.testing.assert_close(got["weight"], model.weight.detach())
+
+
+class _Idx:
+    def __init__(self, docs, dtype=np.int64):
+        self.docs = [np.asarray(d, dtype=dtype) for d in docs]
+        self.sizes = np.array([len(d) for d in docs], dtype=np.int32)
+
+    def get(self, i, offset=0, length=None):
+        d = self.docs[i][offset:]
+        return d if length is None else d[:length]
+
+
+def test_pairwise_dataset_pairs_and_pads():
+    from gpt_neox_b200.data.pairwise_dataset import PairwiseDataset
+    pos = _Idx([[1, 2, 3], [4, 5, 6, 7, 8, 9, 10], [11]])
+    neg = _Idx([[21, 22], [24], [31, 32, 33]])
+    lab = _Idx([[-100, 2, 3], [4] * 7, [11]])
+    ds = PairwiseDataset("t", "p", np.arange(3), pos, neg, num_samples=7, seq_length=4, seed=1,
+                         pos_label_dataset=lab, neg_label_dataset=lab)
+    assert len(ds) == 9
+    seen = set()
+    for i in range(3):
+        s = ds[i]
+        assert s["pos"].shape == (5,) and s["neg"].shape == (5,)
+        doc = {1: 0, 4: 1, 11: 2}[int(s["pos"][0])]
+        seen.add(doc)
+        assert int(s["neg"][0]) == [21, 24, 31][doc]
+        assert s["pos_label"][-1] in (-100, 4)
+    assert seen == {0, 1, 2}
+    ds2 = PairwiseDataset("t", "p", np.arange(3), pos, neg, num_samples=2, seq_length=4, seed=1, allow_chopped=False)
+    assert set(ds2.order.tolist()) == {0, 2}
+
+
+def test_online_dataset_fetches_and_centres():
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200.data.online_dataset import OnlineDataset
+    mpu.destroy_model_parallel()
+    mpu.initialize_model_parallel(1)
+    port = free_port()
+    payload = pickle.dumps([{"prefix": [1, 2], "completions": [[3], [4, 5]], "rewards": [1.0, 3.0]}])
+    srv = socket.socket()
+    srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+    srv.bind(("127.0.0.1", port))
+    srv.listen(1)
+
+    def serve():
+        c, _ = srv.accept()
+        assert c.recv(64) == b"train"
+        c.sendall(payload)
+        c.close()
+    th = threading.Thread(target=serve)
+    th.start()
+    ds = OnlineDataset(num_samples=4, seq_length=6, leave_one_out=True, dataserver_ips="127.0.0.1",
+                       dataserver_ports=port)
+    a, b = ds[0], ds[1]
+    th.join(10)
+    srv.close()
+    assert a["text"].tolist() == [1, 2, 3, 0, 0, 0, 0] and a["label"].tolist()[:3] == [-100, -100, 3]
+    assert a["reward"][0] == pytest.approx(-2.0) and b["reward"][0] == pytest.approx(2.0)
+    assert b["raw_reward"][0] == pytest.approx(3.0)
