@@ -141,6 +141,12 @@ def run_local(script, script_args, devices, node_rank, node_sizes, master_addr, 
             e["NEOX_DEVICE_MAP"] = ",".join(str(d) for d in devices)
         cmd = [sys.executable, "-u", script, f"--local_rank={local_rank}"] + list(script_args)
         procs.append(subprocess.Popen(cmd, env=e))
+    pidfile = os.environ.get("NEOX_PIDFILE", f"/tmp/gpt_neox_b200.{os.getuid()}.pids")
+    try:                                   # read by cluster/kill.sh, which ends exactly these processes
+        with open(pidfile, "w") as f:
+            f.write("\n".join(str(p.pid) for p in procs) + "\n")
+    except OSError:
+        pidfile = None
     rc = 0
     alive = list(procs)
     try:
@@ -164,6 +170,8 @@ def run_local(script, script_args, devices, node_rank, node_sizes, master_addr, 
             p.wait(timeout=30)
         except subprocess.TimeoutExpired:
             p.kill()
+    if pidfile and os.path.exists(pidfile):
+        os.remove(pidfile)
     return rc
 
 
