@@ -38,6 +38,9 @@ def parse():
     p.add_argument("--gas", type=int, default=None, help="override gradient accumulation steps")
     p.add_argument("--mode", type=str, default="fused", choices=("fused", "nccl_baseline"))
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--kernel-table", type=str, default=None,
+                   help="after the timed regions, run one more (untimed) step under torch.profiler and write the "
+                        "per-kernel device-time table of rank 0 to this file")
     return p.parse_args()
 
 
@@ -231,6 +234,16 @@ def main():
         e2e = {"value": tokens / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": gas * micro * (seq + 1) * 8, "d2h_bytes_per_step": 4,
                "final_loss": last_loss}
+
+    if args.kernel_table:
+        from torch.profiler import ProfilerActivity, profile
+        barrier_sync()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            run_steps(dit, 1, read_loss=False)
+            torch.cuda.synchronize()
+        if rank == 0:
+            with open(args.kernel_table, "w") as f:
+                f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=60, max_name_column_width=90))
 
     from gpt_neox_b200.ops import _lib
     dev_err = _lib.read_device_error(clear=False)
