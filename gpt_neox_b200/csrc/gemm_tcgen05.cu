@@ -29,7 +29,9 @@ namespace nx {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;   // producer, MMA issuer, 4 epilogue warps, 4 all-gather push warps
+constexpr int RS_ROW_BYTES = 144;    // 64 bf16 columns + 16 B pad: conflict-free 16-byte rows in shared memory
+constexpr int RS_STAGE_BYTES = 4 * 32 * RS_ROW_BYTES;   // one 32-row x 64-column slab per epilogue warp
 
 enum EpiFlags : int {
   EPI_BIAS = 1,         // + bias[n]
@@ -83,7 +85,8 @@ struct SmemLayout {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem base word
-  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  static constexpr int RS_OFFSET = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 8 * 8;   // + 8 chunk-ready barriers
+  static constexpr int TOTAL = RS_OFFSET + RS_STAGE_BYTES;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
 };
 
@@ -131,6 +134,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  // all-gather mode: barrier k completes when the k-th peer chunk (in consumption order) has arrived
+  auto ag_bar = [&](int k) { return bar_base + 8u * (2 * STAGES + 6 + k); };
+  volatile int* ag_abort = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + 8 * (2 * STAGES + 5));
   volatile uint32_t* tmem_slot_gen =
       reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFFSET + 8 * (2 * STAGES + 4));
 
@@ -147,6 +153,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       mbar_init(tmem_full_bar(a), 1);
       mbar_init(tmem_empty_bar(a), 4);  // one arrival per epilogue warp
     }
+    for (int k = 0; k < 8; ++k) mbar_init(ag_bar(k), 4);  // one arrival per push warp
+    *ag_abort = 0;
     fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {
@@ -184,12 +192,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             mapA = &tmA2;
             m0 -= chunk * p.tiles_m_chunk * BM;
           } else if (chunk != ag_ready_chunk) {
-            // peer shard: wait until every CTA of that peer has pushed its part into this GPU's
-            // gather buffer, then make those generic-proxy writes visible to TMA
-            bool ok = true;
-            for (int c = 0; c < static_cast<int>(gridDim.x) && ok; ++c)
-              ok = wait_flag_ge(p.ag_flags[p.rank] + chunk * 256 + c, p.epoch, p.err, 7);
-            if (!ok) {
+            // peer shard: the push warps poll the peer's per-CTA flags in parallel and complete the
+            // chunk's barrier; then make those generic-proxy writes visible to TMA
+            const int order = (chunk - p.rank + p.ws) % p.ws;     // 1 .. ws-1
+            if (!mbar_wait(ag_bar(order - 1), 0, p.err, 7) || *ag_abort) {
               aborted = true;
               break;
             }
@@ -276,7 +282,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     const int row_in_tile = quad * 32 + lane;
@@ -284,24 +290,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     uint32_t acc_phase = 0;
     const int flags = p.flags;
     const long long chunk_rows = static_cast<long long>(p.tiles_m_chunk) * BM;
-    if (p.comm == COMM_AG) {
-      // Push this rank's shard of A into every rank's gather buffer (peer stores over NVLink) while
-      // the main loop already works on the local chunk; then publish "CTA b of rank r is done".
-      const int kv = p.K >> 3;
-      const long long total = chunk_rows * kv;
-      const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
-      for (long long v = static_cast<long long>(blockIdx.x) * 128 + et; v < total;
-           v += static_cast<long long>(gridDim.x) * 128) {
-        const long long r = v / kv;
-        const int c = static_cast<int>(v - r * kv) * 8;
-        const uint4 x = *reinterpret_cast<const uint4*>(p.ag_src + r * p.ag_ld + c);
-        for (int q = 0; q < p.ws; ++q)
-          *reinterpret_cast<uint4*>(p.ag_dst[q] + (p.rank * chunk_rows + r) * p.K + c) = x;
-      }
-      __threadfence_system();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et < p.ws && et != p.rank) st_release_sys(p.ag_flags[et] + p.rank * 256 + blockIdx.x, p.epoch);
-    }
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int tm, tn, chunk;
       tile_coords_p(tile, p, tm, tn, chunk);
@@ -410,18 +398,34 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           if (p.comm == COMM_RS) {
             const long long crow = row - chunk * chunk_rows;
             if (chunk != p.rank) {
-              // partial tile of a peer's rows: store it into that peer's staging slot for this rank
-              __nv_bfloat16* dp = p.rs_stage[chunk] + (p.rank * chunk_rows + crow) * p.N + col0;
+              // partial tile of a peer's rows: goes into that peer's staging slot for this rank.  A lane owns
+              // a row, so direct stores would scatter 16-byte pieces over 32 rows per instruction; two column
+              // groups are transposed through shared memory and leave as full 128-byte lines instead.
+              uint8_t* slab = smem_gen + L::RS_OFFSET + (warp - 2) * (32 * RS_ROW_BYTES);
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
-                if (col0 + j < p.N) {
-                  uint4 o;
-                  o.x = pack_bf16x2(v[j], v[j + 1]);
-                  o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                  o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                  o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-                  *reinterpret_cast<uint4*>(dp + j) = o;
+                uint4 o;
+                o.x = pack_bf16x2(v[j], v[j + 1]);
+                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(slab + lane * RS_ROW_BYTES + (c & 1) * 64 + j * 2) = o;
+              }
+              const bool last_group = (c == BN / 32 - 1) || (col0 + 32 >= p.N);
+              if ((c & 1) || last_group) {
+                __syncwarp();
+                const int colp = n0 + (c & ~1) * 32;            // first column of the pair
+                const int oct = lane & 7;
+                const long long base_row = (p.rank * chunk_rows + (m0 + quad * 32 - chunk * chunk_rows));
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                  const int rr = it * 4 + (lane >> 3);
+                  const int col = colp + oct * 8;
+                  if (col < p.N && (oct < 4 || (c & 1)))
+                    *reinterpret_cast<uint4*>(p.rs_stage[chunk] + (base_row + rr) * p.N + col) =
+                        *reinterpret_cast<const uint4*>(slab + rr * RS_ROW_BYTES + oct * 16);
                 }
+                __syncwarp();
               }
             } else {
               for (int sr = 0; sr < p.ws; ++sr) {
@@ -516,6 +520,56 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         acc = 0;
         acc_phase ^= 1;
       }
+    }
+  } else if (p.comm == COMM_AG) {
+    // ------------------------------------------------------------------ all-gather push (warps 6..9)
+    // Copy this rank's shard of A into every rank's gather buffer (coalesced 16-byte peer stores over
+    // NVLink, several loads in flight per thread) while the main loop already works on the local chunk;
+    // then publish "CTA b of rank r is done".  Kept off the epilogue warps so that accumulators drain
+    // while the push is running.
+    const long long chunk_rows = static_cast<long long>(p.tiles_m_chunk) * BM;
+    const int kv = p.K >> 3;
+    const long long total = chunk_rows * kv;
+    const int pt = threadIdx.x - 192;  // 0..127 among the push threads
+    const long long stride = static_cast<long long>(gridDim.x) * 128;
+    long long v = static_cast<long long>(blockIdx.x) * 128 + pt;
+    constexpr int U = 4;
+    for (; v + (U - 1) * stride < total; v += U * stride) {
+      uint4 x[U];
+      long long off[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long vv = v + u * stride;
+        const long long r = vv / kv;
+        const int c = static_cast<int>(vv - r * kv) * 8;
+        x[u] = *reinterpret_cast<const uint4*>(p.ag_src + r * p.ag_ld + c);
+        off[u] = (p.rank * chunk_rows + r) * p.K + c;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        for (int q = 0; q < p.ws; ++q) *reinterpret_cast<uint4*>(p.ag_dst[q] + off[u]) = x[u];
+    }
+    for (; v < total; v += stride) {
+      const long long r = v / kv;
+      const int c = static_cast<int>(v - r * kv) * 8;
+      const uint4 x = *reinterpret_cast<const uint4*>(p.ag_src + r * p.ag_ld + c);
+      for (int q = 0; q < p.ws; ++q)
+        *reinterpret_cast<uint4*>(p.ag_dst[q] + (p.rank * chunk_rows + r) * p.K + c) = x;
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (pt < p.ws && pt != p.rank) st_release_sys(p.ag_flags[pt] + p.rank * 256 + blockIdx.x, p.epoch);
+    // wait for the peers' shards in the order the main loop consumes them: 128 threads poll the
+    // gridDim.x flags of a chunk in parallel (one dependent acquire-load each instead of a serial chain)
+    for (int order = 1; order < p.ws; ++order) {
+      const int chunk = (p.rank + order) % p.ws;
+      bool ok = true;
+      for (int c = pt; c < static_cast<int>(gridDim.x) && ok; c += 128)
+        ok = wait_flag_ge(p.ag_flags[p.rank] + chunk * 256 + c, p.epoch, p.err, 7);
+      if (!ok) *ag_abort = 1;
+      __threadfence_block();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ag_bar(order - 1));
     }
   }
 

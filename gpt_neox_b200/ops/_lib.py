@@ -70,6 +70,8 @@ def _declare(lib):
                                   P, P, P, P, P, I, I, I, P])
     sig("nx_wkv6_chunks", [I])
     sig("nx_wkv6_pass", [I, P, P, P, P, L, L, P, P, L, L, I, P, P, P, I, I, I, I, P])
+    sig("nx_gemm_fp8", [P, P, P, I, I, I, L, L, L, I, I, P, P, I, I, P])
+    sig("nx_fp8_quantize", [P, L, P, P, L, P, L, P, I, I, I, P])
     sig("nx_rope", [P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, I, I, P])
     sig("nx_embedding_fwd", [P, P, P, L, I, L, L, P])
     sig("nx_embedding_bwd", [P, P, P, L, I, L, L, P])

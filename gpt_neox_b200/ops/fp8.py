@@ -1,0 +1,132 @@
+"""FP8 linear layers with per-tensor delayed scaling (csrc/gemm_fp8_tcgen05.cu).
+
+Forward and both backward GEMMs run on ``tcgen05.mma.kind::f8f6f4``: activations and weights in e4m3,
+gradients in e5m2 (the "hybrid" format), fp32 accumulation, bf16 outputs, weight gradients accumulated in
+fp32 into ``weight.main_grad`` when the engine provides it.  Scales follow the delayed-scaling recipe the
+reference configures through Transformer Engine (megatron/model/transformer_engine.py:633-670): each
+tensor role keeps a history of absolute maxima; the scale used at step t is ``fp8_max / (2^margin *
+max(history))`` computed from steps before t, and the amax observed at step t is recorded for later.
+All of this state lives on the device: no host synchronisation per step.
+
+Both operands of the fp8 MMA are K-major here, so the backward GEMMs consume transposed fp8 copies that
+the quantisation kernel writes in the same pass as the straight copy.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .gemm import LAUNCHES
+
+E4M3_MAX, E5M2_MAX = 448.0, 57344.0
+
+
+class Fp8TensorMeta:
+    """Scale state of one tensor role (input, weight or output-gradient of one layer)."""
+
+    def __init__(self, device, e5m2=False, history=16, margin=0):
+        self.fp8_max = E5M2_MAX if e5m2 else E4M3_MAX
+        self.e5m2, self.margin = e5m2, margin
+        self.scale = torch.ones(1, device=device, dtype=torch.float32)
+        self.amax = torch.zeros(1, device=device, dtype=torch.float32)            # written by the kernel
+        self.history = torch.zeros(history, device=device, dtype=torch.float32)
+
+    def roll(self):
+        """Record the amax observed since the last call and derive the next scale (device-side ops)."""
+        self.history = torch.roll(self.history, 1)
+        self.history[0] = self.amax[0]
+        self.amax.zero_()
+        m = self.history.max()
+        new = self.fp8_max / (m * (2.0 ** self.margin))
+        self.scale = torch.where((m > 0) & torch.isfinite(new), new, self.scale).reshape(1)
+
+
+class Fp8LinearMeta:
+    def __init__(self, device, history=16, margin=0):
+        self.x = Fp8TensorMeta(device, False, history, margin)
+        self.w = Fp8TensorMeta(device, False, history, margin)
+        self.g = Fp8TensorMeta(device, True, history, margin)
+
+    def roll(self):
+        self.x.roll(), self.w.roll(), self.g.roll()
+
+
+def quantize(x2, meta: Fp8TensorMeta, transpose=False):
+    """bf16 [rows, cols] -> (fp8 [rows, cols], fp8 [cols, rows] or None) as uint8 tensors; updates meta.amax."""
+    rows, cols = x2.shape
+    out = torch.empty((rows, cols), device=x2.device, dtype=torch.uint8)
+    out_t = torch.empty((cols, rows), device=x2.device, dtype=torch.uint8) if transpose else None
+    LAUNCHES["n"] += 1
+    _lib.check(_lib.lib().nx_fp8_quantize(_lib.ptr(x2), x2.stride(0), _lib.ptr(meta.scale), _lib.ptr(out), cols,
+                                          _lib.ptr(out_t), rows, _lib.ptr(meta.amax), rows, cols, int(meta.e5m2),
+                                          _lib.stream()), "nx_fp8_quantize")
+    return out, out_t
+
+
+def gemm_fp8(a8, b8, alpha, *, a_e5m2=False, b_e5m2=False, bias=None, out=None, accumulate=False):
+    """C[M,N] = alpha * a8[M,K] @ b8[N,K]^T (+ bias); bf16 result, or fp32 into ``out`` (optionally +=)."""
+    M, K = a8.shape
+    N = b8.shape[0]
+    out_f32 = out is not None and out.dtype == torch.float32
+    if out is None:
+        out = torch.empty((M, N), device=a8.device, dtype=torch.bfloat16)
+    LAUNCHES["n"] += 1
+    _lib.check(_lib.lib().nx_gemm_fp8(_lib.ptr(a8), _lib.ptr(b8), _lib.ptr(out), M, N, K, a8.stride(0), b8.stride(0),
+                                      out.stride(0), int(a_e5m2), int(b_e5m2), _lib.ptr(alpha), _lib.ptr(bias),
+                                      int(out_f32), int(accumulate), _lib.stream()), "nx_gemm_fp8")
+    return out
+
+
+class _Fp8LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, meta: Fp8LinearMeta):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        need_wgrad = weight.requires_grad
+        x8, x8t = quantize(x2, meta.x, transpose=need_wgrad)
+        w8, w8t = quantize(weight, meta.w, transpose=x.requires_grad)
+        alpha = 1.0 / (meta.x.scale * meta.w.scale)
+        y = gemm_fp8(x8, w8, alpha, bias=bias)
+        ctx.save_for_backward(x8t, w8t, meta.x.scale.clone(), meta.w.scale.clone())
+        ctx.meta, ctx.weight, ctx.has_bias, ctx.x_shape = meta, weight, bias is not None, x.shape
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x8t, w8t, sx, sw = ctx.saved_tensors
+        meta, weight = ctx.meta, ctx.weight
+        g2 = gy.reshape(-1, gy.shape[-1])
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        g8, g8t = quantize(g2, meta.g, transpose=x8t is not None)
+        gx = gw = gb = None
+        if w8t is not None:
+            gx = gemm_fp8(g8, w8t, 1.0 / (meta.g.scale * sw), a_e5m2=True).view(ctx.x_shape)     # dY [M,N] x W^T[K,N]^T
+        if x8t is not None:
+            mg = getattr(weight, "main_grad", None)
+            alpha = 1.0 / (meta.g.scale * sx)
+            if mg is not None and mg.dtype == torch.float32:
+                gemm_fp8(g8t, x8t, alpha, a_e5m2=True, out=mg, accumulate=True)                  # dY^T [N,M] x X^T[K,M]^T
+            else:
+                gw = gemm_fp8(g8t, x8t, alpha, a_e5m2=True)
+                if mg is not None:
+                    mg.add_(gw.to(mg.dtype))
+                    gw = None
+        if ctx.has_bias:
+            from .elementwise import colsum
+            gb = colsum(g2)
+        return gx, gw, gb, None
+
+
+def fp8_linear(x, weight, bias, meta: Fp8LinearMeta):
+    """``F.linear`` with fp8 tensor-core GEMMs. Shapes: tokens % 8 == 0, in/out features % 16 == 0."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16):
+        raise _lib.KernelError("fp8_linear needs CUDA bf16 activations")
+    return _Fp8LinearFn.apply(x, weight, bias, meta)
+
+
+def dequantize_reference(q8, scale, e5m2=False):
+    """uint8 fp8 bit patterns -> fp32 values / scale (test helper)."""
+    dt = torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn
+    return q8.view(dt).float() / scale

@@ -6,7 +6,7 @@ fraction of the measured peaks (``MEASURED_PEAKS.json`` beside the package when 
 numbers passed by ``--peak-tflops`` / ``--peak-gbs``).  ``--once`` runs the operator a few times without
 timing: the form to put under a profiler.
 
-ops: gemm, gemm_wgrad, attn_fwd, attn_bwd, layernorm, scan_fwd, scan_bwd, conv1d, adamw, ce
+ops: gemm, gemm_fp8, gemm_wgrad, attn_fwd, attn_bwd, layernorm, scan_fwd, scan_bwd, conv1d, adamw, ce
 """
 from __future__ import annotations
 
@@ -62,6 +62,15 @@ def build(op, a):
             x, g = rn(K, M), rn(K, N)            # wgrad: x^T g, the reduction runs over rows
             fn = lambda: gemm(x, g, trans_a=True, trans_b=True)
         return fn, 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
+    if op == "gemm_fp8":
+        from . import fp8
+        M, N, K = a.m, a.n, a.k
+        ma, mb = fp8.Fp8TensorMeta(dev), fp8.Fp8TensorMeta(dev)
+        x8, _ = fp8.quantize(rn(M, K), ma)
+        w8, _ = fp8.quantize(rn(N, K), mb)
+        alpha = torch.ones(1, device=dev)
+        fn = lambda: fp8.gemm_fp8(x8, w8, alpha)
+        return fn, 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N
     if op in ("attn_fwd", "attn_bwd"):
         from .attention import flash_attention
         b, s, h, d = a.batch, a.seq, a.heads, a.head_dim
