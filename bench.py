@@ -38,6 +38,9 @@ def parse():
     p.add_argument("--gas", type=int, default=None, help="override gradient accumulation steps")
     p.add_argument("--mode", type=str, default="fused", choices=("fused", "nccl_baseline"))
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--fp8", action="store_true",
+                   help="run the linear layers' GEMMs (forward, dgrad, wgrad) on the fp8 tensor cores with delayed "
+                        "scaling; reported under dtype 'fp8' and never as the bf16 headline")
     p.add_argument("--kernel-table", type=str, default=None,
                    help="after the timed regions, run one more (untimed) step under torch.profiler and write the "
                         "per-kernel device-time table of rank 0 to this file")
@@ -156,6 +159,11 @@ def main():
             "train_micro_batch_size_per_gpu": micro, "gradient_accumulation_steps": gas, "train_batch_size": None,
             "comm_mode": args.mode, "train_iters": total_iters, "lr_decay_iters": 143000, "log_interval": 10 ** 9,
             "make_vocab_size_divisible_by": 128 if tp <= 2 else 64}
+    if args.fp8:
+        over.update(te_columnparallel=True, te_rowparallel=True, te_fp8_amax_history_len=16,
+                    te_fp8_amax_compute_algo="max")
+        if tp > 1:
+            over["comm_mode"] = "nccl_baseline"      # the fused AG/RS GEMM kernels are bf16
     neox_args = NeoXArgs.from_ymls([os.path.join(REPO, "configs", "bench", args.model + ".yml")], overwrite_values=over)
     neox_args.configure_distributed_args()
     neox_args.build_tokenizer()
@@ -254,7 +262,7 @@ def main():
         tflops = get_flops(neox_args, dev_ms / 1000.0, use_checkpointing_factor=False) / 1e12
         out = {"metric": "tokens_per_sec", "value": tps, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
                "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak",
-               "vs_baseline": None, "dtype": "bf16", "data": "synthetic tokens, random-init weights",
+               "vs_baseline": None, "dtype": "fp8" if args.fp8 else "bf16", "data": "synthetic tokens, random-init weights",
                "tflops_per_gpu": tflops, "impl": "ours", "mode": args.mode,
                "config": {"model": args.model, "global_batch": global_batch, "seq_len": seq, "micro_batch": micro,
                           "grad_accum": gas,

@@ -387,11 +387,16 @@ class Engine(torch.nn.Module):
         for g in self.groups:
             g.gather_params()
             g.zero_grad()
+        for m in self._fp8_modules():
+            m.fp8_meta.roll()               # delayed scaling: this step's amax feeds the next steps' scales
         if overflow:
             self.skipped_steps += 1
         elif self.lr_scheduler is not None:
             self.lr_scheduler.step()
         self.global_steps += 1
+
+    def _fp8_modules(self):
+        return [m for m in self.module.modules() if getattr(m, "fp8_meta", None) is not None]
 
     def zero_grad(self):
         for g in self.groups:

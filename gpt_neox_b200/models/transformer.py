@@ -81,6 +81,8 @@ class ParallelMLP(nn.Module):
                            bias=neox_args.use_bias_in_mlp)
 
     def _fusable(self, x):
+        if getattr(self.linear1, "use_fp8", False) or getattr(self.linear2, "use_fp8", False):
+            return False        # fp8 GEMMs run through the per-module path
         return (not self.is_gated) and self.activation_type == "gelu" and x.is_cuda and x.dtype == torch.bfloat16
 
     def forward(self, hidden_states, residual=None):

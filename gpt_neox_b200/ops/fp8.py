@@ -24,9 +24,9 @@ E4M3_MAX, E5M2_MAX = 448.0, 57344.0
 class Fp8TensorMeta:
     """Scale state of one tensor role (input, weight or output-gradient of one layer)."""
 
-    def __init__(self, device, e5m2=False, history=16, margin=0):
+    def __init__(self, device, e5m2=False, history=16, margin=0, algo="max"):
         self.fp8_max = E5M2_MAX if e5m2 else E4M3_MAX
-        self.e5m2, self.margin = e5m2, margin
+        self.e5m2, self.margin, self.algo = e5m2, margin, algo
         self.scale = torch.ones(1, device=device, dtype=torch.float32)
         self.amax = torch.zeros(1, device=device, dtype=torch.float32)            # written by the kernel
         self.history = torch.zeros(history, device=device, dtype=torch.float32)
@@ -36,16 +36,23 @@ class Fp8TensorMeta:
         self.history = torch.roll(self.history, 1)
         self.history[0] = self.amax[0]
         self.amax.zero_()
-        m = self.history.max()
+        m = self.history[0] if self.algo == "most_recent" else self.history.max()
         new = self.fp8_max / (m * (2.0 ** self.margin))
         self.scale = torch.where((m > 0) & torch.isfinite(new), new, self.scale).reshape(1)
 
 
 class Fp8LinearMeta:
-    def __init__(self, device, history=16, margin=0):
-        self.x = Fp8TensorMeta(device, False, history, margin)
-        self.w = Fp8TensorMeta(device, False, history, margin)
-        self.g = Fp8TensorMeta(device, True, history, margin)
+    def __init__(self, device, history=16, margin=0, algo="max", hybrid=True, fp8_wgrad=True):
+        self.x = Fp8TensorMeta(device, False, history, margin, algo)
+        self.w = Fp8TensorMeta(device, False, history, margin, algo)
+        self.g = Fp8TensorMeta(device, hybrid, history, margin, algo)      # hybrid: e5m2 gradients
+        self.fp8_wgrad = fp8_wgrad
+
+    @classmethod
+    def from_args(cls, neox_args, device):
+        return cls(device, history=max(1, neox_args.te_fp8_amax_history_len), margin=neox_args.te_fp8_margin,
+                   algo=neox_args.te_fp8_amax_compute_algo, hybrid=neox_args.te_fp8_format == "hybrid",
+                   fp8_wgrad=bool(neox_args.te_fp8_wgrad))
 
     def roll(self):
         self.x.roll(), self.w.roll(), self.g.roll()
@@ -84,17 +91,18 @@ class _Fp8LinearFn(torch.autograd.Function):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         need_wgrad = weight.requires_grad
-        x8, x8t = quantize(x2, meta.x, transpose=need_wgrad)
+        x8, x8t = quantize(x2, meta.x, transpose=need_wgrad and meta.fp8_wgrad)
         w8, w8t = quantize(weight, meta.w, transpose=x.requires_grad)
         alpha = 1.0 / (meta.x.scale * meta.w.scale)
         y = gemm_fp8(x8, w8, alpha, bias=bias)
-        ctx.save_for_backward(x8t, w8t, meta.x.scale.clone(), meta.w.scale.clone())
+        ctx.save_for_backward(x8t, w8t, meta.x.scale.clone(), meta.w.scale.clone(),
+                              x2 if (need_wgrad and not meta.fp8_wgrad) else None)
         ctx.meta, ctx.weight, ctx.has_bias, ctx.x_shape = meta, weight, bias is not None, x.shape
         return y.view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, gy):
-        x8t, w8t, sx, sw = ctx.saved_tensors
+        x8t, w8t, sx, sw, x_bf16 = ctx.saved_tensors
         meta, weight = ctx.meta, ctx.weight
         g2 = gy.reshape(-1, gy.shape[-1])
         if not g2.is_contiguous():
@@ -102,17 +110,20 @@ class _Fp8LinearFn(torch.autograd.Function):
         g8, g8t = quantize(g2, meta.g, transpose=x8t is not None)
         gx = gw = gb = None
         if w8t is not None:
-            gx = gemm_fp8(g8, w8t, 1.0 / (meta.g.scale * sw), a_e5m2=True).view(ctx.x_shape)     # dY [M,N] x W^T[K,N]^T
+            gx = gemm_fp8(g8, w8t, 1.0 / (meta.g.scale * sw), a_e5m2=meta.g.e5m2).view(ctx.x_shape)     # dY [M,N] x W^T[K,N]^T
         if x8t is not None:
             mg = getattr(weight, "main_grad", None)
             alpha = 1.0 / (meta.g.scale * sx)
             if mg is not None and mg.dtype == torch.float32:
-                gemm_fp8(g8t, x8t, alpha, a_e5m2=True, out=mg, accumulate=True)                  # dY^T [N,M] x X^T[K,M]^T
+                gemm_fp8(g8t, x8t, alpha, a_e5m2=meta.g.e5m2, out=mg, accumulate=True)                  # dY^T [N,M] x X^T[K,M]^T
             else:
-                gw = gemm_fp8(g8t, x8t, alpha, a_e5m2=True)
+                gw = gemm_fp8(g8t, x8t, alpha, a_e5m2=meta.g.e5m2)
                 if mg is not None:
                     mg.add_(gw.to(mg.dtype))
                     gw = None
+        if x_bf16 is not None:
+            from .gemm import wgrad
+            gw = wgrad(g2, x_bf16, weight)                       # te_fp8_wgrad = false: bf16 weight gradient
         if ctx.has_bias:
             from .elementwise import colsum
             gb = colsum(g2)

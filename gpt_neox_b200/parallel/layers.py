@@ -38,6 +38,18 @@ def _device(neox_args):
     return torch.device("cuda", torch.cuda.current_device())
 
 
+def _fp8_or_bf16_linear(mod, x, weight, bias):
+    """The module's GEMM: fp8 tensor cores when the module was built with fp8 enabled (``te_columnparallel`` /
+    ``te_rowparallel`` / ``te_layernorm_mlp``), the bf16 kernel otherwise."""
+    if getattr(mod, "use_fp8", False) and x.is_cuda and x.dtype == torch.bfloat16 and \
+            (x.numel() // x.shape[-1]) % 8 == 0 and weight.shape[0] % 16 == 0 and weight.shape[1] % 16 == 0:
+        from ..ops.fp8 import Fp8LinearMeta, fp8_linear
+        if mod.fp8_meta is None:
+            mod.fp8_meta = Fp8LinearMeta.from_args(mod._fp8_args, x.device)
+        return fp8_linear(x, weight, bias, mod.fp8_meta)
+    return linear_op(x, weight, bias)
+
+
 def _set_tp_attrs(p, is_parallel, dim, stride):
     p.model_parallel = is_parallel
     p.partition_dim = dim
@@ -153,6 +165,8 @@ class ColumnParallelLinear(nn.Module):
         super().__init__()
         self.input_size, self.output_size = input_size, output_size
         self.gather_output, self.skip_bias_add = gather_output, skip_bias_add
+        self.use_fp8 = bool(getattr(neox_args, "te_columnparallel", False) or getattr(neox_args, "te_layernorm_mlp", False))
+        self.fp8_meta, self._fp8_args = None, neox_args
         ws = mpu.get_model_parallel_world_size()
         self.output_size_per_partition = divide(output_size, ws)
         self.sequence_parallel = bool(neox_args.sequence_parallel) and ws > 1
@@ -192,7 +206,7 @@ class ColumnParallelLinear(nn.Module):
                 input_parallel = gather_from_sequence_parallel_region(input_, seq_dim=self.seq_dim)
             else:
                 input_parallel = copy_to_model_parallel_region(input_)
-            output_parallel = linear_op(input_parallel, self.weight, bias)
+            output_parallel = _fp8_or_bf16_linear(self, input_parallel, self.weight, bias)
         output = gather_from_model_parallel_region(output_parallel) if self.gather_output else output_parallel
         return output, (self.bias if self.skip_bias_add else None)
 
@@ -209,6 +223,8 @@ class RowParallelLinear(nn.Module):
         super().__init__()
         self.input_size, self.output_size = input_size, output_size
         self.input_is_parallel, self.skip_bias_add = input_is_parallel, skip_bias_add
+        self.use_fp8 = bool(getattr(neox_args, "te_rowparallel", False) or getattr(neox_args, "te_layernorm_mlp", False))
+        self.fp8_meta, self._fp8_args = None, neox_args
         self.parallel_output = parallel_output
         ws = mpu.get_model_parallel_world_size()
         self.input_size_per_partition = divide(input_size, ws)
@@ -250,7 +266,7 @@ class RowParallelLinear(nn.Module):
             b = self.bias if not self.skip_bias_add else None
             out = linear_rs(input_parallel, self.weight, b, None, be)
             return out, (self.bias if self.skip_bias_add else None)
-        output_parallel = linear_op(input_parallel, self.weight, None)
+        output_parallel = _fp8_or_bf16_linear(self, input_parallel, self.weight, None)
         if self.sequence_parallel and not self.parallel_output:
             output_ = reduce_scatter_to_sequence_parallel_region(output_parallel, seq_dim=self.seq_dim)
         elif not self.parallel_output:

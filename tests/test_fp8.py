@@ -60,3 +60,40 @@ def test_fp8_linear_tracks_bf16_linear():
     rel = lambda a, r: ((a.float() - r).norm() / r.norm()).item()
     assert rel(y, yr) < 0.06 and rel(x.grad, gx) < 0.1 and rel(w.grad, gw) < 0.1 and rel(b.grad, gb) < 0.02
     assert meta.x.scale.item() > 1.0
+
+
+def test_fp8_model_loss_tracks_bf16_model():
+    """Same weights, linear layers on fp8 tensor cores vs bf16: first losses agree, and the fp8 model trains."""
+    from common import tiny_config
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.models.gpt2_model import cross_entropy
+    base = dict(num_layers=2, hidden_size=256, num_attention_heads=4, seq_length=128, max_position_embeddings=128,
+                synthetic_vocab_size=1000, attention_config=[[["flash"], 2]], distributed_backend="nccl",
+                precision="bfloat16")
+    models = []
+    for fp8_on in (False, True):
+        a = NeoXArgs.from_dict(tiny_config(**base, te_columnparallel=fp8_on, te_rowparallel=fp8_on))
+        a.configure_distributed_args()
+        a.build_tokenizer()
+        mpu.destroy_model_parallel()
+        initialize_megatron(a)
+        models.append(training.get_model(a))
+    models[1].load_state_dict(models[0].state_dict())
+    torch.manual_seed(0)
+    tok = torch.randint(0, 1000, (4, 129), device="cuda")
+    x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    pos = torch.arange(128, device="cuda")[None].expand(4, -1)
+    mask = torch.ones(4, 128, device="cuda")
+    losses = []
+    for m in models:
+        l = cross_entropy(m((x, pos, None)), (y, mask))
+        l.backward()
+        losses.append(l.item())
+    assert abs(losses[0] - losses[1]) < 0.05 * abs(losses[0]), losses
+    g0 = dict(models[0].named_parameters())["sequential.2.mlp.linear1.weight"].grad.float()
+    g1 = dict(models[1].named_parameters())["sequential.2.mlp.linear1.weight"].grad.float()
+    assert ((g0 - g1).norm() / g0.norm()).item() < 0.2
+    assert any(getattr(m, "fp8_meta", None) is not None for m in models[1].modules())
