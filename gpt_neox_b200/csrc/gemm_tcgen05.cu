@@ -59,6 +59,16 @@ struct GemmParams {
   float alpha;
   int tiles_m, tiles_n;
   int* err;
+  // ---- grouped (mixture-of-experts) modes; group_mode == GROUP_NONE leaves them unused
+  //  GROUP_ROWS: the rows of A / C are expert segments aligned to BM; grp_tile_expert[tm] names the expert of
+  //              row tile tm (-1: tile unused); B holds the experts' matrices stacked, grp_b_rows apart.
+  //  GROUP_K   : one output matrix per expert (grp_c_stride apart), reduction over the expert's row segment
+  //              [grp_row_offsets[e], grp_row_offsets[e+1]) of MN-major A and B (weight gradients).
+  int group_mode, total_tiles;
+  const int* grp_tile_expert;
+  const int* grp_row_offsets;
+  int grp_b_rows;
+  long long grp_c_stride;
   // ---- fused collective (tensor-parallel group of `ws` ranks, this rank = `rank`); comm == COMM_NONE
   //      leaves everything below unused
   int comm, rank, ws;
@@ -77,6 +87,7 @@ struct GemmParams {
 };
 
 enum CommMode : int { COMM_NONE = 0, COMM_RS = 1, COMM_AG = 2 };
+enum GroupMode : int { GROUP_NONE = 0, GROUP_ROWS = 1, GROUP_K = 2 };
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -117,6 +128,31 @@ __device__ __forceinline__ void tile_coords_p(int tile, const GemmParams& p, int
   int tl;
   tile_coords(tile - order * per_chunk, p.tiles_m_chunk, p.tiles_n, tl, tn);
   tm = chunk * p.tiles_m_chunk + tl;
+}
+
+
+// Grouped modes: expert of the tile and the range of K blocks it reduces over.  Returns false for a tile
+// that has no work (unused row tile / expert without rows); every warp role skips it the same way.
+__device__ __forceinline__ bool group_tile(int tile, const GemmParams& p, int num_kb, int& tm, int& tn, int& chunk,
+                                           int& e, int& kb0, int& kb1) {
+  e = 0;
+  kb0 = 0;
+  kb1 = num_kb;
+  if (p.group_mode == GROUP_K) {
+    const int per = p.tiles_m * p.tiles_n;
+    e = tile / per;
+    chunk = 0;
+    tile_coords(tile - e * per, p.tiles_m, p.tiles_n, tm, tn);
+    kb0 = p.grp_row_offsets[e] / BK;
+    kb1 = p.grp_row_offsets[e + 1] / BK;
+    return kb1 > kb0;
+  }
+  tile_coords_p(tile, p, tm, tn, chunk);
+  if (p.group_mode == GROUP_ROWS) {
+    e = p.grp_tile_expert[tm];
+    return e >= 0;
+  }
+  return true;
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
@@ -170,7 +206,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = p.total_tiles;
   const int num_kb = (p.K + BK - 1) / BK;
   bool aborted = false;
 
@@ -181,10 +217,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       uint32_t phase = 0;
       int ag_ready_chunk = -1;
       for (int tile = blockIdx.x; tile < num_tiles && !aborted; tile += gridDim.x) {
-        int tm, tn, chunk;
-        tile_coords_p(tile, p, tm, tn, chunk);
+        int tm, tn, chunk, ge, kb0, kb1;
+        if (!group_tile(tile, p, num_kb, tm, tn, chunk, ge, kb0, kb1)) continue;
         int m0 = tm * BM;
         const int n0 = tn * BN;
+        const int b_off = p.group_mode == GROUP_ROWS ? ge * p.grp_b_rows : 0;   // expert's block of stacked B
         const CUtensorMap* mapA = &tmA;
         if (p.comm == COMM_AG) {
           if (chunk == p.rank) {
@@ -203,7 +240,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             ag_ready_chunk = chunk;
           }
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, p.err, 1)) {
             aborted = true;
             break;
@@ -220,11 +257,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
               tma_load_2d(a_dst + j * (BK * 128), &tmA, full_bar(stage), m0 + j * 64, k0);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(b_dst, &tmB, full_bar(stage), k0, n0);
+            tma_load_2d(b_dst, &tmB, full_bar(stage), k0, n0 + b_off);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(b_dst + j * (BK * 128), &tmB, full_bar(stage), n0 + j * 64, k0);
+              tma_load_2d(b_dst + j * (BK * 128), &tmB, full_bar(stage), n0 + j * 64, k0 + b_off);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -248,13 +285,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       int acc = 0;
       uint32_t acc_phase = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !aborted; tile += gridDim.x) {
+        int tm_, tn_, chunk_, ge_, kb0, kb1;
+        if (!group_tile(tile, p, num_kb, tm_, tn_, chunk_, ge_, kb0, kb1)) continue;
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, p.err, 2)) {
           aborted = true;
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, p.err, 3)) {
             aborted = true;
             break;
@@ -266,7 +305,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t adesc = umma_smem_desc_sw128(a_addr + k * A_KADV, A_LBO, 1024);
             const uint64_t bdesc = umma_smem_desc_sw128(b_addr + k * B_KADV, B_LBO, 1024);
-            umma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16_ss(d_tmem, adesc, bdesc, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));  // frees the smem slot once these MMAs retire
           if (++stage == STAGES) {
@@ -291,9 +330,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const int flags = p.flags;
     const long long chunk_rows = static_cast<long long>(p.tiles_m_chunk) * BM;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      int tm, tn, chunk;
-      tile_coords_p(tile, p, tm, tn, chunk);
+      int tm, tn, chunk, ge, kb0_, kb1_;
+      if (!group_tile(tile, p, num_kb, tm, tn, chunk, ge, kb0_, kb1_)) continue;
       const int m0 = tm * BM, n0 = tn * BN;
+      const long long c_off = p.group_mode == GROUP_K ? ge * p.grp_c_stride : 0;
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, p.err, 4)) {
         aborted = true;
         break;
@@ -469,7 +509,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
               }
             }
           } else if (flags & EPI_OUT_F32) {
-            float* cp = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
+            float* cp = reinterpret_cast<float*>(p.C) + c_off + row * p.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (col0 + j < p.N) {
@@ -482,7 +522,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
               }
             }
           } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + row * p.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
@@ -599,7 +639,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
     configured = true;
   }
-  const int tiles = p.tiles_m * p.tiles_n;
+  const int tiles = p.total_tiles;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, GEMM_THREADS, L::DYN_BYTES, stream>>>(tmA, tmB, tmA2, p);
   NX_LAUNCH_CHECK();
@@ -626,6 +666,11 @@ struct CommArgs {
   long long ld_res2 = 0;
   const void* ag_src = nullptr;
   long long ag_ld = 0;
+  // grouped (mixture-of-experts) modes
+  int group_mode = 0, experts = 1;
+  const int* tile_expert = nullptr;
+  const int* row_offsets = nullptr;
+  long long c_stride = 0;
 };
 
 static int gemm_common(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
@@ -681,8 +726,9 @@ static int gemm_common(const void* A, const void* B, void* C, int M, int N, int 
   if (!transA) ok = make_tma_2d(&tmA, A, M, K, lda * 2, BM, BK, 2);
   else         ok = make_tma_2d(&tmA, A, K, M, lda * 2, BK, 64, 2);
   if (!ok) return NX_ERR_ARG;
-  if (!transB) ok = make_tma_2d(&tmB, B, N, K, ldb * 2, BN, BK, 2);
-  else         ok = make_tma_2d(&tmB, B, K, N, ldb * 2, BK, 64, 2);
+  const long long eb = ca.group_mode == GROUP_ROWS ? ca.experts : 1;    // stacked expert matrices
+  if (!transB) ok = make_tma_2d(&tmB, B, eb * N, K, ldb * 2, BN, BK, 2);
+  else         ok = make_tma_2d(&tmB, B, eb * K, N, ldb * 2, BK, 64, 2);
   if (!ok) return NX_ERR_ARG;
   tmA2 = tmA;
   if (ca.mode == COMM_AG) {
@@ -699,6 +745,20 @@ static int gemm_common(const void* A, const void* B, void* C, int M, int N, int 
   p.alpha = alpha;
   p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;
+  p.total_tiles = p.tiles_m * p.tiles_n;
+  p.group_mode = ca.group_mode;
+  if (ca.group_mode == GROUP_ROWS) {
+    NX_REQUIRE(!transA && ca.mode == COMM_NONE && ca.tile_expert != nullptr && M % BM == 0,
+               "gemm_grouped: row mode needs row-major A, a tile->expert table and M %% %d == 0", BM);
+    p.grp_tile_expert = ca.tile_expert;
+    p.grp_b_rows = transB ? K : N;
+  } else if (ca.group_mode == GROUP_K) {
+    NX_REQUIRE(transA && transB && ca.mode == COMM_NONE && ca.row_offsets != nullptr,
+               "gemm_grouped: reduction mode needs MN-major A and B and the experts' row offsets");
+    p.grp_row_offsets = ca.row_offsets;
+    p.grp_c_stride = ca.c_stride;
+    p.total_tiles = p.tiles_m * p.tiles_n * ca.experts;
+  }
   p.err = device_error_word();
   if (BN == 128) return dispatch_layout<128, 6>(transA, transB, tmA, tmB, tmA2, p, stream);
   return dispatch_layout<256, 4>(transA, transB, tmA, tmB, tmA2, p, stream);
@@ -714,6 +774,25 @@ NX_API int nx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   CommArgs ca;
   return gemm_common(A, B, C, M, N, K, lda, ldb, ldc, transA, transB, bias, aux_in, aux_out, residual, ld_aux,
                      flags, alpha, ca, static_cast<cudaStream_t>(stream_));
+}
+
+// Grouped GEMMs over expert row segments that are aligned to 128 rows (the layout the MoE permute kernel
+// writes).  mode 1: C[rows, N] = A[rows, K] * op(B_e) with B the experts' matrices stacked ([E*N, K] for
+// transB = 0, [E*K, N] for transB = 1) and tile_expert[row tile] -> expert (or -1).  mode 2: per-expert
+// weight gradient C_e[M, N] (+)= A[rows_e, M]^T * B[rows_e, N], rows_e = [row_offsets[e], row_offsets[e+1]);
+// C_e = C + e * c_stride; experts without rows are left untouched.  All tables live on the device: no host
+// synchronisation on the routing result.
+NX_API int nx_gemm_bf16_grouped(int mode, const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                long long ldb, long long ldc, int transB, int experts, const void* tile_expert,
+                                const void* row_offsets, long long c_stride, const void* aux_in, void* aux_out,
+                                long long ld_aux, int flags, void* stream_) {
+  CommArgs ca;
+  ca.group_mode = mode; ca.experts = experts;
+  ca.tile_expert = static_cast<const int*>(tile_expert);
+  ca.row_offsets = static_cast<const int*>(row_offsets);
+  ca.c_stride = c_stride;
+  return gemm_common(A, B, C, M, N, K, lda, ldb, ldc, mode == 2 ? 1 : 0, mode == 2 ? 1 : transB, nullptr, aux_in,
+                     aux_out, nullptr, ld_aux, flags, 1.0f, ca, static_cast<cudaStream_t>(stream_));
 }
 
 // Number of CTAs the GEMM of this shape launches (the all-gather mode's flag count per source rank).

@@ -72,6 +72,9 @@ class ParallelDroplessMLP(nn.Module):
         mlp_cls = ParallelGroupedLLaMAMLP if gated else ParallelGroupedMLP
         self.mlp = mlp_cls(neox_args=neox_args, init_method=init_method,
                            output_layer_init_method=output_layer_init_method)
+        self.gated = gated
+        self.use_kernels = True        # device-side plan / permute / grouped GEMM path (CUDA bf16, EP = 1)
+        self.bias_gelu_fusion = bool(neox_args.bias_gelu_fusion)
 
     def indices_and_bins(self, top_expert):
         """Sort routed copies by expert: (sorted expert ids, permutation, tokens per expert)."""
@@ -85,6 +88,13 @@ class ParallelDroplessMLP(nn.Module):
         in_shape = x.shape
         x2 = x.reshape(-1, x.shape[-1])
         T, k = expert_indices.shape
+        if (self.use_kernels and x.is_cuda and x.dtype == torch.bfloat16 and self.ep_size == 1 and not self.gated
+                and self.mlp.activation_type == "gelu" and x2.shape[1] % 8 == 0
+                and self.mlp.per_expert_ff_dim % 8 == 0):
+            from ..ops.moe import experts_gelu
+            out = experts_gelu(x2.contiguous(), expert_weights, expert_indices, self.mlp.w1, self.mlp.w2,
+                               self.num_experts, "tanh" if self.bias_gelu_fusion else "erf")
+            return out.view(in_shape)
         indices, _bin_ids, tpe = self.indices_and_bins(expert_indices)
         token_of_copy = torch.div(indices, k, rounding_mode="floor")
         routed = x2.index_select(0, token_of_copy)                      # expert-sorted copies

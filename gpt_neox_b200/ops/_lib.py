@@ -72,6 +72,13 @@ def _declare(lib):
     sig("nx_wkv6_pass", [I, P, P, P, P, L, L, P, P, L, L, I, P, P, P, I, I, I, I, P])
     sig("nx_gemm_fp8", [P, P, P, I, I, I, L, L, L, I, I, P, P, I, I, P])
     sig("nx_fp8_quantize", [P, L, P, P, L, P, L, P, I, I, I, P])
+    sig("nx_moe_blocks", [I])
+    sig("nx_moe_max_rows", [I, I])
+    sig("nx_moe_plan", [P, I, I, P, P, P, P, P, P, P, P])
+    sig("nx_moe_gather_rows", [P, L, P, P, I, P, I, I, P])
+    sig("nx_moe_combine", [P, P, P, I, P, I, I, P])
+    sig("nx_moe_weight_grad", [P, P, P, I, P, I, I, P])
+    sig("nx_gemm_bf16_grouped", [I, P, P, P, I, I, I, L, L, L, I, I, P, P, L, P, P, L, I, P])
     sig("nx_rope", [P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, I, I, P])
     sig("nx_embedding_fwd", [P, P, P, L, I, L, L, P])
     sig("nx_embedding_bwd", [P, P, P, L, I, L, L, P])
