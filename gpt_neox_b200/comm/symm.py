@@ -223,3 +223,60 @@ def backend_for(group):
 
 def reset():
     _BACKENDS.clear()
+
+
+class ZeroWorkspace:
+    """Symmetric home of one flat parameter space's gradient and low-precision parameter buffers, so the
+    ZeRO reduce-scatter and all-gather run in place over peer memory (csrc/comm.cu, zero_* kernels):
+    no staging copies and no NCCL on the optimizer step.  Layout: [flags 64 KiB][gradients][parameters]."""
+
+    def __init__(self, group, grad_bytes: int, param_bytes: int):
+        import torch.distributed._symmetric_memory as symm_mem
+        L = _declare()
+        P, I, LL, U = C.c_void_p, C.c_int, C.c_longlong, C.c_uint
+        PP = C.POINTER(C.c_ulonglong)
+        L.nx_comm_zero_reduce_scatter.argtypes = [PP, I, I, LL, LL, I, I, U, P]
+        L.nx_comm_zero_all_gather.argtypes = [PP, I, I, LL, LL, I, U, P]
+        L.nx_comm_zero_reduce_scatter.restype = L.nx_comm_zero_all_gather.restype = I
+        self.group, self.ws, self.me = group, dist.get_world_size(group), dist.get_rank(group)
+        self.flag_bytes = L.nx_comm_flag_bytes()
+        al = lambda n: (n + 4095) // 4096 * 4096
+        self.grad_off = self.flag_bytes
+        self.param_off = self.grad_off + al(grad_bytes)
+        total = self.param_off + al(param_bytes)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+        self.buf[: self.flag_bytes].zero_()
+        torch.cuda.synchronize()
+        self.hdl = symm_mem.rendezvous(self.buf, group)
+        self.ptrs = (C.c_ulonglong * 8)(*([int(p) for p in self.hdl.buffer_ptrs] + [0] * (8 - self.ws)))
+        self.grad_bytes, self.param_bytes = grad_bytes, param_bytes
+        self.epoch = 1
+        self.grid = min(2 * torch.cuda.get_device_properties(dev).multi_processor_count, 1024)
+        dist.barrier(group)
+
+    def grad_buffer(self, dtype):
+        return self.buf[self.grad_off:self.grad_off + self.grad_bytes].view(dtype)
+
+    def param_buffer(self, dtype):
+        return self.buf[self.param_off:self.param_off + self.param_bytes].view(dtype)
+
+    def _next(self):
+        e = self.epoch
+        self.epoch += 2
+        return e
+
+    def reduce_scatter_grads(self, dtype):
+        """Sum the gradient buffers of all ranks; rank r ends up with the sum in its chunk r (in place)."""
+        LAUNCHES["n"] += 1
+        _lib.check(_lib.lib().nx_comm_zero_reduce_scatter(self.ptrs, self.me, self.ws, self.grad_off,
+                                                          self.grad_bytes // self.ws,
+                                                          0 if dtype == torch.bfloat16 else 1, self.grid, self._next(),
+                                                          _lib.stream()), "nx_comm_zero_reduce_scatter")
+
+    def all_gather_params(self):
+        """Push this rank's chunk of the parameter buffer into every peer's buffer (in place)."""
+        LAUNCHES["n"] += 1
+        _lib.check(_lib.lib().nx_comm_zero_all_gather(self.ptrs, self.me, self.ws, self.param_off,
+                                                      self.param_bytes // self.ws, self.grid, self._next(),
+                                                      _lib.stream()), "nx_comm_zero_all_gather")

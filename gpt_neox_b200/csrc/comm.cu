@@ -135,6 +135,90 @@ __global__ void __launch_bounds__(COMM_THREADS) allgather_kernel(PeerTable t, co
   rank_barrier(t, me, ws, epoch + 1, err, 106);
 }
 
+// ---------------------------------------------------------------------------------------------
+// ZeRO collectives on buffers that LIVE in the symmetric workspace (no staging copies):
+//   zero_reduce_scatter: every rank's gradient buffer is at payload offset `pay`; rank r sums chunk r over
+//     all ranks straight out of the peers' memory (coalesced 16-byte peer loads, four in flight per
+//     thread) and writes the result over its own chunk r, in place.
+//   zero_all_gather: rank r pushes chunk r of its parameter buffer into the same place of every peer.
+// Both are bracketed by rank barriers: the first makes sure every rank's buffer is final (backward /
+// optimizer step done), the second that nobody overwrites a buffer that a peer is still reading.
+// ---------------------------------------------------------------------------------------------
+template <bool BF16>
+__global__ void __launch_bounds__(COMM_THREADS) zero_reduce_scatter_kernel(PeerTable t, int me, int ws, long long pay,
+                                                                           long long shard_bytes, uint32_t epoch,
+                                                                           int* err) {
+  if (!rank_barrier(t, me, ws, epoch, err, 107)) return;
+  const long long nvec = shard_bytes / 16;
+  const long long base = pay + me * shard_bytes;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  char* mine = reinterpret_cast<char*>(t.ptr[me]) + base;
+  constexpr int U = 4;
+  long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (; v + (U - 1) * stride < nvec; v += U * stride) {
+    float acc[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+    for (int r = 0; r < ws; ++r) {
+      const char* src = reinterpret_cast<const char*>(t.ptr[r]) + base;
+      uint4 x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) x[u] = *reinterpret_cast<const uint4*>(src + (v + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (BF16) {
+          acc_bf16x8(acc[u], x[u]);
+        } else {
+          acc[u][0] += __uint_as_float(x[u].x); acc[u][1] += __uint_as_float(x[u].y);
+          acc[u][2] += __uint_as_float(x[u].z); acc[u][3] += __uint_as_float(x[u].w);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      uint4 o;
+      if (BF16) o = pack_acc(acc[u]);
+      else o = make_uint4(__float_as_uint(acc[u][0]), __float_as_uint(acc[u][1]), __float_as_uint(acc[u][2]),
+                          __float_as_uint(acc[u][3]));
+      *reinterpret_cast<uint4*>(mine + (v + u * stride) * 16) = o;
+    }
+  }
+  for (; v < nvec; v += stride)
+    *reinterpret_cast<uint4*>(mine + v * 16) = reduce_vec<BF16>(t, ws, nullptr, base, v * 16);
+  rank_barrier(t, me, ws, epoch + 1, err, 108);
+}
+
+__global__ void __launch_bounds__(COMM_THREADS) zero_all_gather_kernel(PeerTable t, int me, int ws, long long pay,
+                                                                       long long shard_bytes, uint32_t epoch,
+                                                                       int* err) {
+  if (!rank_barrier(t, me, ws, epoch, err, 109)) return;
+  const long long nvec = shard_bytes / 16;
+  const long long base = pay + me * shard_bytes;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const char* mine = reinterpret_cast<const char*>(t.ptr[me]) + base;
+  constexpr int U = 4;
+  long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (; v + (U - 1) * stride < nvec; v += U * stride) {
+    uint4 x[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) x[u] = *reinterpret_cast<const uint4*>(mine + (v + u * stride) * 16);
+    for (int r = 0; r < ws; ++r) {
+      if (r == me) continue;
+      char* dst = reinterpret_cast<char*>(t.ptr[r]) + base;
+#pragma unroll
+      for (int u = 0; u < U; ++u) *reinterpret_cast<uint4*>(dst + (v + u * stride) * 16) = x[u];
+    }
+  }
+  for (; v < nvec; v += stride) {
+    const uint4 x = *reinterpret_cast<const uint4*>(mine + v * 16);
+    for (int r = 0; r < ws; ++r)
+      if (r != me) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.ptr[r]) + base + v * 16) = x;
+  }
+  rank_barrier(t, me, ws, epoch + 1, err, 110);
+}
+
 static bool fill_table(PeerTable& t, const unsigned long long* ptrs, int ws) {
   if (ws < 1 || ws > COMM_MAX_RANKS) return false;
   for (int i = 0; i < COMM_MAX_RANKS; ++i) t.ptr[i] = i < ws ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
@@ -189,6 +273,38 @@ NX_API int nx_comm_allgather(const unsigned long long* peer_ptrs, unsigned long 
   NX_REQUIRE(shard_bytes % 16 == 0, "comm: shard must be a multiple of 16 bytes");
   allgather_kernel<<<COMM_BLOCKS, COMM_THREADS, 0, (cudaStream_t)stream_>>>(
       t, (const void*)mc_ptr, me, ws, payload_off, shard_bytes, in, epoch, device_error_word());
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+
+// In-place ZeRO collectives over buffers inside the symmetric workspace (see the kernels above).
+// grid: every rank must pass the same value (blocks pair up across ranks for the barriers).
+NX_API int nx_comm_zero_reduce_scatter(const unsigned long long* peer_ptrs, int me, int ws, long long payload_off,
+                                       long long shard_bytes, int dtype, int grid, unsigned int epoch, void* stream_) {
+  using namespace nx;
+  PeerTable t;
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws), "comm: world size %d out of range", ws);
+  NX_REQUIRE(shard_bytes % 16 == 0 && payload_off % 16 == 0, "comm: shard / offset must be multiples of 16 bytes");
+  NX_REQUIRE(grid >= 1 && grid * COMM_MAX_RANKS * 4 <= COMM_FLAG_BYTES, "comm: grid %d does not fit the flag area", grid);
+  auto s = (cudaStream_t)stream_;
+  if (dtype == 0)
+    zero_reduce_scatter_kernel<true><<<grid, COMM_THREADS, 0, s>>>(t, me, ws, payload_off, shard_bytes, epoch,
+                                                                   device_error_word());
+  else
+    zero_reduce_scatter_kernel<false><<<grid, COMM_THREADS, 0, s>>>(t, me, ws, payload_off, shard_bytes, epoch,
+                                                                    device_error_word());
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+NX_API int nx_comm_zero_all_gather(const unsigned long long* peer_ptrs, int me, int ws, long long payload_off,
+                                   long long shard_bytes, int grid, unsigned int epoch, void* stream_) {
+  using namespace nx;
+  PeerTable t;
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws), "comm: world size %d out of range", ws);
+  NX_REQUIRE(shard_bytes % 16 == 0 && payload_off % 16 == 0, "comm: shard / offset must be multiples of 16 bytes");
+  NX_REQUIRE(grid >= 1 && grid * COMM_MAX_RANKS * 4 <= COMM_FLAG_BYTES, "comm: grid %d does not fit the flag area", grid);
+  zero_all_gather_kernel<<<grid, COMM_THREADS, 0, (cudaStream_t)stream_>>>(t, me, ws, payload_off, shard_bytes, epoch,
+                                                                           device_error_word());
   NX_LAUNCH_CHECK();
   return NX_OK;
 }

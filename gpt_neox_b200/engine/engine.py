@@ -53,8 +53,13 @@ class FlatGroup:
         unit = dp_size * 256
         self.total = (off + unit - 1) // unit * unit
         self.offsets = offs
-        self.flat_lp = torch.zeros(self.total, dtype=self.lp_dtype, device=self.device)
-        self.main_grad = torch.zeros(self.total, dtype=grad_dtype, device=self.device)
+        self.zero_ws = self._try_symmetric_workspace(grad_dtype)
+        if self.zero_ws is not None:
+            self.flat_lp = self.zero_ws.param_buffer(self.lp_dtype).zero_()
+            self.main_grad = self.zero_ws.grad_buffer(grad_dtype).zero_()
+        else:
+            self.flat_lp = torch.zeros(self.total, dtype=self.lp_dtype, device=self.device)
+            self.main_grad = torch.zeros(self.total, dtype=grad_dtype, device=self.device)
         for p, o in zip(self.params, offs):
             n = p.numel()
             self.flat_lp[o:o + n].copy_(p.data.reshape(-1))
@@ -88,6 +93,28 @@ class FlatGroup:
             if hi > lo:
                 self.segments.append((lo - s, hi - s, wd, rep, skip))
 
+    def _try_symmetric_workspace(self, grad_dtype):
+        """ZeRO over peer memory: put the gradient and parameter buffers into a symmetric allocation of the
+        data-parallel group so the reduce-scatter / all-gather kernels work on them in place.  Every rank of
+        the group takes the same decision (the attempt's outcome is min-reduced)."""
+        import os
+        from ..comm import collectives
+        if not (self.device.type == "cuda" and self.dp_size > 1 and self.zero_stage >= 1
+                and collectives.get_mode() == "fused" and os.environ.get("NEOX_ZERO_SYMM", "1") != "0"
+                and grad_dtype in (torch.float32, torch.bfloat16) and self.dp_size <= 8):
+            return None
+        ws, ok = None, 1
+        try:
+            from ..comm.symm import ZeroWorkspace
+            esz = lambda dt: torch.empty((), dtype=dt).element_size()
+            ws = ZeroWorkspace(self.dp_group, self.total * esz(grad_dtype), self.total * esz(self.lp_dtype))
+        except Exception as e:  # noqa: BLE001 - any failure means "use the NCCL path", decided collectively
+            print(f"ZeRO symmetric workspace unavailable ({type(e).__name__}: {e}); using NCCL collectives", flush=True)
+            ok = 0
+        flag = torch.tensor([ok], device=self.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.dp_group)
+        return ws if int(flag.item()) == 1 else None
+
     def numel(self):
         return sum(p.numel() for p in self.params)
 
@@ -105,6 +132,10 @@ class FlatGroup:
     def reduce_gradients(self):
         if self.dp_size == 1:
             return
+        if self.zero_ws is not None:
+            # reduce-scatter straight out of the peers' gradient buffers, result in place in this rank's shard
+            self.zero_ws.reduce_scatter_grads(self.main_grad.dtype)
+            return
         if self.sharded:
             out = self.grad_shard()
             if self.main_grad.is_cuda:
@@ -115,6 +146,9 @@ class FlatGroup:
             dist.all_reduce(self.main_grad, group=self.dp_group)
 
     def gather_params(self):
+        if self.zero_ws is not None:
+            self.zero_ws.all_gather_params()      # push the updated shard into every peer's parameter buffer
+            return
         if self.sharded:
             lp_shard = self.flat_lp[self.shard_start:self.shard_start + self.shard_size]
             if self.flat_lp.is_cuda:

@@ -50,7 +50,8 @@ def main():
         losses.append(float(ld["lm_loss"].item()))
     err = _lib.read_device_error()
     if int(os.environ.get("RANK", "0")) == 0:
-        print("LOSSES " + json.dumps({"losses": losses, "device_error": err}), flush=True)
+        zs = any(getattr(g, "zero_ws", None) is not None for g in model.groups)
+        print("LOSSES " + json.dumps({"losses": losses, "device_error": err, "zero_symm": zs}), flush=True)
     if torch.distributed.is_initialized():
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()

@@ -14,11 +14,11 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(nproc, *args, timeout=600):
+def _run(nproc, *args, timeout=600, env=None):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
            os.path.join(HERE, "mgpu", "train_losses.py"), *map(str, args)]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=dict(os.environ, **(env or {})))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     line = [l for l in r.stdout.splitlines() if l.startswith("LOSSES ")][-1]
     return json.loads(line[len("LOSSES "):])
@@ -39,3 +39,15 @@ def test_dp2_zero1_trains():
     two = _run(2, "fused", 1, 0, 10, json.dumps(opt))
     assert two["device_error"] == 0
     assert min(two["losses"][4:]) < two["losses"][0]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_zero_over_peer_memory_matches_nccl_zero():
+    """ZeRO-1 with the gradient reduce-scatter / parameter all-gather running in place over peer memory
+    reproduces the NCCL reduce-scatter / all-gather run."""
+    opt = {"optimizer": {"type": "Adam", "params": {"lr": 3e-4, "betas": [0.9, 0.95], "eps": 1e-8}}}
+    nccl = _run(2, "fused", 1, 0, 8, json.dumps(opt), env={"NEOX_ZERO_SYMM": "0"})
+    symm = _run(2, "fused", 1, 0, 8, json.dumps(opt), env={"NEOX_ZERO_SYMM": "1"})
+    assert symm["device_error"] == 0
+    assert symm["losses"] == pytest.approx(nccl["losses"], rel=1e-2)
+    assert symm.get("zero_symm") is True and nccl.get("zero_symm") is False
