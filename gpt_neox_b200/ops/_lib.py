@@ -40,6 +40,7 @@ def _declare(lib):
     sig("nx_sm_count", [])
     sig("nx_abi_version", [])
     sig("nx_gemm_bf16", [P, P, P, I, I, I, L, L, L, I, I, P, P, P, P, L, I, F, P])
+    sig("nx_gemm2_bf16", [P, P, P, I, I, I, L, L, L, I, I, P, P, P, P, L, I, F, P])
     sig("nx_norm_fwd", [I, P, P, P, P, P, P, P, P, P, L, I, F, P])
     sig("nx_norm_bwd_blocks", [L])
     sig("nx_norm_bwd", [I, P, P, P, P, P, P, P, P, P, P, L, I, I, P])

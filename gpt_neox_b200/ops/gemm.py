@@ -28,6 +28,8 @@ EPI_SCALE = 512
 
 #: counts launches of this library's kernels (read by bench.py for its ``gpu_launches`` claim)
 LAUNCHES = {"n": 0}
+#: use the CTA-pair GEMM kernel (csrc/gemm2_tcgen05.cu) for problems of at least one 256 x 256 tile
+PAIR_GEMM = {"on": __import__("os").environ.get("NEOX_GEMM_2CTA", "1") == "1"}
 
 
 def _as_2d(x: torch.Tensor) -> torch.Tensor:
@@ -94,11 +96,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         flags |= EPI_SCALE
     L = _lib.lib()
     LAUNCHES["n"] += 1
-    _lib.check(L.nx_gemm_bf16(
+    fn, name = L.nx_gemm_bf16, "nx_gemm_bf16"
+    if PAIR_GEMM["on"] and M >= 256 and N >= 256:
+        fn, name = L.nx_gemm2_bf16, "nx_gemm2_bf16"      # CTA-pair kernel (cta_group::2, 256 x 256 tiles)
+    _lib.check(fn(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
         int(trans_a), int(trans_b), _lib.ptr(bias), _lib.ptr(dgelu_aux), _lib.ptr(aux_out),
         _lib.ptr(residual), ld_aux, flags, float(alpha if alpha is not None else 1.0),
-        _lib.stream()), "nx_gemm_bf16")
+        _lib.stream()), name)
     return out
 
 
