@@ -35,9 +35,10 @@ def _declare():
     L.nx_comm_allgather.argtypes = [PP, ULL, I, I, LL, LL, P, U, P]
     L.nx_gemm_bf16_comm.argtypes = [P, P, P, I, I, I, LL, LL, LL, I, P, P, P, P, LL, I, I, I, I, U, PP, PP, P, LL,
                                     P, LL, P]
+    L.nx_gemm2_bf16_comm.argtypes = L.nx_gemm_bf16_comm.argtypes
     L.nx_gemm_grid.argtypes = [I, I]
     for n in ("nx_comm_allreduce", "nx_comm_reduce_scatter", "nx_comm_allgather", "nx_gemm_bf16_comm",
-              "nx_gemm_grid"):
+              "nx_gemm2_bf16_comm", "nx_gemm_grid"):
         getattr(L, n).restype = I
     L._comm_declared = True
     return L
@@ -119,7 +120,7 @@ class SymmBackend:
             ld_aux = dgelu_aux.stride(0)
         epoch = self._next_epoch(1)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_gemm_bf16_comm(
+        _lib.check(self._comm_gemm(m)(
             _lib.ptr(gathered), _lib.ptr(w), _lib.ptr(out), m, n, k, k, w.stride(0), out.stride(0), int(trans_b),
             _lib.ptr(bias), _lib.ptr(dgelu_aux), _lib.ptr(aux_out), None, ld_aux, flags, 2, self.me, self.ws, epoch,
             self._table(goff), self._table(self.ag_flag_off), None, 0, _lib.ptr(x_shard), x_shard.stride(0),
@@ -147,13 +148,19 @@ class SymmBackend:
             ld_aux = dgelu_aux.stride(0)
         epoch = self._next_epoch(1)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_gemm_bf16_comm(
+        _lib.check(self._comm_gemm(m)(
             _lib.ptr(a), _lib.ptr(w), _lib.ptr(out), m, n, k, a.stride(0), w.stride(0), out.stride(0), int(trans_b),
             _lib.ptr(bias), _lib.ptr(dgelu_aux), None, _lib.ptr(residual), ld_aux, flags, 1, self.me, self.ws, epoch,
             self._table(self.stage_off[par]), self._table(self.rs_flag_off), _lib.ptr(residual2),
             residual2.stride(0) if residual2 is not None else 0, None, 0, _lib.stream()),
             "nx_gemm_bf16_comm(reduce-scatter)")
         return out
+
+    def _comm_gemm(self, m_full: int):
+        """CTA-pair kernel (256-row tiles) when the rank chunks are whole 256-row tiles, else the 128-row kernel."""
+        from ..ops.gemm import PAIR_GEMM
+        L = _lib.lib()
+        return L.nx_gemm2_bf16_comm if (PAIR_GEMM["on"] and m_full % (self.ws * 256) == 0) else L.nx_gemm_bf16_comm
 
     def supports(self, x: torch.Tensor) -> bool:
         return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and x.is_contiguous()

@@ -28,10 +28,14 @@ constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UK = 16;
 constexpr int STAGES = 6;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;        // producer, MMA issuer, 4 epilogue warps, 4 all-gather push warps
+constexpr int RS_ROW_BYTES = 144;    // 64 bf16 columns + 16 B pad
+constexpr int RS_STAGE_BYTES = 4 * 32 * RS_ROW_BYTES;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-constexpr int DYN_BYTES = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 1024;
+constexpr int RS_OFFSET = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 8 * 8;   // tmem slot, abort word, 8 chunk barriers
+constexpr int DYN_BYTES = RS_OFFSET + RS_STAGE_BYTES + 1024;
+enum Comm : int { COMM_NONE = 0, COMM_RS = 1, COMM_AG = 2 };
 
 enum Epi : int { BIAS = 1, GELU_ERF = 2, GELU_TANH = 4, AUX_OUT = 8, DGELU_ERF = 16, DGELU_TANH = 32, RESIDUAL = 64,
                  ACCUM = 128, OUT_F32 = 256, SCALE = 512 };
@@ -49,6 +53,18 @@ struct Params {
   float alpha;
   int tiles_m, tiles_n;    // 256-row x 256-column tiles
   int* err;
+  // ---- fused tensor-parallel collective (same protocol as csrc/gemm_tcgen05.cu, 256-row tiles)
+  int comm, tp_rank, ws;
+  int tiles_m_chunk;            // row tiles per rank chunk: (M / ws) / 256
+  uint32_t epoch;
+  __nv_bfloat16* rs_stage[8];   // on rank q: staging [src rank][M / ws, N]
+  uint32_t* rs_flags[8];        // on rank q: flags[tile in chunk][src rank][cta of pair][warp]
+  const __nv_bfloat16* residual2;
+  long long ld_res2;
+  const __nv_bfloat16* ag_src;  // this rank's [M / ws, K] shard
+  long long ag_ld;
+  __nv_bfloat16* ag_dst[8];     // on rank q: gather buffer [M, K]
+  uint32_t* ag_flags[8];        // on rank q: flags[src][cta]
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -117,9 +133,26 @@ __device__ __forceinline__ void tile_coords2(int tile, int tiles_m, int tiles_n,
   tn = r / gsize;
 }
 
+// Tile order under a fused collective: whole rank chunks of rows at a time (reduce-scatter: peers' chunks
+// first, own last; all-gather: own chunk first, then the peers' as their shards arrive).
+__device__ __forceinline__ void tile_coords2_p(int tile, const Params& p, int& tm, int& tn, int& chunk) {
+  if (p.comm == COMM_NONE) {
+    tile_coords2(tile, p.tiles_m, p.tiles_n, tm, tn);
+    chunk = 0;
+    return;
+  }
+  const int per_chunk = p.tiles_m_chunk * p.tiles_n;
+  const int order = tile / per_chunk;
+  chunk = p.comm == COMM_RS ? (p.tp_rank + 1 + order) % p.ws : (p.tp_rank + order) % p.ws;
+  int tl;
+  tile_coords2(tile - order * per_chunk, p.tiles_m_chunk, p.tiles_n, tl, tn);
+  tm = chunk * p.tiles_m_chunk + tl;
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-    gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+    gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmA2, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -130,6 +163,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + BAR_OFFSET + 8 * (2 * STAGES + 4));
+  auto ag_bar = [&](int k) { return bar_base + 8u * (2 * STAGES + 6 + k); };
+  volatile int* ag_abort = reinterpret_cast<volatile int*>(smem_gen + BAR_OFFSET + 8 * (2 * STAGES + 5));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
@@ -145,6 +180,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       mbar_init(tmem_full_bar(a), 1);
       mbar_init(tmem_empty_bar(a), 8);         // leader: four epilogue warps of each CTA
     }
+    for (int k = 0; k < 8; ++k) mbar_init(ag_bar(k), 4);   // one arrival per push warp
+    *ag_abort = 0;
     fence_barrier_init();
   }
   if (warp == 0 && lane == 0) {
@@ -172,11 +209,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
+      int ag_ready_chunk = -1;
       for (int tile = pair; tile < num_tiles && !aborted; tile += pairs) {
-        int tm, tn;
-        tile_coords2(tile, p.tiles_m, p.tiles_n, tm, tn);
-        const int m0 = tm * (2 * BM) + rank * BM;
+        int tm, tn, chunk;
+        tile_coords2_p(tile, p, tm, tn, chunk);
+        int m0 = tm * (2 * BM) + rank * BM;
         const int n0 = tn * BN + rank * BNH;
+        const CUtensorMap* mapA = &tmA;
+        if (p.comm == COMM_AG) {
+          if (chunk == p.tp_rank) {
+            mapA = &tmA2;                                   // own shard: read it where it already is
+            m0 -= chunk * p.tiles_m_chunk * (2 * BM);
+          } else if (chunk != ag_ready_chunk) {
+            const int order = (chunk - p.tp_rank + p.ws) % p.ws;
+            if (!mbar_wait(ag_bar(order - 1), 0, p.err, 17) || *ag_abort) {
+              aborted = true;
+              break;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
+            ag_ready_chunk = chunk;
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, p.err, 11)) {
             aborted = true;
@@ -189,7 +242,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
           if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
           const int k0 = kb * BK;
           if constexpr (!A_MN) {
-            tma2_load_2d(a_dst, &tmA, bar, k0, m0);
+            tma2_load_2d(a_dst, mapA, bar, k0, m0);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma2_load_2d(a_dst + j * (BK * 128), &tmA, bar, m0 + j * 64, k0);
@@ -251,16 +304,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
         }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
     const int flags = p.flags;
+    const long long chunk_rows = static_cast<long long>(p.tiles_m_chunk) * (2 * BM);
     for (int tile = pair; tile < num_tiles; tile += pairs) {
-      int tm, tn;
-      tile_coords2(tile, p.tiles_m, p.tiles_n, tm, tn);
+      int tm, tn, chunk;
+      tile_coords2_p(tile, p, tm, tn, chunk);
       const int m0 = tm * (2 * BM) + rank * BM, n0 = tn * BN;
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, p.err, 14)) {
         aborted = true;
@@ -269,6 +323,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       tc_fence_after_sync();
       const long long row = m0 + row_in_tile;
       const bool row_ok = row < p.M;
+      const int tile_in_chunk = (tm - chunk * p.tiles_m_chunk) * p.tiles_n + tn;
+      const int warp_slot = static_cast<int>(rank) * 4 + quad;       // which 32-row band of the 256-row tile
+      if (p.comm == COMM_RS && chunk == p.tp_rank) {
+        // own rows: every peer's warp of the same band must have delivered its partial tile
+        bool ok = true;
+        if (lane < p.ws && lane != p.tp_rank)
+          ok = wait_flag_ge(p.rs_flags[p.tp_rank] + (static_cast<long long>(tile_in_chunk) * p.ws + lane) * 8 + warp_slot,
+                            p.epoch, p.err, 18);
+        if (!__all_sync(0xffffffffu, ok)) {
+          aborted = true;
+          break;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n0 + c * 32;
@@ -283,7 +350,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
         }
-        if (flags & BIAS) {
+        if ((flags & BIAS) && p.comm != COMM_RS) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             if (col0 + j < p.N) {
@@ -349,7 +416,74 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
               }
             }
           }
-          if (flags & OUT_F32) {
+          if (p.comm == COMM_RS) {
+            const long long crow = row - chunk * chunk_rows;
+            if (chunk != p.tp_rank) {
+              // partial tile of a peer's rows -> that peer's staging slot for this rank, as full 128-byte lines
+              uint8_t* slab = smem_gen + RS_OFFSET + (warp - 2) * (32 * RS_ROW_BYTES);
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 o;
+                o.x = pack_bf16x2(v[j], v[j + 1]); o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                o.z = pack_bf16x2(v[j + 4], v[j + 5]); o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(slab + lane * RS_ROW_BYTES + (c & 1) * 64 + j * 2) = o;
+              }
+              const bool last_group = (c == BN / 32 - 1) || (col0 + 32 >= p.N);
+              if ((c & 1) || last_group) {
+                __syncwarp();
+                const int colp = n0 + (c & ~1) * 32;
+                const int oct = lane & 7;
+                const long long base_row = p.tp_rank * chunk_rows + (m0 + quad * 32 - chunk * chunk_rows);
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                  const int rr = it * 4 + (lane >> 3);
+                  const int col = colp + oct * 8;
+                  if (col < p.N && (oct < 4 || (c & 1)))
+                    *reinterpret_cast<uint4*>(p.rs_stage[chunk] + (base_row + rr) * p.N + col) =
+                        *reinterpret_cast<const uint4*>(slab + rr * RS_ROW_BYTES + oct * 16);
+                }
+                __syncwarp();
+              }
+            } else {
+              for (int sr = 0; sr < p.ws; ++sr) {
+                if (sr == p.tp_rank) continue;
+                const __nv_bfloat16* sp = p.rs_stage[p.tp_rank] + (sr * chunk_rows + crow) * p.N + col0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  if (col0 + j < p.N) {
+                    const uint4 a = *reinterpret_cast<const uint4*>(sp + j);
+                    const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y), x2 = unpack_bf16x2(a.z),
+                                 x3 = unpack_bf16x2(a.w);
+                    v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
+                    v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
+                  }
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (col0 + j < p.N) {
+                  if (flags & BIAS) {
+                    const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + j));
+                    const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z),
+                                 b3 = unpack_bf16x2(b.w);
+                    v[j + 0] += b0.x; v[j + 1] += b0.y; v[j + 2] += b1.x; v[j + 3] += b1.y;
+                    v[j + 4] += b2.x; v[j + 5] += b2.y; v[j + 6] += b3.x; v[j + 7] += b3.y;
+                  }
+                  if (p.residual2 != nullptr) {
+                    const uint4 a = *reinterpret_cast<const uint4*>(p.residual2 + crow * p.ld_res2 + col0 + j);
+                    const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y), x2 = unpack_bf16x2(a.z),
+                                 x3 = unpack_bf16x2(a.w);
+                    v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
+                    v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
+                  }
+                  uint4 o;
+                  o.x = pack_bf16x2(v[j], v[j + 1]); o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                  o.z = pack_bf16x2(v[j + 4], v[j + 5]); o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + crow * p.ldc + col0 + j) = o;
+                }
+              }
+            }
+          } else if (flags & OUT_F32) {
             float* cp = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
@@ -383,6 +517,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
           }
         }
       }
+      if (p.comm == COMM_RS && chunk != p.tp_rank) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0)
+          st_release_sys(p.rs_flags[chunk] + (static_cast<long long>(tile_in_chunk) * p.ws + p.tp_rank) * 8 + warp_slot,
+                         p.epoch);
+      }
       // this warp is done with the accumulator: tell the leader's MMA thread
       tc_fence_before_sync();
       __syncwarp();
@@ -391,6 +532,49 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
         acc = 0;
         acc_phase ^= 1;
       }
+    }
+  } else if (p.comm == COMM_AG) {
+    // ------------------------------------------------------------------ all-gather push (warps 6..9, both CTAs)
+    const long long chunk_rows = static_cast<long long>(p.tiles_m_chunk) * (2 * BM);
+    const int kv = p.K >> 3;
+    const long long total = chunk_rows * kv;
+    const int pt = threadIdx.x - 192;
+    const long long stride = static_cast<long long>(gridDim.x) * 128;
+    long long v = static_cast<long long>(blockIdx.x) * 128 + pt;
+    constexpr int U = 4;
+    for (; v + (U - 1) * stride < total; v += U * stride) {
+      uint4 x[U];
+      long long off[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long vv = v + u * stride;
+        const long long r = vv / kv;
+        const int c = static_cast<int>(vv - r * kv) * 8;
+        x[u] = *reinterpret_cast<const uint4*>(p.ag_src + r * p.ag_ld + c);
+        off[u] = (p.tp_rank * chunk_rows + r) * p.K + c;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        for (int q = 0; q < p.ws; ++q) *reinterpret_cast<uint4*>(p.ag_dst[q] + off[u]) = x[u];
+    }
+    for (; v < total; v += stride) {
+      const long long r = v / kv;
+      const int c = static_cast<int>(v - r * kv) * 8;
+      const uint4 x = *reinterpret_cast<const uint4*>(p.ag_src + r * p.ag_ld + c);
+      for (int q = 0; q < p.ws; ++q) *reinterpret_cast<uint4*>(p.ag_dst[q] + (p.tp_rank * chunk_rows + r) * p.K + c) = x;
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (pt < p.ws && pt != p.tp_rank) st_release_sys(p.ag_flags[pt] + p.tp_rank * 256 + blockIdx.x, p.epoch);
+    for (int order = 1; order < p.ws; ++order) {
+      const int chunk = (p.tp_rank + order) % p.ws;
+      bool ok = true;
+      for (int c = pt; c < static_cast<int>(gridDim.x) && ok; c += 128)
+        ok = wait_flag_ge(p.ag_flags[p.tp_rank] + chunk * 256 + c, p.epoch, p.err, 19);
+      if (!ok) *ag_abort = 1;
+      __threadfence_block();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ag_bar(order - 1));
     }
   }
 
@@ -409,7 +593,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 }
 
 template <bool A_MN, bool B_MN>
-static int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, cudaStream_t stream) {
+static int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2, const Params& p,
+                   cudaStream_t stream) {
   auto kern = gemm2_kernel<A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
@@ -419,24 +604,35 @@ static int launch2(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params&
   const int tiles = p.tiles_m * p.tiles_n;
   const int max_pairs = sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<2 * pairs, THREADS, DYN_BYTES, stream>>>(tmA, tmB, p);     // cluster dims are compiled in
+  kern<<<2 * pairs, THREADS, DYN_BYTES, stream>>>(tmA, tmB, tmA2, p);     // cluster dims are compiled in
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
 
 }  // namespace g2
 
-// Same arguments as nx_gemm_bf16.
-NX_API int nx_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
-                         long long ldc, int transA, int transB, const void* bias, const void* aux_in, void* aux_out,
-                         const void* residual, long long ld_aux, int flags, float alpha, void* stream_) {
+struct Comm2Args {
+  int mode = 0, rank = 0, ws = 1;
+  unsigned int epoch = 0;
+  const unsigned long long* data_ptrs = nullptr;
+  const unsigned long long* flag_ptrs = nullptr;
+  const void* residual2 = nullptr;
+  long long ld_res2 = 0;
+  const void* ag_src = nullptr;
+  long long ag_ld = 0;
+};
+
+static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                        long long ldc, int transA, int transB, const void* bias, const void* aux_in, void* aux_out,
+                        const void* residual, long long ld_aux, int flags, float alpha, const Comm2Args& ca,
+                        cudaStream_t s) {
   using namespace g2;
   if (M <= 0 || N <= 0) return NX_OK;
   NX_REQUIRE(K > 0, "gemm2: K must be positive");
   NX_REQUIRE(N % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0, "gemm2: N / lda / ldb must be multiples of 8");
   NX_REQUIRE(ldc % ((flags & OUT_F32) ? 4 : 8) == 0, "gemm2: ldc alignment");
   NX_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0, "gemm2: C must be 16-byte aligned");
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmA2;
   bool ok;
   if (!transA) ok = make_tma_2d(&tmA, A, M, K, lda * 2, BM, BK, 2);
   else         ok = make_tma_2d(&tmA, A, K, M, lda * 2, BK, 64, 2);
@@ -444,6 +640,7 @@ NX_API int nx_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, in
   if (!transB) ok = make_tma_2d(&tmB, B, N, K, ldb * 2, BNH, BK, 2);
   else         ok = make_tma_2d(&tmB, B, K, N, ldb * 2, BK, 64, 2);
   if (!ok) return NX_ERR_ARG;
+  tmA2 = tmA;
   Params p{};
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -454,11 +651,63 @@ NX_API int nx_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, in
   p.tiles_m = (M + 2 * BM - 1) / (2 * BM);
   p.tiles_n = (N + BN - 1) / BN;
   p.err = device_error_word();
-  auto s = static_cast<cudaStream_t>(stream_);
-  if (!transA && !transB) return launch2<false, false>(tmA, tmB, p, s);
-  if (!transA && transB) return launch2<false, true>(tmA, tmB, p, s);
-  if (transA && !transB) return launch2<true, false>(tmA, tmB, p, s);
-  return launch2<true, true>(tmA, tmB, p, s);
+  p.comm = ca.mode;
+  if (ca.mode != COMM_NONE) {
+    NX_REQUIRE(ca.ws >= 2 && ca.ws <= 8 && ca.rank >= 0 && ca.rank < ca.ws, "gemm2_comm: bad rank/world %d/%d", ca.rank, ca.ws);
+    NX_REQUIRE(!transA && M % (ca.ws * 2 * BM) == 0, "gemm2_comm: row-major A and M (%d) %% (ws * 256) == 0 required", M);
+    NX_REQUIRE(!(flags & (OUT_F32 | ACCUM)), "gemm2_comm: fp32 / accumulate outputs are not supported");
+    NX_REQUIRE(ca.data_ptrs != nullptr && ca.flag_ptrs != nullptr, "gemm2_comm: null peer tables");
+    p.tp_rank = ca.rank; p.ws = ca.ws; p.epoch = ca.epoch;
+    p.tiles_m_chunk = (M / ca.ws) / (2 * BM);
+    for (int i = 0; i < ca.ws; ++i) {
+      if (ca.mode == COMM_RS) {
+        p.rs_stage[i] = reinterpret_cast<__nv_bfloat16*>(ca.data_ptrs[i]);
+        p.rs_flags[i] = reinterpret_cast<uint32_t*>(ca.flag_ptrs[i]);
+      } else {
+        p.ag_dst[i] = reinterpret_cast<__nv_bfloat16*>(ca.data_ptrs[i]);
+        p.ag_flags[i] = reinterpret_cast<uint32_t*>(ca.flag_ptrs[i]);
+      }
+    }
+    p.residual2 = static_cast<const __nv_bfloat16*>(ca.residual2);
+    p.ld_res2 = ca.ld_res2;
+    p.ag_src = static_cast<const __nv_bfloat16*>(ca.ag_src);
+    p.ag_ld = ca.ag_ld;
+    if (ca.mode == COMM_RS && ca.residual2 != nullptr) NX_REQUIRE(ca.ld_res2 % 8 == 0, "gemm2_comm: residual2 ld");
+    if (ca.mode == COMM_AG) {
+      NX_REQUIRE(ca.ag_src != nullptr && ca.ag_ld % 8 == 0 && K % 8 == 0 && lda == K,
+                 "gemm2_comm: all-gather mode needs a dense [M, K] gather buffer and an aligned shard");
+      NX_REQUIRE(sm_count() <= 256, "gemm2_comm: flag table holds 256 CTAs per rank");
+      if (!make_tma_2d(&tmA2, ca.ag_src, M / ca.ws, K, ca.ag_ld * 2, BM, BK, 2)) return NX_ERR_ARG;
+    }
+  }
+  if (!transA && !transB) return launch2<false, false>(tmA, tmB, tmA2, p, s);
+  if (!transA && transB) return launch2<false, true>(tmA, tmB, tmA2, p, s);
+  if (transA && !transB) return launch2<true, false>(tmA, tmB, tmA2, p, s);
+  return launch2<true, true>(tmA, tmB, tmA2, p, s);
+}
+
+// Same arguments as nx_gemm_bf16.
+NX_API int nx_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, int transA, int transB, const void* bias, const void* aux_in, void* aux_out,
+                         const void* residual, long long ld_aux, int flags, float alpha, void* stream_) {
+  Comm2Args ca;
+  return gemm2_common(A, B, C, M, N, K, lda, ldb, ldc, transA, transB, bias, aux_in, aux_out, residual, ld_aux, flags,
+                      alpha, ca, static_cast<cudaStream_t>(stream_));
+}
+
+// Same arguments as nx_gemm_bf16_comm; reduce-scatter flags are laid out [tile][src rank][8 warp bands].
+NX_API int nx_gemm2_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                              long long ldc, int transB, const void* bias, const void* aux_in, void* aux_out,
+                              const void* residual, long long ld_aux, int flags, int mode, int rank, int ws,
+                              unsigned int epoch, const unsigned long long* data_ptrs,
+                              const unsigned long long* flag_ptrs, const void* residual2, long long ld_res2,
+                              const void* ag_src, long long ag_ld, void* stream_) {
+  Comm2Args ca;
+  ca.mode = mode; ca.rank = rank; ca.ws = ws; ca.epoch = epoch;
+  ca.data_ptrs = data_ptrs; ca.flag_ptrs = flag_ptrs;
+  ca.residual2 = residual2; ca.ld_res2 = ld_res2; ca.ag_src = ag_src; ca.ag_ld = ag_ld;
+  return gemm2_common(A, B, C, M, N, K, lda, ldb, ldc, 0, transB, bias, aux_in, aux_out, residual, ld_aux, flags, 1.0f,
+                      ca, static_cast<cudaStream_t>(stream_));
 }
 
 }  // namespace nx
