@@ -135,7 +135,10 @@ def load_engine_checkpoint(engine, load_dir, tag=None, load_optimizer_states=Tru
     mp_rank, dp_rank, pp_rank = mpu.get_model_parallel_rank(), mpu.get_data_parallel_rank(), mpu.get_pipe_parallel_rank()
     ms_path = os.path.join(ckpt_dir, model_states_name(mp_rank))
     if not os.path.isfile(ms_path):
-        return None, {}
+        # a tag that was named (by the caller or by the `latest` file) but is not there is damage, not a
+        # fresh start: refuse instead of silently training from scratch over an existing run directory
+        raise FileNotFoundError(f"checkpoint {ckpt_dir} is named by "
+                                f"{'the caller' if tag is None else 'tag ' + repr(str(tag))} but {ms_path} is missing")
     state = torch.load(ms_path, map_location="cpu", weights_only=False)
     is_pipe = engine.neox_args.is_pipe_parallel
     if is_pipe:

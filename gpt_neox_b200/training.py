@@ -530,7 +530,11 @@ def train(neox_args, timers, model, optimizer, lr_scheduler, train_data_iterator
                                       record_shapes=True, profile_memory=True, with_flops=True, with_modules=True,
                                       with_stack=True)
         prof.start()
+    from .obs import heartbeat as _hb
+    hb = _hb.from_args(neox_args)
     while iteration < neox_args.train_iters:
+        if hb is not None:
+            hb.beat(iteration, "train_step")
         if neox_args.profile:
             prof.step()
         if neox_args.profile and iteration == neox_args.profile_step_start and torch.cuda.is_available():
@@ -543,6 +547,14 @@ def train(neox_args, timers, model, optimizer, lr_scheduler, train_data_iterator
             prof.stop()
         iteration += 1
         neox_args.iteration = iteration
+        if iteration % max(1, neox_args.log_interval) == 0:
+            if torch.cuda.is_available():
+                # a bounded wait inside a communication kernel that ran out surfaces here as an exception
+                from .ops import _lib as _klib
+                _klib.raise_on_device_error()
+            if hb is not None and torch.distributed.get_rank() == 0:
+                for s_ in hb.stragglers():
+                    print_rank_0(f"heartbeat: rank {s_['rank']}: {s_['reason']}")
         if neox_args.precision == "fp16":
             overflow_monitor.check(skipped_iter)
         if neox_args.log_gradient_noise_scale and noise_scale_logger is not None:

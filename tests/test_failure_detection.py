@@ -1,0 +1,104 @@
+"""Failure detection without touching a GPU: heartbeat stragglers, a rank that dies before a collective,
+the fp16 overflow watchdog, and the device error word surfacing as an exception (pre-set on the host)."""
+import pytest
+import torch
+import torch.distributed as dist
+
+from common import run_distributed
+
+
+def test_heartbeat_names_silent_and_stuck_ranks():
+    from gpt_neox_b200.obs.heartbeat import Heartbeat
+    store = dist.HashStore()
+    now = [1000.0]
+    clock = lambda: now[0]
+    hbs = [Heartbeat(store, r, 4, interval_s=10, clock=clock) for r in range(4)]
+    for r in (0, 1, 2):
+        hbs[r].beat(5, "forward")
+        hbs[r].publish_once()
+    bad = hbs[0].stragglers()
+    assert [b["rank"] for b in bad] == [3] and bad[0]["reason"] == "no heartbeat"
+    hbs[3].beat(5, "forward")
+    hbs[3].publish_once()
+    assert hbs[0].stragglers() == []
+    # rank 2's process dies (publisher silent); rank 1 keeps publishing but its loop is stuck in iteration 5
+    now[0] += 40
+    for r in (0, 3):
+        hbs[r].beat(9, "backward")
+        hbs[r].publish_once()
+    hbs[1].publish_once()
+    bad = {b["rank"]: b["reason"] for b in hbs[0].stragglers()}
+    assert set(bad) == {1, 2}
+    assert "silent" in bad[2] and "stuck at iteration 5" in bad[1]
+
+
+def test_heartbeat_thread_publishes():
+    import time
+    from gpt_neox_b200.obs.heartbeat import Heartbeat
+    store = dist.HashStore()
+    hb = Heartbeat(store, 0, 1, interval_s=0.05).start()
+    hb.beat(3, "optimizer")
+    time.sleep(0.3)
+    hb.stop()
+    assert hb.read_all()[0]["iteration"] == 3
+
+
+def _rank_dies(rank, world):
+    import datetime
+    import os
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    t = torch.ones(4)
+    dist.all_reduce(t)                       # everyone alive
+    if rank == 1:
+        os._exit(0)                          # leaves between steps, nothing in flight
+    try:
+        dist.all_reduce(t)
+    except Exception as e:  # noqa: BLE001
+        return f"detected: {type(e).__name__}"
+    return "not detected"
+
+
+def test_surviving_rank_gets_an_error_when_a_peer_leaves():
+    import torch.multiprocessing as mp
+    from common import _worker, free_port
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, _rank_dies, (), ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(90)
+    assert not any(p.is_alive() for p in procs)
+    assert ret[0][0] == "ok" and ret[0][1].startswith("detected"), ret.get(0)
+
+
+def test_overflow_monitor_raises_after_n_consecutive_skips():
+    from gpt_neox_b200.utils.common import OverflowMonitor
+
+    class Opt:
+        overflow = True
+    mon = OverflowMonitor(Opt(), n=3)
+    mon.check(True)
+    mon.check(True)
+    with pytest.raises(Exception, match="Skipped 3 iterations"):
+        mon.check(True)
+    mon = OverflowMonitor(Opt(), n=3)
+    for s in (True, False, True):
+        mon.check(s)                         # not consecutive: no error
+
+
+@pytest.mark.gpu
+def test_device_error_word_becomes_an_exception():
+    """A bounded wait that ran out sets the device error word; the host turns it into an exception.  The word
+    is pre-set from the host here: no kernel is made to wait."""
+    from gpt_neox_b200.ops import _lib
+    torch.zeros(1, device="cuda")
+    L = _lib.lib()
+    assert _lib.read_device_error() == 0
+    L.nx_poison_device_error(0x10007)
+    with pytest.raises(_lib.DeviceWaitTimeout):
+        _lib.raise_on_device_error()
+    assert _lib.read_device_error() == 0      # cleared by the read so the context stays usable
+    y = torch.ones(8, device="cuda").sum().item()
+    assert y == 8
