@@ -6,7 +6,8 @@ fraction of the measured peaks (``MEASURED_PEAKS.json`` beside the package when 
 numbers passed by ``--peak-tflops`` / ``--peak-gbs``).  ``--once`` runs the operator a few times without
 timing: the form to put under a profiler.
 
-ops: gemm, gemm_fp8, gemm_wgrad, attn_fwd, attn_bwd, layernorm, scan_fwd, scan_bwd, conv1d, adamw, ce
+ops: gemm, gemm_fp8, gemm_wgrad, attn_fwd, attn_bwd, layernorm, scan_fwd, scan_bwd, conv1d, moe_fwd, moe_fwdbwd,
+     wkv_fwd, wkv_fwdbwd, adamw, ce   (moe: tokens = batch*seq, hidden --n, ffn --k, experts --heads, top-2)
 """
 from __future__ import annotations
 
@@ -113,6 +114,41 @@ def build(op, a):
         g = torch.ones_like(y)
         fn = lambda: torch.autograd.grad(y, leaves, g, retain_graph=True)
         return fn, 0.0, 2.0 * 7 * B * L * D
+    if op in ("moe_fwd", "moe_fwdbwd"):
+        from .moe import experts_gelu
+        T, k, E, h, ffn = a.batch * a.seq, 2, a.heads if a.heads <= 64 else 8, a.n, a.k
+        x = rn(T, h).requires_grad_(True)
+        w1 = (rn(E * ffn, h) * 0.05).requires_grad_(True)
+        w2 = (rn(E * ffn, h) * 0.05).requires_grad_(True)
+        wts, idx = torch.softmax(torch.randn(T, E, device=dev), -1).topk(k, dim=-1)
+        wts = wts.to(bf)
+        flops = 2.0 * 2 * T * k * h * ffn
+        if op == "moe_fwd":
+            def fn():
+                with torch.no_grad():
+                    experts_gelu(x, wts, idx, w1, w2, E)
+            return fn, flops, 2.0 * (2 * E * ffn * h + 4 * T * k * h)
+        def fn2():
+            out = experts_gelu(x, wts, idx, w1, w2, E)
+            torch.autograd.grad(out, (x, w1, w2), torch.ones_like(out))
+        return fn2, 3 * flops, 2.0 * (2 * E * ffn * h + 4 * T * k * h) * 3
+    if op in ("wkv_fwd", "wkv_fwdbwd"):
+        from .wkv import wkv6
+        B, T, H, N = a.batch, a.seq, a.heads, 64
+        C = H * N
+        mk = lambda: (rn(T, B, C) * 0.5).transpose(0, 1)
+        r, k_, v = mk().requires_grad_(True), mk().requires_grad_(True), mk().requires_grad_(True)
+        w = (rn(T, B, C) * 0.5 - 1.5).transpose(0, 1).requires_grad_(True)
+        u = (torch.randn(H, N, device=dev) * 0.3).to(bf).requires_grad_(True)
+        if op == "wkv_fwd":
+            def fn():
+                with torch.no_grad():
+                    wkv6(r, k_, v, w, u)
+            return fn, 4.0 * B * T * C * N, 2.0 * 5 * B * T * C
+        def fn2():
+            y = wkv6(r, k_, v, w, u)
+            torch.autograd.grad(y, (r, k_, v, w, u), torch.ones_like(y))
+        return fn2, 16.0 * B * T * C * N, 2.0 * 14 * B * T * C
     if op == "adamw":
         from . import optim as O
         n = a.m * a.n
