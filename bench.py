@@ -147,15 +147,26 @@ def main():
     from gpt_neox_b200.ops.gemm import LAUNCHES
     from gpt_neox_b200.utils.common import Timers
 
-    tp = 1 if n == 1 else 2
-    dp = n // tp
-    micro = args.micro_batch or (4 if "6-9B" in args.model else 16)
-    per_gpu_seqs = 64 if "6-9B" in args.model else 128         # sequences per GPU per optimizer step
-    global_batch = per_gpu_seqs * n
-    gas = args.gas or global_batch // (micro * dp)
-    global_batch = micro * gas * dp
+    pp = 1
+    if "20B" in args.model:
+        # the named NeoX-20B configuration: TP 4 x PP 2 on 8 GPUs, micro-batch 2, 16 micro-batches per step
+        assert n == 8, "the NeoX-20B benchmark layout (tp4 x pp2) needs --gpus 8"
+        tp, pp = 4, 2
+        dp = n // (tp * pp)
+        micro = args.micro_batch or 2
+        gas = args.gas or 16
+        global_batch = micro * gas * dp
+    else:
+        tp = 1 if n == 1 else 2
+        dp = n // tp
+        micro = args.micro_batch or (4 if "6-9B" in args.model else 16)
+        per_gpu_seqs = 64 if "6-9B" in args.model else 128         # sequences per GPU per optimizer step
+        global_batch = per_gpu_seqs * n
+        gas = args.gas or global_batch // (micro * dp)
+        global_batch = micro * gas * dp
     total_iters = args.warmup + 2 * args.steps + 4
-    over = {"global_num_gpus": n, "model_parallel_size": tp, "sequence_parallel": tp > 1,
+    over = {"global_num_gpus": n, "model_parallel_size": tp, "pipe_parallel_size": pp if pp > 1 else 0,
+            "sequence_parallel": tp > 1,
             "train_micro_batch_size_per_gpu": micro, "gradient_accumulation_steps": gas, "train_batch_size": None,
             "comm_mode": args.mode, "train_iters": total_iters, "lr_decay_iters": 143000, "log_interval": 10 ** 9,
             "make_vocab_size_divisible_by": 128 if tp <= 2 else 64}
@@ -266,7 +277,8 @@ def main():
                "tflops_per_gpu": tflops, "impl": "ours", "mode": args.mode,
                "config": {"model": args.model, "global_batch": global_batch, "seq_len": seq, "micro_batch": micro,
                           "grad_accum": gas,
-                          "parallelism": (f"tp{tp}" + ("+sp" if tp > 1 else "") + f" x dp{dp}, zero1"),
+                          "parallelism": (f"tp{tp}" + ("+sp" if tp > 1 else "") + (f" x pp{pp}" if pp > 1 else "")
+                                          + f" x dp{dp}, zero1"),
                           "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2; "
                                 "no explicit flush"},
                "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "device_error_word": dev_err}
