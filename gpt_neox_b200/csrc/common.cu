@@ -73,9 +73,21 @@ static CUtensorMapDataType dtype_of(int elem_bytes) {
   }
 }
 
+// The tensor-map encoder is a driver entry point and needs a current context in the calling thread.  A
+// thread whose first CUDA activity is one of our launchers (an autograd worker thread that starts with a
+// fused GEMM, for instance) may not have bound the primary context yet: any runtime call binds it.
+static void ensure_thread_context() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 bool make_tma_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                  uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols, int elem_bytes,
                  bool swizzle128) {
+  ensure_thread_context();
   auto fn = get_encode_fn();
   if (fn == nullptr) {
     set_last_error("cuTensorMapEncodeTiled entry point not available");
@@ -106,6 +118,7 @@ bool make_tma_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t col
 bool make_tma_3d(CUtensorMap* map, const void* base, uint64_t d2, uint64_t d1, uint64_t d0,
                  uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box2, uint32_t box1,
                  uint32_t box0, int elem_bytes, bool swizzle128) {
+  ensure_thread_context();
   auto fn = get_encode_fn();
   if (fn == nullptr) {
     set_last_error("cuTensorMapEncodeTiled entry point not available");
@@ -134,6 +147,7 @@ bool make_tma_3d(CUtensorMap* map, const void* base, uint64_t d2, uint64_t d1, u
 bool make_tma_4d(CUtensorMap* map, const void* base, const uint64_t dims[4],
                  const uint64_t strides_bytes[3], const uint32_t box[4], int elem_bytes,
                  bool swizzle128) {
+  ensure_thread_context();
   auto fn = get_encode_fn();
   if (fn == nullptr) {
     set_last_error("cuTensorMapEncodeTiled entry point not available");
