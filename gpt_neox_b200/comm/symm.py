@@ -36,6 +36,8 @@ def _declare():
     L.nx_gemm_bf16_comm.argtypes = [P, P, P, I, I, I, LL, LL, LL, I, P, P, P, P, LL, I, I, I, I, U, PP, PP, P, LL,
                                     P, LL, P]
     L.nx_gemm2_bf16_comm.argtypes = L.nx_gemm_bf16_comm.argtypes
+    L.nx_gemm2_bf16_allreduce.argtypes = [P, P, I, I, I, LL, LL, I, P, P, LL, I, I, I, U, PP, PP, PP, PP, U, P]
+    L.nx_gemm2_bf16_allreduce.restype = I
     L.nx_gemm_grid.argtypes = [I, I]
     for n in ("nx_comm_allreduce", "nx_comm_reduce_scatter", "nx_comm_allgather", "nx_gemm_bf16_comm",
               "nx_gemm2_bf16_comm", "nx_gemm_grid"):
@@ -81,6 +83,9 @@ class SymmBackend:
         self.stage_off = [data0 + 3 * unit, data0 + 4 * unit]
         self.ag_calls = 0
         self.rs_calls = 0
+        self.ar_calls = 0
+        self.ar_count_off = self.ag_flag_off + (8 << 10)      # upper half of the all-gather flag area
+        self.ar_target = 0
         dist.barrier(group)
 
     def _table(self, off):
@@ -154,6 +159,38 @@ class SymmBackend:
             self._table(self.stage_off[par]), self._table(self.rs_flag_off), _lib.ptr(residual2),
             residual2.stride(0) if residual2 is not None else 0, None, 0, _lib.stream()),
             "nx_gemm_bf16_comm(reduce-scatter)")
+        return out
+
+    def can_fuse_ar(self, m: int, k: int, n: int) -> bool:
+        from ..ops.gemm import PAIR_GEMM
+        return bool(PAIR_GEMM["on"]) and m % (self.ws * 256) == 0 and self.can_fuse(m, k, n)
+
+    def gemm_ar(self, a, w, *, trans_b=False, bias=None, residual=None):
+        """``out = all_reduce(a @ op(w) + residual) + bias`` -> [M, N], every rank gets the full result.
+        Reduce-scatter inside the GEMM epilogue, then each owner stores its reduced rows into every rank's
+        output; the result is a view of the symmetric workspace, valid until the second next call."""
+        from ..ops import gemm as G
+        m, k = a.shape
+        n = w.shape[1] if trans_b else w.shape[0]
+        par = self.ar_calls & 1
+        self.ar_calls += 1
+        ooff = self.gather_off[par]
+        out = self.buf[ooff:ooff + m * n * 2].view(torch.bfloat16).view(m, n)
+        flags, ld_aux = 0, 0
+        if bias is not None:
+            flags |= G.EPI_BIAS
+        if residual is not None:
+            flags |= G.EPI_RESIDUAL
+            ld_aux = residual.stride(0)
+        tiles = (m // self.ws // 256) * ((n + 255) // 256)
+        self.ar_target = (self.ar_target + (self.ws - 1) * tiles * 8) & 0xFFFFFFFF
+        epoch = self._next_epoch(1)
+        LAUNCHES["n"] += 2
+        _lib.check(_lib.lib().nx_gemm2_bf16_allreduce(
+            _lib.ptr(a), _lib.ptr(w), m, n, k, a.stride(0), w.stride(0), int(trans_b), _lib.ptr(bias),
+            _lib.ptr(residual), ld_aux, flags, self.me, self.ws, epoch, self._table(self.stage_off[par]),
+            self._table(self.rs_flag_off), self._table(ooff), self._table(self.ar_count_off), self.ar_target,
+            _lib.stream()), "nx_gemm2_bf16_allreduce")
         return out
 
     def _comm_gemm(self, m_full: int):

@@ -35,7 +35,7 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYT
 constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
 constexpr int RS_OFFSET = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16 + 8 * 8;   // tmem slot, abort word, 8 chunk barriers
 constexpr int DYN_BYTES = RS_OFFSET + RS_STAGE_BYTES + 1024;
-enum Comm : int { COMM_NONE = 0, COMM_RS = 1, COMM_AG = 2 };
+enum Comm : int { COMM_NONE = 0, COMM_RS = 1, COMM_AG = 2, COMM_AR = 3 };
 
 enum Epi : int { BIAS = 1, GELU_ERF = 2, GELU_TANH = 4, AUX_OUT = 8, DGELU_ERF = 16, DGELU_TANH = 32, RESIDUAL = 64,
                  ACCUM = 128, OUT_F32 = 256, SCALE = 512 };
@@ -65,6 +65,10 @@ struct Params {
   long long ag_ld;
   __nv_bfloat16* ag_dst[8];     // on rank q: gather buffer [M, K]
   uint32_t* ag_flags[8];        // on rank q: flags[src][cta]
+  // all-reduce mode (reduce-scatter as above, then the owner of a chunk writes the reduced tiles into every
+  // rank's full [M, N] output and bumps that rank's delivery counter once per 32-row band)
+  __nv_bfloat16* ar_out[8];     // on rank q: output [M, N], leading dimension N
+  uint32_t* ar_count[8];        // on rank q: delivery counter
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -143,7 +147,7 @@ __device__ __forceinline__ void tile_coords2_p(int tile, const Params& p, int& t
   }
   const int per_chunk = p.tiles_m_chunk * p.tiles_n;
   const int order = tile / per_chunk;
-  chunk = p.comm == COMM_RS ? (p.tp_rank + 1 + order) % p.ws : (p.tp_rank + order) % p.ws;
+  chunk = p.comm != COMM_AG ? (p.tp_rank + 1 + order) % p.ws : (p.tp_rank + order) % p.ws;
   int tl;
   tile_coords2(tile - order * per_chunk, p.tiles_m_chunk, p.tiles_n, tl, tn);
   tm = chunk * p.tiles_m_chunk + tl;
@@ -325,7 +329,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       const bool row_ok = row < p.M;
       const int tile_in_chunk = (tm - chunk * p.tiles_m_chunk) * p.tiles_n + tn;
       const int warp_slot = static_cast<int>(rank) * 4 + quad;       // which 32-row band of the 256-row tile
-      if (p.comm == COMM_RS && chunk == p.tp_rank) {
+      const bool rs_like = p.comm == COMM_RS || p.comm == COMM_AR;
+      if (rs_like && chunk == p.tp_rank) {
         // own rows: every peer's warp of the same band must have delivered its partial tile
         bool ok = true;
         if (lane < p.ws && lane != p.tp_rank)
@@ -350,7 +355,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
         }
-        if ((flags & BIAS) && p.comm != COMM_RS) {
+        if ((flags & BIAS) && !rs_like) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             if (col0 + j < p.N) {
@@ -416,7 +421,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
               }
             }
           }
-          if (p.comm == COMM_RS) {
+          if (rs_like) {
             const long long crow = row - chunk * chunk_rows;
             if (chunk != p.tp_rank) {
               // partial tile of a peer's rows -> that peer's staging slot for this rank, as full 128-byte lines
@@ -479,7 +484,34 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
                   uint4 o;
                   o.x = pack_bf16x2(v[j], v[j + 1]); o.y = pack_bf16x2(v[j + 2], v[j + 3]);
                   o.z = pack_bf16x2(v[j + 4], v[j + 5]); o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + crow * p.ldc + col0 + j) = o;
+                  if (p.comm == COMM_RS) {
+                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + crow * p.ldc + col0 + j) = o;
+                  } else {
+                    uint8_t* slab = smem_gen + RS_OFFSET + (warp - 2) * (32 * RS_ROW_BYTES);
+                    *reinterpret_cast<uint4*>(slab + lane * RS_ROW_BYTES + (c & 1) * 64 + j * 2) = o;
+                  }
+                }
+              }
+              if (p.comm == COMM_AR) {
+                // reduced rows of this band: out through shared memory as full 128-byte lines, to every rank
+                const uint8_t* slab = smem_gen + RS_OFFSET + (warp - 2) * (32 * RS_ROW_BYTES);
+                const bool last_group = (c == BN / 32 - 1) || (col0 + 32 >= p.N);
+                if ((c & 1) || last_group) {
+                  __syncwarp();
+                  const int colp = n0 + (c & ~1) * 32;
+                  const int oct = lane & 7;
+                  const long long grow0 = m0 + quad * 32;
+#pragma unroll
+                  for (int it = 0; it < 8; ++it) {
+                    const int rr = it * 4 + (lane >> 3);
+                    const int col = colp + oct * 8;
+                    if (col < p.N && (oct < 4 || (c & 1))) {
+                      const uint4 val = *reinterpret_cast<const uint4*>(slab + rr * RS_ROW_BYTES + oct * 16);
+                      for (int q = 0; q < p.ws; ++q)
+                        *reinterpret_cast<uint4*>(p.ar_out[q] + (grow0 + rr) * p.N + col) = val;
+                    }
+                  }
+                  __syncwarp();
                 }
               }
             }
@@ -517,7 +549,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
           }
         }
       }
-      if (p.comm == COMM_RS && chunk != p.tp_rank) {
+      if (p.comm == COMM_AR && chunk == p.tp_rank) {
+        // this band of the reduced tile is in every rank's output: count the delivery on each of them
+        __threadfence_system();
+        __syncwarp();
+        if (lane < p.ws && lane != p.tp_rank)
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.ar_count[lane]) : "memory");
+      }
+      if (rs_like && chunk != p.tp_rank) {
         __threadfence_system();
         __syncwarp();
         if (lane == 0)
@@ -620,6 +659,8 @@ struct Comm2Args {
   long long ld_res2 = 0;
   const void* ag_src = nullptr;
   long long ag_ld = 0;
+  const unsigned long long* ar_out_ptrs = nullptr;     // all-reduce mode: per-rank [M, N] outputs
+  const unsigned long long* ar_count_ptrs = nullptr;   // and delivery counters
 };
 
 static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
@@ -660,9 +701,14 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
     p.tp_rank = ca.rank; p.ws = ca.ws; p.epoch = ca.epoch;
     p.tiles_m_chunk = (M / ca.ws) / (2 * BM);
     for (int i = 0; i < ca.ws; ++i) {
-      if (ca.mode == COMM_RS) {
+      if (ca.mode == COMM_RS || ca.mode == COMM_AR) {
         p.rs_stage[i] = reinterpret_cast<__nv_bfloat16*>(ca.data_ptrs[i]);
         p.rs_flags[i] = reinterpret_cast<uint32_t*>(ca.flag_ptrs[i]);
+        if (ca.mode == COMM_AR) {
+          NX_REQUIRE(ca.ar_out_ptrs != nullptr && ca.ar_count_ptrs != nullptr, "gemm2_comm: all-reduce tables are null");
+          p.ar_out[i] = reinterpret_cast<__nv_bfloat16*>(ca.ar_out_ptrs[i]);
+          p.ar_count[i] = reinterpret_cast<uint32_t*>(ca.ar_count_ptrs[i]);
+        }
       } else {
         p.ag_dst[i] = reinterpret_cast<__nv_bfloat16*>(ca.data_ptrs[i]);
         p.ag_flags[i] = reinterpret_cast<uint32_t*>(ca.flag_ptrs[i]);
@@ -672,7 +718,7 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
     p.ld_res2 = ca.ld_res2;
     p.ag_src = static_cast<const __nv_bfloat16*>(ca.ag_src);
     p.ag_ld = ca.ag_ld;
-    if (ca.mode == COMM_RS && ca.residual2 != nullptr) NX_REQUIRE(ca.ld_res2 % 8 == 0, "gemm2_comm: residual2 ld");
+    if (ca.mode != COMM_AG && ca.residual2 != nullptr) NX_REQUIRE(ca.ld_res2 % 8 == 0, "gemm2_comm: residual2 ld");
     if (ca.mode == COMM_AG) {
       NX_REQUIRE(ca.ag_src != nullptr && ca.ag_ld % 8 == 0 && K % 8 == 0 && lda == K,
                  "gemm2_comm: all-gather mode needs a dense [M, K] gather buffer and an aligned shard");
@@ -708,6 +754,35 @@ NX_API int nx_gemm2_bf16_comm(const void* A, const void* B, void* C, int M, int 
   ca.residual2 = residual2; ca.ld_res2 = ld_res2; ca.ag_src = ag_src; ca.ag_ld = ag_ld;
   return gemm2_common(A, B, C, M, N, K, lda, ldb, ldc, 0, transB, bias, aux_in, aux_out, residual, ld_aux, flags, 1.0f,
                       ca, static_cast<cudaStream_t>(stream_));
+}
+
+namespace g2 {
+// Bounded wait until the delivery counter reaches `target` (all peers' reduced tiles have landed).
+__global__ void wait_counter_kernel(const uint32_t* counter, uint32_t target, int* err) {
+  if (threadIdx.x == 0) wait_flag_ge(counter, target, err, 20);
+}
+}  // namespace g2
+
+// GEMM -> all-reduce over the rows' owners: reduce-scatter as in mode 1, then every owner writes its reduced
+// chunk (+ bias) into each rank's [M, N] output (out_ptrs, leading dimension N) and counts deliveries;
+// a one-thread kernel behind the GEMM waits (bounded) until this rank has received `count_target` bands.
+NX_API int nx_gemm2_bf16_allreduce(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                                   int transB, const void* bias, const void* residual, long long ld_aux, int flags,
+                                   int rank, int ws, unsigned int epoch, const unsigned long long* stage_ptrs,
+                                   const unsigned long long* flag_ptrs, const unsigned long long* out_ptrs,
+                                   const unsigned long long* count_ptrs, unsigned int count_target, void* stream_) {
+  Comm2Args ca;
+  ca.mode = 3; ca.rank = rank; ca.ws = ws; ca.epoch = epoch;
+  ca.data_ptrs = stage_ptrs; ca.flag_ptrs = flag_ptrs;
+  ca.ar_out_ptrs = out_ptrs; ca.ar_count_ptrs = count_ptrs;
+  void* c_local = reinterpret_cast<void*>(out_ptrs[rank]);
+  int st = gemm2_common(A, B, c_local, M, N, K, lda, ldb, N, 0, transB, bias, nullptr, nullptr, residual, ld_aux, flags,
+                        1.0f, ca, static_cast<cudaStream_t>(stream_));
+  if (st != NX_OK) return st;
+  g2::wait_counter_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(
+      reinterpret_cast<const uint32_t*>(count_ptrs[rank]), count_target, device_error_word());
+  NX_LAUNCH_CHECK();
+  return NX_OK;
 }
 
 }  // namespace nx

@@ -4,6 +4,8 @@
                  megatron/mpu/layers.py:567-576); backward = GEMM -> reduce-scatter of dX
   linear_rs      y_shard = reduce_scatter_rows(x @ W^T) + b + r   (row-parallel forward,
                  megatron/mpu/layers.py:773-779); backward = all-gather -> GEMM
+  linear_ar      y = all_reduce(x @ W^T) + b                      (row-parallel forward without sequence
+                 parallelism): reduce-scatter in the GEMM epilogue, owners store the reduced rows to all ranks
   mlp_gelu_sp    the whole MLP of a block, all-gather in front of the first GEMM and the block's
                  single reduce-scatter (GPT-J residual: attention partial sums ride along as a
                  residual of the second GEMM, megatron/model/transformer.py:1116) behind the second
@@ -106,6 +108,34 @@ class _MLPGeluSPFn(torch.autograd.Function):
         dw1 = wgrad(dpre, xf, w1) if ctx.needs_input_grad[1] else None
         db1 = colsum(dpre) if has_b1 else None
         return dx, dw1, db1, dw2, d_pf, d_bt, (g if has_rs else None), None, None
+
+
+class _LinearARFn(torch.autograd.Function):
+    """Row-parallel linear without sequence parallelism: y = all_reduce(x @ W^T) + b with the reduction
+    inside the GEMM kernel (megatron/mpu/layers.py:773-779, mappings.py:31-50).  Backward needs no
+    collective: the incoming gradient is replicated."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, be):
+        x2 = _rows(x)
+        y = be.gemm_ar(x2, w, bias=b).clone()
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias, ctx.x_shape = b is not None, x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        from .gemm import gemm
+        x2, w = ctx.saved_tensors
+        g2 = _rows(gy)
+        dx = gemm(g2, w, trans_b=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw = wgrad(g2, x2, w) if ctx.needs_input_grad[1] else None
+        db = colsum(g2) if ctx.has_bias else None
+        return dx, dw, db, None
+
+
+def linear_ar(x, w, b, be):
+    return _LinearARFn.apply(x, w, b, be)
 
 
 def ag_linear(x_shard, w, b, be):

@@ -266,6 +266,15 @@ class RowParallelLinear(nn.Module):
             b = self.bias if not self.skip_bias_add else None
             out = linear_rs(input_parallel, self.weight, b, None, be)
             return out, (self.bias if self.skip_bias_add else None)
+        if not self.sequence_parallel and not self.parallel_output and mpu.get_model_parallel_world_size() > 1 \
+                and not getattr(self, "use_fp8", False):
+            be = _fused_backend(input_parallel)
+            rows = input_parallel.numel() // input_parallel.shape[-1]
+            if be is not None and be.can_fuse_ar(rows, self.input_size_per_partition, self.output_size):
+                # all-reduce fused into the GEMM (reduce-scatter in the epilogue + owner broadcast over NVLink)
+                from ..ops.fused_tp import linear_ar
+                b = self.bias if not self.skip_bias_add else None
+                return linear_ar(input_parallel, self.weight, b, be), (self.bias if self.skip_bias_add else None)
         output_parallel = _fp8_or_bf16_linear(self, input_parallel, self.weight, None)
         if self.sequence_parallel and not self.parallel_output:
             output_ = reduce_scatter_to_sequence_parallel_region(output_parallel, seq_dim=self.seq_dim)

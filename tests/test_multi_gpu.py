@@ -65,3 +65,13 @@ def test_pipeline_parallel_2_matches_single_stage():
     # bf16 runs on a steep part of the curve (8.5 -> 5.2 in six steps) drift apart by a few percent
     assert two["losses"] == pytest.approx(one["losses"], rel=8e-2)
     assert two["losses"][-1] < two["losses"][0] - 1.0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tp2_without_sequence_parallel_matches_nccl_baseline():
+    """Tensor parallel without sequence parallelism: the row-parallel all-reduce runs inside the GEMM kernel
+    (reduce-scatter in the epilogue + owner broadcast); same loss curve as the NCCL all-reduce run."""
+    base = _run(2, "nccl_baseline", 2, 0, 6)
+    fused = _run(2, "fused", 2, 0, 6)
+    assert fused["device_error"] == 0
+    assert fused["losses"] == pytest.approx(base["losses"], rel=2e-2)
