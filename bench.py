@@ -52,7 +52,8 @@ def reference_arm(args):
     ref = os.path.join(REPO, "baseline", "_ref")
     why = None
     if not os.path.isdir(ref):
-        why = "reference not installed: baseline/_ref is absent (offline pip install of /root/reference failed or was not run)"
+        why = ("reference not installed: baseline/_ref is absent (the reference tree has no setup.py / pyproject.toml, "
+               "so the offline pip install refuses it, and its DeepSpeed runtime is not in the wheelhouse)")
     else:
         sys.path.insert(0, ref)
         try:
@@ -228,7 +229,9 @@ def main():
     l0 = LAUNCHES["n"]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    t_enq = time.perf_counter()
     run_steps(dit, args.steps, read_loss=False)
+    enqueue_ms = (time.perf_counter() - t_enq) * 1000.0 / args.steps     # host time to issue one step's work
     e1.record()
     barrier_sync()
     launches = LAUNCHES["n"] - l0
@@ -281,7 +284,7 @@ def main():
                                           + f" x dp{dp}, zero1"),
                           "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2; "
                                 "no explicit flush"},
-               "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "device_error_word": dev_err}
+               "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "host_enqueue_ms_per_step": enqueue_ms, "device_error_word": dev_err}
         print(json.dumps(out))
     if dist.is_initialized():
         dist.barrier()
