@@ -92,6 +92,20 @@ def build_data_helpers(force: bool = False) -> Path:
     return out
 
 
+def build_data_helpers_sanitized(out_dir, cxx=None) -> Path:
+    """The dataset-index builders compiled with AddressSanitizer + UBSan (host code only; the GPU pool offers
+    no compute-sanitizer).  The library must be loaded into a process that preloads the ASan runtime:
+    ``LD_PRELOAD=$(g++ -print-file-name=libasan.so)``."""
+    out = Path(out_dir) / "libneox_data_asan.so"
+    flags = [f for f in CXX_FLAGS if f not in ("-O3",)] + ["-O1", "-g", "-fsanitize=address,undefined",
+                                                         "-fno-omit-frame-pointer"]
+    cmd = [cxx or os.environ.get("CXX", "g++"), *flags, str(CSRC / "data_helpers.cpp"), "-o", str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"g++ (sanitized) failed:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
 def build_all(force: bool = False, verbose: bool = False):
     a = build_data_helpers(force)
     b = build_cuda(force, verbose)
