@@ -205,9 +205,11 @@ class ParallelSelfAttention(nn.Module):
         self.use_flash_attention = self.attention_type == "flash"
         self.sparse = self.attention_type not in ("global", "flash")
         if self.sparse:
-            raise NotImplementedError(
-                f"attention type '{self.attention_type}': block-sparse attention kernels are not built in this "
-                "framework; use 'global' or 'flash' (optionally with sliding_window_width)")
+            # block-sparse pattern as a token mask on the masked-softmax path (same function, dense FLOPs)
+            from .sparse_attention import token_mask
+            self.register_buffer("sparse_mask", token_mask(self.attention_type, neox_args.seq_length,
+                                                           neox_args.sparsity_config, seed=layer_number),
+                                 persistent=False)
         self.dropout_p = neox_args.attention_dropout
         self.attention_dropout = nn.Dropout(self.dropout_p)
         self.dense = Row(neox_args=neox_args, input_size=neox_args.hidden_size,
@@ -309,7 +311,11 @@ class ParallelSelfAttention(nn.Module):
                                     alibi=self.alibi_embed.slopes if self.pos_emb == "alibi" else None)
                 ctx = o.permute(1, 0, 2, 3).reshape(q.shape[0], q.shape[1], np_ * hn)
             else:
-                ctx = self._global_attention(q, k, v, attention_mask if not self.use_flash_attention else None)
+                mask = attention_mask if not self.use_flash_attention else None
+                if self.sparse:
+                    sk_ = k.shape[0]
+                    mask = self.sparse_mask[..., sk_ - q.shape[0]:sk_, :sk_]
+                ctx = self._global_attention(q, k, v, mask)
         # output projection; bias (and the optional residual) are applied by the caller / epilogue
         if residual is not None and ctx.is_cuda and not self.dense.sequence_parallel and \
                 mpu.get_model_parallel_world_size() == 1:

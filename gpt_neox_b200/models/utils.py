@@ -149,9 +149,10 @@ def _set_use_cache(modules, value: bool):
 
 
 def configure_sparse_attention(neox_args, attention_type, num_attention_heads, mpu_):
-    raise NotImplementedError("block-sparse attention (fixed / variable / bigbird / bslongformer / local) "
-                              "is not built in this framework")
-
+    """-> bool token mask [1, 1, seq, seq] (True = masked) of the block-sparse pattern (megatron/model/utils.py:261-361;
+    the reference returns a DeepSpeed SparseSelfAttention module, here the pattern feeds the masked-softmax path)."""
+    from .sparse_attention import token_mask
+    return token_mask(attention_type, neox_args.seq_length, neox_args.sparsity_config or {})
 
 def reduce_weight_grads_from_model_parallel_region(input_):
     """All-reduce a gradient over the tensor-parallel group (norm weights under sequence

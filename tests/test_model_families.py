@@ -60,3 +60,27 @@ def test_wkv6_kernel(T, H, N):
         s = b.grad.abs().max().item() + 1e-6
         err = (a.grad.float() - b.grad).abs().max().item()
         assert err <= 0.04 * s + 1e-2, f"grad {n}: err {err} scale {s}"
+
+
+def test_sparse_layouts_are_causal_and_have_their_patterns():
+    from gpt_neox_b200.models.sparse_attention import block_layout, token_mask
+    nb = 16
+    fixed = block_layout("sparse_fixed", nb, {"num_local_blocks": 4, "num_global_blocks": 1})
+    assert fixed[5, 4] and fixed[5, 7] and not fixed[5, 8 + 1]          # dense inside window [4, 8)
+    assert fixed[9, 3] and fixed[15, 7] and not fixed[9, 2]               # window summaries (last block) are global
+    local = block_layout("local", nb, {"num_sliding_window_blocks": 4})
+    assert local[6, 4] and local[6, 6] and not local[6, 3] and not local[6, 7]
+    bb = block_layout("bigbird", nb, {})
+    assert bb[10, 0] and bb[0, 10] and bb[10, 9] and bb[10, 11]
+    m = token_mask("bslongformer", 100, {"block": 16})
+    assert m.shape == (1, 1, 100, 100)
+    allowed = ~m[0, 0]
+    assert not torch.triu(allowed, 1).any()                               # causal
+    assert allowed.diagonal().all() and allowed[:, 0].all()               # self and the global first block
+
+
+@pytest.mark.parametrize("kind", ["local", "sparse_fixed", "sparse_variable", "bigbird", "bslongformer"])
+def test_sparse_attention_types_train_on_cpu(kind):
+    cfg = tiny_config(use_cpu_initialization=True, attention_config=[[[kind], 2]], sparsity_config={"block": 4})
+    losses = run_distributed(_train, 1, cfg, 3)[0]
+    assert all(l == l for l in losses)
