@@ -163,7 +163,7 @@ class SymmBackend:
 
     def can_fuse_ar(self, m: int, k: int, n: int) -> bool:
         from ..ops.gemm import PAIR_GEMM
-        if os.environ.get("NEOX_FUSED_AR", "0") != "1":       # opt-in until validated on more shapes
+        if os.environ.get("NEOX_FUSED_AR", "1") == "0":
             return False
         return bool(PAIR_GEMM["on"]) and m % (self.ws * 256) == 0 and self.can_fuse(m, k, n)
 

@@ -51,7 +51,11 @@ def main():
     err = _lib.read_device_error()
     if int(os.environ.get("RANK", "0")) == 0:
         zs = any(getattr(g, "zero_ws", None) is not None for g in getattr(model, "groups", []))
-        print("LOSSES " + json.dumps({"losses": losses, "device_error": err, "zero_symm": zs}), flush=True)
+        from gpt_neox_b200.comm import symm
+        tp_be = symm.backend_for(mpu.get_model_parallel_group())
+        calls = {k: getattr(tp_be, k, 0) for k in ("ag_calls", "rs_calls", "ar_calls")} if tp_be is not None else {}
+        print("LOSSES " + json.dumps({"losses": losses, "device_error": err, "zero_symm": zs, "fused_calls": calls}),
+              flush=True)
     if torch.distributed.is_initialized():
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()

@@ -71,7 +71,9 @@ def test_pipeline_parallel_2_matches_single_stage():
 def test_fused_tp2_without_sequence_parallel_matches_nccl_baseline():
     """Tensor parallel without sequence parallelism: the row-parallel all-reduce runs inside the GEMM kernel
     (reduce-scatter in the epilogue + owner broadcast); same loss curve as the NCCL all-reduce run."""
-    base = _run(2, "nccl_baseline", 2, 0, 6)
-    fused = _run(2, "fused", 2, 0, 6, env={"NEOX_FUSED_AR": "1"})
+    seq = json.dumps({"gpt_j_residual": False})       # sequential residual: every row-parallel linear all-reduces
+    base = _run(2, "nccl_baseline", 2, 0, 6, seq)
+    fused = _run(2, "fused", 2, 0, 6, seq, env={"NEOX_FUSED_AR": "1"})
     assert fused["device_error"] == 0
+    assert fused["fused_calls"]["ar_calls"] > 0                 # the fused path really ran
     assert fused["losses"] == pytest.approx(base["losses"], rel=2e-2)
