@@ -6,11 +6,12 @@
 //   * "dual" forward: the GPT-J parallel-residual block applies two different norms to the
 //     same input (megatron/model/transformer.py:1083); both outputs are produced from one
 //     read of x and one set of statistics.
-//   * backward can add an incoming residual-stream gradient (dx = dx_in + ...), so the sum of
-//     the residual path and the norm paths needs no extra pass.
+//   * backward takes both upstream gradients of a dual norm and an incoming residual-stream
+//     gradient (dx = dx_in + ...): the sum of the residual path and the two norm paths is one
+//     pass over x, dy1, dy2, dx_in.
 // Memory-bound: one block per row in forward, persistent blocks in backward (row-strided) so
 // that dgamma / dbeta accumulate in registers and are reduced across blocks by a second tiny
-// kernel through a caller-provided fp32 workspace [blocks, 2, H].
+// kernel through a caller-provided fp32 workspace [blocks, 2 or 4, H].
 #include "common.h"
 #include "ptx.cuh"
 #include "reduce.cuh"
@@ -108,56 +109,81 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
   }
 }
 
-template <bool RMS>
-__global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
-                                const __nv_bfloat16* __restrict__ x,
-                                const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
-                                const __nv_bfloat16* __restrict__ gamma,
-                                const __nv_bfloat16* __restrict__ dx_in,
-                                __nv_bfloat16* __restrict__ dx, float* __restrict__ ws,
-                                long long rows, int H) {
+// Backward of one norm (DUAL = false) or of two norms of the same input (DUAL = true: the upstream
+// gradients dy1 / dy2 meet in one dx, from one read of x and one pair of row reductions, because
+// dx is linear in w = dy1 * gamma1 + dy2 * gamma2).  Persistent blocks stride over the rows; a thread
+// owns VPT 16-byte column groups and keeps their dgamma / dbeta partial sums in registers (gamma is
+// re-read per row: it stays in L1).  VPT = 1 (64 registers, up to 1024 threads: two resident blocks per SM
+// up to H = 4096, one up to 8192) is the fast form; wider rows take 4 or 8 groups per thread.
+template <bool RMS, int VPT, bool DUAL>
+__global__ void __launch_bounds__(VPT == 1 ? 1024 : 512, 1)
+norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy1, const __nv_bfloat16* __restrict__ dy2,
+                const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean_in,
+                const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ gamma1,
+                const __nv_bfloat16* __restrict__ gamma2, const __nv_bfloat16* __restrict__ dx_in,
+                __nv_bfloat16* __restrict__ dx, float* __restrict__ ws, long long rows, int H) {
   __shared__ float sh[64];
+  constexpr int NOUT = DUAL ? 4 : 2;
   const int nv = H >> 3;
-  float dg[MAXV][8], db[MAXV][8], g[MAXV][8];
+  float dg1[VPT][8], db1[VPT][8], dg2[DUAL ? VPT : 1][8], db2[DUAL ? VPT : 1][8];
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int idx = threadIdx.x + i * blockDim.x;
+  for (int i = 0; i < VPT; ++i) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dg[i][j] = db[i][j] = 0.f;
-    if (idx < nv) unpack8(reinterpret_cast<const uint4*>(gamma)[idx], g[i]);
+    for (int j = 0; j < 8; ++j) {
+      dg1[i][j] = db1[i][j] = 0.f;
+      if (DUAL) dg2[i][j] = db2[i][j] = 0.f;
+    }
   }
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
     const float mean = RMS ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
-    float xh[MAXV][8], wdy[MAXV][8];
+    float xh[VPT][8], w[VPT][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * blockDim.x;
       if (idx < nv) {
-        float xv[8], dv[8];
-        unpack8(reinterpret_cast<const uint4*>(x + row * H)[idx], xv);
-        unpack8(reinterpret_cast<const uint4*>(dy + row * H)[idx], dv);
+        const uint4 xu = reinterpret_cast<const uint4*>(x + row * H)[idx];
+        const uint4 du = reinterpret_cast<const uint4*>(dy1 + row * H)[idx];
+        uint4 eu = make_uint4(0u, 0u, 0u, 0u);
+        if (DUAL) eu = reinterpret_cast<const uint4*>(dy2 + row * H)[idx];
+        float xv[8], dv[8], g[8];
+        unpack8(xu, xv);
+        unpack8(du, dv);
+        unpack8(reinterpret_cast<const uint4*>(gamma1)[idx], g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (xv[j] - mean) * rstd;
-          wdy[i][j] = dv[j] * g[i][j];
-          s1 += wdy[i][j] * xh[i][j];
-          s2 += wdy[i][j];
-          dg[i][j] += dv[j] * xh[i][j];
-          db[i][j] += dv[j];
+          w[i][j] = dv[j] * g[j];
+          dg1[i][j] += dv[j] * xh[i][j];
+          db1[i][j] += dv[j];
+        }
+        if (DUAL) {
+          unpack8(eu, dv);
+          unpack8(reinterpret_cast<const uint4*>(gamma2)[idx], g);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            w[i][j] += dv[j] * g[j];
+            dg2[i][j] += dv[j] * xh[i][j];
+            db2[i][j] += dv[j];
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          s1 += w[i][j] * xh[i][j];
+          s2 += w[i][j];
         }
       }
     }
     const float2 r = block_sum2(s1, s2, sh);
     const float c1 = r.x / H, c2 = RMS ? 0.f : r.y / H;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * blockDim.x;
       if (idx < nv) {
         float o[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (wdy[i][j] - c2 - xh[i][j] * c1);
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (w[i][j] - c2 - xh[i][j] * c1);
         if (dx_in != nullptr) {
           float a[8];
           unpack8(reinterpret_cast<const uint4*>(dx_in + row * H)[idx], a);
@@ -168,52 +194,56 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
       }
     }
   }
-  float* wg = ws + static_cast<long long>(blockIdx.x) * 2 * H;
+  float* wg = ws + static_cast<long long>(blockIdx.x) * NOUT * H;
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
+  for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < nv) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        wg[idx * 8 + j] = dg[i][j];
-        wg[H + idx * 8 + j] = db[i][j];
+      float4* p = reinterpret_cast<float4*>(wg + idx * 8);
+      p[0] = make_float4(dg1[i][0], dg1[i][1], dg1[i][2], dg1[i][3]);
+      p[1] = make_float4(dg1[i][4], dg1[i][5], dg1[i][6], dg1[i][7]);
+      p = reinterpret_cast<float4*>(wg + H + idx * 8);
+      p[0] = make_float4(db1[i][0], db1[i][1], db1[i][2], db1[i][3]);
+      p[1] = make_float4(db1[i][4], db1[i][5], db1[i][6], db1[i][7]);
+      if (DUAL) {
+        p = reinterpret_cast<float4*>(wg + 2 * H + idx * 8);
+        p[0] = make_float4(dg2[i][0], dg2[i][1], dg2[i][2], dg2[i][3]);
+        p[1] = make_float4(dg2[i][4], dg2[i][5], dg2[i][6], dg2[i][7]);
+        p = reinterpret_cast<float4*>(wg + 3 * H + idx * 8);
+        p[0] = make_float4(db2[i][0], db2[i][1], db2[i][2], db2[i][3]);
+        p[1] = make_float4(db2[i][4], db2[i][5], db2[i][6], db2[i][7]);
       }
     }
   }
 }
 
-// out[c] (+)= sum_b ws[b, which, c].  Block = 128 columns x 8 row groups: each thread sums every 8th
-// partial row (eight independent load chains per column instead of one long one), then the groups are
-// combined through shared memory.
+struct NormGradOut {
+  float* out[4];  // dgamma1, dbeta1, dgamma2, dbeta2 (null = not wanted)
+};
+
+// out[which][c] (+)= sum_b ws[b, which, c]; blockIdx.y = which.  Block = 128 columns x 8 row groups:
+// each thread sums every 8th partial row (eight independent load chains per column instead of one
+// long one), then the groups are combined through shared memory.
 __global__ void __launch_bounds__(1024)
-norm_param_grad_reduce(const float* __restrict__ ws, int nblocks, int H, float* __restrict__ dgamma,
-                       float* __restrict__ dbeta, int accumulate) {
-  __shared__ float sa[8][128], sb[8][128];
+norm_param_grad_reduce(const float* __restrict__ ws, int nblocks, int nout, int H, NormGradOut o,
+                       int accumulate) {
+  __shared__ float sa[8][128];
+  float* dst = o.out[blockIdx.y];
+  if (dst == nullptr) return;
   const int c = blockIdx.x * 128 + threadIdx.x;
   const int g = threadIdx.y;
-  float a = 0.f, b = 0.f;
+  float a = 0.f;
   if (c < H) {
-    for (int i = g; i < nblocks; i += 8) {
-      a += ws[static_cast<long long>(i) * 2 * H + c];
-      if (dbeta != nullptr) b += ws[static_cast<long long>(i) * 2 * H + H + c];
-    }
+    const float* src = ws + static_cast<long long>(blockIdx.y) * H + c;
+    for (int i = g; i < nblocks; i += 8) a += src[static_cast<long long>(i) * nout * H];
   }
   sa[g][threadIdx.x] = a;
-  sb[g][threadIdx.x] = b;
   __syncthreads();
   if (g == 0 && c < H) {
 #pragma unroll
-    for (int k = 1; k < 8; ++k) {
-      a += sa[k][threadIdx.x];
-      b += sb[k][threadIdx.x];
-    }
-    if (accumulate) {
-      dgamma[c] += a;
-      if (dbeta != nullptr) dbeta[c] += b;
-    } else {
-      dgamma[c] = a;
-      if (dbeta != nullptr) dbeta[c] = b;
-    }
+    for (int k = 1; k < 8; ++k) a += sa[k][threadIdx.x];
+    if (accumulate) dst[c] += a;
+    else dst[c] = a;
   }
 }
 
@@ -251,36 +281,67 @@ NX_API int nx_norm_fwd(int kind, const void* x, const void* g1, const void* b1, 
   return NX_OK;
 }
 
-// Number of persistent blocks the backward uses == rows of the fp32 workspace [blocks, 2, H].
+// Number of persistent blocks the backward uses == rows of the fp32 workspace [blocks, 2 or 4, H].
 NX_API int nx_norm_bwd_blocks(long long rows) {
-  const long long cap = static_cast<long long>(nx::sm_count()) * 4;
+  const long long cap = static_cast<long long>(nx::sm_count()) * 2;
   return static_cast<int>(rows < cap ? rows : cap);
 }
 
-// dx = dx_in (optional) + norm backward; dgamma/dbeta fp32 (dbeta may be null; accumulate != 0
-// adds into them).  ws: fp32 workspace of nx_norm_bwd_blocks(rows) * 2 * H floats.
-NX_API int nx_norm_bwd(int kind, const void* dy, const void* x, const void* mean, const void* rstd,
-                       const void* gamma, const void* dx_in, void* dx, void* dgamma, void* dbeta,
-                       void* ws, long long rows, int H, int accumulate, void* stream_) {
+namespace nx {
+template <bool RMS, int VPT, bool DUAL>
+static void launch_norm_bwd(int blocks, int threads, cudaStream_t s, const void* dy1, const void* dy2,
+                            const void* x, const void* mean, const void* rstd, const void* g1,
+                            const void* g2, const void* dx_in, void* dx, void* ws, long long rows,
+                            int H) {
+  using bf = __nv_bfloat16;
+  norm_bwd_kernel<RMS, VPT, DUAL><<<blocks, threads, 0, s>>>(
+      (const bf*)dy1, (const bf*)dy2, (const bf*)x, (const float*)mean, (const float*)rstd,
+      (const bf*)g1, (const bf*)g2, (const bf*)dx_in, (bf*)dx, (float*)ws, rows, H);
+}
+}  // namespace nx
+
+// dx = dx_in (optional) + backward of the norm(s) of x.  dy2 / gamma2 non-null: the two norms of a
+// dual forward, both gradients in one pass.  dgamma* / dbeta* fp32 (a null one is skipped;
+// accumulate != 0 adds into them).  ws: fp32 workspace of nx_norm_bwd_blocks(rows) * (dy2 ? 4 : 2) * H.
+NX_API int nx_norm_bwd(int kind, const void* dy1, const void* dy2, const void* x, const void* mean,
+                       const void* rstd, const void* gamma1, const void* gamma2, const void* dx_in,
+                       void* dx, void* dgamma1, void* dbeta1, void* dgamma2, void* dbeta2, void* ws,
+                       long long rows, int H, int accumulate, void* stream_) {
   using namespace nx;
   if (rows <= 0) return NX_OK;
   NX_REQUIRE(H % 8 == 0 && H <= 8 * MAXV * 1024, "norm: H=%d unsupported", H);
   NX_REQUIRE(ws != nullptr, "norm_bwd: workspace is null");
+  NX_REQUIRE((dy2 == nullptr) == (gamma2 == nullptr), "norm_bwd: dy2 and gamma2 go together");
   auto s = static_cast<cudaStream_t>(stream_);
-  const int t = threads_for(H);
+  const int nv = H / 8;
+  const int vpt = nv <= 1024 ? 1 : (nv <= 2048 ? 4 : 8);
+  int threads = ((nv + vpt - 1) / vpt + 31) / 32 * 32;
+  if (threads < 64) threads = 64;
   const int blocks = nx_norm_bwd_blocks(rows);
-  using bf = __nv_bfloat16;
-  if (kind == 0)
-    norm_bwd_kernel<false><<<blocks, t, 0, s>>>((const bf*)dy, (const bf*)x, (const float*)mean,
-                                                 (const float*)rstd, (const bf*)gamma,
-                                                 (const bf*)dx_in, (bf*)dx, (float*)ws, rows, H);
-  else
-    norm_bwd_kernel<true><<<blocks, t, 0, s>>>((const bf*)dy, (const bf*)x, (const float*)mean,
-                                                (const float*)rstd, (const bf*)gamma,
-                                                (const bf*)dx_in, (bf*)dx, (float*)ws, rows, H);
+  const bool dual = dy2 != nullptr, rms = kind != 0;
+#define NX_NORM_BWD(R, V, D)                                                                        \
+  launch_norm_bwd<R, V, D>(blocks, threads, s, dy1, dy2, x, mean, rstd, gamma1, gamma2, dx_in, dx, \
+                           ws, rows, H)
+#define NX_NORM_BWD_V(R, D)                  \
+  do {                                       \
+    if (vpt == 1) NX_NORM_BWD(R, 1, D);      \
+    else if (vpt == 4) NX_NORM_BWD(R, 4, D); \
+    else NX_NORM_BWD(R, 8, D);               \
+  } while (0)
+  if (rms) {
+    if (dual) NX_NORM_BWD_V(true, true);
+    else NX_NORM_BWD_V(true, false);
+  } else {
+    if (dual) NX_NORM_BWD_V(false, true);
+    else NX_NORM_BWD_V(false, false);
+  }
+#undef NX_NORM_BWD_V
+#undef NX_NORM_BWD
   NX_LAUNCH_CHECK();
-  norm_param_grad_reduce<<<(H + 127) / 128, dim3(128, 8), 0, s>>>((const float*)ws, blocks, H,
-                                                         (float*)dgamma, (float*)dbeta, accumulate);
+  const int nout = dual ? 4 : 2;
+  NormGradOut o{{(float*)dgamma1, (float*)dbeta1, (float*)dgamma2, (float*)dbeta2}};
+  norm_param_grad_reduce<<<dim3((H + 127) / 128, nout), dim3(128, 8), 0, s>>>(
+      (const float*)ws, blocks, nout, H, o, accumulate);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }

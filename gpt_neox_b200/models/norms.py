@@ -22,10 +22,13 @@ class LayerNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(self.normalized_shape))
         self.bias = nn.Parameter(torch.zeros(self.normalized_shape))
 
-    def forward(self, x):
+    def forward(self, x, carry=False):
+        """``carry``: return ``(x, y)`` with the residual stream routed through the norm's autograd node
+        (its gradient is then added inside the norm's backward kernel)."""
         n = len(self.normalized_shape)
         if n == 1:
-            return norm_ops.layer_norm(x, self.weight, self.bias, self.eps)
+            return norm_ops.layer_norm(x, self.weight, self.bias, self.eps, carry=carry)
+        assert not carry
         # multi-dim normalised shape (e.g. QK-norm over [heads, head_dim]): flatten the tail
         shp = x.shape
         flat = x.reshape(*shp[:-n], -1)
@@ -60,7 +63,11 @@ class RMSNorm(nn.Module):
         if bias:
             self.offset = nn.Parameter(torch.zeros(dim))
 
-    def forward(self, x):
+    def forward(self, x, carry=False):
+        if carry:
+            if len(self.shape_tail) == 1 and not (0.0 <= self.p <= 1.0) and not self.use_bias:
+                return norm_ops.rms_norm(x, self.scale, self.eps, carry=True)
+            return x, self.forward(x)
         n = len(self.shape_tail)
         shp = x.shape
         if n > 1:

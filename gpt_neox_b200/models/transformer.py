@@ -30,7 +30,7 @@ from ..parallel.mappings import (copy_to_model_parallel_region, gather_from_sequ
                                  reduce_from_model_parallel_region,
                                  reduce_scatter_to_sequence_parallel_region)
 from .activations import get_activation
-from .norms import LayerNorm, get_norm
+from .norms import LayerNorm, RMSNorm, get_norm
 from .positional_embeddings import AliBi, RotaryEmbedding
 
 
@@ -85,24 +85,25 @@ class ParallelMLP(nn.Module):
             return False        # fp8 GEMMs run through the per-module path
         return (not self.is_gated) and self.activation_type == "gelu" and x.is_cuda and x.dtype == torch.bfloat16
 
-    def forward(self, hidden_states, residual=None):
+    def forward(self, hidden_states, residual=None, out_bias=None):
         """-> (output without linear2's bias, that bias). ``residual`` (optional, fused path only)
-        is added inside the second GEMM's epilogue."""
+        is added inside the second GEMM's epilogue; so is ``out_bias`` (a bias vector that already
+        includes linear2's: the returned bias is then None)."""
         if self._fusable(hidden_states):
             if self.sequence_parallel:
                 x = gather_from_sequence_parallel_region(hidden_states, seq_dim=0)
             else:
                 x = copy_to_model_parallel_region(hidden_states)
             kind = "tanh" if self.bias_gelu_fusion else "erf"
-            out = fused_ops.mlp_gelu(x, self.linear1.weight, self.linear1.bias, self.linear2.weight, None,
+            out = fused_ops.mlp_gelu(x, self.linear1.weight, self.linear1.bias, self.linear2.weight, out_bias,
                                      residual=residual, kind=kind, recompute_act=self.recompute_act)
             if not self.parallel_output:
                 if self.sequence_parallel:
                     out = reduce_scatter_to_sequence_parallel_region(out, seq_dim=0)
                 else:
                     out = reduce_from_model_parallel_region(out)
-            return out, self.linear2.bias
-        assert residual is None
+            return out, (None if out_bias is not None else self.linear2.bias)
+        assert residual is None and out_bias is None
         intermediate, bias = self.linear1(hidden_states)
         if self.is_gated:
             if bias is not None:
@@ -353,7 +354,7 @@ class _LinearResidualFn(torch.autograd.Function):
             gy2 = gy2.contiguous()
         gx = gemm_op(gy2, w, trans_b=True).view(ctx.x_shape)
         gw = wgrad(gy2, x2, w)
-        return gx, gw, gy
+        return gx, gw, gy2.view(gy.shape)
 
 
 def _linear_residual(x, w, residual):
@@ -420,9 +421,12 @@ class ParallelTransformerLayer(nn.Module):
             if self.gpt_j_tied:
                 x1 = x2 = self.input_layernorm(x)
             elif self._dual_norm_ok(x):
-                x1, x2 = dual_layer_norm(x, self.input_layernorm.weight, self.input_layernorm.bias,
-                                         self.post_attention_layernorm.weight,
-                                         self.post_attention_layernorm.bias, self.input_layernorm.eps)
+                # the residual stream rides through the norm node: its gradient joins the two norm
+                # gradients inside one backward kernel
+                residual, x1, x2 = dual_layer_norm(x, self.input_layernorm.weight, self.input_layernorm.bias,
+                                                   self.post_attention_layernorm.weight,
+                                                   self.post_attention_layernorm.bias, self.input_layernorm.eps,
+                                                   carry=True)
             else:
                 x1, x2 = self.input_layernorm(x), self.post_attention_layernorm(x)
             fusable = (p == 0.0 and x.is_cuda and self.num_experts <= 1 and not self.use_cache
@@ -450,9 +454,8 @@ class ParallelTransformerLayer(nn.Module):
                 # x + attn + b_attn + mlp + b_mlp with both adds of matrices inside GEMM epilogues:
                 #   t = dense(ctx) + x ;  out = linear2(h) + t ; the two bias vectors are added once.
                 t, b_attn = self.attention(x1, attention_mask, layer_past=layer_past, residual=residual)
-                out, b_mlp = self.mlp(x2, residual=t)
-                bias = _sum_bias(b_attn, b_mlp)
-                return out if bias is None else out + bias
+                out, _ = self.mlp(x2, residual=t, out_bias=_sum_bias(b_attn, self.mlp.linear2.bias))
+                return out
             att = self.attention(x1, attention_mask, layer_past=layer_past)
             if self.use_cache:
                 attention_output, attention_bias, presents = att
@@ -465,8 +468,12 @@ class ParallelTransformerLayer(nn.Module):
             # one reduction for both branches (all-reduce, or reduce-scatter under sequence parallelism)
             return residual + (self.reduce(output) if ws > 1 else output)
         # sequential residual form
-        residual = x
-        att = self.attention(self.input_layernorm(x), attention_mask, layer_past=layer_past)
+        if (isinstance(self.input_layernorm, LayerNorm) and len(self.input_layernorm.normalized_shape) == 1) \
+                or isinstance(self.input_layernorm, RMSNorm):
+            residual, ln_out = self.input_layernorm(x, carry=True)
+        else:
+            residual, ln_out = x, self.input_layernorm(x)
+        att = self.attention(ln_out, attention_mask, layer_past=layer_past)
         if self.use_cache:
             attention_output, attention_bias, presents = att
             self.layer_past = presents

@@ -43,7 +43,7 @@ def _declare(lib):
     sig("nx_gemm2_bf16", [P, P, P, I, I, I, L, L, L, I, I, P, P, P, P, L, I, F, P])
     sig("nx_norm_fwd", [I, P, P, P, P, P, P, P, P, P, L, I, F, P])
     sig("nx_norm_bwd_blocks", [L])
-    sig("nx_norm_bwd", [I, P, P, P, P, P, P, P, P, P, P, L, I, I, P])
+    sig("nx_norm_bwd", [I, P, P, P, P, P, P, P, P, P, P, P, P, P, P, L, I, I, P])
     sig("nx_bias_act_fwd", [P, P, P, L, I, I, P])
     sig("nx_bias_act_bwd", [P, P, P, P, L, I, I, P])
     sig("nx_gated_act_fwd", [P, P, L, I, I, P])

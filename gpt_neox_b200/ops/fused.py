@@ -62,7 +62,7 @@ class _MLPGeluFn(torch.autograd.Function):
         gx = gemm(dpre, w1, trans_b=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
         gw1 = wgrad(dpre, x2, w1) if ctx.needs_input_grad[1] else None
         gb1 = colsum(dpre) if (ctx.has_b1 and ctx.needs_input_grad[2]) else None
-        gres = gy if ctx.has_res else None
+        gres = gy2.view(gy.shape) if ctx.has_res else None     # contiguous from here on down the stack
         return gx, gw1, gb1, gw2, gb2, gres, None, None
 
 

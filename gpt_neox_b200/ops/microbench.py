@@ -4,9 +4,11 @@ Times one operator with CUDA events on the launching stream (3 warm-up runs, a 2
 timed runs to flush L2, median of ``--iters``) and prints one JSON line with the achieved rate and its
 fraction of the measured peaks (``MEASURED_PEAKS.json`` beside the package when present, otherwise the
 numbers passed by ``--peak-tflops`` / ``--peak-gbs``).  ``--once`` runs the operator a few times without
-timing: the form to put under a profiler.
+timing: the form to put under a profiler.  ``--graph`` captures the operator's launches into a CUDA graph
+first and times replays of it, which takes the Python and launch overhead of a many-launch operator
+out of a microsecond-scale measurement.
 
-ops: gemm, gemm_fp8, gemm_wgrad, attn_fwd, attn_bwd, layernorm, scan_fwd, scan_bwd, conv1d, moe_fwd, moe_fwdbwd,
+ops: gemm, gemm_fp8, gemm_wgrad, attn_fwd, attn_bwd, layernorm, dual_norm_bwd, scan_fwd, scan_bwd, conv1d, moe_fwd, moe_fwdbwd,
      wkv_fwd, wkv_fwdbwd, adamw, ce   (moe: tokens = batch*seq, hidden --n, ffn --k, experts --heads, top-2)
 """
 from __future__ import annotations
@@ -91,6 +93,23 @@ def build(op, a):
         x, w, b_ = rn(a.m, a.n), rn(a.n), rn(a.n)
         fn = lambda: layer_norm(x, w, b_, 1e-5)
         return fn, 0.0, 2.0 * 2 * a.m * a.n
+    if op == "dual_norm_bwd":
+        # backward of the parallel-residual block's two LayerNorms + the residual-stream gradient:
+        # reads x, dy1, dy2, g_res and writes dx (five [m, n] bf16 passes); the kernel pair is launched
+        # directly on preallocated buffers
+        from . import _lib
+        L = _lib.lib()
+        x, g0, g1, g2, dx = (rn(a.m, a.n) for _ in range(5))
+        w1, w2 = rn(a.n), rn(a.n)
+        mean, rstd = torch.zeros(a.m, device=dev), torch.ones(a.m, device=dev)
+        blocks = L.nx_norm_bwd_blocks(a.m)
+        ws = torch.empty(blocks * 4 * a.n, device=dev)
+        dg = [torch.empty(a.n, device=dev) for _ in range(4)]
+        P = _lib.ptr
+        fn = lambda: _lib.check(L.nx_norm_bwd(0, P(g1), P(g2), P(x), P(mean), P(rstd), P(w1), P(w2), P(g0), P(dx),
+                                              P(dg[0]), P(dg[1]), P(dg[2]), P(dg[3]), P(ws), a.m, a.n, 0,
+                                              _lib.stream()), "nx_norm_bwd")
+        return fn, 0.0, 2.0 * 5 * a.m * a.n
     if op in ("scan_fwd", "scan_bwd", "conv1d"):
         from .mamba import causal_conv1d_silu, selective_scan
         B, L, D = a.batch, a.seq, a.n
@@ -182,6 +201,7 @@ def main(argv=None):
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--once", action="store_true", help="run 3 times untimed (profiler form)")
+    ap.add_argument("--graph", action="store_true", help="time replays of a CUDA graph of the operator")
     ap.add_argument("--peak-tflops", type=float, default=1590.0)
     ap.add_argument("--peak-gbs", type=float, default=6650.0)
     a = ap.parse_args(argv)
@@ -193,6 +213,14 @@ def main(argv=None):
         torch.cuda.synchronize()
         print(json.dumps({"op": a.op, "ran": 3}))
         return
+    if a.graph:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        fn = graph.replay
     ms = _time(fn, a.iters)
     tf, gbs, src = _peaks(a)
     out = {"op": a.op, "ms": round(ms, 4), "args": {k: v for k, v in vars(a).items() if k not in ("op", "once")}}

@@ -29,8 +29,12 @@ def _accum_param_grad(param: torch.Tensor, g_f32: torch.Tensor):
 
 
 class _NormFn(torch.autograd.Function):
+    """One or two norms of ``x``.  ``carry``: also return ``x`` itself as the first output, so that the
+    gradient of the residual stream flows through this node and is added inside the backward kernel
+    (no separate accumulation pass over the activations)."""
+
     @staticmethod
-    def forward(ctx, kind, x, gamma, beta, eps, gamma2, beta2):
+    def forward(ctx, kind, x, gamma, beta, eps, gamma2, beta2, carry):
         H = x.shape[-1]
         x2 = x.reshape(-1, H)
         if not x2.is_contiguous():
@@ -46,46 +50,54 @@ class _NormFn(torch.autograd.Function):
             kind, _lib.ptr(x2), _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(y1), _lib.ptr(gamma2),
             _lib.ptr(beta2), _lib.ptr(y2), _lib.ptr(mean), _lib.ptr(rstd), rows, H, float(eps),
             _lib.stream()), "nx_norm_fwd")
-        ctx.kind, ctx.dual, ctx.shape = kind, dual, x.shape
+        ctx.kind, ctx.dual, ctx.shape, ctx.carry = kind, dual, x.shape, carry
         ctx.has_beta = beta is not None
         ctx.has_beta2 = beta2 is not None
         ctx.save_for_backward(x2, gamma, gamma2, mean, rstd)
-        if dual:
-            return y1.view(x.shape), y2.view(x.shape)
-        return y1.view(x.shape)
+        outs = (y1.view(x.shape),) + ((y2.view(x.shape),) if dual else ())
+        if carry:
+            return (x2.view(x.shape),) + outs
+        return outs if dual else outs[0]
 
     @staticmethod
     def backward(ctx, *gys):
         x2, gamma, gamma2, mean, rstd = ctx.saved_tensors
         rows, H = x2.shape
         L = _lib.lib()
-        blocks = L.nx_norm_bwd_blocks(rows)
-        ws = torch.empty(blocks * 2 * H, device=x2.device, dtype=torch.float32)
-        dx = torch.empty_like(x2)
-        outs = []
-        dx_in = None
-        for gy, g, has_b in ((gys[0], gamma, ctx.has_beta),
-                             (gys[1] if ctx.dual else None, gamma2, ctx.has_beta2)):
-            if g is None:
-                continue
-            if gy is None:
-                outs.append((None, None))
-                continue
-            gy2 = gy.reshape(rows, H)
-            if not gy2.is_contiguous():
-                gy2 = gy2.contiguous()
-            dg = torch.empty(H, device=x2.device, dtype=torch.float32)
-            db = torch.empty(H, device=x2.device, dtype=torch.float32) if has_b else None
+
+        def flat(t):
+            if t is None:
+                return None
+            t = t.reshape(rows, H)
+            return t if t.is_contiguous() else t.contiguous()
+
+        gres = flat(gys[0]) if ctx.carry else None
+        gys = gys[1:] if ctx.carry else gys
+        g1 = flat(gys[0])
+        g2 = flat(gys[1]) if ctx.dual else None
+        pairs = [(g, gm, hb) for g, gm, hb in ((g1, gamma, ctx.has_beta), (g2, gamma2, ctx.has_beta2))
+                 if g is not None]
+        new = lambda: torch.empty(H, device=x2.device, dtype=torch.float32)
+        grads = {}
+        dx = gres
+        if pairs:
+            (ga, gma, hba), (gb, gmb, hbb) = pairs[0], (pairs[1] if len(pairs) == 2 else (None, None, False))
+            blocks = L.nx_norm_bwd_blocks(rows)
+            ws = torch.empty(blocks * (4 if gb is not None else 2) * H, device=x2.device, dtype=torch.float32)
+            dx = torch.empty_like(x2)
+            dga, dba = new(), (new() if hba else None)
+            dgb, dbb = (new() if gb is not None else None), (new() if hbb else None)
             LAUNCHES["n"] += 2
             _lib.check(L.nx_norm_bwd(
-                ctx.kind, _lib.ptr(gy2), _lib.ptr(x2), _lib.ptr(mean), _lib.ptr(rstd), _lib.ptr(g),
-                _lib.ptr(dx_in), _lib.ptr(dx), _lib.ptr(dg), _lib.ptr(db), _lib.ptr(ws), rows, H, 0,
-                _lib.stream()), "nx_norm_bwd")
-            dx_in = dx  # the second norm of a dual pair adds onto the first one's dx
-            outs.append((dg, db))
-        return (None, dx.view(ctx.shape) if dx_in is not None else None,
-                outs[0][0], outs[0][1], None,
-                outs[1][0] if ctx.dual else None, outs[1][1] if ctx.dual else None)
+                ctx.kind, _lib.ptr(ga), _lib.ptr(gb), _lib.ptr(x2), _lib.ptr(mean), _lib.ptr(rstd),
+                _lib.ptr(gma), _lib.ptr(gmb), _lib.ptr(gres), _lib.ptr(dx), _lib.ptr(dga), _lib.ptr(dba),
+                _lib.ptr(dgb), _lib.ptr(dbb), _lib.ptr(ws), rows, H, 0, _lib.stream()), "nx_norm_bwd")
+            grads[id(gma)] = (dga, dba)
+            if gb is not None:
+                grads[id(gmb)] = (dgb, dbb)
+        d1 = grads.get(id(gamma), (None, None))
+        d2 = grads.get(id(gamma2), (None, None)) if ctx.dual else (None, None)
+        return (None, dx.view(ctx.shape) if dx is not None else None, d1[0], d1[1], None, d2[0], d2[1], None)
 
 
 class _ParamGrad(torch.autograd.Function):
@@ -106,25 +118,34 @@ def _wrap(p):
     return None if p is None else (_ParamGrad.apply(p) if p.requires_grad else p)
 
 
-def layer_norm(x, weight, bias=None, eps: float = 1e-5):
+def layer_norm(x, weight, bias=None, eps: float = 1e-5, carry: bool = False):
+    """``carry``: return ``(x, y)``; the gradient of that ``x`` (the residual stream) is added to the
+    norm's input gradient inside the backward kernel."""
     if _cuda_ok(x):
-        return _NormFn.apply(LN, x, _wrap(weight), _wrap(bias), eps, None, None)
+        return _NormFn.apply(LN, x, _wrap(weight), _wrap(bias), eps, None, None, carry)
+    if carry:
+        return x, layer_norm(x, weight, bias, eps)
     if x.is_cuda:
         raise _lib.KernelError(f"layer_norm: CUDA path needs bf16 and H % 8 == 0, got {x.dtype} {tuple(x.shape)}")
     return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
 
 
-def dual_layer_norm(x, w1, b1, w2, b2, eps: float = 1e-5):
+def dual_layer_norm(x, w1, b1, w2, b2, eps: float = 1e-5, carry: bool = False):
     """Two LayerNorms of the same input from one pass (GPT-J parallel residual,
-    megatron/model/transformer.py:1083)."""
+    megatron/model/transformer.py:1083).  ``carry``: return ``(x, y1, y2)`` where the first output
+    stands for the residual stream; its gradient is added to the norms' input gradient inside the
+    backward kernel."""
     if _cuda_ok(x):
-        return _NormFn.apply(LN, x, _wrap(w1), _wrap(b1), eps, _wrap(w2), _wrap(b2))
-    return layer_norm(x, w1, b1, eps), layer_norm(x, w2, b2, eps)
+        return _NormFn.apply(LN, x, _wrap(w1), _wrap(b1), eps, _wrap(w2), _wrap(b2), carry)
+    y = layer_norm(x, w1, b1, eps), layer_norm(x, w2, b2, eps)
+    return (x,) + y if carry else y
 
 
-def rms_norm(x, weight, eps: float = 1e-8):
+def rms_norm(x, weight, eps: float = 1e-8, carry: bool = False):
     if _cuda_ok(x):
-        return _NormFn.apply(RMS, x, _wrap(weight), None, eps, None, None)
+        return _NormFn.apply(RMS, x, _wrap(weight), None, eps, None, None, carry)
+    if carry:
+        return x, rms_norm(x, weight, eps)
     if x.is_cuda:
         raise _lib.KernelError(f"rms_norm: CUDA path needs bf16 and H % 8 == 0, got {x.dtype}")
     dtype = x.dtype
@@ -135,5 +156,5 @@ def rms_norm(x, weight, eps: float = 1e-8):
 
 def dual_rms_norm(x, w1, w2, eps: float = 1e-8):
     if _cuda_ok(x):
-        return _NormFn.apply(RMS, x, _wrap(w1), None, eps, _wrap(w2), None)
+        return _NormFn.apply(RMS, x, _wrap(w1), None, eps, _wrap(w2), None, False)
     return rms_norm(x, w1, eps), rms_norm(x, w2, eps)

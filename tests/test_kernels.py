@@ -19,7 +19,8 @@ def bf(*shape, scale=1.0, grad=False):
     return t.requires_grad_(grad)
 
 
-@pytest.mark.parametrize("rows,H", [(7, 64), (300, 512), (1024, 2048), (33, 4096), (5, 6144)])
+@pytest.mark.parametrize("rows,H", [(7, 64), (300, 512), (1024, 2048), (33, 4096), (5, 6144), (700, 8192),
+                                     (40, 16384)])
 def test_layernorm_fwd_bwd(rows, H):
     from gpt_neox_b200.ops.norm import layer_norm
     torch.manual_seed(0)
@@ -59,6 +60,47 @@ def test_dual_layernorm_matches_two_norms():
     for i in range(2):
         assert rel(ws[i].grad, wr[i].grad) < 2e-2
         assert rel(bs[i].grad, br[i].grad) < 2e-2
+
+
+@pytest.mark.parametrize("rows,H", [(1000, 4096), (77, 6144), (300, 8192), (9, 16384), (5, 32768)])
+def test_dual_layernorm_with_residual_carry_one_backward_pass(rows, H):
+    """(x, y1, y2) = dual norm with the residual stream carried through the node: dx = g_res + both
+    norm gradients from ONE backward kernel launch."""
+    from gpt_neox_b200.ops.norm import dual_layer_norm
+    torch.manual_seed(4)
+    x = bf(rows, H, grad=True)
+    ws = [(1 + 0.1 * torch.randn(H, device=DEV)).bfloat16().requires_grad_(True) for _ in range(2)]
+    bs = [bf(H, scale=0.1, grad=True) for _ in range(2)]
+    res, y1, y2 = dual_layer_norm(x, ws[0], bs[0], ws[1], bs[1], 1e-5, carry=True)
+    g0, g1, g2 = bf(rows, H), bf(rows, H), bf(rows, H)
+    ((res * g0).sum() + (y1 * g1).sum() + (y2 * g2).sum()).backward()
+    xr = x.detach().float().requires_grad_(True)
+    wr = [w.detach().float().requires_grad_(True) for w in ws]
+    br = [b.detach().float().requires_grad_(True) for b in bs]
+    r1 = F.layer_norm(xr, (H,), wr[0], br[0], 1e-5)
+    r2 = F.layer_norm(xr, (H,), wr[1], br[1], 1e-5)
+    ((xr * g0.float()).sum() + (r1 * g1.float()).sum() + (r2 * g2.float()).sum()).backward()
+    assert torch.equal(res, x)
+    assert rel(y1, r1) < 1e-2 and rel(y2, r2) < 1e-2
+    assert rel(x.grad, xr.grad) < 2e-2
+    for i in range(2):
+        assert rel(ws[i].grad, wr[i].grad) < 2e-2
+        assert rel(bs[i].grad, br[i].grad) < 2e-2
+
+
+def test_rmsnorm_carry_adds_residual_gradient():
+    from gpt_neox_b200.ops.norm import rms_norm
+    torch.manual_seed(5)
+    rows, H = 300, 4096
+    x, w = bf(rows, H, grad=True), (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16().requires_grad_(True)
+    res, y = rms_norm(x, w, 1e-6, carry=True)
+    g0, g = bf(rows, H), bf(rows, H)
+    ((res * g0).sum() + (y * g).sum()).backward()
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = wr * (xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6))
+    ((xr * g0.float()).sum() + (yr * g.float()).sum()).backward()
+    assert rel(x.grad, xr.grad) < 2e-2
+    assert rel(w.grad, wr.grad) < 2e-2
 
 
 @pytest.mark.parametrize("rows,H", [(64, 256), (513, 4096)])
