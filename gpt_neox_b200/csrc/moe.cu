@@ -26,7 +26,7 @@ moe_hist_kernel(const long long* __restrict__ expert, int C, int E, int* __restr
   for (int i = threadIdx.x; i < E; i += MOE_BLOCK) h[i] = 0;
   __syncthreads();
   const int c = blockIdx.x * MOE_BLOCK + threadIdx.x;
-  if (c < C) atomicAdd(&h[static_cast<int>(expert[c])], 1);
+  if (c < C && expert[c] >= 0) atomicAdd(&h[static_cast<int>(expert[c])], 1);   // id < 0: not routed here
   __syncthreads();
   for (int i = threadIdx.x; i < E; i += MOE_BLOCK) hist[blockIdx.x * E + i] = h[i];
 }
@@ -64,6 +64,7 @@ moe_plan_kernel(const int* __restrict__ hist, int nblk, int E, int* __restrict__
 }
 
 // dest_row[c] = offsets[e] + base[block][e] + (copies of e earlier in this block); src_copy[dest] = c.
+// A copy with a negative expert id (expert parallelism: an expert of another rank) gets dest_row -1.
 __global__ void __launch_bounds__(MOE_BLOCK)
 moe_rank_kernel(const long long* __restrict__ expert, int C, int E, const int* __restrict__ base,
                 const int* __restrict__ offsets, int* __restrict__ dest_row, int* __restrict__ src_copy) {
@@ -83,6 +84,8 @@ moe_rank_kernel(const long long* __restrict__ expert, int C, int E, const int* _
     const int d = offsets[e] + base[blockIdx.x * E + e] + before + rank_in_warp;
     dest_row[c] = d;
     src_copy[d] = c;
+  } else if (c < C) {
+    dest_row[c] = -1;   // copy of an expert that lives on another rank
   }
 }
 

@@ -4,7 +4,8 @@ from tensor parallelism.
 Token flow per layer: route (top-k) -> sort the T*k routed copies by expert -> **all-to-all dispatch**
 over the expert-parallel group (each rank owns ``experts / ep`` experts) -> regroup received rows by
 local expert -> grouped expert MLP -> **all-to-all combine** back to the source ranks -> weighted sum of
-the k copies.  The reference instead replicates all tokens on every tensor-parallel rank, slices the
+the k copies.  On CUDA bf16 (GeLU experts) both exchanges run as peer loads inside the permutation
+kernels (ops/moe_ep.py); the NCCL / gloo all-to-all below is the general path.  The reference instead replicates all tokens on every tensor-parallel rank, slices the
 local experts' rows and variable-size all-gathers the outputs (moe.py:85-160,
 mpu/mappings.py:147-183); with EP = 1 both degenerate to the same local computation.
 """
@@ -95,6 +96,18 @@ class ParallelDroplessMLP(nn.Module):
             out = experts_gelu(x2.contiguous(), expert_weights, expert_indices, self.mlp.w1, self.mlp.w2,
                                self.num_experts, "tanh" if self.bias_gelu_fusion else "erf")
             return out.view(in_shape)
+        if (self.use_kernels and x.is_cuda and x.dtype == torch.bfloat16 and self.ep_size > 1 and not self.gated
+                and self.mlp.activation_type == "gelu" and x2.shape[1] % 8 == 0 and self.top_k <= 8
+                and self.mlp.per_expert_ff_dim % 8 == 0):
+            from ..ops import moe_ep
+            group = mpu.get_expert_parallel_group()
+            if moe_ep.enabled() and dist.get_backend(group) == "nccl":
+                # dispatch and combine as peer loads inside the permutation kernels: no NCCL all-to-all
+                # and no host read of the per-expert counts
+                out = moe_ep.experts_gelu_ep(x2.contiguous(), expert_weights, expert_indices, self.mlp.w1,
+                                             self.mlp.w2, self.num_experts, group,
+                                             "tanh" if self.bias_gelu_fusion else "erf")
+                return out.view(in_shape)
         indices, _bin_ids, tpe = self.indices_and_bins(expert_indices)
         token_of_copy = torch.div(indices, k, rounding_mode="floor")
         routed = x2.index_select(0, token_of_copy)                      # expert-sorted copies

@@ -54,7 +54,9 @@ def main():
         from gpt_neox_b200.comm import symm
         tp_be = symm.backend_for(mpu.get_model_parallel_group())
         calls = {k: getattr(tp_be, k, 0) for k in ("ag_calls", "rs_calls", "ar_calls")} if tp_be is not None else {}
-        print("LOSSES " + json.dumps({"losses": losses, "device_error": err, "zero_symm": zs, "fused_calls": calls}),
+        from gpt_neox_b200.ops import moe_ep
+        print("LOSSES " + json.dumps({"losses": losses, "device_error": err, "zero_symm": zs, "fused_calls": calls,
+                                      "moe_p2p": bool(moe_ep._WORKSPACES)}),
               flush=True)
     if torch.distributed.is_initialized():
         torch.distributed.barrier()

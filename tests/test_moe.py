@@ -102,3 +102,56 @@ def test_moe_kernel_path_matches_torch_path(T, k, E, h, ffn):
     assert rel(x.grad, xr.grad) < 3e-2 and rel(w1.grad, w1r.grad) < 3e-2 and rel(w2.grad, w2r.grad) < 3e-2
     assert rel(wts.grad, wr.grad) < 3e-2
     assert _lib.read_device_error() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ws,T,k,E,h,ffn", [(2, 200, 2, 4, 256, 512), (4, 96, 1, 8, 128, 256), (8, 64, 2, 8, 768, 1024)])
+def test_expert_parallel_peer_memory_path_matches_fp32_oracle(ws, T, k, E, h, ffn):
+    """Expert parallelism over peer memory with the ranks emulated on one GPU: ``ws`` workspaces driven in
+    lockstep phase by phase (stream order stands in for the rank barriers), against the fp32 per-expert loop
+    over all ranks' tokens.  Covers the pull-gather, the pull-combine and the routing-weight gradient."""
+    from gpt_neox_b200.ops import _lib
+    from gpt_neox_b200.ops import moe_ep as EP
+    torch.manual_seed(1)
+    dev = "cuda"
+    El = E // ws
+    w1 = (torch.randn(E * ffn, h, device=dev) * 0.05).bfloat16()
+    w2 = (torch.randn(E * ffn, h, device=dev) * 0.05).bfloat16()
+    xs = [torch.randn(T, h, device=dev).bfloat16() for _ in range(ws)]
+    routed = [torch.softmax(torch.randn(T, E, device=dev), -1).topk(k, dim=-1) for _ in range(ws)]
+    wts = [r[0].bfloat16() for r in routed]
+    idx = [r[1] for r in routed]
+    gs = [torch.randn(T, h, device=dev).bfloat16() for _ in range(ws)]
+    w1s = [w1[r * El * ffn:(r + 1) * El * ffn].contiguous() for r in range(ws)]
+    w2s = [w2[r * El * ffn:(r + 1) * El * ffn].contiguous() for r in range(ws)]
+    Ws = EP.EpWorkspace.emulated(ws, T, k, h, El)
+    ids = [i.reshape(-1).to(torch.int32) for i in idx]
+    wfs = [w.reshape(-1).contiguous() for w in wts]
+    for r in range(ws):
+        EP.fwd_publish(Ws[r], xs[r], ids[r])
+    st = [EP.fwd_experts(Ws[r], w1s[r], w2s[r], "erf") for r in range(ws)]
+    outs = [EP.fwd_combine(Ws[r], ids[r], wfs[r]) for r in range(ws)]
+    for r in range(ws):
+        EP.bwd_publish(Ws[r], gs[r], wfs[r])
+    dws = [EP.bwd_experts(Ws[r], *st[r], w1s[r], w2s[r], "erf") for r in range(ws)]
+    back = [EP.bwd_combine(Ws[r], ids[r]) for r in range(ws)]
+    # fp32 statement over the concatenated tokens
+    X = torch.cat(xs).float().requires_grad_(True)
+    Wt = torch.cat(wts).float().requires_grad_(True)
+    I = torch.cat(idx)
+    w1r, w2r = w1.float().requires_grad_(True), w2.float().requires_grad_(True)
+    ref = torch.zeros(ws * T, h, device=dev)
+    for e in range(E):
+        tok, slot = (I == e).nonzero(as_tuple=True)
+        if len(tok) == 0:
+            continue
+        hh = torch.nn.functional.gelu(X[tok] @ w1r[e * ffn:(e + 1) * ffn].t())
+        ref = ref.index_add(0, tok, (hh @ w2r[e * ffn:(e + 1) * ffn]) * Wt[tok, slot].unsqueeze(-1))
+    ref.backward(torch.cat(gs).float())
+    rel = lambda a, b: ((a.float() - b).norm() / (b.norm() + 1e-9)).item()
+    assert rel(torch.cat(outs), ref) < 2e-2
+    assert rel(torch.cat([b[0] for b in back]), X.grad) < 3e-2
+    assert rel(torch.cat([b[1].view(T, k) for b in back]), Wt.grad) < 3e-2
+    assert rel(torch.cat([d[0] for d in dws]), w1r.grad) < 3e-2
+    assert rel(torch.cat([d[1] for d in dws]), w2r.grad) < 3e-2
+    assert _lib.read_device_error() == 0

@@ -77,3 +77,18 @@ def test_fused_tp2_without_sequence_parallel_matches_nccl_baseline():
     assert fused["device_error"] == 0
     assert fused["fused_calls"]["ar_calls"] > 0                 # the fused path really ran
     assert fused["losses"] == pytest.approx(base["losses"], rel=2e-2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_2_over_peer_memory_matches_nccl_all_to_all():
+    """dMoE with two expert-parallel ranks: dispatch / combine as peer loads inside the permutation kernels
+    against the NCCL all-to-all path, same weights and batches."""
+    moe = json.dumps({"moe_num_experts": 4, "moe_top_k": 2, "moe_expert_interval": 1, "gpt_j_residual": False,
+                      "moe_expert_parallel_size": 2, "num_layers": 2, "attention_config": [[["flash"], 2]],
+                      "optimizer": {"type": "Adam", "params": {"lr": 3e-4, "betas": [0.9, 0.95], "eps": 1e-8}}})
+    nccl = _run(2, "fused", 1, 0, 6, moe, env={"NEOX_MOE_P2P": "0"})
+    p2p = _run(2, "fused", 1, 0, 6, moe, env={"NEOX_MOE_P2P": "1"})
+    assert p2p["device_error"] == 0
+    assert p2p["moe_p2p"] is True and nccl["moe_p2p"] is False
+    assert p2p["losses"] == pytest.approx(nccl["losses"], rel=2e-2)
+    assert p2p["losses"][-1] < p2p["losses"][0]
