@@ -27,6 +27,11 @@ from .loss_scaler import LossScaler, build_loss_scaler
 _ALIGN = 64  # elements: keeps every parameter 128-byte aligned inside the flat buffer (TMA needs 16)
 
 
+def _lr_mult(p) -> float:
+    """Per-parameter learning-rate multiplier (muP: 1 / width_mult for matrix-like weights under Adam)."""
+    return float(getattr(p, "lr_mult", 1.0))
+
+
 def _is_replicated(p) -> bool:
     """True for parameters that hold the same values on every tensor-parallel rank."""
     return not getattr(p, "model_parallel", False)
@@ -39,9 +44,10 @@ class FlatGroup:
         # entries: list of (param, weight_decay)
         self.dp_group, self.dp_size, self.dp_rank = dp_group, dp_size, dp_rank
         self.zero_stage = zero_stage
-        order = sorted(range(len(entries)), key=lambda i: (0 if entries[i][1] > 0 else 1,
+        order = sorted(range(len(entries)), key=lambda i: (0 if entries[i][1] > 0 else 1, entries[i][1],
                                                             1 if _is_replicated(entries[i][0]) else 0,
-                                                            1 if getattr(entries[i][0], "_norm_skip", False) else 0))
+                                                            1 if getattr(entries[i][0], "_norm_skip", False) else 0,
+                                                            _lr_mult(entries[i][0])))
         self.params = [entries[i][0] for i in order]
         self.wds = [entries[i][1] for i in order]
         self.device = self.params[0].device
@@ -66,10 +72,10 @@ class FlatGroup:
             p.data = self.flat_lp[o:o + n].view(p.shape)
             p.main_grad = self.main_grad[o:o + n].view(p.shape)
             p.grad = None
-        # regions of constant (weight decay, replicated)
+        # regions of constant (weight decay, replicated, norm-skip, learning-rate multiplier)
         self.regions = []
         for p, o, wd in zip(self.params, offs, self.wds):
-            key = (wd, _is_replicated(p), bool(getattr(p, "_norm_skip", False)))
+            key = (wd, _is_replicated(p), bool(getattr(p, "_norm_skip", False)), _lr_mult(p))
             end = o + (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
             if self.regions and self.regions[-1][2:] == key and self.regions[-1][1] == o:
                 self.regions[-1] = (self.regions[-1][0], end) + key
@@ -86,12 +92,12 @@ class FlatGroup:
             self.master = self.flat_lp[s:e].float()
         self.exp_avg = torch.zeros(self.shard_size, dtype=torch.float32, device=self.device)
         self.exp_avg_sq = torch.zeros(self.shard_size, dtype=torch.float32, device=self.device)
-        # my shard's intersections with the regions: (lo, hi, wd, replicated, norm_skip), shard-relative
+        # my shard's intersections with the regions: (lo, hi, wd, replicated, norm_skip, lr_mult), shard-relative
         self.segments = []
-        for (a, b, wd, rep, skip) in self.regions:
+        for (a, b, wd, rep, skip, lrm) in self.regions:
             lo, hi = max(a, s), min(b, e)
             if hi > lo:
-                self.segments.append((lo - s, hi - s, wd, rep, skip))
+                self.segments.append((lo - s, hi - s, wd, rep, skip, lrm))
 
     def _try_symmetric_workspace(self, grad_dtype):
         """ZeRO over peer memory: put the gradient and parameter buffers into a symmetric allocation of the
@@ -215,12 +221,12 @@ class FlatAdam:
                     for p, o, wd in zip(g.params, g.offsets, g.wds):
                         sp = torch.nn.Parameter(g.master[o:o + p.numel()].view(p.shape), requires_grad=True)
                         self._seg_params.append((g, o, o + p.numel(), sp))
-                        pgs.append({"params": [sp], "weight_decay": wd})
+                        pgs.append({"params": [sp], "weight_decay": wd, "lr_mult": _lr_mult(p)})
                     continue
-                for (lo, hi, wd, _rep, _skip) in g.segments:
+                for (lo, hi, wd, _rep, _skip, lrm) in g.segments:
                     sp = torch.nn.Parameter(g.master[lo:hi], requires_grad=True)
                     self._seg_params.append((g, lo, hi, sp))
-                    pgs.append({"params": [sp], "weight_decay": wd})
+                    pgs.append({"params": [sp], "weight_decay": wd, "lr_mult": lrm})
             self.generic = generic_cls(pgs, lr=lr, **(generic_kwargs or {}))
 
     @property
@@ -237,7 +243,7 @@ class FlatAdam:
                 self.step_count -= 1
                 return
             for pg in self.generic.param_groups:
-                pg["lr"] = lr
+                pg["lr"] = lr * pg.get("lr_mult", 1.0)
             for (g, lo, hi, sp) in self._seg_params:
                 sp.grad = (g.grad_shard()[lo:hi].float() * grad_scale[0]).view(sp.shape)
             self.generic.step()
@@ -248,10 +254,10 @@ class FlatAdam:
         for g in self.groups:
             gs = g.grad_shard()
             lp_shard = g.flat_lp[g.shard_start:g.shard_start + g.shard_size] if g.lp_dtype != torch.float32 else None
-            for (lo, hi, wd, _rep, _skip) in g.segments:
+            for (lo, hi, wd, _rep, _skip, lrm) in g.segments:
                 optim_ops.adamw_step_(g.master[lo:hi], g.exp_avg[lo:hi], g.exp_avg_sq[lo:hi], gs[lo:hi],
                                       lp_shard[lo:hi] if lp_shard is not None else None,
-                                      lr=lr, beta1=b1, beta2=b2, eps=eps, weight_decay=wd, step=self.step_count,
+                                      lr=lr * lrm, beta1=b1, beta2=b2, eps=eps, weight_decay=wd, step=self.step_count,
                                       adam_w_mode=self.adam_w_mode, grad_scale=grad_scale, skip=skip)
 
     def zero_grad(self, set_to_none=True):
@@ -300,7 +306,9 @@ class Engine(torch.nn.Module):
         for pg in param_groups:
             wd = pg.get("weight_decay", a.weight_decay)
             for p in pg["params"]:
-                (expert if getattr(p, "expert_parallel", False) else dense).append((p, wd))
+                # muP scales the decay of matrix-like weights by their width multiplier (lr * wd stays fixed)
+                (expert if getattr(p, "expert_parallel", False) else dense).append(
+                    (p, wd * float(getattr(p, "wd_mult", 1.0))))
         self.groups = []
         # one flat space per (reduction group, parameter dtype): parameters deliberately kept in fp32
         # inside a bf16 model (Mamba's A_log / D) keep their precision
@@ -399,7 +407,7 @@ class Engine(torch.nn.Module):
         tp_rank0 = mpu.get_model_parallel_rank() == 0
         for g in self.groups:
             gs = g.grad_shard()
-            for (lo, hi, _wd, rep, skip) in g.segments:
+            for (lo, hi, _wd, rep, skip, _lrm) in g.segments:
                 if skip or (rep and not tp_rank0):
                     continue   # counted by another owner (tensor-parallel replica / tied pipeline copy)
                 optim_ops.sumsq_(gs[lo:hi], self._acc)

@@ -148,7 +148,8 @@ class GPT2ModelPipe(nn.Module):
 
         def _logits_helper(embedding, lm_output):
             if a.use_mup:
-                lm_output = lm_output / self.tied_modules["embed"].word_embeddings.weight.infshape.width_mult()
+                # MuReadout for the tied read-out: the embedding matrix grows with width in its fan-in
+                lm_output = lm_output / embedding.word_embeddings.weight.infshape.width_mult()
             return parallel_lm_logits(lm_output, embedding.word_embeddings_weight, self.parallel_output,
                                       seq_parallel=a.sequence_parallel)
 

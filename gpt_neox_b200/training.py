@@ -85,7 +85,7 @@ def pretrain(neox_args):
         neox_args=neox_args, data_loaders=data_loaders)
     timers("train/valid/test data iterators").stop()
     if neox_args.use_mup and neox_args.coord_check:
-        raise NotImplementedError("muP coordinate check needs the `mup` package, which is not available here")
+        mup_coord_check(neox_args, timers, train_data_iterator)
     print_rank_0("done with setups ...")
     timers.log(["train/valid/test data loaders", "model and optimizer", "train/valid/test data iterators"])
     print_rank_0("training ...")
@@ -274,6 +274,66 @@ def forward_step(data_iterator, model, neox_args, timers, return_logits=False, i
 
 
 # ----------------------------------------------------------------------------------------- set-up
+def _mup_optimizer_kind(neox_args) -> str:
+    ot = (neox_args.optimizer_type or "adam").lower()
+    assert ot in ("adam", "sgd"), \
+        f"If use_mup == True, you must specify either the adam or sgd optimizers. You passed: {ot}"
+    return ot
+
+
+def save_base_shapes(neox_args, path, use_cache, base_shapes):
+    """Write the muP base-shapes file of this rank and stop (megatron/training.py:86-136): the model as
+    configured is the base model, a second one ``mup_width_scale`` times wider tells which dimensions grow."""
+    from . import mup
+    old = neox_args.hidden_size
+    neox_args.hidden_size = old * neox_args.mup_width_scale
+    delta = GPT2ModelPipe(neox_args=neox_args, num_tokentypes=0, parallel_output=neox_args.train_impl != "rm",
+                          topology=mpu.get_topology(), use_cache=use_cache)
+    if not neox_args.is_pipe_parallel:
+        delta = delta.to_sequential()
+    neox_args.hidden_size = old
+    print(f"saving base shapes at {path}", flush=True)
+    mup.make_base_shapes(base_shapes, mup.get_shapes(delta), savefile=path)
+    print("base shapes saved...exiting", flush=True)
+    sys.exit(1)
+
+
+def mup_coord_check(neox_args, timers, train_data_iterator):
+    """Activation scale against width, with muP and with the standard parametrisation
+    (megatron/training.py:139-171): ``coord_check_{up,sp}.<rank>.json`` (+ ``.jpg`` with matplotlib)."""
+    from . import mup
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    widths = [neox_args.num_attention_heads * (2 ** p) for p in range(2, 9)]
+    if neox_args.mup_coord_check_widths:
+        widths = list(neox_args.mup_coord_check_widths)
+
+    def lazy_model(hidden_size):
+        def gen():
+            old = neox_args.hidden_size
+            neox_args.hidden_size = hidden_size
+            try:
+                model, opt, sched, _ref = setup_model_and_optimizer(neox_args=neox_args, use_cache=False)
+            finally:
+                neox_args.hidden_size = old
+            model._coord_check_state = (opt, sched)
+            return model
+        return gen
+
+    def one_step(model):
+        opt, sched = model._coord_check_state
+        train_step(neox_args=neox_args, timers=timers, data_iterator=train_data_iterator, model=model,
+                   optimizer=opt, lr_scheduler=sched)
+
+    out = {}
+    for tag, flag in (("up", True), ("sp", False)):
+        neox_args.use_mup = flag
+        recs = mup.get_coord_data({w: lazy_model(w) for w in widths}, one_step, nsteps=neox_args.mup_coord_check_steps)
+        mup.save_coord_data(recs, f"coord_check_{tag}.{rank}")
+        out[tag] = recs
+    neox_args.use_mup = True
+    return out
+
+
 def get_model(neox_args, use_cache=False):
     """Build the model on its device in ``params_dtype``; flatten to sequential when there is no
     pipeline parallelism; ZeRO >= 2 is refused with tensor / pipeline parallelism as in the
@@ -290,8 +350,8 @@ def get_model(neox_args, use_cache=False):
         if neox_args.model_parallel_size > 1:
             print_rank_0("ZeRO stage 2/3 and model paralleism are not currently supported simultaneously")
             sys.exit()
-    old_use_mup = neox_args.use_mup
-    neox_args.use_mup = False
+    # muP: the modules read ``use_mup`` at construction (embedding multipliers, 1/d attention scale,
+    # ``mup_init_scale``); the width-dependent parts follow below, once the base shapes are attached
     model = GPT2ModelPipe(neox_args=neox_args, num_tokentypes=0, parallel_output=neox_args.train_impl != "rm",
                           topology=mpu.get_topology(), use_cache=use_cache)
     if neox_args.soft_prompt_tuning is not None and neox_args.soft_prompt_tuning.get("enabled", False):
@@ -306,9 +366,14 @@ def get_model(neox_args, use_cache=False):
                 param.requires_grad = False
     if not neox_args.is_pipe_parallel:
         model = model.to_sequential()
-    neox_args.use_mup = old_use_mup
     if neox_args.use_mup:
-        raise NotImplementedError("muP needs the `mup` package (base shapes / infshape), which is not installed")
+        from . import mup
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        base_shapes = f"{neox_args.base_shapes_file}.{rank}"
+        if neox_args.save_base_shapes:
+            save_base_shapes(neox_args, base_shapes, use_cache, mup.get_shapes(model))
+        mup.set_base_shapes(model, base_shapes)
+        mup.apply_mup(model, optimizer=_mup_optimizer_kind(neox_args))
     dev = _device()
     model = model.to(device=dev)
     for p in model.parameters():
