@@ -5,16 +5,22 @@
 // flash_attn_func with causal=True, window_size, alibi_slopes) and, for the "global" path, the
 // baddbmm -> fused softmax -> bmm chain (megatron/model/transformer.py:473-571).
 //
-// One CTA per (128 query rows, head, batch); 192 threads:
+// One CTA per (128 query rows, head, batch); 320 threads:
 //   warp 0      TMA producer: Q once, then K_j / V_j blocks of 128 keys through a 2-deep ring
 //   warp 1      tcgen05.mma issuer:  S_j = Q K_j^T  (two S buffers in TMEM, so S_{j+1} is computed
 //               while the softmax warps work on S_j),  O += P_j V_j  with P_j read from TMEM
-//   warps 2..5  softmax: thread t owns query row t; reads S from TMEM, applies scale / masks /
-//               ALiBi, online max and sum in base 2, writes P (bf16) back to TMEM, rescales the O
-//               accumulator only when the running max moved by more than 2^8 (lazy rescale),
-//               and finally normalises and stores O.
+//   warps 2..9  softmax: two warps per TMEM lane quadrant, each owning 64 of the block's 128 key
+//               columns of its 32 query rows (eight warps keep the exp2 pipe busy where four, one per
+//               scheduler, left it half idle).  A thread reads its half row of S from TMEM, applies
+//               scale / masks / ALiBi, exchanges the half-row maximum with its partner through shared
+//               memory (a tagged word polled with a bound, never a blocking barrier), keeps online max
+//               and sum in base 2, writes P (bf16) back to TMEM, rescales its half of the O columns only
+//               when the running max moved by more than 2^8 (lazy rescale), and finally normalises and
+//               stores its half of O.
 // TMEM columns: S0 [0,128) S1 [128,256) O [256,256+DP) P0 [384,448) P1 [448,512).
 // Head dims up to 128 are zero-padded to DP in {64,128} by TMA out-of-bounds fill.
+#include <cstdlib>
+
 #include "common.h"
 #include "ptx.cuh"
 
@@ -22,7 +28,7 @@ namespace nx {
 
 constexpr int ATT_BM = 128;  // query rows per CTA
 constexpr int ATT_BN = 128;  // keys per block
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;
 
 struct AttnFwdParams {
   __nv_bfloat16* o;
@@ -46,15 +52,17 @@ struct AttnSmem {
   // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2],
   // pv_done[2]  = 17 barriers, then the TMEM base word in slot 17
   static constexpr int NBAR = 18;
-  static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
+  // max / sum exchange between the two column halves: [parity][half][row] 8-byte tagged words
+  static constexpr int XCH_OFF = BAR_OFF + NBAR * 8 + 16;
+  static constexpr int TOTAL = XCH_OFF + 2 * 2 * ATT_BM * 8;
   static constexpr int DYN = TOTAL + 1024;
 };
 
 // Row maximum of raw scores (no mask, no ALiBi), four independent chains for ILP.
-__device__ __forceinline__ float row_max_plain(const uint32_t (&sv)[4][32]) {
+__device__ __forceinline__ float row_max_plain(const uint32_t (&sv)[2][32]) {
   float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < 2; ++c) {
 #pragma unroll
     for (int j = 0; j < 32; j += 4) {
       m0 = fmaxf(m0, __uint_as_float(sv[c][j]));
@@ -67,17 +75,17 @@ __device__ __forceinline__ float row_max_plain(const uint32_t (&sv)[4][32]) {
 }
 // Rewrites raw scores in place as base-2 logits: x = s * scale_log2 (+ slope2 * (col - qpos)),
 // -inf outside the live column range [lo, hi] of this block; returns the row maximum.
-// rel0 = (first column of the block) - (query position).
+// rel0 = (first column of the block) - (query position); col0 = first block column of this half row.
 template <bool ALIBI>
-__device__ __forceinline__ float prep_scores(uint32_t (&sv)[4][32], float scale_log2, float slope2,
-                                             int rel0, int lo, int hi) {
+__device__ __forceinline__ float prep_scores(uint32_t (&sv)[2][32], float scale_log2, float slope2,
+                                             int rel0, int lo, int hi, int col0) {
   float m0 = -INFINITY, m1 = -INFINITY;
   const float bias0 = ALIBI ? slope2 * static_cast<float>(rel0) : 0.f;
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < 2; ++c) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      const int idx = c * 32 + j;
+      const int idx = col0 + c * 32 + j;
       float x = __uint_as_float(sv[c][j]) * scale_log2;
       if (ALIBI) x += fmaf(slope2, static_cast<float>(idx), bias0);
       if (idx < lo || idx > hi) x = -INFINITY;
@@ -88,7 +96,31 @@ __device__ __forceinline__ float prep_scores(uint32_t (&sv)[4][32], float scale_
   return fmaxf(m0, m1);
 }
 
-template <int DP>
+// exp2 on the FMA / ALU pipes: round-to-nearest split x = n + f, f in [-0.5, 0.5], cubic for 2^f
+// (relative error 1.9e-4, below the bf16 rounding of P), n added into the exponent field.  Sharing the
+// exponentials between this and the MUFU ex2 unit, and packing P to bf16 with integer adds + a byte
+// permute instead of the float->bf16 convert (which issues on the same 16-lane pipe as ex2), unloads
+// that pipe; kept as a selectable variant.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = __fadd_rn(x, 12582912.f);  // 1.5 * 2^23: the rounded integer lands in the low mantissa bits
+  const float f = __fsub_rn(x, __fsub_rn(t, 12582912.f));
+  float q = fmaf(f, 0.05587554f, 0.24229462f);
+  q = fmaf(q, f, 0.69312727f);
+  q = fmaf(q, f, 0.99994826f);
+  return __uint_as_float(__float_as_uint(q) + (__float_as_uint(t) << 23));
+}
+// (lo, hi) -> packed bf16x2, round-half-up on the magnitude; inputs finite and non-negative.
+__device__ __forceinline__ uint32_t pack_bf16x2_alu(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
+
+// EXPV: 0 = every exp2 on the MUFU unit, convert instruction for the packing (default: fastest as measured,
+// 0.306 ms against 0.313 / 0.331 ms for batch 4, 32 heads, 2048 x 128: the softmax warps are bound by the
+// S -> P dependency chain per block, not by the MUFU pipe, so extra ALU instructions cost more than they
+// save); 1 = MUFU + integer packing; 2 = every second exp2 as the polynomial + integer packing
+// (NEOX_ATTN_EXP selects).
+template <int DP, int EXPV>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
@@ -122,10 +154,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   if (threadIdx.x == 0) {
     for (int i = 0; i < 17; ++i) {
       const bool softmax_arrives = (i >= S_EMPTY && i < S_EMPTY + 2) || (i >= P_FULL && i < P_FULL + 2);
-      mbar_init(bar0 + 8u * i, softmax_arrives ? 4 : 1);
+      mbar_init(bar0 + 8u * i, softmax_arrives ? 8 : 1);
     }
     fence_barrier_init();
   }
+  for (int i = threadIdx.x; i < 2 * 2 * ATT_BM; i += ATT_THREADS)
+    reinterpret_cast<unsigned long long*>(sgen + L::XCH_OFF)[i] = 0ull;
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -212,8 +246,27 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // which 64 of the block's 128 key columns (and which half of O)
+    const int col0 = half * 64;
     const int r = quad * 32 + lane;  // row in tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    volatile unsigned long long* xch = reinterpret_cast<volatile unsigned long long*>(sgen + L::XCH_OFF);
+    // publish `v` under tag `seq` and fetch the partner's value with the same tag (bounded poll)
+    auto exchange = [&](float v, uint32_t seq, float& other) -> bool {
+      const int par = seq & 1;
+      xch[(par * 2 + half) * ATT_BM + r] = (static_cast<unsigned long long>(seq) << 32) | __float_as_uint(v);
+      volatile unsigned long long* src = xch + (par * 2 + (half ^ 1)) * ATT_BM + r;
+      for (int spin = 0; spin < (1 << 22); ++spin) {
+        const unsigned long long w = *src;
+        if (static_cast<uint32_t>(w >> 32) == seq) {
+          other = __uint_as_float(static_cast<uint32_t>(w));
+          return true;
+        }
+        if (spin > 4096) __nanosleep(64);
+      }
+      if (p.err != nullptr) atomicExch(p.err, 22);
+      return false;
+    };
     const int qi = q0 + r;
     const int qpos = qi + off;
     float m_used = -INFINITY, l = 0.f;
@@ -225,9 +278,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       if (!mbar_wait(bar(S_FULL, st), ph, p.err, 18)) { aborted = true; break; }
       tc_fence_after_sync();
       // One read of the whole score row into registers.
-      uint32_t sv[4][32];
+      uint32_t sv[2][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(T_S + st * 128 + c * 32 + lane_off, sv[c]);
+      for (int c = 0; c < 2; ++c) tmem_ld_32x32b_x32(T_S + st * 128 + col0 + c * 32 + lane_off, sv[c]);
       tmem_ld_wait();
       // Does this block need per-element masking?  (warp-uniform decision)
       const bool need_mask = (k0 + ATT_BN > p.Sk) || (p.causal && k0 + ATT_BN - 1 > q0 + quad * 32 + off) ||
@@ -242,8 +295,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         int hi = p.Sk - k0 - 1;
         if (p.causal) hi = min(hi, -rel0);
         const int lo = p.window >= 0 ? -rel0 - p.window : -(1 << 30);
-        mx = p.alibi != nullptr ? prep_scores<true>(sv, p.scale_log2, slope2, rel0, lo, hi)
-                                : prep_scores<false>(sv, p.scale_log2, slope2, rel0, lo, hi);
+        mx = p.alibi != nullptr ? prep_scores<true>(sv, p.scale_log2, slope2, rel0, lo, hi, col0)
+                                : prep_scores<false>(sv, p.scale_log2, slope2, rel0, lo, hi, col0);
+      }
+      {
+        // the row maximum over both column halves: both partners then take identical decisions
+        float other;
+        bool ok = exchange(mx, static_cast<uint32_t>(i + 1), other);
+        if (!__all_sync(0xffffffffu, ok)) { aborted = true; break; }
+        mx = fmaxf(mx, other);
       }
       float alpha = 1.f;
       bool rescale = false;
@@ -261,7 +321,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         if (!mbar_wait(bar(PV_DONE, (i - 1) & 1), ((i - 1) >> 1) & 1, p.err, 19)) { aborted = true; break; }
         tc_fence_after_sync();
 #pragma unroll 1
-        for (int c = 0; c < DP / 32; ++c) {
+        for (int c = half * (DP / 64); c < (half + 1) * (DP / 64); ++c) {   // this half's O columns
           uint32_t ov[32];
           tmem_ld_32x32b_x32(T_O + c * 32 + lane_off, ov);
           tmem_ld_wait();
@@ -279,22 +339,24 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       const float msub = m_used == -INFINITY ? 0.f : m_used;
       float rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          float p0, p1;
+          float x0, x1;
           if (plain) {
-            p0 = exp2f(fmaf(__uint_as_float(sv[c][j]), p.scale_log2, -msub));
-            p1 = exp2f(fmaf(__uint_as_float(sv[c][j + 1]), p.scale_log2, -msub));
+            x0 = fmaf(__uint_as_float(sv[c][j]), p.scale_log2, -msub);
+            x1 = fmaf(__uint_as_float(sv[c][j + 1]), p.scale_log2, -msub);
           } else {
-            p0 = exp2f(__uint_as_float(sv[c][j]) - msub);
-            p1 = exp2f(__uint_as_float(sv[c][j + 1]) - msub);
+            x0 = __uint_as_float(sv[c][j]) - msub;
+            x1 = __uint_as_float(sv[c][j + 1]) - msub;
           }
+          const float p0 = exp2f(x0);
+          const float p1 = EXPV == 2 ? exp2_poly(x1) : exp2f(x1);
           rs[(j >> 1) & 3] += p0 + p1;
-          pk[j >> 1] = pack_bf16x2(p0, p1);
+          pk[j >> 1] = EXPV == 0 ? pack_bf16x2(p0, p1) : pack_bf16x2_alu(p0, p1);
         }
-        tmem_st_32x32b_x16(T_P + st * 64 + c * 16 + lane_off, pk);
+        tmem_st_32x32b_x16(T_P + st * 64 + half * 32 + c * 16 + lane_off, pk);
       }
       const float rowsum = (rs[0] + rs[1]) + (rs[2] + rs[3]);
       l += rowsum;
@@ -312,11 +374,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       tc_fence_after_sync();
     }
     if (!aborted) {
+      // total row sum = this half's + the partner's (same running max on both sides)
+      float other = 0.f;
+      const bool ok = exchange(l, static_cast<uint32_t>(nblk + 1), other);
+      if (!__all_sync(0xffffffffu, ok)) aborted = true;
+      l += other;
+    }
+    if (!aborted) {
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
       const bool row_ok = qi < p.Sq;
       __nv_bfloat16* orow = p.o + batch * p.o_sb + head * p.o_sh + static_cast<long long>(qi) * p.o_ss;
 #pragma unroll 1
-      for (int c = 0; c < DP / 32; ++c) {
+      for (int c = half * (DP / 64); c < (half + 1) * (DP / 64); ++c) {
         uint32_t ov[32];
         if (nblk > 0) {
           tmem_ld_32x32b_x32(T_O + c * 32 + lane_off, ov);
@@ -339,7 +408,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
           }
         }
       }
-      if (row_ok) {
+      if (row_ok && half == 0) {
         // base-2 log-sum-exp of the scaled scores; rows are padded to a multiple of 128
         const float lse2 = l > 0.f ? m_used + log2f(l) : -INFINITY;
         p.lse[(static_cast<long long>(batch) * p.H + head) * p.Sq_pad + qi] = lse2;
@@ -402,23 +471,31 @@ NX_API int nx_flash_attn_fwd(const void* q, const void* k, const void* v, void* 
   p.err = device_error_word();
   dim3 grid((Sq + ATT_BM - 1) / ATT_BM, H, B);
   auto s = (cudaStream_t)stream_;
+  static const int expv = [] {
+    const char* e = getenv("NEOX_ATTN_EXP");
+    const int v = e ? atoi(e) : 0;
+    return v < 0 || v > 2 ? 0 : v;
+  }();
+#define NX_ATTN_LAUNCH(DPV, EV)                                                                              \
+  do {                                                                                                       \
+    static bool cfg = false;                                                                                 \
+    if (!cfg) {                                                                                              \
+      NX_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<DPV, EV>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         AttnSmem<DPV>::DYN));                                               \
+      cfg = true;                                                                                            \
+    }                                                                                                        \
+    attn_fwd_kernel<DPV, EV><<<grid, ATT_THREADS, AttnSmem<DPV>::DYN, s>>>(tq, tk, tv, p);                   \
+  } while (0)
   if (D <= 64) {
-    static bool cfg = false;
-    if (!cfg) {
-      NX_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         AttnSmem<64>::DYN));
-      cfg = true;
-    }
-    attn_fwd_kernel<64><<<grid, ATT_THREADS, AttnSmem<64>::DYN, s>>>(tq, tk, tv, p);
+    if (expv == 0) NX_ATTN_LAUNCH(64, 0);
+    else if (expv == 1) NX_ATTN_LAUNCH(64, 1);
+    else NX_ATTN_LAUNCH(64, 2);
   } else {
-    static bool cfg = false;
-    if (!cfg) {
-      NX_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         AttnSmem<128>::DYN));
-      cfg = true;
-    }
-    attn_fwd_kernel<128><<<grid, ATT_THREADS, AttnSmem<128>::DYN, s>>>(tq, tk, tv, p);
+    if (expv == 0) NX_ATTN_LAUNCH(128, 0);
+    else if (expv == 1) NX_ATTN_LAUNCH(128, 1);
+    else NX_ATTN_LAUNCH(128, 2);
   }
+#undef NX_ATTN_LAUNCH
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
