@@ -99,7 +99,7 @@ class SymmBackend:
                 <= (1 << 20))
 
     def ag_gemm(self, x_shard, w, *, trans_b=False, bias=None, gelu=None, aux_out=None, dgelu_aux=None,
-                dgelu=None):
+                dgelu=None, aux_deriv=False):
         """``y = all_gather_rows(x_shard) @ op(w) (+ epilogue)``. Returns (y [M, N], gathered x [M, K]): the
         gathered matrix is a view of the symmetric gather buffer, valid until the second next call."""
         from ..ops import gemm as G
@@ -117,11 +117,10 @@ class SymmBackend:
             flags |= G.EPI_BIAS
         if gelu is not None:
             flags |= G.EPI_GELU_TANH if gelu == "tanh" else G.EPI_GELU_ERF
+        flags |= G.aux_flags(gelu, aux_out, aux_deriv, dgelu_aux, dgelu)
         if aux_out is not None:
-            flags |= G.EPI_AUX_OUT
             ld_aux = aux_out.stride(0)
         if dgelu_aux is not None:
-            flags |= G.EPI_DGELU_TANH if dgelu == "tanh" else G.EPI_DGELU_ERF
             ld_aux = dgelu_aux.stride(0)
         epoch = self._next_epoch(1)
         LAUNCHES["n"] += 1

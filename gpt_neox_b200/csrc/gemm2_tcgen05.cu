@@ -38,7 +38,9 @@ constexpr int DYN_BYTES = RS_OFFSET + RS_STAGE_BYTES + 1024;
 enum Comm : int { COMM_NONE = 0, COMM_RS = 1, COMM_AG = 2, COMM_AR = 3 };
 
 enum Epi : int { BIAS = 1, GELU_ERF = 2, GELU_TANH = 4, AUX_OUT = 8, DGELU_ERF = 16, DGELU_TANH = 32, RESIDUAL = 64,
-                 ACCUM = 128, OUT_F32 = 256, SCALE = 512 };
+                 ACCUM = 128, OUT_F32 = 256, SCALE = 512,
+                 AUX_DERIV = 1024,   // aux_out receives gelu'(pre-activation) instead of the pre-activation
+                 MUL_AUX = 2048 };   // multiply by aux_in (the stored derivative): no erf / exp in the backward epilogue
 
 struct Params {
   int M, N, K;
@@ -373,14 +375,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
+                float d[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  d[q] = v[j + q];
+                  if (flags & AUX_DERIV) {   // derivative out, activation in place (the GeLU step below is skipped)
+                    if (flags & GELU_TANH) gelu_tanh_both(v[j + q], v[j + q], d[q]);
+                    else gelu_erf_both(v[j + q], v[j + q], d[q]);
+                  }
+                }
                 uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]); o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]); o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                o.x = pack_bf16x2(d[0], d[1]); o.y = pack_bf16x2(d[2], d[3]);
+                o.z = pack_bf16x2(d[4], d[5]); o.w = pack_bf16x2(d[6], d[7]);
                 *reinterpret_cast<uint4*>(ap + j) = o;
               }
             }
           }
-          if (flags & (DGELU_ERF | DGELU_TANH)) {
+          if (flags & (DGELU_ERF | DGELU_TANH | MUL_AUX)) {
             const __nv_bfloat16* ap = p.aux_in + row * p.ld_aux + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -390,7 +401,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                   const float2 x = unpack_bf16x2(aw[q]);
-                  if (flags & DGELU_ERF) {
+                  if (flags & MUL_AUX) {
+                    v[j + 2 * q] *= x.x;
+                    v[j + 2 * q + 1] *= x.y;
+                  } else if (flags & DGELU_ERF) {
                     v[j + 2 * q] *= gelu_erf_grad(x.x);
                     v[j + 2 * q + 1] *= gelu_erf_grad(x.y);
                   } else {
@@ -401,7 +415,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
               }
             }
           }
-          if (flags & GELU_ERF) {
+          if (flags & AUX_DERIV) {
+            // activation already applied together with its derivative
+          } else if (flags & GELU_ERF) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
           } else if (flags & GELU_TANH) {
@@ -673,6 +689,11 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
   NX_REQUIRE(N % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0, "gemm2: N / lda / ldb must be multiples of 8");
   NX_REQUIRE(ldc % ((flags & OUT_F32) ? 4 : 8) == 0, "gemm2: ldc alignment");
   NX_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0, "gemm2: C must be 16-byte aligned");
+  if (flags & (DGELU_ERF | DGELU_TANH | MUL_AUX))
+    NX_REQUIRE(aux_in != nullptr && ld_aux % 8 == 0, "gemm2: aux_in is required by the epilogue flags");
+  if (flags & AUX_OUT) NX_REQUIRE(aux_out != nullptr && ld_aux % 8 == 0, "gemm2: aux_out is required by the flags");
+  if (flags & RESIDUAL) NX_REQUIRE(residual != nullptr && ld_aux % 8 == 0, "gemm2: residual is required by the flags");
+  if (flags & BIAS) NX_REQUIRE(bias != nullptr, "gemm2: bias is required by the flags");
   CUtensorMap tmA, tmB, tmA2;
   bool ok;
   if (!transA) ok = make_tma_2d(&tmA, A, M, K, lda * 2, BM, BK, 2);

@@ -44,6 +44,9 @@ enum EpiFlags : int {
   EPI_ACCUM = 128,      // C += result (read-modify-write)
   EPI_OUT_F32 = 256,    // C is fp32 instead of bf16
   EPI_SCALE = 512,      // result *= alpha (applied first)
+  EPI_AUX_DERIV = 1024, // with AUX_OUT + a GeLU flag: aux_out receives gelu'(pre-activation) instead of it, so
+                        // that the backward GEMM's epilogue is one multiply (EPI_MUL_AUX) with no erf / exp
+  EPI_MUL_AUX = 2048,   // multiply by aux_in
 };
 
 struct GemmParams {
@@ -385,16 +388,25 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
+                float d[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  d[q] = v[j + q];
+                  if (flags & EPI_AUX_DERIV) {   // derivative out, activation in place (the GeLU step below is skipped)
+                    if (flags & EPI_GELU_TANH) gelu_tanh_both(v[j + q], v[j + q], d[q]);
+                    else gelu_erf_both(v[j + q], v[j + q], d[q]);
+                  }
+                }
                 uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]);
-                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                o.x = pack_bf16x2(d[0], d[1]);
+                o.y = pack_bf16x2(d[2], d[3]);
+                o.z = pack_bf16x2(d[4], d[5]);
+                o.w = pack_bf16x2(d[6], d[7]);
                 *reinterpret_cast<uint4*>(ap + j) = o;
               }
             }
           }
-          if (flags & (EPI_DGELU_ERF | EPI_DGELU_TANH)) {
+          if (flags & (EPI_DGELU_ERF | EPI_DGELU_TANH | EPI_MUL_AUX)) {
             const __nv_bfloat16* ap = p.aux_in + row * p.ld_aux + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -404,7 +416,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                   const float2 x = unpack_bf16x2(aw[q]);
-                  if (flags & EPI_DGELU_ERF) {
+                  if (flags & EPI_MUL_AUX) {
+                    v[j + 2 * q] *= x.x;
+                    v[j + 2 * q + 1] *= x.y;
+                  } else if (flags & EPI_DGELU_ERF) {
                     v[j + 2 * q] *= gelu_erf_grad(x.x);
                     v[j + 2 * q + 1] *= gelu_erf_grad(x.y);
                   } else {
@@ -415,7 +430,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
               }
             }
           }
-          if (flags & EPI_GELU_ERF) {
+          if (flags & EPI_AUX_DERIV) {
+            // activation already applied together with its derivative
+          } else if (flags & EPI_GELU_ERF) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
           } else if (flags & EPI_GELU_TANH) {
@@ -685,7 +702,8 @@ static int gemm_common(const void* A, const void* B, void* C, int M, int N, int 
   NX_REQUIRE(ldc % ((flags & EPI_OUT_F32) ? 4 : 8) == 0, "gemm: ldc alignment");
   NX_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0, "gemm: C must be 16-byte aligned");
   if (flags & EPI_BIAS) NX_REQUIRE(bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15) == 0, "gemm: bias null/unaligned");
-  if (flags & (EPI_DGELU_ERF | EPI_DGELU_TANH)) NX_REQUIRE(aux_in != nullptr && ld_aux % 8 == 0, "gemm: aux_in");
+  if (flags & (EPI_DGELU_ERF | EPI_DGELU_TANH | EPI_MUL_AUX))
+    NX_REQUIRE(aux_in != nullptr && ld_aux % 8 == 0, "gemm: aux_in");
   if (flags & EPI_AUX_OUT) NX_REQUIRE(aux_out != nullptr && ld_aux % 8 == 0, "gemm: aux_out");
   if (flags & EPI_RESIDUAL) NX_REQUIRE(residual != nullptr && ld_aux % 8 == 0, "gemm: residual");
 

@@ -364,6 +364,29 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
   const float t = tanhf(0.79788456f * x * (1.0f + 0.044715f * x * x));
   return 0.5f * x * ((1.0f - t * t) * (0.79788456f + 0.1070322243f * x * x)) + 0.5f * (1.0f + t);
 }
+// GeLU and its derivative together, for the GEMM epilogue that stores the derivative for the backward pass.
+// erf form: the normal CDF by Abramowitz-Stegun 7.1.26 (absolute error < 1e-7), which shares its exponential
+// exp(-x^2/2) with the density term of the derivative: one ex2 + one reciprocal + a few FMAs for both values,
+// with no cancellation in the negative tail (Phi(x) = q for x < 0, 1 - q otherwise).
+__device__ __forceinline__ void gelu_erf_both(float x, float& g, float& dg) {
+  const float ay = fabsf(x) * 0.70710678118654752440f;
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, ay, 1.0f));
+  const float e = exp2f(x * x * -0.72134752044448170368f);  // exp(-x^2 / 2)
+  float poly = fmaf(t, 1.061405429f, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float q = 0.5f * poly * t * e;
+  const float cdf = x < 0.0f ? q : 1.0f - q;
+  g = x * cdf;
+  dg = fmaf(x * 0.39894228040143267794f, e, cdf);
+}
+__device__ __forceinline__ void gelu_tanh_both(float x, float& g, float& dg) {
+  const float t = tanhf(0.79788456f * x * (1.0f + 0.044715f * x * x));
+  const float h = 0.5f * (1.0f + t);
+  g = x * h;
+  dg = fmaf(0.5f * x * (1.0f - t * t), fmaf(0.1070322243f, x * x, 0.79788456f), h);
+}
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float silu_grad(float x) {
   const float s = 1.0f / (1.0f + __expf(-x));

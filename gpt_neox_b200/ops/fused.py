@@ -34,8 +34,10 @@ class _MLPGeluFn(torch.autograd.Function):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         M = x2.shape[0]
+        # aux: the pre-activation when the activation is recomputed in backward, otherwise gelu'(pre-activation)
+        # so that the backward GEMM epilogue is one multiply
         pre = torch.empty((M, w1.shape[0]), device=x.device, dtype=x.dtype)
-        h = gemm(x2, w1, bias=b1, gelu=kind, aux_out=pre)
+        h = gemm(x2, w1, bias=b1, gelu=kind, aux_out=pre, aux_deriv=not recompute_act)
         r2 = residual.reshape(M, -1) if residual is not None else None
         if r2 is not None and not r2.is_contiguous():
             r2 = r2.contiguous()
@@ -56,7 +58,7 @@ class _MLPGeluFn(torch.autograd.Function):
             from .elementwise import bias_act
             h = bias_act(pre, None, "gelu_tanh" if ctx.kind == "tanh" else "gelu")
         # d(pre) = (gy @ W2) * gelu'(pre)   -- derivative applied in the GEMM epilogue
-        dpre = gemm(gy2, w2, trans_b=True, dgelu_aux=pre, dgelu=ctx.kind)
+        dpre = gemm(gy2, w2, trans_b=True, dgelu_aux=pre, dgelu=ctx.kind if ctx.recompute_act else "mul")
         gw2 = wgrad(gy2, h, w2) if ctx.needs_input_grad[3] else None
         gb2 = colsum(gy2) if (ctx.has_b2 and ctx.needs_input_grad[4]) else None
         gx = gemm(dpre, w1, trans_b=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None

@@ -79,7 +79,7 @@ class _MLPGeluSPFn(torch.autograd.Function):
         x2 = _rows(x_shard)
         m = x2.shape[0] * be.ws
         pre = torch.empty((m, w1.shape[0]), device=x2.device, dtype=x2.dtype)
-        h, gathered = be.ag_gemm(x2, w1, bias=b1, gelu=kind, aux_out=pre)
+        h, gathered = be.ag_gemm(x2, w1, bias=b1, gelu=kind, aux_out=pre, aux_deriv=True)     # pre = gelu'(.)
         xf = gathered.clone()
         pf = _rows(partial_full) if partial_full is not None else None
         rs = _rows(res_shard) if res_shard is not None else None
@@ -98,7 +98,7 @@ class _MLPGeluSPFn(torch.autograd.Function):
         be = ctx.be
         g2 = _rows(g)
         # d(pre) = (all_gather(g) @ W2) * gelu'(pre): gather fused in front, derivative in the epilogue
-        dpre, g_full = be.ag_gemm(g2, w2, trans_b=True, dgelu_aux=pre, dgelu=ctx.kind)
+        dpre, g_full = be.ag_gemm(g2, w2, trans_b=True, dgelu_aux=pre, dgelu="mul")
         dw2 = wgrad(g_full, h, w2) if ctx.needs_input_grad[3] else None
         d_pf = g_full.clone().view(ctx.pf_shape) if has_pf else None
         # every rank adds bias_total to its own rows only; its gradient over ALL rows, divided by the

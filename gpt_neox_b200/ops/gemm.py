@@ -25,6 +25,8 @@ EPI_RESIDUAL = 64
 EPI_ACCUM = 128
 EPI_OUT_F32 = 256
 EPI_SCALE = 512
+EPI_AUX_DERIV = 1024       # aux_out receives gelu'(pre-activation) instead of the pre-activation
+EPI_MUL_AUX = 2048         # multiply by dgelu_aux as it is (a stored derivative)
 
 #: counts launches of this library's kernels (read by bench.py for its ``gpu_launches`` claim)
 LAUNCHES = {"n": 0}
@@ -39,17 +41,34 @@ def _as_2d(x: torch.Tensor) -> torch.Tensor:
     return x2
 
 
+def aux_flags(gelu, aux_out, aux_deriv, dgelu_aux, dgelu) -> int:
+    """Epilogue flags of the auxiliary operands.  ``aux_deriv``: ``aux_out`` receives gelu'(pre-activation)
+    instead of the pre-activation; the matching backward GEMM passes it as ``dgelu_aux`` with ``dgelu="mul"``,
+    so its epilogue is one multiply instead of an erf / exp evaluation per element."""
+    flags = 0
+    if aux_out is not None:
+        flags |= EPI_AUX_OUT
+        if aux_deriv:
+            assert gelu is not None, "aux_deriv needs a GeLU epilogue"
+            flags |= EPI_AUX_DERIV
+    if dgelu_aux is not None:
+        flags |= {"tanh": EPI_DGELU_TANH, "mul": EPI_MUL_AUX}.get(dgelu, EPI_DGELU_ERF)
+    return flags
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
          bias: torch.Tensor | None = None, gelu: str | None = None,
          aux_out: torch.Tensor | None = None, dgelu_aux: torch.Tensor | None = None,
          dgelu: str | None = None, residual: torch.Tensor | None = None,
          out: torch.Tensor | None = None, accumulate: bool = False,
-         out_dtype: torch.dtype = torch.bfloat16, alpha: float | None = None) -> torch.Tensor:
+         out_dtype: torch.dtype = torch.bfloat16, alpha: float | None = None,
+         aux_deriv: bool = False) -> torch.Tensor:
     """``C = epilogue(op(a) @ op(b))`` with 2-D row-major bf16 operands.
 
     ``trans_a=False``: a is [M,K]; ``True``: a is [K,M].
     ``trans_b=False``: b is [N,K] (weight layout); ``True``: b is [K,N].
-    Epilogue order: scale, +bias, store ``aux_out``, ×gelu'(``dgelu_aux``), GeLU, +residual,
+    Epilogue order: scale, +bias, store ``aux_out`` (the pre-activation, or its GeLU derivative with
+    ``aux_deriv``), ×gelu'(``dgelu_aux``) (``dgelu="mul"``: × ``dgelu_aux`` itself), GeLU, +residual,
     (+= out if ``accumulate``).
     """
     assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
@@ -84,10 +103,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
             assert t.shape == (M, N) and t.stride(1) == 1 and t.dtype == torch.bfloat16
             assert ld_aux in (0, t.stride(0)), "aux tensors must share one leading dimension"
             ld_aux = t.stride(0)
-    if aux_out is not None:
-        flags |= EPI_AUX_OUT
-    if dgelu_aux is not None:
-        flags |= EPI_DGELU_TANH if dgelu == "tanh" else EPI_DGELU_ERF
+    flags |= aux_flags(gelu, aux_out, aux_deriv, dgelu_aux, dgelu)
     if residual is not None:
         flags |= EPI_RESIDUAL
     if accumulate:

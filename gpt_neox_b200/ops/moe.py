@@ -11,8 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .gemm import EPI_ACCUM, EPI_AUX_OUT, EPI_DGELU_ERF, EPI_DGELU_TANH, EPI_GELU_ERF, EPI_GELU_TANH, \
-    EPI_OUT_F32, LAUNCHES
+from .gemm import EPI_ACCUM, EPI_GELU_ERF, EPI_GELU_TANH, EPI_OUT_F32, LAUNCHES, aux_flags
 
 
 class Plan:
@@ -67,7 +66,8 @@ def weight_grad(g, y, plan: Plan):
     return dw
 
 
-def grouped_gemm_rows(a, w, plan: Plan, n_out, *, trans_b, gelu=None, aux_out=None, dgelu_aux=None, dgelu=None):
+def grouped_gemm_rows(a, w, plan: Plan, n_out, *, trans_b, gelu=None, aux_out=None, dgelu_aux=None, dgelu=None,
+                      aux_deriv=False):
     """C[rows, n_out] = A[rows, K] x op(W_e) per 128-row tile; ``w`` stacks the experts' matrices
     ([E * n_out, K] for trans_b False, [E * K, n_out] for trans_b True)."""
     rows, K = a.shape
@@ -75,11 +75,10 @@ def grouped_gemm_rows(a, w, plan: Plan, n_out, *, trans_b, gelu=None, aux_out=No
     flags, ld_aux = 0, 0
     if gelu is not None:
         flags |= EPI_GELU_TANH if gelu == "tanh" else EPI_GELU_ERF
+    flags |= aux_flags(gelu, aux_out, aux_deriv, dgelu_aux, dgelu)
     if aux_out is not None:
-        flags |= EPI_AUX_OUT
         ld_aux = aux_out.stride(0)
     if dgelu_aux is not None:
-        flags |= EPI_DGELU_TANH if dgelu == "tanh" else EPI_DGELU_ERF
         ld_aux = dgelu_aux.stride(0)
     LAUNCHES["n"] += 1
     _lib.check(_lib.lib().nx_gemm_bf16_grouped(1, _lib.ptr(a), _lib.ptr(w), _lib.ptr(out), rows, n_out, K, a.stride(0),
@@ -119,7 +118,7 @@ class _ExpertsGeluFn(torch.autograd.Function):
         ffn = w1.shape[0] // num_experts
         xp = gather_rows(x2, plan)
         pre = torch.empty((plan.max_rows, ffn), device=x2.device, dtype=x2.dtype)
-        h = grouped_gemm_rows(xp, w1, plan, ffn, trans_b=False, gelu=kind, aux_out=pre)
+        h = grouped_gemm_rows(xp, w1, plan, ffn, trans_b=False, gelu=kind, aux_out=pre, aux_deriv=True)  # gelu'(.)
         y = grouped_gemm_rows(h, w2, plan, w2.shape[1], trans_b=True)
         wf = weights.reshape(-1).contiguous()
         out = combine(y, plan, wf)
@@ -135,7 +134,7 @@ class _ExpertsGeluFn(torch.autograd.Function):
         g = g.contiguous()
         d_w = weight_grad(g, y, plan).view(ctx.w_shape)
         dy = gather_rows(g, plan, scale=wf)                               # [rows, hidden], zero padding
-        dpre = grouped_gemm_rows(dy, w2, plan, w2.shape[0] // plan.E, trans_b=False, dgelu_aux=pre, dgelu=ctx.kind)
+        dpre = grouped_gemm_rows(dy, w2, plan, w2.shape[0] // plan.E, trans_b=False, dgelu_aux=pre, dgelu="mul")
         dw2 = grouped_wgrad(h, dy, plan, w2)
         dxp = grouped_gemm_rows(dpre, w1, plan, w1.shape[1], trans_b=True)
         dw1 = grouped_wgrad(dpre, xp, plan, w1)

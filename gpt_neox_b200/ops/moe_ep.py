@@ -155,7 +155,7 @@ def fwd_experts(W: EpWorkspace, w1, w2, kind):
     ffn = w1.shape[0] // W.e_local
     xp = W.gather(plan)
     pre = torch.empty((plan.max_rows, ffn), device=xp.device, dtype=xp.dtype)
-    h = grouped_gemm_rows(xp, w1, plan, ffn, trans_b=False, gelu=kind, aux_out=pre)
+    h = grouped_gemm_rows(xp, w1, plan, ffn, trans_b=False, gelu=kind, aux_out=pre, aux_deriv=True)   # pre = gelu'(.)
     y = grouped_gemm_rows(h, w2, plan, w2.shape[1], trans_b=True)
     W.rows.copy_(y)
     W.dest.copy_(plan.dest_row)
@@ -173,7 +173,7 @@ def bwd_publish(W: EpWorkspace, g, wf):
 
 def bwd_experts(W: EpWorkspace, plan, xp, pre, h, y, w1, w2, kind, need=(True, True)):
     dy = W.gather(plan, scaled=True, dot_with=y)            # also leaves <g, y> per row in W.aux
-    dpre = grouped_gemm_rows(dy, w2, plan, w2.shape[0] // plan.E, trans_b=False, dgelu_aux=pre, dgelu=kind)
+    dpre = grouped_gemm_rows(dy, w2, plan, w2.shape[0] // plan.E, trans_b=False, dgelu_aux=pre, dgelu="mul")
     dw2 = grouped_wgrad(h, dy, plan, w2) if need[1] else None
     dxp = grouped_gemm_rows(dpre, w1, plan, w1.shape[1], trans_b=True)
     dw1 = grouped_wgrad(dpre, xp, plan, w1) if need[0] else None
