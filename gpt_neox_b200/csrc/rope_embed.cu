@@ -57,6 +57,43 @@ __global__ void rope_kernel(const RopeArgs a) {
   }
 }
 
+// In-place form for 16-byte aligned views with r/2 a multiple of 8: a thread rotates eight (j, j + r/2)
+// pairs with two 16-byte loads and stores (the scalar kernel above moves 2 bytes per access, which costs a
+// full sector each on the 64-byte rotary slice of a head).
+__global__ void rope_vec8_kernel(const RopeArgs a) {
+  const int half = a.R >> 1;
+  const int groups = half >> 3;  // 8-wide groups per head
+  const long long total = static_cast<long long>(a.S) * a.B * a.NH * groups;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int j = static_cast<int>(i % groups) * 8;
+    long long t = i / groups;
+    const int h = static_cast<int>(t % a.NH);
+    t /= a.NH;
+    const int b = static_cast<int>(t % a.B);
+    const int s = static_cast<int>(t / a.B);
+    __nv_bfloat16* ptr = a.out + s * a.os + b * a.ob + h * a.oh;
+    const uint4 u1 = *reinterpret_cast<const uint4*>(ptr + j);
+    const uint4 u2 = *reinterpret_cast<const uint4*>(ptr + j + half);
+    const float4* cp = reinterpret_cast<const float4*>(a.cos + static_cast<long long>(a.pos0 + s) * half + j);
+    const float4* sp = reinterpret_cast<const float4*>(a.sin + static_cast<long long>(a.pos0 + s) * half + j);
+    const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const uint32_t w1[4] = {u1.x, u1.y, u1.z, u1.w}, w2[4] = {u2.x, u2.y, u2.z, u2.w};
+    uint32_t o1[4], o2[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 x1 = unpack_bf16x2(w1[q]), x2 = unpack_bf16x2(w2[q]);
+      const float sa = sn[2 * q] * a.sin_sign, sb = sn[2 * q + 1] * a.sin_sign;
+      o1[q] = pack_bf16x2(x1.x * c[2 * q] - x2.x * sa, x1.y * c[2 * q + 1] - x2.y * sb);
+      o2[q] = pack_bf16x2(x2.x * c[2 * q] + x1.x * sa, x2.y * c[2 * q + 1] + x1.y * sb);
+    }
+    *reinterpret_cast<uint4*>(ptr + j) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+    *reinterpret_cast<uint4*>(ptr + j + half) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+  }
+}
+
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids,
                                      const __nv_bfloat16* __restrict__ table,
                                      __nv_bfloat16* __restrict__ out, long long n, int H,
@@ -105,10 +142,20 @@ NX_API int nx_rope(const void* in, void* out, const void* cos, const void* sin, 
   a.S = S; a.B = B; a.NH = NH; a.D = D; a.R = R;
   a.is = is; a.ib = ib; a.ih = ih; a.os = os; a.ob = ob; a.oh = oh;
   a.pos0 = pos0; a.sin_sign = inverse ? -1.f : 1.f;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  const bool vec = in == out && (R / 2) % 8 == 0 && os % 8 == 0 && ob % 8 == 0 && oh % 8 == 0 &&
+                   (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(cos) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(sin) & 15) == 0;
+  if (vec) {
+    const long long total = static_cast<long long>(S) * B * NH * (R / 16);
+    const long long g = (total + 255) / 256;
+    rope_vec8_kernel<<<(int)(g < cap ? g : cap), 256, 0, (cudaStream_t)stream_>>>(a);
+    NX_LAUNCH_CHECK();
+    return NX_OK;
+  }
   const int per_head = (in != out) ? (R / 2 + (D - R)) : R / 2;
   const long long total = static_cast<long long>(S) * B * NH * per_head;
   long long g = (total + 255) / 256;
-  const long long cap = static_cast<long long>(sm_count()) * 16;
   rope_kernel<<<(int)(g < cap ? g : cap), 256, 0, (cudaStream_t)stream_>>>(a);
   NX_LAUNCH_CHECK();
   return NX_OK;

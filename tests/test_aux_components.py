@@ -1,4 +1,5 @@
 """Curriculum scheduler, gradient noise scale, weight server, pairwise / online datasets."""
+import os
 import pickle
 import socket
 import threading
@@ -122,3 +123,53 @@ def test_online_dataset_fetches_and_centres():
     assert a["text"].tolist() == [1, 2, 3, 0, 0, 0, 0] and a["label"].tolist()[:3] == [-100, -100, 3]
     assert a["reward"][0] == pytest.approx(-2.0) and b["reward"][0] == pytest.approx(2.0)
     assert b["raw_reward"][0] == pytest.approx(3.0)
+
+
+def test_online_data_server_feeds_the_online_dataset(tmp_path):
+    """The sampling server (toy sampler / reward, byte tokenizer) answers the OnlineDataset protocol."""
+    import importlib.util
+    import threading
+    spec = importlib.util.spec_from_file_location(
+        "online_data_server", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                           "post-training", "online_data_server.py"))
+    ods = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ods)
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200.data.online_dataset import OnlineDataset
+    srv = ods.OnlineDataServer(0, 1, ods.load_prompts(None), ods.ByteTokenizer(), ods.toy_sampler, ods.length_reward,
+                               batch_per_rank=3, num_completions=4, max_completion_len=64, base_port=0)
+    t = threading.Thread(target=srv.serve_once, daemon=True)
+    t.start()
+    mpu.destroy_model_parallel()
+    ds = OnlineDataset(num_samples=100, seq_length=48, leave_one_out=True, dataserver_ports=srv.port)
+    ds.global_rank = 0
+    item = ds[0]
+    t.join(timeout=20)
+    groups = srv.make_batch("valid")
+    srv.close()
+    assert len(ds.online_batching_data) == 3 * 4 - 1                 # 3 prompts x 4 completions, one consumed
+    assert item["text"].shape == (49,) and item["label"].shape == (49,)
+    n_prefix = int((item["label"] == -100).nonzero()[0][-1]) + 1 if (item["label"] == -100).any() else 0
+    assert n_prefix > 0 and (item["label"][:4] == -100).all()      # the prompt is masked out of the loss
+    assert len(groups) == 3 and all(len(g["completions"]) == 4 and len(g["rewards"]) == 4 for g in groups)
+
+
+def test_prepare_preference_data_writes_the_recipe_files(tmp_path):
+    import importlib.util
+    import json
+    spec = importlib.util.spec_from_file_location(
+        "prepare_preference_data", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                                "post-training", "prepare_preference_data.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    u = {"role": "user", "content": "q"}
+    good = {"chosen": [u, {"role": "assistant", "content": "a"}], "rejected": [u, {"role": "assistant", "content": "b"}]}
+    same = {"chosen": good["chosen"], "rejected": good["chosen"]}
+    src = tmp_path / "in.jsonl"
+    src.write_text("\n".join(json.dumps(r) for r in (good, same, good)) + "\n")
+    mod.main(["--input", str(src), "--out", str(tmp_path / "data"), "--name", "t", "--split", "train"])
+    rd = lambda p: [json.loads(l) for l in open(p)]
+    assert len(rd(tmp_path / "data" / "pairwise" / "t_dpo_train.jsonl")) == 2
+    assert rd(tmp_path / "data" / "sft" / "t_sft_train.jsonl")[0] == {"messages": good["chosen"]}
+    kto = rd(tmp_path / "data" / "kto" / "t_kto_train.jsonl")
+    assert [r["reward"] for r in kto] == [1, -1, 1, -1]
