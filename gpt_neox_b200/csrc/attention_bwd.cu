@@ -417,6 +417,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       if (!key_ok) hi = -(1 << 30);
       const bool need_mask = __any_sync(0xffffffffu, lo > 0 || hi < AB - 1);
       const float bias0 = slope2 * static_cast<float>(rel0);
+      const bool plain = !need_mask && p.alibi == nullptr;   // warp-uniform: no per-element compares in the hot path
 #pragma unroll 1
       for (int c = 0; c < AB / 32; ++c) {
         uint32_t sv[32], dv[32];
@@ -424,25 +425,44 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
         tmem_ld_32x32b_x32(T_DPT + c * 32 + lane_off, dv);
         tmem_ld_wait();
         uint32_t pp[16], pd[16];
+        if (plain) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 l4 = v_lse[(c * 32 + j) >> 2];
-          const float4 d4 = v_del[(c * 32 + j) >> 2];
-          const float lq[4] = {l4.x, l4.y, l4.z, l4.w}, dq_[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pr[4], ds[4];
+          for (int j = 0; j < 32; j += 4) {
+            const float4 l4 = v_lse[(c * 32 + j) >> 2];
+            const float4 d4 = v_del[(c * 32 + j) >> 2];
+            const float lq[4] = {l4.x, l4.y, l4.z, l4.w}, dq_[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pr[4], ds[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int idx = c * 32 + j + e;
-            float x = fmaf(__uint_as_float(sv[j + e]), p.scale_log2, -lq[e]);
-            if (p.alibi != nullptr) x += fmaf(-slope2, static_cast<float>(idx), bias0);
-            pr[e] = exp2f(x);
-            if (need_mask && (idx < lo || idx > hi)) pr[e] = 0.f;
-            ds[e] = pr[e] * p.scale * (__uint_as_float(dv[j + e]) - dq_[e]);
+            for (int e = 0; e < 4; ++e) {
+              pr[e] = exp2f(fmaf(__uint_as_float(sv[j + e]), p.scale_log2, -lq[e]));
+              ds[e] = pr[e] * ((__uint_as_float(dv[j + e]) - dq_[e]) * p.scale);
+            }
+            pp[j >> 1] = pack_bf16x2(pr[0], pr[1]);
+            pp[(j >> 1) + 1] = pack_bf16x2(pr[2], pr[3]);
+            pd[j >> 1] = pack_bf16x2(ds[0], ds[1]);
+            pd[(j >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
           }
-          pp[j >> 1] = pack_bf16x2(pr[0], pr[1]);
-          pp[(j >> 1) + 1] = pack_bf16x2(pr[2], pr[3]);
-          pd[j >> 1] = pack_bf16x2(ds[0], ds[1]);
-          pd[(j >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 l4 = v_lse[(c * 32 + j) >> 2];
+            const float4 d4 = v_del[(c * 32 + j) >> 2];
+            const float lq[4] = {l4.x, l4.y, l4.z, l4.w}, dq_[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pr[4], ds[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int idx = c * 32 + j + e;
+              float x = fmaf(__uint_as_float(sv[j + e]), p.scale_log2, -lq[e]);
+              if (p.alibi != nullptr) x += fmaf(-slope2, static_cast<float>(idx), bias0);
+              pr[e] = exp2f(x);
+              if (idx < lo || idx > hi) pr[e] = 0.f;
+              ds[e] = pr[e] * p.scale * (__uint_as_float(dv[j + e]) - dq_[e]);
+            }
+            pp[j >> 1] = pack_bf16x2(pr[0], pr[1]);
+            pp[(j >> 1) + 1] = pack_bf16x2(pr[2], pr[3]);
+            pd[j >> 1] = pack_bf16x2(ds[0], ds[1]);
+            pd[(j >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
+          }
         }
         tmem_st_32x32b_x16(T_ST + c * 16 + lane_off, pp);
         tmem_st_32x32b_x16(T_DPT + c * 16 + lane_off, pd);
