@@ -230,8 +230,9 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
         if (!need_mask && p.alibi == nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
-            const float p0 = exp2f(fmaf(__uint_as_float(sv[j]), p.scale_log2, -lse2)) * p.scale;
-            const float p1 = exp2f(fmaf(__uint_as_float(sv[j + 1]), p.scale_log2, -lse2)) * p.scale;
+            // the softmax scale of dS is applied once, to dQ, in the epilogue
+            const float p0 = exp2f(fmaf(__uint_as_float(sv[j]), p.scale_log2, -lse2));
+            const float p1 = exp2f(fmaf(__uint_as_float(sv[j + 1]), p.scale_log2, -lse2));
             pk[j >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[j]) - delta),
                                      p1 * (__uint_as_float(dv[j + 1]) - delta));
           }
@@ -244,7 +245,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
               const int idx = c * 32 + j + e;
               float x = fmaf(__uint_as_float(sv[j + e]), p.scale_log2,
                              fmaf(slope2, static_cast<float>(idx), bias0));
-              float pr = exp2f(x) * p.scale;
+              float pr = exp2f(x);
               if (idx < lo || idx > hi) pr = 0.f;
               ds[e] = pr * (__uint_as_float(dv[j + e]) - delta);
             }
@@ -281,11 +282,12 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             if (c * 32 + j < p.D) {
+              const float sc = p.scale;
               uint4 o4;
-              o4.x = pack_bf16x2(__uint_as_float(ov[j]), __uint_as_float(ov[j + 1]));
-              o4.y = pack_bf16x2(__uint_as_float(ov[j + 2]), __uint_as_float(ov[j + 3]));
-              o4.z = pack_bf16x2(__uint_as_float(ov[j + 4]), __uint_as_float(ov[j + 5]));
-              o4.w = pack_bf16x2(__uint_as_float(ov[j + 6]), __uint_as_float(ov[j + 7]));
+              o4.x = pack_bf16x2(__uint_as_float(ov[j]) * sc, __uint_as_float(ov[j + 1]) * sc);
+              o4.y = pack_bf16x2(__uint_as_float(ov[j + 2]) * sc, __uint_as_float(ov[j + 3]) * sc);
+              o4.z = pack_bf16x2(__uint_as_float(ov[j + 4]) * sc, __uint_as_float(ov[j + 5]) * sc);
+              o4.w = pack_bf16x2(__uint_as_float(ov[j + 6]) * sc, __uint_as_float(ov[j + 7]) * sc);
               *reinterpret_cast<uint4*>(orow + c * 32 + j) = o4;
             }
           }
@@ -435,7 +437,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               pr[e] = exp2f(fmaf(__uint_as_float(sv[j + e]), p.scale_log2, -lq[e]));
-              ds[e] = pr[e] * ((__uint_as_float(dv[j + e]) - dq_[e]) * p.scale);
+              ds[e] = pr[e] * (__uint_as_float(dv[j + e]) - dq_[e]);     // softmax scale: once, on dK, in the epilogue
             }
             pp[j >> 1] = pack_bf16x2(pr[0], pr[1]);
             pp[(j >> 1) + 1] = pack_bf16x2(pr[2], pr[3]);
@@ -456,7 +458,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
               if (p.alibi != nullptr) x += fmaf(-slope2, static_cast<float>(idx), bias0);
               pr[e] = exp2f(x);
               if (idx < lo || idx > hi) pr[e] = 0.f;
-              ds[e] = pr[e] * p.scale * (__uint_as_float(dv[j + e]) - dq_[e]);
+              ds[e] = pr[e] * (__uint_as_float(dv[j + e]) - dq_[e]);
             }
             pp[j >> 1] = pack_bf16x2(pr[0], pr[1]);
             pp[(j >> 1) + 1] = pack_bf16x2(pr[2], pr[3]);
@@ -498,11 +500,12 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (c * 32 + j < p.D) {
+                const float sc = which == 0 ? p.scale : 1.f;     // dK carries the softmax scale of dS
                 uint4 o4;
-                o4.x = pack_bf16x2(__uint_as_float(ov[j]), __uint_as_float(ov[j + 1]));
-                o4.y = pack_bf16x2(__uint_as_float(ov[j + 2]), __uint_as_float(ov[j + 3]));
-                o4.z = pack_bf16x2(__uint_as_float(ov[j + 4]), __uint_as_float(ov[j + 5]));
-                o4.w = pack_bf16x2(__uint_as_float(ov[j + 6]), __uint_as_float(ov[j + 7]));
+                o4.x = pack_bf16x2(__uint_as_float(ov[j]) * sc, __uint_as_float(ov[j + 1]) * sc);
+                o4.y = pack_bf16x2(__uint_as_float(ov[j + 2]) * sc, __uint_as_float(ov[j + 3]) * sc);
+                o4.z = pack_bf16x2(__uint_as_float(ov[j + 4]) * sc, __uint_as_float(ov[j + 5]) * sc);
+                o4.w = pack_bf16x2(__uint_as_float(ov[j + 6]) * sc, __uint_as_float(ov[j + 7]) * sc);
                 *reinterpret_cast<uint4*>(orow + c * 32 + j) = o4;
               }
             }
