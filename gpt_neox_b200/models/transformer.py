@@ -323,7 +323,6 @@ class ParallelSelfAttention(nn.Module):
             out = _linear_residual(ctx, self.dense.weight, residual)
             bias = self.dense.bias
         else:
-            assert residual is None or True
             out, bias = self.dense(ctx)
             if residual is not None:
                 out = out + residual

@@ -106,7 +106,8 @@ class SoftEmbedding(nn.Module):
             embedding, attention_mask = args
             layer_past = None
         soft = self.soft_embedding_weight.to(embedding.dtype).repeat(embedding.shape[0], 1, 1)
-        if layer_past is None or (torch.is_tensor(layer_past) and layer_past.numel() == 0) or True:
+        # the soft prompt is prepended once, on the first (cache-less) step of a generation
+        if layer_past is None or (torch.is_tensor(layer_past) and layer_past.numel() == 0):
             embedding = torch.cat((soft, embedding), dim=1)[:, : self.neox_args.seq_length]
         if in_inference and layer_past is not None:
             return embedding, layer_past, attention_mask

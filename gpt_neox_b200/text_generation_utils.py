@@ -353,8 +353,7 @@ def precompute_logits(neox_args, model):
             if logits is None:
                 continue
             lp = torch.log_softmax(logits.float(), dim=-1)
-            if neox_args.precompute_model_name is not None or True:
-                rows.append(torch.gather(lp, 2, labels.unsqueeze(-1)).squeeze(-1).cpu().numpy())
+            rows.append(torch.gather(lp, 2, labels.unsqueeze(-1)).squeeze(-1).cpu().numpy())
     if is_mp_rank_0() and rows:
         np.save(os.path.join(out_dir, f"{mdl}_ref_logp_rank{mpu.get_data_parallel_rank()}.npy"),
                 np.concatenate(rows, axis=0))
