@@ -157,6 +157,13 @@ def main():
         micro = args.micro_batch or 2
         gas = args.gas or 16
         global_batch = micro * gas * dp
+    elif "dmoe" in args.model:
+        # 125M dropless MoE: expert parallel over all GPUs (8 experts), micro-batch 8, one micro-batch per step
+        tp, dp = 1, n
+        assert 8 % n == 0, "the dMoE benchmark shards 8 experts over the GPUs"
+        micro = args.micro_batch or 8
+        gas = args.gas or 1
+        global_batch = micro * gas * dp
     else:
         tp = 1 if n == 1 else 2
         dp = n // tp
@@ -171,6 +178,8 @@ def main():
             "train_micro_batch_size_per_gpu": micro, "gradient_accumulation_steps": gas, "train_batch_size": None,
             "comm_mode": args.mode, "train_iters": total_iters, "lr_decay_iters": 143000, "log_interval": 10 ** 9,
             "make_vocab_size_divisible_by": 128 if tp <= 2 else 64}
+    if "dmoe" in args.model:
+        over["moe_expert_parallel_size"] = n
     if args.fp8:
         over.update(te_columnparallel=True, te_rowparallel=True, te_fp8_amax_history_len=16,
                     te_fp8_amax_compute_algo="max")
@@ -274,6 +283,11 @@ def main():
         tps = tokens / (dev_ms / 1000.0)
         neox_args.train_batch_size = global_batch
         tflops = get_flops(neox_args, dev_ms / 1000.0, use_checkpointing_factor=False) / 1e12
+        if "dmoe" in args.model:
+            # the dense formula counts one FFN per token; a top-k MoE layer runs k expert FFNs (active-parameter FLOPs)
+            ffn = neox_args.intermediate_size or 4 * neox_args.hidden_size
+            extra = 3 * 4.0 * neox_args.hidden_size * ffn * (neox_args.moe_top_k - 1) * neox_args.num_layers * tokens
+            tflops += extra / (dev_ms / 1000.0) / n / 1e12
         out = {"metric": "tokens_per_sec", "value": tps, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
                "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak",
                "vs_baseline": None, "dtype": "fp8" if args.fp8 else "bf16", "data": "synthetic tokens, random-init weights",
@@ -281,7 +295,7 @@ def main():
                "config": {"model": args.model, "global_batch": global_batch, "seq_len": seq, "micro_batch": micro,
                           "grad_accum": gas,
                           "parallelism": (f"tp{tp}" + ("+sp" if tp > 1 else "") + (f" x pp{pp}" if pp > 1 else "")
-                                          + f" x dp{dp}, zero1"),
+                                          + f" x dp{dp}, zero1" + (f", ep{n}" if "dmoe" in args.model else "")),
                           "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2; "
                                 "no explicit flush"},
                "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "host_enqueue_ms_per_step": enqueue_ms, "device_error_word": dev_err}
