@@ -67,7 +67,8 @@ def reference_arm(args):
                 why = f"reference package does not import on this image: {type(e).__name__}: {e}"
     if why is None:
         why = "reference entry point train.py hard-requires its DeepSpeed launcher; not runnable here"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if int(os.environ.get("RANK", "0")) == 0:          # one line per job, also when launched by torchrun
+        print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
 
