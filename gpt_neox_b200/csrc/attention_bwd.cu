@@ -60,6 +60,41 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
   if (lane == 0) delta[(static_cast<long long>(b) * H + h) * Sq_pad + q] = s;
 }
 
+// Same for head dims 64 / 128 with 16-byte aligned rows: a group of D/8 lanes reads one row with one 16-byte
+// load per lane and tensor, so a warp covers 32 / (D/8) rows per pass (the scalar-pair form above moves
+// 4 bytes per lane and load).
+template <int LPR>   // lanes per row = D / 8, a power of two
+__global__ void attn_delta_vec8_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dO,
+                                       float* __restrict__ delta, int B, int H, int Sq, int Sq_pad, long long o_sb,
+                                       long long o_sh, long long o_ss, long long d_sb, long long d_sh,
+                                       long long d_ss) {
+  constexpr int RPW = 32 / LPR;  // rows per warp
+  const int lane = threadIdx.x & 31;
+  const long long warp = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long row = warp * RPW + lane / LPR;
+  const long long total = static_cast<long long>(B) * H * Sq;
+  float s = 0.f;
+  int q = 0, h = 0, b = 0;
+  const bool live = row < total;
+  if (live) {
+    q = static_cast<int>(row % Sq);
+    h = static_cast<int>((row / Sq) % H);
+    b = static_cast<int>(row / (static_cast<long long>(Sq) * H));
+    const int c = (lane % LPR) * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(o + b * o_sb + h * o_sh + q * o_ss + c);
+    const uint4 g = *reinterpret_cast<const uint4*>(dO + b * d_sb + h * d_sh + q * d_ss + c);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 x = unpack_bf16x2(aw[k]), y = unpack_bf16x2(gw[k]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+#pragma unroll
+  for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (live && (lane % LPR) == 0) delta[(static_cast<long long>(b) * H + h) * Sq_pad + q] = s;
+}
+
 template <int DP>
 struct BwdSmem {
   static constexpr int TILE = AB * DP * 2;
@@ -582,9 +617,26 @@ NX_API int nx_flash_attn_bwd(const void* q, const void* k, const void* v, const 
   {
     const long long rows = static_cast<long long>(B) * H * Sq;
     const int wpb = 8;
-    attn_delta_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, s>>>(
-        (const __nv_bfloat16*)o, (const __nv_bfloat16*)dO, (float*)delta, B, H, Sq, (Sq + AB - 1) / AB * AB, D, o_sb, o_sh, o_ss,
-        do_sb, do_sh, do_ss);
+    const int sq_pad = (Sq + AB - 1) / AB * AB;
+    const bool aligned = ((o_sb | o_sh | o_ss | do_sb | do_sh | do_ss) % 8) == 0 &&
+                         ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(dO)) & 15) == 0;
+    if (aligned && (D == 128 || D == 64)) {
+      const int rpw = D == 128 ? 2 : 4;
+      const long long warps = (rows + rpw - 1) / rpw;
+      const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
+      if (D == 128)
+        attn_delta_vec8_kernel<16><<<grid, wpb * 32, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dO,
+                                                            (float*)delta, B, H, Sq, sq_pad, o_sb, o_sh, o_ss, do_sb,
+                                                            do_sh, do_ss);
+      else
+        attn_delta_vec8_kernel<8><<<grid, wpb * 32, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dO,
+                                                           (float*)delta, B, H, Sq, sq_pad, o_sb, o_sh, o_ss, do_sb,
+                                                           do_sh, do_ss);
+    } else {
+      attn_delta_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, s>>>(
+          (const __nv_bfloat16*)o, (const __nv_bfloat16*)dO, (float*)delta, B, H, Sq, sq_pad, D, o_sb, o_sh, o_ss,
+          do_sb, do_sh, do_ss);
+    }
     NX_LAUNCH_CHECK();
   }
   CUtensorMap tq, tk, tv, tdo;
