@@ -168,7 +168,11 @@ def get_batch(neox_args, data_iterator):
     neg = g(keys=keys[1], label_mask_zero=True)
     ref = mpu.broadcast_data(["pos_ref", "neg_ref"], data, torch.float) if neox_args.precompute_model_name \
         else {"pos_ref": None}
-    out = [torch.cat((p, n), dim=0) if p is not None else None for p, n in zip(pos, neg)]
+    # tokens / labels / loss mask / position ids are stacked [chosen; rejected]; the causal attention mask is one
+    # batch-broadcast [1, 1, s, s] tensor and stays that way (stacking two of them would not broadcast against
+    # the doubled batch on the non-flash attention path)
+    out = [None if p is None else (p if (i == 3 and p.shape[0] == 1) else torch.cat((p, n), dim=0))
+           for i, (p, n) in enumerate(zip(pos, neg))]
     out.append(torch.cat((ref["pos_ref"], ref["neg_ref"]), dim=0)[:, :-1].contiguous()
                if ref["pos_ref"] is not None else None)
     return out
