@@ -1,0 +1,64 @@
+"""fp16 loss scaling: the dynamic scaler's schedule and the engine skipping a step on overflow
+(reference behaviour: DeepSpeed's DynamicLossScaler driven by the `fp16` config block)."""
+import pytest
+import torch
+
+from common import run_distributed, tiny_config
+from gpt_neox_b200.engine.loss_scaler import DynamicLossScaler, LossScaler, build_loss_scaler
+
+
+def test_static_and_dynamic_construction():
+    s = build_loss_scaler({"loss_scale": 128})
+    assert isinstance(s, LossScaler) and not s.dynamic and s.cur_scale == 128.0
+    d = build_loss_scaler({"loss_scale": 0, "initial_scale_power": 12, "loss_scale_window": 4, "hysteresis": 2,
+                           "min_loss_scale": 1})
+    assert isinstance(d, DynamicLossScaler) and d.cur_scale == 4096.0
+
+
+def test_dynamic_scaler_schedule():
+    d = DynamicLossScaler(init_scale=1024, scale_window=3, min_scale=64, hysteresis=2)
+    d.update_scale(True)                  # first overflow is absorbed by the hysteresis
+    assert d.cur_scale == 1024
+    d.update_scale(True)                  # second one halves
+    assert d.cur_scale == 512
+    for _ in range(2):
+        d.update_scale(False)
+    assert d.cur_scale == 512
+    d.update_scale(False)                 # third clean step since the overflow: double
+    assert d.cur_scale == 1024
+    for _ in range(20):                   # never below the floor
+        d.update_scale(True)
+    assert d.cur_scale == 64
+    sd = d.state_dict()
+    e = DynamicLossScaler(init_scale=1, scale_window=3, min_scale=64, hysteresis=2)
+    e.load_state_dict(sd)
+    assert e.cur_scale == 64 and e.cur_iter == d.cur_iter
+
+
+def _train(rank, world, cfg, steps):
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    torch.set_num_threads(1)
+    mpu.destroy_model_parallel()
+    a = NeoXArgs.from_dict(dict(cfg, global_num_gpus=world, train_iters=steps))
+    a.configure_distributed_args()
+    a.build_tokenizer()
+    losses = []
+    training.collect_loss_for_unit_test = lambda l: losses.append(float(l))
+    model = training.pretrain(a)
+    return {"losses": losses, "skipped": model.skipped_steps, "scale": model.loss_scaler.cur_scale,
+            "steps": model.global_steps}
+
+
+def test_fp16_training_skips_overflowing_steps_and_recovers():
+    """Start with an absurd loss scale: the first steps overflow in fp16, are skipped (weights untouched) and halve
+    the scale until gradients are finite; training then proceeds."""
+    cfg = tiny_config(use_cpu_initialization=True, precision="fp16",
+                      fp16={"enabled": True, "loss_scale": 0, "initial_scale_power": 26, "loss_scale_window": 1000,
+                            "hysteresis": 1, "min_loss_scale": 1})
+    r = run_distributed(_train, 1, cfg, 24)[0]
+    assert r["skipped"] >= 3 and r["skipped"] < 24
+    assert r["scale"] == 2.0 ** 26 / 2 ** r["skipped"]
+    assert all(l == l for l in r["losses"])
+    assert r["losses"][-1] < r["losses"][0]
