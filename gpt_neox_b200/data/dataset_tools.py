@@ -31,7 +31,7 @@ def merge(input_dir: str, output_prefix: str):
         if builder is None:
             first = indexed_dataset.make_dataset(pfx, "mmap", skip_warmup=True)
             builder = indexed_dataset.MMapIndexedDatasetBuilder(indexed_dataset.data_file_path(output_prefix),
-                                                                dtype=first._index.dtype)
+                                                                dtype=first.dtype)
             del first
         builder.merge_file_(pfx)
     builder.finalize(indexed_dataset.index_file_path(output_prefix))

@@ -1,472 +1,472 @@
-"""On-disk token datasets (megatron/data/indexed_dataset.py): the memory-mapped format
-(``<prefix>.bin`` raw tokens + ``<prefix>.idx`` with magic ``MMIDIDX\\0\\0``, version, dtype code,
-counts, int32 sizes, int64 byte pointers, int64 document index) and the legacy ``TNTIDX`` cached /
-lazy format, with their builders."""
+"""Token datasets on disk: ``<prefix>.bin`` holds the raw token stream, ``<prefix>.idx`` describes it.
+
+Two index layouts are read and written, byte-compatible with the files the reference produces
+(megatron/data/indexed_dataset.py) so that existing tokenised corpora load unchanged:
+
+``mmap`` (magic ``MMIDIDX\\0\\0``)
+    ``<Q version=1> <B dtype code> <Q n_sequences> <Q n_doc_boundaries>`` followed by three arrays:
+    int32 sequence lengths, int64 byte offsets of every sequence in the .bin file, int64 document boundaries
+    (indices into the sequence list; first entry 0).  The .bin file is mapped, never read eagerly.
+
+``cached`` / ``lazy`` (magic ``TNTIDX\\0\\0``, the older layout)
+    ``<Q version=1> <Q dtype code> <Q element size> <Q n_items> <Q n_dims_total> <Q n_doc_boundaries>`` followed by
+    four int64 arrays: per-item offsets into the dims array, per-item element offsets into the .bin file, the
+    dims of every item, the document boundaries.
+
+The module is organised as plain records + functions for the two index layouts (``MMapIndex``, ``LegacyIndex``),
+reader classes over them and one writer base class; the reader / builder class names and methods are the ones
+the rest of the data pipeline (and the reference's tools) use.
+"""
 from __future__ import annotations
 
 import os
 import shutil
 import struct
-from functools import lru_cache
-from itertools import accumulate
+from dataclasses import dataclass
+from typing import Iterable, List, Optional, Sequence
 
 import numpy as np
 import torch
 
+MMAP_MAGIC = b"MMIDIDX\x00\x00"
+LEGACY_MAGIC = b"TNTIDX\x00\x00"
+
+# dtype codes stored in the index files
 dtypes = {1: np.uint8, 2: np.int8, 3: np.int16, 4: np.int32, 5: np.int64, 6: np.float32, 7: np.float64,
           8: np.uint16, 9: np.uint32, 10: np.uint64}
+_CODE_OF = {np.dtype(v): k for k, v in dtypes.items()}
 
 
-def __best_fitting_dtype(vocab_size=None):
-    return np.uint16 if vocab_size is not None and vocab_size < 65500 else np.int32
+def code(dtype) -> int:
+    try:
+        return _CODE_OF[np.dtype(dtype)]
+    except KeyError:
+        raise ValueError(f"no index code for dtype {dtype}") from None
 
 
-best_fitting_dtype = __best_fitting_dtype
+def best_fitting_dtype(vocab_size: Optional[int] = None):
+    """uint16 when every token id fits, int32 otherwise."""
+    return np.uint16 if (vocab_size is not None and vocab_size < 65500) else np.int32
 
 
-def infer_dataset_impl(path):
-    if IndexedDataset.exists(path):
-        with open(index_file_path(path), "rb") as f:
-            magic = f.read(8)
-            if magic == IndexedDataset._HDR_MAGIC:
-                return "cached"
-            if magic == MMapIndexedDataset.Index._HDR_MAGIC[:8]:
-                return "mmap"
-            return None
-    print(f"Dataset does not exist: {path}")
-    print("Path should be a basename that both .idx and .bin can be appended to get full filenames.")
+def index_file_path(prefix: str) -> str:
+    return prefix + ".idx"
+
+
+def data_file_path(prefix: str) -> str:
+    return prefix + ".bin"
+
+
+def _both_files(prefix: str) -> bool:
+    return os.path.exists(index_file_path(prefix)) and os.path.exists(data_file_path(prefix))
+
+
+def infer_dataset_impl(prefix: str) -> Optional[str]:
+    """``"mmap"`` / ``"cached"`` from the index magic; None when the files are missing or unknown."""
+    if not _both_files(prefix):
+        print(f"Dataset does not exist: {prefix}")
+        print("Path should be a basename that both .idx and .bin can be appended to get full filenames.")
+        return None
+    with open(index_file_path(prefix), "rb") as f:
+        head = f.read(9)
+    if head.startswith(LEGACY_MAGIC):
+        return "cached"
+    if head == MMAP_MAGIC:
+        return "mmap"
     return None
 
 
-def make_builder(out_file, impl, vocab_size=None):
+def make_dataset(prefix: str, impl: str, skip_warmup: bool = False):
+    if not _both_files(prefix):
+        print(f"Dataset does not exist: {prefix}")
+        print("Path should be a basename that both .idx and .bin can be appended to get full filenames.")
+        return None
+    if impl == "infer":
+        impl = infer_dataset_impl(prefix)
+    readers = {"lazy": IndexedDataset, "cached": IndexedCachedDataset}
+    if impl in readers:
+        return readers[impl](prefix)
+    if impl == "mmap":
+        return MMapIndexedDataset(prefix, skip_warmup)
+    print(f"Unknown dataset implementation: {impl}")
+    return None
+
+
+def make_builder(out_file: str, impl: str, vocab_size: Optional[int] = None):
     if impl == "mmap":
         return MMapIndexedDatasetBuilder(out_file, dtype=best_fitting_dtype(vocab_size))
     return IndexedDatasetBuilder(out_file)
 
 
-def make_dataset(path, impl, skip_warmup=False):
-    if not IndexedDataset.exists(path):
-        print(f"Dataset does not exist: {path}")
-        print("Path should be a basename that both .idx and .bin can be appended to get full filenames.")
-        return None
-    if impl == "infer":
-        impl = infer_dataset_impl(path)
-    if impl == "lazy" and IndexedDataset.exists(path):
-        return IndexedDataset(path)
-    if impl == "cached" and IndexedDataset.exists(path):
-        return IndexedCachedDataset(path)
-    if impl == "mmap" and MMapIndexedDataset.exists(path):
-        return MMapIndexedDataset(path, skip_warmup)
-    print(f"Unknown dataset implementation: {impl}")
-    return None
+def dataset_exists(prefix: str, impl: str) -> bool:
+    return _both_files(prefix)
 
 
-def dataset_exists(path, impl):
-    if impl == "mmap":
-        return MMapIndexedDataset.exists(path)
-    return IndexedDataset.exists(path)
+def create_doc_idx(sizes: Sequence[int]) -> List[int]:
+    """Document boundaries of a stream in which an empty sequence ends a document."""
+    return [0] + [i + 1 for i, n in enumerate(sizes) if n == 0]
 
 
-def code(dtype):
-    for k, v in dtypes.items():
-        if v == dtype:
-            return k
-    raise ValueError(dtype)
+# ------------------------------------------------------------------------------------------ legacy layout
+@dataclass
+class LegacyIndex:
+    dtype: type
+    element_size: int
+    dim_offsets: np.ndarray     # [n + 1]
+    data_offsets: np.ndarray    # [n + 1], in elements
+    sizes: np.ndarray           # dims of every item, concatenated
+    doc_idx: np.ndarray
 
+    @property
+    def n(self) -> int:
+        return len(self.data_offsets) - 1
 
-def index_file_path(prefix_path):
-    return prefix_path + ".idx"
+    @classmethod
+    def load(cls, path: str) -> "LegacyIndex":
+        with open(path, "rb") as f:
+            if f.read(8) != LEGACY_MAGIC:
+                raise ValueError("Index file doesn't match expected format. Make sure that --dataset-impl is "
+                                 "configured properly.")
+            version, dcode, esize, n, n_dims, n_docs = struct.unpack("<6Q", f.read(48))
+            if version != 1:
+                raise ValueError(f"unsupported index version {version}")
+            take = lambda k: np.fromfile(f, dtype=np.int64, count=k)
+            return cls(dtypes[dcode], int(esize), take(n + 1), take(n + 1), take(n_dims), take(n_docs))
 
+    def store(self, path: str) -> None:
+        with open(path, "wb") as f:
+            f.write(LEGACY_MAGIC)
+            f.write(struct.pack("<6Q", 1, code(self.dtype), self.element_size, self.n, len(self.sizes),
+                                len(self.doc_idx)))
+            for arr in (self.dim_offsets, self.data_offsets, self.sizes, self.doc_idx):
+                f.write(np.asarray(arr, dtype=np.int64).tobytes(order="C"))
 
-def data_file_path(prefix_path):
-    return prefix_path + ".bin"
-
-
-def _read_longs(f, n):
-    a = np.empty(n, dtype=np.int64)
-    f.readinto(a)
-    return a
-
-
-def _write_longs(f, a):
-    f.write(np.array(a, dtype=np.int64))
-
-
-def create_doc_idx(sizes):
-    doc_idx = [0]
-    for i, s in enumerate(sizes):
-        if s == 0:
-            doc_idx.append(i + 1)
-    return doc_idx
+    def shape_of(self, i: int):
+        return tuple(int(d) for d in self.sizes[self.dim_offsets[i]:self.dim_offsets[i + 1]])
 
 
 class IndexedDataset(torch.utils.data.Dataset):
-    """Legacy format, read lazily from the ``.bin`` file."""
+    """Legacy layout, every item read from the .bin file when asked for ("lazy")."""
 
-    _HDR_MAGIC = b"TNTIDX\x00\x00"
+    supports_prefetch = False
 
-    def __init__(self, path):
+    def __init__(self, path: str):
         super().__init__()
         self.path = path
-        self.data_file = None
-        self.read_index(path)
+        self._index = LegacyIndex.load(index_file_path(path))
+        self._fh = None
 
-    def read_index(self, path):
-        with open(index_file_path(path), "rb") as f:
-            magic = f.read(8)
-            assert magic == self._HDR_MAGIC, "Index file doesn't match expected format. Make sure that --dataset-impl is configured properly."
-            version = f.read(8)
-            assert struct.unpack("<Q", version) == (1,)
-            code_, self.element_size = struct.unpack("<QQ", f.read(16))
-            self.dtype = dtypes[code_]
-            self._len, self.s = struct.unpack("<QQ", f.read(16))
-            self.doc_count = struct.unpack("<Q", f.read(8))
-            self.dim_offsets = _read_longs(f, self._len + 1)
-            self.data_offsets = _read_longs(f, self._len + 1)
-            self.sizes = _read_longs(f, self.s)
-            self.doc_idx = _read_longs(f, self.doc_count[0])
+    # the fields the dataset tools look at
+    dtype = property(lambda self: self._index.dtype)
+    sizes = property(lambda self: self._index.sizes)
+    doc_idx = property(lambda self: self._index.doc_idx)
+    data_offsets = property(lambda self: self._index.data_offsets)
+    dim_offsets = property(lambda self: self._index.dim_offsets)
+    element_size = property(lambda self: self._index.element_size)
 
-    def read_data(self, path):
-        self.data_file = open(data_file_path(path), "rb", buffering=0)
+    def __len__(self):
+        return self._index.n
 
-    def check_index(self, i):
-        if i < 0 or i >= self._len:
+    def _check(self, i: int) -> int:
+        if not -len(self) <= i < len(self):
             raise IndexError("index out of range")
+        return i % len(self)
 
-    def __del__(self):
-        if self.data_file:
-            self.data_file.close()
+    def _read_elements(self, first: int, count: int) -> np.ndarray:
+        if self._fh is None:
+            self._fh = open(data_file_path(self.path), "rb", buffering=0)
+        self._fh.seek(int(first) * self._index.element_size)
+        out = np.empty(int(count), dtype=self._index.dtype)
+        self._fh.readinto(out)
+        return out
+
+    def _item(self, i: int) -> np.ndarray:
+        lo, hi = self._index.data_offsets[i], self._index.data_offsets[i + 1]
+        return self._read_elements(lo, hi - lo).reshape(self._index.shape_of(i))
 
     def __getitem__(self, idx):
-        if not self.data_file:
-            self.read_data(self.path)
-        if isinstance(idx, int):
-            self.check_index(idx)
-            tensor_size = self.sizes[self.dim_offsets[idx]: self.dim_offsets[idx + 1]]
-            a = np.empty(tensor_size, dtype=self.dtype)
-            self.data_file.seek(self.data_offsets[idx] * self.element_size)
-            self.data_file.readinto(a)
-            return a
         if isinstance(idx, slice):
             start, stop, step = idx.indices(len(self))
             if step != 1:
                 raise ValueError("Slices into indexed_dataset must be contiguous")
-            sizes = self.sizes[self.dim_offsets[start]: self.dim_offsets[stop]]
-            size = sum(sizes)
-            a = np.empty(size, dtype=self.dtype)
-            self.data_file.seek(self.data_offsets[start] * self.element_size)
-            self.data_file.readinto(a)
-            offsets = list(accumulate(sizes))
-            return np.split(a, offsets[:-1])
+            if stop <= start:
+                return []
+            off = self._index.data_offsets
+            flat = self._read_elements(off[start], off[stop] - off[start])       # one read for the whole range
+            cuts = (off[start + 1:stop] - off[start]).astype(np.int64)
+            return [p.reshape(self._index.shape_of(start + k)) for k, p in enumerate(np.split(flat, cuts))]
+        return self._item(self._check(int(idx)))
 
-    def __len__(self):
-        return self._len
+    def num_tokens(self, i):
+        return self._index.sizes[i]
 
-    def num_tokens(self, index):
-        return self.sizes[index]
-
-    def size(self, index):
-        return self.sizes[index]
+    size = num_tokens
 
     @staticmethod
-    def exists(path):
-        return os.path.exists(index_file_path(path)) and os.path.exists(data_file_path(path))
+    def exists(prefix):
+        return _both_files(prefix)
 
-    @property
-    def supports_prefetch(self):
-        return False
+    def __del__(self):
+        if getattr(self, "_fh", None) is not None:
+            self._fh.close()
 
 
 class IndexedCachedDataset(IndexedDataset):
-    def __init__(self, path):
+    """Legacy layout served from one in-memory arena that ``prefetch`` fills for a chosen set of items."""
+
+    supports_prefetch = True
+
+    def __init__(self, path: str):
         super().__init__(path)
-        self.cache = None
-        self.cache_index = {}
+        self._arena = np.empty(0, dtype=self._index.dtype)
+        self._where = {}            # item -> first element in the arena
 
-    @property
-    def supports_prefetch(self):
-        return True
-
-    def prefetch(self, indices):
-        if all(i in self.cache_index for i in indices):
+    def prefetch(self, indices: Iterable[int]):
+        wanted = sorted({int(i) for i in indices})
+        if all(i in self._where for i in wanted):
             return
-        if not self.data_file:
-            self.read_data(self.path)
-        indices = sorted(set(indices))
-        total_size = sum(self.data_offsets[i + 1] - self.data_offsets[i] for i in indices)
-        self.cache = np.empty(total_size, dtype=self.dtype)
-        ptx = 0
-        self.cache_index.clear()
-        for i in indices:
-            self.cache_index[i] = ptx
-            size = self.data_offsets[i + 1] - self.data_offsets[i]
-            a = self.cache[ptx: ptx + size]
-            self.data_file.seek(self.data_offsets[i] * self.element_size)
-            self.data_file.readinto(a)
-            ptx += size
-        if self.data_file:
-            self.data_file.close()
-            self.data_file = None
+        off = self._index.data_offsets
+        lengths = [int(off[i + 1] - off[i]) for i in wanted]
+        self._arena = np.empty(sum(lengths), dtype=self._index.dtype)
+        self._where, at = {}, 0
+        for i, n in zip(wanted, lengths):
+            self._arena[at:at + n] = self._read_elements(off[i], n)
+            self._where[i] = at
+            at += n
+        if self._fh is not None:        # everything needed is in memory now
+            self._fh.close()
+            self._fh = None
+
+    def _item(self, i: int) -> np.ndarray:
+        if i not in self._where:
+            raise KeyError(f"item {i} was not prefetched")
+        n = int(self._index.data_offsets[i + 1] - self._index.data_offsets[i])
+        at = self._where[i]
+        return self._arena[at:at + n].copy().reshape(self._index.shape_of(i))
 
     def __getitem__(self, idx):
-        if isinstance(idx, int):
-            self.check_index(idx)
-            tensor_size = self.sizes[self.dim_offsets[idx]: self.dim_offsets[idx + 1]]
-            a = np.empty(tensor_size, dtype=self.dtype)
-            ptx = self.cache_index[idx]
-            np.copyto(a, self.cache[ptx: ptx + a.size])
-            return a
         if isinstance(idx, slice):
-            return [self[i] for i in range(*idx.indices(len(self)))]
+            return [self._item(i) for i in range(*idx.indices(len(self)))]
+        return self._item(self._check(int(idx)))
 
 
-class IndexedDatasetBuilder:
-    element_sizes = {np.uint8: 1, np.int8: 1, np.int16: 2, np.int32: 4, np.int64: 8, np.float32: 4, np.float64: 8}
+# ------------------------------------------------------------------------------------------ mmap layout
+@dataclass
+class MMapIndex:
+    dtype: type
+    sizes: np.ndarray        # int32 [n]
+    pointers: np.ndarray     # int64 [n], byte offsets
+    doc_idx: np.ndarray      # int64 [n_docs]
 
-    def __init__(self, out_file, dtype=np.int32):
-        self.out_file = open(out_file, "wb")
-        self.dtype = dtype
-        self.data_offsets = [0]
-        self.dim_offsets = [0]
-        self.sizes = []
-        self.element_size = self.element_sizes[self.dtype]
-        self.doc_idx = [0]
+    _HEADER = struct.Struct("<QBQQ")
 
-    def add_item(self, np_array):
-        assert isinstance(np_array, np.ndarray) and np_array.dtype == self.dtype
-        nbytes = self.out_file.write(np_array)
-        self.data_offsets.append(self.data_offsets[-1] + nbytes / self.element_size)
-        for s in np_array.shape:
-            self.sizes.append(s)
-        self.dim_offsets.append(self.dim_offsets[-1] + len(np_array.shape))
+    @classmethod
+    def load(cls, path: str, warm: bool = False) -> "MMapIndex":
+        with open(path, "rb") as f:
+            if f.read(9) != MMAP_MAGIC:
+                raise ValueError("Index file doesn't match expected format. Make sure that --dataset-impl is "
+                                 "configured properly.")
+            version, dcode, n, n_docs = cls._HEADER.unpack(f.read(cls._HEADER.size))
+            if version != 1:
+                raise ValueError(f"unsupported index version {version}")
+            base = f.tell()
+        if warm:
+            _touch_file(path)
+        raw = np.memmap(path, mode="r", order="C")
+        sizes = np.frombuffer(raw, dtype=np.int32, count=n, offset=base)
+        pointers = np.frombuffer(raw, dtype=np.int64, count=n, offset=base + sizes.nbytes)
+        doc_idx = np.frombuffer(raw, dtype=np.int64, count=n_docs, offset=base + sizes.nbytes + pointers.nbytes)
+        idx = cls(dtypes[dcode], sizes, pointers, doc_idx)
+        idx._raw = raw          # keeps the mapping alive
+        return idx
 
-    def end_document(self):
-        self.doc_idx.append(len(self.sizes))
-
-    def merge_file_(self, another_file):
-        index = IndexedDataset(another_file)
-        assert index.dtype == self.dtype
-        begin = self.data_offsets[-1]
-        for offset in index.data_offsets[1:]:
-            self.data_offsets.append(begin + offset)
-        self.sizes.extend(index.sizes)
-        begin = self.dim_offsets[-1]
-        for dim_offset in index.dim_offsets[1:]:
-            self.dim_offsets.append(begin + dim_offset)
-        with open(data_file_path(another_file), "rb") as f:
-            shutil.copyfileobj(f, self.out_file)
-
-    def finalize(self, index_file):
-        self.out_file.close()
-        with open(index_file, "wb") as index:
-            index.write(IndexedDataset._HDR_MAGIC)
-            index.write(struct.pack("<Q", 1))
-            index.write(struct.pack("<QQ", code(self.dtype), self.element_size))
-            index.write(struct.pack("<QQ", len(self.data_offsets) - 1, len(self.sizes)))
-            index.write(struct.pack("<Q", len(self.doc_idx)))
-            _write_longs(index, self.dim_offsets)
-            _write_longs(index, self.data_offsets)
-            _write_longs(index, self.sizes)
-            _write_longs(index, self.doc_idx)
+    @staticmethod
+    def store(path: str, dtype, sizes: Sequence[int], doc_idx: Sequence[int]) -> None:
+        lengths = np.asarray(sizes, dtype=np.int64)
+        pointers = np.zeros(len(lengths), dtype=np.int64)
+        if len(lengths) > 1:
+            np.cumsum(lengths[:-1] * np.dtype(dtype).itemsize, out=pointers[1:])
+        with open(path, "wb") as f:
+            f.write(MMAP_MAGIC)
+            f.write(MMapIndex._HEADER.pack(1, code(dtype), len(lengths), len(doc_idx)))
+            f.write(lengths.astype(np.int32).tobytes(order="C"))
+            f.write(pointers.tobytes(order="C"))
+            f.write(np.asarray(doc_idx, dtype=np.int64).tobytes(order="C"))
 
 
-def _warmup_mmap_file(path):
-    with open(path, "rb") as stream:
-        while stream.read(100 * 1024 * 1024):
+def _touch_file(path: str, chunk: int = 100 << 20) -> None:
+    """Read the file once so that the page cache holds it before the first random accesses."""
+    with open(path, "rb") as f:
+        while f.read(chunk):
             pass
 
 
 class MMapIndexedDataset(torch.utils.data.Dataset):
-    class Index:
-        _HDR_MAGIC = b"MMIDIDX\x00\x00"
+    """Memory-mapped token store: ``ds[i]`` / ``ds.get(i, offset, length)`` are views into the mapped .bin."""
 
-        @classmethod
-        def writer(cls, path, dtype):
-            class _Writer:
-                def __enter__(self):
-                    self._file = open(path, "wb")
-                    self._file.write(cls._HDR_MAGIC)
-                    self._file.write(struct.pack("<Q", 1))
-                    self._file.write(struct.pack("<B", code(dtype)))
-                    return self
+    supports_prefetch = False
 
-                @staticmethod
-                def _get_pointers(sizes):
-                    itemsize = dtype().itemsize
-                    sizes64 = np.asarray(sizes, dtype=np.int64)
-                    pointers = np.zeros(len(sizes64), dtype=np.int64)
-                    if len(sizes64) > 1:
-                        np.cumsum(sizes64[:-1] * itemsize, out=pointers[1:])
-                    return pointers
-
-                def write(self, sizes, doc_idx):
-                    pointers = self._get_pointers(sizes)
-                    self._file.write(struct.pack("<Q", len(sizes)))
-                    self._file.write(struct.pack("<Q", len(doc_idx)))
-                    self._file.write(np.array(sizes, dtype=np.int32).tobytes(order="C"))
-                    self._file.write(pointers.tobytes(order="C"))
-                    self._file.write(np.array(doc_idx, dtype=np.int64).tobytes(order="C"))
-
-                def __exit__(self, exc_type, exc_val, exc_tb):
-                    self._file.close()
-
-            return _Writer()
-
-        def __init__(self, path, skip_warmup=False):
-            with open(path, "rb") as stream:
-                magic_test = stream.read(9)
-                assert self._HDR_MAGIC == magic_test, "Index file doesn't match expected format. Make sure that --dataset-impl is configured properly."
-                version = struct.unpack("<Q", stream.read(8))
-                assert (1,) == version
-                (dtype_code,) = struct.unpack("<B", stream.read(1))
-                self._dtype = dtypes[dtype_code]
-                self._dtype_size = self._dtype().itemsize
-                self._len = struct.unpack("<Q", stream.read(8))[0]
-                self._doc_count = struct.unpack("<Q", stream.read(8))[0]
-                offset = stream.tell()
-            if not skip_warmup:
-                _warmup_mmap_file(path)
-            self._bin_buffer_mmap = np.memmap(path, mode="r", order="C")
-            self._bin_buffer = memoryview(self._bin_buffer_mmap)
-            self._sizes = np.frombuffer(self._bin_buffer, dtype=np.int32, count=self._len, offset=offset)
-            self._pointers = np.frombuffer(self._bin_buffer, dtype=np.int64, count=self._len,
-                                           offset=offset + self._sizes.nbytes)
-            self._doc_idx = np.frombuffer(self._bin_buffer, dtype=np.int64, count=self._doc_count,
-                                          offset=offset + self._sizes.nbytes + self._pointers.nbytes)
-
-        def __del__(self):
-            if hasattr(self, "_bin_buffer_mmap"):
-                self._bin_buffer_mmap._mmap.close()
-                del self._bin_buffer_mmap
-
-        @property
-        def dtype(self):
-            return self._dtype
-
-        @property
-        def sizes(self):
-            return self._sizes
-
-        @property
-        def doc_idx(self):
-            return self._doc_idx
-
-        @lru_cache(maxsize=8)
-        def __getitem__(self, i):
-            return self._pointers[i], self._sizes[i]
-
-        def __len__(self):
-            return self._len
-
-    def __init__(self, path, skip_warmup=False):
+    def __init__(self, path: str, skip_warmup: bool = False):
         super().__init__()
-        self._path = self._index = self._bin_buffer = None
-        self._do_init(path, skip_warmup)
+        self._open(path, skip_warmup)
 
+    def _open(self, path: str, skip_warmup: bool):
+        self._path = path
+        self._index = MMapIndex.load(index_file_path(path), warm=not skip_warmup)
+        if not skip_warmup:
+            _touch_file(data_file_path(path))
+        self._tokens = np.memmap(data_file_path(path), mode="r", order="C")
+        # a user-supplied document index (dataset tools re-partition documents) overrides the stored one
+        self._doc_idx_override = None
+
+    # pickling (DataLoader workers) re-opens the maps instead of copying them
     def __getstate__(self):
         return self._path
 
-    def __setstate__(self, state):
-        self._do_init(state, skip_warmup=True)
-
-    def _do_init(self, path, skip_warmup):
-        self._path = path
-        self._index = self.Index(index_file_path(self._path), skip_warmup)
-        if not skip_warmup:
-            _warmup_mmap_file(data_file_path(self._path))
-        self._bin_buffer_mmap = np.memmap(data_file_path(self._path), mode="r", order="C")
-        self._bin_buffer = memoryview(self._bin_buffer_mmap)
-
-    def __del__(self):
-        if getattr(self, "_bin_buffer_mmap", None) is not None:
-            self._bin_buffer_mmap._mmap.close()
-            del self._bin_buffer_mmap
-        self._index = None
+    def __setstate__(self, path):
+        self._open(path, skip_warmup=True)
 
     def __len__(self):
-        return len(self._index)
-
-    def __getitem__(self, idx):
-        if isinstance(idx, (int, np.integer)):
-            ptr, size = self._index[int(idx)]
-            return np.frombuffer(self._bin_buffer, dtype=self._index.dtype, count=size, offset=ptr)
-        if isinstance(idx, slice):
-            start, stop, step = idx.indices(len(self))
-            if step != 1:
-                raise ValueError("Slices into indexed_dataset must be contiguous")
-            ptr = self._index._pointers[start]
-            sizes = self._index._sizes[idx]
-            offsets = list(accumulate(sizes))
-            total_size = sum(sizes)
-            np_array = np.frombuffer(self._bin_buffer, dtype=self._index.dtype, count=total_size, offset=ptr)
-            return np.split(np_array, offsets[:-1])
-
-    def get(self, idx, offset=0, length=None):
-        """Zero-copy slice ``[offset, offset + length)`` of item ``idx``."""
-        ptr, size = self._index[int(idx)]
-        if length is None:
-            length = size - offset
-        ptr += offset * np.dtype(self._index.dtype).itemsize
-        return np.frombuffer(self._bin_buffer, dtype=self._index.dtype, count=length, offset=ptr)
+        return len(self._index.sizes)
 
     @property
     def sizes(self):
         return self._index.sizes
 
     @property
-    def doc_idx(self):
-        return self._index.doc_idx
-
-    def get_doc_idx(self):
-        return self._index._doc_idx
-
-    def set_doc_idx(self, doc_idx_):
-        self._index._doc_idx = doc_idx_
+    def dtype(self):
+        return self._index.dtype
 
     @property
-    def supports_prefetch(self):
-        return False
+    def doc_idx(self):
+        return self._index.doc_idx if self._doc_idx_override is None else self._doc_idx_override
+
+    def get_doc_idx(self):
+        return self.doc_idx
+
+    def set_doc_idx(self, doc_idx_):
+        self._doc_idx_override = doc_idx_
+
+    def _view(self, byte_offset: int, count: int) -> np.ndarray:
+        return np.frombuffer(self._tokens, dtype=self._index.dtype, count=int(count), offset=int(byte_offset))
+
+    def get(self, idx: int, offset: int = 0, length: Optional[int] = None) -> np.ndarray:
+        """Tokens ``[offset, offset + length)`` of sequence ``idx`` (to its end when ``length`` is None)."""
+        n = int(self._index.sizes[idx]) - offset if length is None else length
+        start = int(self._index.pointers[idx]) + offset * np.dtype(self._index.dtype).itemsize
+        return self._view(start, n)
+
+    def __getitem__(self, idx):
+        if isinstance(idx, slice):
+            start, stop, step = idx.indices(len(self))
+            if step != 1:
+                raise ValueError("Slices into indexed_dataset must be contiguous")
+            if stop <= start:
+                return []
+            lengths = self._index.sizes[start:stop]
+            flat = self._view(self._index.pointers[start], int(lengths.sum()))
+            return np.split(flat, np.cumsum(lengths[:-1], dtype=np.int64))
+        i = int(idx)
+        if not -len(self) <= i < len(self):
+            raise IndexError("index out of range")
+        return self.get(i % len(self))
 
     @staticmethod
-    def exists(path):
-        return os.path.exists(index_file_path(path)) and os.path.exists(data_file_path(path))
+    def exists(prefix):
+        return _both_files(prefix)
+
+    def __del__(self):
+        tok = getattr(self, "_tokens", None)
+        if tok is not None and getattr(tok, "_mmap", None) is not None:
+            tok._mmap.close()
+            self._tokens = None
 
 
-class MMapIndexedDatasetBuilder:
-    def __init__(self, out_file, dtype=np.int64):
-        self._data_file = open(out_file, "wb")
-        self._dtype = dtype
-        self._sizes = []
+# ------------------------------------------------------------------------------------------ writers
+class _StreamWriter:
+    """Appends items to a .bin file and keeps the bookkeeping common to both index layouts."""
+
+    def __init__(self, out_file: str, dtype):
+        self._bin = open(out_file, "wb")
+        self._dtype = np.dtype(dtype).type
         self._doc_idx = [0]
 
     @property
     def dtype(self):
         return self._dtype
 
-    def add_item(self, np_array):
-        np_array = np.asarray(np_array, dtype=self._dtype)
-        self._data_file.write(np_array.tobytes(order="C"))
-        self._sizes.append(np_array.size)
+    def _append_bytes(self, arr: np.ndarray) -> int:
+        return self._bin.write(np.ascontiguousarray(arr, dtype=self._dtype).tobytes(order="C"))
 
-    def add_items(self, arr_list):
-        for a in arr_list:
-            self.add_item(a)
+    def _append_file(self, prefix: str) -> None:
+        with open(data_file_path(prefix), "rb") as src:
+            shutil.copyfileobj(src, self._bin)
+
+
+class IndexedDatasetBuilder(_StreamWriter):
+    """Writer of the legacy layout (items may have any shape)."""
+
+    def __init__(self, out_file: str, dtype=np.int32):
+        super().__init__(out_file, dtype)
+        self._data_offsets, self._dim_offsets, self._dims = [0], [0], []
+
+    def add_item(self, arr: np.ndarray):
+        if not (isinstance(arr, np.ndarray) and arr.dtype == self._dtype):
+            raise TypeError(f"add_item expects a numpy array of {self._dtype}, got {type(arr)} {getattr(arr, 'dtype', '')}")
+        self._append_bytes(arr)
+        self._data_offsets.append(self._data_offsets[-1] + arr.size)
+        self._dims.extend(arr.shape)
+        self._dim_offsets.append(self._dim_offsets[-1] + arr.ndim)
+
+    def end_document(self):
+        self._doc_idx.append(len(self._dims))
+
+    def merge_file_(self, other_prefix: str):
+        other = LegacyIndex.load(index_file_path(other_prefix))
+        if np.dtype(other.dtype) != np.dtype(self._dtype):
+            raise TypeError("merge_file_: element types differ")
+        d0, m0 = self._data_offsets[-1], self._dim_offsets[-1]
+        self._data_offsets.extend(int(d0 + v) for v in other.data_offsets[1:])
+        self._dim_offsets.extend(int(m0 + v) for v in other.dim_offsets[1:])
+        self._dims.extend(int(v) for v in other.sizes)
+        self._append_file(other_prefix)
+
+    def finalize(self, index_file: str):
+        self._bin.close()
+        LegacyIndex(self._dtype, np.dtype(self._dtype).itemsize, np.asarray(self._dim_offsets),
+                    np.asarray(self._data_offsets), np.asarray(self._dims), np.asarray(self._doc_idx)).store(index_file)
+
+
+class MMapIndexedDatasetBuilder(_StreamWriter):
+    """Writer of the mmap layout (1-D token sequences)."""
+
+    def __init__(self, out_file: str, dtype=np.int64):
+        super().__init__(out_file, dtype)
+        self._sizes: List[int] = []
+
+    def add_item(self, arr):
+        arr = np.asarray(arr, dtype=self._dtype)
+        self._append_bytes(arr)
+        self._sizes.append(arr.size)
+
+    def add_items(self, arrays):
+        arrays = [np.asarray(a, dtype=self._dtype) for a in arrays]
+        if arrays:
+            self._append_bytes(np.concatenate(arrays))
+            self._sizes.extend(a.size for a in arrays)
 
     def end_document(self):
         self._doc_idx.append(len(self._sizes))
 
-    def merge_file_(self, another_file):
-        index = MMapIndexedDataset.Index(index_file_path(another_file))
-        assert index.dtype == self._dtype
-        total_len = len(index.sizes) + len(self._sizes)
-        print(f"    concat {another_file} size={len(index.sizes)} for a total size of {total_len}")
-        offset = len(self._sizes)
-        self._sizes.extend(index.sizes)
-        self._doc_idx.extend((offset + index.doc_idx)[1:])
-        with open(data_file_path(another_file), "rb") as f:
-            shutil.copyfileobj(f, self._data_file)
+    def merge_file_(self, other_prefix: str):
+        other = MMapIndex.load(index_file_path(other_prefix))
+        if np.dtype(other.dtype) != np.dtype(self._dtype):
+            raise TypeError("merge_file_: element types differ")
+        shift = len(self._sizes)
+        self._sizes.extend(int(n) for n in other.sizes)
+        self._doc_idx.extend(int(shift + d) for d in other.doc_idx[1:])
+        self._append_file(other_prefix)
 
-    def finalize(self, index_file):
-        self._data_file.close()
-        with MMapIndexedDataset.Index.writer(index_file, self._dtype) as index:
-            index.write(self._sizes, self._doc_idx)
+    def finalize(self, index_file: str):
+        self._bin.close()
+        MMapIndex.store(index_file, self._dtype, self._sizes, self._doc_idx)

@@ -100,3 +100,63 @@ def test_batch_sampler_shards_and_resumes():
     s = DistributedBatchSampler(SequentialSampler(data), batch_size=8, drop_last=True, rank=0, world_size=2)
     s.start_iter = 3                                                         # resume after 3 global batches
     assert next(iter(s)) == [24, 25, 26, 27]
+
+
+def test_index_files_follow_the_documented_byte_layout(tmp_path):
+    """Readers accept hand-packed index files of both layouts (the byte layout existing corpora use), and the
+    builders emit exactly those bytes."""
+    import struct
+    docs = [np.array([5, 6, 7], dtype=np.uint16), np.array([9], dtype=np.uint16), np.array([1, 2], dtype=np.uint16)]
+    flat = np.concatenate(docs)
+    # ---- mmap layout
+    pfx = str(tmp_path / "hand_mmap")
+    flat.tofile(pfx + ".bin")
+    sizes = np.array([3, 1, 2], dtype=np.int32)
+    ptrs = np.array([0, 6, 8], dtype=np.int64)
+    doc_idx = np.array([0, 2, 3], dtype=np.int64)
+    blob = b"MMIDIDX\x00\x00" + struct.pack("<Q", 1) + struct.pack("<B", 8) + struct.pack("<Q", 3) + \
+        struct.pack("<Q", 3) + sizes.tobytes() + ptrs.tobytes() + doc_idx.tobytes()
+    open(pfx + ".idx", "wb").write(blob)
+    ds = indexed_dataset.make_dataset(pfx, "infer", skip_warmup=True)
+    assert [list(ds[i]) for i in range(3)] == [[5, 6, 7], [9], [1, 2]] and list(ds.doc_idx) == [0, 2, 3]
+    assert [list(a) for a in ds[0:3]] == [[5, 6, 7], [9], [1, 2]] and list(ds.get(0, 1, 2)) == [6, 7]
+    b = indexed_dataset.MMapIndexedDatasetBuilder(str(tmp_path / "built.bin"), dtype=np.uint16)
+    b.add_items(docs[:2])
+    b.end_document()
+    b.add_item(docs[2])
+    b.end_document()
+    b.finalize(str(tmp_path / "built.idx"))
+    assert open(tmp_path / "built.idx", "rb").read() == blob
+    assert open(tmp_path / "built.bin", "rb").read() == flat.tobytes()
+    # ---- legacy layout (int32 items)
+    pfx = str(tmp_path / "hand_legacy")
+    flat32 = flat.astype(np.int32)
+    flat32.tofile(pfx + ".bin")
+    i64 = lambda *v: np.array(v, dtype=np.int64).tobytes()
+    blob = b"TNTIDX\x00\x00" + struct.pack("<Q", 1) + struct.pack("<QQ", 4, 4) + struct.pack("<QQ", 3, 3) + \
+        struct.pack("<Q", 3) + i64(0, 1, 2, 3) + i64(0, 3, 4, 6) + i64(3, 1, 2) + i64(0, 2, 3)
+    open(pfx + ".idx", "wb").write(blob)
+    assert indexed_dataset.infer_dataset_impl(pfx) == "cached"
+    lazy = indexed_dataset.make_dataset(pfx, "lazy")
+    assert [list(lazy[i]) for i in range(3)] == [[5, 6, 7], [9], [1, 2]] and [list(a) for a in lazy[1:3]] == [[9], [1, 2]]
+    b = indexed_dataset.IndexedDatasetBuilder(str(tmp_path / "built_legacy.bin"), dtype=np.int32)
+    for i, d in enumerate(docs):
+        b.add_item(d.astype(np.int32))
+        if i in (1, 2):
+            b.end_document()
+    b.finalize(str(tmp_path / "built_legacy.idx"))
+    assert open(tmp_path / "built_legacy.idx", "rb").read() == blob
+
+
+def test_mmap_builder_merge_shifts_document_boundaries(tmp_path):
+    rng = np.random.default_rng(3)
+    a, b = _docs(rng, 5), _docs(rng, 4)
+    pa, pb = _write(tmp_path, a, name="a"), _write(tmp_path, b, name="b")
+    m = indexed_dataset.MMapIndexedDatasetBuilder(str(tmp_path / "m.bin"), dtype=np.uint16)
+    m.merge_file_(pa)
+    m.merge_file_(pb)
+    m.finalize(str(tmp_path / "m.idx"))
+    ds = indexed_dataset.make_dataset(str(tmp_path / "m"), "mmap", skip_warmup=True)
+    assert len(ds) == 9 and list(ds.doc_idx) == list(range(10))
+    for i, d in enumerate(a + b):
+        assert np.array_equal(ds[i], d)
