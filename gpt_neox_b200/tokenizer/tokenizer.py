@@ -1,371 +1,283 @@
-"""Tokenizers behind one interface (``vocab_size``, ``tokenize``, ``detokenize``, ``eod``) and the
-vocabulary padding rule (megatron/tokenizer/tokenizer.py:30-404): GPT-2 byte-level BPE from
-vocab/merges files, HF ``tokenizers`` JSON, HF GPT2 fast tokenizer, SentencePiece, character level
-and tiktoken.  A ``SyntheticTokenizer`` (new here) stands in when training on synthetic tokens."""
+"""Tokenizers behind one small interface and the vocabulary padding rule.
+
+Every tokenizer is a :class:`Tokenizer`: ``tokenize(text) -> ids``, ``detokenize(ids) -> text``, ``vocab_size``,
+``eod`` (end-of-document id), optionally ``pad`` and ``tokenize_batch``.  A subclass only supplies the backend
+calls (``_encode``, ``_decode``, ``_size``, optionally ``_get_vocab``); everything else is derived here.
+``build_tokenizer`` picks the class from a registry keyed by ``tokenizer_type`` and stores the padded vocabulary
+size in the arguments.  Types and padding rule as in megatron/tokenizer/tokenizer.py:30-404; the
+``SyntheticTokenizer`` (ids are their own tokens) exists only here, for training on synthetic tokens.
+"""
 from __future__ import annotations
 
-import json
-from abc import ABC, abstractmethod
-from functools import lru_cache
-from typing import List, Union
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Union
 
 import numpy as np
+
+EOD_TEXT, PAD_TEXT = "<|endoftext|>", "<|padding|>"
+
+
+def _vocab_size_with_padding(orig_vocab_size: int, args) -> int:
+    """Vocabulary rounded up to a multiple of ``make_vocab_size_divisible_by * model_parallel_size``
+    (50277 -> 50304 at MP 1, 50432 at MP 2), so every tensor-parallel rank holds an equal, aligned slice."""
+    unit = args.make_vocab_size_divisible_by * args.model_parallel_size
+    padded = -(-orig_vocab_size // unit) * unit
+    if args.rank in (0, None):
+        print(f" > padded vocab (size: {orig_vocab_size}) with {padded - orig_vocab_size} dummy tokens "
+              f"(new size: {padded})", flush=True)
+    return padded
+
+
+class Tokenizer:
+    """Interface + shared behaviour.  ``eod_id`` / ``pad_id`` are set by the subclass (None = not available)."""
+
+    name = "tokenizer"
+    eod_id: Optional[int] = None
+    pad_id: Optional[int] = None
+
+    # ---- backend hooks
+    def _encode(self, text: str) -> List[int]:
+        raise NotImplementedError
+
+    def _decode(self, ids: List[int]) -> str:
+        raise NotImplementedError(f"detokenizer is not implemented for {self.name} tokenizer")
+
+    def _size(self) -> int:
+        raise NotImplementedError
+
+    def _get_vocab(self) -> Dict[str, int]:
+        raise NotImplementedError(f"{self.name} does not implement vocabulary access.")
+
+    # ---- public surface
+    @property
+    def vocab_size(self) -> int:
+        return self._size()
+
+    @property
+    def vocab(self) -> Dict[str, int]:
+        return self._get_vocab()
+
+    @property
+    def inv_vocab(self) -> Dict[int, str]:
+        return {i: t for t, i in self._get_vocab().items()}
+
+    def tokenize(self, text: str) -> List[int]:
+        return self._encode(text)
+
+    def tokenize_batch(self, texts: Union[str, Sequence[str]]):
+        return [self._encode(t) for t in ([texts] if isinstance(texts, str) else texts)]
+
+    def detokenize(self, token_ids: Iterable[int]) -> str:
+        return self._decode([int(t) for t in token_ids])
+
+    def _special(self, what: str, value: Optional[int]) -> int:
+        if value is None:
+            raise NotImplementedError(f"{what} is not provided for {self.name} tokenizer")
+        return value
+
+    eod = property(lambda self: self._special("EOD", self.eod_id))
+    pad = property(lambda self: self._special("PAD", self.pad_id))
+    cls = property(lambda self: self._special("CLS", None))
+    sep = property(lambda self: self._special("SEP", None))
+    mask = property(lambda self: self._special("MASK", None))
+
+
+AbstractTokenizer = Tokenizer       # the name other code bases import
+
+
+class SyntheticTokenizer(Tokenizer):
+    """Fixed-size vocabulary without text: ids are their own tokens (synthetic-token training)."""
+
+    name, eod_id, pad_id = "Synthetic", 0, 1
+
+    def __init__(self, vocab_size: int):
+        self._n = int(vocab_size)
+
+    def _size(self):
+        return self._n
+
+    def _get_vocab(self):
+        return {str(i): i for i in range(self._n)}
+
+    def _encode(self, text):
+        return [int(t) % self._n for t in str(text).split() if t.lstrip("-").isdigit()]
+
+    def _decode(self, ids):
+        return " ".join(str(i) for i in ids)
+
+
+class _TokenizersBackend(Tokenizer):
+    """Anything driven by a ``tokenizers.Tokenizer`` object in ``self.tokenizer``."""
+
+    def _size(self):
+        return self.tokenizer.get_vocab_size()
+
+    def _get_vocab(self):
+        return self.tokenizer.get_vocab()
+
+    def _encode(self, text):
+        return self.tokenizer.encode(text).ids
+
+    def _decode(self, ids):
+        return self.tokenizer.decode(ids)
+
+
+class _GPT2BPETokenizer(_TokenizersBackend):
+    """Byte-level BPE from ``vocab.json`` + ``merges.txt``."""
+
+    name = "GPT2 BPE"
+
+    def __init__(self, vocab_file: str, merge_file: str):
+        from tokenizers import Tokenizer as _Tok, decoders, models, pre_tokenizers
+        self.tokenizer = _Tok(models.BPE.from_file(vocab_file, merge_file))
+        self.tokenizer.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+        self.tokenizer.decoder = decoders.ByteLevel()
+        self.eod_id = self.tokenizer.token_to_id(EOD_TEXT)
+        if self.eod_id is None:
+            raise KeyError(f"{vocab_file} has no {EOD_TEXT} token")
+
+
+class HFTokenizer(_TokenizersBackend):
+    """A ``tokenizers`` JSON file (e.g. the 20B tokenizer)."""
+
+    name = "HFTokenizer"
+
+    def __init__(self, vocab_file: str):
+        from tokenizers import Tokenizer as _Tok
+        self.tokenizer = _Tok.from_file(vocab_file)
+        self.eod_id = self.tokenizer.token_to_id(EOD_TEXT)
+        self.pad_id = self.tokenizer.token_to_id(PAD_TEXT)
+
+    def tokenize_batch(self, texts):
+        return self.tokenizer.encode_batch(texts)       # Encoding objects, as the preprocessing tools expect
+
+
+class SentencePieceTokenizer(Tokenizer):
+    name = "SPM"
+
+    def __init__(self, vocab_file: str):
+        import sentencepiece as spm
+        self.tokenizer = spm.SentencePieceProcessor(model_file=vocab_file)
+        self.eod_id = self.tokenizer.piece_to_id(EOD_TEXT)
+
+    def _size(self):
+        return self.tokenizer.get_piece_size()
+
+    def _get_vocab(self):
+        return {self.tokenizer.id_to_piece(i): i for i in range(self._size())}
+
+    def _encode(self, text):
+        return self.tokenizer.encode(text)
+
+    def _decode(self, ids):
+        return self.tokenizer.decode(ids)
+
+
+class HFGPT2Tokenizer(Tokenizer):
+    """``transformers`` GPT-2 tokenizer (fast by default) from a local path or the hub name ``gpt2``."""
+
+    def __init__(self, vocab_file: Optional[str] = None, fast: bool = True):
+        from transformers import GPT2Tokenizer, GPT2TokenizerFast
+        self.name = "HFGPT2TokenizerFast" if fast else "HFGPT2Tokenizer"
+        self.tokenizer = (GPT2TokenizerFast if fast else GPT2Tokenizer).from_pretrained(vocab_file or "gpt2")
+        self.tokenizer.add_special_tokens({"pad_token": PAD_TEXT})
+        self.eod_id, self.pad_id = self.tokenizer.eos_token_id, self.tokenizer.pad_token_id
+
+    def _size(self):
+        return len(self.tokenizer)
+
+    def _get_vocab(self):
+        return self.tokenizer.get_vocab()
+
+    def _encode(self, text):
+        return self.tokenizer.encode(text)
+
+    def _decode(self, ids):
+        return self.tokenizer.decode(ids)
+
+
+class CharLevelTokenizer(Tokenizer):
+    """One token per UTF-8 byte; 0 = end of document, 1 = padding.  Decoding maps ids below 32 to a space-range
+    character so that control bytes never reach a terminal."""
+
+    name, eod_id, pad_id = "CharLevelTokenizer", 0, 1
+
+    def __init__(self, vocab_size: int):
+        self._n = vocab_size
+
+    def _size(self):
+        return self._n
+
+    def clamp(self, n: int) -> int:
+        return max(32, min(n, self._n))
+
+    def decode_token(self, token: int) -> str:
+        return chr(self.clamp(token))
+
+    def _encode(self, text):
+        return list(np.frombuffer(text.encode("utf-8", errors="replace"), dtype=np.uint8).astype(np.int64))
+
+    def tokenize_batch(self, texts):
+        return [self._encode(t) for t in texts] if isinstance(texts, list) else self._encode(texts)
+
+    def _decode(self, ids):
+        return "".join(self.decode_token(i) for i in ids)
+
+
+class TiktokenTokenizer(Tokenizer):
+    name = "TiktokenTokenizer"
+
+    def __init__(self, vocab_file: str):
+        import tiktoken
+        self.tokenizer = tiktoken.get_encoding(vocab_file)
+        self.eod_id = self.tokenizer.eot_token
+
+    def _size(self):
+        return self.tokenizer.n_vocab
+
+    def _encode(self, text):
+        return self.tokenizer.encode(text)
+
+    def tokenize_batch(self, texts):
+        return self.tokenizer.encode_batch(texts, allowed_special="all")
+
+    def _decode(self, ids):
+        return self.tokenizer.decode(tokens=ids, errors="strict")
+
+
+def _need(args, *fields):
+    for f in fields:
+        if getattr(args, f) is None:
+            raise AssertionError(f"tokenizer_type {args.tokenizer_type} needs `{f}`")
+
+
+def _make_hf_gpt2(args):
+    if args.vocab_file is None:
+        print("WARNING: No vocab file found, loading Huggingface's pretrained GPT2Tokenizer")
+    return HFGPT2Tokenizer(args.vocab_file)
+
+
+# tokenizer_type (lower case) -> (required argument fields, constructor from the arguments)
+_REGISTRY: Dict[str, tuple] = {
+    "gpt2bpetokenizer": (("vocab_file", "merge_file"), lambda a: _GPT2BPETokenizer(a.vocab_file, a.merge_file)),
+    "spmtokenizer": (("vocab_file",), lambda a: SentencePieceTokenizer(a.vocab_file)),
+    "hftokenizer": (("vocab_file",), lambda a: HFTokenizer(a.vocab_file)),
+    "hfgpt2tokenizer": ((), _make_hf_gpt2),
+    "charleveltokenizer": ((), lambda a: CharLevelTokenizer(vocab_size=512)),
+    "tiktokentokenizer": (("vocab_file",), lambda a: TiktokenTokenizer(a.vocab_file)),
+}
 
 
 def build_tokenizer(args):
     """Build the tokenizer named by ``args.tokenizer_type`` and set ``args.padded_vocab_size``."""
     if args.rank in (0, None):
         print(f"> building {args.tokenizer_type} tokenizer ...", flush=True)
-    t = args.tokenizer_type.lower()
     if getattr(args, "dataset_impl", None) == "synthetic" and args.vocab_file is None:
         tokenizer = SyntheticTokenizer(args.synthetic_vocab_size)
-    elif t == "GPT2BPETokenizer".lower():
-        assert args.vocab_file is not None
-        assert args.merge_file is not None
-        tokenizer = _GPT2BPETokenizer(args.vocab_file, args.merge_file)
-    elif t == "SPMTokenizer".lower():
-        assert args.vocab_file is not None
-        tokenizer = SentencePieceTokenizer(args.vocab_file)
-    elif t == "HFTokenizer".lower():
-        assert args.vocab_file is not None
-        tokenizer = HFTokenizer(args.vocab_file)
-    elif t == "HFGPT2Tokenizer".lower():
-        if args.vocab_file is None:
-            print("WARNING: No vocab file found, loading Huggingface's pretrained GPT2Tokenizer")
-        tokenizer = HFGPT2Tokenizer(args.vocab_file)
-    elif t == "CharLevelTokenizer".lower():
-        tokenizer = CharLevelTokenizer(vocab_size=512)
-    elif t == "TiktokenTokenizer".lower():
-        assert args.vocab_file is not None
-        tokenizer = TiktokenTokenizer(args.vocab_file)
     else:
-        raise NotImplementedError(f"{args.tokenizer_type} tokenizer is not implemented.")
+        entry = _REGISTRY.get(args.tokenizer_type.lower())
+        if entry is None:
+            raise NotImplementedError(f"{args.tokenizer_type} tokenizer is not implemented.")
+        _need(args, *entry[0])
+        tokenizer = entry[1](args)
     args.padded_vocab_size = _vocab_size_with_padding(tokenizer.vocab_size, args)
     return tokenizer
-
-
-def _vocab_size_with_padding(orig_vocab_size, args):
-    """Round the vocabulary up to a multiple of ``make_vocab_size_divisible_by * model_parallel_size``
-    (50277 -> 50304 at MP 1, 50432 at MP 2)."""
-    multiple = args.make_vocab_size_divisible_by * args.model_parallel_size
-    after = orig_vocab_size
-    while after % multiple != 0:
-        after += 1
-    if args.rank in (0, None):
-        print(f" > padded vocab (size: {orig_vocab_size}) with {after - orig_vocab_size} dummy tokens "
-              f"(new size: {after})", flush=True)
-    return after
-
-
-class AbstractTokenizer(ABC):
-    def __init__(self, name):
-        self.name = name
-
-    @property
-    @abstractmethod
-    def vocab_size(self):
-        ...
-
-    @property
-    @abstractmethod
-    def vocab(self):
-        ...
-
-    @property
-    @abstractmethod
-    def inv_vocab(self):
-        ...
-
-    @abstractmethod
-    def tokenize(self, text):
-        ...
-
-    def detokenize(self, token_ids):
-        raise NotImplementedError(f"detokenizer is not implemented for {self.name} tokenizer")
-
-    @property
-    def cls(self):
-        raise NotImplementedError(f"CLS is not provided for {self.name} tokenizer")
-
-    @property
-    def sep(self):
-        raise NotImplementedError(f"SEP is not provided for {self.name} tokenizer")
-
-    @property
-    def pad(self):
-        raise NotImplementedError(f"PAD is not provided for {self.name} tokenizer")
-
-    @property
-    def eod(self):
-        raise NotImplementedError(f"EOD is not provided for {self.name} tokenizer")
-
-    @property
-    def mask(self):
-        raise NotImplementedError(f"MASK is not provided for {self.name} tokenizer")
-
-
-class SyntheticTokenizer(AbstractTokenizer):
-    """Fixed-size vocabulary without text: ids are their own tokens (synthetic-token training)."""
-
-    def __init__(self, vocab_size):
-        super().__init__("Synthetic")
-        self._n = int(vocab_size)
-        self.eod_id = 0
-        self.pad_id = 1
-
-    @property
-    def vocab_size(self):
-        return self._n
-
-    @property
-    def vocab(self):
-        return {str(i): i for i in range(self._n)}
-
-    @property
-    def inv_vocab(self):
-        return {i: str(i) for i in range(self._n)}
-
-    def tokenize(self, text):
-        return [int(t) % self._n for t in str(text).split() if t.lstrip("-").isdigit()]
-
-    def detokenize(self, token_ids):
-        return " ".join(str(int(t)) for t in token_ids)
-
-    @property
-    def eod(self):
-        return self.eod_id
-
-
-@lru_cache()
-def _bytes_to_unicode():
-    bs = list(range(ord("!"), ord("~") + 1)) + list(range(ord("¡"), ord("¬") + 1)) + list(range(ord("®"), ord("ÿ") + 1))
-    cs = bs[:]
-    n = 0
-    for b in range(2 ** 8):
-        if b not in bs:
-            bs.append(b)
-            cs.append(2 ** 8 + n)
-            n += 1
-    return dict(zip(bs, [chr(c) for c in cs]))
-
-
-class _GPT2BPETokenizer(AbstractTokenizer):
-    """Byte-level BPE from ``vocab.json`` + ``merges.txt``, executed by the ``tokenizers`` library."""
-
-    def __init__(self, vocab_file, merge_file):
-        super().__init__("GPT2 BPE")
-        from tokenizers import Tokenizer, decoders, models, pre_tokenizers
-        tok = Tokenizer(models.BPE.from_file(vocab_file, merge_file))
-        tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
-        tok.decoder = decoders.ByteLevel()
-        self.tokenizer = tok
-        self._vocab = tok.get_vocab()
-        self._inv = {v: k for k, v in self._vocab.items()}
-        self.eod_id = self._vocab["<|endoftext|>"]
-
-    @property
-    def vocab_size(self):
-        return len(self._vocab)
-
-    @property
-    def vocab(self):
-        return self._vocab
-
-    @property
-    def inv_vocab(self):
-        return self._inv
-
-    def tokenize(self, text):
-        return self.tokenizer.encode(text).ids
-
-    def detokenize(self, token_ids):
-        return self.tokenizer.decode(list(map(int, token_ids)))
-
-    @property
-    def eod(self):
-        return self.eod_id
-
-
-class SentencePieceTokenizer(AbstractTokenizer):
-    def __init__(self, vocab_file):
-        super().__init__("SPM")
-        import sentencepiece as spm
-        self.tokenizer = spm.SentencePieceProcessor(model_file=vocab_file)
-        self.eod_id = self.tokenizer.piece_to_id("<|endoftext|>")
-
-    @property
-    def vocab_size(self):
-        return self.tokenizer.get_piece_size()
-
-    @property
-    def vocab(self):
-        return {self.tokenizer.id_to_piece(i): i for i in range(self.tokenizer.get_piece_size())}
-
-    @property
-    def inv_vocab(self):
-        return {i: self.tokenizer.id_to_piece(i) for i in range(self.tokenizer.get_piece_size())}
-
-    def tokenize(self, text):
-        return self.tokenizer.encode(text)
-
-    def detokenize(self, token_ids):
-        return self.tokenizer.decode(list(map(int, token_ids)))
-
-    @property
-    def eod(self):
-        return self.eod_id
-
-
-class HFTokenizer(AbstractTokenizer):
-    """A ``tokenizers`` JSON file (e.g. the 20B tokenizer)."""
-
-    def __init__(self, vocab_file):
-        super().__init__("HFTokenizer")
-        from tokenizers import Tokenizer
-        self.tokenizer = Tokenizer.from_file(vocab_file)
-        self.eod_id = self.tokenizer.token_to_id("<|endoftext|>")
-        self.pad_id = self.tokenizer.token_to_id("<|padding|>")
-
-    @property
-    def vocab_size(self):
-        return self.tokenizer.get_vocab_size()
-
-    @property
-    def vocab(self):
-        return self.tokenizer.get_vocab()
-
-    @property
-    def inv_vocab(self):
-        return {v: k for k, v in self.tokenizer.get_vocab().items()}
-
-    def tokenize(self, text: str):
-        return self.tokenizer.encode(text).ids
-
-    def tokenize_batch(self, text_batch: Union[List[str], str]):
-        return self.tokenizer.encode_batch(text_batch)
-
-    def detokenize(self, token_ids):
-        return self.tokenizer.decode(list(map(int, token_ids)))
-
-    @property
-    def eod(self):
-        return self.eod_id
-
-
-class HFGPT2Tokenizer(AbstractTokenizer):
-    def __init__(self, vocab_file=None, fast=True):
-        name = "HFGPT2TokenizerFast" if fast else "HFGPT2Tokenizer"
-        super().__init__(name)
-        if vocab_file is None:
-            vocab_file = "gpt2"
-        from transformers import GPT2Tokenizer, GPT2TokenizerFast
-        self.tokenizer = (GPT2TokenizerFast if fast else GPT2Tokenizer).from_pretrained(vocab_file)
-        self.tokenizer.add_special_tokens({"pad_token": "<|padding|>"})
-        self.eod_id = self.tokenizer.eos_token_id
-        self.pad_id = self.tokenizer.pad_token_id
-
-    @property
-    def vocab_size(self):
-        return len(self.tokenizer)
-
-    @property
-    def vocab(self):
-        return self.tokenizer.get_vocab()
-
-    @property
-    def inv_vocab(self):
-        return {v: k for k, v in self.tokenizer.get_vocab().items()}
-
-    def tokenize(self, text: str):
-        return self.tokenizer.encode(text)
-
-    def tokenize_batch(self, text_batch):
-        return [self.tokenize(t) for t in ([text_batch] if isinstance(text_batch, str) else text_batch)]
-
-    def detokenize(self, token_ids):
-        return self.tokenizer.decode(list(map(int, token_ids)))
-
-    @property
-    def eod(self):
-        return self.eod_id
-
-
-class CharLevelTokenizer(AbstractTokenizer):
-    """One token per byte; 0 = end of document, 1 = padding."""
-
-    def __init__(self, vocab_size):
-        super().__init__("CharLevelTokenizer")
-        self._vocab_size = vocab_size
-        self.eod_id = 0
-        self.pad_id = 1
-
-    def clamp(self, n):
-        return max(32, min(n, self.vocab_size))
-
-    @property
-    def vocab_size(self):
-        return self._vocab_size
-
-    @property
-    def vocab(self):
-        raise NotImplementedError
-
-    @property
-    def inv_vocab(self):
-        raise NotImplementedError
-
-    def decode_token(self, token: int):
-        return str(chr(self.clamp(token)))
-
-    def tokenize(self, text: str):
-        return list(np.frombuffer(text.encode("utf-8", errors="replace"), dtype=np.uint8).astype(np.int64))
-
-    def tokenize_batch(self, text_batch):
-        if isinstance(text_batch, list):
-            return [self.tokenize(s) for s in text_batch]
-        return self.tokenize(text_batch)
-
-    def detokenize(self, token_ids):
-        return "".join(map(self.decode_token, token_ids))
-
-    @property
-    def eod(self):
-        return self.eod_id
-
-
-class TiktokenTokenizer(AbstractTokenizer):
-    def __init__(self, vocab_file):
-        super().__init__("TiktokenTokenizer")
-        import tiktoken
-        self.tokenizer = tiktoken.get_encoding(vocab_file)
-        self.eod_id = self.tokenizer.eot_token
-        self.pad_id = None
-
-    @property
-    def vocab_size(self):
-        return self.tokenizer.n_vocab
-
-    @property
-    def vocab(self):
-        raise NotImplementedError("TiktokenTokenizer does not implement vocabulary access.")
-
-    @property
-    def inv_vocab(self):
-        raise NotImplementedError("TiktokenTokenizer does not implement vocabulary access.")
-
-    def tokenize(self, text: str):
-        return self.tokenizer.encode(text)
-
-    def tokenize_batch(self, text_batch: List[str]):
-        return self.tokenizer.encode_batch(text_batch, allowed_special="all")
-
-    def detokenize(self, token_ids):
-        return self.tokenizer.decode(tokens=list(map(int, token_ids)), errors="strict")
-
-    @property
-    def eod(self):
-        return self.eod_id
-
-    @property
-    def pad(self):
-        raise NotImplementedError
