@@ -146,7 +146,7 @@ def test_forward_step_dpo_starts_at_log2_and_learns():
     ref = copy.deepcopy(model)
     batch = _pairs()
     loss, metrics = training.forward_step(iter([batch]), model, a, None, is_train=True, reference_model=ref)
-    assert float(loss) == pytest.approx(math.log(2.0), rel=1e-4)
+    assert loss.item() == pytest.approx(math.log(2.0), rel=1e-4)
     assert float(metrics["margins"]) == pytest.approx(0.0, abs=1e-5)
     opt = torch.optim.SGD(model.parameters(), lr=0.5)
     for _ in range(8):
