@@ -154,7 +154,7 @@ def test_forward_step_dpo_starts_at_log2_and_learns():
         loss, metrics = training.forward_step(iter([batch]), model, a, None, is_train=True, reference_model=ref)
         loss.backward()
         opt.step()
-    assert float(loss) < math.log(2.0) - 0.05 and float(metrics["reward_acc"]) == 1.0
+    assert loss.item() < math.log(2.0) - 0.05 and float(metrics["reward_acc"]) == 1.0
 
 
 def test_forward_step_reward_model_uses_a_scalar_head():
