@@ -341,6 +341,7 @@ class Engine(torch.nn.Module):
         self.store_gradients = False
         self.stored_gradients = None
         self.timer_values = None
+        self.curriculum_scheduler = None
         self.training_dataloader = None
 
     # ------------------------------------------------------------------ reference-engine surface
@@ -349,6 +350,12 @@ class Engine(torch.nn.Module):
         return self
 
     def forward(self, *inputs, **kwargs):
+        # sequence-length curriculum: while training, the current difficulty is handed to the model, which
+        # truncates the batch to it (models/utils.py SequentialWrapper.forward) and records it in the arguments
+        # so that the loss side truncates labels and mask the same way
+        sched = getattr(self, "curriculum_scheduler", None)
+        if sched is not None and self.module.training and "curriculum_seqlen" not in kwargs:
+            kwargs["curriculum_seqlen"] = sched.update_difficulty(self.global_steps + 1)
         return self.module(*inputs, **kwargs)
 
     def is_gradient_accumulation_boundary(self):

@@ -173,3 +173,43 @@ def test_prepare_preference_data_writes_the_recipe_files(tmp_path):
     assert rd(tmp_path / "data" / "sft" / "t_sft_train.jsonl")[0] == {"messages": good["chosen"]}
     kto = rd(tmp_path / "data" / "kto" / "t_kto_train.jsonl")
     assert [r["reward"] for r in kto] == [1, -1, 1, -1]
+
+
+def _train_curriculum(rank, world, cfg, steps):
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    from gpt_neox_b200.models import utils as model_utils
+    torch.set_num_threads(1)
+    mpu.destroy_model_parallel()
+    a = NeoXArgs.from_dict(dict(cfg, global_num_gpus=world, train_iters=steps))
+    a.configure_distributed_args()
+    a.build_tokenizer()
+    seen, losses = [], []
+    inner = model_utils.SequentialWrapper.forward
+
+    def spy(self, forward_input, curriculum_seqlen=None, labels=None, neox_args=None):
+        if self.training:
+            seen.append(curriculum_seqlen)
+        return inner(self, forward_input, curriculum_seqlen=curriculum_seqlen, labels=labels, neox_args=neox_args)
+    model_utils.SequentialWrapper.forward = spy
+    training.collect_loss_for_unit_test = lambda l: losses.append(float(l))
+    try:
+        training.pretrain(a)
+    finally:
+        model_utils.SequentialWrapper.forward = inner
+    return {"seen": seen, "losses": losses}
+
+
+def test_sequence_length_curriculum_reaches_the_model():
+    """The engine hands the scheduled length to the model on every training step; the batch (and the loss side)
+    are truncated to it, and it grows to the full length over `total_curriculum_step` steps."""
+    from common import run_distributed, tiny_config
+    cfg = tiny_config(use_cpu_initialization=True,
+                      curriculum_learning={"enabled": True, "curriculum_type": "seqlen", "min_difficulty": 8,
+                                           "max_difficulty": 32, "schedule_type": "fixed_linear",
+                                           "schedule_config": {"total_curriculum_step": 4, "difficulty_step": 8}})
+    r = run_distributed(_train_curriculum, 1, cfg, 6)[0]
+    assert r["seen"][0] is not None and r["seen"][0] < 32
+    assert r["seen"] == sorted(r["seen"]) and r["seen"][-1] == 32
+    assert len(r["losses"]) == 6 and all(l == l for l in r["losses"])
