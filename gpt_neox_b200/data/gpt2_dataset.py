@@ -70,7 +70,20 @@ class GPT2Dataset(torch.utils.data.Dataset):
             out_lengths.append(len(p))
         return np.concatenate(pieces), (lengths if is_reward else out_lengths)
 
+    def _whole_docs(self, dataset, first_doc, last_doc, is_reward, lengths):
+        """Documents [first_doc, last_doc) in full, concatenated (the unpacked and pack-until-overflow items: an
+        item never borrows a token from the document after it)."""
+        pieces, out_lengths = [], []
+        for j, d in enumerate(range(first_doc, last_doc)):
+            if is_reward:
+                pieces.append(np.full(lengths[j], dataset.get(self.doc_idx[d])[0]))
+            else:
+                pieces.append(dataset.get(self.doc_idx[d]))
+                out_lengths.append(len(pieces[-1]))
+        return np.concatenate(pieces), (lengths if is_reward else out_lengths)
+
     def __getitem__(self, idx):
+        asked = idx
         try:
             idx = self.shuffle_idx[idx]
             first_doc, off_first = self.sample_idx[idx]
@@ -84,8 +97,11 @@ class GPT2Dataset(torch.utils.data.Dataset):
                 streams.append(("ref", self.ref_dataset, np.float32))
             ret, lengths = {}, []
             for key, ds, dt in streams:
-                sample, lengths = self._span(ds, int(first_doc), int(last_doc), int(off_first), int(off_last),
-                                             key == "reward", lengths)
+                if self.pack_impl == "packed":
+                    sample, lengths = self._span(ds, int(first_doc), int(last_doc), int(off_first), int(off_last),
+                                                 key == "reward", lengths)
+                else:
+                    sample, lengths = self._whole_docs(ds, int(first_doc), int(last_doc), key == "reward", lengths)
                 want = self.seq_length + 1
                 if len(sample) < want:
                     sample = np.pad(sample, (0, want - len(sample)), mode="constant",
@@ -95,8 +111,10 @@ class GPT2Dataset(torch.utils.data.Dataset):
                 ret[key] = np.array(sample, dtype=dt)
             return ret
         except IndexError as err:
-            new_idx = idx % len(self)
-            print(f"WARNING: Got index out of bounds error with index {idx} - taking modulo of index instead "
+            new_idx = int(asked) % len(self)
+            if new_idx == asked:
+                raise                   # already in range: a real indexing fault, not a wrap-around request
+            print(f"WARNING: Got index out of bounds error with index {asked} - taking modulo of index instead "
                   f"({new_idx}), error: {err}")
             return self[new_idx]
 
@@ -174,7 +192,7 @@ def _build_index_mappings(name, data_prefix, documents, sizes, label_dataset, nu
             np_rng.shuffle(order)
             running, cur = 0, 0
             while len(sample_idx) < num_samples:
-                d = order[cur]
+                d = int(documents[order[cur]])          # document id in the indexed dataset (splits start anywhere)
                 skip = (not allow_chopped and sizes[d] > seq_length + 1) or \
                        (label_dataset is not None and np.all(label_dataset.get(d)[: seq_length + 1] == -100))
                 if not skip:
@@ -201,13 +219,18 @@ def _build_index_mappings(name, data_prefix, documents, sizes, label_dataset, nu
             np_rng.shuffle(shuffle_idx)
             sample_idx = np.zeros((num_samples + 1, 2), dtype=np.int64)
             sample_idx[:, 0] = np.arange(num_samples + 1)
-            doc_idx, d = [], 0
+            doc_idx, at, examined = [], 0, 0
             while len(doc_idx) <= num_samples:
+                d = int(documents[at])                  # document id in the indexed dataset (splits start anywhere)
                 skip = (not allow_chopped and sizes[d] > seq_length + 1) or \
                        (label_dataset is not None and np.all(label_dataset.get(d)[:seq_length] == -100))
                 if not skip:
                     doc_idx.append(d)
-                d = (d + 1) % len(documents)
+                at = (at + 1) % len(documents)
+                examined += 1
+                if examined == len(documents) and not doc_idx:
+                    raise ValueError(f"{name}: every document is either longer than seq_length + 1 (allow_chopped "
+                                     f"is off) or fully masked by its labels")
             np.save(doc_idx_filename, doc_idx, allow_pickle=True)
             np.save(sample_idx_filename, sample_idx, allow_pickle=True)
             np.save(shuffle_idx_filename, shuffle_idx, allow_pickle=True)

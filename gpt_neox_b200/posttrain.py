@@ -39,8 +39,10 @@ def rm_loss(outputs, loss_mask, z_loss):
     metrics = {}
     pos, neg = torch.chunk(_first(outputs), 2, 0)
     pos_mask, neg_mask = torch.chunk(loss_mask, 2, 0)
-    pos_idx = pos_mask.nonzero()[:, 1].unsqueeze(1)
-    neg_idx = neg_mask.nonzero()[:, 1].unsqueeze(1)
+    # the score of a sequence is read at its LAST unmasked position (data prepared for reward modelling labels
+    # only that token; with a whole completion labelled the last of its tokens is taken)
+    last = lambda m: (m > 0).float().mul(torch.arange(1, m.shape[1] + 1, device=m.device)).argmax(dim=1, keepdim=True)
+    pos_idx, neg_idx = last(pos_mask), last(neg_mask)
     pos = torch.gather(pos.squeeze(-1), dim=1, index=pos_idx)
     neg = torch.gather(neg.squeeze(-1), dim=1, index=neg_idx)
     with torch.no_grad():

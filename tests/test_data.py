@@ -160,3 +160,30 @@ def test_mmap_builder_merge_shifts_document_boundaries(tmp_path):
     assert len(ds) == 9 and list(ds.doc_idx) == list(range(10))
     for i, d in enumerate(a + b):
         assert np.array_equal(ds[i], d)
+
+
+@pytest.mark.parametrize("pack_impl", ["unpacked", "pack_until_overflow"])
+def test_whole_document_items_respect_the_split_and_never_borrow_tokens(tmp_path, pack_impl):
+    """`unpacked` / `pack_until_overflow` items are made of whole documents of THEIR split (a split that starts
+    at document 30 must not read document 0) and carry no token of the following document."""
+    from gpt_neox_b200.data.gpt2_dataset import GPT2Dataset
+    rng = np.random.default_rng(5)
+    docs = [np.full(int(rng.integers(3, 9)), 100 + i, dtype=np.int32) for i in range(40)]     # doc i is all (100 + i)
+    prefix = _write(tmp_path, docs)
+    ds = indexed_dataset.make_dataset(prefix, "mmap", skip_warmup=True)
+    split = np.arange(30, 40, dtype=np.int32)
+    seq = 16
+    g = GPT2Dataset("valid", prefix, split, ds, num_samples=12, num_epochs=None, seq_length=seq, seed=1,
+                    pack_impl=pack_impl, use_shared_fs=True)
+    seen = set()
+    for i in range(len(g)):
+        item = g[i]["text"]
+        assert item.shape == (seq + 1,)
+        body = item[item != 0]                                   # zero padding at the end
+        ids = sorted(set(int(t) - 100 for t in body))
+        assert all(30 <= d < 40 for d in ids)                    # only documents of the split
+        assert len(body) == sum(len(docs[d]) for d in ids)       # whole documents, nothing borrowed
+        if pack_impl == "unpacked":
+            assert len(ids) == 1
+        seen.update(ids)
+    assert len(seen) >= 5

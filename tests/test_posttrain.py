@@ -66,6 +66,10 @@ def test_rm_loss_reads_the_last_unmasked_position():
     pos, neg = torch.tensor([2.0, 1.0]), torch.tensor([0.5, 3.0])
     assert float(loss) == pytest.approx(float(-F.logsigmoid(pos - neg).mean()), rel=1e-6)
     assert float(m["accuracy"]) == 0.5 and float(m["margin"]) == pytest.approx(-0.25)
+    # a whole completion labelled: still the last unmasked position of each row
+    wide = torch.tensor([[1, 1, 0], [0, 1, 1], [1, 1, 0], [1, 1, 1]], dtype=torch.float32)
+    same, _ = posttrain.rm_loss(values, wide, z_loss=0.0)
+    assert float(same) == pytest.approx(float(loss))
     with_z, _ = posttrain.rm_loss(values, mask, z_loss=0.1)
     assert float(with_z - loss) == pytest.approx(0.1 * float((pos ** 2 + neg ** 2).mean()), rel=1e-6)
 
