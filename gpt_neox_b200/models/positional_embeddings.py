@@ -19,6 +19,17 @@ class SinusoidalPositionalEmbedding(nn.Module):
         self.precision = precision
 
     def forward(self, x, seq_dim=1):
+        """``x``: an integer tensor of position ids [b, s] -> the table rows of those positions [b, s, dim] (so a
+        decoding step with a KV cache, which feeds one token at position t, gets row t and not row 0); any other
+        tensor -> rows 0 .. s-1 along ``seq_dim`` as [1, s, dim]."""
+        if not x.is_floating_point() and x.dim() == 2:
+            sinusoid_inp = x.to(self.inv_freq.dtype).unsqueeze(-1) * self.inv_freq
+            if self.precision == torch.bfloat16:
+                sinusoid_inp = sinusoid_inp.float()
+            sin, cos = sinusoid_inp.sin(), sinusoid_inp.cos()
+            if self.precision == torch.bfloat16:
+                sin, cos = sin.bfloat16(), cos.bfloat16()
+            return torch.cat((sin, cos), dim=-1)
         t = torch.arange(x.shape[seq_dim], device=x.device).type_as(self.inv_freq)
         sinusoid_inp = torch.einsum("i,j->ij", t, self.inv_freq)
         if self.precision == torch.bfloat16:

@@ -150,6 +150,9 @@ def stream_tokens(neox_args, model, context_tokens: List[List[int]], eos_token_i
     pos = first = int(start_index.min().item())
     last = min(neox_args.seq_length - 1, pos + maximum_tokens - 1)
     pipe = bool(neox_args.is_pipe_parallel)
+    if any(k in ("mamba", "rwkv") for k in (neox_args.attention_config or [])):
+        # the recurrent blocks keep no state between calls: every step runs the whole prefix
+        recompute = True
     with torch.no_grad():
         done = torch.zeros(bsz, dtype=torch.bool, device=dev)
         end_index = torch.full((bsz,), -1, dtype=torch.long, device=dev)

@@ -42,7 +42,8 @@ def test_pad_batch_and_stop_tokens():
     assert not stop_tokens_in_completion([torch.tensor([6, 8])], ctx, 0, 3)
 
 
-@pytest.mark.parametrize("over", [dict(), dict(pos_emb="learned"), dict(gpt_j_residual=False, num_kv_heads=2)])
+@pytest.mark.parametrize("over", [dict(), dict(pos_emb="learned"), dict(gpt_j_residual=False, num_kv_heads=2),
+                                  dict(pos_emb="sinusoidal"), dict(pos_emb="alibi"), dict(sliding_window_width=4)])
 def test_kv_cache_decoding_matches_recompute(over):
     from gpt_neox_b200.text_generation_utils import stream_tokens
     a, m = _model(**over)
@@ -110,3 +111,38 @@ def test_eval_adapter_loglikelihood_matches_direct_computation():
         assert ll == pytest.approx(want, rel=1e-4, abs=1e-4)
         assert greedy == bool((lp.argmax(-1) == torch.tensor(t)).all())
     assert len(ad.loglikelihood_rolling([("some document text " * 5,)])) == 1
+
+
+def test_recurrent_stacks_decode_by_recompute():
+    """Mamba / RWKV blocks keep no state between calls, so asking for cached decoding must still run the whole
+    prefix: same tokens as an explicit recompute."""
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.text_generation_utils import stream_tokens
+    a = NeoXArgs.from_dict(tiny_config(use_cpu_initialization=True, attention_config=[[["rwkv"], 2]],
+                                       num_attention_heads=1))
+    a.configure_distributed_args()
+    a.build_tokenizer()
+    mpu.destroy_model_parallel()
+    initialize_megatron(a)
+    m = training.get_model(a, use_cache=True)
+    outs = []
+    for recompute in (True, False):
+        m.inference_mode(use_cache=not recompute)
+        m.clear_cache()
+        last = None
+        for last in stream_tokens(a, m, [[5, 9, 11, 3], [7, 2]], maximum_tokens=6, recompute=recompute,
+                                  eos_token_id=10 ** 6):
+            pass
+        outs.append(last[0][:, :10].clone())
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_sinusoidal_table_rows_follow_position_ids():
+    from gpt_neox_b200.models.positional_embeddings import SinusoidalPositionalEmbedding
+    e = SinusoidalPositionalEmbedding(8, precision=torch.float32)
+    full = e(torch.arange(6)[None])                     # [1, 6, 8]
+    one = e(torch.tensor([[4]]))                        # the row a cached decoding step asks for
+    torch.testing.assert_close(one[0, 0], full[0, 4])
