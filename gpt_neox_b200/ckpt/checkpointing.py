@@ -77,6 +77,15 @@ def check_forward_pass(neox_args, model, checkpoint_logits, inference):
                 "validate_checkpoint_forward() forward after load of checkpoint does not yield a close result"
 
 
+def restore_rng_state(rng):
+    random.setstate(rng["random_rng_state"])
+    np.random.set_state(rng["np_rng_state"])
+    torch.set_rng_state(rng["torch_rng_state"])
+    if torch.cuda.is_available() and rng.get("cuda_rng_state") is not None:
+        torch.cuda.set_rng_state(rng["cuda_rng_state"])
+    mpu.get_cuda_rng_tracker().set_states(rng["rng_tracker_states"])
+
+
 def ensure_directory_exists(filename):
     os.makedirs(os.path.dirname(filename), exist_ok=True)
 
@@ -225,12 +234,13 @@ def load_checkpoint(neox_args, model, optimizer, lr_scheduler, inference=False, 
                   f"data available in checkpoint {checkpoint_name}")
     if not neox_args.finetune and not neox_args.no_load_rng:
         try:
-            random.setstate(state_dict["random_rng_state"])
-            np.random.set_state(state_dict["np_rng_state"])
-            torch.set_rng_state(state_dict["torch_rng_state"])
-            if torch.cuda.is_available() and state_dict.get("cuda_rng_state") is not None:
-                torch.cuda.set_rng_state(state_dict["cuda_rng_state"])
-            mpu.get_cuda_rng_tracker().set_states(state_dict["rng_tracker_states"])
+            rng = {k: state_dict[k] for k in ("random_rng_state", "np_rng_state", "torch_rng_state",
+                                              "rng_tracker_states")}
+            rng["cuda_rng_state"] = state_dict.get("cuda_rng_state")
+            restore_rng_state(rng)
+            # building the data iterators after this point draws from the global generators (DataLoader worker
+            # seeds); the training loop re-applies the saved state right before its first step
+            neox_args.pending_rng_state = rng
         except KeyError:
             print_rank_0(f"Unable to load optimizer from checkpoint {checkpoint_name}. Specify --no-load-rng or "
                          "--finetune to prevent attempting to load the optimizer state, exiting ...")

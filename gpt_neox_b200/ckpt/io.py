@@ -7,6 +7,9 @@
         counters, lr-scheduler state, data/model-parallel sizes and the caller's client state
   <dir>/<tag>/layer_<IDX:02d>-model_<MP:02d>-model_states.pt   pipeline runs: one file per layer
   <dir>/<tag>/zero_pp_rank_<DP>_mp_rank_<MP:02d>_optim_states.pt   optimizer shard of each rank
+  <dir>/<tag>/expert_ep_rank_<EP:02d>_mp_rank_<MP:02d>_model_states.pt   expert parallelism > 1: the expert
+        parameters of one expert-parallel rank (the per-MP-rank file above is written by data-parallel rank 0 and
+        therefore only holds expert-parallel rank 0's experts)
 
 Writes are atomic at directory level: every rank writes into ``<tag>.tmp``, then rank 0 renames it
 and rewrites ``latest``; a crash never leaves a half-written tag behind ``latest``.
@@ -43,6 +46,19 @@ def layer_file_name(layer_idx: int, mp_rank: int) -> str:
 def optim_states_name(dp_rank: int, mp_rank: int, bf16: bool = False) -> str:
     prefix = "bf16_" if bf16 else ""
     return f"{prefix}zero_pp_rank_{dp_rank}_mp_rank_{mp_rank:02d}_optim_states.pt"
+
+
+def expert_states_name(ep_rank: int, mp_rank: int) -> str:
+    return f"expert_ep_rank_{ep_rank:02d}_mp_rank_{mp_rank:02d}_model_states.pt"
+
+
+def _expert_param_names(module):
+    return [n for n, p in module.named_parameters() if getattr(p, "expert_parallel", False)]
+
+
+def _expert_state_dict(module):
+    names = set(_expert_param_names(module))
+    return {k: v.detach().cpu() for k, v in module.state_dict().items() if k in names}
 
 
 def _module_state_dict(engine):
@@ -95,6 +111,11 @@ def save_engine_checkpoint(engine, save_dir, tag=None, client_state=None):
         }
         state.update(client_state or {})
         torch.save(state, os.path.join(tmp_dir, model_states_name(mp_rank)))
+    ep = mpu.get_expert_parallel_world_size()
+    if ep > 1 and not is_pipe and dp_rank < ep:        # one writer per expert-parallel rank (expert-DP rank 0)
+        esd = _expert_state_dict(engine.module)
+        if esd:
+            torch.save(esd, os.path.join(tmp_dir, expert_states_name(mpu.get_expert_parallel_rank(), mp_rank)))
     if engine.optimizer is not None:
         name = optim_states_name(dp_rank + pp_rank * 0, mp_rank, bf16=engine.bfloat16_enabled)
         if is_pipe:
@@ -160,6 +181,13 @@ def load_engine_checkpoint(engine, load_dir, tag=None, load_optimizer_states=Tru
     else:
         sd = state["module"]
         _load_into_flat(engine.module, sd, strict=load_module_strict)
+        if mpu.get_expert_parallel_world_size() > 1 and _expert_param_names(engine.module):
+            ef = os.path.join(ckpt_dir, expert_states_name(mpu.get_expert_parallel_rank(), mp_rank))
+            if os.path.isfile(ef):
+                _load_into_flat(engine.module, torch.load(ef, map_location="cpu", weights_only=False), strict=False)
+            elif mpu.get_expert_parallel_rank() > 0:
+                raise FileNotFoundError(f"{ef} is missing: the checkpoint holds no experts for expert-parallel "
+                                        f"rank {mpu.get_expert_parallel_rank()}")
     for g in engine.groups:
         g.refresh_master_from_lp()
     if not load_module_only:

@@ -267,7 +267,9 @@ class FlatAdam:
     def state_dict(self):
         return {"step": self.step_count, "param_groups": [{k: v for k, v in pg.items() if k != "params"}
                                                            for pg in self.param_groups],
-                "shards": [g.shard_state() for g in self.groups], "cur_scale": self.cur_scale}
+                "shards": [g.shard_state() for g in self.groups], "cur_scale": self.cur_scale,
+                # SM3 / MADGRAD / Lion / SGD keep their own per-parameter state (covers, momenta)
+                "generic": None if self.generic is None else self.generic.state_dict()}
 
     def load_state_dict(self, sd):
         self.step_count = sd.get("step", 0)
@@ -277,6 +279,12 @@ class FlatAdam:
         for g, s in zip(self.groups, sd.get("shards", [])):
             ok = g.load_shard_state(s) and ok
         self.cur_scale = sd.get("cur_scale", self.cur_scale)
+        if self.generic is not None and sd.get("generic") is not None:
+            try:
+                self.generic.load_state_dict(sd["generic"])
+            except (ValueError, RuntimeError, KeyError) as e:       # different sharding: its state starts afresh
+                print(f"WARNING: state of {type(self.generic).__name__} not restored ({e})", flush=True)
+                ok = False
         return ok
 
 

@@ -70,3 +70,22 @@ def test_damaged_checkpoints(tmp_path):
     f.write_bytes(data[: len(data) // 2])
     with pytest.raises(Exception):
         run_distributed(_train, 1, _cfg(d), 8)
+
+
+@pytest.mark.parametrize("world,over", [
+    (2, dict(moe_num_experts=4, moe_top_k=2, gpt_j_residual=False, moe_router_type="topk", moe_expert_parallel_size=2)),
+    (1, dict(optimizer={"type": "sm3", "params": {"lr": 1e-3}})),
+    (1, dict(gradient_accumulation_steps=2, hidden_dropout=0.1)),
+], ids=["moe_expert_parallel_2", "sm3_state", "dropout_rng"])
+def test_resume_is_exact_for_expert_parallel_generic_optimizer_and_dropout(tmp_path, world, over):
+    """Things a resume has to carry beyond the dense weights and Adam moments: the experts of every expert-parallel
+    rank (one state file per rank), the own state of SM3 / MADGRAD / Lion / SGD, and the random streams (re-applied
+    after the data iterators are rebuilt, which draw from them)."""
+    full = run_distributed(_train, world, _cfg(tmp_path / "a", **over), 8)[0]
+    first = run_distributed(_train, world, _cfg(tmp_path / "b", **over), 4)[0]
+    rest = run_distributed(_train, world, _cfg(tmp_path / "b", **over), 8)[0]
+    assert first == pytest.approx(full[:4], rel=1e-6)
+    assert len(rest) == 4 and rest == pytest.approx(full[4:], rel=2e-5)
+    if "moe_expert_parallel_size" in over:
+        files = os.listdir(tmp_path / "b" / "global_step8")
+        assert sum(f.startswith("expert_ep_rank_") for f in files) == 2
