@@ -48,8 +48,9 @@ def optim_states_name(dp_rank: int, mp_rank: int, bf16: bool = False) -> str:
     return f"{prefix}zero_pp_rank_{dp_rank}_mp_rank_{mp_rank:02d}_optim_states.pt"
 
 
-def expert_states_name(ep_rank: int, mp_rank: int) -> str:
-    return f"expert_ep_rank_{ep_rank:02d}_mp_rank_{mp_rank:02d}_model_states.pt"
+def expert_states_name(ep_rank: int, mp_rank: int, pp_rank: int = None) -> str:
+    stage = "" if pp_rank is None else f"_pp{pp_rank:02d}"
+    return f"expert_ep_rank_{ep_rank:02d}_mp_rank_{mp_rank:02d}{stage}_model_states.pt"
 
 
 def _expert_param_names(module):
@@ -112,10 +113,11 @@ def save_engine_checkpoint(engine, save_dir, tag=None, client_state=None):
         state.update(client_state or {})
         torch.save(state, os.path.join(tmp_dir, model_states_name(mp_rank)))
     ep = mpu.get_expert_parallel_world_size()
-    if ep > 1 and not is_pipe and dp_rank < ep:        # one writer per expert-parallel rank (expert-DP rank 0)
+    if ep > 1 and dp_rank < ep:        # one writer per expert-parallel rank (expert-DP rank 0), per pipeline stage
         esd = _expert_state_dict(engine.module)
         if esd:
-            torch.save(esd, os.path.join(tmp_dir, expert_states_name(mpu.get_expert_parallel_rank(), mp_rank)))
+            torch.save(esd, os.path.join(tmp_dir, expert_states_name(mpu.get_expert_parallel_rank(), mp_rank,
+                                                                     pp_rank if is_pipe else None)))
     if engine.optimizer is not None:
         name = optim_states_name(dp_rank + pp_rank * 0, mp_rank, bf16=engine.bfloat16_enabled)
         if is_pipe:
@@ -181,13 +183,14 @@ def load_engine_checkpoint(engine, load_dir, tag=None, load_optimizer_states=Tru
     else:
         sd = state["module"]
         _load_into_flat(engine.module, sd, strict=load_module_strict)
-        if mpu.get_expert_parallel_world_size() > 1 and _expert_param_names(engine.module):
-            ef = os.path.join(ckpt_dir, expert_states_name(mpu.get_expert_parallel_rank(), mp_rank))
-            if os.path.isfile(ef):
-                _load_into_flat(engine.module, torch.load(ef, map_location="cpu", weights_only=False), strict=False)
-            elif mpu.get_expert_parallel_rank() > 0:
-                raise FileNotFoundError(f"{ef} is missing: the checkpoint holds no experts for expert-parallel "
-                                        f"rank {mpu.get_expert_parallel_rank()}")
+    if mpu.get_expert_parallel_world_size() > 1 and _expert_param_names(engine.module):
+        ef = os.path.join(ckpt_dir, expert_states_name(mpu.get_expert_parallel_rank(), mp_rank,
+                                                       pp_rank if is_pipe else None))
+        if os.path.isfile(ef):
+            _load_into_flat(engine.module, torch.load(ef, map_location="cpu", weights_only=False), strict=False)
+        elif mpu.get_expert_parallel_rank() > 0:
+            raise FileNotFoundError(f"{ef} is missing: the checkpoint holds no experts for expert-parallel "
+                                    f"rank {mpu.get_expert_parallel_rank()}")
     for g in engine.groups:
         g.refresh_master_from_lp()
     if not load_module_only:
