@@ -21,6 +21,17 @@ from .engine import Engine
 _DTYPES = [torch.float32, torch.float16, torch.bfloat16, torch.int64, torch.int32, torch.uint8, torch.bool]
 
 
+class _StageGrid:
+    """The pipeline group this rank belongs to, as generation / evaluation code addresses it
+    (``engine.grid.stage_to_global(stage)`` -> global rank of that stage in this rank's pipeline)."""
+
+    def __init__(self, ranks):
+        self.ranks = list(ranks)
+
+    def stage_to_global(self, stage_id: int) -> int:
+        return self.ranks[stage_id]
+
+
 class PipelineEngine(Engine):
     def __init__(self, module, neox_args, param_groups, optimizer_cfg=None, lr_scheduler=None,
                  generic_optimizer=None):
@@ -28,6 +39,7 @@ class PipelineEngine(Engine):
         self.num_stages = mpu.get_pipe_parallel_world_size()
         self.stage_id = mpu.get_pipe_parallel_rank()
         ranks = mpu.get_pipe_parallel_ranks()
+        self.grid = _StageGrid(ranks)
         self.prev_rank = ranks[self.stage_id - 1] if self.stage_id > 0 else None
         self.next_rank = ranks[self.stage_id + 1] if self.stage_id < self.num_stages - 1 else None
         self.micro_batches = neox_args.gradient_accumulation_steps

@@ -257,7 +257,12 @@ class ParallelSelfAttention(nn.Module):
                 s4 = self.alibi_embed(s4)
             mask = attention_mask
             if mask is not None and (mask.shape[-2] != sq or mask.shape[-1] != sk):
-                mask = mask[..., sk - sq:sk, :sk]        # decoding with a KV cache: rows of the new positions
+                if mask.shape[-2] >= sk and mask.shape[-1] >= sk:
+                    mask = mask[..., sk - sq:sk, :sk]    # decoding with a KV cache: rows of the new positions
+                else:
+                    # a mask built for the new tokens only (pipeline stages build it from the step's input):
+                    # the causal / sliding-window mask over the cached keys is derived from positions below
+                    mask = None
             if mask is None:
                 qpos = torch.arange(sq, device=q.device)[:, None] + (sk - sq)
                 kpos = torch.arange(sk, device=q.device)[None, :]

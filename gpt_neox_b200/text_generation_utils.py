@@ -153,6 +153,18 @@ def stream_tokens(neox_args, model, context_tokens: List[List[int]], eos_token_i
     if any(k in ("mamba", "rwkv") for k in (neox_args.attention_config or [])):
         # the recurrent blocks keep no state between calls: every step runs the whole prefix
         recompute = True
+    if pipe and mpu.get_pipe_parallel_world_size() > 1:
+        # the pipeline engine derives positions and masks from the tokens it is given and fixes the shape of the
+        # activations between stages on first use: a one-token cached step does not fit, so the prefix is re-run
+        recompute = True
+    if recompute:
+        # whoever switched the layers to cached decoding (generate.py does, by default) must not make a
+        # recomputing loop append the whole prefix to the cache at every step
+        net = getattr(model, "module", model)
+        if hasattr(net, "inference_mode"):
+            net.inference_mode(use_cache=False)
+        if hasattr(net, "clear_cache"):
+            net.clear_cache()
     with torch.no_grad():
         done = torch.zeros(bsz, dtype=torch.bool, device=dev)
         end_index = torch.full((bsz,), -1, dtype=torch.long, device=dev)

@@ -146,3 +146,40 @@ def test_sinusoidal_table_rows_follow_position_ids():
     full = e(torch.arange(6)[None])                     # [1, 6, 8]
     one = e(torch.tensor([[4]]))                        # the row a cached decoding step asks for
     torch.testing.assert_close(one[0, 0], full[0, 4])
+
+
+def _generate(rank, world, cfg, recompute):
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.text_generation_utils import stream_tokens
+    torch.set_num_threads(1)
+    mpu.destroy_model_parallel()
+    a = NeoXArgs.from_dict(dict(cfg, global_num_gpus=world))
+    a.configure_distributed_args()
+    a.build_tokenizer()
+    initialize_megatron(a)
+    model, _, _, _ = training.setup_model_and_optimizer(neox_args=a, use_cache=True)
+    model.eval()
+    net = getattr(model, "module", model)
+    net.inference_mode(use_cache=not recompute)
+    net.clear_cache()
+    last = None
+    for last in stream_tokens(a, model, [[5, 9, 11, 3], [7, 2]], maximum_tokens=6, recompute=recompute,
+                              eos_token_id=10 ** 6):
+        pass
+    return last[0][:, :10].tolist()
+
+
+def test_greedy_generation_is_the_same_under_tensor_and_pipeline_parallelism():
+    """Same master weights (CPU initialisation) and the same padded vocabulary: one rank, two tensor-parallel ranks
+    and two pipeline stages (whose engine re-runs the prefix instead of using the KV cache) emit the same tokens."""
+    from common import run_distributed
+    base = dict(use_cpu_initialization=True, make_vocab_size_divisible_by=64, attention_config=[[["global"], 2]],
+                optimizer=None, no_load_optim=True)
+    one = run_distributed(_generate, 1, tiny_config(**base), False)[0]
+    tp2 = run_distributed(_generate, 2, tiny_config(model_parallel_size=2, **base), False)[0]
+    pp2 = run_distributed(_generate, 2, tiny_config(pipe_parallel_size=2, **base), False)[0]
+    assert one[0][:4] == [5, 9, 11, 3] and one[1][:2] == [7, 2]
+    assert tp2 == one and pp2 == one
