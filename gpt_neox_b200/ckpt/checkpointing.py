@@ -77,6 +77,16 @@ def check_forward_pass(neox_args, model, checkpoint_logits, inference):
                 "validate_checkpoint_forward() forward after load of checkpoint does not yield a close result"
 
 
+_PENDING_RNG = [None]      # random-stream state of the loaded checkpoint, until the training loop takes it
+
+
+def apply_pending_rng_state():
+    """Re-apply (once) the random-stream state of the checkpoint that was loaded last."""
+    rng, _PENDING_RNG[0] = _PENDING_RNG[0], None
+    if rng is not None:
+        restore_rng_state(rng)
+
+
 def restore_rng_state(rng):
     random.setstate(rng["random_rng_state"])
     np.random.set_state(rng["np_rng_state"])
@@ -240,7 +250,7 @@ def load_checkpoint(neox_args, model, optimizer, lr_scheduler, inference=False, 
             restore_rng_state(rng)
             # building the data iterators after this point draws from the global generators (DataLoader worker
             # seeds); the training loop re-applies the saved state right before its first step
-            neox_args.pending_rng_state = rng
+            _PENDING_RNG[0] = rng
         except KeyError:
             print_rank_0(f"Unable to load optimizer from checkpoint {checkpoint_name}. Specify --no-load-rng or "
                          "--finetune to prevent attempting to load the optimizer state, exiting ...")

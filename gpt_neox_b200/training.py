@@ -93,12 +93,10 @@ def pretrain(neox_args):
     if neox_args.save and neox_args.extra_save_iters and 0 in neox_args.extra_save_iters and iteration == 0:
         save_checkpoint(neox_args=neox_args, iteration=iteration, model=model, optimizer=optimizer,
                         lr_scheduler=lr_scheduler)
-    pending = getattr(neox_args, "pending_rng_state", None)
-    if pending is not None:
-        # a resumed run continues the random streams of the interrupted one from its first step on
-        from .ckpt.checkpointing import restore_rng_state
-        restore_rng_state(pending)
-        neox_args.pending_rng_state = None
+    # a resumed run continues the random streams of the interrupted one from its first step on (building the data
+    # iterators above drew from them)
+    from .ckpt.checkpointing import apply_pending_rng_state
+    apply_pending_rng_state()
     if neox_args.do_train and neox_args.train_iters > 0:
         iteration = train(neox_args=neox_args, timers=timers, model=model, reference_model=reference_model,
                           optimizer=optimizer, lr_scheduler=lr_scheduler, train_data_iterator=train_data_iterator,
