@@ -125,3 +125,64 @@ def test_raw_llama_unpermute_is_inverse_of_interleave():
            "layers.0.ffn_norm.weight": torch.ones(8)}
     hf = convert.raw_llama_to_hf_names([raw], cfg)
     torch.testing.assert_close(hf["model.layers.0.self_attn.q_proj.weight"], w_hf)
+
+
+_LLAMA = dict(norm="rmsnorm", activation="swiglu", use_bias_in_mlp=False, use_bias_in_attn_linear=False,
+              gpt_j_residual=False, rotary_pct=1.0, mlp_multiple_of=32, rms_norm_epsilon=1e-6, no_weight_tying=True)
+
+
+def _rank_logits(rank, world, cfg, tokens, train_iters):
+    """Train (``train_iters`` > 0, saving at the end) or load, then return the full-vocabulary logits of ``tokens``."""
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.utils.common import get_attn_mask
+    torch.set_num_threads(1)
+    mpu.destroy_model_parallel()
+    a = NeoXArgs.from_dict(dict(cfg, global_num_gpus=world, train_iters=max(train_iters, 1)))
+    a.configure_distributed_args()
+    a.build_tokenizer()
+    if train_iters > 0:
+        model = training.pretrain(a)
+    else:
+        initialize_megatron(a)
+        model, _, _, _ = training.setup_model_and_optimizer(neox_args=a, use_cache=False)
+    net = getattr(model, "module", model)
+    net.eval()
+    t = torch.tensor(tokens)
+    pos = torch.arange(t.shape[1])[None].expand(t.shape[0], -1)
+    with torch.no_grad():
+        out = net((t, pos, get_attn_mask(t.shape[1], "cpu", None))).float()
+        if world > 1:
+            out = mpu.gather_from_model_parallel_region(out)
+    return out.tolist()
+
+
+def test_tp2_checkpoint_files_round_trip_through_huggingface(tmp_path):
+    """Real files, tensor parallel 2, grouped-query attention: (a) train, save, merge + convert to a Hugging Face
+    Llama folder: same logits; (b) split that folder back into a TP-2 NeoX checkpoint, load it: same logits."""
+    import transformers
+    import yaml
+    from common import run_distributed
+    from gpt_neox_b200.ckpt import convert
+    tokens = torch.randint(0, 100, (2, 24), generator=torch.Generator().manual_seed(0)).tolist()
+    base = tiny_config(use_cpu_initialization=True, attention_config=[[["global"], 2]], make_vocab_size_divisible_by=64,
+                       model_parallel_size=2, num_kv_heads=2, **_LLAMA)
+    cfg = dict(base, save=str(tmp_path / "ck"), checkpoint_factor=2)
+    ours = torch.tensor(run_distributed(_rank_logits, 2, cfg, tokens, 2)[0])
+    with open(tmp_path / "cfg.yml", "w") as f:
+        yaml.safe_dump(cfg, f)
+    convert.convert_neox_to_hf(str(tmp_path / "ck" / "global_step2"), str(tmp_path / "cfg.yml"), str(tmp_path / "hf"),
+                               architecture="llama")
+    hf = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path / "hf"), attn_implementation="eager").eval().float()
+    with torch.no_grad():
+        theirs = hf(torch.tensor(tokens)).logits.float()
+    torch.testing.assert_close(ours[..., :theirs.shape[-1]], theirs, rtol=2e-4, atol=2e-4)
+    back = dict(base, load=str(tmp_path / "neox"), finetune=True, optimizer=None, no_load_optim=True)
+    with open(tmp_path / "back.yml", "w") as f:
+        yaml.safe_dump(back, f)
+    convert.convert_hf_to_neox(str(tmp_path / "hf"), str(tmp_path / "back.yml"), str(tmp_path / "neox"), tp=2,
+                               architecture="llama")
+    again = torch.tensor(run_distributed(_rank_logits, 2, back, tokens, 0)[0])
+    torch.testing.assert_close(again[..., :theirs.shape[-1]], theirs, rtol=2e-4, atol=2e-4)
