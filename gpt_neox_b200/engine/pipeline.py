@@ -203,9 +203,17 @@ class PipelineEngine(Engine):
         self._take_model_step()
         return self._aggregate_loss(losses)
 
+    def _forget_shapes(self):
+        """The shape of the activations between stages is announced once and then assumed; evaluation and
+        generation feed other batch shapes than training does (and change them from call to call), so the
+        announcement is repeated around every such call.  Both neighbours reset at the same points."""
+        self._recv_meta = None
+        self._sent_meta = False
+
     def eval_batch(self, data_iter, return_logits=False):
         was_training = self.module.training
         self.module.eval()
+        self._forget_shapes()
         losses, logits = [], []
         micro = 1 if return_logits else self.micro_batches
         with torch.no_grad():
@@ -215,6 +223,7 @@ class PipelineEngine(Engine):
                 self._exchange(send_next=None if self.is_last_stage() else out)
         if was_training:
             self.module.train()
+        self._forget_shapes()
         loss = self._aggregate_loss(losses)
         if return_logits:
             return loss, (torch.cat(logits, dim=0) if logits else None)

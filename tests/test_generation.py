@@ -183,3 +183,35 @@ def test_greedy_generation_is_the_same_under_tensor_and_pipeline_parallelism():
     pp2 = run_distributed(_generate, 2, tiny_config(pipe_parallel_size=2, **base), False)[0]
     assert one[0][:4] == [5, 9, 11, 3] and one[1][:2] == [7, 2]
     assert tp2 == one and pp2 == one
+
+
+def _loglikelihoods(rank, world, cfg, reqs):
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    from gpt_neox_b200.eval_tasks.eval_adapter import EvalHarnessAdapter
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.text_generation_utils import forward_model
+    torch.set_num_threads(1)
+    mpu.destroy_model_parallel()
+    a = NeoXArgs.from_dict(dict(cfg, global_num_gpus=world))
+    a.configure_distributed_args()
+    a.build_tokenizer()
+    initialize_megatron(a)
+    model, _, _, _ = training.setup_model_and_optimizer(neox_args=a, use_cache=False)
+    ad = EvalHarnessAdapter(model, forward_model, a, batch_size=2)
+    return [(round(float(l), 3), bool(g)) for l, g in ad.loglikelihood(reqs)]
+
+
+def test_eval_adapter_scores_are_layout_independent():
+    """Requests of different lengths (so the batches have different shapes, which the pipeline stages must
+    re-announce to each other): one rank, two pipeline stages and two tensor-parallel ranks give the same scores."""
+    from common import run_distributed
+    base = dict(use_cpu_initialization=True, make_vocab_size_divisible_by=64, attention_config=[[["global"], 2]],
+                optimizer=None, no_load_optim=True, tokenizer_type="CharLevelTokenizer", dataset_impl="gpt2")
+    reqs = [("hello wor", "ld"), ("", "abc"), ("some longer context here", " and a continuation"), ("x", "y")]
+    one = run_distributed(_loglikelihoods, 1, tiny_config(**base), reqs)[0]
+    pp2 = run_distributed(_loglikelihoods, 2, tiny_config(pipe_parallel_size=2, **base), reqs)[0]
+    tp2 = run_distributed(_loglikelihoods, 2, tiny_config(model_parallel_size=2, **base), reqs)[0]
+    assert len(one) == 4 and all(l < 0 for l, _ in one)
+    assert pp2 == one and tp2 == one
