@@ -311,7 +311,7 @@ class NeoXArgs:
         then ``--deepspeed_config`` and ``--megatron_config`` as base64 JSON."""
         args_list = []
         for n, (g, _t, d) in FIELDS.items():
-            if g != "launcher":
+            if g != "launcher" or n == "autotuning_run":       # the latter travels as --autotuning below
                 continue
             v = getattr(self, n)
             if v != d:

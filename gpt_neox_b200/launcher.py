@@ -221,8 +221,38 @@ def _node_rank_from_env():
     raise RuntimeError("cannot determine the node rank from the environment")
 
 
+def _job_size(args):
+    """Number of processes the job would start (for the autotuner's data-parallel degree)."""
+    pool = fetch_hostfile(args.hostfile)
+    if not pool:
+        if args.include or args.exclude:
+            active = parse_resource_filter({"localhost": _local_gpu_count()}, args.include, args.exclude)
+            return sum(len(d) for d in active.values())
+        return args.num_gpus if args.num_gpus > 0 else _local_gpu_count()
+    active = parse_resource_filter(pool, args.include, args.exclude)
+    if args.num_nodes > 0:
+        active = OrderedDict(list(active.items())[:args.num_nodes])
+    if args.num_gpus > 0:
+        active = OrderedDict((h, d[:args.num_gpus]) for h, d in active.items())
+    return sum(len(d) for d in active.values())
+
+
 def main(argv=None):
-    args = parse_args(sys.argv[1:] if argv is None else argv)
+    argv = list(sys.argv[1:] if argv is None else argv)
+    args = parse_args(argv)
+    if args.autotuning and not args.world_info:
+        # trial runs, then (mode "run") the job itself, each through this same entry without the flag
+        from . import autotuning
+        if args.autotuning not in ("tune", "run"):
+            raise ValueError("--autotuning takes 'tune' or 'run'")
+        head = argv[:len(argv) - len(args.user_args)]
+        i = head.index("--autotuning") if "--autotuning" in head else None
+        if i is not None:
+            del head[i:i + 2]
+        else:
+            head = [a for a in head if not a.startswith("--autotuning=")]
+        return autotuning.run_from_launcher(args.autotuning, list(args.user_args), _job_size(args),
+                                            lambda user_args: main(head + list(user_args)))
     if args.world_info:                                   # second level: we are on one host of the job
         hosts = OrderedDict()
         for item in args.world_info.split(","):

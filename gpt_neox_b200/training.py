@@ -605,6 +605,8 @@ def train(neox_args, timers, model, optimizer, lr_scheduler, train_data_iterator
         prof.start()
     from .obs import heartbeat as _hb
     hb = _hb.from_args(neox_args)
+    from .autotuning import ProfileWindow
+    window, first_iteration = ProfileWindow.from_args(neox_args), iteration
     while iteration < neox_args.train_iters:
         if hb is not None:
             hb.beat(iteration, "train_step")
@@ -620,6 +622,12 @@ def train(neox_args, timers, model, optimizer, lr_scheduler, train_data_iterator
             prof.stop()
         iteration += 1
         neox_args.iteration = iteration
+        if window is not None and window.after_step(iteration - first_iteration,
+                                                    dist.get_rank() if dist.is_initialized() else 0):
+            print_rank_0(f"autotuning: profile window closed after {iteration - first_iteration} steps, exiting")
+            if dist.is_initialized():
+                dist.barrier()
+            sys.exit(0)
         if iteration % max(1, neox_args.log_interval) == 0:
             if torch.cuda.is_available():
                 # a bounded wait inside a communication kernel that ran out surfaces here as an exception

@@ -13,7 +13,8 @@ from gpt_neox_b200.config import NeoXArgs
 CONF = os.path.join(ROOT, "configs")
 SETUP_ONLY = ("local_setup", "slurm_local", "text_generation", "cpu_mock_config", "prof.yml")
 OVERLAYS = ("sparse.yml", "llama/train_config.yml")                        # no model shape of its own: applied on top of a model config
-FILES = sorted(os.path.relpath(f, CONF) for f in glob.glob(os.path.join(CONF, "**", "*.yml"), recursive=True))
+FILES = sorted(os.path.relpath(f, CONF) for ext in ("*.yml", "autotuning_configs/*.json")
+               for f in glob.glob(os.path.join(CONF, "**", ext), recursive=True))
 MODELS = [f for f in FILES if not any(s in f for s in SETUP_ONLY)]
 
 
