@@ -24,6 +24,22 @@ def get_mode() -> str:
     return _MODE["mode"]
 
 
+_OBSERVER = None          # a comms logger (obs.profiling.CommsLogger) timing the NVLink collectives below
+
+
+def set_observer(obs):
+    global _OBSERVER
+    _OBSERVER = obs
+
+
+def _own(op, x, nbytes, group, call):
+    """Run one of this library's own collectives, timed when a comms logger is installed."""
+    if _OBSERVER is None:
+        return call()
+    with _OBSERVER.observe(op + "[nvlink]", nbytes, dist.get_world_size(group), cuda=x.is_cuda):
+        return call()
+
+
 def _log(kind, t):
     s = STATS[kind]
     s[0] += 1
@@ -42,7 +58,7 @@ def all_reduce(x: torch.Tensor, group=None, op=dist.ReduceOp.SUM) -> torch.Tenso
     _log("all_reduce", x)
     be = _fused_backend(x, group) if op == dist.ReduceOp.SUM else None
     if be is not None and be.supports(x):
-        return be.all_reduce(x)
+        return _own("all_reduce", x, x.numel() * x.element_size(), group, lambda: be.all_reduce(x))
     dist.all_reduce(x, op=op, group=group)
     return x
 
@@ -63,7 +79,7 @@ def all_gather_dim(x: torch.Tensor, dim: int, group=None) -> torch.Tensor:
     be = _fused_backend(x, group)
     if dim == 0:
         if be is not None and be.supports(x):
-            return be.all_gather0(x)
+            return _own("all_gather", x, ws * x.numel() * x.element_size(), group, lambda: be.all_gather0(x))
         out = torch.empty((ws * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(out, x, group=group)
         return out
@@ -80,7 +96,7 @@ def reduce_scatter_dim(x: torch.Tensor, dim: int, group=None) -> torch.Tensor:
     if dim == 0:
         x = x.contiguous()
         if be is not None and be.supports(x):
-            return be.reduce_scatter0(x)
+            return _own("reduce_scatter", x, x.numel() * x.element_size(), group, lambda: be.reduce_scatter0(x))
         out = torch.empty((x.shape[0] // ws,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         if x.is_cuda:
             dist.reduce_scatter_tensor(out, x, group=group)

@@ -14,6 +14,7 @@ all-gathered once.  No per-parameter launches, no host synchronisation in bf16 m
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from contextlib import contextmanager
 
@@ -351,6 +352,15 @@ class Engine(torch.nn.Module):
         self.timer_values = None
         self.curriculum_scheduler = None
         self.training_dataloader = None
+        # engine-side observability switches (all off by default)
+        from ..obs import profiling
+        self.breakdown = profiling.StepBreakdown(a.steps_per_print, dev) if a.wall_clock_breakdown else None
+        self.flops_profiler = profiling.FlopsProfiler.from_args(module, a)
+        self.comms_logger = profiling.CommsLogger.from_args(a)
+        if self.comms_logger is not None:
+            self.comms_logger.install()
+        if a.dump_state:
+            profiling.dump_state(self)
 
     # ------------------------------------------------------------------ reference-engine surface
     def train(self, mode=True):
@@ -364,7 +374,13 @@ class Engine(torch.nn.Module):
         sched = getattr(self, "curriculum_scheduler", None)
         if sched is not None and self.module.training and "curriculum_seqlen" not in kwargs:
             kwargs["curriculum_seqlen"] = sched.update_difficulty(self.global_steps + 1)
-        return self.module(*inputs, **kwargs)
+        if self.flops_profiler is not None and self.module.training:
+            self.flops_profiler.before_forward(self.global_steps + 1)
+        with self._span("forward"):
+            return self.module(*inputs, **kwargs)
+
+    def _span(self, phase):
+        return self.breakdown.span(phase) if self.breakdown is not None else contextlib.nullcontext()
 
     def is_gradient_accumulation_boundary(self):
         return (self.micro_steps + 1) % self.gradient_accumulation_steps == 0
@@ -381,7 +397,8 @@ class Engine(torch.nn.Module):
         scaled = loss / self.gradient_accumulation_steps
         if self.fp16_enabled:
             scaled = scaled * self.loss_scaler.cur_scale
-        scaled.backward(retain_graph=retain_graph)
+        with self._span("backward"):
+            scaled.backward(retain_graph=retain_graph)
         return loss
 
     def _sync_sequence_parallel_grads(self):
@@ -415,8 +432,9 @@ class Engine(torch.nn.Module):
         self._sync_sequence_parallel_grads()
         if self.store_gradients:
             self.stored_gradients = [p.main_grad.detach().clone() for g in self.groups for p in g.params]
-        for g in self.groups:
-            g.reduce_gradients()
+        with self._span("grad_reduce"):
+            for g in self.groups:
+                g.reduce_gradients()
         # global gradient norm: every element is owned (counted) by exactly one rank of the world
         self._acc.zero_()
         tp_rank0 = mpu.get_model_parallel_rank() == 0
@@ -440,10 +458,12 @@ class Engine(torch.nn.Module):
         if self.optimizer is not None:
             self.optimizer.overflow = overflow
             self.optimizer.cur_scale = self.loss_scaler.cur_scale
-            self.optimizer.step(self._scale, self._skip)
-        for g in self.groups:
-            g.gather_params()
-            g.zero_grad()
+            with self._span("optimizer"):
+                self.optimizer.step(self._scale, self._skip)
+        with self._span("param_gather"):
+            for g in self.groups:
+                g.gather_params()
+                g.zero_grad()
         for m in self._fp8_modules():
             m.fp8_meta.roll()               # delayed scaling: this step's amax feeds the next steps' scales
         if overflow:
@@ -451,6 +471,10 @@ class Engine(torch.nn.Module):
         elif self.lr_scheduler is not None:
             self.lr_scheduler.step()
         self.global_steps += 1
+        if self.flops_profiler is not None:
+            self.flops_profiler.after_step(self.global_steps)
+        if self.breakdown is not None:
+            self.breakdown.end_step(self)
 
     def _fp8_modules(self):
         return [m for m in self.module.modules() if getattr(m, "fp8_meta", None) is not None]

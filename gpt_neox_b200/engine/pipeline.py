@@ -112,6 +112,10 @@ class PipelineEngine(Engine):
 
     def _exchange(self, send_next=None, send_prev=None, recv_prev=False, recv_next=False):
         """One batched group of point-to-point operations; returns (from_prev, from_next)."""
+        with self._span("pipe_comm"):
+            return self._exchange_now(send_next, send_prev, recv_prev, recv_next)
+
+    def _exchange_now(self, send_next, send_prev, recv_prev, recv_next):
         ops, from_prev, from_next = [], None, None
         if send_next is not None and self.next_rank is not None:
             if not self._sent_meta:
@@ -146,11 +150,14 @@ class PipelineEngine(Engine):
         else:
             inp = recv.requires_grad_(torch.is_grad_enabled())
             x = self._wrap_input(inp)
-        out = self._unwrap_output(self.module.forward_stage(x))
+        if self.flops_profiler is not None and self.module.training:
+            self.flops_profiler.before_forward(self.global_steps + 1)
+        with self._span("forward"):
+            out = self._unwrap_output(self.module.forward_stage(x))
+            loss = self.module.loss_fn(out, labels) if self.is_last_stage() else None
         if self.is_last_stage():
             if keep_logits is not None:
                 keep_logits.append(out)
-            loss = self.module.loss_fn(out, labels)
             losses.append(loss.detach())
             out = loss / self.micro_batches
         else:
@@ -158,6 +165,10 @@ class PipelineEngine(Engine):
         return inp, out
 
     def _backward_micro(self, inp, out, out_grad):
+        with self._span("backward"):
+            return self._backward_now(inp, out, out_grad)
+
+    def _backward_now(self, inp, out, out_grad):
         if self.is_last_stage():
             scaled = out * self.loss_scaler.cur_scale if self.fp16_enabled else out
             scaled.backward()

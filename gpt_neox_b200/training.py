@@ -114,6 +114,10 @@ def pretrain(neox_args):
         evaluate_and_print_results(neox_args=neox_args, prefix=prefix, forward_step_func=forward_step,
                                    data_iterator=test_data_iterator, model=model, iteration=iteration, verbose=True,
                                    timers=timers, chart_name="test", reference_model=reference_model)
+    comms = getattr(model, "comms_logger", None)
+    if comms is not None:                       # comms_logger: the table of every collective of the run
+        comms.log_summary()
+        comms.uninstall()
     return model
 
 
