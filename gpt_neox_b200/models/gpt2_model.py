@@ -122,6 +122,14 @@ class GPT2ModelPipe(nn.Module):
         else:
             self.specs.append(LayerSpec(EmbeddingPipe, *emb_args))
         self.specs.append(_pre_transformer_block)
+        rpe_emb = None
+        if a.pos_emb == "rpe":
+            # T5 relative-position bias: ONE table per rank, shared by all of its attention layers
+            # (megatron/model/gpt2_model.py:227-240)
+            from ..parallel.layers import ParallelRelativePositionBias
+            rpe_emb = ParallelRelativePositionBias(
+                neox_args=a, scale=math.sqrt(a.hidden_size // a.num_attention_heads), causal=True,
+                num_buckets=a.rpe_num_buckets, max_distance=a.rpe_max_distance, heads=a.num_attention_heads)
         for i in range(a.num_layers):
             layer_type = a.attention_config[i]
             if layer_type in ("gmlp", "amlp"):
@@ -141,7 +149,7 @@ class GPT2ModelPipe(nn.Module):
                                             attention_mask_func=gpt2_attention_mask_func,
                                             init_method=self.init_method,
                                             output_layer_init_method=self.output_layer_init_method, layer_number=i,
-                                            rpe=None, rotary=a.pos_emb == "rotary", use_cache=self.use_cache))
+                                            rpe=rpe_emb, rotary=a.pos_emb == "rotary", use_cache=self.use_cache))
         self.specs.append(_post_transformer_block)
         norm, eps = get_norm(a)
         self.specs.append(LayerSpec(NormPipe, norm, a.hidden_size, eps=eps))

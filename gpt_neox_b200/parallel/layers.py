@@ -142,7 +142,8 @@ class ParallelRelativePositionBias(nn.Module):
 
     def compute_bias(self, q_len, k_len):
         dev = self.weight.device
-        q_pos = torch.arange(q_len, dtype=torch.long, device=dev)
+        # the queries are the LAST q_len positions of the keys (incremental decoding: one query at k_len - 1)
+        q_pos = torch.arange(k_len - q_len, k_len, dtype=torch.long, device=dev)
         k_pos = torch.arange(k_len, dtype=torch.long, device=dev)
         rel = k_pos[None, :] - q_pos[:, None]
         bucket = self._relative_position_bucket(rel, self.num_buckets, self.max_distance)

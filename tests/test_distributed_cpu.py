@@ -105,3 +105,15 @@ def test_moe_expert_parallel_2_matches_single_rank():
     out = run_distributed(_train, 2, dict(cfg, moe_expert_parallel_size=2), 3)
     assert out[0] == pytest.approx(out[1], rel=1e-6)
     assert out[0] == pytest.approx(ref, rel=1e-4)
+
+
+def test_t5_relative_position_bias_tp2_pp2_match_single_rank():
+    """``pos_emb: rpe``: one bucketed bias table per rank shared by its layers, heads sharded over tensor
+    parallel.  The shared table receives the gradients of every layer (the loss falls) and the TP-2 run
+    reproduces the TP-1 losses."""
+    cfg = tiny_config(use_cpu_initialization=True, pos_emb="rpe", rpe_num_buckets=8, rpe_max_distance=16,
+                      make_vocab_size_divisible_by=256, use_bias_in_attn_linear=False, use_bias_in_mlp=False)
+    ref = _single(cfg, 6)
+    assert ref[-1] < ref[0]
+    out = run_distributed(_train, 2, dict(cfg, model_parallel_size=2, make_vocab_size_divisible_by=128), 6)
+    assert out[0] == pytest.approx(ref, rel=5e-5)

@@ -43,7 +43,8 @@ def test_pad_batch_and_stop_tokens():
 
 
 @pytest.mark.parametrize("over", [dict(), dict(pos_emb="learned"), dict(gpt_j_residual=False, num_kv_heads=2),
-                                  dict(pos_emb="sinusoidal"), dict(pos_emb="alibi"), dict(sliding_window_width=4)])
+                                  dict(pos_emb="sinusoidal"), dict(pos_emb="alibi"), dict(sliding_window_width=4),
+                                  dict(pos_emb="rpe", rpe_num_buckets=8, rpe_max_distance=16)])
 def test_kv_cache_decoding_matches_recompute(over):
     from gpt_neox_b200.text_generation_utils import stream_tokens
     a, m = _model(**over)
