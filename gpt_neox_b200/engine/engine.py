@@ -136,8 +136,21 @@ class FlatGroup:
     def grad_shard(self):
         return self.main_grad[self.shard_start:self.shard_start + self.shard_size]
 
+    #: gradients are multiplied by 1 / predivide before the reduction (the engine folds the factor back into
+    #: its post-reduction scale); comm_dtype, when set, is the dtype the reduction runs in
+    predivide = 1.0
+    comm_dtype = None
+
     def reduce_gradients(self):
+        if self.predivide != 1.0:
+            self.main_grad.mul_(1.0 / self.predivide)
         if self.dp_size == 1:
+            return
+        if self.comm_dtype is not None and self.comm_dtype != self.main_grad.dtype:
+            # reduce in another precision (``communication_data_type``): one cast each way, plain collectives
+            buf = self.main_grad.to(self.comm_dtype)
+            dist.all_reduce(buf, group=self.dp_group)
+            self.main_grad.copy_(buf)
             return
         if self.zero_ws is not None:
             # reduce-scatter straight out of the peers' gradient buffers, result in place in this rank's shard
@@ -352,6 +365,17 @@ class Engine(torch.nn.Module):
         self.timer_values = None
         self.curriculum_scheduler = None
         self.training_dataloader = None
+        # prescale_gradients: the data-parallel average is taken before the reduction instead of after it;
+        # gradient_predivide_factor f: divide by f before and by dp / f after (fp16 / bf16 reductions of many
+        # ranks stay in range).  communication_data_type: dtype of the gradient reduction.
+        f = float(a.gradient_predivide_factor or 1.0)
+        if a.prescale_gradients and f == 1.0:
+            f = float(max([g.dp_size for g in self.groups] or [1]))
+        self._predivide = f if any(g.dp_size > 1 for g in self.groups) else 1.0
+        comm = {None: None, "fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16,
+                "bfp16": torch.bfloat16}[a.communication_data_type]
+        for g in self.groups:
+            g.predivide, g.comm_dtype = self._predivide, comm
         # engine-side observability switches (all off by default)
         from ..obs import profiling
         self.breakdown = profiling.StepBreakdown(a.steps_per_print, dev) if a.wall_clock_breakdown else None
@@ -448,6 +472,7 @@ class Engine(torch.nn.Module):
             dist.all_reduce(self._acc[0:1])
             dist.all_reduce(self._acc[1:2], op=dist.ReduceOp.MAX)
         dp_avg = 1.0 / max(g.dp_size for g in self.groups) if self.groups else 1.0
+        dp_avg *= self._predivide                      # undo what reduce_gradients divided by beforehand
         inv_scale = dp_avg / (self.loss_scaler.cur_scale if self.fp16_enabled else 1.0)
         optim_ops.clip_coef_(self._acc, self.gradient_clipping, inv_scale, self._scale, self._skip)
         self._last_grad_norm = self._scale[1]

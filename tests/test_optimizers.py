@@ -68,3 +68,39 @@ def test_engine_runs_with_in_tree_optimizers(name, params):
     cfg = tiny_config(use_cpu_initialization=True, optimizer={"type": name, "params": params})
     losses = run_distributed(_train, 1, cfg, 4)[0]
     assert all(l == l for l in losses)
+
+
+def _losses_with(rank, world, cfg, steps):
+    import torch
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    torch.set_num_threads(1)
+    mpu.destroy_model_parallel()
+    a = NeoXArgs.from_dict(dict(cfg, global_num_gpus=world, train_iters=steps, lr_decay_iters=steps))
+    a.configure_distributed_args()
+    a.build_tokenizer()
+    losses = []
+    training.collect_loss_for_unit_test = lambda l: losses.append(float(l))
+    model = training.pretrain(a)
+    return losses, float(model.get_global_grad_norm())
+
+
+def test_gradient_predivide_and_prescale_leave_the_step_unchanged():
+    """``gradient_predivide_factor`` / ``prescale_gradients`` move the data-parallel average in front of the
+    reduction and ``communication_data_type`` picks its dtype: in fp32 the losses and the reported gradient
+    norm stay those of the default engine."""
+    import pytest
+    from common import run_distributed, tiny_config
+    cfg = tiny_config(use_cpu_initialization=True)
+    ref = run_distributed(_losses_with, 2, cfg, 4)[0]
+    for over in (dict(gradient_predivide_factor=2.0), dict(prescale_gradients=True),
+                 dict(gradient_predivide_factor=4.0, communication_data_type="fp32"),
+                 dict(zero_optimization={"stage": 0}, prescale_gradients=True)):
+        got = run_distributed(_losses_with, 2, dict(cfg, **over), 4)[0]
+        if "zero_optimization" in over:
+            base = run_distributed(_losses_with, 2, dict(cfg, zero_optimization={"stage": 0}), 4)[0]
+        else:
+            base = ref
+        assert got[0] == pytest.approx(base[0], rel=1e-5), over
+        assert got[1] == pytest.approx(base[1], rel=1e-4), over
