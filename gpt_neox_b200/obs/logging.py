@@ -109,11 +109,47 @@ def get_flops(neox_args, iter_time_s, use_checkpointing_factor=True) -> float:
     return flops / (iter_time_s * world_size)
 
 
+class CsvMonitor:
+    """``csv_monitor: {enabled, output_path, job_name}``: one ``<key>.csv`` of ``step,value`` rows per scalar
+    under ``output_path/job_name`` (what the reference gets from the DeepSpeed monitor,
+    megatron/neox_arguments/deepspeed_args.py csv_monitor)."""
+
+    def __init__(self, output_path="", job_name="gpt-neox-b200"):
+        self.dir = os.path.join(output_path or "csv_monitor", job_name or "gpt-neox-b200")
+        os.makedirs(self.dir, exist_ok=True)
+        self.seen = set()
+
+    def write(self, key, value, step):
+        name = key.replace("/", "_").replace(" ", "_")
+        path = os.path.join(self.dir, name + ".csv")
+        new = name not in self.seen and not os.path.exists(path)
+        self.seen.add(name)
+        with open(path, "a") as f:
+            if new:
+                f.write(f"step,{name}\n")
+            f.write(f"{int(step)},{float(value)}\n")
+
+
+_CSV = {"monitor": None}
+
+
+def configure_csv_monitor(neox_args):
+    cfg = getattr(neox_args, "csv_monitor", None) or {}
+    _CSV["monitor"] = CsvMonitor(cfg.get("output_path", ""), cfg.get("job_name", "")) \
+        if cfg.get("enabled") and get_rank() == 0 else None
+    return _CSV["monitor"]
+
+
 def tb_wandb_log(key, value, iteration_no, use_wandb, tensorboard_writer=None, comet_experiment=None,
                  all_ranks=False):
     """Write one scalar to every configured sink (rank 0 unless ``all_ranks``)."""
     do_log = get_rank() == 0 or all_ranks
     if do_log and value is not None:
+        if _CSV["monitor"] is not None and get_rank() == 0:
+            try:
+                _CSV["monitor"].write(key, value, iteration_no)
+            except (TypeError, ValueError):
+                pass                                   # not a scalar
         if tensorboard_writer:
             tensorboard_writer.add_scalar(key, value, iteration_no)
         if use_wandb:

@@ -97,6 +97,8 @@ def pretrain(neox_args):
     # iterators above drew from them)
     from .ckpt.checkpointing import apply_pending_rng_state
     apply_pending_rng_state()
+    from .obs.logging import configure_csv_monitor
+    configure_csv_monitor(neox_args)
     if neox_args.do_train and neox_args.train_iters > 0:
         iteration = train(neox_args=neox_args, timers=timers, model=model, reference_model=reference_model,
                           optimizer=optimizer, lr_scheduler=lr_scheduler, train_data_iterator=train_data_iterator,

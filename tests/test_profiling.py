@@ -88,3 +88,18 @@ def test_comms_logger_prof_ops_filter_and_bus_factor():
         pass
     assert list(c.records) == ["all_reduce"] and c.records["all_reduce"][1024][0] == 1
     assert "1.00 KB" in c.summary()
+
+
+def _train_csv(rank, world, cfg):
+    _train(rank, world, cfg, 4)
+    return True
+
+
+def test_csv_monitor_writes_one_file_per_scalar(tmp_path):
+    cfg = tiny_config(use_cpu_initialization=True, log_interval=1,
+                      csv_monitor={"enabled": True, "output_path": str(tmp_path), "job_name": "job"})
+    run_distributed(_train_csv, 1, cfg)
+    rows = (tmp_path / "job" / "train_lm_loss.csv").read_text().strip().splitlines()
+    assert rows[0] == "step,train_lm_loss" and len(rows) == 5
+    assert [int(r.split(",")[0]) for r in rows[1:]] == [1, 2, 3, 4]
+    assert (tmp_path / "job" / "train_learning_rate.csv").exists()
