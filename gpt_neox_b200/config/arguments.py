@@ -420,6 +420,14 @@ class NeoXArgs:
                 import comet_ml
                 self.comet_experiment = comet_ml.Experiment(workspace=self.comet_workspace,
                                                             project_name=self.comet_project)
+                self.comet_experiment.__internal_api__log_parameters__(
+                    self.non_default_values(), framework="gpt-neox", source="manual", flatten_nested=True)
+                if self.comet_experiment_name:
+                    self.comet_experiment.set_name(self.comet_experiment_name)
+                if self.comet_tags:
+                    self.comet_experiment.add_tags(self.comet_tags)
+                if self.comet_others:
+                    self.comet_experiment.log_others(self.comet_others)
             except Exception as e:
                 print(f"WARNING: Comet logging requested but unavailable ({e})", flush=True)
 

@@ -213,3 +213,38 @@ def test_sequence_length_curriculum_reaches_the_model():
     assert r["seen"][0] is not None and r["seen"][0] < 32
     assert r["seen"] == sorted(r["seen"]) and r["seen"][-1] == 32
     assert len(r["losses"]) == 6 and all(l == l for l in r["losses"])
+
+
+def test_comet_experiment_gets_name_tags_and_parameters(monkeypatch):
+    """``use_comet``: the experiment is created on rank 0 and receives the run's name, tags, extra fields and
+    the non-default arguments (megatron/neox_arguments/arguments.py:190-212), here against a fake module."""
+    import sys
+    import types
+    from common import tiny_config
+    from gpt_neox_b200.config import NeoXArgs
+    calls = {}
+
+    class Experiment:
+        def __init__(self, **kw):
+            calls["init"] = kw
+
+        def set_name(self, n):
+            calls["name"] = n
+
+        def add_tags(self, t):
+            calls["tags"] = t
+
+        def log_others(self, o):
+            calls["others"] = o
+
+        def __internal_api__log_parameters__(self, params, **kw):
+            calls["params"] = params
+
+    monkeypatch.setitem(sys.modules, "comet_ml", types.SimpleNamespace(Experiment=Experiment))
+    a = NeoXArgs.from_dict(tiny_config(use_comet=True, comet_workspace="ws", comet_project="proj",
+                                       comet_experiment_name="run-7", comet_tags=["a", "b"], comet_others={"k": 1}))
+    a.rank = 0
+    a.initialize_comet()
+    assert calls["init"] == dict(workspace="ws", project_name="proj")
+    assert calls["name"] == "run-7" and calls["tags"] == ["a", "b"] and calls["others"] == {"k": 1}
+    assert calls["params"]["hidden_size"] == 64
