@@ -507,6 +507,16 @@ class NeoXArgs:
             raise AssertionError(f"(global_num_gpus / pp_size) / mp_size [({self.global_num_gpus} / {pp_size}) / "
                                  f"{mp_size}] must be a whole number")
         dp_world_size = int(dp_world_size)
+        if self.elasticity and self.elasticity.get("enabled"):
+            # one global batch for every allowed GPU count; micro-batch and accumulation follow from this one
+            from ..elasticity import compute_elastic_config
+            given = [k for k in ("train_batch_size", "train_micro_batch_size_per_gpu") if getattr(self, k) is not None]
+            if given and not self.elasticity.get("ignore_non_elastic_batch_info", False):
+                raise AssertionError(f"elasticity is enabled: remove {given} or set ignore_non_elastic_batch_info")
+            block = dict(self.elasticity, model_parallel_size=1)
+            tb_e, _valid, mb_e = compute_elastic_config(block, dp_world_size)
+            self.update_values({"train_batch_size": tb_e, "train_micro_batch_size_per_gpu": mb_e,
+                                "gradient_accumulation_steps": tb_e // (mb_e * dp_world_size)})
         tb, mb, ga = self.calculate_batch_parameters(dp_world_size, self.train_batch_size,
                                                      self.train_micro_batch_size_per_gpu,
                                                      self.gradient_accumulation_steps)

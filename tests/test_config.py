@@ -73,3 +73,32 @@ def test_no_field_is_declared_twice():
         for name, _t, _d in rows:
             assert name not in seen, f"{name} in {group} and {seen[name]}"
             seen[name] = group
+
+
+def test_elasticity_keeps_one_global_batch_over_gpu_counts():
+    import pytest
+    from common import tiny_config
+    from gpt_neox_b200.elasticity import ElasticityError, compute_elastic_config, valid_gpu_counts
+    block = {"enabled": True, "max_train_batch_size": 2000, "micro_batch_sizes": [2, 4, 6], "min_gpus": 1,
+             "max_gpus": 64, "prefer_larger_batch": True}
+    batch, valid, _ = compute_elastic_config(block)
+    assert batch <= 2000 and valid == valid_gpu_counts(batch, [2, 4, 6], 1, 64)
+    assert len(valid) >= 20 and {1, 2, 4, 8, 24}.issubset(valid)
+    for g in valid:                                                   # every valid size really forms the batch
+        assert any(batch % (m * g) == 0 for m in (2, 4, 6))
+    seen = set()
+    for world in (8, 12, 24):
+        cfg = tiny_config(elasticity=block, global_num_gpus=world)
+        for k in ("train_micro_batch_size_per_gpu", "gradient_accumulation_steps"):
+            cfg.pop(k)
+        a = NeoXArgs.from_dict(cfg)
+        assert a.train_batch_size == batch
+        assert a.train_micro_batch_size_per_gpu * a.gradient_accumulation_steps * world == batch
+        seen.add(a.train_micro_batch_size_per_gpu)
+    assert seen <= {2, 4, 6}
+    with pytest.raises(ElasticityError):
+        compute_elastic_config(block, 7 * 11)                         # 77 ranks cannot divide the batch
+    with pytest.raises(AssertionError):
+        NeoXArgs.from_dict(tiny_config(elasticity=block, global_num_gpus=8))   # explicit batch keys conflict
+    small, v2, _ = compute_elastic_config(dict(block, prefer_larger_batch=False))
+    assert len(v2) == len(valid) and small <= batch
