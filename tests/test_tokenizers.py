@@ -90,3 +90,47 @@ def test_sentencepiece_round_trip(tmp_path):
 def test_unknown_type_is_rejected():
     with pytest.raises(NotImplementedError):
         T.build_tokenizer(_args(tokenizer_type="NoSuchTokenizer", vocab_file="x"))
+
+
+def test_train_bpe_tokenizer_and_load_it(tmp_path):
+    """Train on a small jsonl corpus (one file gzipped), load the result through HFTokenizer and round-trip text
+    (reference: megatron/tokenizer/train_tokenizer.py)."""
+    import gzip
+    import json
+    from types import SimpleNamespace
+    from gpt_neox_b200.tokenizer import build_tokenizer
+    from gpt_neox_b200.tokenizer.train_tokenizer import iter_documents, main, parse_args
+    docs = [f"the quick brown fox number {i} jumps over the lazy dog" for i in range(200)]
+    with open(tmp_path / "a.jsonl", "w") as f:
+        for d in docs[:100]:
+            f.write(json.dumps({"text": d}) + "\n")
+    with gzip.open(tmp_path / "b.jsonl.gz", "wt") as f:
+        for d in docs[100:]:
+            f.write(json.dumps({"text": d, "meta": 1}) + "\n")
+        f.write("\n" + json.dumps({"other": "no text"}) + "\n")
+    assert sum(1 for _ in iter_documents(str(tmp_path))) == 200
+    out = tmp_path / "tok" / "tokenizer.json"
+    main(parse_args(["--json_input_dir", str(tmp_path), "--tokenizer_output_path", str(out), "-v", "400"]))
+    args = SimpleNamespace(tokenizer_type="HFTokenizer", vocab_file=str(out), rank=0, make_vocab_size_divisible_by=128,
+                           model_parallel_size=1)
+    tok = build_tokenizer(args)
+    assert 256 < tok.vocab_size <= 400
+    ids = tok.tokenize("the quick brown fox")
+    assert len(ids) < len("the quick brown fox") // 2 and tok.detokenize(ids).strip() == "the quick brown fox"
+    assert tok.eod == tok.vocab["<|endoftext|>"] and tok.pad == tok.vocab["<|padding|>"]
+
+
+def test_devutil_times_a_method():
+    import torch
+    from gpt_neox_b200.utils.devutil import Metric, monitor_method_wall_times
+    m = Metric("linear forward")
+    lin = torch.nn.Linear(8, 8)
+    undo = monitor_method_wall_times(m, lin, "forward")
+    for _ in range(5):
+        lin(torch.randn(2, 8))
+    undo()
+    lin(torch.randn(2, 8))
+    assert len(m.get_measurements()) == 5 and all(v >= 0 for v in m.measurements) and m.deciles().numel() == 10
+    lines = []
+    m.report(lines.append)
+    assert "linear forward: n=5" in lines[0]
