@@ -100,6 +100,14 @@ def ensure_directory_exists(filename):
     os.makedirs(os.path.dirname(filename), exist_ok=True)
 
 
+def get_checkpoint_name(checkpoints_path, iteration, release=False, mp_rank=None):
+    """Path of the single-file (Megatron-style) checkpoint of one tensor-parallel rank
+    (megatron/checkpointing.py:138-151); the engine's own checkpoints are tag directories, see below."""
+    sub = "release" if release else f"iter_{int(iteration):07d}"
+    rank = mpu.get_model_parallel_rank() if mp_rank is None else mp_rank
+    return os.path.join(checkpoints_path, sub, f"mp_rank_{rank:02d}", "model_optim_rng.pt")
+
+
 def get_checkpoint_tag(iteration: int) -> str:
     return f"global_step{iteration}"
 

@@ -13,6 +13,16 @@ from .norms import LayerNorm, NonParametricLayernorm, RMSNorm, ScaleNorm
 _NORM_TYPES = (LayerNorm, RMSNorm, ScaleNorm, NonParametricLayernorm, nn.LayerNorm)
 
 
+def get_fusion_type(neox_args):
+    """The softmax fusion the configuration asks for (megatron/model/utils.py:364-370)."""
+    from .fused_softmax import SoftmaxFusionTypes
+    if neox_args.scaled_upper_triang_masked_softmax_fusion:
+        return SoftmaxFusionTypes.upper_triang
+    if neox_args.scaled_masked_softmax_fusion:
+        return SoftmaxFusionTypes.general
+    return SoftmaxFusionTypes.none
+
+
 def get_params_for_weight_decay_optimization(module, neox_args):
     """Two groups: decayed, and not decayed (every parameter of a norm module, every ``bias``, every
     parameter flagged ``_no_weight_decay``). With ``weight_decay == 0`` a single group."""

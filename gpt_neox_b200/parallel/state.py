@@ -205,6 +205,15 @@ def get_model_parallel_ranks():
     return list(_S.model_ranks) if _S.model_ranks else [0]
 
 
+# the same group under the names newer callers use (megatron/mpu/initialize.py:190-260)
+get_tensor_model_parallel_group = get_model_parallel_group
+get_tensor_model_parallel_world_size = get_model_parallel_world_size
+get_tensor_model_parallel_rank = get_model_parallel_rank
+get_tensor_model_parallel_src_rank = get_model_parallel_src_rank
+set_tensor_model_parallel_world_size = set_model_parallel_world_size
+set_tensor_model_parallel_rank = set_model_parallel_rank
+
+
 def get_data_parallel_world_size() -> int:
     return _S.dp_size
 

@@ -32,6 +32,56 @@ def get_rank():
     return dist.get_rank() if dist.is_initialized() else 0
 
 
+def is_bnb_available() -> bool:
+    """True if the bitsandbytes package can be imported."""
+    import importlib.util
+    return importlib.util.find_spec("bitsandbytes") is not None
+
+
+def get_total_params(model) -> int:
+    """Parameters of the whole model: each model-parallel shard counted once (data-parallel rank 0 of every
+    shard contributes), summed over all ranks (megatron/utils.py:403-419)."""
+    from .. import parallel as mpu
+    params = 0
+    if mpu.get_data_parallel_rank() == 0:
+        params = sum(p.nelement() for p in model.parameters())
+        print(f" > number of parameters on model parallel rank {mpu.get_model_parallel_rank()}: {params}", flush=True)
+    if torch.distributed.is_initialized():
+        dev = next(model.parameters()).device
+        t = torch.tensor([params], dtype=torch.int64, device=dev)
+        torch.distributed.all_reduce(t)
+        params = int(t.item())
+    return params
+
+
+def make_viewless_tensor(inp, requires_grad=None, keep_graph=True):
+    """A tensor that shares ``inp``'s data but is not a view of another tensor (``._base is None``), so that
+    its storage can be released or replaced independently (megatron/utils.py make_viewless_tensor).  With
+    ``keep_graph`` the result stays connected to the autograd graph."""
+    if inp._base is None:
+        return inp
+    if keep_graph:
+        return _MakeViewless.apply(inp, inp.requires_grad if requires_grad is None else requires_grad)
+    out = torch.empty((1,), dtype=inp.dtype, device=inp.device, requires_grad=bool(requires_grad))
+    out.data = inp.data
+    return out
+
+
+class _MakeViewless(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, inp, requires_grad):
+        out = torch.empty((1,), dtype=inp.dtype, device=inp.device)
+        out.data = inp.data
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad, None
+
+
+MakeViewlessTensor = _MakeViewless
+
+
 def print_rank_0(*message):
     if get_rank() == 0:
         print(*message, flush=True)

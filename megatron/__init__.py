@@ -44,10 +44,14 @@ class _AliasLoader(importlib.abc.Loader):
         self.target = target
 
     def create_module(self, spec):
-        return importlib.import_module(self.target)
+        real = importlib.import_module(self.target)
+        self.real_spec = real.__spec__
+        return real
 
     def exec_module(self, module):
-        pass
+        # the import machinery has just stamped the alias spec onto the real module: put its own spec back, so
+        # that relative imports inside it keep resolving against its real package
+        module.__spec__ = self.real_spec
 
 
 class _AliasFinder(importlib.abc.MetaPathFinder):

@@ -92,3 +92,33 @@ def test_tee_duplicates_writes(tmp_path, capsys):
         t.close() if hasattr(t, "close") else t.__del__()
     assert "hello tee" in path.read_text()
     assert "hello tee" in capsys.readouterr().out
+
+
+def test_reference_helper_names_resolve_and_behave():
+    import torch
+    from megatron import mpu
+    from megatron.checkpointing import get_checkpoint_name
+    from megatron.model.fused_softmax import SoftmaxFusionTypes
+    from megatron.model.utils import get_fusion_type
+    from megatron.utils import get_total_params, is_bnb_available, make_viewless_tensor
+    from types import SimpleNamespace as NS
+    assert mpu.get_tensor_model_parallel_world_size() == mpu.get_model_parallel_world_size()
+    assert mpu.get_tensor_model_parallel_rank() == mpu.get_model_parallel_rank()
+    assert get_checkpoint_name("/ck", 12, mp_rank=3) == "/ck/iter_0000012/mp_rank_03/model_optim_rng.pt"
+    assert get_checkpoint_name("/ck", 0, release=True, mp_rank=0).startswith("/ck/release/")
+    assert get_fusion_type(NS(scaled_upper_triang_masked_softmax_fusion=True, scaled_masked_softmax_fusion=True)) \
+        == SoftmaxFusionTypes.upper_triang
+    assert get_fusion_type(NS(scaled_upper_triang_masked_softmax_fusion=False, scaled_masked_softmax_fusion=True)) \
+        == SoftmaxFusionTypes.general
+    assert get_fusion_type(NS(scaled_upper_triang_masked_softmax_fusion=False, scaled_masked_softmax_fusion=False)) \
+        == SoftmaxFusionTypes.none
+    assert isinstance(is_bnb_available(), bool)
+    assert get_total_params(torch.nn.Linear(4, 3)) == 15
+    base = torch.randn(4, 6, requires_grad=True)
+    view = base.view(2, 12)
+    out = make_viewless_tensor(view)
+    assert view._base is not None and out._base is None and out.data_ptr() == view.data_ptr()
+    out.sum().backward()
+    assert torch.equal(base.grad, torch.ones_like(base))
+    assert make_viewless_tensor(base) is base
+    assert make_viewless_tensor(view.detach(), requires_grad=False, keep_graph=False)._base is None
