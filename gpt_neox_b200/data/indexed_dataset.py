@@ -470,3 +470,17 @@ class MMapIndexedDatasetBuilder(_StreamWriter):
     def finalize(self, index_file: str):
         self._bin.close()
         MMapIndex.store(index_file, self._dtype, self._sizes, self._doc_idx)
+
+
+def read_longs(f, n: int):
+    """``n`` little-endian int64 values from the binary file object ``f``."""
+    a = np.empty(int(n), dtype=np.int64)
+    got = f.readinto(a)
+    if got != a.nbytes:
+        raise EOFError(f"wanted {a.nbytes} bytes, file had {got}")
+    return a
+
+
+def write_longs(f, a):
+    """Write the sequence ``a`` to ``f`` as int64."""
+    f.write(np.asarray(a, dtype=np.int64).tobytes())

@@ -29,3 +29,13 @@ def fused_apply_rotary_pos_emb_cached(t: torch.Tensor, cos_: torch.Tensor, sin_:
 def fused_apply_rotary_pos_emb(t: torch.Tensor, freqs: torch.Tensor, transpose_output_memory: bool = False) -> torch.Tensor:
     f = freqs.float()
     return fused_apply_rotary_pos_emb_cached(t, torch.cos(f), torch.sin(f), transpose_output_memory)
+
+
+class FusedRoPEFunc:
+    """``FusedRoPEFunc.apply(t, freqs, transpose_output_memory)`` (differentiable)."""
+    apply = staticmethod(fused_apply_rotary_pos_emb)
+
+
+class FusedRoPECachedFunc:
+    """``FusedRoPECachedFunc.apply(t, cos_, sin_, transpose_output_memory)`` (differentiable)."""
+    apply = staticmethod(fused_apply_rotary_pos_emb_cached)

@@ -96,3 +96,27 @@ def get_init_methods(args):
             fn = _scaled(fn, args.mup_init_scale)
         return fn
     return _get(args.init_method), _get(args.output_layer_init_method)
+
+
+# ------------------------------------------------------------------ the reference's factory names
+def _named(factory):
+    """``factory(..., use_mup_outer=False, mup_init_scale=1.0)`` -> ``init_(tensor, use_mup=use_mup_outer)``:
+    the calling convention of megatron/model/init_functions.py:25-185."""
+    def make(*args, use_mup_outer=False, mup_init_scale=1.0, **kwargs):
+        plain = factory(*args, **kwargs)
+        scaled = _scaled(plain, mup_init_scale)
+
+        def init_(tensor, use_mup=use_mup_outer):
+            return scaled(tensor) if use_mup else plain(tensor)
+        return init_
+    return make
+
+
+init_method_normal = _named(normal)
+scaled_init_method_normal = _named(lambda sigma, num_layers, num_residuals_per_layer=2:
+                                   scaled_normal(sigma, num_layers, num_residuals_per_layer))
+orthogonal_init_method = _named(orthogonal)
+xavier_uniform_init_method = _named(xavier_uniform)
+xavier_normal_init_method = _named(xavier_normal)
+small_init_init_method = _named(small_init)
+wang_init_method = _named(wang_init)

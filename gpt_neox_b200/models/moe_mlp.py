@@ -161,3 +161,10 @@ class ParallelGroupedLLaMAMLP(nn.Module):
         up = grouped_linear(x, v(self.w3), sizes, trans_b=True)
         h = torch.nn.functional.silu(gate) * up
         return grouped_linear(h, v(self.w2), sizes, trans_b=False)
+
+
+# The reference's "memory optimized" variants recompute the activation in backward to save one
+# [tokens, ffn] tensor; the grouped kernels here always keep only the pre-activation (as its derivative),
+# so the plain classes already have that footprint.
+MemoryOptimizedParallelGroupedMLP = ParallelGroupedMLP
+MemoryOptimizedParallelGroupedLLaMAMLP = ParallelGroupedLLaMAMLP

@@ -84,3 +84,22 @@ class AliBi(nn.Module):
     def forward(self, x):
         sq, sk = x.shape[-2], x.shape[-1]
         return x + self.bias(sq, sk, x.device, x.dtype)[None]
+
+
+# ------------------------------------------------------------------ functional rotary helpers
+def rotate_half(x):
+    """``[x1 | x2] -> [-x2 | x1]`` on the last dimension."""
+    h = x.shape[-1] // 2
+    return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
+
+
+def apply_rotary_pos_emb_torch(q, k, cos, sin, offset: int = 0):
+    """Rotate ``q`` and ``k`` (``[s, b, heads, d]``) with tables ``[>= offset + s, 1, 1, d]`` whose two halves
+    are equal (megatron/model/positional_embeddings.py apply_rotary_pos_emb*).  Plain PyTorch in the
+    tables' precision; the model itself uses the kernel in `ops.rope`."""
+    s = q.shape[0]
+    c, sn = cos[offset:offset + s], sin[offset:offset + s]
+    return (q * c) + (rotate_half(q) * sn), (k * c) + (rotate_half(k) * sn)
+
+
+apply_rotary_pos_emb = apply_rotary_pos_emb_torch

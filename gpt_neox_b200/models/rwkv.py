@@ -180,3 +180,11 @@ class RWKVResidualLayerPipe(RWKVResidualLayer):
         assert len(args) == 2
         hidden_states, mask = args
         return super().forward(hidden_states), mask
+
+
+def RUN_CUDA_RWKV(B, T, C, H, r, k, v, w, u):
+    """The WKV-6 recurrence under the reference's entry point (megatron/model/rwkv/v6/rwkv.py:95): ``r k v w``
+    are ``[B, T, C]``, ``u`` is ``[H, C // H]``; any ``T`` (no compile-time sequence length)."""
+    from ..ops.wkv import wkv6
+    assert r.shape == (B, T, C) and u.shape[0] == H
+    return wkv6(r, k, v, w, u)

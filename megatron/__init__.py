@@ -11,6 +11,11 @@ import importlib.util
 import sys
 
 _PREFIXES = [
+    ("megatron.model.rwkv.v6.rwkv", "gpt_neox_b200.models.rwkv"),
+    ("megatron.model.rwkv.v6", "gpt_neox_b200.models.rwkv"),
+    ("megatron.model.mamba.mamba", "gpt_neox_b200.models.mamba"),
+    ("megatron.mup_substitute", "gpt_neox_b200.mup"),
+    ("megatron.devutil", "gpt_neox_b200.utils.devutil"),
     ("megatron.neox_arguments.arguments", "gpt_neox_b200.config.arguments"),
     ("megatron.neox_arguments", "gpt_neox_b200.config"),
     ("megatron.mpu", "gpt_neox_b200.parallel"),
@@ -28,6 +33,9 @@ _PREFIXES = [
     ("megatron.gradient_noise_scale", "gpt_neox_b200.gradient_noise_scale"),
     ("megatron.fused_kernels", "gpt_neox_b200.ops.softmax"),
 ]
+
+
+_NESTED = ("gpt_neox_b200.models.rwkv", "gpt_neox_b200.models.mamba")
 
 
 def _target(name):
@@ -52,6 +60,8 @@ class _AliasLoader(importlib.abc.Loader):
         # the import machinery has just stamped the alias spec onto the real module: put its own spec back, so
         # that relative imports inside it keep resolving against its real package
         module.__spec__ = self.real_spec
+        if self.target in _NESTED and not hasattr(module, "__path__"):
+            module.__path__ = []          # a plain module here, a package in the reference: let submodule aliases resolve
 
 
 class _AliasFinder(importlib.abc.MetaPathFinder):

@@ -105,3 +105,56 @@ def test_transformer_engine_names_build_on_the_fp8_path():
     a.te_fp8_format = "e5m2"
     with pytest.raises(ValueError):
         TEDelayedScaling(a)
+
+
+def test_named_factories_and_functional_helpers():
+    import io
+    import numpy as np
+    from megatron.data.indexed_dataset import read_longs, write_longs
+    from megatron.model.activations import Gated_Activation, GeLUFunction, bias_gelu, bias_gelu_back, erf_gelu
+    from megatron.model.fused_rope import FusedRoPECachedFunc
+    from megatron.model.init_functions import (init_method_normal, scaled_init_method_normal, small_init_init_method,
+                                               wang_init_method, xavier_normal_init_method)
+    from megatron.model.moe_mlp import MemoryOptimizedParallelGroupedMLP, ParallelGroupedMLP
+    from megatron.model.positional_embeddings import apply_rotary_pos_emb, rotate_half
+    from megatron.model.rwkv import RUN_CUDA_RWKV
+    torch.manual_seed(0)
+    t = torch.empty(256, 256)
+    assert abs(float(init_method_normal(0.02)(t).std()) - 0.02) < 2e-3
+    assert abs(float(init_method_normal(0.02, use_mup_outer=True, mup_init_scale=3.0)(t).std()) - 0.06) < 6e-3
+    assert abs(float(init_method_normal(0.02, mup_init_scale=3.0)(t, use_mup=True).std()) - 0.06) < 6e-3
+    assert abs(float(scaled_init_method_normal(0.02, 8)(t).std()) - 0.02 / 4) < 1e-3
+    assert abs(float(scaled_init_method_normal(0.02, 8, num_residuals_per_layer=1)(t).std()) - 0.02 / math.sqrt(8)) < 1e-3
+    assert abs(float(small_init_init_method(256)(t).std()) - math.sqrt(2 / (5 * 256))) < 3e-3
+    assert abs(float(wang_init_method(4, 256)(t).std()) - 2 / 4 / 16) < 3e-3
+    assert xavier_normal_init_method()(t) is t
+    x, b = torch.randn(5, 8), torch.randn(8)
+    assert torch.allclose(erf_gelu(x), torch.nn.functional.gelu(x), atol=1e-6)
+    assert torch.allclose(bias_gelu(b, x), torch.nn.functional.gelu(x + b, approximate="tanh"), atol=1e-5)
+    assert torch.allclose(GeLUFunction.apply(x, b), bias_gelu(b, x))
+    xr = x.clone().requires_grad_(True)
+    torch.nn.functional.gelu(xr + b, approximate="tanh").sum().backward()
+    assert torch.allclose(bias_gelu_back(torch.ones_like(x), b, x), xr.grad, atol=1e-5)
+    g = Gated_Activation("swiglu")(torch.cat([x, x], -1))
+    assert torch.allclose(g, x * torch.nn.functional.silu(x), atol=1e-6)
+    assert torch.equal(rotate_half(torch.tensor([1., 2., 3., 4.])), torch.tensor([-3., -4., 1., 2.]))
+    s, d = 6, 8
+    q, k = torch.randn(s, 2, 3, d), torch.randn(s, 2, 3, d)
+    inv = 1.0 / (10000 ** (torch.arange(0, d, 2).float() / d))
+    f = torch.outer(torch.arange(s + 2).float(), inv)
+    emb = torch.cat([f, f], -1)[:, None, None, :]
+    q2, k2 = apply_rotary_pos_emb(q, k, emb.cos(), emb.sin(), offset=2)
+    assert torch.allclose(q2, FusedRoPECachedFunc.apply(q, emb.cos()[2:], emb.sin()[2:]), atol=1e-5)
+    assert (q2.norm(dim=-1) - q.norm(dim=-1)).abs().max() < 1e-4 and k2.shape == k.shape
+    assert MemoryOptimizedParallelGroupedMLP is ParallelGroupedMLP
+    B, T, H, N = 1, 5, 2, 4
+    r, kk, v = (torch.randn(B, T, H * N) for _ in range(3))
+    w, u = -torch.rand(B, T, H * N), torch.randn(H, N)
+    from gpt_neox_b200.ops.wkv import wkv6_reference
+    assert torch.allclose(RUN_CUDA_RWKV(B, T, H * N, H, r, kk, v, w, u), wkv6_reference(r, kk, v, w, u))
+    buf = io.BytesIO()
+    write_longs(buf, [1, 2, 2 ** 40])
+    buf.seek(0)
+    assert read_longs(buf, 3).tolist() == [1, 2, 2 ** 40]
+    with pytest.raises(EOFError):
+        read_longs(buf, 1)
