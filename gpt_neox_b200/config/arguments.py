@@ -431,6 +431,11 @@ class NeoXArgs:
             except Exception as e:
                 print(f"WARNING: Comet logging requested but unavailable ({e})", flush=True)
 
+    def enable_logging(self):
+        """Copy stdout / stderr of this process into ``log_dir/<hostname>_std{out,err}.txt``."""
+        from ..obs.logging import enable_logging
+        enable_logging(self)
+
     def print(self):
         """Dump the arguments sorted by name, defaults marked."""
         print("-------------------- arguments --------------------", flush=True)

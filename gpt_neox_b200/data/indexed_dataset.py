@@ -202,6 +202,10 @@ class IndexedDataset(torch.utils.data.Dataset):
 
     size = num_tokens
 
+    @property
+    def supports_prefetch(self):
+        return False          # IndexedCachedDataset overrides this
+
     @staticmethod
     def exists(prefix):
         return _both_files(prefix)
@@ -220,6 +224,10 @@ class IndexedCachedDataset(IndexedDataset):
         super().__init__(path)
         self._arena = np.empty(0, dtype=self._index.dtype)
         self._where = {}            # item -> first element in the arena
+
+    @property
+    def supports_prefetch(self):
+        return True
 
     def prefetch(self, indices: Iterable[int]):
         wanted = sorted({int(i) for i in indices})
@@ -332,6 +340,16 @@ class MMapIndexedDataset(torch.utils.data.Dataset):
     @property
     def sizes(self):
         return self._index.sizes
+
+    def size(self, index):
+        return self._index.sizes[index]
+
+    def num_tokens(self, index):
+        return self._index.sizes[index]
+
+    @property
+    def supports_prefetch(self):
+        return False          # the file is memory-mapped: the page cache does the prefetching
 
     @property
     def dtype(self):
