@@ -385,7 +385,14 @@ def _gated(cfg):
     return cfg.get("activation", "gelu") in ("swiglu", "geglu", "reglu", "bilinear", "glu")
 
 
-def convert_neox_to_hf(input_dir, config_file, output_dir, architecture="neox", vocab_size=None):
+_PRECISIONS = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32, "auto": None, None: None}
+
+
+def convert_neox_to_hf(input_dir, config_file, output_dir, architecture="neox", vocab_size=None, precision=None,
+                       pad_token_id=None, save_tokenizer=True):
+    """``precision``: cast the floating-point weights (``auto`` / None keeps the checkpoint's dtype);
+    ``pad_token_id``: written into ``config.json``; ``save_tokenizer``: copy the ``vocab_file`` of an
+    ``HFTokenizer`` config beside the weights as ``tokenizer.json``."""
     cfg = _load_config(config_file)
     shards = load_neox_shards(input_dir)
     full = merge_tp(shards, gated_mlp=_gated(cfg))
@@ -398,10 +405,22 @@ def convert_neox_to_hf(input_dir, config_file, output_dir, architecture="neox", 
         for k in (emb_key, "embed_out.weight", "lm_head.weight"):
             if k in hf:
                 hf[k] = hf[k][:vocab].clone()
+    dtype = _PRECISIONS[precision]
+    if dtype is not None:
+        hf = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in hf.items()}
     os.makedirs(output_dir, exist_ok=True)
+    hf_cfg = hf_config_from_neox(cfg, architecture, vocab)
+    if dtype is not None:
+        hf_cfg["torch_dtype"] = str(dtype).replace("torch.", "")
+    if pad_token_id is not None:
+        hf_cfg["pad_token_id"] = int(pad_token_id)
     with open(os.path.join(output_dir, "config.json"), "w") as f:
-        json.dump(hf_config_from_neox(cfg, architecture, vocab), f, indent=2)
+        json.dump(hf_cfg, f, indent=2)
     torch.save({k: v.contiguous() for k, v in hf.items()}, os.path.join(output_dir, "pytorch_model.bin"))
+    vocab_file = cfg.get("vocab_file")
+    if save_tokenizer and cfg.get("tokenizer_type", "") == "HFTokenizer" and vocab_file and os.path.exists(vocab_file):
+        import shutil
+        shutil.copyfile(vocab_file, os.path.join(output_dir, "tokenizer.json"))
     return hf
 
 
@@ -476,6 +495,50 @@ def inspect(path, out=print):
         walk(torch.load(f, map_location="cpu", weights_only=False), 2)
 
 
+def _flatten(obj, prefix=""):
+    out = {}
+    if isinstance(obj, dict):
+        for k, v in obj.items():
+            out.update(_flatten(v, f"{prefix}{k}." if not torch.is_tensor(v) else f"{prefix}{k}"))
+    elif isinstance(obj, (list, tuple)):
+        for i, v in enumerate(obj):
+            out.update(_flatten(v, f"{prefix}{i}." if not torch.is_tensor(v) else f"{prefix}{i}"))
+    else:
+        out[prefix.rstrip(".") if not torch.is_tensor(obj) else prefix] = obj
+    return out
+
+
+def diff(path_a, path_b, attributes=(), out=print):
+    """Compare two checkpoint files key by key: entries present on one side only, tensors whose shape or dtype
+    differ, and the largest absolute difference of those that match in shape.  ``attributes`` names extra
+    tensor reductions to print for differing tensors (``mean``, ``std``, ``norm``, ``min``, ``max``).
+    Returns the number of differing entries."""
+    a = _flatten(torch.load(path_a, map_location="cpu", weights_only=False))
+    b = _flatten(torch.load(path_b, map_location="cpu", weights_only=False))
+    n = 0
+    for k in sorted(set(a) | set(b)):
+        if k not in a or k not in b:
+            out(f"{'<' if k in a else '>'} {k}: only in {path_a if k in a else path_b}")
+            n += 1
+            continue
+        va, vb = a[k], b[k]
+        if torch.is_tensor(va) and torch.is_tensor(vb):
+            if va.shape != vb.shape or va.dtype != vb.dtype:
+                out(f"! {k}: {tuple(va.shape)} {va.dtype} vs {tuple(vb.shape)} {vb.dtype}")
+                n += 1
+            elif not torch.equal(va, vb):
+                d = (va.double() - vb.double()).abs().max().item()
+                extra = "".join(f" {at}: {getattr(va.double(), at)().item():.6g} vs {getattr(vb.double(), at)().item():.6g}"
+                                for at in attributes)
+                out(f"~ {k}: max |a - b| = {d:.6g}{extra}")
+                n += 1
+        elif torch.is_tensor(va) != torch.is_tensor(vb) or va != vb:
+            out(f"~ {k}: {va!r} vs {vb!r}")
+            n += 1
+    out(f"{n} differing entries")
+    return n
+
+
 def upload(hf_dir, repo_id, private=False):
     try:
         from huggingface_hub import HfApi
@@ -494,9 +557,14 @@ def main(argv=None):
     a.add_argument("--output_dir", required=True); a.add_argument("--architecture", default="neox",
                                                                    choices=["neox", "llama", "mistral"])
     a.add_argument("--vocab_size", type=int, default=None)
+    a.add_argument("--precision", default="auto", choices=["auto", "fp16", "bf16", "fp32"])
+    a.add_argument("--pad-token-id", "--pad_token_id", dest="pad_token_id", type=int, default=None)
+    a.add_argument("--no_save_tokenizer", action="store_true")
     a = sub.add_parser("hf-to-neox")
     a.add_argument("--hf_dir", required=True); a.add_argument("--config_file", required=True, nargs="+")
     a.add_argument("--output_dir", required=True); a.add_argument("--tp", type=int, default=1)
+    a.add_argument("--pp", type=int, default=0, help="accepted for parity: the per-layer files written here load "
+                                                     "under any pipeline-parallel size")
     a = sub.add_parser("raw-llama-to-neox")
     a.add_argument("--input_dir", required=True); a.add_argument("--config_file", required=True, nargs="+")
     a.add_argument("--output_dir", required=True); a.add_argument("--tp", type=int, default=1)
@@ -506,13 +574,17 @@ def main(argv=None):
     a = sub.add_parser("neox-to-mamba-ssm")
     a.add_argument("--input_dir", required=True); a.add_argument("--output_dir", required=True)
     a = sub.add_parser("inspect")
-    a.add_argument("path")
+    a.add_argument("path", nargs="?")
+    a.add_argument("--diff", "--compare", dest="diff", nargs=2, metavar=("A", "B"), default=None)
+    a.add_argument("--attributes", nargs="*", default=[])
     a = sub.add_parser("upload")
     a.add_argument("--hf_dir", required=True); a.add_argument("--repo_id", required=True)
     a.add_argument("--private", action="store_true")
     args = p.parse_args(argv)
     if args.cmd == "neox-to-hf":
-        convert_neox_to_hf(args.input_dir, args.config_file, args.output_dir, args.architecture, args.vocab_size)
+        convert_neox_to_hf(args.input_dir, args.config_file, args.output_dir, args.architecture, args.vocab_size,
+                           precision=args.precision, pad_token_id=args.pad_token_id,
+                           save_tokenizer=not args.no_save_tokenizer)
     elif args.cmd == "hf-to-neox":
         convert_hf_to_neox(args.hf_dir, args.config_file, args.output_dir, args.tp)
     elif args.cmd == "raw-llama-to-neox":
@@ -525,7 +597,10 @@ def main(argv=None):
         torch.save(neox_to_mamba_ssm_state(merge_tp(load_neox_shards(args.input_dir))),
                    os.path.join(args.output_dir, "pytorch_model.bin"))
     elif args.cmd == "inspect":
-        inspect(args.path)
+        if args.diff:
+            diff(args.diff[0], args.diff[1], args.attributes)
+        else:
+            inspect(args.path)
     elif args.cmd == "upload":
         upload(args.hf_dir, args.repo_id, args.private)
 

@@ -186,3 +186,29 @@ def test_tp2_checkpoint_files_round_trip_through_huggingface(tmp_path):
                                architecture="llama")
     again = torch.tensor(run_distributed(_rank_logits, 2, back, tokens, 0)[0])
     torch.testing.assert_close(again[..., :theirs.shape[-1]], theirs, rtol=2e-4, atol=2e-4)
+    # the command-line form with a cast and a padding token
+    convert.main(["neox-to-hf", "--input_dir", str(tmp_path / "ck" / "global_step2"), "--config_file",
+                  str(tmp_path / "cfg.yml"), "--output_dir", str(tmp_path / "hf16"), "--architecture", "llama",
+                  "--precision", "bf16", "--pad-token-id", "3", "--no_save_tokenizer"])
+    import json
+    hcfg = json.load(open(tmp_path / "hf16" / "config.json"))
+    assert hcfg["torch_dtype"] == "bfloat16" and hcfg["pad_token_id"] == 3
+    sd = torch.load(tmp_path / "hf16" / "pytorch_model.bin")
+    assert all(v.dtype == torch.bfloat16 for v in sd.values() if v.is_floating_point())
+
+
+def test_checkpoint_diff_and_cli_flags(tmp_path):
+    from gpt_neox_b200.ckpt import convert
+    a = {"module": {"w": torch.ones(2, 3), "b": torch.zeros(3)}, "iteration": 5, "only_a": 1}
+    b = {"module": {"w": torch.ones(2, 3) * 1.5, "b": torch.zeros(4)}, "iteration": 6}
+    torch.save(a, tmp_path / "a.pt")
+    torch.save(b, tmp_path / "b.pt")
+    lines = []
+    n = convert.diff(str(tmp_path / "a.pt"), str(tmp_path / "b.pt"), attributes=["mean"], out=lines.append)
+    assert n == 4
+    text = "\n".join(lines)
+    assert "~ module.w: max |a - b| = 0.5 mean: 1 vs 1.5" in text and "! module.b" in text
+    assert "< only_a" in text and "~ iteration: 5 vs 6" in text
+    assert convert.diff(str(tmp_path / "a.pt"), str(tmp_path / "a.pt"), out=lines.append) == 0
+    convert.main(["inspect", "--diff", str(tmp_path / "a.pt"), str(tmp_path / "b.pt"), "--attributes", "std"])
+    convert.main(["inspect", str(tmp_path / "a.pt")])
