@@ -17,6 +17,7 @@ comma-separated list.  Outputs: ``<prefix>_<key>_document.{bin,idx}`` (+ ``_labe
 from __future__ import annotations
 
 import argparse
+import os
 import gzip
 import io
 import json
@@ -174,10 +175,33 @@ class Encoder:
 
 
 # ----------------------------------------------------------------------------------------- driver
+def process_share_from_env(env=None):
+    """(rank, world size) of this process among the preprocessing workers of a multi-node job: ``RANK`` /
+    ``WORLD_SIZE`` first, then SLURM's, then Open MPI's variables (tools/datasets/multinode_prepare_data.sh:15-16);
+    (0, 1) when none is set."""
+    env = os.environ if env is None else env
+    for r, w in (("RANK", "WORLD_SIZE"), ("SLURM_PROCID", "SLURM_NTASKS"),
+                 ("OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE")):
+        if r in env and w in env:
+            return int(env[r]), int(env[w])
+    return 0, 1
+
+
+def share_of(items, rank: int, world: int):
+    """Contiguous, balanced share of ``items`` for ``rank``: the first ``len % world`` ranks get one more."""
+    n, rem = divmod(len(items), world)
+    lo = rank * n + min(rank, rem)
+    return list(items[lo:lo + n + (1 if rank < rem else 0)])
+
+
 def get_args(input_args=None):
     p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     g = p.add_argument_group("input data")
-    g.add_argument("--input", type=str, required=True, help="comma-separated input files")
+    g.add_argument("--input", type=str, default=None, help="comma-separated input files")
+    g.add_argument("--input-list", type=str, default=None,
+                   help="text file with one input path per line; with several processes (RANK / WORLD_SIZE, or the "
+                        "SLURM / Open MPI equivalents) each takes a contiguous share of the lines and appends its "
+                        "rank to --output-prefix (merge the parts with data/dataset_tools.py merge)")
     g.add_argument("--jsonl-keys", nargs="+", default=None, help="keys to extract (default: text / conversation)")
     g.add_argument("--num-docs", type=int, default=None, help="number of documents, for the progress report")
     g.add_argument("--mask-before-token", type=str, default=None,
@@ -204,6 +228,19 @@ def get_args(input_args=None):
     g.add_argument("--workers", type=int, default=1)
     g.add_argument("--log-interval", type=int, default=100)
     a = p.parse_args(input_args)
+    if (a.input is None) == (a.input_list is None):
+        p.error("give exactly one of --input and --input-list")
+    if a.input_list is not None:
+        rank, world = process_share_from_env()
+        with open(a.input_list) as f:
+            paths = [ln.strip() for ln in f if ln.strip()]
+        mine = share_of(paths, rank, world)
+        if not mine:
+            p.error(f"rank {rank} of {world}: no input files in its share of {a.input_list}")
+        a.input = ",".join(mine)
+        if world > 1:
+            a.output_prefix = f"{a.output_prefix}{rank}"
+        print(f"rank {rank} of {world}: {len(mine)} of {len(paths)} input files -> {a.output_prefix}")
     if a.chat_template:
         if a.tokenizer_path is None:
             p.error("--chat-template needs --tokenizer-path")

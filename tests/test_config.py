@@ -102,3 +102,14 @@ def test_elasticity_keeps_one_global_batch_over_gpu_counts():
         NeoXArgs.from_dict(tiny_config(elasticity=block, global_num_gpus=8))   # explicit batch keys conflict
     small, v2, _ = compute_elastic_config(dict(block, prefer_larger_batch=False))
     assert len(v2) == len(valid) and small <= batch
+
+
+def test_argument_reference_document_is_current():
+    """configs/neox_arguments.md is generated from the schema; a schema change must regenerate it."""
+    import importlib.util
+    import os
+    from common import ROOT
+    spec = importlib.util.spec_from_file_location("gen_docs_script", os.path.join(ROOT, "configs", "gen_docs.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.main(["--check"]) == 0

@@ -100,3 +100,36 @@ def test_launcher_runs_local_ranks(tmp_path):
     bad = tmp_path / "bad.py"
     bad.write_text("import os,sys,time\nsys.exit(7) if os.environ['RANK']=='1' else time.sleep(30)\n")
     assert launcher.main(["--hostfile", "/nonexistent", "--num_gpus", "2", str(bad)]) == 7
+
+
+def test_multinode_preprocessing_shares_and_merge(tmp_path, monkeypatch):
+    """Three 'ranks' each tokenise their share of five input files; the merged parts hold every document once,
+    in file order (reference: tools/datasets/multinode_prepare_data.sh)."""
+    import json
+    import numpy as np
+    from gpt_neox_b200.data import dataset_tools, preprocess_data
+    from gpt_neox_b200.data.indexed_dataset import make_dataset
+    assert [preprocess_data.share_of(list(range(5)), r, 3) for r in range(3)] == [[0, 1], [2, 3], [4]]
+    assert preprocess_data.process_share_from_env({"SLURM_PROCID": "2", "SLURM_NTASKS": "4"}) == (2, 4)
+    assert preprocess_data.process_share_from_env({"RANK": "1", "WORLD_SIZE": "2", "SLURM_PROCID": "9",
+                                                   "SLURM_NTASKS": "10"}) == (1, 2)
+    assert preprocess_data.process_share_from_env({}) == (0, 1)
+    paths = []
+    for i in range(5):
+        p = tmp_path / f"in{i}.jsonl"
+        p.write_text("".join(json.dumps({"text": f"file {i} doc {j}"}) + "\n" for j in range(3)))
+        paths.append(str(p))
+    (tmp_path / "files.txt").write_text("\n".join(paths) + "\n")
+    parts = tmp_path / "parts"
+    parts.mkdir()
+    for rank in range(3):
+        monkeypatch.setenv("RANK", str(rank))
+        monkeypatch.setenv("WORLD_SIZE", "3")
+        preprocess_data.main(["--input-list", str(tmp_path / "files.txt"), "--tokenizer-type", "CharLevelTokenizer",
+                              "--output-prefix", str(parts / "part"), "--append-eod"])
+    assert sorted(f.name for f in parts.iterdir() if f.suffix == ".idx") == [f"part{r}_text_document.idx" for r in range(3)]
+    dataset_tools.main(["merge", "--input", str(parts), "--output-prefix", str(tmp_path / "merged")])
+    ds = make_dataset(str(tmp_path / "merged"), "mmap")
+    assert len(ds) == 15
+    texts = ["".join(chr(int(t)) for t in np.asarray(ds[i])[:-1]) for i in range(15)]
+    assert texts == [f"file {i} doc {j}" for i in range(5) for j in range(3)]
