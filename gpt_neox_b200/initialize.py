@@ -52,7 +52,8 @@ def setup_activation_checkpointing(neox_args):
     configure_checkpointing(partition_activations=neox_args.partition_activations,
                             contiguous_checkpointing=neox_args.contiguous_checkpointing,
                             num_checkpoints=num_layers, checkpoint_in_cpu=neox_args.checkpoint_in_cpu,
-                            synchronize=neox_args.synchronize_each_layer, profile=neox_args.profile_backward)
+                            synchronize=neox_args.synchronize_each_layer, profile=neox_args.profile_backward,
+                            sequence_parallel=bool(neox_args.sequence_parallel))
 
 
 def _initialize_distributed(neox_args):

@@ -105,7 +105,7 @@ class _CheckpointFunction(torch.autograd.Function):
         ctx.tracker_states = _TRACKER.get_states()
         with torch.no_grad():
             outputs = run_function(*args)
-        ctx.inputs = args
+        ctx.inputs = tuple(_stash(a) for a in args)
         return outputs
 
     @staticmethod
@@ -117,8 +117,9 @@ class _CheckpointFunction(torch.autograd.Function):
         if ctx.cuda:
             torch.cuda.set_rng_state(ctx.cuda_state)
         _TRACKER.set_states(ctx.tracker_states)
-        detached = tuple(a.detach().requires_grad_(a.requires_grad) if isinstance(a, torch.Tensor) else a
-                         for a in ctx.inputs)
+        detached = tuple(_unstash(a) for a in ctx.inputs)
+        if _CKPT_CONFIG["synchronize"] and ctx.cuda:
+            torch.cuda.synchronize()
         with torch.enable_grad():
             outputs = ctx.run_function(*detached)
         torch.set_rng_state(bwd_cpu)
@@ -135,17 +136,50 @@ class _CheckpointFunction(torch.autograd.Function):
 
 
 _CKPT_CONFIG = {"partition_activations": False, "contiguous": False, "cpu": False, "num_layers": None,
-                "synchronize": False, "profile": False}
+                "synchronize": False, "profile": False, "sequence_parallel": False}
+
+
+def _stash(a):
+    """What a checkpointed region keeps of one argument until backward.  ``partition_activations``: a
+    floating-point tensor that is replicated over the tensor-parallel group (no sequence parallelism) is kept
+    as this rank's 1/tp slice and re-assembled by an all-gather in backward.  ``checkpoint_in_cpu``: the kept
+    tensor (slice) waits in host memory."""
+    if not isinstance(a, torch.Tensor):
+        return ("raw", a)
+    from . import state as mpu
+    cfg = _CKPT_CONFIG
+    tp = mpu.get_model_parallel_world_size()
+    keep, kind = a.detach(), "full"
+    if cfg["partition_activations"] and tp > 1 and not cfg["sequence_parallel"] and a.is_floating_point() \
+            and a.numel() > 0 and a.numel() % tp == 0:
+        keep = keep.reshape(-1).chunk(tp)[mpu.get_model_parallel_rank()].clone()
+        kind = "slice"
+    if cfg["cpu"] and keep.device.type != "cpu":
+        keep = keep.to("cpu", non_blocking=True)
+    return (kind, keep, a.shape, a.requires_grad, a.device)
+
+
+def _unstash(entry):
+    if entry[0] == "raw":
+        return entry[1]
+    kind, keep, shape, requires_grad, device = entry
+    if keep.device != device:
+        keep = keep.to(device, non_blocking=True)
+    if kind == "slice":
+        from . import state as mpu
+        from ..comm import collectives
+        keep = collectives.all_gather_dim(keep, 0, mpu.get_model_parallel_group()).view(shape)
+    return keep.detach().requires_grad_(requires_grad)
 
 
 def configure_checkpointing(partition_activations=False, contiguous_checkpointing=False, num_checkpoints=None,
-                            checkpoint_in_cpu=False, synchronize=False, profile=False):
+                            checkpoint_in_cpu=False, synchronize=False, profile=False, sequence_parallel=False):
     """Counterpart of ``deepspeed.checkpointing.configure`` (megatron/initialize.py:103-118). Under
     sequence parallelism the layer inputs are already sharded over the tensor-parallel group, which
     is what ``partition_activations`` buys in the reference."""
     _CKPT_CONFIG.update(partition_activations=partition_activations, contiguous=contiguous_checkpointing,
                         num_layers=num_checkpoints, cpu=checkpoint_in_cpu, synchronize=synchronize,
-                        profile=profile)
+                        profile=profile, sequence_parallel=sequence_parallel)
 
 
 def checkpoint(function, *args):

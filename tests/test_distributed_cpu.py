@@ -117,3 +117,41 @@ def test_t5_relative_position_bias_tp2_pp2_match_single_rank():
     assert ref[-1] < ref[0]
     out = run_distributed(_train, 2, dict(cfg, model_parallel_size=2, make_vocab_size_divisible_by=128), 6)
     assert out[0] == pytest.approx(ref, rel=5e-5)
+
+
+def test_partitioned_and_offloaded_activation_checkpoints_tp2():
+    """``partition_activations`` keeps 1/tp of every checkpointed layer input per rank (re-assembled by an
+    all-gather in backward) and ``checkpoint_in_cpu`` parks it in host memory: the losses are those of plain
+    activation checkpointing, with and without sequence parallelism (where the inputs are sharded already)."""
+    cfg = tiny_config(use_cpu_initialization=True, model_parallel_size=2, make_vocab_size_divisible_by=128,
+                      checkpoint_activations=True, checkpoint_num_layers=1)
+    ref = run_distributed(_train, 2, cfg, 3)[0]
+    got = run_distributed(_train, 2, dict(cfg, partition_activations=True, checkpoint_in_cpu=True,
+                                          synchronize_each_layer=True), 3)[0]
+    assert got == pytest.approx(ref, rel=1e-6)
+    sp = run_distributed(_train, 2, dict(cfg, sequence_parallel=True), 3)[0]
+    got = run_distributed(_train, 2, dict(cfg, sequence_parallel=True, partition_activations=True), 3)[0]
+    assert got == pytest.approx(sp, rel=1e-6)
+
+
+def _stash_sizes(rank, world):
+    import torch.distributed as dist
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200.parallel import random as prandom
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    mpu.destroy_model_parallel()
+    mpu.initialize_model_parallel(2)
+    prandom.configure_checkpointing(partition_activations=True)
+    x = torch.arange(24, dtype=torch.float32).view(4, 6).requires_grad_(True)
+    mask = torch.ones(4, 4, dtype=torch.bool)
+    kept = prandom._stash(x)
+    back = prandom._unstash(kept)
+    out = (kept[0], kept[1].numel(), prandom._stash(mask)[0], bool(torch.equal(back, x)), back.requires_grad)
+    prandom.configure_checkpointing()
+    dist.destroy_process_group()
+    return out
+
+
+def test_activation_stash_keeps_one_slice_per_rank():
+    for r in run_distributed(_stash_sizes, 2):
+        assert r == ("slice", 12, "full", True, True)
