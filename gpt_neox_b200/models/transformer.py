@@ -467,6 +467,12 @@ class ParallelTransformerLayer(nn.Module):
             else:
                 attention_output, attention_bias = att
             attention_output = bias_dropout_add(attention_output, attention_bias, None, p, self.training)
+            if self.num_experts > 1:
+                # the MoE layer returns one complete tensor (no bias, nothing left to sum over the tensor-parallel
+                # group), so only the attention branch goes through the reduction.  (The reference unpacks two
+                # values here and cannot run this combination, megatron/model/transformer.py:1103.)
+                moe_output = self.mlp(x2)
+                return residual + (self.reduce(attention_output) if ws > 1 else attention_output) + moe_output
             mlp_output, mlp_bias = self.mlp(x2)
             output = bias_dropout_add(mlp_output, mlp_bias, attention_output, p, self.training)
             # one reduction for both branches (all-reduce, or reduce-scatter under sequence parallelism)

@@ -188,6 +188,12 @@ def mark_norms_for_sequence_parallel_grad_sync(module, neox_args):
             for p in m.parameters(recurse=False):
                 if p.requires_grad:
                     p.sequence_parallel_grad_sync = True
+        # MoE routers and experts are replicated over the tensor-parallel group (expert parallelism is a
+        # separate axis here) and, under sequence parallelism, see only this rank's part of the sequence
+        elif type(m).__name__ == "ParallelDroplessMoE":
+            for p in m.parameters(recurse=True):
+                if p.requires_grad and not getattr(p, "model_parallel", False):
+                    p.sequence_parallel_grad_sync = True
 
 
 def get_parallel_linear(neox_args):

@@ -97,9 +97,11 @@ def test_pipeline_2_x_tensor_2_with_tied_embeddings():
     assert out[0] == pytest.approx(ref, rel=5e-5)
 
 
-def test_moe_expert_parallel_2_matches_single_rank():
-    """Dropless MoE with all-to-all dispatch over 2 expert-parallel ranks == the single-rank MoE."""
-    cfg = tiny_config(use_cpu_initialization=True, gpt_j_residual=False, moe_num_experts=4, moe_top_k=2,
+@pytest.mark.parametrize("gpt_j", [False, True])
+def test_moe_expert_parallel_2_matches_single_rank(gpt_j):
+    """Dropless MoE with all-to-all dispatch over 2 expert-parallel ranks == the single-rank MoE, for the
+    sequential and the parallel (GPT-J) residual form."""
+    cfg = tiny_config(use_cpu_initialization=True, gpt_j_residual=gpt_j, moe_num_experts=4, moe_top_k=2,
                       moe_router_type="topk", moe_expert_interval=1, train_micro_batch_size_per_gpu=2)
     ref = _single(dict(cfg, train_micro_batch_size_per_gpu=4), 3)
     out = run_distributed(_train, 2, dict(cfg, moe_expert_parallel_size=2), 3)
@@ -155,3 +157,17 @@ def _stash_sizes(rank, world):
 def test_activation_stash_keeps_one_slice_per_rank():
     for r in run_distributed(_stash_sizes, 2):
         assert r == ("slice", 12, "full", True, True)
+
+
+@pytest.mark.parametrize("gpt_j", [False, True])
+def test_moe_under_tensor_and_sequence_parallelism_matches_tp1(gpt_j):
+    """MoE routers and experts are replicated over the tensor-parallel group; under sequence parallelism each
+    rank routes only its part of the sequence, so their gradients are summed over the group (a second step
+    that differs from TP-1 is the symptom when they are not)."""
+    cfg = tiny_config(use_cpu_initialization=True, gpt_j_residual=gpt_j, moe_num_experts=4, moe_top_k=2,
+                      moe_router_type="topk", moe_expert_interval=1, make_vocab_size_divisible_by=256,
+                      use_bias_in_attn_linear=False, use_bias_in_mlp=False)
+    ref = _single(cfg, 3)
+    out = run_distributed(_train, 2, dict(cfg, model_parallel_size=2, sequence_parallel=True,
+                                          make_vocab_size_divisible_by=128), 3)[0]
+    assert out == pytest.approx(ref, rel=2e-6)
