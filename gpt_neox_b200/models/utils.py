@@ -184,6 +184,11 @@ def mark_norms_for_sequence_parallel_grad_sync(module, neox_args):
     if not neox_args.sequence_parallel:
         return
     for name, m in module.named_modules():
+        if name.endswith("qk_layernorm"):
+            # normalises this rank's heads of the FULL sequence (the QKV projection gathered it): its
+            # parameters are per partition and their gradients complete; summing them over the group would
+            # mix the partitions (the reference flags them by name and does, megatron/model/utils.py:398-412)
+            continue
         if "norm" in name.lower() or isinstance(m, _NORM_TYPES):
             for p in m.parameters(recurse=False):
                 if p.requires_grad:

@@ -171,3 +171,13 @@ def test_moe_under_tensor_and_sequence_parallelism_matches_tp1(gpt_j):
     out = run_distributed(_train, 2, dict(cfg, model_parallel_size=2, sequence_parallel=True,
                                           make_vocab_size_divisible_by=128), 3)[0]
     assert out == pytest.approx(ref, rel=2e-6)
+
+
+def test_qk_layernorm_is_not_summed_over_the_group_under_sequence_parallelism():
+    """The QK norm works on this rank's heads of the full sequence, so sequence parallelism must leave its
+    gradients alone: TP-2 with and without sequence parallelism train identically."""
+    cfg = tiny_config(use_cpu_initialization=True, model_parallel_size=2, make_vocab_size_divisible_by=128,
+                      use_qk_layernorm=True, gpt_j_residual=False)
+    a = run_distributed(_train, 2, cfg, 4)[0]
+    b = run_distributed(_train, 2, dict(cfg, sequence_parallel=True), 4)[0]
+    assert b == pytest.approx(a, rel=2e-6)
