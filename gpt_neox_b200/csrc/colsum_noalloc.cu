@@ -1,6 +1,8 @@
 // Column sums without a caller-provided workspace: see no_alloc.h for the contract.
 #include "no_alloc.h"
 
+#include <mutex>
+
 #include "common.h"
 #include "ptx.cuh"
 
@@ -68,8 +70,12 @@ __global__ void final_sums(const float* __restrict__ ws, float* __restrict__ out
 }
 
 // Device address of the scratch array, resolved once per device with that device current.
+// The small cache is filled under a lock, so first calls from several host threads are safe.  It is
+// not refreshed after cudaDeviceReset: a process that resets a device must not call in again.
 float* scratch_for_current_device(int* status) {
   static float* ptrs[64] = {nullptr};
+  static std::mutex mu;
+  std::lock_guard<std::mutex> guard(mu);
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= 64) {

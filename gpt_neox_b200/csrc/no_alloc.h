@@ -16,8 +16,11 @@
 //     (N <= 16384 for any row count); larger requests are rejected with NX_ERR_ARG and a message in
 //     nx_last_error().
 //   * Set-up: the first call on each device resolves the array's device address
-//     (cudaGetSymbolAddress) with that device current.  Make that first call before any stream
-//     capture begins on that device.
+//     (cudaGetSymbolAddress) with that device current; with CUDA's lazy module loading it may also
+//     be the call that loads this library's device code, which is when the driver sets the 4 MiB
+//     aside.  Make that first call at start-up, before any stream capture begins on that device.
+//     First calls from several host threads are serialised by a lock.  The cached address does
+//     not survive cudaDeviceReset: do not call in again after resetting a device.
 //   * Sharing: every call on a device uses the same array, which keeps the previous call's
 //     contents.  Each call overwrites every element it later reads, so nothing has to be cleared,
 //     but two calls that overlap on the GPU (different streams without ordering) race on it.

@@ -248,6 +248,10 @@ class FlatAdam:
         return self.param_groups[0]["lr"]
 
     def step(self, grad_scale, skip):
+        if self.overflow:
+            # fp16 overflow, already known on the host: the step is skipped and not counted, so the bias
+            # corrections and the saved ``step`` stay those of the updates that really happened
+            return
         self.step_count += 1
         lr = self.param_groups[0]["lr"]
         b1, b2 = self.param_groups[0]["betas"]
@@ -463,6 +467,9 @@ class Engine(torch.nn.Module):
         self._acc.zero_()
         tp_rank0 = mpu.get_model_parallel_rank() == 0
         for g in self.groups:
+            if not g.sharded and g.dp_size > 1 and g.dp_rank != 0:
+                continue       # unsharded group (ZeRO stage 0): every data-parallel rank holds the same reduced
+                               # gradient, so only the first one counts it
             gs = g.grad_shard()
             for (lo, hi, _wd, rep, skip, _lrm) in g.segments:
                 if skip or (rep and not tp_rank0):

@@ -655,10 +655,16 @@ def train(neox_args, timers, model, optimizer, lr_scheduler, train_data_iterator
                                           loss_scale=model.cur_scale if neox_args.precision == "fp16" else None,
                                           report_memory_flag=report_memory_flag, skipped_iter=skipped_iter,
                                           model=model, optimizer=optimizer, noise_scale_logger=noise_scale_logger)
-        if neox_args.save and is_save_iter(neox_args, iteration):
+        saving = neox_args.save and is_save_iter(neox_args, iteration)
+        evaluating = neox_args.eval_interval and iteration % neox_args.eval_interval == 0 and neox_args.do_valid
+        if (saving or evaluating) and torch.cuda.is_available():
+            # never write or score weights that a timed-out communication kernel may have left invalid
+            from .ops import _lib as _klib
+            _klib.raise_on_device_error()
+        if saving:
             save_checkpoint(neox_args=neox_args, iteration=iteration, model=model, optimizer=optimizer,
                             lr_scheduler=lr_scheduler)
-        if neox_args.eval_interval and iteration % neox_args.eval_interval == 0 and neox_args.do_valid:
+        if evaluating:
             prefix = "iteration {}".format(iteration)
             evaluate_and_print_results(neox_args=neox_args, prefix=prefix, forward_step_func=forward_step,
                                        data_iterator=valid_data_iterator, model=model, iteration=iteration,

@@ -24,6 +24,23 @@ def _train(rank, world, cfg, steps):
     return losses
 
 
+def _train_with_norms(rank, world, cfg, steps):
+    """As _train, but also returns the global gradient norm the engine reports after every step."""
+    from gpt_neox_b200 import training
+    norms = []
+    orig = training.train_step
+
+    def wrapped(*a, **kw):
+        out = orig(*a, **kw)
+        norms.append(kw["model"].get_global_grad_norm())
+        return out
+    training.train_step = wrapped
+    try:
+        return _train(rank, world, cfg, steps), norms
+    finally:
+        training.train_step = orig
+
+
 def _single(cfg, steps):
     return run_distributed(_train, 1, cfg, steps)[0]
 
@@ -40,6 +57,22 @@ def test_config1_plumbing_zero1_dp2_matches_single_process():
     assert out[0] == pytest.approx(out[1], rel=1e-6)
     assert out[0] == pytest.approx(ref, rel=2e-5)
     assert min(ref[5:]) < ref[0]
+
+
+@pytest.mark.parametrize("layout", ["dp2", "pp2_dp2"])
+def test_zero_stage0_grad_norm_and_clipping_match_single_process(layout):
+    """Without ZeRO sharding every data-parallel rank holds the whole reduced gradient: the global norm must
+    count it once, not once per rank.  Clipping is set low enough to bite on every step, so a wrong norm
+    would change the loss curve too."""
+    cfg = tiny_config(use_cpu_initialization=True, zero_optimization={"stage": 0}, gradient_clipping=0.05,
+                      num_layers=4, train_micro_batch_size_per_gpu=4, gradient_accumulation_steps=2)
+    pp = {"pipe_parallel_size": 2} if layout == "pp2_dp2" else {}
+    ref, ref_norms = run_distributed(_train_with_norms, 2 if pp else 1, dict(cfg, **pp), 4)[0]
+    out = run_distributed(_train_with_norms, 4 if pp else 2, dict(cfg, train_micro_batch_size_per_gpu=2, **pp), 4)
+    losses, norms = out[0]
+    assert min(ref_norms) > 0.05                       # the clip is active
+    assert norms == pytest.approx(ref_norms, rel=1e-4)
+    assert losses == pytest.approx(ref, rel=5e-5)
 
 
 @pytest.mark.parametrize("sp", [False, True])

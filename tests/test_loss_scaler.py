@@ -48,7 +48,7 @@ def _train(rank, world, cfg, steps):
     training.collect_loss_for_unit_test = lambda l: losses.append(float(l))
     model = training.pretrain(a)
     return {"losses": losses, "skipped": model.skipped_steps, "scale": model.loss_scaler.cur_scale,
-            "steps": model.global_steps}
+            "steps": model.global_steps, "opt_steps": model.optimizer.step_count}
 
 
 def test_fp16_training_skips_overflowing_steps_and_recovers():
@@ -62,3 +62,5 @@ def test_fp16_training_skips_overflowing_steps_and_recovers():
     assert r["scale"] == 2.0 ** 26 / 2 ** r["skipped"]
     assert all(l == l for l in r["losses"])
     assert r["losses"][-1] < r["losses"][0]
+    # a skipped step is not an optimizer step: Adam's bias corrections count real updates only
+    assert r["opt_steps"] == r["steps"] - r["skipped"]
