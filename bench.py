@@ -2,7 +2,13 @@
 """Headline benchmark: bf16 training throughput (tokens/s, TFLOP/s per GPU) of the Pythia-6.9B
 shape on N GPUs of one node, synthetic tokens, random-init weights.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--model pythia-6-9B] [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--model pythia-6-9B] [--impl ours|reference|library]
+
+``--impl library`` runs the same model shape, batch layout and optimizer step in plain PyTorch on
+vendor kernels (cuBLAS, flash-attn, NCCL; baseline/library_arm.py) and prints the same JSON line with
+``"impl": "library"``: a same-box baseline at step level.  It is not the reference implementation.
+At ``--gpus 8`` the default run also measures the second headline configuration, GPT-NeoX-20B on
+tp4 x pp2, in child processes and reports it under ``"neox_20b"``.
 
 N = 1: TP 1;  N >= 2: TP 2 + sequence parallel x DP N/2, ZeRO-1.  Micro-batch 4, global batch
 64 * N sequences of 2048 tokens (512 at N = 8): per-GPU work is fixed as N grows (weak scaling).
@@ -32,12 +38,14 @@ def parse():
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=3)
     p.add_argument("--warmup", type=int, default=3)
-    p.add_argument("--impl", type=str, default="ours", choices=("ours", "reference"))
+    p.add_argument("--impl", type=str, default="ours", choices=("ours", "reference", "library"))
     p.add_argument("--model", type=str, default=os.environ.get("NEOX_BENCH_MODEL", "pythia-6-9B"))
     p.add_argument("--micro-batch", type=int, default=None)
     p.add_argument("--gas", type=int, default=None, help="override gradient accumulation steps")
     p.add_argument("--mode", type=str, default="fused", choices=("fused", "nccl_baseline"))
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-20b", action="store_true", help="at --gpus 8: skip the NeoX-20B (tp4 x pp2) measurement")
+    p.add_argument("--json-out", type=str, default=None, help="rank 0 also writes its JSON line to this file")
     p.add_argument("--fp8", action="store_true",
                    help="run the linear layers' GEMMs (forward, dgrad, wgrad) on the fp8 tensor cores with delayed "
                         "scaling; reported under dtype 'fp8' and never as the bf16 headline")
@@ -125,10 +133,139 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def library_arm(args):
+    """Same shape, same batch layout, same step - plain PyTorch on library kernels (baseline/library_arm.py)."""
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.join(REPO, "baseline"))
+    import library_arm as la
+
+    n = args.gpus
+    rank, local_rank = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    if args.model not in la.SHAPES:
+        if rank == 0:
+            print(json.dumps({"impl": "library", "unavailable": f"the library arm has no {args.model} layout"}))
+        return 0
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if n > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    seq = 2048
+    micro = args.micro_batch or (4 if "6-9B" in args.model else 16)
+    model, opt, tp, dp, dp_rank = la.build(args.model, n, rank, dev, seq)
+    per_gpu_seqs = 64 if "6-9B" in args.model else 128
+    gas = args.gas or (per_gpu_seqs * n) // (micro * dp)
+    global_batch = micro * gas * dp
+    g = torch.Generator(device="cpu")
+    g.manual_seed(1234 + dp_rank)
+    pool = [torch.randint(0, 50277, (micro, seq + 1), generator=g, dtype=torch.int64).to(dev) for _ in range(min(gas, 8))]
+    host = [torch.randint(0, 50277, (micro, seq + 1), generator=g, dtype=torch.int64).pin_memory() for _ in range(gas)]
+
+    def barrier_sync():
+        if n > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if n > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def device_step():
+        return la.train_step(model, opt, [pool[i % len(pool)] for i in range(gas)])
+
+    def e2e_step():
+        loss = la.train_step(model, opt, [h.to(dev, non_blocking=True) for h in host])
+        return float(loss.item())
+
+    for _ in range(args.warmup):
+        device_step()
+    sampler = ClockSampler(local_rank)
+    barrier_sync()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        device_step()
+    e1.record()
+    barrier_sync()
+    clocks = sampler.stop() if rank == 0 else None
+    dev_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    e2e = None
+    if not args.no_e2e:
+        e2e_step()
+        barrier_sync()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            last = e2e_step()
+        barrier_sync()
+        e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1000.0) / args.steps
+        e2e = {"value": global_batch * seq / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": gas * micro * (seq + 1) * 8, "d2h_bytes_per_step": 4, "final_loss": last}
+    if rank == 0:
+        tokens = global_batch * seq
+        out = {"metric": "tokens_per_sec", "value": tokens / (dev_ms / 1000.0), "unit": "tokens/s", "n_gpus": n,
+               "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True,
+               "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic tokens, random-init weights",
+               "tflops_per_gpu": la.flops_per_step(args.model, global_batch, seq) / (dev_ms / 1000.0) / n / 1e12,
+               "impl": "library",
+               "library": "torch %s: F.linear (cuBLAS), %s, F.layer_norm, AdamW(fused), NCCL" % (
+                   torch.__version__, "flash_attn_func" if la._flash is not None else "F.scaled_dot_product_attention"),
+               "config": {"model": args.model, "global_batch": global_batch, "seq_len": seq, "micro_batch": micro,
+                          "grad_accum": gas, "parallelism": f"tp{tp}" + ("+sp" if tp > 1 else "") + f" x dp{dp}, zero1",
+                          "l2": "working set far exceeds the 126 MB L2; no explicit flush"},
+               "clocks": clocks, "e2e": e2e, "gpu_launches": 0}
+        print(json.dumps(out))
+        if args.json_out:
+            with open(args.json_out, "w") as f:
+                f.write(json.dumps(out) + "\n")
+    if n > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def neox_20b_children(args, rank, local_rank):
+    """The second headline configuration, measured after the main run in one fresh child process per rank
+    (the parent has left its process group and released its device memory).  Rank 0 returns the child's
+    JSON line as a dict; a failure is reported as {"unavailable": reason}, never raised."""
+    import tempfile
+    out_path = os.path.join(tempfile.gettempdir(), f"neox20b_bench_{os.environ.get('MASTER_PORT', '0')}.json")
+    env = dict(os.environ)
+    env["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29511")) + 17)
+    for k in ("TORCHELASTIC_RUN_ID", "TORCHELASTIC_RESTART_COUNT", "TORCHELASTIC_MAX_RESTARTS",
+              "TORCHELASTIC_USE_AGENT_STORE", "TORCH_NCCL_ASYNC_ERROR_HANDLING"):
+        env.pop(k, None)
+    cmd = [sys.executable, os.path.abspath(__file__), "--gpus", "8", "--model", "neox-20B", "--steps",
+           "10", "--warmup", "3", "--mode", args.mode, "--no-20b",
+           "--json-out", out_path]
+    try:
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+        if rank != 0:
+            return None
+        if r.returncode != 0 or not os.path.exists(out_path):
+            tail = (r.stderr or r.stdout or "").strip().splitlines()[-3:]
+            return {"unavailable": f"child exited {r.returncode}: " + " | ".join(tail)}
+        with open(out_path) as f:
+            d = json.loads(f.read())
+        os.remove(out_path)
+        keep = ("value", "unit", "ms_per_step", "tflops_per_gpu", "steps", "warmup", "e2e", "config", "clocks",
+                "gpu_launches", "device_error_word")
+        return {k: d.get(k) for k in keep}
+    except Exception as e:  # noqa: BLE001 - the main number must be printed whatever happens here
+        return {"unavailable": f"{type(e).__name__}: {e}"} if rank == 0 else None
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.impl == "library":
+        return library_arm(args)
     import torch
     import torch.distributed as dist
 
@@ -300,10 +437,25 @@ def main():
                           "l2": "working set (weights + activations, tens of GB) far exceeds the 126 MB L2; "
                                 "no explicit flush"},
                "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "host_enqueue_ms_per_step": enqueue_ms, "device_error_word": dev_err}
-        print(json.dumps(out))
+    with_20b = (n == 8 and args.model == "pythia-6-9B" and not args.no_20b and not args.fp8
+                and os.environ.get("NEOX_BENCH_20B", "1") != "0")
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
+    if with_20b:
+        # release this process's device memory, then measure GPT-NeoX-20B (tp4 x pp2) in child processes
+        del model, optimizer, lr_scheduler, pool, dit
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        extra = neox_20b_children(args, rank, local_rank)
+        if rank == 0:
+            out["neox_20b"] = extra
+    if rank == 0:
+        print(json.dumps(out))
+        if args.json_out:
+            with open(args.json_out, "w") as f:
+                f.write(json.dumps(out) + "\n")
     return 0
 
 

@@ -561,8 +561,11 @@ def main(argv=None):
     a.add_argument("--pad-token-id", "--pad_token_id", dest="pad_token_id", type=int, default=None)
     a.add_argument("--no_save_tokenizer", action="store_true")
     a = sub.add_parser("hf-to-neox")
-    a.add_argument("--hf_dir", required=True); a.add_argument("--config_file", required=True, nargs="+")
-    a.add_argument("--output_dir", required=True); a.add_argument("--tp", type=int, default=1)
+    # the second spelling of each flag is the one the reference's convert_hf_to_sequential.py takes
+    a.add_argument("--hf_dir", "--hf-model-name", dest="hf_dir", required=True)
+    a.add_argument("--config_file", "--config", dest="config_file", required=True, nargs="+")
+    a.add_argument("--output_dir", "--output-dir", dest="output_dir", required=True)
+    a.add_argument("--tp", type=int, default=1)
     a.add_argument("--pp", type=int, default=0, help="accepted for parity: the per-layer files written here load "
                                                      "under any pipeline-parallel size")
     a = sub.add_parser("raw-llama-to-neox")

@@ -1,5 +1,6 @@
 // Library-wide host state: last error text, per-device error word, TMA descriptor encoder.
 #include "common.h"
+#include "ptx.cuh"
 
 #include <cudaTypedefs.h>
 #include <stdarg.h>
@@ -18,7 +19,8 @@ void set_last_error(const char* fmt, ...) {
   va_end(ap);
 }
 
-__device__ int g_error_word = 0;
+// [0] error word, [1] unused, [2..3] run-time wait budget in cycles as one 64-bit value (0 = default)
+__device__ __align__(16) int g_error_word[4] = {0, 0, 0, 0};
 
 static int* g_err_ptr[64] = {nullptr};
 static int g_sm_count[64] = {0};
@@ -200,6 +202,38 @@ NX_API int nx_poison_device_error(int value) {
   int* p = nx::device_error_word();
   if (p == nullptr) return NX_ERR_CUDA;
   NX_CUDA_CHECK(cudaMemcpy(p, &value, sizeof(int), cudaMemcpyHostToDevice));
+  return NX_OK;
+}
+
+// Replaces the cycle budget of every bounded wait on the current device (mbarrier and flag waits of
+// all kernels launched afterwards); 0 restores the compile-time default.  Synchronises the device.
+NX_API int nx_set_wait_budget_cycles(long long cycles) {
+  int* p = nx::device_error_word();
+  if (p == nullptr) return NX_ERR_CUDA;
+  NX_REQUIRE(cycles >= 0, "wait budget must be >= 0");
+  NX_CUDA_CHECK(cudaDeviceSynchronize());
+  NX_CUDA_CHECK(cudaMemcpy(p + 2, &cycles, sizeof(long long), cudaMemcpyHostToDevice));
+  return NX_OK;
+}
+
+namespace nx {
+// Waits on an mbarrier that nothing ever arrives on: the bounded wait must give up, record
+// {ERR_WAIT_TIMEOUT, site 21} and let the kernel return.  out[0] = 1 if the wait reported success.
+__global__ void mbar_timeout_probe_kernel(int* err, int* out) {
+  __shared__ __align__(8) unsigned long long bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
+    out[0] = mbar_wait(smem_u32(&bar), 0, err, 21) ? 1 : 0;
+  }
+}
+}  // namespace nx
+
+// Self-test of the bounded mbarrier wait (see the kernel above).  Set a small budget first.
+NX_API int nx_mbar_timeout_probe(void* out_i32, void* stream_) {
+  nx::mbar_timeout_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(nx::device_error_word(),
+                                                                                 static_cast<int*>(out_i32));
+  NX_LAUNCH_CHECK();
   return NX_OK;
 }
 

@@ -806,4 +806,13 @@ NX_API int nx_gemm2_bf16_allreduce(const void* A, const void* B, int M, int N, i
   return NX_OK;
 }
 
+// The delivery wait on its own: returns once *counter >= target or the wait budget ran out (then the
+// device error word holds {ERR_PEER_TIMEOUT, site 20}).
+NX_API int nx_wait_counter(const void* counter, unsigned int target, void* stream_) {
+  g2::wait_counter_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(static_cast<const uint32_t*>(counter), target,
+                                                                            device_error_word());
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+
 }  // namespace nx

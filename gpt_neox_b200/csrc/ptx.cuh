@@ -21,10 +21,18 @@ enum ErrCode : int {
   ERR_PEER_TIMEOUT = 3,   // a bounded wait on a peer's signal ran out
 };
 
-// Wait budget in SM clock cycles (about 2 s at 2 GHz, longer at lower clocks).
+// Default wait budget in SM clock cycles (about 2 s at 2 GHz, longer at lower clocks).  The host can
+// replace it at run time (nx_set_wait_budget_cycles): the error word is the first of four ints, and
+// ints 2..3 hold the budget as one 64-bit value (0 = use the default).
 #ifndef NX_WAIT_BUDGET_CYCLES
 #define NX_WAIT_BUDGET_CYCLES (4000000000LL)
 #endif
+
+__device__ __forceinline__ long long wait_budget(const int* err_word) {
+  long long b = 0;
+  if (err_word != nullptr) b = *reinterpret_cast<const volatile long long*>(err_word + 2);
+  return b > 0 ? b : NX_WAIT_BUDGET_CYCLES;
+}
 
 __device__ __forceinline__ void report_error(int* err_word, int code, int where) {
   if (err_word != nullptr) {
@@ -89,11 +97,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait. Returns false (and records ERR_WAIT_TIMEOUT) if the budget ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err_word, int where) {
   if (mbar_try_wait(bar, parity)) return true;
-  long long t0 = clock64();
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ff) == 0) {
-      if (clock64() - t0 > NX_WAIT_BUDGET_CYCLES) {
+      if (clock64() - t0 > wait_budget(err_word)) {
         report_error(err_word, ERR_WAIT_TIMEOUT, where);
         return false;
       }
@@ -309,11 +317,11 @@ __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
 // Bounded wait until *p >= target (monotone epoch counters; never reset).
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target, int* err_word,
                                              int where) {
-  long long t0 = clock64();
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (static_cast<int32_t>(ld_acquire_sys(p) - target) < 0) {
     if ((++spins & 0xff) == 0) {
-      if (clock64() - t0 > NX_WAIT_BUDGET_CYCLES) {
+      if (clock64() - t0 > wait_budget(err_word)) {
         report_error(err_word, ERR_PEER_TIMEOUT, where);
         return false;
       }

@@ -7,7 +7,12 @@ micro-batches: ``min(stages - stage - 1, M)`` warm-up forwards, then one-forward
 the cool-down backwards.  Only the hidden states cross a stage boundary: the causal mask is rebuilt
 on the receiver instead of being shipped with every micro-batch (the reference sends the dense
 [1,1,s,s] mask along, megatron/model/gpt2_model.py:220-223).  Send and receive of one exchange are
-issued as one batched p2p group so that neighbouring stages never wait on each other's sends.
+issued as one batched p2p group so that neighbouring stages never wait on each other's sends; an
+exchange that only sends is not waited for until the next exchange has been posted, so the compute
+stream runs on while the activation or gradient is in flight.  (Between two stages of one NVSwitch
+node a transfer of the sequence-parallel shard takes tens of microseconds against milliseconds of
+compute per micro-batch: the cost of the schedule is its (stages - 1) / (micro-batches + stages - 1)
+bubble, not the transfers.)
 """
 from __future__ import annotations
 
@@ -48,6 +53,7 @@ class PipelineEngine(Engine):
         self._recv_meta = None          # (shape, dtype) of the activation arriving from the previous stage
         self._sent_meta = False
         self.first_output_send = True
+        self._pending_sends = []         # (requests, tensors) of send-only exchanges not waited for yet
         self.pipe_recv_buf = None
         self.is_pipe_parallel = True
         self._needs_mask = any(t not in ("flash", "rwkv", "mamba") for t in (neox_args.attention_config or []))
@@ -102,11 +108,13 @@ class PipelineEngine(Engine):
         meta[1] = _DTYPES.index(t.dtype)
         for i, s in enumerate(t.shape):
             meta[2 + i] = s
-        dist.send(meta, dst)
+        for req in dist.batch_isend_irecv([dist.P2POp(dist.isend, meta, dst)]):     # batched: same NCCL path as the
+            req.wait()                                                              # tensors, no lone send / recv
 
     def _recv_meta_from(self, src):
         meta = torch.zeros(8, dtype=torch.int64, device=self._device())
-        dist.recv(meta, src)
+        for req in dist.batch_isend_irecv([dist.P2POp(dist.irecv, meta, src)]):
+            req.wait()
         meta = meta.tolist()
         return tuple(meta[2:2 + meta[0]]), _DTYPES[meta[1]]
 
@@ -134,9 +142,24 @@ class PipelineEngine(Engine):
             from_next = torch.empty(self._out_shape, dtype=self._out_dtype, device=self._device())
             ops.append(dist.P2POp(dist.irecv, from_next, self.next_rank))
         if ops:
-            for req in dist.batch_isend_irecv(ops):
-                req.wait()
+            reqs = dist.batch_isend_irecv(ops)
+            # requests of earlier send-only groups are settled after the new operations are posted (so a
+            # neighbour that is waiting for this rank's receive is never kept waiting by them)
+            self._settle_sends()
+            if from_prev is None and from_next is None:
+                # nothing arrives in this group: the compute stream does not wait for the send to finish; the
+                # tensors stay referenced until the request is settled at the next exchange
+                self._pending_sends.append((reqs, [op.tensor for op in ops]))
+            else:
+                for req in reqs:
+                    req.wait()
         return from_prev, from_next
+
+    def _settle_sends(self):
+        pending, self._pending_sends = self._pending_sends, []
+        for reqs, _tensors in pending:
+            for req in reqs:
+                req.wait()
 
     # ------------------------------------------------------------------ one micro-batch
     def _forward_micro(self, recv, data_iter, losses, keep_logits=None):
@@ -207,6 +230,7 @@ class PipelineEngine(Engine):
             _, out_grad = self._exchange(recv_next=True)
             in_grad = self._backward_micro(inp0, out0, out_grad)
             self._exchange(send_prev=in_grad)
+        self._settle_sends()
         self._sync_tied_grads()
         self.micro_steps += M - 1          # _take_model_step is the boundary micro-step
         self.micro_steps += 1
@@ -232,6 +256,7 @@ class PipelineEngine(Engine):
                 recv, _ = self._exchange(recv_prev=True)
                 _, out = self._forward_micro(recv, data_iter, losses, keep_logits=logits if return_logits else None)
                 self._exchange(send_next=None if self.is_last_stage() else out)
+        self._settle_sends()
         if was_training:
             self.module.train()
         self._forget_shapes()

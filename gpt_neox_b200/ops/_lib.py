@@ -38,6 +38,9 @@ def _declare(lib):
     sig("nx_read_device_error", [I])
     sig("nx_poison_device_error", [I])
     sig("nx_sm_count", [])
+    sig("nx_set_wait_budget_cycles", [L])
+    sig("nx_mbar_timeout_probe", [P, P])
+    sig("nx_wait_counter", [P, C.c_uint, P])
     sig("nx_abi_version", [])
     sig("nx_gemm_bf16", [P, P, P, I, I, I, L, L, L, I, I, P, P, P, P, L, I, F, P])
     sig("nx_gemm2_bf16", [P, P, P, I, I, I, L, L, L, I, I, P, P, P, P, L, I, F, P])
@@ -127,6 +130,12 @@ def stream():
 
 def read_device_error(clear: bool = True) -> int:
     return int(lib().nx_read_device_error(1 if clear else 0))
+
+
+def set_wait_budget_cycles(cycles: int):
+    """Cycle budget of every bounded wait (mbarrier / flag) in kernels launched afterwards on the current
+    device; 0 restores the built-in default (4e9 cycles, about two seconds)."""
+    check(lib().nx_set_wait_budget_cycles(int(cycles)), "nx_set_wait_budget_cycles")
 
 
 def raise_on_device_error():

@@ -102,3 +102,43 @@ def test_device_error_word_becomes_an_exception():
     assert _lib.read_device_error() == 0      # cleared by the read so the context stays usable
     y = torch.ones(8, device="cuda").sum().item()
     assert y == 8
+
+
+@pytest.mark.gpu
+def test_bounded_waits_run_out_return_and_leave_the_context_usable():
+    """With a ~1 ms budget, a flag wait on a counter nobody increments and an mbarrier wait nobody arrives on
+    both give up: the kernels return, the error word names the code and the site, and after it is cleared an
+    ordinary GEMM gives the right answer.  Nothing stalls: each wait ends by itself after its budget."""
+    import ctypes as C
+    from gpt_neox_b200.ops import _lib
+    from gpt_neox_b200.ops.gemm import linear
+    L = _lib.lib()
+    torch.zeros(1, device="cuda")
+    assert _lib.read_device_error() == 0
+    _lib.set_wait_budget_cycles(2_000_000)                    # about 1 ms at the clocks seen under load
+    try:
+        counter = torch.zeros(4, dtype=torch.int32, device="cuda")
+        _lib.check(L.nx_wait_counter(_lib.ptr(counter), C.c_uint(5), _lib.stream()), "nx_wait_counter")
+        torch.cuda.synchronize()
+        v = _lib.read_device_error(clear=True)
+        assert (v & 0xff, v >> 8) == (3, 20), hex(v)          # ERR_PEER_TIMEOUT at the delivery-counter wait
+        out = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+        _lib.check(L.nx_mbar_timeout_probe(_lib.ptr(out), _lib.stream()), "nx_mbar_timeout_probe")
+        torch.cuda.synchronize()
+        v = _lib.read_device_error(clear=True)
+        assert (v & 0xff, v >> 8) == (1, 21), hex(v)          # ERR_WAIT_TIMEOUT at the probe's mbarrier
+        assert int(out.item()) == 0                           # the wait reported failure to its caller
+        # a counter that is already there does not time out
+        counter.fill_(5)
+        _lib.check(L.nx_wait_counter(_lib.ptr(counter), C.c_uint(5), _lib.stream()), "nx_wait_counter")
+        torch.cuda.synchronize()
+        assert _lib.read_device_error() == 0
+    finally:
+        _lib.set_wait_budget_cycles(0)
+    torch.manual_seed(0)
+    x = torch.randn(512, 256, device="cuda").to(torch.bfloat16)
+    w = torch.randn(384, 256, device="cuda").to(torch.bfloat16)
+    y = linear(x, w)
+    ref = x.float() @ w.float().t()
+    assert ((y.float() - ref).abs().max() / ref.abs().max()).item() < 1e-2
+    assert _lib.read_device_error() == 0

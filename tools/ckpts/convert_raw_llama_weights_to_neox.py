@@ -1,0 +1,13 @@
+#!/usr/bin/env python
+"""Raw LLaMA weights (consolidated.NN.pth) -> NeoX checkpoint files.
+
+Forwards its command line to ``python -m gpt_neox_b200.ckpt.convert raw-llama-to-neox`` (reference script: tools/ckpts/convert_raw_llama_weights_to_neox.py)."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from gpt_neox_b200.ckpt.convert import main  # noqa: E402
+
+if __name__ == "__main__":
+    main(["raw-llama-to-neox"] + sys.argv[1:])
