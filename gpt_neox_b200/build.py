@@ -48,16 +48,22 @@ def _stale(target: Path, deps) -> bool:
     return any(Path(d).stat().st_mtime > t for d in deps)
 
 
-def _compile_one(src: Path, headers, force: bool, verbose: bool):
-    obj = OBJ / (src.stem + ".o")
+#: sources without 16-bit tensor code: compiled once.  Every other .cu file is compiled twice, for bf16 and
+#: (``-DNX_HALF``: namespace nxh, exported symbols ``nx_*_f16``) for fp16.
+SINGLE_BUILD = {"common.cu", "colsum_noalloc.cu"}
+
+
+def _compile_one(src: Path, headers, force: bool, verbose: bool, half: bool = False):
+    stem = src.stem + ("_f16" if half else "")
+    obj = OBJ / (stem + ".o")
     if not force and not _stale(obj, [src, *headers]):
         return obj, ""
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *(["-DNX_HALF"] if half else []), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
     log = r.stderr
-    (OBJ / (src.stem + ".ptxas.log")).write_text(log)
+    (OBJ / (stem + ".ptxas.log")).write_text(log)
     if verbose:
         print(log)
     return obj, log
@@ -68,8 +74,9 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     LIB.mkdir(parents=True, exist_ok=True)
     srcs = sorted(CSRC.glob("*.cu"))
     headers = sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")))
+    jobs = [(s, False) for s in srcs] + [(s, True) for s in srcs if s.name not in SINGLE_BUILD]
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
-        objs = [o for o, _ in ex.map(lambda s: _compile_one(s, headers, force, verbose), srcs)]
+        objs = [o for o, _ in ex.map(lambda j: _compile_one(j[0], headers, force, verbose, j[1]), jobs)]
     out = LIB / "libneox_b200.so"
     if force or _stale(out, objs):
         cmd = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a",

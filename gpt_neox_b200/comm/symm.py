@@ -29,19 +29,19 @@ def _declare():
         return L
     P, I, LL, U, ULL = C.c_void_p, C.c_int, C.c_longlong, C.c_uint, C.c_ulonglong
     PP = C.POINTER(C.c_ulonglong)
-    L.nx_comm_flag_bytes.restype = I
-    L.nx_comm_allreduce.argtypes = [PP, ULL, I, I, LL, LL, I, U, P]
-    L.nx_comm_reduce_scatter.argtypes = [PP, ULL, I, I, LL, LL, P, I, U, P]
-    L.nx_comm_allgather.argtypes = [PP, ULL, I, I, LL, LL, P, U, P]
-    L.nx_gemm_bf16_comm.argtypes = [P, P, P, I, I, I, LL, LL, LL, I, P, P, P, P, LL, I, I, I, I, U, PP, PP, P, LL,
-                                    P, LL, P]
-    L.nx_gemm2_bf16_comm.argtypes = L.nx_gemm_bf16_comm.argtypes
-    L.nx_gemm2_bf16_allreduce.argtypes = [P, P, I, I, I, LL, LL, I, P, P, LL, I, I, I, U, PP, PP, PP, PP, U, P]
-    L.nx_gemm2_bf16_allreduce.restype = I
-    L.nx_gemm_grid.argtypes = [I, I]
-    for n in ("nx_comm_allreduce", "nx_comm_reduce_scatter", "nx_comm_allgather", "nx_gemm_bf16_comm",
-              "nx_gemm2_bf16_comm", "nx_gemm_grid"):
-        getattr(L, n).restype = I
+    gemm_comm = [P, P, P, I, I, I, LL, LL, LL, I, P, P, P, P, LL, I, I, I, I, U, PP, PP, P, LL, P, LL, P]
+    sigs = {"nx_comm_flag_bytes": [], "nx_comm_allreduce": [PP, ULL, I, I, LL, LL, I, U, P],
+            "nx_comm_reduce_scatter": [PP, ULL, I, I, LL, LL, P, I, U, P],
+            "nx_comm_allgather": [PP, ULL, I, I, LL, LL, P, U, P],
+            "nx_gemm_bf16_comm": gemm_comm, "nx_gemm2_bf16_comm": gemm_comm,
+            "nx_gemm2_bf16_allreduce": [P, P, I, I, I, LL, LL, I, P, P, LL, I, I, I, U, PP, PP, PP, PP, U, P],
+            "nx_gemm_grid": [I, I],
+            "nx_comm_zero_reduce_scatter": [PP, I, I, LL, LL, I, I, U, P],
+            "nx_comm_zero_all_gather": [PP, I, I, LL, LL, I, U, P]}
+    for name, argtypes in sigs.items():
+        for nm in (name, name + "_f16"):            # the bf16 build and the fp16 build of every entry point
+            fn = getattr(L, nm)
+            fn.argtypes, fn.restype = argtypes, I
     L._comm_declared = True
     return L
 
@@ -109,8 +109,8 @@ class SymmBackend:
         par = self.ag_calls & 1
         self.ag_calls += 1
         goff = self.gather_off[par]
-        gathered = self.buf[goff:goff + m * k * 2].view(torch.bfloat16).view(m, k)
-        out = torch.empty((m, n), device=x_shard.device, dtype=torch.bfloat16)
+        gathered = self.buf[goff:goff + m * k * 2].view(x_shard.dtype).view(m, k)
+        out = torch.empty((m, n), device=x_shard.device, dtype=x_shard.dtype)
         flags = 0
         ld_aux = 0
         if bias is not None:
@@ -124,7 +124,7 @@ class SymmBackend:
             ld_aux = dgelu_aux.stride(0)
         epoch = self._next_epoch(1)
         LAUNCHES["n"] += 1
-        _lib.check(self._comm_gemm(m)(
+        _lib.check(self._comm_gemm(m, x_shard)(
             _lib.ptr(gathered), _lib.ptr(w), _lib.ptr(out), m, n, k, k, w.stride(0), out.stride(0), int(trans_b),
             _lib.ptr(bias), _lib.ptr(dgelu_aux), _lib.ptr(aux_out), None, ld_aux, flags, 2, self.me, self.ws, epoch,
             self._table(goff), self._table(self.ag_flag_off), None, 0, _lib.ptr(x_shard), x_shard.stride(0),
@@ -138,7 +138,7 @@ class SymmBackend:
         n = w.shape[1] if trans_b else w.shape[0]
         par = self.rs_calls & 1
         self.rs_calls += 1
-        out = torch.empty((m // self.ws, n), device=a.device, dtype=torch.bfloat16)
+        out = torch.empty((m // self.ws, n), device=a.device, dtype=a.dtype)
         flags = 0
         ld_aux = 0
         if bias is not None:
@@ -152,7 +152,7 @@ class SymmBackend:
             ld_aux = dgelu_aux.stride(0)
         epoch = self._next_epoch(1)
         LAUNCHES["n"] += 1
-        _lib.check(self._comm_gemm(m)(
+        _lib.check(self._comm_gemm(m, a)(
             _lib.ptr(a), _lib.ptr(w), _lib.ptr(out), m, n, k, a.stride(0), w.stride(0), out.stride(0), int(trans_b),
             _lib.ptr(bias), _lib.ptr(dgelu_aux), None, _lib.ptr(residual), ld_aux, flags, 1, self.me, self.ws, epoch,
             self._table(self.stage_off[par]), self._table(self.rs_flag_off), _lib.ptr(residual2),
@@ -176,7 +176,7 @@ class SymmBackend:
         par = self.ar_calls & 1
         self.ar_calls += 1
         ooff = self.gather_off[par]
-        out = self.buf[ooff:ooff + m * n * 2].view(torch.bfloat16).view(m, n)
+        out = self.buf[ooff:ooff + m * n * 2].view(a.dtype).view(m, n)
         flags, ld_aux = 0, 0
         if bias is not None:
             flags |= G.EPI_BIAS
@@ -187,21 +187,22 @@ class SymmBackend:
         self.ar_target = (self.ar_target + (self.ws - 1) * tiles * 8) & 0xFFFFFFFF
         epoch = self._next_epoch(1)
         LAUNCHES["n"] += 2
-        _lib.check(_lib.lib().nx_gemm2_bf16_allreduce(
+        _lib.check(_lib.lib(a).nx_gemm2_bf16_allreduce(
             _lib.ptr(a), _lib.ptr(w), m, n, k, a.stride(0), w.stride(0), int(trans_b), _lib.ptr(bias),
             _lib.ptr(residual), ld_aux, flags, self.me, self.ws, epoch, self._table(self.stage_off[par]),
             self._table(self.rs_flag_off), self._table(ooff), self._table(self.ar_count_off), self.ar_target,
             _lib.stream()), "nx_gemm2_bf16_allreduce")
         return out
 
-    def _comm_gemm(self, m_full: int):
-        """CTA-pair kernel (256-row tiles) when the rank chunks are whole 256-row tiles, else the 128-row kernel."""
+    def _comm_gemm(self, m_full: int, like):
+        """CTA-pair kernel (256-row tiles) when the rank chunks are whole 256-row tiles, else the 128-row kernel;
+        the bf16 or the fp16 build by the dtype of ``like``."""
         from ..ops.gemm import PAIR_GEMM
-        L = _lib.lib()
+        L = _lib.lib(like)
         return L.nx_gemm2_bf16_comm if (PAIR_GEMM["on"] and m_full % (self.ws * 256) == 0) else L.nx_gemm_bf16_comm
 
     def supports(self, x: torch.Tensor) -> bool:
-        return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and x.is_contiguous()
+        return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16, torch.float32) and x.is_contiguous()
                 and (x.numel() * x.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0)
 
     def _next_epoch(self, n=2):
@@ -220,8 +221,8 @@ class SymmBackend:
         stage = self._view(nb, x.dtype, x.shape)
         stage.copy_(x)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_comm_allreduce(self.ptrs, self.mc, self.me, self.ws, self.coll_off, nb,
-                                                0 if x.dtype == torch.bfloat16 else 1, self._next_epoch(),
+        _lib.check(_lib.lib(x).nx_comm_allreduce(self.ptrs, self.mc, self.me, self.ws, self.coll_off, nb,
+                                                1 if x.dtype == torch.float32 else 0, self._next_epoch(),
                                                 _lib.stream()), "nx_comm_allreduce")
         x.copy_(stage)
         return x
@@ -236,8 +237,8 @@ class SymmBackend:
         self._view(nb, x.dtype, x.shape).copy_(x)
         out = torch.empty((x.shape[0] // self.ws,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_comm_reduce_scatter(self.ptrs, self.mc, self.me, self.ws, self.coll_off, shard, _lib.ptr(out),
-                                                     0 if x.dtype == torch.bfloat16 else 1, self._next_epoch(),
+        _lib.check(_lib.lib(x).nx_comm_reduce_scatter(self.ptrs, self.mc, self.me, self.ws, self.coll_off, shard, _lib.ptr(out),
+                                                     1 if x.dtype == torch.float32 else 0, self._next_epoch(),
                                                      _lib.stream()), "nx_comm_reduce_scatter")
         return out
 
@@ -280,9 +281,6 @@ class ZeroWorkspace:
         L = _declare()
         P, I, LL, U = C.c_void_p, C.c_int, C.c_longlong, C.c_uint
         PP = C.POINTER(C.c_ulonglong)
-        L.nx_comm_zero_reduce_scatter.argtypes = [PP, I, I, LL, LL, I, I, U, P]
-        L.nx_comm_zero_all_gather.argtypes = [PP, I, I, LL, LL, I, U, P]
-        L.nx_comm_zero_reduce_scatter.restype = L.nx_comm_zero_all_gather.restype = I
         self.group, self.ws, self.me = group, dist.get_world_size(group), dist.get_rank(group)
         self.flag_bytes = L.nx_comm_flag_bytes()
         al = lambda n: (n + 4095) // 4096 * 4096
@@ -314,9 +312,9 @@ class ZeroWorkspace:
     def reduce_scatter_grads(self, dtype):
         """Sum the gradient buffers of all ranks; rank r ends up with the sum in its chunk r (in place)."""
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_comm_zero_reduce_scatter(self.ptrs, self.me, self.ws, self.grad_off,
+        _lib.check(_lib.lib(dtype).nx_comm_zero_reduce_scatter(self.ptrs, self.me, self.ws, self.grad_off,
                                                           self.grad_bytes // self.ws,
-                                                          0 if dtype == torch.bfloat16 else 1, self.grid, self._next(),
+                                                          1 if dtype == torch.float32 else 0, self.grid, self._next(),
                                                           _lib.stream()), "nx_comm_zero_reduce_scatter")
 
     def all_gather_params(self):

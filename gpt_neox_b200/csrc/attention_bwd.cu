@@ -28,7 +28,7 @@ struct AttnBwdParams {
   const float* lse;    // [B,H,Sq_pad] base-2 log-sum-exp, +inf in the padding
   const float* delta;  // [B,H,Sq_pad], 0 in the padding
   const float* alibi;
-  __nv_bfloat16 *dq, *dk, *dv;
+  h16 *dq, *dk, *dv;
   long long dq_sb, dq_sh, dq_ss, dk_sb, dk_sh, dk_ss, dv_sb, dv_sh, dv_ss;
   int B, H, Hk, Sq, Sk, D, Sq_pad;
   float scale, scale_log2;
@@ -37,8 +37,8 @@ struct AttnBwdParams {
 };
 
 // delta = rowsum(O * dO); one warp per (b, h, q) row.
-__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
-                                  const __nv_bfloat16* __restrict__ dO, float* __restrict__ delta,
+__global__ void attn_delta_kernel(const h16* __restrict__ o,
+                                  const h16* __restrict__ dO, float* __restrict__ delta,
                                   int B, int H, int Sq, int Sq_pad, int D, long long o_sb, long long o_sh,
                                   long long o_ss, long long d_sb, long long d_sh, long long d_ss) {
   const long long row = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -48,12 +48,12 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
   const int q = static_cast<int>(row % Sq);
   const int h = static_cast<int>((row / Sq) % H);
   const int b = static_cast<int>(row / (static_cast<long long>(Sq) * H));
-  const __nv_bfloat16* op = o + b * o_sb + h * o_sh + q * o_ss;
-  const __nv_bfloat16* dp = dO + b * d_sb + h * d_sh + q * d_ss;
+  const h16* op = o + b * o_sb + h * o_sh + q * o_ss;
+  const h16* dp = dO + b * d_sb + h * d_sh + q * d_ss;
   float s = 0.f;
   for (int d = lane * 2; d < D; d += 64) {
-    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(op + d));
-    const float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dp + d));
+    const float2 a = unpack_h16x2(*reinterpret_cast<const uint32_t*>(op + d));
+    const float2 g = unpack_h16x2(*reinterpret_cast<const uint32_t*>(dp + d));
     s += a.x * g.x + a.y * g.y;
   }
   s = warp_sum(s);
@@ -64,7 +64,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
 // load per lane and tensor, so a warp covers 32 / (D/8) rows per pass (the scalar-pair form above moves
 // 4 bytes per lane and load).
 template <int LPR>   // lanes per row = D / 8, a power of two
-__global__ void attn_delta_vec8_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dO,
+__global__ void attn_delta_vec8_kernel(const h16* __restrict__ o, const h16* __restrict__ dO,
                                        float* __restrict__ delta, int B, int H, int Sq, int Sq_pad, long long o_sb,
                                        long long o_sh, long long o_ss, long long d_sb, long long d_sh,
                                        long long d_ss) {
@@ -86,7 +86,7 @@ __global__ void attn_delta_vec8_kernel(const __nv_bfloat16* __restrict__ o, cons
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      const float2 x = unpack_bf16x2(aw[k]), y = unpack_bf16x2(gw[k]);
+      const float2 x = unpack_h16x2(aw[k]), y = unpack_h16x2(gw[k]);
       s += x.x * y.x + x.y * y.y;
     }
   }
@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
             // the softmax scale of dS is applied once, to dQ, in the epilogue
             const float p0 = exp2f(fmaf(__uint_as_float(sv[j]), p.scale_log2, -lse2));
             const float p1 = exp2f(fmaf(__uint_as_float(sv[j + 1]), p.scale_log2, -lse2));
-            pk[j >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[j]) - delta),
+            pk[j >> 1] = pack_h16x2(p0 * (__uint_as_float(dv[j]) - delta),
                                      p1 * (__uint_as_float(dv[j + 1]) - delta));
           }
         } else {
@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
               if (idx < lo || idx > hi) pr = 0.f;
               ds[e] = pr * (__uint_as_float(dv[j + e]) - delta);
             }
-            pk[j >> 1] = pack_bf16x2(ds[0], ds[1]);
+            pk[j >> 1] = pack_h16x2(ds[0], ds[1]);
           }
         }
         tmem_st_32x32b_x16(T_DS + st * 64 + c * 16 + lane_off, pk);
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       tc_fence_after_sync();
     }
     if (!aborted) {
-      __nv_bfloat16* orow = p.dq + batch * p.dq_sb + head * p.dq_sh + static_cast<long long>(qi) * p.dq_ss;
+      h16* orow = p.dq + batch * p.dq_sb + head * p.dq_sh + static_cast<long long>(qi) * p.dq_ss;
 #pragma unroll 1
       for (int c = 0; c < DP / 32; ++c) {
         uint32_t ov[32];
@@ -319,10 +319,10 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
             if (c * 32 + j < p.D) {
               const float sc = p.scale;
               uint4 o4;
-              o4.x = pack_bf16x2(__uint_as_float(ov[j]) * sc, __uint_as_float(ov[j + 1]) * sc);
-              o4.y = pack_bf16x2(__uint_as_float(ov[j + 2]) * sc, __uint_as_float(ov[j + 3]) * sc);
-              o4.z = pack_bf16x2(__uint_as_float(ov[j + 4]) * sc, __uint_as_float(ov[j + 5]) * sc);
-              o4.w = pack_bf16x2(__uint_as_float(ov[j + 6]) * sc, __uint_as_float(ov[j + 7]) * sc);
+              o4.x = pack_h16x2(__uint_as_float(ov[j]) * sc, __uint_as_float(ov[j + 1]) * sc);
+              o4.y = pack_h16x2(__uint_as_float(ov[j + 2]) * sc, __uint_as_float(ov[j + 3]) * sc);
+              o4.z = pack_h16x2(__uint_as_float(ov[j + 4]) * sc, __uint_as_float(ov[j + 5]) * sc);
+              o4.w = pack_h16x2(__uint_as_float(ov[j + 6]) * sc, __uint_as_float(ov[j + 7]) * sc);
               *reinterpret_cast<uint4*>(orow + c * 32 + j) = o4;
             }
           }
@@ -474,10 +474,10 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
               pr[e] = exp2f(fmaf(__uint_as_float(sv[j + e]), p.scale_log2, -lq[e]));
               ds[e] = pr[e] * (__uint_as_float(dv[j + e]) - dq_[e]);     // softmax scale: once, on dK, in the epilogue
             }
-            pp[j >> 1] = pack_bf16x2(pr[0], pr[1]);
-            pp[(j >> 1) + 1] = pack_bf16x2(pr[2], pr[3]);
-            pd[j >> 1] = pack_bf16x2(ds[0], ds[1]);
-            pd[(j >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
+            pp[j >> 1] = pack_h16x2(pr[0], pr[1]);
+            pp[(j >> 1) + 1] = pack_h16x2(pr[2], pr[3]);
+            pd[j >> 1] = pack_h16x2(ds[0], ds[1]);
+            pd[(j >> 1) + 1] = pack_h16x2(ds[2], ds[3]);
           }
         } else {
 #pragma unroll
@@ -495,10 +495,10 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
               if (idx < lo || idx > hi) pr[e] = 0.f;
               ds[e] = pr[e] * (__uint_as_float(dv[j + e]) - dq_[e]);
             }
-            pp[j >> 1] = pack_bf16x2(pr[0], pr[1]);
-            pp[(j >> 1) + 1] = pack_bf16x2(pr[2], pr[3]);
-            pd[j >> 1] = pack_bf16x2(ds[0], ds[1]);
-            pd[(j >> 1) + 1] = pack_bf16x2(ds[2], ds[3]);
+            pp[j >> 1] = pack_h16x2(pr[0], pr[1]);
+            pp[(j >> 1) + 1] = pack_h16x2(pr[2], pr[3]);
+            pd[j >> 1] = pack_h16x2(ds[0], ds[1]);
+            pd[(j >> 1) + 1] = pack_h16x2(ds[2], ds[3]);
           }
         }
         tmem_st_32x32b_x16(T_ST + c * 16 + lane_off, pp);
@@ -517,10 +517,10 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const uint32_t T = which == 0 ? T_DK : T_DV;
-        __nv_bfloat16* base = which == 0 ? p.dk : p.dv;
+        h16* base = which == 0 ? p.dk : p.dv;
         const long long sb = which == 0 ? p.dk_sb : p.dv_sb, sh = which == 0 ? p.dk_sh : p.dv_sh,
                         ss = which == 0 ? p.dk_ss : p.dv_ss;
-        __nv_bfloat16* orow = base + batch * sb + kv_head * sh + static_cast<long long>(kcol) * ss;
+        h16* orow = base + batch * sb + kv_head * sh + static_cast<long long>(kcol) * ss;
 #pragma unroll 1
         for (int c = 0; c < DP / 32; ++c) {
           uint32_t ov[32];
@@ -537,10 +537,10 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
               if (c * 32 + j < p.D) {
                 const float sc = which == 0 ? p.scale : 1.f;     // dK carries the softmax scale of dS
                 uint4 o4;
-                o4.x = pack_bf16x2(__uint_as_float(ov[j]) * sc, __uint_as_float(ov[j + 1]) * sc);
-                o4.y = pack_bf16x2(__uint_as_float(ov[j + 2]) * sc, __uint_as_float(ov[j + 3]) * sc);
-                o4.z = pack_bf16x2(__uint_as_float(ov[j + 4]) * sc, __uint_as_float(ov[j + 5]) * sc);
-                o4.w = pack_bf16x2(__uint_as_float(ov[j + 6]) * sc, __uint_as_float(ov[j + 7]) * sc);
+                o4.x = pack_h16x2(__uint_as_float(ov[j]) * sc, __uint_as_float(ov[j + 1]) * sc);
+                o4.y = pack_h16x2(__uint_as_float(ov[j + 2]) * sc, __uint_as_float(ov[j + 3]) * sc);
+                o4.z = pack_h16x2(__uint_as_float(ov[j + 4]) * sc, __uint_as_float(ov[j + 5]) * sc);
+                o4.w = pack_h16x2(__uint_as_float(ov[j + 6]) * sc, __uint_as_float(ov[j + 7]) * sc);
                 *reinterpret_cast<uint4*>(orow + c * 32 + j) = o4;
               }
             }
@@ -593,7 +593,7 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 // Views as in nx_flash_attn_fwd (element strides batch, head, seq).  delta: fp32 scratch [B,H,Sq]
 // provided by the caller.  dq/dk/dv: bf16 strided outputs, fully overwritten.
-NX_API int nx_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dO,
+NX_API int NX_SYM(nx_flash_attn_bwd)(const void* q, const void* k, const void* v, const void* o, const void* dO,
                              const void* lse, void* delta, void* dq, void* dk, void* dv,
                              const void* alibi, int B, int H, int Hk, int Sq, int Sk, int D,
                              long long q_sb, long long q_sh, long long q_ss, long long k_sb,
@@ -625,16 +625,16 @@ NX_API int nx_flash_attn_bwd(const void* q, const void* k, const void* v, const 
       const long long warps = (rows + rpw - 1) / rpw;
       const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
       if (D == 128)
-        attn_delta_vec8_kernel<16><<<grid, wpb * 32, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dO,
+        attn_delta_vec8_kernel<16><<<grid, wpb * 32, 0, s>>>((const h16*)o, (const h16*)dO,
                                                             (float*)delta, B, H, Sq, sq_pad, o_sb, o_sh, o_ss, do_sb,
                                                             do_sh, do_ss);
       else
-        attn_delta_vec8_kernel<8><<<grid, wpb * 32, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dO,
+        attn_delta_vec8_kernel<8><<<grid, wpb * 32, 0, s>>>((const h16*)o, (const h16*)dO,
                                                            (float*)delta, B, H, Sq, sq_pad, o_sb, o_sh, o_ss, do_sb,
                                                            do_sh, do_ss);
     } else {
       attn_delta_kernel<<<(unsigned)((rows + wpb - 1) / wpb), wpb * 32, 0, s>>>(
-          (const __nv_bfloat16*)o, (const __nv_bfloat16*)dO, (float*)delta, B, H, Sq, sq_pad, D, o_sb, o_sh, o_ss,
+          (const h16*)o, (const h16*)dO, (float*)delta, B, H, Sq, sq_pad, D, o_sb, o_sh, o_ss,
           do_sb, do_sh, do_ss);
     }
     NX_LAUNCH_CHECK();
@@ -646,7 +646,7 @@ NX_API int nx_flash_attn_bwd(const void* q, const void* k, const void* v, const 
   if (!bwd_map(&tdo, dO, B, H, Sq, D, do_sb, do_sh, do_ss)) return NX_ERR_ARG;
   AttnBwdParams p;
   p.lse = (const float*)lse; p.delta = (const float*)delta; p.alibi = (const float*)alibi;
-  p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.dq = (h16*)dq; p.dk = (h16*)dk; p.dv = (h16*)dv;
   p.dq_sb = dq_sb; p.dq_sh = dq_sh; p.dq_ss = dq_ss;
   p.dk_sb = dk_sb; p.dk_sh = dk_sh; p.dk_ss = dk_ss;
   p.dv_sb = dv_sb; p.dv_sh = dv_sh; p.dv_ss = dv_ss;

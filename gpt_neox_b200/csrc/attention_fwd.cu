@@ -31,7 +31,7 @@ constexpr int ATT_BN = 128;  // keys per block
 constexpr int ATT_THREADS = 320;
 
 struct AttnFwdParams {
-  __nv_bfloat16* o;
+  h16* o;
   float* lse;
   const float* alibi;  // per query head, or null
   int B, H, Hk, Sq, Sk, D, Sq_pad;
@@ -110,9 +110,13 @@ __device__ __forceinline__ float exp2_poly(float x) {
   q = fmaf(q, f, 0.99994826f);
   return __uint_as_float(__float_as_uint(q) + (__float_as_uint(t) << 23));
 }
-// (lo, hi) -> packed bf16x2, round-half-up on the magnitude; inputs finite and non-negative.
-__device__ __forceinline__ uint32_t pack_bf16x2_alu(float lo, float hi) {
+// (lo, hi) -> packed 16-bit pair (bf16: round-half-up on the magnitude; inputs finite and non-negative.
+__device__ __forceinline__ uint32_t pack_h16x2_alu(float lo, float hi) {
+#ifdef NX_HALF
+  return pack_h16x2(lo, hi);      // the byte-permute trick only holds for bf16 (the top half of an fp32)
+#else
   return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+#endif
 }
 
 // EXPV: 0 = every exp2 on the MUFU unit, convert instruction for the packing (default: fastest as measured,
@@ -354,7 +358,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
           const float p0 = exp2f(x0);
           const float p1 = EXPV == 2 ? exp2_poly(x1) : exp2f(x1);
           rs[(j >> 1) & 3] += p0 + p1;
-          pk[j >> 1] = EXPV == 0 ? pack_bf16x2(p0, p1) : pack_bf16x2_alu(p0, p1);
+          pk[j >> 1] = EXPV == 0 ? pack_h16x2(p0, p1) : pack_h16x2_alu(p0, p1);
         }
         tmem_st_32x32b_x16(T_P + st * 64 + half * 32 + c * 16 + lane_off, pk);
       }
@@ -383,7 +387,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     if (!aborted) {
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
       const bool row_ok = qi < p.Sq;
-      __nv_bfloat16* orow = p.o + batch * p.o_sb + head * p.o_sh + static_cast<long long>(qi) * p.o_ss;
+      h16* orow = p.o + batch * p.o_sb + head * p.o_sh + static_cast<long long>(qi) * p.o_ss;
 #pragma unroll 1
       for (int c = half * (DP / 64); c < (half + 1) * (DP / 64); ++c) {
         uint32_t ov[32];
@@ -399,10 +403,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
           for (int j = 0; j < 32; j += 8) {
             if (c * 32 + j < p.D) {
               uint4 o4;
-              o4.x = pack_bf16x2(__uint_as_float(ov[j]) * inv_l, __uint_as_float(ov[j + 1]) * inv_l);
-              o4.y = pack_bf16x2(__uint_as_float(ov[j + 2]) * inv_l, __uint_as_float(ov[j + 3]) * inv_l);
-              o4.z = pack_bf16x2(__uint_as_float(ov[j + 4]) * inv_l, __uint_as_float(ov[j + 5]) * inv_l);
-              o4.w = pack_bf16x2(__uint_as_float(ov[j + 6]) * inv_l, __uint_as_float(ov[j + 7]) * inv_l);
+              o4.x = pack_h16x2(__uint_as_float(ov[j]) * inv_l, __uint_as_float(ov[j + 1]) * inv_l);
+              o4.y = pack_h16x2(__uint_as_float(ov[j + 2]) * inv_l, __uint_as_float(ov[j + 3]) * inv_l);
+              o4.z = pack_h16x2(__uint_as_float(ov[j + 4]) * inv_l, __uint_as_float(ov[j + 5]) * inv_l);
+              o4.w = pack_h16x2(__uint_as_float(ov[j + 6]) * inv_l, __uint_as_float(ov[j + 7]) * inv_l);
               *reinterpret_cast<uint4*>(orow + c * 32 + j) = o4;
             }
           }
@@ -443,7 +447,7 @@ static bool attn_map(CUtensorMap* m, const void* base, int B, int Hh, int S, int
 // sequence; head dim contiguous); lse: fp32 [B,H,Sq_pad] (Sq rounded up to 128), receives the
 // base-2 log-sum-exp of the scaled scores for rows < Sq (the caller pre-fills it with +inf).  alibi: fp32 [H] or null.
 // window < 0: no sliding window.  D % 8 == 0, D <= 128.
-NX_API int nx_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, void* lse,
+NX_API int NX_SYM(nx_flash_attn_fwd)(const void* q, const void* k, const void* v, void* o, void* lse,
                              const void* alibi, int B, int H, int Hk, int Sq, int Sk, int D,
                              long long q_sb, long long q_sh, long long q_ss, long long k_sb,
                              long long k_sh, long long k_ss, long long v_sb, long long v_sh,
@@ -462,7 +466,7 @@ NX_API int nx_flash_attn_fwd(const void* q, const void* k, const void* v, void* 
   if (!attn_map(&tk, k, B, Hk, Sk, D, k_sb, k_sh, k_ss, ATT_BN)) return NX_ERR_ARG;
   if (!attn_map(&tv, v, B, Hk, Sk, D, v_sb, v_sh, v_ss, ATT_BN)) return NX_ERR_ARG;
   AttnFwdParams p;
-  p.o = (__nv_bfloat16*)o; p.lse = (float*)lse; p.alibi = (const float*)alibi;
+  p.o = (h16*)o; p.lse = (float*)lse; p.alibi = (const float*)alibi;
   p.B = B; p.H = H; p.Hk = Hk; p.Sq = Sq; p.Sk = Sk; p.D = D;
   p.Sq_pad = (Sq + ATT_BM - 1) / ATT_BM * ATT_BM;
   p.o_sb = o_sb; p.o_sh = o_sh; p.o_ss = o_ss;

@@ -16,8 +16,8 @@ constexpr int COLS = 64;  // columns per block
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
   const uint4 u = *reinterpret_cast<const uint4*>(p);
-  const float2 a = nx::unpack_bf16x2(u.x), b = nx::unpack_bf16x2(u.y), c = nx::unpack_bf16x2(u.z),
-               d = nx::unpack_bf16x2(u.w);
+  const float2 a = nx::unpack_h16x2(u.x), b = nx::unpack_h16x2(u.y), c = nx::unpack_h16x2(u.z),
+               d = nx::unpack_h16x2(u.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
 
@@ -103,7 +103,8 @@ float* scratch_for_current_device(int* status) {
 
 extern "C" __attribute__((visibility("default"))) int nx_colsum_bf16_noalloc(
     const void* x, void* out_f32, long long rows, int N, long long ld, int accumulate, void* stream_) {
-  NX_REQUIRE(x != nullptr && out_f32 != nullptr, "colsum_noalloc: null input or output");
+  // an empty input (rows == 0) may come with a null pointer: the sums are then all zero
+  NX_REQUIRE((x != nullptr || rows == 0) && out_f32 != nullptr, "colsum_noalloc: null input or output");
   NX_REQUIRE(rows >= 0 && N >= 0, "colsum_noalloc: negative size");
   NX_REQUIRE(N % 8 == 0 && ld % 8 == 0 && ld >= N, "colsum_noalloc: N and ld must be multiples of 8, ld >= N");
   NX_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0, "colsum_noalloc: x must be 16-byte aligned");

@@ -44,14 +44,14 @@ __device__ __forceinline__ float4 add4(float4 a, float4 b) {
   return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
 }
 __device__ __forceinline__ void acc_bf16x8(float (&acc)[8], uint4 u) {
-  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  const float2 a = unpack_h16x2(u.x), b = unpack_h16x2(u.y), c = unpack_h16x2(u.z), d = unpack_h16x2(u.w);
   acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
   acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
 }
 __device__ __forceinline__ uint4 pack_acc(const float (&acc)[8]) {
   uint4 o;
-  o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-  o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+  o.x = pack_h16x2(acc[0], acc[1]); o.y = pack_h16x2(acc[2], acc[3]);
+  o.z = pack_h16x2(acc[4], acc[5]); o.w = pack_h16x2(acc[6], acc[7]);
   return o;
 }
 
@@ -227,13 +227,13 @@ static bool fill_table(PeerTable& t, const unsigned long long* ptrs, int ws) {
 
 }  // namespace nx
 
-NX_API int nx_comm_flag_bytes() { return nx::COMM_FLAG_BYTES; }
-NX_API int nx_comm_epochs_per_call() { return 2; }
+NX_API int NX_SYM(nx_comm_flag_bytes)() { return nx::COMM_FLAG_BYTES; }
+NX_API int NX_SYM(nx_comm_epochs_per_call)() { return 2; }
 
 // dtype: 0 = bf16, 1 = fp32.  peer_ptrs: host array of ws workspace base addresses (as mapped here).
 // mc_ptr: NVLS multicast address of the workspace or 0.  epoch: first of the two epochs this call
 // consumes (the caller advances its counter by nx_comm_epochs_per_call()).
-NX_API int nx_comm_allreduce(const unsigned long long* peer_ptrs, unsigned long long mc_ptr, int me, int ws,
+NX_API int NX_SYM(nx_comm_allreduce)(const unsigned long long* peer_ptrs, unsigned long long mc_ptr, int me, int ws,
                              long long payload_off, long long bytes, int dtype, unsigned int epoch, void* stream_) {
   using namespace nx;
   PeerTable t;
@@ -249,7 +249,7 @@ NX_API int nx_comm_allreduce(const unsigned long long* peer_ptrs, unsigned long 
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_comm_reduce_scatter(const unsigned long long* peer_ptrs, unsigned long long mc_ptr, int me, int ws,
+NX_API int NX_SYM(nx_comm_reduce_scatter)(const unsigned long long* peer_ptrs, unsigned long long mc_ptr, int me, int ws,
                                   long long payload_off, long long shard_bytes, void* out, int dtype, unsigned int epoch, void* stream_) {
   using namespace nx;
   PeerTable t;
@@ -265,7 +265,7 @@ NX_API int nx_comm_reduce_scatter(const unsigned long long* peer_ptrs, unsigned 
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_comm_allgather(const unsigned long long* peer_ptrs, unsigned long long mc_ptr, int me, int ws,
+NX_API int NX_SYM(nx_comm_allgather)(const unsigned long long* peer_ptrs, unsigned long long mc_ptr, int me, int ws,
                              long long payload_off, long long shard_bytes, const void* in, unsigned int epoch, void* stream_) {
   using namespace nx;
   PeerTable t;
@@ -279,7 +279,7 @@ NX_API int nx_comm_allgather(const unsigned long long* peer_ptrs, unsigned long 
 
 // In-place ZeRO collectives over buffers inside the symmetric workspace (see the kernels above).
 // grid: every rank must pass the same value (blocks pair up across ranks for the barriers).
-NX_API int nx_comm_zero_reduce_scatter(const unsigned long long* peer_ptrs, int me, int ws, long long payload_off,
+NX_API int NX_SYM(nx_comm_zero_reduce_scatter)(const unsigned long long* peer_ptrs, int me, int ws, long long payload_off,
                                        long long shard_bytes, int dtype, int grid, unsigned int epoch, void* stream_) {
   using namespace nx;
   PeerTable t;
@@ -296,7 +296,7 @@ NX_API int nx_comm_zero_reduce_scatter(const unsigned long long* peer_ptrs, int 
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_comm_zero_all_gather(const unsigned long long* peer_ptrs, int me, int ws, long long payload_off,
+NX_API int NX_SYM(nx_comm_zero_all_gather)(const unsigned long long* peer_ptrs, int me, int ws, long long payload_off,
                                    long long shard_bytes, int grid, unsigned int epoch, void* stream_) {
   using namespace nx;
   PeerTable t;

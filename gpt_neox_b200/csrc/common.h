@@ -41,6 +41,20 @@ bool make_tma_4d(CUtensorMap* map, const void* base, const uint64_t dims[4],
 
 }  // namespace nx
 
+// The kernels that work on 16-bit floating-point tensors are compiled twice from the same sources:
+// once for bf16 (namespace nx, exported symbols nx_*) and once with -DNX_HALF for fp16 (namespace
+// nxh, exported symbols nx_*_f16).  In the second build every `nx` below this point names `nxh`; the
+// host helpers declared above stay shared through the using-directive.
+#ifdef NX_HALF
+namespace nxh {
+using namespace nx;
+}
+#define nx nxh
+#define NX_SYM(name) name##_f16
+#else
+#define NX_SYM(name) name
+#endif
+
 #define NX_CUDA_CHECK(expr)                                                              \
   do {                                                                                   \
     cudaError_t _e = (expr);                                                             \

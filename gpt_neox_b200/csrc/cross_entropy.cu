@@ -27,8 +27,8 @@ __device__ __forceinline__ float ldf(const T* p);
 template <>
 __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
 template <>
-__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) {
-  return __bfloat162float(*p);
+__device__ __forceinline__ float ldf<h16>(const h16* p) {
+  return h16_to_float(*p);
 }
 
 template <typename T>
@@ -42,8 +42,8 @@ __global__ void ce_fwd_kernel(const T* __restrict__ logits, const long long* __r
     const uint4* lv = reinterpret_cast<const uint4*>(lr);
     for (int i = threadIdx.x; i < V / 8; i += blockDim.x) {
       const uint4 u = lv[i];
-      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z),
-                   d = unpack_bf16x2(u.w);
+      const float2 a = unpack_h16x2(u.x), b = unpack_h16x2(u.y), c = unpack_h16x2(u.z),
+                   d = unpack_h16x2(u.w);
       const float mx8 = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(b.x, b.y)),
                               fmaxf(fmaxf(c.x, c.y), fmaxf(d.x, d.y)));
       if (mx8 > m) {
@@ -97,11 +97,11 @@ __global__ void ce_fwd_kernel(const T* __restrict__ logits, const long long* __r
 template <typename T>
 __global__ void ce_bwd_kernel(const T* __restrict__ logits, const long long* __restrict__ labels,
                               const float* __restrict__ lse, const float* __restrict__ gscale,
-                              __nv_bfloat16* __restrict__ dlogits, int V, long long ld,
+                              h16* __restrict__ dlogits, int V, long long ld,
                               long long ld_out, int vocab_start) {
   const long long row = blockIdx.x;
   const T* lr = logits + row * ld;
-  __nv_bfloat16* dr = dlogits + row * ld_out;
+  h16* dr = dlogits + row * ld_out;
   const float l = lse[row], g = gscale[row];
   const long long lab = labels[row] - vocab_start;
   if (sizeof(T) == 2 && (V % 8) == 0 && (ld % 8) == 0 && (ld_out % 8) == 0) {
@@ -113,18 +113,18 @@ __global__ void ce_bwd_kernel(const T* __restrict__ logits, const long long* __r
       uint32_t o[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float2 a = unpack_bf16x2(w[q]);
+        const float2 a = unpack_h16x2(w[q]);
         const int c = i * 8 + q * 2;
         const float p0 = (__expf(a.x - l) - (c == lab ? 1.f : 0.f)) * g;
         const float p1 = (__expf(a.y - l) - (c + 1 == lab ? 1.f : 0.f)) * g;
-        o[q] = pack_bf16x2(p0, p1);
+        o[q] = pack_h16x2(p0, p1);
       }
       dv[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   } else {
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
       const float p = (__expf(ldf<T>(lr + i) - l) - (i == lab ? 1.f : 0.f)) * g;
-      dr[i] = __float2bfloat16(p);
+      dr[i] = float_to_h16(p);
     }
   }
 }
@@ -132,15 +132,15 @@ __global__ void ce_bwd_kernel(const T* __restrict__ logits, const long long* __r
 }  // namespace nx
 
 // dtype: 0 = bf16 logits, 1 = fp32 logits.  stats: float[rows, 3] = (max, sumexp, target logit).
-NX_API int nx_ce_fwd(const void* logits, const void* labels, void* stats, long long rows, int V,
+NX_API int NX_SYM(nx_ce_fwd)(const void* logits, const void* labels, void* stats, long long rows, int V,
                      long long ld, int vocab_start, int dtype, void* stream_) {
   using namespace nx;
   if (rows == 0) return NX_OK;
   NX_REQUIRE(rows < (1ll << 31), "ce: too many rows");
   auto s = (cudaStream_t)stream_;
   if (dtype == 0)
-    ce_fwd_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, s>>>(
-        (const __nv_bfloat16*)logits, (const long long*)labels, (float*)stats, V, ld, vocab_start);
+    ce_fwd_kernel<h16><<<(unsigned)rows, 256, 0, s>>>(
+        (const h16*)logits, (const long long*)labels, (float*)stats, V, ld, vocab_start);
   else
     ce_fwd_kernel<float><<<(unsigned)rows, 256, 0, s>>>((const float*)logits,
                                                         (const long long*)labels, (float*)stats, V,
@@ -148,7 +148,7 @@ NX_API int nx_ce_fwd(const void* logits, const void* labels, void* stats, long l
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_ce_bwd(const void* logits, const void* labels, const void* lse, const void* gscale,
+NX_API int NX_SYM(nx_ce_bwd)(const void* logits, const void* labels, const void* lse, const void* gscale,
                      void* dlogits, long long rows, int V, long long ld, long long ld_out,
                      int vocab_start, int dtype, void* stream_) {
   using namespace nx;
@@ -156,13 +156,13 @@ NX_API int nx_ce_bwd(const void* logits, const void* labels, const void* lse, co
   NX_REQUIRE(rows < (1ll << 31), "ce: too many rows");
   auto s = (cudaStream_t)stream_;
   if (dtype == 0)
-    ce_bwd_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, s>>>(
-        (const __nv_bfloat16*)logits, (const long long*)labels, (const float*)lse,
-        (const float*)gscale, (__nv_bfloat16*)dlogits, V, ld, ld_out, vocab_start);
+    ce_bwd_kernel<h16><<<(unsigned)rows, 256, 0, s>>>(
+        (const h16*)logits, (const long long*)labels, (const float*)lse,
+        (const float*)gscale, (h16*)dlogits, V, ld, ld_out, vocab_start);
   else
     ce_bwd_kernel<float><<<(unsigned)rows, 256, 0, s>>>(
         (const float*)logits, (const long long*)labels, (const float*)lse, (const float*)gscale,
-        (__nv_bfloat16*)dlogits, V, ld, ld_out, vocab_start);
+        (h16*)dlogits, V, ld, ld_out, vocab_start);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }

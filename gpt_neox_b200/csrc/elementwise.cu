@@ -39,25 +39,25 @@ __device__ __forceinline__ float act_grad(int a, float x) {
   }
 }
 
-__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&f)[8]) {
+__device__ __forceinline__ void ld8(const h16* p, float (&f)[8]) {
   const uint4 u = *reinterpret_cast<const uint4*>(p);
-  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z),
-               d = unpack_bf16x2(u.w);
+  const float2 a = unpack_h16x2(u.x), b = unpack_h16x2(u.y), c = unpack_h16x2(u.z),
+               d = unpack_h16x2(u.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
-__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&f)[8]) {
+__device__ __forceinline__ void st8(h16* p, const float (&f)[8]) {
   uint4 u;
-  u.x = pack_bf16x2(f[0], f[1]);
-  u.y = pack_bf16x2(f[2], f[3]);
-  u.z = pack_bf16x2(f[4], f[5]);
-  u.w = pack_bf16x2(f[6], f[7]);
+  u.x = pack_h16x2(f[0], f[1]);
+  u.y = pack_h16x2(f[2], f[3]);
+  u.z = pack_h16x2(f[4], f[5]);
+  u.w = pack_h16x2(f[6], f[7]);
   *reinterpret_cast<uint4*>(p) = u;
 }
 
 // y[r, c] = act(x[r, c] + bias[c])
-__global__ void bias_act_fwd_kernel(const __nv_bfloat16* __restrict__ x,
-                                    const __nv_bfloat16* __restrict__ bias,
-                                    __nv_bfloat16* __restrict__ y, long long nvec, int ncols8,
+__global__ void bias_act_fwd_kernel(const h16* __restrict__ x,
+                                    const h16* __restrict__ bias,
+                                    h16* __restrict__ y, long long nvec, int ncols8,
                                     int act) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
@@ -75,10 +75,10 @@ __global__ void bias_act_fwd_kernel(const __nv_bfloat16* __restrict__ x,
 }
 
 // dx[r, c] = dy[r, c] * act'(x[r, c] + bias[c])
-__global__ void bias_act_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
-                                    const __nv_bfloat16* __restrict__ x,
-                                    const __nv_bfloat16* __restrict__ bias,
-                                    __nv_bfloat16* __restrict__ dx, long long nvec, int ncols8,
+__global__ void bias_act_bwd_kernel(const h16* __restrict__ dy,
+                                    const h16* __restrict__ x,
+                                    const h16* __restrict__ bias,
+                                    h16* __restrict__ dx, long long nvec, int ncols8,
                                     int act) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
@@ -97,8 +97,8 @@ __global__ void bias_act_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
 }
 
 // x: [rows, 2F] = [value | gate];  y[r, f] = value * act(gate)
-__global__ void gated_act_fwd_kernel(const __nv_bfloat16* __restrict__ x,
-                                     __nv_bfloat16* __restrict__ y, long long rows, int F, int act) {
+__global__ void gated_act_fwd_kernel(const h16* __restrict__ x,
+                                     h16* __restrict__ y, long long rows, int F, int act) {
   const int f8 = F >> 3;
   const long long nvec = rows * f8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
@@ -114,9 +114,9 @@ __global__ void gated_act_fwd_kernel(const __nv_bfloat16* __restrict__ x,
   }
 }
 // dx[:, :F] = dy * act(gate);  dx[:, F:] = dy * value * act'(gate)
-__global__ void gated_act_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
-                                     const __nv_bfloat16* __restrict__ x,
-                                     __nv_bfloat16* __restrict__ dx, long long rows, int F, int act) {
+__global__ void gated_act_bwd_kernel(const h16* __restrict__ dy,
+                                     const h16* __restrict__ x,
+                                     h16* __restrict__ dx, long long rows, int F, int act) {
   const int f8 = F >> 3;
   const long long nvec = rows * f8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
@@ -138,10 +138,10 @@ __global__ void gated_act_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
 }
 
 // out = residual + dropout(x + bias, p) ; mask (uint8, optional) records kept elements.
-__global__ void bias_dropout_add_kernel(const __nv_bfloat16* __restrict__ x,
-                                        const __nv_bfloat16* __restrict__ bias,
-                                        const __nv_bfloat16* __restrict__ residual,
-                                        __nv_bfloat16* __restrict__ out,
+__global__ void bias_dropout_add_kernel(const h16* __restrict__ x,
+                                        const h16* __restrict__ bias,
+                                        const h16* __restrict__ residual,
+                                        h16* __restrict__ out,
                                         uint8_t* __restrict__ mask, long long nvec, int ncols8,
                                         float p, unsigned long long seed,
                                         unsigned long long offset) {
@@ -178,8 +178,8 @@ __global__ void bias_dropout_add_kernel(const __nv_bfloat16* __restrict__ x,
   }
 }
 // dx = dy * mask * 1/(1-p)   (mask bit-packed, one byte per 8 elements)
-__global__ void dropout_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
-                                   const uint8_t* __restrict__ mask, __nv_bfloat16* __restrict__ dx,
+__global__ void dropout_bwd_kernel(const h16* __restrict__ dy,
+                                   const uint8_t* __restrict__ mask, h16* __restrict__ dx,
                                    long long nvec, float p) {
   const float keep_scale = 1.f / (1.f - p);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
@@ -196,7 +196,7 @@ __global__ void dropout_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
 // out[c] (+)= sum_r x[r, c]   (bf16 in, fp32 out).  Stage 1: each block reduces a row slab for
 // 64 columns into ws[slab, c]; stage 2 sums the slabs.
 constexpr int CS_COLS = 64;
-__global__ void colsum_stage1(const __nv_bfloat16* __restrict__ x, float* __restrict__ ws,
+__global__ void colsum_stage1(const h16* __restrict__ x, float* __restrict__ ws,
                               long long rows, int N, long long ld, int slabs) {
   __shared__ float sh[8][CS_COLS];
   const int c0 = blockIdx.x * CS_COLS;
@@ -235,28 +235,28 @@ __global__ void colsum_stage1(const __nv_bfloat16* __restrict__ x, float* __rest
   }
 }
 __global__ void colsum_stage2(const float* __restrict__ ws, float* __restrict__ out_f32,
-                              __nv_bfloat16* __restrict__ out_bf16, int N, int slabs,
+                              h16* __restrict__ out_bf16, int N, int slabs,
                               int accumulate) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= N) return;
   float s = 0.f;
   for (int i = 0; i < slabs; ++i) s += ws[static_cast<long long>(i) * N + c];
   if (out_f32 != nullptr) out_f32[c] = accumulate ? out_f32[c] + s : s;
-  if (out_bf16 != nullptr) out_bf16[c] = __float2bfloat16(s);
+  if (out_bf16 != nullptr) out_bf16[c] = float_to_h16(s);
 }
 
-__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y,
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ x, h16* __restrict__ y,
                                         long long n, float scale) {
   for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < n;
        i += (long long)gridDim.x * blockDim.x * 4) {
     if (i + 4 <= n) {
       const float4 v = *reinterpret_cast<const float4*>(x + i);
       uint2 o;
-      o.x = pack_bf16x2(v.x * scale, v.y * scale);
-      o.y = pack_bf16x2(v.z * scale, v.w * scale);
+      o.x = pack_h16x2(v.x * scale, v.y * scale);
+      o.y = pack_h16x2(v.z * scale, v.w * scale);
       *reinterpret_cast<uint2*>(y + i) = o;
     } else {
-      for (long long j = i; j < n; ++j) y[j] = __float2bfloat16(x[j] * scale);
+      for (long long j = i; j < n; ++j) y[j] = float_to_h16(x[j] * scale);
     }
   }
 }
@@ -269,9 +269,9 @@ static inline int grid_for(long long nvec, int threads) {
 
 }  // namespace nx
 
-using bf = __nv_bfloat16;
+using bf = h16;
 
-NX_API int nx_bias_act_fwd(const void* x, const void* bias, void* y, long long rows, int cols,
+NX_API int NX_SYM(nx_bias_act_fwd)(const void* x, const void* bias, void* y, long long rows, int cols,
                            int act, void* stream_) {
   using namespace nx;
   NX_REQUIRE(cols % 8 == 0, "bias_act: cols %% 8 != 0");
@@ -282,7 +282,7 @@ NX_API int nx_bias_act_fwd(const void* x, const void* bias, void* y, long long r
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_bias_act_bwd(const void* dy, const void* x, const void* bias, void* dx, long long rows,
+NX_API int NX_SYM(nx_bias_act_bwd)(const void* dy, const void* x, const void* bias, void* dx, long long rows,
                            int cols, int act, void* stream_) {
   using namespace nx;
   NX_REQUIRE(cols % 8 == 0, "bias_act: cols %% 8 != 0");
@@ -293,7 +293,7 @@ NX_API int nx_bias_act_bwd(const void* dy, const void* x, const void* bias, void
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_gated_act_fwd(const void* x, void* y, long long rows, int F, int act, void* stream_) {
+NX_API int NX_SYM(nx_gated_act_fwd)(const void* x, void* y, long long rows, int F, int act, void* stream_) {
   using namespace nx;
   NX_REQUIRE(F % 8 == 0, "gated_act: F %% 8 != 0");
   const long long nvec = rows * (F / 8);
@@ -303,7 +303,7 @@ NX_API int nx_gated_act_fwd(const void* x, void* y, long long rows, int F, int a
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_gated_act_bwd(const void* dy, const void* x, void* dx, long long rows, int F, int act,
+NX_API int NX_SYM(nx_gated_act_bwd)(const void* dy, const void* x, void* dx, long long rows, int F, int act,
                             void* stream_) {
   using namespace nx;
   NX_REQUIRE(F % 8 == 0, "gated_act: F %% 8 != 0");
@@ -314,7 +314,7 @@ NX_API int nx_gated_act_bwd(const void* dy, const void* x, void* dx, long long r
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_bias_dropout_add(const void* x, const void* bias, const void* residual, void* out,
+NX_API int NX_SYM(nx_bias_dropout_add)(const void* x, const void* bias, const void* residual, void* out,
                                void* mask, long long rows, int cols, float p,
                                unsigned long long seed, unsigned long long offset, void* stream_) {
   using namespace nx;
@@ -328,7 +328,7 @@ NX_API int nx_bias_dropout_add(const void* x, const void* bias, const void* resi
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_dropout_bwd(const void* dy, const void* mask, void* dx, long long n, float p,
+NX_API int NX_SYM(nx_dropout_bwd)(const void* dy, const void* mask, void* dx, long long n, float p,
                           void* stream_) {
   using namespace nx;
   NX_REQUIRE(n % 8 == 0, "dropout_bwd: n %% 8 != 0");
@@ -340,19 +340,19 @@ NX_API int nx_dropout_bwd(const void* dy, const void* mask, void* dx, long long 
 }
 
 // Slabs of the column-sum workspace: ws holds nx_colsum_slabs(rows) * N floats.
-NX_API int nx_colsum_slabs(long long rows) {
+NX_API int NX_SYM(nx_colsum_slabs)(long long rows) {
   long long s = rows / 256;
   if (s < 1) s = 1;
   if (s > 64) s = 64;
   return static_cast<int>(s);
 }
-NX_API int nx_colsum_bf16(const void* x, void* out_f32, void* out_bf16, void* ws, long long rows,
+NX_API int NX_SYM(nx_colsum_bf16)(const void* x, void* out_f32, void* out_bf16, void* ws, long long rows,
                           int N, long long ld, int accumulate, void* stream_) {
   using namespace nx;
   NX_REQUIRE(N % 8 == 0 && ld % 8 == 0, "colsum: N and ld must be multiples of 8");
   NX_REQUIRE(ws != nullptr, "colsum: workspace is null");
   if (N == 0) return NX_OK;
-  const int slabs = nx_colsum_slabs(rows);
+  const int slabs = NX_SYM(nx_colsum_slabs)(rows);
   dim3 grid((N + CS_COLS - 1) / CS_COLS, slabs);
   colsum_stage1<<<grid, 256, 0, (cudaStream_t)stream_>>>((const bf*)x, (float*)ws, rows, N, ld,
                                                          slabs);
@@ -362,7 +362,7 @@ NX_API int nx_colsum_bf16(const void* x, void* out_f32, void* out_bf16, void* ws
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_cast_f32_to_bf16(const void* x, void* y, long long n, float scale, void* stream_) {
+NX_API int NX_SYM(nx_cast_f32_to_bf16)(const void* x, void* y, long long n, float scale, void* stream_) {
   using namespace nx;
   if (n == 0) return NX_OK;
   cast_f32_to_bf16_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, (cudaStream_t)stream_>>>(

@@ -46,10 +46,10 @@ struct Params {
   int M, N, K;
   void* C;
   long long ldc;
-  const __nv_bfloat16* bias;
-  const __nv_bfloat16* aux_in;
-  __nv_bfloat16* aux_out;
-  const __nv_bfloat16* residual;
+  const h16* bias;
+  const h16* aux_in;
+  h16* aux_out;
+  const h16* residual;
   long long ld_aux;
   int flags;
   float alpha;
@@ -59,17 +59,17 @@ struct Params {
   int comm, tp_rank, ws;
   int tiles_m_chunk;            // row tiles per rank chunk: (M / ws) / 256
   uint32_t epoch;
-  __nv_bfloat16* rs_stage[8];   // on rank q: staging [src rank][M / ws, N]
+  h16* rs_stage[8];   // on rank q: staging [src rank][M / ws, N]
   uint32_t* rs_flags[8];        // on rank q: flags[tile in chunk][src rank][cta of pair][warp]
-  const __nv_bfloat16* residual2;
+  const h16* residual2;
   long long ld_res2;
-  const __nv_bfloat16* ag_src;  // this rank's [M / ws, K] shard
+  const h16* ag_src;  // this rank's [M / ws, K] shard
   long long ag_ld;
-  __nv_bfloat16* ag_dst[8];     // on rank q: gather buffer [M, K]
+  h16* ag_dst[8];     // on rank q: gather buffer [M, K]
   uint32_t* ag_flags[8];        // on rank q: flags[src][cta]
   // all-reduce mode (reduce-scatter as above, then the owner of a chunk writes the reduced tiles into every
   // rank's full [M, N] output and bumps that rank's delivery counter once per 32-row band)
-  __nv_bfloat16* ar_out[8];     // on rank q: output [M, N], leading dimension N
+  h16* ar_out[8];     // on rank q: output [M, N], leading dimension N
   uint32_t* ar_count[8];        // on rank q: delivery counter
 };
 
@@ -362,8 +362,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
           for (int j = 0; j < 32; j += 8) {
             if (col0 + j < p.N) {
               const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + j));
-              const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z),
-                           b3 = unpack_bf16x2(b.w);
+              const float2 b0 = unpack_h16x2(b.x), b1 = unpack_h16x2(b.y), b2 = unpack_h16x2(b.z),
+                           b3 = unpack_h16x2(b.w);
               v[j + 0] += b0.x; v[j + 1] += b0.y; v[j + 2] += b1.x; v[j + 3] += b1.y;
               v[j + 4] += b2.x; v[j + 5] += b2.y; v[j + 6] += b3.x; v[j + 7] += b3.y;
             }
@@ -371,7 +371,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
         }
         if (row_ok) {
           if (flags & AUX_OUT) {
-            __nv_bfloat16* ap = p.aux_out + row * p.ld_aux + col0;
+            h16* ap = p.aux_out + row * p.ld_aux + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
@@ -385,14 +385,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
                   }
                 }
                 uint4 o;
-                o.x = pack_bf16x2(d[0], d[1]); o.y = pack_bf16x2(d[2], d[3]);
-                o.z = pack_bf16x2(d[4], d[5]); o.w = pack_bf16x2(d[6], d[7]);
+                o.x = pack_h16x2(d[0], d[1]); o.y = pack_h16x2(d[2], d[3]);
+                o.z = pack_h16x2(d[4], d[5]); o.w = pack_h16x2(d[6], d[7]);
                 *reinterpret_cast<uint4*>(ap + j) = o;
               }
             }
           }
           if (flags & (DGELU_ERF | DGELU_TANH | MUL_AUX)) {
-            const __nv_bfloat16* ap = p.aux_in + row * p.ld_aux + col0;
+            const h16* ap = p.aux_in + row * p.ld_aux + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
@@ -400,7 +400,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
                 const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                  const float2 x = unpack_bf16x2(aw[q]);
+                  const float2 x = unpack_h16x2(aw[q]);
                   if (flags & MUL_AUX) {
                     v[j + 2 * q] *= x.x;
                     v[j + 2 * q + 1] *= x.y;
@@ -425,13 +425,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
             for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
           }
           if (flags & RESIDUAL) {
-            const __nv_bfloat16* rp = p.residual + row * p.ld_aux + col0;
+            const h16* rp = p.residual + row * p.ld_aux + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
                 const uint4 a = *reinterpret_cast<const uint4*>(rp + j);
-                const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y), x2 = unpack_bf16x2(a.z),
-                             x3 = unpack_bf16x2(a.w);
+                const float2 x0 = unpack_h16x2(a.x), x1 = unpack_h16x2(a.y), x2 = unpack_h16x2(a.z),
+                             x3 = unpack_h16x2(a.w);
                 v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
                 v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
               }
@@ -445,8 +445,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]); o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]); o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                o.x = pack_h16x2(v[j], v[j + 1]); o.y = pack_h16x2(v[j + 2], v[j + 3]);
+                o.z = pack_h16x2(v[j + 4], v[j + 5]); o.w = pack_h16x2(v[j + 6], v[j + 7]);
                 *reinterpret_cast<uint4*>(slab + lane * RS_ROW_BYTES + (c & 1) * 64 + j * 2) = o;
               }
               const bool last_group = (c == BN / 32 - 1) || (col0 + 32 >= p.N);
@@ -468,13 +468,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
             } else {
               for (int sr = 0; sr < p.ws; ++sr) {
                 if (sr == p.tp_rank) continue;
-                const __nv_bfloat16* sp = p.rs_stage[p.tp_rank] + (sr * chunk_rows + crow) * p.N + col0;
+                const h16* sp = p.rs_stage[p.tp_rank] + (sr * chunk_rows + crow) * p.N + col0;
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                   if (col0 + j < p.N) {
                     const uint4 a = *reinterpret_cast<const uint4*>(sp + j);
-                    const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y), x2 = unpack_bf16x2(a.z),
-                                 x3 = unpack_bf16x2(a.w);
+                    const float2 x0 = unpack_h16x2(a.x), x1 = unpack_h16x2(a.y), x2 = unpack_h16x2(a.z),
+                                 x3 = unpack_h16x2(a.w);
                     v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
                     v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
                   }
@@ -485,23 +485,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
                 if (col0 + j < p.N) {
                   if (flags & BIAS) {
                     const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + j));
-                    const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z),
-                                 b3 = unpack_bf16x2(b.w);
+                    const float2 b0 = unpack_h16x2(b.x), b1 = unpack_h16x2(b.y), b2 = unpack_h16x2(b.z),
+                                 b3 = unpack_h16x2(b.w);
                     v[j + 0] += b0.x; v[j + 1] += b0.y; v[j + 2] += b1.x; v[j + 3] += b1.y;
                     v[j + 4] += b2.x; v[j + 5] += b2.y; v[j + 6] += b3.x; v[j + 7] += b3.y;
                   }
                   if (p.residual2 != nullptr) {
                     const uint4 a = *reinterpret_cast<const uint4*>(p.residual2 + crow * p.ld_res2 + col0 + j);
-                    const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y), x2 = unpack_bf16x2(a.z),
-                                 x3 = unpack_bf16x2(a.w);
+                    const float2 x0 = unpack_h16x2(a.x), x1 = unpack_h16x2(a.y), x2 = unpack_h16x2(a.z),
+                                 x3 = unpack_h16x2(a.w);
                     v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
                     v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
                   }
                   uint4 o;
-                  o.x = pack_bf16x2(v[j], v[j + 1]); o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                  o.z = pack_bf16x2(v[j + 4], v[j + 5]); o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                  o.x = pack_h16x2(v[j], v[j + 1]); o.y = pack_h16x2(v[j + 2], v[j + 3]);
+                  o.z = pack_h16x2(v[j + 4], v[j + 5]); o.w = pack_h16x2(v[j + 6], v[j + 7]);
                   if (p.comm == COMM_RS) {
-                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + crow * p.ldc + col0 + j) = o;
+                    *reinterpret_cast<uint4*>(reinterpret_cast<h16*>(p.C) + crow * p.ldc + col0 + j) = o;
                   } else {
                     uint8_t* slab = smem_gen + RS_OFFSET + (warp - 2) * (32 * RS_ROW_BYTES);
                     *reinterpret_cast<uint4*>(slab + lane * RS_ROW_BYTES + (c & 1) * 64 + j * 2) = o;
@@ -545,20 +545,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
               }
             }
           } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+            h16* cp = reinterpret_cast<h16*>(p.C) + row * p.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
                 if (flags & ACCUM) {
                   const uint4 a = *reinterpret_cast<const uint4*>(cp + j);
-                  const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y), x2 = unpack_bf16x2(a.z),
-                               x3 = unpack_bf16x2(a.w);
+                  const float2 x0 = unpack_h16x2(a.x), x1 = unpack_h16x2(a.y), x2 = unpack_h16x2(a.z),
+                               x3 = unpack_h16x2(a.w);
                   v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
                   v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
                 }
                 uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]); o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]); o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                o.x = pack_h16x2(v[j], v[j + 1]); o.y = pack_h16x2(v[j + 2], v[j + 3]);
+                o.z = pack_h16x2(v[j + 4], v[j + 5]); o.w = pack_h16x2(v[j + 6], v[j + 7]);
                 *reinterpret_cast<uint4*>(cp + j) = o;
               }
             }
@@ -705,10 +705,10 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
   tmA2 = tmA;
   Params p{};
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc;
-  p.bias = static_cast<const __nv_bfloat16*>(bias);
-  p.aux_in = static_cast<const __nv_bfloat16*>(aux_in);
-  p.aux_out = static_cast<__nv_bfloat16*>(aux_out);
-  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.bias = static_cast<const h16*>(bias);
+  p.aux_in = static_cast<const h16*>(aux_in);
+  p.aux_out = static_cast<h16*>(aux_out);
+  p.residual = static_cast<const h16*>(residual);
   p.ld_aux = ld_aux; p.flags = flags; p.alpha = alpha;
   p.tiles_m = (M + 2 * BM - 1) / (2 * BM);
   p.tiles_n = (N + BN - 1) / BN;
@@ -723,21 +723,21 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
     p.tiles_m_chunk = (M / ca.ws) / (2 * BM);
     for (int i = 0; i < ca.ws; ++i) {
       if (ca.mode == COMM_RS || ca.mode == COMM_AR) {
-        p.rs_stage[i] = reinterpret_cast<__nv_bfloat16*>(ca.data_ptrs[i]);
+        p.rs_stage[i] = reinterpret_cast<h16*>(ca.data_ptrs[i]);
         p.rs_flags[i] = reinterpret_cast<uint32_t*>(ca.flag_ptrs[i]);
         if (ca.mode == COMM_AR) {
           NX_REQUIRE(ca.ar_out_ptrs != nullptr && ca.ar_count_ptrs != nullptr, "gemm2_comm: all-reduce tables are null");
-          p.ar_out[i] = reinterpret_cast<__nv_bfloat16*>(ca.ar_out_ptrs[i]);
+          p.ar_out[i] = reinterpret_cast<h16*>(ca.ar_out_ptrs[i]);
           p.ar_count[i] = reinterpret_cast<uint32_t*>(ca.ar_count_ptrs[i]);
         }
       } else {
-        p.ag_dst[i] = reinterpret_cast<__nv_bfloat16*>(ca.data_ptrs[i]);
+        p.ag_dst[i] = reinterpret_cast<h16*>(ca.data_ptrs[i]);
         p.ag_flags[i] = reinterpret_cast<uint32_t*>(ca.flag_ptrs[i]);
       }
     }
-    p.residual2 = static_cast<const __nv_bfloat16*>(ca.residual2);
+    p.residual2 = static_cast<const h16*>(ca.residual2);
     p.ld_res2 = ca.ld_res2;
-    p.ag_src = static_cast<const __nv_bfloat16*>(ca.ag_src);
+    p.ag_src = static_cast<const h16*>(ca.ag_src);
     p.ag_ld = ca.ag_ld;
     if (ca.mode != COMM_AG && ca.residual2 != nullptr) NX_REQUIRE(ca.ld_res2 % 8 == 0, "gemm2_comm: residual2 ld");
     if (ca.mode == COMM_AG) {
@@ -754,7 +754,7 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
 }
 
 // Same arguments as nx_gemm_bf16.
-NX_API int nx_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+NX_API int NX_SYM(nx_gemm2_bf16)(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                          long long ldc, int transA, int transB, const void* bias, const void* aux_in, void* aux_out,
                          const void* residual, long long ld_aux, int flags, float alpha, void* stream_) {
   Comm2Args ca;
@@ -763,7 +763,7 @@ NX_API int nx_gemm2_bf16(const void* A, const void* B, void* C, int M, int N, in
 }
 
 // Same arguments as nx_gemm_bf16_comm; reduce-scatter flags are laid out [tile][src rank][8 warp bands].
-NX_API int nx_gemm2_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+NX_API int NX_SYM(nx_gemm2_bf16_comm)(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                               long long ldc, int transB, const void* bias, const void* aux_in, void* aux_out,
                               const void* residual, long long ld_aux, int flags, int mode, int rank, int ws,
                               unsigned int epoch, const unsigned long long* data_ptrs,
@@ -787,7 +787,7 @@ __global__ void wait_counter_kernel(const uint32_t* counter, uint32_t target, in
 // GEMM -> all-reduce over the rows' owners: reduce-scatter as in mode 1, then every owner writes its reduced
 // chunk (+ bias) into each rank's [M, N] output (out_ptrs, leading dimension N) and counts deliveries;
 // a one-thread kernel behind the GEMM waits (bounded) until this rank has received `count_target` bands.
-NX_API int nx_gemm2_bf16_allreduce(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+NX_API int NX_SYM(nx_gemm2_bf16_allreduce)(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
                                    int transB, const void* bias, const void* residual, long long ld_aux, int flags,
                                    int rank, int ws, unsigned int epoch, const unsigned long long* stage_ptrs,
                                    const unsigned long long* flag_ptrs, const unsigned long long* out_ptrs,
@@ -808,7 +808,7 @@ NX_API int nx_gemm2_bf16_allreduce(const void* A, const void* B, int M, int N, i
 
 // The delivery wait on its own: returns once *counter >= target or the wait budget ran out (then the
 // device error word holds {ERR_PEER_TIMEOUT, site 20}).
-NX_API int nx_wait_counter(const void* counter, unsigned int target, void* stream_) {
+NX_API int NX_SYM(nx_wait_counter)(const void* counter, unsigned int target, void* stream_) {
   g2::wait_counter_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(static_cast<const uint32_t*>(counter), target,
                                                                             device_error_word());
   NX_LAUNCH_CHECK();

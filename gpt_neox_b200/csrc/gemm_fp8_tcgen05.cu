@@ -32,7 +32,7 @@ struct Fp8GemmParams {
   void* C;
   long long ldc;
   const float* alpha;               // device scalar
-  const __nv_bfloat16* bias;
+  const h16* bias;
   int out_f32, accumulate;
   int tiles_m, tiles_n;
   uint32_t idesc;
@@ -195,8 +195,8 @@ __global__ void __launch_bounds__(f8::THREADS, 1)
           for (int j = 0; j < 32; j += 8) {
             if (col0 + j < p.N) {
               const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + j));
-              const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z),
-                           b3 = unpack_bf16x2(b.w);
+              const float2 b0 = unpack_h16x2(b.x), b1 = unpack_h16x2(b.y), b2 = unpack_h16x2(b.z),
+                           b3 = unpack_h16x2(b.w);
               v[j + 0] += b0.x; v[j + 1] += b0.y; v[j + 2] += b1.x; v[j + 3] += b1.y;
               v[j + 4] += b2.x; v[j + 5] += b2.y; v[j + 6] += b3.x; v[j + 7] += b3.y;
             }
@@ -217,15 +217,15 @@ __global__ void __launch_bounds__(f8::THREADS, 1)
               }
             }
           } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+            h16* cp = reinterpret_cast<h16*>(p.C) + row * p.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
                 uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]);
-                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                o.x = pack_h16x2(v[j], v[j + 1]);
+                o.y = pack_h16x2(v[j + 2], v[j + 3]);
+                o.z = pack_h16x2(v[j + 4], v[j + 5]);
+                o.w = pack_h16x2(v[j + 6], v[j + 7]);
                 *reinterpret_cast<uint4*>(cp + j) = o;
               }
             }
@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(f8::THREADS, 1)
 
 // A [M, K] and B [N, K]: fp8 bytes, leading dimensions in elements (multiples of 16); a_e5m2 / b_e5m2
 // select the operand formats.  C: bf16 [M, N] or fp32 (out_f32; accumulate adds into it).
-NX_API int nx_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+NX_API int NX_SYM(nx_gemm_fp8)(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                        long long ldc, int a_e5m2, int b_e5m2, const void* alpha, const void* bias, int out_f32,
                        int accumulate, cudaStream_t stream) {
   using namespace f8;
@@ -271,7 +271,7 @@ NX_API int nx_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int 
   Fp8GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc;
   p.alpha = static_cast<const float*>(alpha);
-  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.bias = static_cast<const h16*>(bias);
   p.out_f32 = out_f32; p.accumulate = accumulate;
   p.tiles_m = (M + BM - 1) / BM; p.tiles_n = (N + BN - 1) / BN;
   p.idesc = idesc_f8(a_e5m2, b_e5m2);
@@ -299,7 +299,7 @@ __device__ __forceinline__ uint8_t to_fp8(float v) {
 // 64 x 64 tiles; block 256 threads (each thread 16 elements: 2 rows x 8 columns per pass).
 template <bool E5M2>
 __global__ void __launch_bounds__(256)
-fp8_quantize_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const float* __restrict__ scale,
+fp8_quantize_kernel(const h16* __restrict__ x, long long ldx, const float* __restrict__ scale,
                     uint8_t* __restrict__ out, long long ldo, uint8_t* __restrict__ out_t, long long ldt,
                     float* __restrict__ amax, int rows, int cols) {
   __shared__ uint8_t tile[64][64 + 16];
@@ -318,7 +318,7 @@ fp8_quantize_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const fl
       uint8_t q[8];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack_bf16x2(w[j]);
+        const float2 f = unpack_h16x2(w[j]);
         m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
         q[2 * j] = to_fp8<E5M2>(f.x * sc);
         q[2 * j + 1] = to_fp8<E5M2>(f.y * sc);
@@ -359,16 +359,16 @@ fp8_quantize_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const fl
 
 // x bf16 [rows, cols] (cols % 8 == 0, rows % 8 == 0 when the transpose is requested); scale / amax device
 // floats; out [rows, cols] fp8; out_t [cols, rows] fp8 or null.
-NX_API int nx_fp8_quantize(const void* x, long long ldx, const void* scale, void* out, long long ldo, void* out_t,
+NX_API int NX_SYM(nx_fp8_quantize)(const void* x, long long ldx, const void* scale, void* out, long long ldo, void* out_t,
                            long long ldt, void* amax, int rows, int cols, int e5m2, cudaStream_t stream) {
   NX_REQUIRE(cols % 8 == 0 && ldx % 8 == 0 && ldo % 8 == 0, "fp8_quantize: columns / leading dimensions must be multiples of 8");
   NX_REQUIRE(out_t == nullptr || (rows % 8 == 0 && ldt % 8 == 0), "fp8_quantize: transpose needs rows % 8 == 0");
   dim3 grid((cols + 63) / 64, (rows + 63) / 64);
   if (e5m2)
-    fp8_quantize_kernel<true><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (const float*)scale, (uint8_t*)out,
+    fp8_quantize_kernel<true><<<grid, 256, 0, stream>>>((const h16*)x, ldx, (const float*)scale, (uint8_t*)out,
                                                         ldo, (uint8_t*)out_t, ldt, (float*)amax, rows, cols);
   else
-    fp8_quantize_kernel<false><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, (const float*)scale, (uint8_t*)out,
+    fp8_quantize_kernel<false><<<grid, 256, 0, stream>>>((const h16*)x, ldx, (const float*)scale, (uint8_t*)out,
                                                          ldo, (uint8_t*)out_t, ldt, (float*)amax, rows, cols);
   NX_LAUNCH_CHECK();
   return NX_OK;

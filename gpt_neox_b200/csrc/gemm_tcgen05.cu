@@ -53,10 +53,10 @@ struct GemmParams {
   int M, N, K;
   void* C;
   long long ldc;
-  const __nv_bfloat16* bias;
-  const __nv_bfloat16* aux_in;
-  __nv_bfloat16* aux_out;
-  const __nv_bfloat16* residual;
+  const h16* bias;
+  const h16* aux_in;
+  h16* aux_out;
+  const h16* residual;
   long long ld_aux;
   int flags;
   float alpha;
@@ -78,14 +78,14 @@ struct GemmParams {
   int tiles_m_chunk;            // row tiles per rank chunk: (M / ws) / BM
   uint32_t epoch;               // value written to / expected in the flags of this call
   // COMM_RS (GEMM -> reduce-scatter over rows): C points to this rank's [M/ws, N] output.
-  __nv_bfloat16* rs_stage[8];   // on rank q: staging area [ws][M/ws, N]; slot = source rank
+  h16* rs_stage[8];   // on rank q: staging area [ws][M/ws, N]; slot = source rank
   uint32_t* rs_flags[8];        // on rank q: flags[tile_in_chunk][src][4 epilogue warps]
-  const __nv_bfloat16* residual2;  // [M/ws, N] added on the owner after the reduction (may be null)
+  const h16* residual2;  // [M/ws, N] added on the owner after the reduction (may be null)
   long long ld_res2;
   // COMM_AG (all-gather over rows -> GEMM): A's shard is pushed to every rank's gather buffer first
-  const __nv_bfloat16* ag_src;  // this rank's shard [M/ws, K], leading dimension ag_ld
+  const h16* ag_src;  // this rank's shard [M/ws, K], leading dimension ag_ld
   long long ag_ld;
-  __nv_bfloat16* ag_dst[8];     // on rank q: gather buffer [M, K] (dense, leading dimension K)
+  h16* ag_dst[8];     // on rank q: gather buffer [M, K] (dense, leading dimension K)
   uint32_t* ag_flags[8];        // on rank q: flags[src][cta]
 };
 
@@ -375,8 +375,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           for (int j = 0; j < 32; j += 8) {
             if (col0 + j < p.N) {
               const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + j));
-              const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y),
-                           b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+              const float2 b0 = unpack_h16x2(b.x), b1 = unpack_h16x2(b.y),
+                           b2 = unpack_h16x2(b.z), b3 = unpack_h16x2(b.w);
               v[j + 0] += b0.x; v[j + 1] += b0.y; v[j + 2] += b1.x; v[j + 3] += b1.y;
               v[j + 4] += b2.x; v[j + 5] += b2.y; v[j + 6] += b3.x; v[j + 7] += b3.y;
             }
@@ -384,7 +384,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         if (row_ok) {
           if (flags & EPI_AUX_OUT) {
-            __nv_bfloat16* ap = p.aux_out + row * p.ld_aux + col0;
+            h16* ap = p.aux_out + row * p.ld_aux + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
@@ -398,16 +398,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                   }
                 }
                 uint4 o;
-                o.x = pack_bf16x2(d[0], d[1]);
-                o.y = pack_bf16x2(d[2], d[3]);
-                o.z = pack_bf16x2(d[4], d[5]);
-                o.w = pack_bf16x2(d[6], d[7]);
+                o.x = pack_h16x2(d[0], d[1]);
+                o.y = pack_h16x2(d[2], d[3]);
+                o.z = pack_h16x2(d[4], d[5]);
+                o.w = pack_h16x2(d[6], d[7]);
                 *reinterpret_cast<uint4*>(ap + j) = o;
               }
             }
           }
           if (flags & (EPI_DGELU_ERF | EPI_DGELU_TANH | EPI_MUL_AUX)) {
-            const __nv_bfloat16* ap = p.aux_in + row * p.ld_aux + col0;
+            const h16* ap = p.aux_in + row * p.ld_aux + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                  const float2 x = unpack_bf16x2(aw[q]);
+                  const float2 x = unpack_h16x2(aw[q]);
                   if (flags & EPI_MUL_AUX) {
                     v[j + 2 * q] *= x.x;
                     v[j + 2 * q + 1] *= x.y;
@@ -440,13 +440,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
           }
           if (flags & EPI_RESIDUAL) {
-            const __nv_bfloat16* rp = p.residual + row * p.ld_aux + col0;
+            const h16* rp = p.residual + row * p.ld_aux + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
                 const uint4 a = *reinterpret_cast<const uint4*>(rp + j);
-                const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y),
-                             x2 = unpack_bf16x2(a.z), x3 = unpack_bf16x2(a.w);
+                const float2 x0 = unpack_h16x2(a.x), x1 = unpack_h16x2(a.y),
+                             x2 = unpack_h16x2(a.z), x3 = unpack_h16x2(a.w);
                 v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
                 v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
               }
@@ -462,10 +462,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
                 uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]);
-                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                o.x = pack_h16x2(v[j], v[j + 1]);
+                o.y = pack_h16x2(v[j + 2], v[j + 3]);
+                o.z = pack_h16x2(v[j + 4], v[j + 5]);
+                o.w = pack_h16x2(v[j + 6], v[j + 7]);
                 *reinterpret_cast<uint4*>(slab + lane * RS_ROW_BYTES + (c & 1) * 64 + j * 2) = o;
               }
               const bool last_group = (c == BN / 32 - 1) || (col0 + 32 >= p.N);
@@ -487,13 +487,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             } else {
               for (int sr = 0; sr < p.ws; ++sr) {
                 if (sr == p.rank) continue;
-                const __nv_bfloat16* sp = p.rs_stage[p.rank] + (sr * chunk_rows + crow) * p.N + col0;
+                const h16* sp = p.rs_stage[p.rank] + (sr * chunk_rows + crow) * p.N + col0;
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                   if (col0 + j < p.N) {
                     const uint4 a = *reinterpret_cast<const uint4*>(sp + j);
-                    const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y),
-                                 x2 = unpack_bf16x2(a.z), x3 = unpack_bf16x2(a.w);
+                    const float2 x0 = unpack_h16x2(a.x), x1 = unpack_h16x2(a.y),
+                                 x2 = unpack_h16x2(a.z), x3 = unpack_h16x2(a.w);
                     v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
                     v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
                   }
@@ -504,24 +504,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 if (col0 + j < p.N) {
                   if (flags & EPI_BIAS) {
                     const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + j));
-                    const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y),
-                                 b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+                    const float2 b0 = unpack_h16x2(b.x), b1 = unpack_h16x2(b.y),
+                                 b2 = unpack_h16x2(b.z), b3 = unpack_h16x2(b.w);
                     v[j + 0] += b0.x; v[j + 1] += b0.y; v[j + 2] += b1.x; v[j + 3] += b1.y;
                     v[j + 4] += b2.x; v[j + 5] += b2.y; v[j + 6] += b3.x; v[j + 7] += b3.y;
                   }
                   if (p.residual2 != nullptr) {
                     const uint4 a = *reinterpret_cast<const uint4*>(p.residual2 + crow * p.ld_res2 + col0 + j);
-                    const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y),
-                                 x2 = unpack_bf16x2(a.z), x3 = unpack_bf16x2(a.w);
+                    const float2 x0 = unpack_h16x2(a.x), x1 = unpack_h16x2(a.y),
+                                 x2 = unpack_h16x2(a.z), x3 = unpack_h16x2(a.w);
                     v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
                     v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
                   }
                   uint4 o;
-                  o.x = pack_bf16x2(v[j], v[j + 1]);
-                  o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                  o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                  o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.C) + crow * p.ldc + col0 + j) = o;
+                  o.x = pack_h16x2(v[j], v[j + 1]);
+                  o.y = pack_h16x2(v[j + 2], v[j + 3]);
+                  o.z = pack_h16x2(v[j + 4], v[j + 5]);
+                  o.w = pack_h16x2(v[j + 6], v[j + 7]);
+                  *reinterpret_cast<uint4*>(reinterpret_cast<h16*>(p.C) + crow * p.ldc + col0 + j) = o;
                 }
               }
             }
@@ -539,22 +539,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
               }
             }
           } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + row * p.ldc + col0;
+            h16* cp = reinterpret_cast<h16*>(p.C) + c_off + row * p.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j < p.N) {
                 if (flags & EPI_ACCUM) {
                   const uint4 a = *reinterpret_cast<const uint4*>(cp + j);
-                  const float2 x0 = unpack_bf16x2(a.x), x1 = unpack_bf16x2(a.y),
-                               x2 = unpack_bf16x2(a.z), x3 = unpack_bf16x2(a.w);
+                  const float2 x0 = unpack_h16x2(a.x), x1 = unpack_h16x2(a.y),
+                               x2 = unpack_h16x2(a.z), x3 = unpack_h16x2(a.w);
                   v[j + 0] += x0.x; v[j + 1] += x0.y; v[j + 2] += x1.x; v[j + 3] += x1.y;
                   v[j + 4] += x2.x; v[j + 5] += x2.y; v[j + 6] += x3.x; v[j + 7] += x3.y;
                 }
                 uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]);
-                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                o.x = pack_h16x2(v[j], v[j + 1]);
+                o.y = pack_h16x2(v[j + 2], v[j + 3]);
+                o.z = pack_h16x2(v[j + 4], v[j + 5]);
+                o.w = pack_h16x2(v[j + 6], v[j + 7]);
                 *reinterpret_cast<uint4*>(cp + j) = o;
               }
             }
@@ -721,16 +721,16 @@ static int gemm_common(const void* A, const void* B, void* C, int M, int N, int 
     p.tiles_m_chunk = (M / ca.ws) / BM;
     for (int i = 0; i < ca.ws; ++i) {
       if (ca.mode == COMM_RS) {
-        p.rs_stage[i] = reinterpret_cast<__nv_bfloat16*>(ca.data_ptrs[i]);
+        p.rs_stage[i] = reinterpret_cast<h16*>(ca.data_ptrs[i]);
         p.rs_flags[i] = reinterpret_cast<uint32_t*>(ca.flag_ptrs[i]);
       } else {
-        p.ag_dst[i] = reinterpret_cast<__nv_bfloat16*>(ca.data_ptrs[i]);
+        p.ag_dst[i] = reinterpret_cast<h16*>(ca.data_ptrs[i]);
         p.ag_flags[i] = reinterpret_cast<uint32_t*>(ca.flag_ptrs[i]);
       }
     }
-    p.residual2 = static_cast<const __nv_bfloat16*>(ca.residual2);
+    p.residual2 = static_cast<const h16*>(ca.residual2);
     p.ld_res2 = ca.ld_res2;
-    p.ag_src = static_cast<const __nv_bfloat16*>(ca.ag_src);
+    p.ag_src = static_cast<const h16*>(ca.ag_src);
     p.ag_ld = ca.ag_ld;
     if (ca.mode == COMM_RS && ca.residual2 != nullptr) NX_REQUIRE(ca.ld_res2 % 8 == 0, "gemm_comm: residual2 ld");
     if (ca.mode == COMM_AG) {
@@ -754,10 +754,10 @@ static int gemm_common(const void* A, const void* B, void* C, int M, int N, int 
   }
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc;
-  p.bias = static_cast<const __nv_bfloat16*>(bias);
-  p.aux_in = static_cast<const __nv_bfloat16*>(aux_in);
-  p.aux_out = static_cast<__nv_bfloat16*>(aux_out);
-  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.bias = static_cast<const h16*>(bias);
+  p.aux_in = static_cast<const h16*>(aux_in);
+  p.aux_out = static_cast<h16*>(aux_out);
+  p.residual = static_cast<const h16*>(residual);
   p.ld_aux = ld_aux;
   p.flags = flags;
   p.alpha = alpha;
@@ -785,7 +785,7 @@ static int gemm_common(const void* A, const void* B, void* C, int M, int N, int 
 // C[M,N] = epilogue(op(A) * op(B)).  Leading dimensions in elements.  bias/aux/residual may be
 // null when their flag is clear.  ld_aux is the leading dimension shared by aux_in, aux_out
 // and residual.  Returns an NxStatus.
-NX_API int nx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+NX_API int NX_SYM(nx_gemm_bf16)(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                         long long ldb, long long ldc, int transA, int transB, const void* bias,
                         const void* aux_in, void* aux_out, const void* residual, long long ld_aux,
                         int flags, float alpha, void* stream_) {
@@ -800,7 +800,7 @@ NX_API int nx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
 // weight gradient C_e[M, N] (+)= A[rows_e, M]^T * B[rows_e, N], rows_e = [row_offsets[e], row_offsets[e+1]);
 // C_e = C + e * c_stride; experts without rows are left untouched.  All tables live on the device: no host
 // synchronisation on the routing result.
-NX_API int nx_gemm_bf16_grouped(int mode, const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+NX_API int NX_SYM(nx_gemm_bf16_grouped)(int mode, const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                                 long long ldb, long long ldc, int transB, int experts, const void* tile_expert,
                                 const void* row_offsets, long long c_stride, const void* aux_in, void* aux_out,
                                 long long ld_aux, int flags, void* stream_) {
@@ -814,7 +814,7 @@ NX_API int nx_gemm_bf16_grouped(int mode, const void* A, const void* B, void* C,
 }
 
 // Number of CTAs the GEMM of this shape launches (the all-gather mode's flag count per source rank).
-NX_API int nx_gemm_grid(int M, int N) {
+NX_API int NX_SYM(nx_gemm_grid)(int M, int N) {
   const int BN = (N <= 128) ? 128 : 256;
   const long long tiles = static_cast<long long>((M + nx::BM - 1) / nx::BM) * ((N + BN - 1) / BN);
   return static_cast<int>(tiles < nx::sm_count() ? tiles : nx::sm_count());
@@ -825,7 +825,7 @@ NX_API int nx_gemm_grid(int M, int N) {
 // mode 2: all-gather of the rows of A -> GEMM, A = this rank's dense [M, K] gather buffer, ag_src =
 // this rank's [M/ws, K] shard).  data_ptrs / flag_ptrs: per-rank addresses (as mapped on this
 // rank) of the staging / gather area and of its flag array; epoch: this call's flag value.
-NX_API int nx_gemm_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+NX_API int NX_SYM(nx_gemm_bf16_comm)(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                              long long ldb, long long ldc, int transB, const void* bias, const void* aux_in,
                              void* aux_out, const void* residual, long long ld_aux, int flags, int mode,
                              int rank, int ws, unsigned int epoch, const unsigned long long* data_ptrs,

@@ -24,13 +24,13 @@ namespace nx {
 // ---------------------------------------------------------------------------------------------
 constexpr int CONV_TILE = 64;   // timesteps per thread
 
-__device__ __forceinline__ float ldbf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float ldbf(const h16* p) { return h16_to_float(*p); }
 
 // y[b,t,d] = silu(bias[d] + sum_k w[d,k] * x[b, t-(W-1)+k, d])
 __global__ void __launch_bounds__(128)
-conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long xsb, long long xst,
-                       const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
-                       __nv_bfloat16* __restrict__ y, long long ysb, long long yst, int L, int D, int W) {
+conv1d_silu_fwd_kernel(const h16* __restrict__ x, long long xsb, long long xst,
+                       const h16* __restrict__ w, const h16* __restrict__ bias,
+                       h16* __restrict__ y, long long ysb, long long yst, int L, int D, int W) {
   const int d = blockIdx.x * 128 + threadIdx.x;
   if (d >= D) return;
   const int t0 = blockIdx.y * CONV_TILE;
@@ -38,7 +38,7 @@ conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long xsb, long 
   float wk[4] = {0.f, 0.f, 0.f, 0.f};
   for (int k = 0; k < W; ++k) wk[4 - W + k] = ldbf(w + (long long)d * W + k);
   const float bv = bias ? ldbf(bias + d) : 0.f;
-  const __nv_bfloat16* xp = x + b * xsb + d;
+  const h16* xp = x + b * xsb + d;
   float win[4];
 #pragma unroll
   for (int k = 0; k < 3; ++k) {
@@ -50,16 +50,16 @@ conv1d_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, long long xsb, long 
     win[0] = win[1]; win[1] = win[2]; win[2] = win[3];
     win[3] = ldbf(xp + t * xst);
     const float pre = bv + wk[0] * win[0] + wk[1] * win[1] + wk[2] * win[2] + wk[3] * win[3];
-    y[b * ysb + t * yst + d] = __float2bfloat16(silu(pre));
+    y[b * ysb + t * yst + d] = float_to_h16(silu(pre));
   }
 }
 
 // dx[t] = sum_k w[k] * dpre[t + (3-k)];  dw[k] += dpre[t] * x[t-3+k];  dbias += dpre[t]
 __global__ void __launch_bounds__(128)
-conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xsb, long long xst,
-                       const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
-                       const __nv_bfloat16* __restrict__ dy, long long dsb, long long dst,
-                       __nv_bfloat16* __restrict__ dx, long long gsb, long long gst,
+conv1d_silu_bwd_kernel(const h16* __restrict__ x, long long xsb, long long xst,
+                       const h16* __restrict__ w, const h16* __restrict__ bias,
+                       const h16* __restrict__ dy, long long dsb, long long dst,
+                       h16* __restrict__ dx, long long gsb, long long gst,
                        float* __restrict__ dw, float* __restrict__ dbias, int L, int D, int W) {
   const int d = blockIdx.x * 128 + threadIdx.x;
   if (d >= D) return;
@@ -68,8 +68,8 @@ conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xsb, long 
   float wk[4] = {0.f, 0.f, 0.f, 0.f};
   for (int k = 0; k < W; ++k) wk[4 - W + k] = ldbf(w + (long long)d * W + k);
   const float bv = bias ? ldbf(bias + d) : 0.f;
-  const __nv_bfloat16* xp = x + b * xsb + d;
-  const __nv_bfloat16* gp = dy + b * dsb + d;
+  const h16* xp = x + b * xsb + d;
+  const h16* gp = dy + b * dsb + d;
   float win[4], dp[4] = {0.f, 0.f, 0.f, 0.f};
   float aw[4] = {0.f, 0.f, 0.f, 0.f}, ab = 0.f;
 #pragma unroll
@@ -95,33 +95,33 @@ conv1d_silu_bwd_kernel(const __nv_bfloat16* __restrict__ x, long long xsb, long 
     const int to = t - 3;
     if (to >= t0 && to < t_own)
       dx[b * gsb + to * gst + d] =
-          __float2bfloat16(wk[3] * dp[0] + wk[2] * dp[1] + wk[1] * dp[2] + wk[0] * dp[3]);
+          float_to_h16(wk[3] * dp[0] + wk[2] * dp[1] + wk[1] * dp[2] + wk[0] * dp[3]);
   }
   for (int k = 0; k < W; ++k) atomicAdd(dw + (long long)d * W + k, aw[4 - W + k]);
   if (dbias) atomicAdd(dbias + d, ab);
 }
 
-NX_API int nx_conv1d_silu_fwd(const void* x, long long xsb, long long xst, const void* w, const void* bias,
+NX_API int NX_SYM(nx_conv1d_silu_fwd)(const void* x, long long xsb, long long xst, const void* w, const void* bias,
                               void* y, long long ysb, long long yst, int B, int L, int D, int W,
                               cudaStream_t stream) {
   NX_REQUIRE(W >= 1 && W <= 4, "conv1d: kernel width %d not in [1, 4]", W);
   dim3 grid((D + 127) / 128, (L + CONV_TILE - 1) / CONV_TILE, B);
-  conv1d_silu_fwd_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)x, xsb, xst, (const __nv_bfloat16*)w,
-                                                   (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, ysb, yst, L, D, W);
+  conv1d_silu_fwd_kernel<<<grid, 128, 0, stream>>>((const h16*)x, xsb, xst, (const h16*)w,
+                                                   (const h16*)bias, (h16*)y, ysb, yst, L, D, W);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
 
 // dw [D, W] and dbias [D] are fp32 and must be zeroed by the caller.
-NX_API int nx_conv1d_silu_bwd(const void* x, long long xsb, long long xst, const void* w, const void* bias,
+NX_API int NX_SYM(nx_conv1d_silu_bwd)(const void* x, long long xsb, long long xst, const void* w, const void* bias,
                               const void* dy, long long dsb, long long dst, void* dx, long long gsb,
                               long long gst, void* dw, void* dbias, int B, int L, int D, int W,
                               cudaStream_t stream) {
   NX_REQUIRE(W >= 1 && W <= 4, "conv1d: kernel width %d not in [1, 4]", W);
   dim3 grid((D + 127) / 128, (L + CONV_TILE - 1) / CONV_TILE, B);
   conv1d_silu_bwd_kernel<<<grid, 128, 0, stream>>>(
-      (const __nv_bfloat16*)x, xsb, xst, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias,
-      (const __nv_bfloat16*)dy, dsb, dst, (__nv_bfloat16*)dx, gsb, gst, (float*)dw, (float*)dbias, L, D, W);
+      (const h16*)x, xsb, xst, (const h16*)w, (const h16*)bias,
+      (const h16*)dy, dsb, dst, (h16*)dx, gsb, gst, (float*)dw, (float*)dbias, L, D, W);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
@@ -137,10 +137,10 @@ constexpr int SC_NSUB = SC_CHUNK / SC_SUB;
 constexpr int SC_THREADS = SC_CH * 4;
 
 struct ScanParams {
-  const __nv_bfloat16 *x, *dt, *z, *Bm, *Cm, *dout;
+  const h16 *x, *dt, *z, *Bm, *Cm, *dout;
   long long xsb, xst, dsb, dst, zsb, zst, bsb, bst, csb, cst, gsb, gst;
   const float *A, *Dv, *dt_bias;
-  __nv_bfloat16 *out, *dx, *ddt, *dz;       // [.., D] with strides osb / ost
+  h16 *out, *dx, *ddt, *dz;       // [.., D] with strides osb / ost
   long long osb, ost;
   float *chunk_state, *chunk_sumdt, *chunk_h0, *chunk_E;   // [B, NC, D, 16] / [B, NC, D]
   float *partBC;                                           // [ceil(D/64), B, L, 32]
@@ -237,7 +237,7 @@ scan_fwd_kernel(const ScanParams p) {
         if (tt < t_end && dx_ < p.D) {
           float y = ys[t][cc];
           if (p.z) y *= silu(ldbf(p.z + b * p.zsb + tt * p.zst + dx_));
-          p.out[b * p.osb + tt * p.ost + dx_] = __float2bfloat16(y);
+          p.out[b * p.osb + tt * p.ost + dx_] = float_to_h16(y);
         }
       }
     }
@@ -447,9 +447,9 @@ scan_bwd_final_kernel(const ScanParams p) {
       const int t = i / SC_CH, cc = i % SC_CH, tt = t0 + t, dx_ = d0 + cc;
       if (tt < t_end && dx_ < p.D) {
         const long long o = b * p.osb + tt * p.ost + dx_;
-        p.dx[o] = __float2bfloat16(s.o_dx[t][cc]);
-        p.ddt[o] = __float2bfloat16(s.o_ddt[t][cc]);
-        if (p.dz) p.dz[o] = __float2bfloat16(s.o_dz[t][cc]);
+        p.dx[o] = float_to_h16(s.o_dx[t][cc]);
+        p.ddt[o] = float_to_h16(s.o_ddt[t][cc]);
+        if (p.dz) p.dz[o] = float_to_h16(s.o_dz[t][cc]);
       }
     }
     for (int i = threadIdx.x; i < SC_SUB * 32; i += SC_THREADS) {
@@ -472,26 +472,26 @@ scan_bwd_final_kernel(const ScanParams p) {
   }
 }
 
-NX_API int nx_scan_chunks(int L) { return (L + SC_CHUNK - 1) / SC_CHUNK; }
-NX_API int nx_scan_channel_blocks(int D) { return (D + SC_CH - 1) / SC_CH; }
+NX_API int NX_SYM(nx_scan_chunks)(int L) { return (L + SC_CHUNK - 1) / SC_CHUNK; }
+NX_API int NX_SYM(nx_scan_channel_blocks)(int D) { return (D + SC_CH - 1) / SC_CH; }
 
 // A [D,16] fp32 (negative), Dv [D] fp32 or null, dt_bias [D] fp32; x/dt/z/out bf16 addressed by
 // (batch stride, time stride); Bm/Cm bf16 [.., 16]. Scratch (fp32): chunk_state / chunk_h0
 // [B, NC, D, 16], chunk_sumdt [B, NC, D].
-NX_API int nx_selective_scan_fwd(const void* x, long long xsb, long long xst, const void* dt, long long dsb,
+NX_API int NX_SYM(nx_selective_scan_fwd)(const void* x, long long xsb, long long xst, const void* dt, long long dsb,
                                  long long dst, const void* z, long long zsb, long long zst, const void* Bm,
                                  long long bsb, long long bst, const void* Cm, long long csb, long long cst,
                                  const void* A, const void* Dv, const void* dt_bias, void* out, long long osb,
                                  long long ost, void* chunk_state, void* chunk_sumdt, void* chunk_h0, int B,
                                  int L, int D, cudaStream_t stream) {
   ScanParams p{};
-  p.x = (const __nv_bfloat16*)x; p.xsb = xsb; p.xst = xst;
-  p.dt = (const __nv_bfloat16*)dt; p.dsb = dsb; p.dst = dst;
-  p.z = (const __nv_bfloat16*)z; p.zsb = zsb; p.zst = zst;
-  p.Bm = (const __nv_bfloat16*)Bm; p.bsb = bsb; p.bst = bst;
-  p.Cm = (const __nv_bfloat16*)Cm; p.csb = csb; p.cst = cst;
+  p.x = (const h16*)x; p.xsb = xsb; p.xst = xst;
+  p.dt = (const h16*)dt; p.dsb = dsb; p.dst = dst;
+  p.z = (const h16*)z; p.zsb = zsb; p.zst = zst;
+  p.Bm = (const h16*)Bm; p.bsb = bsb; p.bst = bst;
+  p.Cm = (const h16*)Cm; p.csb = csb; p.cst = cst;
   p.A = (const float*)A; p.Dv = (const float*)Dv; p.dt_bias = (const float*)dt_bias;
-  p.out = (__nv_bfloat16*)out; p.osb = osb; p.ost = ost;
+  p.out = (h16*)out; p.osb = osb; p.ost = ost;
   p.chunk_state = (float*)chunk_state; p.chunk_sumdt = (float*)chunk_sumdt; p.chunk_h0 = (float*)chunk_h0;
   p.B = B; p.L = L; p.D = D; p.NC = (L + SC_CHUNK - 1) / SC_CHUNK;
   dim3 grid((D + SC_CH - 1) / SC_CH, p.NC, B);
@@ -506,7 +506,7 @@ NX_API int nx_selective_scan_fwd(const void* x, long long xsb, long long xst, co
 
 // dx / ddt / dz: bf16 with strides (osb, ost). partBC fp32 [ceil(D/64), B, L, 32] (written fully);
 // dA [D,16], dD [D], dbias [D] fp32, zeroed by the caller. chunk_* from the forward; chunk_E scratch.
-NX_API int nx_selective_scan_bwd(const void* x, long long xsb, long long xst, const void* dt, long long dsb,
+NX_API int NX_SYM(nx_selective_scan_bwd)(const void* x, long long xsb, long long xst, const void* dt, long long dsb,
                                  long long dst, const void* z, long long zsb, long long zst, const void* Bm,
                                  long long bsb, long long bst, const void* Cm, long long csb, long long cst,
                                  const void* A, const void* Dv, const void* dt_bias, const void* dout,
@@ -515,14 +515,14 @@ NX_API int nx_selective_scan_bwd(const void* x, long long xsb, long long xst, co
                                  void* chunk_sumdt, void* chunk_h0, void* chunk_E, int B, int L, int D,
                                  cudaStream_t stream) {
   ScanParams p{};
-  p.x = (const __nv_bfloat16*)x; p.xsb = xsb; p.xst = xst;
-  p.dt = (const __nv_bfloat16*)dt; p.dsb = dsb; p.dst = dst;
-  p.z = (const __nv_bfloat16*)z; p.zsb = zsb; p.zst = zst;
-  p.Bm = (const __nv_bfloat16*)Bm; p.bsb = bsb; p.bst = bst;
-  p.Cm = (const __nv_bfloat16*)Cm; p.csb = csb; p.cst = cst;
-  p.dout = (const __nv_bfloat16*)dout; p.gsb = gsb; p.gst = gst;
+  p.x = (const h16*)x; p.xsb = xsb; p.xst = xst;
+  p.dt = (const h16*)dt; p.dsb = dsb; p.dst = dst;
+  p.z = (const h16*)z; p.zsb = zsb; p.zst = zst;
+  p.Bm = (const h16*)Bm; p.bsb = bsb; p.bst = bst;
+  p.Cm = (const h16*)Cm; p.csb = csb; p.cst = cst;
+  p.dout = (const h16*)dout; p.gsb = gsb; p.gst = gst;
   p.A = (const float*)A; p.Dv = (const float*)Dv; p.dt_bias = (const float*)dt_bias;
-  p.dx = (__nv_bfloat16*)dx; p.ddt = (__nv_bfloat16*)ddt; p.dz = (__nv_bfloat16*)dz; p.osb = osb; p.ost = ost;
+  p.dx = (h16*)dx; p.ddt = (h16*)ddt; p.dz = (h16*)dz; p.osb = osb; p.ost = ost;
   p.partBC = (float*)partBC; p.dA = (float*)dA; p.dD = (float*)dD; p.dbias = (float*)dbias;
   p.chunk_sumdt = (float*)chunk_sumdt; p.chunk_h0 = (float*)chunk_h0; p.chunk_E = (float*)chunk_E;
   p.B = B; p.L = L; p.D = D; p.NC = (L + SC_CHUNK - 1) / SC_CHUNK;

@@ -92,8 +92,8 @@ moe_rank_kernel(const long long* __restrict__ expert, int C, int E, const int* _
 // Row gather by destination: out[row] = scale * src[src_copy[row] / k] (zeros for padding rows).
 // scale: per-copy weights (indexed by copy id) or null.  One warp per row; H % 8 == 0.
 __global__ void __launch_bounds__(256)
-moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long lds, const int* __restrict__ src_copy,
-                       const __nv_bfloat16* __restrict__ scale, int k, __nv_bfloat16* __restrict__ out, int rows,
+moe_gather_rows_kernel(const h16* __restrict__ src, long long lds, const int* __restrict__ src_copy,
+                       const h16* __restrict__ scale, int k, h16* __restrict__ out, int rows,
                        int H) {
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -108,13 +108,13 @@ moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long lds, con
   if (scale == nullptr) {
     for (int v = lane; v < H / 8; v += 32) o[v] = s[v];
   } else {
-    const float w = __bfloat162float(scale[c]);
+    const float w = h16_to_float(scale[c]);
     for (int v = lane; v < H / 8; v += 32) {
       const uint4 u = s[v];
-      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      const float2 a = unpack_h16x2(u.x), b = unpack_h16x2(u.y), cc = unpack_h16x2(u.z), d = unpack_h16x2(u.w);
       uint4 r;
-      r.x = pack_bf16x2(a.x * w, a.y * w); r.y = pack_bf16x2(b.x * w, b.y * w);
-      r.z = pack_bf16x2(cc.x * w, cc.y * w); r.w = pack_bf16x2(d.x * w, d.y * w);
+      r.x = pack_h16x2(a.x * w, a.y * w); r.y = pack_h16x2(b.x * w, b.y * w);
+      r.z = pack_h16x2(cc.x * w, cc.y * w); r.w = pack_h16x2(d.x * w, d.y * w);
       o[v] = r;
     }
   }
@@ -123,8 +123,8 @@ moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long lds, con
 // Weighted combine by token: out[t] = sum_j w[t*k+j] * y[dest_row[t*k+j]] (w null: unit weights).
 // One warp per token, fp32 accumulation, deterministic.
 __global__ void __launch_bounds__(256)
-moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ dest_row,
-                   const __nv_bfloat16* __restrict__ w, int k, __nv_bfloat16* __restrict__ out, int T, int H) {
+moe_combine_kernel(const h16* __restrict__ y, const int* __restrict__ dest_row,
+                   const h16* __restrict__ w, int k, h16* __restrict__ out, int T, int H) {
   const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (t >= T) return;
   const int lane = threadIdx.x & 31;
@@ -132,23 +132,23 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ 
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int j = 0; j < k; ++j) {
       const int c = t * k + j;
-      const float wj = w ? __bfloat162float(w[c]) : 1.f;
+      const float wj = w ? h16_to_float(w[c]) : 1.f;
       const uint4 u = reinterpret_cast<const uint4*>(y + static_cast<long long>(dest_row[c]) * H)[v];
-      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      const float2 a = unpack_h16x2(u.x), b = unpack_h16x2(u.y), cc = unpack_h16x2(u.z), d = unpack_h16x2(u.w);
       acc[0] += wj * a.x; acc[1] += wj * a.y; acc[2] += wj * b.x; acc[3] += wj * b.y;
       acc[4] += wj * cc.x; acc[5] += wj * cc.y; acc[6] += wj * d.x; acc[7] += wj * d.y;
     }
     uint4 r;
-    r.x = pack_bf16x2(acc[0], acc[1]); r.y = pack_bf16x2(acc[2], acc[3]);
-    r.z = pack_bf16x2(acc[4], acc[5]); r.w = pack_bf16x2(acc[6], acc[7]);
+    r.x = pack_h16x2(acc[0], acc[1]); r.y = pack_h16x2(acc[2], acc[3]);
+    r.z = pack_h16x2(acc[4], acc[5]); r.w = pack_h16x2(acc[6], acc[7]);
     reinterpret_cast<uint4*>(out + static_cast<long long>(t) * H)[v] = r;
   }
 }
 
 // Gradient of the routing weights: dw[c] = <g[c / k], y[dest_row[c]]>.  One warp per copy.
 __global__ void __launch_bounds__(256)
-moe_weight_grad_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ y,
-                       const int* __restrict__ dest_row, int k, __nv_bfloat16* __restrict__ dw, int C, int H) {
+moe_weight_grad_kernel(const h16* __restrict__ g, const h16* __restrict__ y,
+                       const int* __restrict__ dest_row, int k, h16* __restrict__ dw, int C, int H) {
   const int c = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (c >= C) return;
   const int lane = threadIdx.x & 31;
@@ -160,26 +160,26 @@ moe_weight_grad_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16*
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const float2 x = unpack_bf16x2(aw[q]), z = unpack_bf16x2(bw[q]);
+      const float2 x = unpack_h16x2(aw[q]), z = unpack_h16x2(bw[q]);
       acc += x.x * z.x + x.y * z.y;
     }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) dw[c] = __float2bfloat16(acc);
+  if (lane == 0) dw[c] = float_to_h16(acc);
 }
 
-NX_API int nx_moe_blocks(int C) { return (C + MOE_BLOCK - 1) / MOE_BLOCK; }
-NX_API int nx_moe_max_rows(int C, int E) { return (C + E * (MOE_ALIGN - 1) + MOE_ALIGN - 1) / MOE_ALIGN * MOE_ALIGN; }
+NX_API int NX_SYM(nx_moe_blocks)(int C) { return (C + MOE_BLOCK - 1) / MOE_BLOCK; }
+NX_API int NX_SYM(nx_moe_max_rows)(int C, int E) { return (C + E * (MOE_ALIGN - 1) + MOE_ALIGN - 1) / MOE_ALIGN * MOE_ALIGN; }
 
 // expert: int64 [C]; scratch hist / base: int32 [blocks * E]; outputs: counts [E], offsets [E+1],
 // tile_expert [max_rows / 128], dest_row [C], src_copy [max_rows] (filled with -1 here).
-NX_API int nx_moe_plan(const void* expert, int C, int E, void* hist, void* base, void* counts, void* offsets,
+NX_API int NX_SYM(nx_moe_plan)(const void* expert, int C, int E, void* hist, void* base, void* counts, void* offsets,
                        void* tile_expert, void* dest_row, void* src_copy, cudaStream_t stream) {
   NX_REQUIRE(E >= 1 && E <= MOE_MAX_E, "moe_plan: %d experts (max %d)", E, MOE_MAX_E);
   NX_REQUIRE(C > 0, "moe_plan: no routed copies");
   const int nblk = (C + MOE_BLOCK - 1) / MOE_BLOCK;
-  const int max_rows = nx_moe_max_rows(C, E);
+  const int max_rows = NX_SYM(nx_moe_max_rows)(C, E);
   NX_CUDA_CHECK(cudaMemsetAsync(src_copy, 0xff, sizeof(int) * static_cast<size_t>(max_rows), stream));
   moe_hist_kernel<<<nblk, MOE_BLOCK, 0, stream>>>((const long long*)expert, C, E, (int*)hist);
   NX_LAUNCH_CHECK();
@@ -192,29 +192,29 @@ NX_API int nx_moe_plan(const void* expert, int C, int E, void* hist, void* base,
   return NX_OK;
 }
 
-NX_API int nx_moe_gather_rows(const void* src, long long lds, const void* src_copy, const void* scale, int k, void* out,
+NX_API int NX_SYM(nx_moe_gather_rows)(const void* src, long long lds, const void* src_copy, const void* scale, int k, void* out,
                               int rows, int H, cudaStream_t stream) {
   NX_REQUIRE(H % 8 == 0 && lds % 8 == 0, "moe_gather_rows: hidden size must be a multiple of 8");
-  moe_gather_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>((const __nv_bfloat16*)src, lds, (const int*)src_copy,
-                                                             (const __nv_bfloat16*)scale, k, (__nv_bfloat16*)out, rows, H);
+  moe_gather_rows_kernel<<<(rows + 7) / 8, 256, 0, stream>>>((const h16*)src, lds, (const int*)src_copy,
+                                                             (const h16*)scale, k, (h16*)out, rows, H);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
 
-NX_API int nx_moe_combine(const void* y, const void* dest_row, const void* w, int k, void* out, int T, int H,
+NX_API int NX_SYM(nx_moe_combine)(const void* y, const void* dest_row, const void* w, int k, void* out, int T, int H,
                           cudaStream_t stream) {
   NX_REQUIRE(H % 8 == 0, "moe_combine: hidden size must be a multiple of 8");
-  moe_combine_kernel<<<(T + 7) / 8, 256, 0, stream>>>((const __nv_bfloat16*)y, (const int*)dest_row,
-                                                      (const __nv_bfloat16*)w, k, (__nv_bfloat16*)out, T, H);
+  moe_combine_kernel<<<(T + 7) / 8, 256, 0, stream>>>((const h16*)y, (const int*)dest_row,
+                                                      (const h16*)w, k, (h16*)out, T, H);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
 
-NX_API int nx_moe_weight_grad(const void* g, const void* y, const void* dest_row, int k, void* dw, int C, int H,
+NX_API int NX_SYM(nx_moe_weight_grad)(const void* g, const void* y, const void* dest_row, int k, void* dw, int C, int H,
                               cudaStream_t stream) {
   NX_REQUIRE(H % 8 == 0, "moe_weight_grad: hidden size must be a multiple of 8");
-  moe_weight_grad_kernel<<<(C + 7) / 8, 256, 0, stream>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)y,
-                                                          (const int*)dest_row, k, (__nv_bfloat16*)dw, C, H);
+  moe_weight_grad_kernel<<<(C + 7) / 8, 256, 0, stream>>>((const h16*)g, (const h16*)y,
+                                                          (const int*)dest_row, k, (h16*)dw, C, H);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }

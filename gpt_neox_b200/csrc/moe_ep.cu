@@ -57,7 +57,7 @@ __global__ void ep_stage_ids_kernel(EpPeers p, long long idx_off, int ws, int Ck
 // <unscaled source row, dot_with[row]>.  One warp per row.
 __global__ void __launch_bounds__(256)
 ep_gather_kernel(EpPeers p, long long tok_off, long long scale_off, const int* __restrict__ src_copy, int Ck, int k,
-                 __nv_bfloat16* __restrict__ out, int rows, int H, const __nv_bfloat16* __restrict__ dot_with,
+                 h16* __restrict__ out, int rows, int H, const h16* __restrict__ dot_with,
                  float* __restrict__ dot_out) {
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -72,7 +72,7 @@ ep_gather_kernel(EpPeers p, long long tok_off, long long scale_off, const int* _
   const int r = c / Ck, lc = c - r * Ck;
   const uint4* s = reinterpret_cast<const uint4*>(p.base[r] + tok_off) + static_cast<long long>(lc / k) * (H / 8);
   float w = 1.f;
-  if (scale_off >= 0) w = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.base[r] + scale_off)[lc]);
+  if (scale_off >= 0) w = h16_to_float(reinterpret_cast<const h16*>(p.base[r] + scale_off)[lc]);
   const uint4* d = dot_with ? reinterpret_cast<const uint4*>(dot_with + static_cast<long long>(row) * H) : nullptr;
   float acc = 0.f;
   for (int v = lane; v < H / 8; v += 32) {
@@ -86,12 +86,12 @@ ep_gather_kernel(EpPeers p, long long tok_off, long long scale_off, const int* _
     }
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const float2 a = unpack_bf16x2(uw[q]);
+      const float2 a = unpack_h16x2(uw[q]);
       if (d != nullptr) {
-        const float2 b = unpack_bf16x2(dw[q]);
+        const float2 b = unpack_h16x2(dw[q]);
         acc += a.x * b.x + a.y * b.y;
       }
-      ow[q] = scale_off >= 0 ? pack_bf16x2(a.x * w, a.y * w) : uw[q];
+      ow[q] = scale_off >= 0 ? pack_h16x2(a.x * w, a.y * w) : uw[q];
     }
     o[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
   }
@@ -108,8 +108,8 @@ ep_gather_kernel(EpPeers p, long long tok_off, long long scale_off, const int* _
 __global__ void __launch_bounds__(256)
 ep_combine_kernel(EpPeers p, long long rows_off, long long dest_off, long long aux_off,
                   const int* __restrict__ expert_id, int E_local, int me, int ws, int Ck, int k,
-                  const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, int T, int H,
-                  __nv_bfloat16* __restrict__ aux_out, int* err) {
+                  const h16* __restrict__ w, h16* __restrict__ out, int T, int H,
+                  h16* __restrict__ aux_out, int* err) {
   const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (t >= T) return;
   const int lane = threadIdx.x & 31;
@@ -128,22 +128,22 @@ ep_combine_kernel(EpPeers p, long long rows_off, long long dest_off, long long a
       continue;
     }
     src[j] = reinterpret_cast<const uint4*>(p.base[owner] + rows_off) + static_cast<long long>(row) * (H / 8);
-    wj[j] = w ? __bfloat162float(w[c]) : 1.f;
+    wj[j] = w ? h16_to_float(w[c]) : 1.f;
     if (aux_off >= 0 && lane == 0)
-      aux_out[c] = __float2bfloat16(reinterpret_cast<const float*>(p.base[owner] + aux_off)[row]);
+      aux_out[c] = float_to_h16(reinterpret_cast<const float*>(p.base[owner] + aux_off)[row]);
   }
   for (int v = lane; v < H / 8; v += 32) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int j = 0; j < k && j < MAXK; ++j) {
       if (src[j] == nullptr) continue;
       const uint4 u = src[j][v];
-      const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), cc = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      const float2 a = unpack_h16x2(u.x), b = unpack_h16x2(u.y), cc = unpack_h16x2(u.z), d = unpack_h16x2(u.w);
       acc[0] += wj[j] * a.x; acc[1] += wj[j] * a.y; acc[2] += wj[j] * b.x; acc[3] += wj[j] * b.y;
       acc[4] += wj[j] * cc.x; acc[5] += wj[j] * cc.y; acc[6] += wj[j] * d.x; acc[7] += wj[j] * d.y;
     }
     uint4 r;
-    r.x = pack_bf16x2(acc[0], acc[1]); r.y = pack_bf16x2(acc[2], acc[3]);
-    r.z = pack_bf16x2(acc[4], acc[5]); r.w = pack_bf16x2(acc[6], acc[7]);
+    r.x = pack_h16x2(acc[0], acc[1]); r.y = pack_h16x2(acc[2], acc[3]);
+    r.z = pack_h16x2(acc[4], acc[5]); r.w = pack_h16x2(acc[6], acc[7]);
     reinterpret_cast<uint4*>(out + static_cast<long long>(t) * H)[v] = r;
   }
 }
@@ -156,9 +156,9 @@ static EpPeers make_peers(const unsigned long long* ptrs, int ws) {
 
 }  // namespace nx
 
-NX_API int nx_moe_ep_flag_bytes() { return 4096; }
+NX_API int NX_SYM(nx_moe_ep_flag_bytes)() { return 4096; }
 
-NX_API int nx_moe_ep_barrier(const unsigned long long* peer_ptrs, int me, int ws, unsigned epoch, void* stream_) {
+NX_API int NX_SYM(nx_moe_ep_barrier)(const unsigned long long* peer_ptrs, int me, int ws, unsigned epoch, void* stream_) {
   using namespace nx;
   NX_REQUIRE(ws >= 1 && ws <= EP_MAX_RANKS && me >= 0 && me < ws, "moe_ep_barrier: rank %d of %d", me, ws);
   ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(make_peers(peer_ptrs, ws), me, ws, epoch,
@@ -168,7 +168,7 @@ NX_API int nx_moe_ep_barrier(const unsigned long long* peer_ptrs, int me, int ws
 }
 
 // expert_local: int64 [ws * Ck] (input of nx_moe_plan with E_local experts).
-NX_API int nx_moe_ep_stage_ids(const unsigned long long* peer_ptrs, int ws, long long idx_off, int Ck, int e_lo,
+NX_API int NX_SYM(nx_moe_ep_stage_ids)(const unsigned long long* peer_ptrs, int ws, long long idx_off, int Ck, int e_lo,
                                int E_local, void* expert_local, void* stream_) {
   using namespace nx;
   NX_REQUIRE(ws >= 1 && ws <= EP_MAX_RANKS && Ck > 0 && idx_off % 4 == 0, "moe_ep_stage_ids: bad arguments");
@@ -180,7 +180,7 @@ NX_API int nx_moe_ep_stage_ids(const unsigned long long* peer_ptrs, int ws, long
 }
 
 // scale_off < 0: no scaling.  dot_with / dot_out may be null.
-NX_API int nx_moe_ep_gather(const unsigned long long* peer_ptrs, int ws, long long tok_off, long long scale_off,
+NX_API int NX_SYM(nx_moe_ep_gather)(const unsigned long long* peer_ptrs, int ws, long long tok_off, long long scale_off,
                             const void* src_copy, int Ck, int k, void* out, int rows, int H, const void* dot_with,
                             void* dot_out, void* stream_) {
   using namespace nx;
@@ -189,14 +189,14 @@ NX_API int nx_moe_ep_gather(const unsigned long long* peer_ptrs, int ws, long lo
   NX_REQUIRE((dot_with == nullptr) == (dot_out == nullptr), "moe_ep_gather: dot_with and dot_out go together");
   ep_gather_kernel<<<(rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
       make_peers(peer_ptrs, ws), tok_off, scale_off, static_cast<const int*>(src_copy), Ck, k,
-      static_cast<__nv_bfloat16*>(out), rows, H, static_cast<const __nv_bfloat16*>(dot_with),
+      static_cast<h16*>(out), rows, H, static_cast<const h16*>(dot_with),
       static_cast<float*>(dot_out));
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
 
 // aux_off < 0: no per-copy scalar.  w may be null (unit weights).
-NX_API int nx_moe_ep_combine(const unsigned long long* peer_ptrs, int ws, int me, long long rows_off,
+NX_API int NX_SYM(nx_moe_ep_combine)(const unsigned long long* peer_ptrs, int ws, int me, long long rows_off,
                              long long dest_off, long long aux_off, const void* expert_id, int E_local, int Ck, int k,
                              const void* w, void* out, int T, int H, void* aux_out, void* stream_) {
   using namespace nx;
@@ -205,8 +205,8 @@ NX_API int nx_moe_ep_combine(const unsigned long long* peer_ptrs, int ws, int me
   NX_REQUIRE(k >= 1 && k <= 8 && T * k == Ck, "moe_ep_combine: k=%d T=%d Ck=%d", k, T, Ck);
   ep_combine_kernel<<<(T + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream_)>>>(
       make_peers(peer_ptrs, ws), rows_off, dest_off, aux_off, static_cast<const int*>(expert_id), E_local, me, ws, Ck, k,
-      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(out), T, H,
-      static_cast<__nv_bfloat16*>(aux_out), device_error_word());
+      static_cast<const h16*>(w), static_cast<h16*>(out), T, H,
+      static_cast<h16*>(aux_out), device_error_word());
   NX_LAUNCH_CHECK();
   return NX_OK;
 }

@@ -21,25 +21,25 @@ namespace nx {
 constexpr int MAXV = 4;  // 16-byte vectors cached per thread
 
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
-  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z),
-               d = unpack_bf16x2(u.w);
+  const float2 a = unpack_h16x2(u.x), b = unpack_h16x2(u.y), c = unpack_h16x2(u.z),
+               d = unpack_h16x2(u.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
 __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   uint4 u;
-  u.x = pack_bf16x2(f[0], f[1]);
-  u.y = pack_bf16x2(f[2], f[3]);
-  u.z = pack_bf16x2(f[4], f[5]);
-  u.w = pack_bf16x2(f[6], f[7]);
+  u.x = pack_h16x2(f[0], f[1]);
+  u.y = pack_h16x2(f[2], f[3]);
+  u.z = pack_h16x2(f[4], f[5]);
+  u.w = pack_h16x2(f[6], f[7]);
   return u;
 }
 
 template <bool RMS>
-__global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
-                                const __nv_bfloat16* __restrict__ g1,
-                                const __nv_bfloat16* __restrict__ b1, __nv_bfloat16* __restrict__ y1,
-                                const __nv_bfloat16* __restrict__ g2,
-                                const __nv_bfloat16* __restrict__ b2, __nv_bfloat16* __restrict__ y2,
+__global__ void norm_fwd_kernel(const h16* __restrict__ x,
+                                const h16* __restrict__ g1,
+                                const h16* __restrict__ b1, h16* __restrict__ y1,
+                                const h16* __restrict__ g2,
+                                const h16* __restrict__ b2, h16* __restrict__ y2,
                                 float* __restrict__ mean_out, float* __restrict__ rstd_out, int H,
                                 float eps) {
   __shared__ float sh[64];
@@ -117,11 +117,11 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
 // up to H = 4096, one up to 8192) is the fast form; wider rows take 4 or 8 groups per thread.
 template <bool RMS, int VPT, bool DUAL>
 __global__ void __launch_bounds__(VPT == 1 ? 1024 : 512, 1)
-norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy1, const __nv_bfloat16* __restrict__ dy2,
-                const __nv_bfloat16* __restrict__ x, const float* __restrict__ mean_in,
-                const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ gamma1,
-                const __nv_bfloat16* __restrict__ gamma2, const __nv_bfloat16* __restrict__ dx_in,
-                __nv_bfloat16* __restrict__ dx, float* __restrict__ ws, long long rows, int H) {
+norm_bwd_kernel(const h16* __restrict__ dy1, const h16* __restrict__ dy2,
+                const h16* __restrict__ x, const float* __restrict__ mean_in,
+                const float* __restrict__ rstd_in, const h16* __restrict__ gamma1,
+                const h16* __restrict__ gamma2, const h16* __restrict__ dx_in,
+                h16* __restrict__ dx, float* __restrict__ ws, long long rows, int H) {
   __shared__ float sh[64];
   constexpr int NOUT = DUAL ? 4 : 2;
   const int nv = H >> 3;
@@ -258,7 +258,7 @@ static int threads_for(int H) {
 }  // namespace nx
 
 // kind: 0 = LayerNorm, 1 = RMSNorm.  g2/b2/y2 null -> single output.  beta pointers may be null.
-NX_API int nx_norm_fwd(int kind, const void* x, const void* g1, const void* b1, void* y1,
+NX_API int NX_SYM(nx_norm_fwd)(int kind, const void* x, const void* g1, const void* b1, void* y1,
                        const void* g2, const void* b2, void* y2, void* mean, void* rstd,
                        long long rows, int H, float eps, void* stream_) {
   using namespace nx;
@@ -268,7 +268,7 @@ NX_API int nx_norm_fwd(int kind, const void* x, const void* g1, const void* b1, 
   NX_REQUIRE(rows < (1ll << 31), "norm: too many rows");
   auto s = static_cast<cudaStream_t>(stream_);
   const int t = threads_for(H);
-  using bf = __nv_bfloat16;
+  using bf = h16;
   if (kind == 0)
     norm_fwd_kernel<false><<<(unsigned)rows, t, 0, s>>>((const bf*)x, (const bf*)g1, (const bf*)b1,
                                                          (bf*)y1, (const bf*)g2, (const bf*)b2,
@@ -282,7 +282,7 @@ NX_API int nx_norm_fwd(int kind, const void* x, const void* g1, const void* b1, 
 }
 
 // Number of persistent blocks the backward uses == rows of the fp32 workspace [blocks, 2 or 4, H].
-NX_API int nx_norm_bwd_blocks(long long rows) {
+NX_API int NX_SYM(nx_norm_bwd_blocks)(long long rows) {
   const long long cap = static_cast<long long>(nx::sm_count()) * 2;
   return static_cast<int>(rows < cap ? rows : cap);
 }
@@ -293,7 +293,7 @@ static void launch_norm_bwd(int blocks, int threads, cudaStream_t s, const void*
                             const void* x, const void* mean, const void* rstd, const void* g1,
                             const void* g2, const void* dx_in, void* dx, void* ws, long long rows,
                             int H) {
-  using bf = __nv_bfloat16;
+  using bf = h16;
   norm_bwd_kernel<RMS, VPT, DUAL><<<blocks, threads, 0, s>>>(
       (const bf*)dy1, (const bf*)dy2, (const bf*)x, (const float*)mean, (const float*)rstd,
       (const bf*)g1, (const bf*)g2, (const bf*)dx_in, (bf*)dx, (float*)ws, rows, H);
@@ -303,7 +303,7 @@ static void launch_norm_bwd(int blocks, int threads, cudaStream_t s, const void*
 // dx = dx_in (optional) + backward of the norm(s) of x.  dy2 / gamma2 non-null: the two norms of a
 // dual forward, both gradients in one pass.  dgamma* / dbeta* fp32 (a null one is skipped;
 // accumulate != 0 adds into them).  ws: fp32 workspace of nx_norm_bwd_blocks(rows) * (dy2 ? 4 : 2) * H.
-NX_API int nx_norm_bwd(int kind, const void* dy1, const void* dy2, const void* x, const void* mean,
+NX_API int NX_SYM(nx_norm_bwd)(int kind, const void* dy1, const void* dy2, const void* x, const void* mean,
                        const void* rstd, const void* gamma1, const void* gamma2, const void* dx_in,
                        void* dx, void* dgamma1, void* dbeta1, void* dgamma2, void* dbeta2, void* ws,
                        long long rows, int H, int accumulate, void* stream_) {
@@ -317,7 +317,7 @@ NX_API int nx_norm_bwd(int kind, const void* dy1, const void* dy2, const void* x
   const int vpt = nv <= 1024 ? 1 : (nv <= 2048 ? 4 : 8);
   int threads = ((nv + vpt - 1) / vpt + 31) / 32 * 32;
   if (threads < 64) threads = 64;
-  const int blocks = nx_norm_bwd_blocks(rows);
+  const int blocks = NX_SYM(nx_norm_bwd_blocks)(rows);
   const bool dual = dy2 != nullptr, rms = kind != 0;
 #define NX_NORM_BWD(R, V, D)                                                                        \
   launch_norm_bwd<R, V, D>(blocks, threads, s, dy1, dy2, x, mean, rstd, gamma1, gamma2, dx_in, dx, \

@@ -25,15 +25,15 @@ __device__ __forceinline__ float4 load_grad4<float>(const float* g, long long i)
   return *reinterpret_cast<const float4*>(g + i);
 }
 template <>
-__device__ __forceinline__ float4 load_grad4<__nv_bfloat16>(const __nv_bfloat16* g, long long i) {
+__device__ __forceinline__ float4 load_grad4<h16>(const h16* g, long long i) {
   const uint2 u = *reinterpret_cast<const uint2*>(g + i);
-  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+  const float2 a = unpack_h16x2(u.x), b = unpack_h16x2(u.y);
   return make_float4(a.x, a.y, b.x, b.y);
 }
 
 template <typename G>
 __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
-                             const G* __restrict__ g, __nv_bfloat16* __restrict__ p_bf16,
+                             const G* __restrict__ g, h16* __restrict__ p_bf16,
                              long long n, AdamArgs a, const float* __restrict__ grad_scale,
                              const int* __restrict__ skip) {
   if (skip != nullptr && *skip != 0) return;
@@ -65,14 +65,14 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
       *reinterpret_cast<float4*>(v + i) = make_float4(vvv[0], vvv[1], vvv[2], vvv[3]);
       if (p_bf16 != nullptr) {
         uint2 o;
-        o.x = pack_bf16x2(pp[0], pp[1]);
-        o.y = pack_bf16x2(pp[2], pp[3]);
+        o.x = pack_h16x2(pp[0], pp[1]);
+        o.y = pack_h16x2(pp[2], pp[3]);
         *reinterpret_cast<uint2*>(p_bf16 + i) = o;
       }
     } else {
       for (long long j = i; j < n; ++j) {
         float gr;
-        if (sizeof(G) == 2) gr = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g)[j]);
+        if (sizeof(G) == 2) gr = h16_to_float(reinterpret_cast<const h16*>(g)[j]);
         else gr = reinterpret_cast<const float*>(g)[j];
         gr *= gs;
         float pj = p[j];
@@ -83,7 +83,7 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
         if (a.adam_w_mode) pj -= a.lr * a.weight_decay * pj;
         pj -= step * (mj / denom);
         p[j] = pj; m[j] = mj; v[j] = vj;
-        if (p_bf16 != nullptr) p_bf16[j] = __float2bfloat16(pj);
+        if (p_bf16 != nullptr) p_bf16[j] = float_to_h16(pj);
       }
     }
   }
@@ -103,7 +103,7 @@ __global__ void sumsq_kernel(const G* __restrict__ x, long long n, float* __rest
     } else {
       for (long long j = i; j < n; ++j) {
         float f;
-        if (sizeof(G) == 2) f = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[j]);
+        if (sizeof(G) == 2) f = h16_to_float(reinterpret_cast<const h16*>(x)[j]);
         else f = reinterpret_cast<const float*>(x)[j];
         s += f * f;
       }
@@ -133,7 +133,7 @@ __global__ void clip_coef_kernel(const float* __restrict__ acc, float max_norm, 
 
 // grad_dtype: 0 = bf16, 1 = fp32.  grad_scale (device float*, nullable) multiplies every gradient;
 // skip (device int*, nullable) non-zero turns the launch into a no-op.
-NX_API int nx_adamw_step(void* p, void* m, void* v, const void* g, void* p_bf16, long long n,
+NX_API int NX_SYM(nx_adamw_step)(void* p, void* m, void* v, const void* g, void* p_bf16, long long n,
                          float lr, float beta1, float beta2, float eps, float weight_decay,
                          float bias_corr1, float bias_corr2, int adam_w_mode,
                          const void* grad_scale, const void* skip, int grad_dtype, void* stream_) {
@@ -146,17 +146,17 @@ NX_API int nx_adamw_step(void* p, void* m, void* v, const void* g, void* p_bf16,
   const int grid = static_cast<int>(g_ < cap ? g_ : cap);
   auto s = (cudaStream_t)stream_;
   if (grad_dtype == 0)
-    adamw_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((float*)p, (float*)m, (float*)v,
-                                                     (const __nv_bfloat16*)g, (__nv_bfloat16*)p_bf16,
+    adamw_kernel<h16><<<grid, 256, 0, s>>>((float*)p, (float*)m, (float*)v,
+                                                     (const h16*)g, (h16*)p_bf16,
                                                      n, a, (const float*)grad_scale, (const int*)skip);
   else
     adamw_kernel<float><<<grid, 256, 0, s>>>((float*)p, (float*)m, (float*)v, (const float*)g,
-                                             (__nv_bfloat16*)p_bf16, n, a, (const float*)grad_scale,
+                                             (h16*)p_bf16, n, a, (const float*)grad_scale,
                                              (const int*)skip);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_sumsq(const void* x, long long n, void* acc, int dtype, void* stream_) {
+NX_API int NX_SYM(nx_sumsq)(const void* x, long long n, void* acc, int dtype, void* stream_) {
   using namespace nx;
   if (n == 0) return NX_OK;
   const long long nvec = (n + 3) / 4;
@@ -164,12 +164,12 @@ NX_API int nx_sumsq(const void* x, long long n, void* acc, int dtype, void* stre
   const long long cap = static_cast<long long>(sm_count()) * 8;
   const int grid = static_cast<int>(g_ < cap ? g_ : cap);
   auto s = (cudaStream_t)stream_;
-  if (dtype == 0) sumsq_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, n, (float*)acc);
+  if (dtype == 0) sumsq_kernel<h16><<<grid, 256, 0, s>>>((const h16*)x, n, (float*)acc);
   else sumsq_kernel<float><<<grid, 256, 0, s>>>((const float*)x, n, (float*)acc);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_clip_coef(const void* acc, float max_norm, float inv_scale, void* out, void* skip,
+NX_API int NX_SYM(nx_clip_coef)(const void* acc, float max_norm, float inv_scale, void* out, void* skip,
                         void* stream_) {
   nx::clip_coef_kernel<<<1, 1, 0, (cudaStream_t)stream_>>>((const float*)acc, max_norm, inv_scale,
                                                            (float*)out, (int*)skip);

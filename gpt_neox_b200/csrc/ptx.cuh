@@ -6,8 +6,17 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+// The 16-bit floating-point storage type of this build of the kernels (see common.h: the same
+// sources are compiled for bf16 and, with -DNX_HALF, for fp16).
+#ifdef NX_HALF
+using h16 = __half;
+#else
+using h16 = __nv_bfloat16;
+#endif
 
 namespace nx {
 
@@ -290,12 +299,17 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
-// Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
-// c_format (F32=1) at bit 4, a/b format (BF16=1) at bits 7/10, a/b major (1 = MN-major)
-// at bits 15/16, N>>3 at bit 17, M>>4 at bit 24.
+// Instruction descriptor for kind::f16 with 16-bit inputs (bf16, or fp16 in the NX_HALF build) and
+// fp32 accumulation.  c_format (F32=1) at bit 4, a/b format (F16=0, BF16=1) at bits 7/10, a/b major
+// (1 = MN-major) at bits 15/16, N>>3 at bit 17, M>>4 at bit 24.
+#ifdef NX_HALF
+constexpr uint32_t UMMA_AB_FORMAT = 0u;
+#else
+constexpr uint32_t UMMA_AB_FORMAT = 1u;
+#endif
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_mn_major,
                                                        int b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+  return (1u << 4) | (UMMA_AB_FORMAT << 7) | (UMMA_AB_FORMAT << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
          (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
          (static_cast<uint32_t>(M >> 4) << 24);
 }
@@ -333,7 +347,11 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target,
 // 16-byte switch-side reduction load of 8 bf16 values with fp32 accumulation.
 __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_ptr) {
   uint4 v;
+#ifdef NX_HALF
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+#else
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+#endif
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(mc_ptr)
                : "memory");
@@ -401,13 +419,28 @@ __device__ __forceinline__ float silu_grad(float x) {
   return s * (1.0f + x * (1.0f - s));
 }
 
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+#ifdef NX_HALF
+__device__ __forceinline__ uint32_t pack_h16x2(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float2 unpack_h16x2(uint32_t u) {
+  __half2 v = *reinterpret_cast<__half2*>(&u);
+  return __half22float2(v);
+}
+__device__ __forceinline__ float h16_to_float(h16 x) { return __half2float(x); }
+__device__ __forceinline__ h16 float_to_h16(float x) { return __float2half_rn(x); }
+#else
+__device__ __forceinline__ uint32_t pack_h16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
+__device__ __forceinline__ float2 unpack_h16x2(uint32_t u) {
   __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
   return __bfloat1622float2(v);
 }
+__device__ __forceinline__ float h16_to_float(h16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ h16 float_to_h16(float x) { return __float2bfloat16(x); }
+#endif
 
 }  // namespace nx

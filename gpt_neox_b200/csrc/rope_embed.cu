@@ -18,8 +18,8 @@
 namespace nx {
 
 struct RopeArgs {
-  const __nv_bfloat16* in;
-  __nv_bfloat16* out;
+  const h16* in;
+  h16* out;
   const float* cos;  // [max_pos, r/2]
   const float* sin;
   int S, B, NH, D, R;
@@ -42,14 +42,14 @@ __global__ void rope_kernel(const RopeArgs a) {
     t /= a.NH;
     const int b = static_cast<int>(t % a.B);
     const int s = static_cast<int>(t / a.B);
-    const __nv_bfloat16* ip = a.in + s * a.is + b * a.ib + h * a.ih;
-    __nv_bfloat16* op = a.out + s * a.os + b * a.ob + h * a.oh;
+    const h16* ip = a.in + s * a.is + b * a.ib + h * a.ih;
+    h16* op = a.out + s * a.os + b * a.ob + h * a.oh;
     if (j < half) {
       const float c = a.cos[static_cast<long long>(a.pos0 + s) * half + j];
       const float sn = a.sin[static_cast<long long>(a.pos0 + s) * half + j] * a.sin_sign;
-      const float x1 = __bfloat162float(ip[j]), x2 = __bfloat162float(ip[j + half]);
-      op[j] = __float2bfloat16(x1 * c - x2 * sn);
-      op[j + half] = __float2bfloat16(x2 * c + x1 * sn);
+      const float x1 = h16_to_float(ip[j]), x2 = h16_to_float(ip[j + half]);
+      op[j] = float_to_h16(x1 * c - x2 * sn);
+      op[j + half] = float_to_h16(x2 * c + x1 * sn);
     } else {
       const int d = a.R + (j - half);
       op[d] = ip[d];
@@ -72,7 +72,7 @@ __global__ void rope_vec8_kernel(const RopeArgs a) {
     t /= a.NH;
     const int b = static_cast<int>(t % a.B);
     const int s = static_cast<int>(t / a.B);
-    __nv_bfloat16* ptr = a.out + s * a.os + b * a.ob + h * a.oh;
+    h16* ptr = a.out + s * a.os + b * a.ob + h * a.oh;
     const uint4 u1 = *reinterpret_cast<const uint4*>(ptr + j);
     const uint4 u2 = *reinterpret_cast<const uint4*>(ptr + j + half);
     const float4* cp = reinterpret_cast<const float4*>(a.cos + static_cast<long long>(a.pos0 + s) * half + j);
@@ -84,10 +84,10 @@ __global__ void rope_vec8_kernel(const RopeArgs a) {
     uint32_t o1[4], o2[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const float2 x1 = unpack_bf16x2(w1[q]), x2 = unpack_bf16x2(w2[q]);
+      const float2 x1 = unpack_h16x2(w1[q]), x2 = unpack_h16x2(w2[q]);
       const float sa = sn[2 * q] * a.sin_sign, sb = sn[2 * q + 1] * a.sin_sign;
-      o1[q] = pack_bf16x2(x1.x * c[2 * q] - x2.x * sa, x1.y * c[2 * q + 1] - x2.y * sb);
-      o2[q] = pack_bf16x2(x2.x * c[2 * q] + x1.x * sa, x2.y * c[2 * q + 1] + x1.y * sb);
+      o1[q] = pack_h16x2(x1.x * c[2 * q] - x2.x * sa, x1.y * c[2 * q + 1] - x2.y * sb);
+      o2[q] = pack_h16x2(x2.x * c[2 * q] + x1.x * sa, x2.y * c[2 * q + 1] + x1.y * sb);
     }
     *reinterpret_cast<uint4*>(ptr + j) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
     *reinterpret_cast<uint4*>(ptr + j + half) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
@@ -95,8 +95,8 @@ __global__ void rope_vec8_kernel(const RopeArgs a) {
 }
 
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids,
-                                     const __nv_bfloat16* __restrict__ table,
-                                     __nv_bfloat16* __restrict__ out, long long n, int H,
+                                     const h16* __restrict__ table,
+                                     h16* __restrict__ out, long long n, int H,
                                      long long vocab_start, long long v_local) {
   const int h8 = H >> 3;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n * h8;
@@ -111,7 +111,7 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ ids,
 }
 // grad_table (fp32) [v_local, H] += dout rows
 __global__ void embedding_bwd_kernel(const long long* __restrict__ ids,
-                                     const __nv_bfloat16* __restrict__ dout,
+                                     const h16* __restrict__ dout,
                                      float* __restrict__ grad_table, long long n, int H,
                                      long long vocab_start, long long v_local) {
   const int h2 = H >> 1;
@@ -121,7 +121,7 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids,
     const int c = static_cast<int>(i - r * h2) * 2;
     const long long id = ids[r] - vocab_start;
     if (id >= 0 && id < v_local) {
-      const float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dout + r * H + c));
+      const float2 g = unpack_h16x2(*reinterpret_cast<const uint32_t*>(dout + r * H + c));
       atomicAdd(grad_table + id * H + c, g.x);
       atomicAdd(grad_table + id * H + c + 1, g.y);
     }
@@ -130,14 +130,14 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids,
 
 }  // namespace nx
 
-NX_API int nx_rope(const void* in, void* out, const void* cos, const void* sin, int S, int B, int NH,
+NX_API int NX_SYM(nx_rope)(const void* in, void* out, const void* cos, const void* sin, int S, int B, int NH,
                    int D, int R, long long is, long long ib, long long ih, long long os,
                    long long ob, long long oh, int pos0, int inverse, void* stream_) {
   using namespace nx;
   NX_REQUIRE(R % 2 == 0 && R <= D, "rope: rotary dims %d invalid for head dim %d", R, D);
   if (S == 0 || B == 0 || NH == 0 || (R == 0 && in == out)) return NX_OK;
   RopeArgs a;
-  a.in = (const __nv_bfloat16*)in; a.out = (__nv_bfloat16*)out;
+  a.in = (const h16*)in; a.out = (h16*)out;
   a.cos = (const float*)cos; a.sin = (const float*)sin;
   a.S = S; a.B = B; a.NH = NH; a.D = D; a.R = R;
   a.is = is; a.ib = ib; a.ih = ih; a.os = os; a.ob = ob; a.oh = oh;
@@ -160,7 +160,7 @@ NX_API int nx_rope(const void* in, void* out, const void* cos, const void* sin, 
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_embedding_fwd(const void* ids, const void* table, void* out, long long n, int H,
+NX_API int NX_SYM(nx_embedding_fwd)(const void* ids, const void* table, void* out, long long n, int H,
                             long long vocab_start, long long v_local, void* stream_) {
   using namespace nx;
   NX_REQUIRE(H % 8 == 0, "embedding: H %% 8 != 0");
@@ -168,12 +168,12 @@ NX_API int nx_embedding_fwd(const void* ids, const void* table, void* out, long 
   long long g = (n * (H / 8) + 255) / 256;
   const long long cap = static_cast<long long>(sm_count()) * 16;
   embedding_fwd_kernel<<<(int)(g < cap ? g : cap), 256, 0, (cudaStream_t)stream_>>>(
-      (const long long*)ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, n, H, vocab_start,
+      (const long long*)ids, (const h16*)table, (h16*)out, n, H, vocab_start,
       v_local);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_embedding_bwd(const void* ids, const void* dout, void* grad_table, long long n, int H,
+NX_API int NX_SYM(nx_embedding_bwd)(const void* ids, const void* dout, void* grad_table, long long n, int H,
                             long long vocab_start, long long v_local, void* stream_) {
   using namespace nx;
   NX_REQUIRE(H % 2 == 0, "embedding: H %% 2 != 0");
@@ -181,7 +181,7 @@ NX_API int nx_embedding_bwd(const void* ids, const void* dout, void* grad_table,
   long long g = (n * (H / 2) + 255) / 256;
   const long long cap = static_cast<long long>(sm_count()) * 16;
   embedding_bwd_kernel<<<(int)(g < cap ? g : cap), 256, 0, (cudaStream_t)stream_>>>(
-      (const long long*)ids, (const __nv_bfloat16*)dout, (float*)grad_table, n, H, vocab_start,
+      (const long long*)ids, (const h16*)dout, (float*)grad_table, n, H, vocab_start,
       v_local);
   NX_LAUNCH_CHECK();
   return NX_OK;

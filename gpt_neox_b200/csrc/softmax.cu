@@ -16,15 +16,15 @@ namespace nx {
 
 // One block per row; generic in row length.
 template <bool CAUSAL>
-__global__ void softmax_fwd_kernel(const __nv_bfloat16* __restrict__ x,
-                                   __nv_bfloat16* __restrict__ y, const uint8_t* __restrict__ mask,
+__global__ void softmax_fwd_kernel(const h16* __restrict__ x,
+                                   h16* __restrict__ y, const uint8_t* __restrict__ mask,
                                    int sq, int sk, int np, int mask_batch_stride_is_zero,
                                    float scale) {
   __shared__ float sh[64];
   const long long row = blockIdx.x;  // over attn_batches * sq
   const int qi = static_cast<int>(row % sq);
-  const __nv_bfloat16* xr = x + row * sk;
-  __nv_bfloat16* yr = y + row * sk;
+  const h16* xr = x + row * sk;
+  h16* yr = y + row * sk;
   const int limit = CAUSAL ? min(sk, qi + 1 + (sk - sq)) : sk;
   const uint8_t* mr = nullptr;
   if (!CAUSAL && mask != nullptr) {
@@ -33,14 +33,14 @@ __global__ void softmax_fwd_kernel(const __nv_bfloat16* __restrict__ x,
   }
   float mx = -INFINITY;
   for (int c = threadIdx.x; c < limit; c += blockDim.x) {
-    float v = __bfloat162float(xr[c]) * scale;
+    float v = h16_to_float(xr[c]) * scale;
     if (mr != nullptr && mr[c]) v = -10000.f;
     mx = fmaxf(mx, v);
   }
   mx = block_max(mx, sh);
   float sum = 0.f;
   for (int c = threadIdx.x; c < limit; c += blockDim.x) {
-    float v = __bfloat162float(xr[c]) * scale;
+    float v = h16_to_float(xr[c]) * scale;
     if (mr != nullptr && mr[c]) v = -10000.f;
     sum += __expf(v - mx);
   }
@@ -49,29 +49,29 @@ __global__ void softmax_fwd_kernel(const __nv_bfloat16* __restrict__ x,
   for (int c = threadIdx.x; c < sk; c += blockDim.x) {
     float o = 0.f;
     if (c < limit) {
-      float v = __bfloat162float(xr[c]) * scale;
+      float v = h16_to_float(xr[c]) * scale;
       if (mr != nullptr && mr[c]) v = -10000.f;
       o = __expf(v - mx) * inv;
     }
-    yr[c] = __float2bfloat16(o);
+    yr[c] = float_to_h16(o);
   }
 }
 
 // dx = scale * y * (dy - sum(dy * y))
-__global__ void softmax_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
-                                   const __nv_bfloat16* __restrict__ y,
-                                   __nv_bfloat16* __restrict__ dx, int sk, float scale) {
+__global__ void softmax_bwd_kernel(const h16* __restrict__ dy,
+                                   const h16* __restrict__ y,
+                                   h16* __restrict__ dx, int sk, float scale) {
   __shared__ float sh[64];
   const long long row = blockIdx.x;
-  const __nv_bfloat16* dyr = dy + row * sk;
-  const __nv_bfloat16* yr = y + row * sk;
+  const h16* dyr = dy + row * sk;
+  const h16* yr = y + row * sk;
   float s = 0.f;
   for (int c = threadIdx.x; c < sk; c += blockDim.x)
-    s += __bfloat162float(dyr[c]) * __bfloat162float(yr[c]);
+    s += h16_to_float(dyr[c]) * h16_to_float(yr[c]);
   s = block_sum(s, sh);
   for (int c = threadIdx.x; c < sk; c += blockDim.x) {
-    const float yv = __bfloat162float(yr[c]);
-    dx[row * sk + c] = __float2bfloat16(scale * yv * (__bfloat162float(dyr[c]) - s));
+    const float yv = h16_to_float(yr[c]);
+    dx[row * sk + c] = float_to_h16(scale * yv * (h16_to_float(dyr[c]) - s));
   }
 }
 
@@ -79,9 +79,9 @@ static int softmax_threads(int sk) { return sk <= 256 ? 64 : (sk <= 1024 ? 128 :
 
 }  // namespace nx
 
-using bf = __nv_bfloat16;
+using bf = h16;
 
-NX_API int nx_softmax_causal_fwd(const void* x, void* y, long long attn_batches, int sq, int sk,
+NX_API int NX_SYM(nx_softmax_causal_fwd)(const void* x, void* y, long long attn_batches, int sq, int sk,
                                  float scale, void* stream_) {
   using namespace nx;
   const long long rows = attn_batches * sq;
@@ -92,7 +92,7 @@ NX_API int nx_softmax_causal_fwd(const void* x, void* y, long long attn_batches,
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_softmax_masked_fwd(const void* x, const void* mask, void* y, int b, int np, int sq,
+NX_API int NX_SYM(nx_softmax_masked_fwd)(const void* x, const void* mask, void* y, int b, int np, int sq,
                                  int sk, int mask_batch, float scale, void* stream_) {
   using namespace nx;
   const long long rows = static_cast<long long>(b) * np * sq;
@@ -104,7 +104,7 @@ NX_API int nx_softmax_masked_fwd(const void* x, const void* mask, void* y, int b
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
-NX_API int nx_softmax_bwd(const void* dy, const void* y, void* dx, long long rows, int sk, float scale,
+NX_API int NX_SYM(nx_softmax_bwd)(const void* dy, const void* y, void* dx, long long rows, int sk, float scale,
                           void* stream_) {
   using namespace nx;
   if (rows == 0) return NX_OK;
@@ -117,7 +117,7 @@ NX_API int nx_softmax_bwd(const void* dy, const void* y, void* dx, long long row
 // Parity with the reference's scaled_masked_softmax_cuda.get_batch_per_block
 // (megatron/fused_kernels/scaled_masked_softmax.h:338-352): rows one 128-thread block of the
 // warp-per-row scheme would cover. Only used by callers that size their launches from it.
-NX_API int nx_softmax_batch_per_block(int sq, int sk, int b, int np) {
+NX_API int NX_SYM(nx_softmax_batch_per_block)(int sq, int sk, int b, int np) {
   int p2 = 1;
   while (p2 < sk) p2 <<= 1;
   const int warp_size = p2 < 32 ? p2 : 32;

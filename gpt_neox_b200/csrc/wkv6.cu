@@ -28,7 +28,7 @@ constexpr int WK_SUB = 16;
 struct WkvParams {
   // "a/b/c" roles: column sweep out[j] = sum_i a[i] (u[i] b[i] c[j] + S[i][j]),  S += b[i] c[j]
   //                row sweep    out[i] = sum_j a[j] (u[i] b[i] c[j] + S[i][j]),  S += b[i] c[j]
-  const __nv_bfloat16 *a, *b, *c, *w;
+  const h16 *a, *b, *c, *w;
   long long sb, st;                 // batch / time strides (elements) shared by a, b, c, w
   const float* u;                   // [H, N]
   void* out;                        // [B, T, C] contiguous in (osb, ost); bf16 or fp32
@@ -40,7 +40,7 @@ struct WkvParams {
   int B, T, H, NC;
 };
 
-__device__ __forceinline__ float ldb(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float ldb(const h16* p) { return h16_to_float(*p); }
 
 template <int N>
 struct WkvStage {
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(N) wkv_fold_kernel(const WkvParams p) {
 template <int N>
 __device__ __forceinline__ void wkv_store(const WkvParams& p, long long o, float v) {
   if (p.out_f32) reinterpret_cast<float*>(p.out)[o] = v;
-  else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16(v);
+  else reinterpret_cast<h16*>(p.out)[o] = float_to_h16(v);
 }
 
 // ROW = false: thread j owns S[:, j]; ROW = true: thread i owns S[i, :].
@@ -186,18 +186,18 @@ static int wkv_run(const WkvParams& p, int mode, cudaStream_t stream) {
   return NX_OK;
 }
 
-NX_API int nx_wkv6_chunks(int T) { return (T + WK_CHUNK - 1) / WK_CHUNK; }
+NX_API int NX_SYM(nx_wkv6_chunks)(int T) { return (T + WK_CHUNK - 1) / WK_CHUNK; }
 
 // mode: 0/1 local state fwd/rev, 2/3 fold fwd/rev, 4 y, 5 gv, 6 gr, 7 gk (see wkv_run).
 // a, b, c, w: bf16 [B, T, H*N] addressed by (sb, st); u fp32 [H, N]; out bf16 or fp32 by (osb, ost).
 // local / start: fp32 [B, H, NC, N, N]; sumew fp32 [B, H, NC, N].
-NX_API int nx_wkv6_pass(int mode, const void* a, const void* b, const void* c, const void* w, long long sb,
+NX_API int NX_SYM(nx_wkv6_pass)(int mode, const void* a, const void* b, const void* c, const void* w, long long sb,
                         long long st, const void* u, void* out, long long osb, long long ost, int out_f32,
                         void* local, void* start, void* sumew, int B, int T, int H, int N, cudaStream_t stream) {
   NX_REQUIRE(N == 64 || N == 32, "wkv6: head size %d not supported (32 or 64)", N);
   WkvParams p{};
-  p.a = (const __nv_bfloat16*)a; p.b = (const __nv_bfloat16*)b; p.c = (const __nv_bfloat16*)c;
-  p.w = (const __nv_bfloat16*)w; p.sb = sb; p.st = st; p.u = (const float*)u;
+  p.a = (const h16*)a; p.b = (const h16*)b; p.c = (const h16*)c;
+  p.w = (const h16*)w; p.sb = sb; p.st = st; p.u = (const float*)u;
   p.out = out; p.osb = osb; p.ost = ost; p.out_f32 = out_f32;
   p.local = (float*)local; p.start = (float*)start; p.sumew = (float*)sumew;
   p.B = B; p.T = T; p.H = H; p.NC = (T + WK_CHUNK - 1) / WK_CHUNK;

@@ -108,7 +108,7 @@ class FlatGroup:
         from ..comm import collectives
         if not (self.device.type == "cuda" and self.dp_size > 1 and self.zero_stage >= 1
                 and collectives.get_mode() == "fused" and os.environ.get("NEOX_ZERO_SYMM", "1") != "0"
-                and grad_dtype in (torch.float32, torch.bfloat16) and self.dp_size <= 8):
+                and grad_dtype in (torch.float32, torch.bfloat16, torch.float16) and self.dp_size <= 8):
             return None
         ws, ok = None, 1
         try:

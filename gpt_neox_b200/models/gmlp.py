@@ -56,7 +56,7 @@ class TinyAttention(nn.Module):
         s, b, _ = x.shape
         qkv = linear(x, self.proj_qkv.weight, self.proj_qkv.bias)
         q, k, v = (t.transpose(0, 1).unsqueeze(2) for t in qkv.chunk(3, dim=-1))      # [b, s, 1, d]
-        if x.is_cuda and x.dtype == torch.bfloat16 and self.d_attn in (64, 128):
+        if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and self.d_attn in (64, 128):
             o = flash_attention(q.contiguous(), k.contiguous(), v.contiguous(), scale=self.scale, causal=True)
         else:
             o, _ = attention_reference(q, k, v, scale=self.scale, causal=True)
@@ -89,7 +89,7 @@ class SpatialGatingUnit(nn.Module):
             weight = torch.tril(weight)
         d = gate.shape[-1]
         g2 = gate.reshape(n, b * d)
-        if g2.is_cuda and g2.dtype == torch.bfloat16 and n % 8 == 0 and (b * d) % 8 == 0:
+        if g2.is_cuda and g2.dtype in (torch.bfloat16, torch.float16) and n % 8 == 0 and (b * d) % 8 == 0:
             out = _SpatialProj.apply(weight.contiguous(), g2)
         else:
             out = weight @ g2

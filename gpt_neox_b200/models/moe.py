@@ -89,14 +89,14 @@ class ParallelDroplessMLP(nn.Module):
         in_shape = x.shape
         x2 = x.reshape(-1, x.shape[-1])
         T, k = expert_indices.shape
-        if (self.use_kernels and x.is_cuda and x.dtype == torch.bfloat16 and self.ep_size == 1 and not self.gated
+        if (self.use_kernels and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and self.ep_size == 1 and not self.gated
                 and self.mlp.activation_type == "gelu" and x2.shape[1] % 8 == 0
                 and self.mlp.per_expert_ff_dim % 8 == 0):
             from ..ops.moe import experts_gelu
             out = experts_gelu(x2.contiguous(), expert_weights, expert_indices, self.mlp.w1, self.mlp.w2,
                                self.num_experts, "tanh" if self.bias_gelu_fusion else "erf")
             return out.view(in_shape)
-        if (self.use_kernels and x.is_cuda and x.dtype == torch.bfloat16 and self.ep_size > 1 and not self.gated
+        if (self.use_kernels and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and self.ep_size > 1 and not self.gated
                 and self.mlp.activation_type == "gelu" and x2.shape[1] % 8 == 0 and self.top_k <= 8
                 and self.mlp.per_expert_ff_dim % 8 == 0):
             from ..ops import moe_ep

@@ -88,7 +88,7 @@ class _LinearNN(torch.autograd.Function):
 
 
 def _linear_nn(x, w):
-    if x.is_cuda and x.dtype == torch.bfloat16:
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16):
         return _LinearNN.apply(x, w)
     return x @ w
 

@@ -83,7 +83,7 @@ class ParallelMLP(nn.Module):
     def _fusable(self, x):
         if getattr(self.linear1, "use_fp8", False) or getattr(self.linear2, "use_fp8", False):
             return False        # fp8 GEMMs run through the per-module path
-        return (not self.is_gated) and self.activation_type == "gelu" and x.is_cuda and x.dtype == torch.bfloat16
+        return (not self.is_gated) and self.activation_type == "gelu" and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)
 
     def forward(self, hidden_states, residual=None, out_bias=None):
         """-> (output without linear2's bias, that bias). ``residual`` (optional, fused path only)
@@ -362,7 +362,7 @@ class _LinearResidualFn(torch.autograd.Function):
 
 
 def _linear_residual(x, w, residual):
-    if x.is_cuda and x.dtype == torch.bfloat16:
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16):
         return _LinearResidualFn.apply(x, w, residual)
     return F.linear(x, w) + residual
 

@@ -13,6 +13,7 @@ from pathlib import Path
 import torch
 
 _LIB = None
+_HALF = None
 _LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libneox_b200.so"
 
 c_void_p, c_int, c_ll, c_float = C.c_void_p, C.c_int, C.c_longlong, C.c_float
@@ -26,10 +27,37 @@ class DeviceWaitTimeout(RuntimeError):
     """The device error word was set: a bounded wait inside a kernel ran out."""
 
 
+#: the 16-bit floating-point dtypes the kernels are built for: every ``nx_*`` entry point that touches
+#: 16-bit tensors exists twice, ``nx_name`` for bf16 and ``nx_name_f16`` for fp16 (same signature)
+H16 = (torch.bfloat16, torch.float16)
+
+
+def is_h16(t) -> bool:
+    return t.dtype in H16
+
+
+class _HalfView:
+    """Attribute access on this object resolves ``nx_name`` to the fp16 build ``nx_name_f16`` where one
+    exists (entry points without 16-bit tensors exist once and are shared)."""
+
+    def __init__(self, lib):
+        self._lib = lib
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name + "_f16", None)
+        if fn is None:
+            fn = getattr(self._lib, name)
+        setattr(self, name, fn)
+        return fn
+
+
 def _declare(lib):
     def sig(name, argtypes, restype=c_int):
-        fn = getattr(lib, name, None)
-        if fn is not None:
+        for nm in (name, name + "_f16"):
+            try:
+                fn = getattr(lib, nm)
+            except AttributeError:
+                continue
             fn.argtypes = argtypes
             fn.restype = restype
 
@@ -95,8 +123,13 @@ def available() -> bool:
     return _LIB_PATH.exists()
 
 
-def lib():
-    global _LIB
+def lib(like=None):
+    """The kernel library.  ``like``: a tensor or dtype; for ``torch.float16`` the returned object resolves
+    every entry point to its fp16 build."""
+    global _LIB, _HALF
+    if _LIB is not None:
+        dt = getattr(like, "dtype", like)
+        return _HALF if dt == torch.float16 else _LIB
     if _LIB is None:
         if not _LIB_PATH.exists():
             raise KernelError(
@@ -104,7 +137,8 @@ def lib():
                 "(the CUDA ops have no PyTorch fallback on a GPU)"
             )
         _LIB = _declare(C.CDLL(str(_LIB_PATH), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL") else 0))
-    return _LIB
+        _HALF = _HalfView(_LIB)
+    return lib(like)
 
 
 def check(status: int, what: str = "kernel"):

@@ -70,7 +70,7 @@ def _fwd(q, k, v, scale, causal, window, alibi):
     sq_pad = (sq + 127) // 128 * 128
     lse = torch.full((b, h, sq_pad), float("inf"), device=q.device, dtype=torch.float32)
     LAUNCHES["n"] += 1
-    _lib.check(_lib.lib().nx_flash_attn_fwd(
+    _lib.check(_lib.lib(q).nx_flash_attn_fwd(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(alibi),
         b, h, hk, sq, sk, d, *_strides_bhs(q), *_strides_bhs(k), *_strides_bhs(v), *_strides_bhs(o),
         float(scale), int(causal), int(window), _lib.stream()), "nx_flash_attn_fwd")
@@ -97,7 +97,7 @@ class _FlashAttnFn(torch.autograd.Function):
         dv = torch.empty((b, sk, hk, d), device=q.device, dtype=q.dtype)
         delta = torch.zeros(lse.shape, device=q.device, dtype=torch.float32)
         LAUNCHES["n"] += 3
-        _lib.check(_lib.lib().nx_flash_attn_bwd(
+        _lib.check(_lib.lib(q).nx_flash_attn_bwd(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse),
             _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(alibi),
             b, h, hk, sq, sk, d, *_strides_bhs(q), *_strides_bhs(k), *_strides_bhs(v), *_strides_bhs(o),
@@ -113,7 +113,7 @@ def flash_attention(q, k, v, *, scale: float | None = None, causal: bool = True,
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
     window = -1 if window is None else int(window)
     if q.is_cuda:
-        if q.dtype != torch.bfloat16 or d % 8 or d > 128:
+        if q.dtype not in _lib.H16 or d % 8 or d > 128:
             raise _lib.KernelError(f"flash_attention: CUDA path needs bf16 and head dim % 8 == 0, <= 128 (got {q.dtype}, {d})")
         fix = lambda t: t if (t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0) else t.contiguous()
         if alibi is not None:

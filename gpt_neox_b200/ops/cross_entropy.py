@@ -42,9 +42,9 @@ class _VocabParallelCE(torch.autograd.Function):
         lab = labels.reshape(-1).contiguous()
         rows = l2.shape[0]
         stats = torch.empty((rows, 3), device=logits.device, dtype=torch.float32)
-        dtype = 0 if logits.dtype == torch.bfloat16 else 1
+        dtype = 1 if logits.dtype == torch.float32 else 0
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_ce_fwd(_lib.ptr(l2), _lib.ptr(lab), _lib.ptr(stats), rows, V, l2.stride(0),
+        _lib.check(_lib.lib(l2).nx_ce_fwd(_lib.ptr(l2), _lib.ptr(lab), _lib.ptr(stats), rows, V, l2.stride(0),
                                         int(vocab_start), dtype, _lib.stream()), "nx_ce_fwd")
         lse, tgt = _combine_stats(stats, group)
         ctx.save_for_backward(l2, lab, lse)
@@ -56,10 +56,10 @@ class _VocabParallelCE(torch.autograd.Function):
         l2, lab, lse = ctx.saved_tensors
         rows, V = l2.shape
         g = gloss.reshape(-1).float().contiguous()
-        # The gradient overwrites the logits buffer when it is bf16 (it is dead after this op).
+        # The gradient overwrites the logits buffer when it is 16-bit (it is dead after this op).
         out = l2 if ctx.dtype == 0 else torch.empty(l2.shape, device=l2.device, dtype=torch.bfloat16)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_ce_bwd(_lib.ptr(l2), _lib.ptr(lab), _lib.ptr(lse), _lib.ptr(g), _lib.ptr(out),
+        _lib.check(_lib.lib(l2).nx_ce_bwd(_lib.ptr(l2), _lib.ptr(lab), _lib.ptr(lse), _lib.ptr(g), _lib.ptr(out),
                                         rows, V, l2.stride(0), out.stride(0), ctx.vocab_start, ctx.dtype,
                                         _lib.stream()), "nx_ce_bwd")
         if ctx.dtype != 0:
@@ -71,7 +71,7 @@ def vocab_parallel_cross_entropy(logits: torch.Tensor, labels: torch.Tensor, voc
                                  group=None) -> torch.Tensor:
     """Per-token loss; ``logits`` [..., V_local] holds vocabulary ids
     [vocab_start, vocab_start + V_local) of the full vocabulary."""
-    if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32):
+    if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float16, torch.float32):
         if labels.device != logits.device or labels.dtype != torch.int64:
             raise _lib.KernelError(f"cross_entropy: labels must be int64 on {logits.device}, got {labels.dtype} "
                                    f"on {labels.device}")

@@ -41,7 +41,7 @@ def _torch_act(name: str, x: torch.Tensor) -> torch.Tensor:
 
 
 def _cuda_ok(x):
-    return x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
+    return x.is_cuda and x.dtype in _lib.H16 and x.shape[-1] % 8 == 0
 
 
 def colsum(x2: torch.Tensor, out_dtype=None) -> torch.Tensor:
@@ -49,7 +49,7 @@ def colsum(x2: torch.Tensor, out_dtype=None) -> torch.Tensor:
     if not x2.is_cuda:
         return x2.float().sum(0).to(out_dtype or x2.dtype)
     rows, N = x2.shape
-    L = _lib.lib()
+    L = _lib.lib(x2)
     slabs = L.nx_colsum_slabs(rows)
     ws = torch.empty(slabs * N, device=x2.device, dtype=torch.float32)
     out_dtype = out_dtype or x2.dtype
@@ -57,7 +57,7 @@ def colsum(x2: torch.Tensor, out_dtype=None) -> torch.Tensor:
     LAUNCHES["n"] += 2
     _lib.check(L.nx_colsum_bf16(
         _lib.ptr(x2), _lib.ptr(out) if out_dtype == torch.float32 else None,
-        _lib.ptr(out) if out_dtype == torch.bfloat16 else None, _lib.ptr(ws), rows, N, x2.stride(0),
+        _lib.ptr(out) if out_dtype == x2.dtype else None, _lib.ptr(ws), rows, N, x2.stride(0),
         0, _lib.stream()), "nx_colsum_bf16")
     return out
 
@@ -68,7 +68,7 @@ class _BiasActFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         y = torch.empty_like(x2)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_bias_act_fwd(_lib.ptr(x2), _lib.ptr(bias), _lib.ptr(y), x2.shape[0],
+        _lib.check(_lib.lib(x2).nx_bias_act_fwd(_lib.ptr(x2), _lib.ptr(bias), _lib.ptr(y), x2.shape[0],
                                               x2.shape[1], act_id, _lib.stream()), "nx_bias_act_fwd")
         ctx.save_for_backward(x2, bias)
         ctx.act_id, ctx.shape = act_id, x.shape
@@ -80,7 +80,7 @@ class _BiasActFn(torch.autograd.Function):
         gy2 = gy.reshape(x2.shape).contiguous()
         dx = torch.empty_like(x2)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_bias_act_bwd(_lib.ptr(gy2), _lib.ptr(x2), _lib.ptr(bias), _lib.ptr(dx),
+        _lib.check(_lib.lib(gy2).nx_bias_act_bwd(_lib.ptr(gy2), _lib.ptr(x2), _lib.ptr(bias), _lib.ptr(dx),
                                               x2.shape[0], x2.shape[1], ctx.act_id, _lib.stream()),
                    "nx_bias_act_bwd")
         gb = colsum(dx) if (bias is not None and ctx.needs_input_grad[1]) else None
@@ -103,7 +103,7 @@ class _GatedActFn(torch.autograd.Function):
         x2 = x.reshape(-1, F2).contiguous()
         y = torch.empty((x2.shape[0], F2 // 2), device=x.device, dtype=x.dtype)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_gated_act_fwd(_lib.ptr(x2), _lib.ptr(y), x2.shape[0], F2 // 2, act_id,
+        _lib.check(_lib.lib(x2).nx_gated_act_fwd(_lib.ptr(x2), _lib.ptr(y), x2.shape[0], F2 // 2, act_id,
                                                _lib.stream()), "nx_gated_act_fwd")
         ctx.save_for_backward(x2)
         ctx.act_id, ctx.shape = act_id, x.shape
@@ -115,7 +115,7 @@ class _GatedActFn(torch.autograd.Function):
         gy2 = gy.reshape(x2.shape[0], -1).contiguous()
         dx = torch.empty_like(x2)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_gated_act_bwd(_lib.ptr(gy2), _lib.ptr(x2), _lib.ptr(dx), x2.shape[0],
+        _lib.check(_lib.lib(gy2).nx_gated_act_bwd(_lib.ptr(gy2), _lib.ptr(x2), _lib.ptr(dx), x2.shape[0],
                                                x2.shape[1] // 2, ctx.act_id, _lib.stream()),
                    "nx_gated_act_bwd")
         return dx.view(ctx.shape), None
@@ -142,7 +142,7 @@ class _BiasDropoutAddFn(torch.autograd.Function):
         out = torch.empty_like(x2)
         mask = torch.empty(x2.numel() // 8, device=x.device, dtype=torch.uint8) if p > 0 else None
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_bias_dropout_add(
+        _lib.check(_lib.lib(x2).nx_bias_dropout_add(
             _lib.ptr(x2), _lib.ptr(bias), _lib.ptr(r2), _lib.ptr(out), _lib.ptr(mask), x2.shape[0], H,
             float(p), int(seed), int(offset), _lib.stream()), "nx_bias_dropout_add")
         ctx.p, ctx.shape, ctx.has_bias, ctx.has_res = p, x.shape, bias is not None, residual is not None
@@ -156,7 +156,7 @@ class _BiasDropoutAddFn(torch.autograd.Function):
         if ctx.p > 0:
             dx = torch.empty_like(gy2)
             LAUNCHES["n"] += 1
-            _lib.check(_lib.lib().nx_dropout_bwd(_lib.ptr(gy2), _lib.ptr(mask), _lib.ptr(dx), gy2.numel(),
+            _lib.check(_lib.lib(gy2).nx_dropout_bwd(_lib.ptr(gy2), _lib.ptr(mask), _lib.ptr(dx), gy2.numel(),
                                                  float(ctx.p), _lib.stream()), "nx_dropout_bwd")
         else:
             dx = gy2

@@ -70,7 +70,7 @@ class _MLPGeluFn(torch.autograd.Function):
 
 def mlp_gelu(x, w1, b1, w2, b2=None, residual=None, kind: str = "erf", recompute_act: bool = False):
     """``gelu(x @ w1^T + b1) @ w2^T (+ b2) (+ residual)``; kind in {"erf", "tanh"}."""
-    if x.is_cuda and x.dtype == torch.bfloat16:
+    if x.is_cuda and x.dtype in _lib.H16:
         return _MLPGeluFn.apply(x, w1, b1, w2, b2, residual, kind, recompute_act)
     if x.is_cuda:
         raise _lib.KernelError("mlp_gelu: CUDA path needs bf16")
@@ -106,7 +106,7 @@ class _QKVAttentionFn(torch.autograd.Function):
         sq_pad = (s + 127) // 128 * 128
         lse = torch.full((b, np_, sq_pad), float("inf"), device=qkv.device, dtype=torch.float32)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_flash_attn_fwd(
+        _lib.check(_lib.lib(qkv).nx_flash_attn_fwd(
             _lib.ptr(qb), _lib.ptr(kb), _lib.ptr(vb), _lib.ptr(ob), _lib.ptr(lse), _lib.ptr(alibi),
             b, np_, kvp, s, s, hn, *_strides_bhs(qb), *_strides_bhs(kb), *_strides_bhs(vb), *_strides_bhs(ob),
             float(scale), 1, int(window), _lib.stream()), "nx_flash_attn_fwd")
@@ -130,7 +130,7 @@ class _QKVAttentionFn(torch.autograd.Function):
         dob = perm(gout.view(s, b, np_, hn))
         delta = torch.zeros(lse.shape, device=qkv.device, dtype=torch.float32)
         LAUNCHES["n"] += 3
-        _lib.check(_lib.lib().nx_flash_attn_bwd(
+        _lib.check(_lib.lib(qkv).nx_flash_attn_bwd(
             _lib.ptr(qb), _lib.ptr(kb), _lib.ptr(vb), _lib.ptr(ob), _lib.ptr(dob), _lib.ptr(lse),
             _lib.ptr(delta), _lib.ptr(dqb), _lib.ptr(dkb), _lib.ptr(dvb), _lib.ptr(alibi),
             b, np_, kvp, s, s, hn, *_strides_bhs(qb), *_strides_bhs(kb), *_strides_bhs(vb), *_strides_bhs(ob),
@@ -150,7 +150,7 @@ def qkv_attention(qkv, *, num_heads: int, num_kv_heads: int, head_dim: int, rota
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     window = -1 if window is None else int(window)
     if qkv.is_cuda:
-        if qkv.dtype != torch.bfloat16 or head_dim % 8 or head_dim > 128:
+        if qkv.dtype not in _lib.H16 or head_dim % 8 or head_dim > 128:
             raise _lib.KernelError(f"qkv_attention: CUDA path needs bf16 and head dim % 8 == 0, <= 128 "
                                    f"(got {qkv.dtype}, {head_dim})")
         if not qkv.is_contiguous():

@@ -23,7 +23,7 @@ from .gemm import wgrad
 
 def backend(x, group):
     """The symmetric-memory backend of ``group`` if the fused path can serve ``x``."""
-    if collectives.get_mode() != "fused" or not x.is_cuda or x.dtype != torch.bfloat16:
+    if collectives.get_mode() != "fused" or not x.is_cuda or x.dtype not in _lib.H16:
         return None
     return symm.backend_for(group)
 

@@ -61,9 +61,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
          aux_out: torch.Tensor | None = None, dgelu_aux: torch.Tensor | None = None,
          dgelu: str | None = None, residual: torch.Tensor | None = None,
          out: torch.Tensor | None = None, accumulate: bool = False,
-         out_dtype: torch.dtype = torch.bfloat16, alpha: float | None = None,
+         out_dtype: torch.dtype | None = None, alpha: float | None = None,
          aux_deriv: bool = False) -> torch.Tensor:
-    """``C = epilogue(op(a) @ op(b))`` with 2-D row-major bf16 operands.
+    """``C = epilogue(op(a) @ op(b))`` with 2-D row-major 16-bit operands (bf16 or fp16, both the same dtype).
 
     ``trans_a=False``: a is [M,K]; ``True``: a is [K,M].
     ``trans_b=False``: b is [N,K] (weight layout); ``True``: b is [K,N].
@@ -71,7 +71,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     ``aux_deriv``), ×gelu'(``dgelu_aux``) (``dgelu="mul"``: × ``dgelu_aux`` itself), GeLU, +residual,
     (+= out if ``accumulate``).
     """
-    assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.is_cuda and a.dtype in _lib.H16 and b.dtype == a.dtype, (a.dtype, b.dtype)
     if trans_a:
         K, M = a.shape
     else:
@@ -84,23 +84,23 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     assert a.stride(1) == 1 and b.stride(1) == 1
     if out is None:
         assert not accumulate
-        out = torch.empty((M, N), device=a.device, dtype=out_dtype)
+        out = torch.empty((M, N), device=a.device, dtype=out_dtype or a.dtype)
     else:
         assert out.shape == (M, N) and out.stride(1) == 1
     flags = 0
     if out.dtype == torch.float32:
         flags |= EPI_OUT_F32
     else:
-        assert out.dtype == torch.bfloat16
+        assert out.dtype == a.dtype, (out.dtype, a.dtype)
     if bias is not None:
-        assert bias.dtype == torch.bfloat16 and bias.numel() == N
+        assert bias.dtype == a.dtype and bias.numel() == N
         flags |= EPI_BIAS
     if gelu is not None:
         flags |= EPI_GELU_TANH if gelu == "tanh" else EPI_GELU_ERF
     ld_aux = 0
     for t in (aux_out, dgelu_aux, residual):
         if t is not None:
-            assert t.shape == (M, N) and t.stride(1) == 1 and t.dtype == torch.bfloat16
+            assert t.shape == (M, N) and t.stride(1) == 1 and t.dtype == a.dtype
             assert ld_aux in (0, t.stride(0)), "aux tensors must share one leading dimension"
             ld_aux = t.stride(0)
     flags |= aux_flags(gelu, aux_out, aux_deriv, dgelu_aux, dgelu)
@@ -110,7 +110,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         flags |= EPI_ACCUM
     if alpha is not None:
         flags |= EPI_SCALE
-    L = _lib.lib()
+    L = _lib.lib(a)
     LAUNCHES["n"] += 1
     fn, name = L.nx_gemm_bf16, "nx_gemm_bf16"
     if PAIR_GEMM["on"] and M >= 256 and N >= 256:
@@ -165,9 +165,9 @@ def wgrad(gy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor):
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
-    """``F.linear`` on the tcgen05 GEMM for CUDA bf16 tensors; PyTorch on CPU (oracle path)."""
-    if x.is_cuda and x.dtype == torch.bfloat16:
+    """``F.linear`` on the tcgen05 GEMM for CUDA bf16 / fp16 tensors; PyTorch on CPU (oracle path)."""
+    if x.is_cuda and x.dtype in _lib.H16:
         return _LinearFn.apply(x, weight, bias)
     if x.is_cuda:
-        raise _lib.KernelError(f"linear: CUDA path needs bf16 activations, got {x.dtype}")
+        raise _lib.KernelError(f"linear: the CUDA kernels take bf16 or fp16 activations, got {x.dtype}")
     return F.linear(x, weight, bias)

@@ -35,7 +35,7 @@ class _ConvFn(torch.autograd.Function):
         B, L, D = x.shape
         y = torch.empty((L, B, D), device=x.device, dtype=x.dtype).transpose(0, 1)   # time-major memory
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_conv1d_silu_fwd(_lib.ptr(x), x.stride(0), x.stride(1), _lib.ptr(weight),
+        _lib.check(_lib.lib(x).nx_conv1d_silu_fwd(_lib.ptr(x), x.stride(0), x.stride(1), _lib.ptr(weight),
                                                  _lib.ptr(bias), _lib.ptr(y), y.stride(0), y.stride(1), B, L, D,
                                                  weight.shape[1], _lib.stream()), "nx_conv1d_silu_fwd")
         ctx.save_for_backward(x, weight, bias)
@@ -51,7 +51,7 @@ class _ConvFn(torch.autograd.Function):
         dw = torch.zeros(weight.shape, device=x.device, dtype=torch.float32)
         db = torch.zeros(D, device=x.device, dtype=torch.float32) if bias is not None else None
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_conv1d_silu_bwd(_lib.ptr(x), x.stride(0), x.stride(1), _lib.ptr(weight),
+        _lib.check(_lib.lib(x).nx_conv1d_silu_bwd(_lib.ptr(x), x.stride(0), x.stride(1), _lib.ptr(weight),
                                                  _lib.ptr(bias), _lib.ptr(gy), gy.stride(0), gy.stride(1),
                                                  _lib.ptr(dx), dx.stride(0), dx.stride(1), _lib.ptr(dw),
                                                  _lib.ptr(db), B, L, D, weight.shape[1], _lib.stream()),
@@ -63,7 +63,7 @@ def causal_conv1d_silu(x, weight, bias=None):
     """``silu(depthwise_causal_conv(x))`` for x [b, l, d] (strided ok), weight [d, w<=4], bias [d]."""
     _btd(x)
     if x.is_cuda:
-        if x.dtype != torch.bfloat16 or weight.shape[1] > 4:
+        if x.dtype not in _lib.H16 or weight.shape[1] > 4:
             raise _lib.KernelError("causal_conv1d_silu: CUDA path needs bf16 and kernel width <= 4")
         return _ConvFn.apply(x, weight.contiguous(), None if bias is None else bias.contiguous())
     return causal_conv1d_silu_reference(x, weight, bias)
@@ -95,7 +95,7 @@ def selective_scan_reference(x, dt, A, Bm, Cm, D=None, z=None, dt_bias=None):
 class _ScanFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, dt, A, Bm, Cm, D, z, dt_bias):
-        L_ = _lib.lib()
+        L_ = _lib.lib(x)
         B, L, Dm = x.shape
         dev = x.device
         nc = L_.nx_scan_chunks(L)
@@ -116,7 +116,7 @@ class _ScanFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, gout):
         x, dt, A, Bm, Cm, D, z, dt_bias, sumdt, h0 = ctx.saved_tensors
-        L_ = _lib.lib()
+        L_ = _lib.lib(x)
         B, L, Dm = x.shape
         dev = x.device
         if gout.stride(2) != 1:
@@ -153,7 +153,7 @@ def selective_scan(x, dt, A, Bm, Cm, D=None, z=None, dt_bias=None):
     D, dt_bias [d] fp32."""
     _btd(x), _btd(dt), _btd(Bm), _btd(Cm)
     if x.is_cuda:
-        if x.dtype != torch.bfloat16 or A.shape[1] != 16:
+        if x.dtype not in _lib.H16 or A.shape[1] != 16:
             raise _lib.KernelError("selective_scan: CUDA path needs bf16 activations and d_state == 16")
         if dt_bias is None:
             dt_bias = torch.zeros(x.shape[2], device=x.device, dtype=torch.float32)

@@ -42,7 +42,7 @@ def gather_rows(src, plan: Plan, scale=None):
     H = src.shape[1]
     out = torch.empty((plan.max_rows, H), device=src.device, dtype=src.dtype)
     LAUNCHES["n"] += 1
-    _lib.check(_lib.lib().nx_moe_gather_rows(_lib.ptr(src), src.stride(0), _lib.ptr(plan.src_copy), _lib.ptr(scale),
+    _lib.check(_lib.lib(src).nx_moe_gather_rows(_lib.ptr(src), src.stride(0), _lib.ptr(plan.src_copy), _lib.ptr(scale),
                                              plan.k, _lib.ptr(out), plan.max_rows, H, _lib.stream()),
                "nx_moe_gather_rows")
     return out
@@ -53,7 +53,7 @@ def combine(y, plan: Plan, weights=None):
     T, H = plan.C // plan.k, y.shape[1]
     out = torch.empty((T, H), device=y.device, dtype=y.dtype)
     LAUNCHES["n"] += 1
-    _lib.check(_lib.lib().nx_moe_combine(_lib.ptr(y), _lib.ptr(plan.dest_row), _lib.ptr(weights), plan.k,
+    _lib.check(_lib.lib(y).nx_moe_combine(_lib.ptr(y), _lib.ptr(plan.dest_row), _lib.ptr(weights), plan.k,
                                          _lib.ptr(out), T, H, _lib.stream()), "nx_moe_combine")
     return out
 
@@ -61,7 +61,7 @@ def combine(y, plan: Plan, weights=None):
 def weight_grad(g, y, plan: Plan):
     dw = torch.empty(plan.C, device=g.device, dtype=g.dtype)
     LAUNCHES["n"] += 1
-    _lib.check(_lib.lib().nx_moe_weight_grad(_lib.ptr(g), _lib.ptr(y), _lib.ptr(plan.dest_row), plan.k,
+    _lib.check(_lib.lib(g).nx_moe_weight_grad(_lib.ptr(g), _lib.ptr(y), _lib.ptr(plan.dest_row), plan.k,
                                              _lib.ptr(dw), plan.C, g.shape[1], _lib.stream()), "nx_moe_weight_grad")
     return dw
 
@@ -81,7 +81,7 @@ def grouped_gemm_rows(a, w, plan: Plan, n_out, *, trans_b, gelu=None, aux_out=No
     if dgelu_aux is not None:
         ld_aux = dgelu_aux.stride(0)
     LAUNCHES["n"] += 1
-    _lib.check(_lib.lib().nx_gemm_bf16_grouped(1, _lib.ptr(a), _lib.ptr(w), _lib.ptr(out), rows, n_out, K, a.stride(0),
+    _lib.check(_lib.lib(a).nx_gemm_bf16_grouped(1, _lib.ptr(a), _lib.ptr(w), _lib.ptr(out), rows, n_out, K, a.stride(0),
                                                w.stride(0), out.stride(0), int(trans_b), plan.E,
                                                _lib.ptr(plan.tile_expert), None, 0, _lib.ptr(dgelu_aux),
                                                _lib.ptr(aux_out), ld_aux, flags, _lib.stream()),
@@ -100,7 +100,7 @@ def grouped_wgrad(a, b, plan: Plan, weight):
         out = torch.zeros((plan.E * M, N), device=a.device, dtype=a.dtype)
         flags, ret = 0, out
     LAUNCHES["n"] += 1
-    _lib.check(_lib.lib().nx_gemm_bf16_grouped(2, _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, a.shape[0], a.stride(0),
+    _lib.check(_lib.lib(a).nx_gemm_bf16_grouped(2, _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, a.shape[0], a.stride(0),
                                                b.stride(0), N, 1, plan.E, None, _lib.ptr(plan.offsets), M * N, None,
                                                None, 0, flags, _lib.stream()), "nx_gemm_bf16_grouped(wgrad)")
     if ret is not None and mg is not None:

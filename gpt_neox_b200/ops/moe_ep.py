@@ -33,14 +33,14 @@ def _declare():
     if not _DECLARED:
         P, I, LL, U = C.c_void_p, C.c_int, C.c_longlong, C.c_uint
         PP = C.POINTER(C.c_ulonglong)
-        L.nx_moe_ep_flag_bytes.argtypes = []
-        L.nx_moe_ep_barrier.argtypes = [PP, I, I, U, P]
-        L.nx_moe_ep_stage_ids.argtypes = [PP, I, LL, I, I, I, P, P]
-        L.nx_moe_ep_gather.argtypes = [PP, I, LL, LL, P, I, I, P, I, I, P, P, P]
-        L.nx_moe_ep_combine.argtypes = [PP, I, I, LL, LL, LL, P, I, I, I, P, P, I, I, P, P]
-        for f in (L.nx_moe_ep_flag_bytes, L.nx_moe_ep_barrier, L.nx_moe_ep_stage_ids, L.nx_moe_ep_gather,
-                  L.nx_moe_ep_combine):
-            f.restype = I
+        sigs = {"nx_moe_ep_flag_bytes": [], "nx_moe_ep_barrier": [PP, I, I, U, P],
+                "nx_moe_ep_stage_ids": [PP, I, LL, I, I, I, P, P],
+                "nx_moe_ep_gather": [PP, I, LL, LL, P, I, I, P, I, I, P, P, P],
+                "nx_moe_ep_combine": [PP, I, I, LL, LL, LL, P, I, I, I, P, P, I, I, P, P]}
+        for name, argtypes in sigs.items():
+            for nm in (name, name + "_f16"):        # the bf16 build and the fp16 build
+                f = getattr(L, nm)
+                f.argtypes, f.restype = argtypes, I
         _DECLARED = True
     return L
 
@@ -62,24 +62,25 @@ def _layout(ws, T, k, H, e_local):
 class EpWorkspace:
     """One rank's symmetric workspace and its view of the peers'."""
 
-    def __init__(self, buf, ptrs, me, ws, T, k, H, e_local, barrier):
+    def __init__(self, buf, ptrs, me, ws, T, k, H, e_local, barrier, dtype=torch.bfloat16):
         self.buf, self.me, self.ws, self.T, self.k, self.H, self.e_local = buf, me, ws, T, k, H, e_local
         self.Ck = T * k
         self.off, self.nbytes, self.max_rows = _layout(ws, T, k, H, e_local)
         self.ptrs = (C.c_ulonglong * 8)(*([int(p) for p in ptrs] + [0] * (8 - ws)))
         self.use_barrier = barrier
+        self.dtype = dtype           # 16-bit dtype of tokens, routing weights and expert rows
         self.epoch = 0
         v = lambda name, n, dt: buf[self.off[name]:self.off[name] + n * torch.empty(0, dtype=dt).element_size()].view(dt)
         self.idx = v("idx", self.Ck, torch.int32)
-        self.wf = v("wf", self.Ck, torch.bfloat16)
-        self.tok = v("tok", T * H, torch.bfloat16).view(T, H)
+        self.wf = v("wf", self.Ck, dtype)
+        self.tok = v("tok", T * H, dtype).view(T, H)
         self.dest = v("dest", ws * self.Ck, torch.int32)
         self.aux = v("aux", self.max_rows, torch.float32)
-        self.rows = v("rows", self.max_rows * H, torch.bfloat16).view(self.max_rows, H)
+        self.rows = v("rows", self.max_rows * H, dtype).view(self.max_rows, H)
 
     # ------------------------------------------------------------------ construction
     @classmethod
-    def create(cls, group, T, k, H, e_local):
+    def create(cls, group, T, k, H, e_local, dtype=torch.bfloat16):
         """Collective over ``group``: allocate and exchange the symmetric buffers."""
         import torch.distributed._symmetric_memory as symm_mem
         ws, me = dist.get_world_size(group), dist.get_rank(group)
@@ -89,21 +90,21 @@ class EpWorkspace:
         buf[: _declare().nx_moe_ep_flag_bytes()].zero_()
         torch.cuda.synchronize()
         hdl = symm_mem.rendezvous(buf, group)
-        w = cls(buf, hdl.buffer_ptrs, me, ws, T, k, H, e_local, barrier=True)
+        w = cls(buf, hdl.buffer_ptrs, me, ws, T, k, H, e_local, barrier=True, dtype=dtype)
         w.hdl = hdl
         dist.barrier(group)
         return w
 
     @classmethod
-    def emulated(cls, ws, T, k, H, e_local, device="cuda"):
+    def emulated(cls, ws, T, k, H, e_local, device="cuda", dtype=torch.bfloat16):
         """``ws`` workspaces on ONE device, for driving emulated ranks in lockstep without barrier kernels."""
         _, nbytes, _ = _layout(ws, T, k, H, e_local)
         bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(ws)]
         ptrs = [b.data_ptr() for b in bufs]
-        return [cls(bufs[r], ptrs, r, ws, T, k, H, e_local, barrier=False) for r in range(ws)]
+        return [cls(bufs[r], ptrs, r, ws, T, k, H, e_local, barrier=False, dtype=dtype) for r in range(ws)]
 
-    def fits(self, T, k, H, e_local):
-        return (T, k, H, e_local) == (self.T, self.k, self.H, self.e_local)
+    def fits(self, T, k, H, e_local, dtype=torch.bfloat16):
+        return (T, k, H, e_local, dtype) == (self.T, self.k, self.H, self.e_local, self.dtype)
 
     # ------------------------------------------------------------------ kernels
     def barrier(self):
@@ -124,9 +125,10 @@ class EpWorkspace:
 
     def gather(self, plan, scaled=False, dot_with=None):
         """Pull the published token rows of all ranks into the padded expert-sorted layout."""
-        out = torch.empty((plan.max_rows, self.H), device=self.buf.device, dtype=torch.bfloat16)
+        out = torch.empty((plan.max_rows, self.H), device=self.buf.device, dtype=self.dtype)
         LAUNCHES["n"] += 1
-        _lib.check(_declare().nx_moe_ep_gather(
+        _declare()
+        _lib.check(_lib.lib(self.dtype).nx_moe_ep_gather(
             self.ptrs, self.ws, self.off["tok"], self.off["wf"] if scaled else -1, _lib.ptr(plan.src_copy), self.Ck,
             self.k, _lib.ptr(out), plan.max_rows, self.H, _lib.ptr(dot_with),
             _lib.ptr(self.aux) if dot_with is not None else None, _lib.stream()), "nx_moe_ep_gather")
@@ -134,10 +136,11 @@ class EpWorkspace:
 
     def combine(self, expert_ids_i32, weights=None, want_aux=False):
         """Pull this rank's tokens' expert results from their owners and sum the k copies."""
-        out = torch.empty((self.T, self.H), device=self.buf.device, dtype=torch.bfloat16)
-        aux = torch.empty(self.Ck, device=self.buf.device, dtype=torch.bfloat16) if want_aux else None
+        out = torch.empty((self.T, self.H), device=self.buf.device, dtype=self.dtype)
+        aux = torch.empty(self.Ck, device=self.buf.device, dtype=self.dtype) if want_aux else None
         LAUNCHES["n"] += 1
-        _lib.check(_declare().nx_moe_ep_combine(
+        _declare()
+        _lib.check(_lib.lib(self.dtype).nx_moe_ep_combine(
             self.ptrs, self.ws, self.me, self.off["rows"], self.off["dest"], self.off["aux"] if want_aux else -1,
             _lib.ptr(expert_ids_i32), self.e_local, self.Ck, self.k, _lib.ptr(weights), _lib.ptr(out), self.T, self.H,
             _lib.ptr(aux), _lib.stream()), "nx_moe_ep_combine")
@@ -220,13 +223,13 @@ def enabled() -> bool:
     return os.environ.get("NEOX_MOE_P2P", "1") != "0"
 
 
-def workspace_for(group, T, k, H, e_local):
+def workspace_for(group, T, k, H, e_local, dtype=torch.bfloat16):
     """The expert-parallel group's workspace (one per group, shared by all layers; re-created when the
     token count or layer shape changes: a collective, every rank takes the same branch)."""
     key = id(group)
     W = _WORKSPACES.get(key)
-    if W is None or not W.fits(T, k, H, e_local):
-        W = EpWorkspace.create(group, T, k, H, e_local)
+    if W is None or not W.fits(T, k, H, e_local, dtype):
+        W = EpWorkspace.create(group, T, k, H, e_local, dtype=dtype)
         _WORKSPACES[key] = W
     return W
 
@@ -240,5 +243,5 @@ def experts_gelu_ep(x2, weights, indices, w1, w2, num_experts, group, kind="erf"
     expert ids); w1, w2 [E_local * ffn, h] this rank's experts."""
     ws = dist.get_world_size(group)
     T, k = indices.shape
-    W = workspace_for(group, T, k, x2.shape[1], num_experts // ws)
+    W = workspace_for(group, T, k, x2.shape[1], num_experts // ws, x2.dtype)
     return _ExpertsGeluEPFn.apply(x2, weights.to(x2.dtype), indices, w1, w2, W, kind)

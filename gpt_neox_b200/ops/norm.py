@@ -16,7 +16,7 @@ LN, RMS = 0, 1
 
 
 def _cuda_ok(x: torch.Tensor) -> bool:
-    return x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
+    return x.is_cuda and x.dtype in _lib.H16 and x.shape[-1] % 8 == 0
 
 
 def _accum_param_grad(param: torch.Tensor, g_f32: torch.Tensor):
@@ -46,7 +46,7 @@ class _NormFn(torch.autograd.Function):
         mean = torch.empty(rows, device=x.device, dtype=torch.float32) if kind == LN else None
         rstd = torch.empty(rows, device=x.device, dtype=torch.float32)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_norm_fwd(
+        _lib.check(_lib.lib(x2).nx_norm_fwd(
             kind, _lib.ptr(x2), _lib.ptr(gamma), _lib.ptr(beta), _lib.ptr(y1), _lib.ptr(gamma2),
             _lib.ptr(beta2), _lib.ptr(y2), _lib.ptr(mean), _lib.ptr(rstd), rows, H, float(eps),
             _lib.stream()), "nx_norm_fwd")
@@ -63,7 +63,7 @@ class _NormFn(torch.autograd.Function):
     def backward(ctx, *gys):
         x2, gamma, gamma2, mean, rstd = ctx.saved_tensors
         rows, H = x2.shape
-        L = _lib.lib()
+        L = _lib.lib(x2)
 
         def flat(t):
             if t is None:

@@ -12,9 +12,9 @@ def sumsq_(x: torch.Tensor, acc: torch.Tensor):
     if x.numel() == 0:
         return
     if x.is_cuda:
-        assert x.is_contiguous() and x.dtype in (torch.bfloat16, torch.float32)
+        assert x.is_contiguous() and x.dtype in (torch.bfloat16, torch.float16, torch.float32)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_sumsq(_lib.ptr(x), x.numel(), _lib.ptr(acc), 0 if x.dtype == torch.bfloat16 else 1,
+        _lib.check(_lib.lib(x).nx_sumsq(_lib.ptr(x), x.numel(), _lib.ptr(acc), 1 if x.dtype == torch.float32 else 0,
                                        _lib.stream()), "nx_sumsq")
     else:
         s = x.float().pow(2).sum()
@@ -47,13 +47,15 @@ def adamw_step_(p32, m, v, g, p_lp, *, lr, beta1, beta2, eps, weight_decay, step
     if p32.is_cuda:
         assert p32.is_contiguous() and g.is_contiguous()
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_adamw_step(
+        lp16 = p_lp is not None and p_lp.dtype in _lib.H16
+        assert g.dtype == torch.float32 or not lp16 or g.dtype == p_lp.dtype, (g.dtype, p_lp.dtype)
+        _lib.check(_lib.lib(p_lp if lp16 else g).nx_adamw_step(
             _lib.ptr(p32), _lib.ptr(m), _lib.ptr(v), _lib.ptr(g),
-            _lib.ptr(p_lp) if (p_lp is not None and p_lp.dtype == torch.bfloat16) else None,
+            _lib.ptr(p_lp) if lp16 else None,
             p32.numel(), float(lr), float(beta1), float(beta2), float(eps), float(weight_decay),
             float(bc1), float(bc2), int(adam_w_mode), _lib.ptr(grad_scale), _lib.ptr(skip),
-            0 if g.dtype == torch.bfloat16 else 1, _lib.stream()), "nx_adamw_step")
-        if p_lp is not None and p_lp.dtype != torch.bfloat16:
+            1 if g.dtype == torch.float32 else 0, _lib.stream()), "nx_adamw_step")
+        if p_lp is not None and not lp16:
             p_lp.copy_(p32)
         return
     if skip is not None and int(skip[0]) != 0:

@@ -24,7 +24,7 @@ def _launch(x, out, cos, sin, rot, pos0, inverse):
     S, B, NH, D = x.shape
     assert x.stride(3) == 1 and out.stride(3) == 1
     LAUNCHES["n"] += 1
-    _lib.check(_lib.lib().nx_rope(_lib.ptr(x), _lib.ptr(out), _lib.ptr(cos), _lib.ptr(sin), S, B, NH, D, rot,
+    _lib.check(_lib.lib(x).nx_rope(_lib.ptr(x), _lib.ptr(out), _lib.ptr(cos), _lib.ptr(sin), S, B, NH, D, rot,
                                   x.stride(0), x.stride(1), x.stride(2), out.stride(0), out.stride(1),
                                   out.stride(2), int(pos0), int(inverse), _lib.stream()), "nx_rope")
 
@@ -53,7 +53,7 @@ def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rot_dim:
     dims of each head with positions pos0 .. pos0+s-1, passes the rest through."""
     if rot_dim == 0:
         return x
-    if x.is_cuda and x.dtype == torch.bfloat16:
+    if x.is_cuda and x.dtype in _lib.H16:
         return _RopeFn.apply(x, cos, sin, rot_dim, pos0)
     if x.is_cuda:
         raise _lib.KernelError("apply_rotary: CUDA path needs bf16")

@@ -14,7 +14,7 @@ from .gemm import LAUNCHES
 
 
 def _cuda_ok(x):
-    return x.is_cuda and x.dtype == torch.bfloat16
+    return x.is_cuda and x.dtype in _lib.H16
 
 
 class _CausalSoftmaxFn(torch.autograd.Function):
@@ -24,7 +24,7 @@ class _CausalSoftmaxFn(torch.autograd.Function):
         xc = x.contiguous()
         y = torch.empty_like(xc)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_softmax_causal_fwd(_lib.ptr(xc), _lib.ptr(y), xc.shape[0], xc.shape[1],
+        _lib.check(_lib.lib(xc).nx_softmax_causal_fwd(_lib.ptr(xc), _lib.ptr(y), xc.shape[0], xc.shape[1],
                                                     xc.shape[2], float(scale), _lib.stream()),
                    "nx_softmax_causal_fwd")
         ctx.scale = scale
@@ -37,7 +37,7 @@ class _CausalSoftmaxFn(torch.autograd.Function):
         gyc = gy.contiguous()
         dx = torch.empty_like(y)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_softmax_bwd(_lib.ptr(gyc), _lib.ptr(y), _lib.ptr(dx),
+        _lib.check(_lib.lib(gyc).nx_softmax_bwd(_lib.ptr(gyc), _lib.ptr(y), _lib.ptr(dx),
                                              y.shape[0] * y.shape[1], y.shape[2], float(ctx.scale),
                                              _lib.stream()), "nx_softmax_bwd")
         return dx, None
@@ -56,7 +56,7 @@ class _MaskedSoftmaxFn(torch.autograd.Function):
             mb = m.shape[0]
         y = torch.empty_like(xc)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_softmax_masked_fwd(_lib.ptr(xc), _lib.ptr(m), _lib.ptr(y), b, np_, sq, sk,
+        _lib.check(_lib.lib(xc).nx_softmax_masked_fwd(_lib.ptr(xc), _lib.ptr(m), _lib.ptr(y), b, np_, sq, sk,
                                                     mb, float(scale), _lib.stream()),
                    "nx_softmax_masked_fwd")
         ctx.scale = scale
@@ -69,7 +69,7 @@ class _MaskedSoftmaxFn(torch.autograd.Function):
         gyc = gy.contiguous()
         dx = torch.empty_like(y)
         LAUNCHES["n"] += 1
-        _lib.check(_lib.lib().nx_softmax_bwd(_lib.ptr(gyc), _lib.ptr(y), _lib.ptr(dx),
+        _lib.check(_lib.lib(gyc).nx_softmax_bwd(_lib.ptr(gyc), _lib.ptr(y), _lib.ptr(dx),
                                              y.numel() // y.shape[-1], y.shape[-1], float(ctx.scale),
                                              _lib.stream()), "nx_softmax_bwd")
         return dx, None, None

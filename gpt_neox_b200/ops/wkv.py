@@ -49,7 +49,7 @@ def decay_grad_from_gr_gk(r, k, v, w, u, gy, gr, gk):
 def _pass(mode, a, b, c, w, u, out, local, start, sumew, B, T, H, N):
     LAUNCHES["n"] += 1
     o = (out.stride(0), out.stride(1), int(out.dtype == torch.float32)) if out is not None else (0, 0, 0)
-    _lib.check(_lib.lib().nx_wkv6_pass(mode, _lib.ptr(a), _lib.ptr(b), _lib.ptr(c), _lib.ptr(w), b.stride(0),
+    _lib.check(_lib.lib(b).nx_wkv6_pass(mode, _lib.ptr(a), _lib.ptr(b), _lib.ptr(c), _lib.ptr(w), b.stride(0),
                                        b.stride(1), _lib.ptr(u), _lib.ptr(out), o[0], o[1], o[2], _lib.ptr(local),
                                        _lib.ptr(start), _lib.ptr(sumew), B, T, H, N, _lib.stream()), "nx_wkv6_pass")
 
@@ -120,7 +120,7 @@ class _WkvFn(torch.autograd.Function):
 def wkv6(r, k, v, w, u):
     """y [b, t, c] of the RWKV-6 recurrence; differentiable in all five arguments."""
     if r.is_cuda:
-        if r.dtype != torch.bfloat16 or u.shape[1] not in (32, 64):
+        if r.dtype not in _lib.H16 or u.shape[1] not in (32, 64):
             raise _lib.KernelError("wkv6: CUDA path needs bf16 and head size 32 or 64")
         return _WkvFn.apply(r, k, v, w, u)
     return wkv6_reference(r, k, v, w, u)

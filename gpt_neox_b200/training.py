@@ -461,6 +461,12 @@ def setup_model_and_optimizer(neox_args, use_cache=False, iteration=None):
     """-> (engine, optimizer, lr_scheduler, reference_model)."""
     if neox_args.memory_profiling and torch.cuda.is_available():
         torch.cuda.memory._record_memory_history(True, trace_alloc_max_entries=100000, trace_alloc_record_context=True)
+    if _device().type == "cuda" and neox_args.params_dtype == torch.float32:
+        # said once, before anything is built, instead of a kernel error in the middle of the first step
+        raise ValueError('"precision": "fp32" is not built for the GPU: the sm_100a kernels take 16-bit activations '
+                         'and weights with fp32 accumulation, master weights and optimizer state. Use '
+                         '"precision": "bfloat16" or "fp16" (an "fp16" block with dynamic loss scaling works '
+                         'unchanged); fp32 runs on CPU ("distributed_backend": "gloo").')
     model = get_model(neox_args=neox_args, use_cache=use_cache)
     reference_model = None
     needs_ref = (neox_args.train_impl == "dpo" and neox_args.precompute_model_name is None

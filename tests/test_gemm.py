@@ -3,6 +3,15 @@ import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+DT = torch.bfloat16     # the 16-bit dtype under test; every test below runs once for bf16 and once for fp16
+
+
+@pytest.fixture(autouse=True, params=[torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+def _dtype(request):
+    global DT
+    DT = request.param
+    yield
+    DT = torch.bfloat16
 
 
 def _ref(a, b, ta, tb):
@@ -28,8 +37,8 @@ def test_gemm_layouts(ta, tb, M, N, K):
     torch.manual_seed(0)
     if ta and M % 8:
         pytest.skip("transposed A needs M % 8 == 0")
-    a = torch.randn((K, M) if ta else (M, K), device="cuda", dtype=torch.bfloat16)
-    b = torch.randn((K, N) if tb else (N, K), device="cuda", dtype=torch.bfloat16)
+    a = torch.randn((K, M) if ta else (M, K), device="cuda", dtype=DT)
+    b = torch.randn((K, N) if tb else (N, K), device="cuda", dtype=DT)
     out = gemm(a, b, trans_a=ta, trans_b=tb)
     torch.cuda.synchronize()
     _check(out, _ref(a, b, ta, tb), K)
@@ -39,12 +48,12 @@ def test_gemm_epilogues():
     from gpt_neox_b200.ops.gemm import gemm
     torch.manual_seed(1)
     M, N, K = 512, 768, 320
-    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
-    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
-    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
-    res = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    a = torch.randn(M, K, device="cuda", dtype=DT)
+    b = torch.randn(N, K, device="cuda", dtype=DT) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=DT)
+    res = torch.randn(M, N, device="cuda", dtype=DT)
     pre = a.float() @ b.float().t() + bias.float()
-    aux = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    aux = torch.empty(M, N, device="cuda", dtype=DT)
     out = gemm(a, b, bias=bias, gelu="erf", aux_out=aux, residual=res)
     ref = torch.nn.functional.gelu(pre) + res.float()
     _check(aux, pre, K)
@@ -66,9 +75,9 @@ def test_gemm_epilogues():
 def test_linear_autograd():
     from gpt_neox_b200.ops.gemm import linear
     torch.manual_seed(2)
-    x = torch.randn(4, 96, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-    w = (torch.randn(384, 256, device="cuda", dtype=torch.bfloat16) * 0.05).requires_grad_(True)
-    b = torch.randn(384, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    x = torch.randn(4, 96, 256, device="cuda", dtype=DT, requires_grad=True)
+    w = (torch.randn(384, 256, device="cuda", dtype=DT) * 0.05).requires_grad_(True)
+    b = torch.randn(384, device="cuda", dtype=DT).requires_grad_(True)
     y = linear(x, w, b)
     gy = torch.randn_like(y)
     y.backward(gy)

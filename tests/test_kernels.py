@@ -7,6 +7,15 @@ import torch.nn.functional as F
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
+DT = torch.bfloat16     # the 16-bit dtype under test; every test below runs once for bf16 and once for fp16
+
+
+@pytest.fixture(autouse=True, params=[torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+def _dtype(request):
+    global DT
+    DT = request.param
+    yield
+    DT = torch.bfloat16
 
 
 def rel(a, b):
@@ -15,7 +24,7 @@ def rel(a, b):
 
 
 def bf(*shape, scale=1.0, grad=False):
-    t = (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+    t = (torch.randn(*shape, device=DEV) * scale).to(DT)
     return t.requires_grad_(grad)
 
 
@@ -24,7 +33,7 @@ def bf(*shape, scale=1.0, grad=False):
 def test_layernorm_fwd_bwd(rows, H):
     from gpt_neox_b200.ops.norm import layer_norm
     torch.manual_seed(0)
-    x, w, b = bf(rows, H, grad=True), (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16().requires_grad_(True), \
+    x, w, b = bf(rows, H, grad=True), (1 + 0.1 * torch.randn(H, device=DEV)).to(DT).requires_grad_(True), \
         bf(H, scale=0.1, grad=True)
     y = layer_norm(x, w, b, 1e-5)
     g = bf(rows, H)
@@ -43,7 +52,7 @@ def test_dual_layernorm_matches_two_norms():
     torch.manual_seed(1)
     rows, H = 257, 1024
     x = bf(rows, H, grad=True)
-    ws = [(1 + 0.1 * torch.randn(H, device=DEV)).bfloat16().requires_grad_(True) for _ in range(2)]
+    ws = [(1 + 0.1 * torch.randn(H, device=DEV)).to(DT).requires_grad_(True) for _ in range(2)]
     bs = [bf(H, scale=0.1, grad=True) for _ in range(2)]
     y1, y2 = dual_layer_norm(x, ws[0], bs[0], ws[1], bs[1], 1e-5)
     g1, g2 = bf(rows, H), bf(rows, H)
@@ -69,7 +78,7 @@ def test_dual_layernorm_with_residual_carry_one_backward_pass(rows, H):
     from gpt_neox_b200.ops.norm import dual_layer_norm
     torch.manual_seed(4)
     x = bf(rows, H, grad=True)
-    ws = [(1 + 0.1 * torch.randn(H, device=DEV)).bfloat16().requires_grad_(True) for _ in range(2)]
+    ws = [(1 + 0.1 * torch.randn(H, device=DEV)).to(DT).requires_grad_(True) for _ in range(2)]
     bs = [bf(H, scale=0.1, grad=True) for _ in range(2)]
     res, y1, y2 = dual_layer_norm(x, ws[0], bs[0], ws[1], bs[1], 1e-5, carry=True)
     g0, g1, g2 = bf(rows, H), bf(rows, H), bf(rows, H)
@@ -92,7 +101,7 @@ def test_rmsnorm_carry_adds_residual_gradient():
     from gpt_neox_b200.ops.norm import rms_norm
     torch.manual_seed(5)
     rows, H = 300, 4096
-    x, w = bf(rows, H, grad=True), (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16().requires_grad_(True)
+    x, w = bf(rows, H, grad=True), (1 + 0.1 * torch.randn(H, device=DEV)).to(DT).requires_grad_(True)
     res, y = rms_norm(x, w, 1e-6, carry=True)
     g0, g = bf(rows, H), bf(rows, H)
     ((res * g0).sum() + (y * g).sum()).backward()
@@ -107,7 +116,7 @@ def test_rmsnorm_carry_adds_residual_gradient():
 def test_rmsnorm_fwd_bwd(rows, H):
     from gpt_neox_b200.ops.norm import rms_norm
     torch.manual_seed(2)
-    x, w = bf(rows, H, grad=True), (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16().requires_grad_(True)
+    x, w = bf(rows, H, grad=True), (1 + 0.1 * torch.randn(H, device=DEV)).to(DT).requires_grad_(True)
     y = rms_norm(x, w, 1e-8)
     g = bf(rows, H)
     y.backward(g)
@@ -160,7 +169,7 @@ def test_bias_dropout_add_and_colsum():
     y.sum().backward()
     assert rel(b.grad, torch.full((1024,), 64.0, device=DEV)) < 1e-2
     # dropout: kept fraction and scaling
-    x2 = torch.ones(512, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    x2 = torch.ones(512, 1024, device=DEV, dtype=DT, requires_grad=True)
     y2 = bias_dropout_add(x2, None, None, 0.25, True)
     kept = (y2 != 0).float().mean().item()
     assert abs(kept - 0.75) < 0.02
@@ -216,7 +225,7 @@ def test_cross_entropy(V, start, full):
         # a shard of a larger vocabulary: (max, sumexp, target) statistics must match
         from gpt_neox_b200.ops import _lib
         stats = torch.empty(rows, 3, device=DEV)
-        _lib.check(_lib.lib().nx_ce_fwd(_lib.ptr(logits), _lib.ptr(labels), _lib.ptr(stats), rows, V, V, start, 0,
+        _lib.check(_lib.lib(logits).nx_ce_fwd(_lib.ptr(logits), _lib.ptr(labels), _lib.ptr(stats), rows, V, V, start, 0,
                                         _lib.stream()))
         lf = logits.detach().float()
         m = lf.max(-1).values
@@ -234,10 +243,10 @@ def test_adamw_sumsq_clip():
     p = torch.randn(n, device=DEV)
     pr = p.clone().requires_grad_(True)
     m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
-    lp = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    lp = torch.empty(n, device=DEV, dtype=DT)
     opt = torch.optim.AdamW([pr], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
     for step in range(1, 4):
-        g = torch.randn(n, device=DEV).bfloat16()
+        g = torch.randn(n, device=DEV).to(DT)
         acc = torch.zeros(2, device=DEV)
         sumsq_(g, acc)
         assert rel(acc[0], g.float().pow(2).sum()) < 1e-3
@@ -253,7 +262,7 @@ def test_adamw_sumsq_clip():
         assert rel(p, pr.detach()) < 1e-4
         assert rel(lp, pr.detach()) < 1e-2
     # non-finite gradients set the skip flag and the update is a no-op
-    g = torch.full((n,), float("inf"), device=DEV).bfloat16()
+    g = torch.full((n,), float("inf"), device=DEV).to(DT)
     acc = torch.zeros(2, device=DEV)
     sumsq_(g, acc)
     clip_coef_(acc, 1.0, 1.0, out, skip)

@@ -24,12 +24,14 @@ def _build(cfg):
     dict(), dict(gpt_j_residual=False), dict(norm="rmsnorm", activation="swiglu", use_bias_in_mlp=False,
                                              use_bias_in_attn_linear=False, mlp_multiple_of=64),
     dict(num_kv_heads=2), dict(pos_emb="alibi"), dict(sliding_window_width=64), dict(bias_gelu_fusion=True)])
-def test_fused_model_matches_fp32_oracle(variant):
+@pytest.mark.parametrize("precision", ["bfloat16", "fp16"])
+def test_fused_model_matches_fp32_oracle(variant, precision):
     from gpt_neox_b200.models.gpt2_model import cross_entropy
     base = dict(num_layers=2, hidden_size=256, num_attention_heads=4, seq_length=256, max_position_embeddings=256,
                 synthetic_vocab_size=1000, attention_config=[[["flash"], 2]], distributed_backend="nccl")
     base.update(variant)
-    a_gpu, m_gpu = _build(tiny_config(precision="bfloat16", **base))
+    a_gpu, m_gpu = _build(tiny_config(precision=precision, **base))
+    assert next(m_gpu.parameters()).dtype == (torch.float16 if precision == "fp16" else torch.bfloat16)
     sd = {k: v.detach().float().cpu() for k, v in m_gpu.state_dict().items()}
     a_cpu, m_cpu = _build(tiny_config(precision="fp32", use_cpu_initialization=True, **base))
     m_cpu = m_cpu.cpu().float()
@@ -61,14 +63,15 @@ def test_fused_model_matches_fp32_oracle(variant):
     ("gmlp", dict(attention_config=[[["gmlp"], 2]], pos_emb="none", gpt_j_residual=False)),
     ("dmoe", dict(moe_num_experts=4, moe_top_k=2, moe_expert_interval=1, gpt_j_residual=False)),
 ])
-def test_other_model_families_match_fp32_oracle_loss(family, variant):
+@pytest.mark.parametrize("precision", ["bfloat16", "fp16"])
+def test_other_model_families_match_fp32_oracle_loss(family, variant, precision):
     """Mamba / RWKV-6 / gMLP / dMoE stacks: the bf16 CUDA-kernel model and the fp32 PyTorch statement of the
     same model (same weights) agree on the loss, and the CUDA backward produces finite gradients everywhere."""
     from gpt_neox_b200.models.gpt2_model import cross_entropy
     base = dict(num_layers=2, hidden_size=256, num_attention_heads=4, seq_length=256, max_position_embeddings=256,
                 synthetic_vocab_size=1000, attention_config=[[["flash"], 2]], distributed_backend="nccl")
     base.update(variant)
-    a_gpu, m_gpu = _build(tiny_config(precision="bfloat16", **base))
+    a_gpu, m_gpu = _build(tiny_config(precision=precision, **base))
     sd = {k: v.detach().float().cpu() for k, v in m_gpu.state_dict().items()}
     a_cpu, m_cpu = _build(tiny_config(precision="fp32", use_cpu_initialization=True, **base))
     m_cpu = m_cpu.cpu().float()
