@@ -94,6 +94,10 @@ def restore_rng_state(rng):
     if torch.cuda.is_available() and rng.get("cuda_rng_state") is not None:
         torch.cuda.set_rng_state(rng["cuda_rng_state"])
     mpu.get_cuda_rng_tracker().set_states(rng["rng_tracker_states"])
+    if rng.get("kernel_dropout_counters") is not None:
+        # the dropout kernels derive their seeds from call counters, which are part of the random state
+        from ..parallel.random import _kernel_dropout_counters
+        _kernel_dropout_counters(tuple(rng["kernel_dropout_counters"]))
 
 
 def ensure_directory_exists(filename):
@@ -139,6 +143,8 @@ def save_ds_checkpoint(iteration, model, neox_args):
         sd["torch_rng_state"] = torch.get_rng_state()
         sd["cuda_rng_state"] = torch.cuda.get_rng_state() if torch.cuda.is_available() else None
         sd["rng_tracker_states"] = mpu.get_cuda_rng_tracker().get_states()
+        from ..parallel.random import _kernel_dropout_counters
+        sd["kernel_dropout_counters"] = _kernel_dropout_counters()
     if neox_args.checkpoint_validation_with_forward_pass:
         sd["checkpoint_validation_logits"] = do_forward_pass(neox_args=neox_args, model=model)
     tag = get_checkpoint_tag(iteration)
@@ -255,6 +261,7 @@ def load_checkpoint(neox_args, model, optimizer, lr_scheduler, inference=False, 
             rng = {k: state_dict[k] for k in ("random_rng_state", "np_rng_state", "torch_rng_state",
                                               "rng_tracker_states")}
             rng["cuda_rng_state"] = state_dict.get("cuda_rng_state")
+            rng["kernel_dropout_counters"] = state_dict.get("kernel_dropout_counters")
             restore_rng_state(rng)
             # building the data iterators after this point draws from the global generators (DataLoader worker
             # seeds); the training loop re-applies the saved state right before its first step

@@ -248,11 +248,21 @@ def _reshard_optimizer_state(engine, ckpt_dir, mp_rank, pp_rank, is_pipe):
     sds = [torch.load(files[i], map_location="cpu", weights_only=False)["optimizer_state_dict"] for i in sorted(files)]
     for gi, g in enumerate(engine.groups):
         full = {}
-        for key in ("master", "exp_avg", "exp_avg_sq"):
+        eight_bit = g.state_bits == 8 or sds[0]["shards"][gi]["exp_avg"].dtype == torch.uint8
+        if eight_bit:
+            # 8-bit moments are codes relative to per-segment block scales: they do not survive a re-partition.
+            # The master weights are re-cut; the moments restart from zero.
+            print("WARNING: 8-bit optimizer moments are not re-partitioned across a data-parallel resize; "
+                  "they restart from zero", flush=True)
+            for t in (g.exp_avg, g.exp_avg_sq, *(g.q8_scales or [])):
+                t.zero_()
+        for key in (("master",) if eight_bit else ("master", "exp_avg", "exp_avg_sq")):
             parts = [s["shards"][gi][key] for s in sds]
             full[key] = torch.cat(parts) if sds[0]["shards"][gi]["shard_size"] != sds[0]["shards"][gi]["total"] else parts[0]
         n_used = g.offsets[-1] + g.params[-1].numel() if g.params else 0
         for key, dst in (("exp_avg", g.exp_avg), ("exp_avg_sq", g.exp_avg_sq), ("master", g.master)):
+            if key not in full:
+                continue
             src = torch.zeros(g.total, dtype=torch.float32)
             n = min(full[key].numel(), g.total)
             src[:n] = full[key][:n]

@@ -34,6 +34,10 @@ struct AttnBwdParams {
   float scale, scale_log2;
   int causal, window;
   int* err;
+  // dropout as in the forward (same seed and threshold): dP is masked and scaled before delta is subtracted,
+  // and the P^T that feeds dV is the dropped one
+  uint32_t drop_thr, seed_lo, seed_hi;
+  float drop_rp;
 };
 
 // delta = rowsum(O * dO); one warp per (b, h, q) row.
@@ -139,7 +143,7 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_
 // dQ kernel.  smem tiles: 0 = Q, 1 = dO, 2..3 = K ring, 4..5 = V ring.
 // TMEM: S [0,128) dP [128,256) dQ [256,256+DP) dS0 [384,448) dS1 [448,512)
 // ------------------------------------------------------------------------------------------------
-template <int DP>
+template <int DP, bool DROP>
 __global__ void __launch_bounds__(AB_THREADS, 1)
     attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -261,6 +265,18 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
         tmem_ld_32x32b_x32(T_S + c * 32 + lane_off, sv);
         tmem_ld_32x32b_x32(T_DP + c * 32 + lane_off, dv);
         tmem_ld_wait();
+        if (DROP) {
+          // dP of a dropped probability is zero, of a kept one it carries the 1 / (1 - p) factor
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const int kk = k0 + c * 32 + j;
+            const uint32_t patch = dropout_patch(p.seed_lo, p.seed_hi, static_cast<uint32_t>(batch * p.H + head),
+                                                 static_cast<uint32_t>(qi) >> 1, static_cast<uint32_t>(kk) >> 1);
+            dv[j] = dropout_keep(patch, qi, kk, p.drop_thr) ? __float_as_uint(__uint_as_float(dv[j]) * p.drop_rp) : 0u;
+            dv[j + 1] = dropout_keep(patch, qi, kk + 1, p.drop_thr)
+                            ? __float_as_uint(__uint_as_float(dv[j + 1]) * p.drop_rp) : 0u;
+          }
+        }
         uint32_t pk[16];
         if (!need_mask && p.alibi == nullptr) {
 #pragma unroll
@@ -347,7 +363,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 // TMEM: S^T [0,128) (P^T bf16 overwrites cols [0,64)), dP^T [128,256) (dS^T bf16 over [128,192)),
 //       dK [256,256+DP), dV [384,384+DP)
 // ------------------------------------------------------------------------------------------------
-template <int DP>
+template <int DP, bool DROP>
 __global__ void __launch_bounds__(AB_THREADS, 1)
     attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -462,6 +478,17 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
         tmem_ld_32x32b_x32(T_DPT + c * 32 + lane_off, dv);
         tmem_ld_wait();
         uint32_t pp[16], pd[16];
+        float keepf[32];      // DROP: 0 or 1 / (1 - p) per query column of this chunk (unused otherwise)
+        if (DROP) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const int qq = q0 + c * 32 + j;
+            const uint32_t patch = dropout_patch(p.seed_lo, p.seed_hi, static_cast<uint32_t>(batch * p.H + head),
+                                                 static_cast<uint32_t>(qq) >> 1, static_cast<uint32_t>(kcol) >> 1);
+            keepf[j] = dropout_keep(patch, qq, kcol, p.drop_thr) ? p.drop_rp : 0.f;
+            keepf[j + 1] = dropout_keep(patch, qq + 1, kcol, p.drop_thr) ? p.drop_rp : 0.f;
+          }
+        }
         if (plain) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
@@ -472,7 +499,9 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               pr[e] = exp2f(fmaf(__uint_as_float(sv[j + e]), p.scale_log2, -lq[e]));
-              ds[e] = pr[e] * (__uint_as_float(dv[j + e]) - dq_[e]);     // softmax scale: once, on dK, in the epilogue
+              const float dpe = DROP ? __uint_as_float(dv[j + e]) * keepf[j + e] : __uint_as_float(dv[j + e]);
+              ds[e] = pr[e] * (dpe - dq_[e]);     // softmax scale: once, on dK, in the epilogue
+              if (DROP) pr[e] *= keepf[j + e];    // dV takes the dropped probabilities
             }
             pp[j >> 1] = pack_h16x2(pr[0], pr[1]);
             pp[(j >> 1) + 1] = pack_h16x2(pr[2], pr[3]);
@@ -493,7 +522,9 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
               if (p.alibi != nullptr) x += fmaf(-slope2, static_cast<float>(idx), bias0);
               pr[e] = exp2f(x);
               if (idx < lo || idx > hi) pr[e] = 0.f;
-              ds[e] = pr[e] * (__uint_as_float(dv[j + e]) - dq_[e]);
+              const float dpe = DROP ? __uint_as_float(dv[j + e]) * keepf[j + e] : __uint_as_float(dv[j + e]);
+              ds[e] = pr[e] * (dpe - dq_[e]);
+              if (DROP) pr[e] *= keepf[j + e];
             }
             pp[j >> 1] = pack_h16x2(pr[0], pr[1]);
             pp[(j >> 1) + 1] = pack_h16x2(pr[2], pr[3]);
@@ -569,22 +600,22 @@ static bool bwd_map(CUtensorMap* m, const void* base, int B, int Hh, int S, int 
   return make_tma_4d(m, base, dims, strides, box, 2, true);
 }
 
-template <int DP>
+template <int DP, bool DROP>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                       const CUtensorMap& tdo, const AttnBwdParams& p, cudaStream_t s) {
   static bool cfg = false;
   if (!cfg) {
-    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel<DP, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        BwdSmem<DP>::DYN));
-    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<DP, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        BwdSmem<DP>::DYN));
     cfg = true;
   }
   dim3 gq((p.Sq + AB - 1) / AB, p.H, p.B);
-  attn_bwd_dq_kernel<DP><<<gq, AB_THREADS, BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
+  attn_bwd_dq_kernel<DP, DROP><<<gq, AB_THREADS, BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
   NX_LAUNCH_CHECK();
   dim3 gk((p.Sk + AB - 1) / AB, p.Hk, p.B);
-  attn_bwd_dkv_kernel<DP><<<gk, AB_THREADS, BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
+  attn_bwd_dkv_kernel<DP, DROP><<<gk, AB_THREADS, BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
@@ -592,7 +623,8 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 }  // namespace nx
 
 // Views as in nx_flash_attn_fwd (element strides batch, head, seq).  delta: fp32 scratch [B,H,Sq]
-// provided by the caller.  dq/dk/dv: bf16 strided outputs, fully overwritten.
+// provided by the caller.  dq/dk/dv: 16-bit strided outputs, fully overwritten.  dropout_p / seed: the
+// values the forward was given.
 NX_API int NX_SYM(nx_flash_attn_bwd)(const void* q, const void* k, const void* v, const void* o, const void* dO,
                              const void* lse, void* delta, void* dq, void* dk, void* dv,
                              const void* alibi, int B, int H, int Hk, int Sq, int Sk, int D,
@@ -602,9 +634,11 @@ NX_API int NX_SYM(nx_flash_attn_bwd)(const void* q, const void* k, const void* v
                              long long do_sb, long long do_sh, long long do_ss, long long dq_sb,
                              long long dq_sh, long long dq_ss, long long dk_sb, long long dk_sh,
                              long long dk_ss, long long dv_sb, long long dv_sh, long long dv_ss,
-                             float scale, int causal, int window, void* stream_) {
+                             float scale, int causal, int window, float dropout_p,
+                             unsigned long long seed, void* stream_) {
   using namespace nx;
   if (B == 0 || H == 0 || Sq == 0 || Sk == 0) return NX_OK;
+  NX_REQUIRE(dropout_p >= 0.f && dropout_p < 1.f, "flash_attn_bwd: dropout probability %f outside [0, 1)", dropout_p);
   NX_REQUIRE(D % 8 == 0 && D <= 128 && D > 0, "flash_attn_bwd: head dim %d unsupported", D);
   NX_REQUIRE(Hk > 0 && H % Hk == 0, "flash_attn_bwd: H=%d not a multiple of Hk=%d", H, Hk);
   auto aligned = [](const void* ptr, long long a, long long b, long long c) {
@@ -655,6 +689,12 @@ NX_API int NX_SYM(nx_flash_attn_bwd)(const void* q, const void* k, const void* v
   p.scale = scale; p.scale_log2 = scale * LOG2E;
   p.causal = causal; p.window = window;
   p.err = device_error_word();
-  if (D <= 64) return launch_bwd<64>(tq, tk, tv, tdo, p, s);
-  return launch_bwd<128>(tq, tk, tv, tdo, p, s);
+  p.drop_thr = static_cast<uint32_t>(dropout_p * 256.f + 0.5f);
+  if (p.drop_thr > 255u) p.drop_thr = 255u;
+  p.drop_rp = 256.f / static_cast<float>(256u - p.drop_thr);
+  p.seed_lo = static_cast<uint32_t>(seed);
+  p.seed_hi = static_cast<uint32_t>(seed >> 32);
+  if (p.drop_thr > 0u) return D <= 64 ? launch_bwd<64, true>(tq, tk, tv, tdo, p, s) : launch_bwd<128, true>(tq, tk, tv, tdo, p, s);
+  if (D <= 64) return launch_bwd<64, false>(tq, tk, tv, tdo, p, s);
+  return launch_bwd<128, false>(tq, tk, tv, tdo, p, s);
 }

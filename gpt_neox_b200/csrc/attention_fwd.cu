@@ -40,6 +40,10 @@ struct AttnFwdParams {
   int causal;
   int window;  // < 0: unlimited look-back
   int* err;
+  // dropout on the normalised probabilities (DROP kernels only): keep iff hash byte >= drop_thr, kept
+  // values scaled by drop_rp = 256 / (256 - drop_thr)
+  uint32_t drop_thr, seed_lo, seed_hi;
+  float drop_rp;
 };
 
 template <int DP>
@@ -124,7 +128,8 @@ __device__ __forceinline__ uint32_t pack_h16x2_alu(float lo, float hi) {
 // S -> P dependency chain per block, not by the MUFU pipe, so extra ALU instructions cost more than they
 // save); 1 = MUFU + integer packing; 2 = every second exp2 as the polynomial + integer packing
 // (NEOX_ATTN_EXP selects).
-template <int DP, int EXPV>
+// DROP: dropout on the probabilities (the row sum stays that of the undropped softmax).
+template <int DP, int EXPV, bool DROP = false>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
@@ -355,9 +360,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             x0 = __uint_as_float(sv[c][j]) - msub;
             x1 = __uint_as_float(sv[c][j + 1]) - msub;
           }
-          const float p0 = exp2f(x0);
-          const float p1 = EXPV == 2 ? exp2_poly(x1) : exp2f(x1);
+          float p0 = exp2f(x0);
+          float p1 = EXPV == 2 ? exp2_poly(x1) : exp2f(x1);
           rs[(j >> 1) & 3] += p0 + p1;
+          if (DROP) {
+            const int kk = k0 + col0 + c * 32 + j;        // even: (kk, kk + 1) share one patch
+            const uint32_t patch = dropout_patch(p.seed_lo, p.seed_hi, static_cast<uint32_t>(batch * p.H + head),
+                                                 static_cast<uint32_t>(qi) >> 1, static_cast<uint32_t>(kk) >> 1);
+            if (!dropout_keep(patch, qi, kk, p.drop_thr)) p0 = 0.f;
+            if (!dropout_keep(patch, qi, kk + 1, p.drop_thr)) p1 = 0.f;
+          }
           pk[j >> 1] = EXPV == 0 ? pack_h16x2(p0, p1) : pack_h16x2_alu(p0, p1);
         }
         tmem_st_32x32b_x16(T_P + st * 64 + half * 32 + c * 16 + lane_off, pk);
@@ -385,7 +397,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       l += other;
     }
     if (!aborted) {
-      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      const float inv_l = (l > 0.f ? 1.f / l : 0.f) * (DROP ? p.drop_rp : 1.f);
       const bool row_ok = qi < p.Sq;
       h16* orow = p.o + batch * p.o_sb + head * p.o_sh + static_cast<long long>(qi) * p.o_ss;
 #pragma unroll 1
@@ -446,16 +458,20 @@ static bool attn_map(CUtensorMap* m, const void* base, int B, int Hh, int S, int
 // q [B,H,Sq,D], k/v [B,Hk,Sk,D], o [B,H,Sq,D] as strided views (element strides for batch, head,
 // sequence; head dim contiguous); lse: fp32 [B,H,Sq_pad] (Sq rounded up to 128), receives the
 // base-2 log-sum-exp of the scaled scores for rows < Sq (the caller pre-fills it with +inf).  alibi: fp32 [H] or null.
-// window < 0: no sliding window.  D % 8 == 0, D <= 128.
+// window < 0: no sliding window.  D % 8 == 0, D <= 128.  dropout_p > 0: dropout on the probabilities with
+// the mask of dropout_patch() under `seed` (the backward must be given the same p and seed).
 NX_API int NX_SYM(nx_flash_attn_fwd)(const void* q, const void* k, const void* v, void* o, void* lse,
                              const void* alibi, int B, int H, int Hk, int Sq, int Sk, int D,
                              long long q_sb, long long q_sh, long long q_ss, long long k_sb,
                              long long k_sh, long long k_ss, long long v_sb, long long v_sh,
                              long long v_ss, long long o_sb, long long o_sh, long long o_ss,
-                             float scale, int causal, int window, void* stream_) {
+                             float scale, int causal, int window, float dropout_p,
+                             unsigned long long seed, void* stream_) {
   using namespace nx;
   if (B == 0 || H == 0 || Sq == 0) return NX_OK;
   NX_REQUIRE(D % 8 == 0 && D <= 128 && D > 0, "flash_attn: head dim %d unsupported (need %%8, <=128)", D);
+  NX_REQUIRE(dropout_p >= 0.f && dropout_p < 1.f, "flash_attn: dropout probability %f outside [0, 1)", dropout_p);
+  NX_REQUIRE(dropout_p == 0.f || (Sq <= 131072 && Sk <= 131072), "flash_attn: dropout needs sequences <= 131072");
   NX_REQUIRE(Hk > 0 && H % Hk == 0, "flash_attn: H=%d not a multiple of Hk=%d", H, Hk);
   NX_REQUIRE(Sk >= 1, "flash_attn: empty key sequence");
   NX_REQUIRE((o_ss % 8) == 0 && (o_sh % 8) == 0 && (o_sb % 8) == 0 &&
@@ -473,6 +489,12 @@ NX_API int NX_SYM(nx_flash_attn_fwd)(const void* q, const void* k, const void* v
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal; p.window = window;
   p.err = device_error_word();
+  p.drop_thr = static_cast<uint32_t>(dropout_p * 256.f + 0.5f);     // p in steps of 1 / 256
+  if (p.drop_thr > 255u) p.drop_thr = 255u;
+  p.drop_rp = 256.f / static_cast<float>(256u - p.drop_thr);
+  p.seed_lo = static_cast<uint32_t>(seed);
+  p.seed_hi = static_cast<uint32_t>(seed >> 32);
+  const bool drop = p.drop_thr > 0u;
   dim3 grid((Sq + ATT_BM - 1) / ATT_BM, H, B);
   auto s = (cudaStream_t)stream_;
   static const int expv = [] {
@@ -480,17 +502,20 @@ NX_API int NX_SYM(nx_flash_attn_fwd)(const void* q, const void* k, const void* v
     const int v = e ? atoi(e) : 0;
     return v < 0 || v > 2 ? 0 : v;
   }();
-#define NX_ATTN_LAUNCH(DPV, EV)                                                                              \
+#define NX_ATTN_LAUNCH(DPV, EV, ...)                                                                         \
   do {                                                                                                       \
     static bool cfg = false;                                                                                 \
+    auto kern = attn_fwd_kernel<DPV, EV, ##__VA_ARGS__>;                                                     \
     if (!cfg) {                                                                                              \
-      NX_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<DPV, EV>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                         AttnSmem<DPV>::DYN));                                               \
+      NX_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<DPV>::DYN)); \
       cfg = true;                                                                                            \
     }                                                                                                        \
-    attn_fwd_kernel<DPV, EV><<<grid, ATT_THREADS, AttnSmem<DPV>::DYN, s>>>(tq, tk, tv, p);                   \
+    kern<<<grid, ATT_THREADS, AttnSmem<DPV>::DYN, s>>>(tq, tk, tv, p);                                       \
   } while (0)
-  if (D <= 64) {
+  if (drop) {
+    if (D <= 64) NX_ATTN_LAUNCH(64, 0, true);
+    else NX_ATTN_LAUNCH(128, 0, true);
+  } else if (D <= 64) {
     if (expv == 0) NX_ATTN_LAUNCH(64, 0);
     else if (expv == 1) NX_ATTN_LAUNCH(64, 1);
     else NX_ATTN_LAUNCH(64, 2);

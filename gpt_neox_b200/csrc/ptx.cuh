@@ -413,6 +413,30 @@ __device__ __forceinline__ void gelu_tanh_both(float x, float& g, float& dg) {
   g = x * h;
   dg = fmaf(0.5f * x * (1.0f - t * t), fmaf(0.1070322243f, x * x, 0.79788456f), h);
 }
+// ---------------------------------------------------------------------------
+// attention dropout: the keep / drop decision of probability (q, k) of one (batch, head) is a pure
+// function of (seed, batch * heads + head, q, k), so the forward and both backward kernels regenerate
+// the same mask whatever their thread-to-element mapping.  One 32-bit hash serves the 2 x 2 patch
+// (q & ~1, k & ~1): byte (q & 1) * 2 + (k & 1) is compared with the threshold.  p is quantised to 1/256.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7feb352du;
+  x ^= x >> 15;
+  x *= 0x846ca68bu;
+  x ^= x >> 16;
+  return x;
+}
+// q2 = q >> 1, k2 = k >> 1 (each below 65536).
+__device__ __forceinline__ uint32_t dropout_patch(uint32_t seed_lo, uint32_t seed_hi, uint32_t bh, uint32_t q2,
+                                                  uint32_t k2) {
+  uint32_t x = mix32(((q2 << 16) | k2) ^ seed_lo);
+  return mix32(x + bh * 0x9e3779b9u + seed_hi);
+}
+__device__ __forceinline__ bool dropout_keep(uint32_t patch, int q, int k, uint32_t threshold) {
+  return ((patch >> ((((q & 1) << 1) | (k & 1)) * 8)) & 0xffu) >= threshold;
+}
+
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float silu_grad(float x) {
   const float s = 1.0f / (1.0f + __expf(-x));

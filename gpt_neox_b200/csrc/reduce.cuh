@@ -32,6 +32,21 @@ __device__ __forceinline__ float2 block_sum2(float a, float b, float* sh) {
   rb = warp_sum(rb);
   return make_float2(ra, rb);
 }
+// Block-wide maximum of two non-negative values at once; `sh` must hold 2 * 32 floats. All threads get the result.
+__device__ __forceinline__ float2 block_max2(float a, float b, float* sh) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  a = warp_max(a);
+  b = warp_max(b);
+  __syncthreads();
+  if (lane == 0) {
+    sh[warp] = a;
+    sh[32 + warp] = b;
+  }
+  __syncthreads();
+  float ra = lane < nw ? sh[lane] : 0.f;
+  float rb = lane < nw ? sh[32 + lane] : 0.f;
+  return make_float2(warp_max(ra), warp_max(rb));
+}
 __device__ __forceinline__ float block_sum(float a, float* sh) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
   a = warp_sum(a);

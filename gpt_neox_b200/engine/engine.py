@@ -41,7 +41,7 @@ def _is_replicated(p) -> bool:
 class FlatGroup:
     """One flat parameter space reduced over one data-parallel process group."""
 
-    def __init__(self, entries, dp_group, dp_size, dp_rank, zero_stage, grad_dtype):
+    def __init__(self, entries, dp_group, dp_size, dp_rank, zero_stage, grad_dtype, state_bits=32):
         # entries: list of (param, weight_decay)
         self.dp_group, self.dp_size, self.dp_rank = dp_group, dp_size, dp_rank
         self.zero_stage = zero_stage
@@ -91,14 +91,22 @@ class FlatGroup:
             self.master = self.flat_lp[s:e]
         else:
             self.master = self.flat_lp[s:e].float()
-        self.exp_avg = torch.zeros(self.shard_size, dtype=torch.float32, device=self.device)
-        self.exp_avg_sq = torch.zeros(self.shard_size, dtype=torch.float32, device=self.device)
+        # Adam moments of the shard: fp32, or (``use_bnb_optimizer``) one byte per element with one fp32 scale per
+        # 2048 elements of every segment (ops/optim.py adamw8bit_step_)
+        self.state_bits = state_bits
+        state_dtype = torch.float32 if state_bits == 32 else torch.uint8
+        self.exp_avg = torch.zeros(self.shard_size, dtype=state_dtype, device=self.device)
+        self.exp_avg_sq = torch.zeros(self.shard_size, dtype=state_dtype, device=self.device)
         # my shard's intersections with the regions: (lo, hi, wd, replicated, norm_skip, lr_mult), shard-relative
         self.segments = []
         for (a, b, wd, rep, skip, lrm) in self.regions:
             lo, hi = max(a, s), min(b, e)
             if hi > lo:
                 self.segments.append((lo - s, hi - s, wd, rep, skip, lrm))
+        self.q8_scales = None
+        if state_bits == 8:
+            self.q8_scales = [torch.zeros((2, optim_ops.q8_blocks(hi - lo)), dtype=torch.float32, device=self.device)
+                              for (lo, hi, *_rest) in self.segments]
 
     def _try_symmetric_workspace(self, grad_dtype):
         """ZeRO over peer memory: put the gradient and parameter buffers into a symmetric allocation of the
@@ -188,10 +196,18 @@ class FlatGroup:
         return {"master": self.master.detach().clone().cpu() if self.lp_dtype != torch.float32 else
                 self.master.detach().clone().cpu(),
                 "exp_avg": self.exp_avg.cpu(), "exp_avg_sq": self.exp_avg_sq.cpu(),
+                "q8_scales": None if self.q8_scales is None else [t.cpu() for t in self.q8_scales],
                 "shard_start": self.shard_start, "shard_size": self.shard_size, "total": self.total}
 
     def load_shard_state(self, sd):
-        if sd["shard_size"] == self.shard_size and sd["shard_start"] == self.shard_start:
+        if sd["shard_size"] == self.shard_size and sd["shard_start"] == self.shard_start and \
+                sd["exp_avg"].dtype == self.exp_avg.dtype:
+            if self.q8_scales is not None:
+                saved = sd.get("q8_scales") or []
+                if [tuple(t.shape) for t in saved] != [tuple(t.shape) for t in self.q8_scales]:
+                    return False
+                for dst, src in zip(self.q8_scales, saved):
+                    dst.copy_(src)
             self.exp_avg.copy_(sd["exp_avg"])
             self.exp_avg_sq.copy_(sd["exp_avg_sq"])
             if self.lp_dtype != torch.float32:
@@ -210,7 +226,7 @@ class FlatAdam:
     reads them from its engine's optimizer (megatron/training.py:1380,1518)."""
 
     def __init__(self, groups, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, adam_w_mode=True,
-                 generic_cls=None, generic_kwargs=None):
+                 generic_cls=None, generic_kwargs=None, state_bits=32):
         self.groups = groups
         self.defaults = {"lr": lr, "betas": tuple(betas), "eps": eps, "weight_decay": weight_decay}
         self.adam_w_mode = adam_w_mode
@@ -272,7 +288,14 @@ class FlatAdam:
         for g in self.groups:
             gs = g.grad_shard()
             lp_shard = g.flat_lp[g.shard_start:g.shard_start + g.shard_size] if g.lp_dtype != torch.float32 else None
-            for (lo, hi, wd, _rep, _skip, lrm) in g.segments:
+            for i, (lo, hi, wd, _rep, _skip, lrm) in enumerate(g.segments):
+                if g.state_bits == 8:
+                    optim_ops.adamw8bit_step_(g.master[lo:hi], g.exp_avg[lo:hi], g.exp_avg_sq[lo:hi], g.q8_scales[i][0],
+                                              g.q8_scales[i][1], gs[lo:hi],
+                                              lp_shard[lo:hi] if lp_shard is not None else None, lr=lr * lrm, beta1=b1,
+                                              beta2=b2, eps=eps, weight_decay=wd, step=self.step_count,
+                                              adam_w_mode=self.adam_w_mode, grad_scale=grad_scale, skip=skip)
+                    continue
                 optim_ops.adamw_step_(g.master[lo:hi], g.exp_avg[lo:hi], g.exp_avg_sq[lo:hi], gs[lo:hi],
                                       lp_shard[lo:hi] if lp_shard is not None else None,
                                       lr=lr * lrm, beta1=b1, beta2=b2, eps=eps, weight_decay=wd, step=self.step_count,
@@ -328,6 +351,8 @@ class Engine(torch.nn.Module):
         self.bfloat16_enabled = a.precision == "bfloat16"
         self.loss_scaler = build_loss_scaler(a.fp16) if self.fp16_enabled else LossScaler(1.0)
         grad_dtype = torch.float32 if (a.fp32_grad_accum or a.precision == "fp32") else a.params_dtype
+        # 8-bit Adam moments when the optimizer configuration asks for them (and the fused Adam path is the optimizer)
+        state_bits = int((optimizer_cfg or {}).get("state_bits", 32)) if not generic_optimizer else 32
         dense, expert = [], []
         for pg in param_groups:
             wd = pg.get("weight_decay", a.weight_decay)
@@ -347,13 +372,13 @@ class Engine(torch.nn.Module):
         for ents in by_dtype(dense):
             gd = torch.float32 if ents[0][0].dtype == torch.float32 else grad_dtype
             self.groups.append(FlatGroup(ents, mpu.get_data_parallel_group(), mpu.get_data_parallel_world_size(),
-                                         mpu.get_data_parallel_rank(), self.zero_stage, gd))
+                                         mpu.get_data_parallel_rank(), self.zero_stage, gd, state_bits))
         for ents in by_dtype(expert):
             ep = mpu.get_expert_parallel_world_size()
             gd = torch.float32 if ents[0][0].dtype == torch.float32 else grad_dtype
             self.groups.append(FlatGroup(ents, mpu.get_expert_data_parallel_group(),
                                          mpu.get_data_parallel_world_size() // ep,
-                                         mpu.get_data_parallel_rank() // ep, self.zero_stage, gd))
+                                         mpu.get_data_parallel_rank() // ep, self.zero_stage, gd, state_bits))
         self.optimizer = None
         if optimizer_cfg is not None and self.groups:
             self.optimizer = FlatAdam(self.groups, **optimizer_cfg, **(generic_optimizer or {}))

@@ -209,19 +209,34 @@ class EvalHarnessAdapter:
 
     # ------------------------------------------------------------------ harness driver
     def run_eval(self, eval_tasks=None, num_fewshot=0, bootstrap_iters=2, use_cache=False, name="neox", limit=None):
-        try:
-            from lm_eval import evaluator, tasks        # noqa: F401
-        except ImportError as e:
-            raise ImportError("run_eval needs the `lm_eval` package (LM Evaluation Harness); the adapter's "
-                              "loglikelihood / loglikelihood_rolling / generate_until work without it") from e
-        was_training = self._module().training
-        self._module().eval()
+        """Tasks that name local ``.jsonl`` files (eval_tasks/local_tasks.py) are evaluated in-tree, with no further
+        package and no network; every other task goes to ``lm_eval.evaluator`` as in the reference."""
+        from . import local_tasks
         eval_tasks = eval_tasks or ["lambada_openai", "piqa", "hellaswag", "winogrande", "mathqa", "pubmedqa",
                                     "triviaqa"]
-        results = evaluator.simple_evaluate(model=self, tasks=eval_tasks, num_fewshot=num_fewshot, limit=limit,
-                                            bootstrap_iters=bootstrap_iters)
-        if was_training:
-            self._module().train()
+        local = [t for t in eval_tasks if local_tasks.resolve(t) is not None]
+        remote = [t for t in eval_tasks if t not in local]
+        if remote:
+            try:
+                from lm_eval import evaluator, tasks        # noqa: F401
+            except ImportError as e:
+                raise ImportError(f"tasks {remote} need the `lm_eval` package (LM Evaluation Harness); tasks stored as "
+                                  "local .jsonl files (NEOX_EVAL_TASK_DIR) run without it") from e
+        was_training = self._module().training
+        self._module().eval()
+        results = {"results": {}, "versions": {}, "config": {}}
+        try:
+            if remote:
+                results = evaluator.simple_evaluate(model=self, tasks=remote, num_fewshot=num_fewshot, limit=limit,
+                                                    bootstrap_iters=bootstrap_iters)
+            if local:
+                mine = local_tasks.evaluate(self, local, num_fewshot=num_fewshot, limit=limit)
+                results["results"].update(mine["results"])
+                results.setdefault("versions", {}).update(mine["versions"])
+                results.setdefault("config", {}).update(mine["config"])
+        finally:
+            if was_training:
+                self._module().train()
         return results
 
 

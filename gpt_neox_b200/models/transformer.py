@@ -19,7 +19,7 @@ import torch.nn.functional as F
 
 from .. import parallel as mpu
 from ..ops import fused as fused_ops
-from ..ops.attention import flash_attention
+from ..ops.attention import flash_attention, next_dropout_seed
 from ..ops.elementwise import bias_dropout_add
 from ..ops.gemm import gemm as gemm_op
 from ..ops.gemm import linear as linear_op
@@ -287,7 +287,11 @@ class ParallelSelfAttention(nn.Module):
             self.hidden_size_per_attention_head
         has_past = layer_past is not None and (not torch.is_tensor(layer_past) or layer_past.numel() > 0)
         simple = (self.use_flash_attention and not self.use_cache and not has_past and not self.use_qk_layernorm
-                  and self.rpe is None and (self.dropout_p == 0 or not self.training))
+                  and self.rpe is None)
+        # attention dropout runs inside the flash kernels (mask regenerated in the backward); every
+        # tensor-parallel rank draws its own seed stream, as its heads are different heads
+        drop_p = self.dropout_p if self.training else 0.0
+        drop_seed = next_dropout_seed(mpu.get_model_parallel_rank()) if drop_p > 0 else None
         cos = sin = None
         if self.rotary_emb is not None:
             cos, sin = self.rotary_emb(seq_len=mixed.shape[0] + (layer_past[0].shape[0] if has_past else 0))
@@ -295,7 +299,7 @@ class ParallelSelfAttention(nn.Module):
             ctx = fused_ops.qkv_attention(
                 mixed, num_heads=np_, num_kv_heads=kvp, head_dim=hn, rotary_dim=self.rotary_dim, cos=cos, sin=sin,
                 window=self.sliding_window_width if self.sliding_window_width is not None else -1,
-                alibi=self.alibi_embed.slopes if self.pos_emb == "alibi" else None)
+                alibi=self.alibi_embed.slopes if self.pos_emb == "alibi" else None, dropout_p=drop_p, seed=drop_seed)
             present = None
         else:
             q, k, v = self._split_qkv(mixed)
@@ -310,11 +314,12 @@ class ParallelSelfAttention(nn.Module):
                 k = torch.cat((layer_past[0].type_as(k), k), dim=0)
                 v = torch.cat((layer_past[1].type_as(v), v), dim=0)
             present = torch.stack((k, v)) if self.use_cache else None
-            if self.use_flash_attention and (self.dropout_p == 0 or not self.training) and self.rpe is None:
+            if self.use_flash_attention and self.rpe is None:
                 o = flash_attention(q.permute(1, 0, 2, 3), k.permute(1, 0, 2, 3), v.permute(1, 0, 2, 3),
                                     causal=True,
                                     window=self.sliding_window_width if self.sliding_window_width is not None else -1,
-                                    alibi=self.alibi_embed.slopes if self.pos_emb == "alibi" else None)
+                                    alibi=self.alibi_embed.slopes if self.pos_emb == "alibi" else None,
+                                    dropout_p=drop_p, seed=drop_seed)
                 ctx = o.permute(1, 0, 2, 3).reshape(q.shape[0], q.shape[1], np_ * hn)
             else:
                 mask = attention_mask if not self.use_flash_attention else None

@@ -13,10 +13,25 @@ from ..parallel.mappings import scatter_to_sequence_parallel_region
 from .positional_embeddings import SinusoidalPositionalEmbedding
 
 
+class StableEmbedding(nn.Embedding):
+    """Embedding followed by a LayerNorm (parameters under ``norm.``), Xavier-uniform initialised: what the
+    reference takes from bitsandbytes for the serial (position / token-type) embeddings when ``use_bnb_optimizer``
+    is set (megatron/model/word_embeddings.py:71-81), as a plain module here."""
+
+    def __init__(self, num_embeddings, embedding_dim):
+        super().__init__(num_embeddings, embedding_dim)
+        self.norm = nn.LayerNorm(embedding_dim)
+        nn.init.xavier_uniform_(self.weight)
+
+    def forward(self, ids):
+        return self.norm(super().forward(ids))
+
+
 class Embedding(nn.Module):
     def __init__(self, neox_args, hidden_size, vocab_size, max_sequence_length, embedding_dropout_prob,
                  init_method, num_tokentypes=0, use_pos_emb=True):
         super().__init__()
+        self.embedding_module = StableEmbedding if neox_args.use_bnb_optimizer else nn.Embedding
         self.hidden_size, self.init_method, self.num_tokentypes = hidden_size, init_method, num_tokentypes
         self.sequence_parallel = bool(neox_args.sequence_parallel) and mpu.get_model_parallel_world_size() > 1
         self.use_mup = neox_args.use_mup
@@ -27,13 +42,13 @@ class Embedding(nn.Module):
         self.use_pos_emb = use_pos_emb
         self.embedding_type = neox_args.pos_emb if use_pos_emb else None
         if self.use_pos_emb and self.embedding_type == "learned":
-            self.position_embeddings = nn.Embedding(max_sequence_length, hidden_size)
+            self.position_embeddings = self.embedding_module(max_sequence_length, hidden_size)
             self.init_method(self.position_embeddings.weight)
             self.opt_pos_emb_offset = neox_args.opt_pos_emb_offset
         elif self.use_pos_emb and self.embedding_type == "sinusoidal":
             self.position_embeddings = SinusoidalPositionalEmbedding(hidden_size)
         if num_tokentypes > 0:
-            self.tokentype_embeddings = nn.Embedding(num_tokentypes, hidden_size)
+            self.tokentype_embeddings = self.embedding_module(num_tokentypes, hidden_size)
             self.init_method(self.tokentype_embeddings.weight)
         else:
             self.tokentype_embeddings = None
@@ -43,7 +58,7 @@ class Embedding(nn.Module):
         if self.tokentype_embeddings is not None:
             raise Exception("tokentype embeddings is already initialized")
         self.num_tokentypes = num_tokentypes
-        self.tokentype_embeddings = nn.Embedding(num_tokentypes, self.hidden_size)
+        self.tokentype_embeddings = self.embedding_module(num_tokentypes, self.hidden_size)
         self.init_method(self.tokentype_embeddings.weight)
 
     def forward(self, input_ids, position_ids, tokentype_ids=None):

@@ -91,6 +91,7 @@ def _declare(lib):
     sig("nx_ce_fwd", [P, P, P, L, I, L, I, I, P])
     sig("nx_ce_bwd", [P, P, P, P, P, L, I, L, L, I, I, P])
     sig("nx_adamw_step", [P, P, P, P, P, L, F, F, F, F, F, F, F, I, P, P, I, P])
+    sig("nx_adamw8bit_step", [P, P, P, P, P, P, P, L, F, F, F, F, F, F, F, I, P, P, I, P])
     sig("nx_sumsq", [P, L, P, I, P])
     sig("nx_clip_coef", [P, F, F, P, P, P])
     sig("nx_conv1d_silu_fwd", [P, L, L, P, P, P, L, L, I, I, I, I, P])
@@ -114,8 +115,8 @@ def _declare(lib):
     sig("nx_rope", [P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, I, I, P])
     sig("nx_embedding_fwd", [P, P, P, L, I, L, L, P])
     sig("nx_embedding_bwd", [P, P, P, L, I, L, L, P])
-    sig("nx_flash_attn_fwd", [P] * 6 + [I] * 6 + [L] * 12 + [F, I, I, P])
-    sig("nx_flash_attn_bwd", [P] * 11 + [I] * 6 + [L] * 24 + [F, I, I, P])
+    sig("nx_flash_attn_fwd", [P] * 6 + [I] * 6 + [L] * 12 + [F, I, I, F, U, P])
+    sig("nx_flash_attn_bwd", [P] * 11 + [I] * 6 + [L] * 24 + [F, I, I, F, U, P])
     return lib
 
 

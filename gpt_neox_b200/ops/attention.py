@@ -1,4 +1,4 @@
-"""Causal flash attention (GQA, ALiBi, sliding window) on the tcgen05 kernels of
+"""Causal flash attention (GQA, ALiBi, sliding window, dropout, cached decoding with sq != sk) on the tcgen05 kernels of
 csrc/attention_fwd.cu / csrc/attention_bwd.cu, with a PyTorch reference used on CPU and as the
 test oracle.
 
@@ -29,8 +29,58 @@ def alibi_slopes(n_heads: int) -> torch.Tensor:
     return torch.tensor(s, dtype=torch.float32)
 
 
-def attention_reference(q, k, v, *, scale=None, causal=True, window: int = -1, alibi=None):
-    """Plain PyTorch attention in fp32. q [b,sq,h,d], k/v [b,sk,hk,d] -> ([b,sq,h,d], lse [b,h,sq])."""
+_M32 = 0xFFFFFFFF
+
+
+def _mul32(x, c):
+    """(x * c) mod 2^32 on int64 tensors holding 32-bit values, without overflowing 64 bits."""
+    return (x * (c & 0xFFFF) + (((x * (c >> 16)) & 0xFFFF) << 16)) & _M32
+
+
+def _mix32(x):
+    x = x ^ (x >> 16)
+    x = _mul32(x, 0x7FEB352D)
+    x = x ^ (x >> 15)
+    x = _mul32(x, 0x846CA68B)
+    return x ^ (x >> 16)
+
+
+def dropout_threshold(p: float) -> int:
+    """The kernels quantise the dropout probability to 1/256: keep iff hash byte >= this threshold."""
+    return min(255, int(p * 256.0 + 0.5))
+
+
+def dropout_keep_mask(b: int, h: int, sq: int, sk: int, p: float, seed: int, device="cpu") -> torch.Tensor:
+    """The attention kernels' dropout mask as a bool tensor [b, h, sq, sk] (True = kept): the PyTorch
+    statement of ``dropout_patch`` / ``dropout_keep`` in csrc/ptx.cuh.  A pure function of
+    (seed, batch * h + head, q, k), so forward and backward of any implementation agree on it."""
+    thr = dropout_threshold(p)
+    seed &= 0xFFFFFFFFFFFFFFFF
+    seed_lo, seed_hi = seed & _M32, seed >> 32
+    q = torch.arange(sq, device=device, dtype=torch.int64)[:, None]
+    k = torch.arange(sk, device=device, dtype=torch.int64)[None, :]
+    x = _mix32((((q >> 1) << 16) | (k >> 1)) ^ seed_lo)                       # [sq, sk]
+    bh = torch.arange(b * h, device=device, dtype=torch.int64)[:, None, None]
+    patch = _mix32((x[None] + _mul32(bh, 0x9E3779B9) + seed_hi) & _M32)       # [b*h, sq, sk]
+    byte = (patch >> ((((q & 1) << 1) | (k & 1)) * 8)[None]) & 0xFF
+    return (byte >= thr).view(b, h, sq, sk)
+
+
+_DROPOUT_CALLS = {"n": 0}
+
+
+def next_dropout_seed(stream_id: int = 0) -> int:
+    """A fresh 64-bit seed per dropout call: the process seed, a call counter (saved and replayed by activation
+    checkpointing, parallel/random.py) and ``stream_id`` (the tensor-parallel rank: ranks hold different heads)."""
+    _DROPOUT_CALLS["n"] += 1
+    return (torch.initial_seed() * 0x9E3779B97F4A7C15 + _DROPOUT_CALLS["n"] * 0xD1B54A32D192ED03
+            + stream_id * 0x8CB92BA72F3D8DD7) & 0xFFFFFFFFFFFFFFFF
+
+
+def attention_reference(q, k, v, *, scale=None, causal=True, window: int = -1, alibi=None, dropout_p: float = 0.0,
+                        seed: int = 0):
+    """Plain PyTorch attention in fp32. q [b,sq,h,d], k/v [b,sk,hk,d] -> ([b,sq,h,d], lse [b,h,sq]).
+    ``dropout_p`` > 0 applies the kernels' own mask (``dropout_keep_mask``) to the normalised probabilities."""
     b, sq, h, d = q.shape
     sk, hk = k.shape[1], k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
@@ -52,6 +102,9 @@ def attention_reference(q, k, v, *, scale=None, causal=True, window: int = -1, a
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse.unsqueeze(-1))
     p = torch.nan_to_num(p, nan=0.0)
+    if dropout_p > 0:
+        keep = dropout_keep_mask(b, h, sq, sk, dropout_p, seed, q.device)
+        p = p * keep * (256.0 / (256 - dropout_threshold(dropout_p)))
     o = torch.einsum("bhqk,bkhd->bqhd", p, vf)
     return o.to(q.dtype), lse
 
@@ -61,7 +114,7 @@ def _strides_bhs(t):
     return t.stride(0), t.stride(2), t.stride(1)
 
 
-def _fwd(q, k, v, scale, causal, window, alibi):
+def _fwd(q, k, v, scale, causal, window, alibi, dropout_p=0.0, seed=0):
     b, sq, h, d = q.shape
     sk, hk = k.shape[1], k.shape[2]
     o = torch.empty((b, sq, h, d), device=q.device, dtype=q.dtype)
@@ -73,16 +126,16 @@ def _fwd(q, k, v, scale, causal, window, alibi):
     _lib.check(_lib.lib(q).nx_flash_attn_fwd(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(alibi),
         b, h, hk, sq, sk, d, *_strides_bhs(q), *_strides_bhs(k), *_strides_bhs(v), *_strides_bhs(o),
-        float(scale), int(causal), int(window), _lib.stream()), "nx_flash_attn_fwd")
+        float(scale), int(causal), int(window), float(dropout_p), int(seed), _lib.stream()), "nx_flash_attn_fwd")
     return o, lse
 
 
 class _FlashAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, scale, causal, window, alibi):
-        o, lse = _fwd(q, k, v, scale, causal, window, alibi)
+    def forward(ctx, q, k, v, scale, causal, window, alibi, dropout_p=0.0, seed=0):
+        o, lse = _fwd(q, k, v, scale, causal, window, alibi, dropout_p, seed)
         ctx.save_for_backward(q, k, v, o, lse, alibi)
-        ctx.scale, ctx.causal, ctx.window = scale, causal, window
+        ctx.scale, ctx.causal, ctx.window, ctx.dropout = scale, causal, window, (dropout_p, seed)
         return o
 
     @staticmethod
@@ -102,13 +155,19 @@ class _FlashAttnFn(torch.autograd.Function):
             _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(alibi),
             b, h, hk, sq, sk, d, *_strides_bhs(q), *_strides_bhs(k), *_strides_bhs(v), *_strides_bhs(o),
             *_strides_bhs(do), *_strides_bhs(dq), *_strides_bhs(dk), *_strides_bhs(dv),
-            float(ctx.scale), int(ctx.causal), int(ctx.window), _lib.stream()), "nx_flash_attn_bwd")
-        return dq, dk, dv, None, None, None, None
+            float(ctx.scale), int(ctx.causal), int(ctx.window), float(ctx.dropout[0]), int(ctx.dropout[1]),
+            _lib.stream()), "nx_flash_attn_bwd")
+        return dq, dk, dv, None, None, None, None, None, None
 
 
 def flash_attention(q, k, v, *, scale: float | None = None, causal: bool = True, window: int = -1,
-                    alibi: torch.Tensor | None = None) -> torch.Tensor:
-    """q [b,sq,h,d]; k, v [b,sk,hk,d] (h % hk == 0). Query i sits at position i + (sk - sq)."""
+                    alibi: torch.Tensor | None = None, dropout_p: float = 0.0, seed: int | None = None) -> torch.Tensor:
+    """q [b,sq,h,d]; k, v [b,sk,hk,d] (h % hk == 0). Query i sits at position i + (sk - sq) (cached decoding:
+    sq new tokens against sk keys).  ``dropout_p`` > 0: dropout on the probabilities, mask regenerated in the
+    backward from ``seed`` (default: a fresh one per call)."""
+    if dropout_p > 0 and seed is None:
+        seed = next_dropout_seed()
+    seed = seed or 0
     d = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
     window = -1 if window is None else int(window)
@@ -118,5 +177,6 @@ def flash_attention(q, k, v, *, scale: float | None = None, causal: bool = True,
         fix = lambda t: t if (t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0) else t.contiguous()
         if alibi is not None:
             alibi = alibi.to(device=q.device, dtype=torch.float32).contiguous()
-        return _FlashAttnFn.apply(fix(q), fix(k), fix(v), scale, causal, window, alibi)
-    return attention_reference(q, k, v, scale=scale, causal=causal, window=window, alibi=alibi)[0]
+        return _FlashAttnFn.apply(fix(q), fix(k), fix(v), scale, causal, window, alibi, float(dropout_p), seed)
+    return attention_reference(q, k, v, scale=scale, causal=causal, window=window, alibi=alibi, dropout_p=dropout_p,
+                               seed=seed)[0]

@@ -94,7 +94,7 @@ def _qkv_views(qkv, np_, kvp, hn):
 
 class _QKVAttentionFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, qkv, cos, sin, np_, kvp, hn, rot, pos0, scale, window, alibi):
+    def forward(ctx, qkv, cos, sin, np_, kvp, hn, rot, pos0, scale, window, alibi, dropout_p=0.0, seed=0):
         s, b = qkv.shape[0], qkv.shape[1]
         q, k, v = _qkv_views(qkv, np_, kvp, hn)
         if rot > 0:
@@ -109,9 +109,10 @@ class _QKVAttentionFn(torch.autograd.Function):
         _lib.check(_lib.lib(qkv).nx_flash_attn_fwd(
             _lib.ptr(qb), _lib.ptr(kb), _lib.ptr(vb), _lib.ptr(ob), _lib.ptr(lse), _lib.ptr(alibi),
             b, np_, kvp, s, s, hn, *_strides_bhs(qb), *_strides_bhs(kb), *_strides_bhs(vb), *_strides_bhs(ob),
-            float(scale), 1, int(window), _lib.stream()), "nx_flash_attn_fwd")
+            float(scale), 1, int(window), float(dropout_p), int(seed), _lib.stream()), "nx_flash_attn_fwd")
         ctx.save_for_backward(qkv, out, lse, cos, sin, alibi)
         ctx.cfg = (np_, kvp, hn, rot, pos0, scale, window)
+        ctx.dropout = (float(dropout_p), int(seed))
         return out.view(s, b, np_ * hn)
 
     @staticmethod
@@ -135,20 +136,24 @@ class _QKVAttentionFn(torch.autograd.Function):
             _lib.ptr(delta), _lib.ptr(dqb), _lib.ptr(dkb), _lib.ptr(dvb), _lib.ptr(alibi),
             b, np_, kvp, s, s, hn, *_strides_bhs(qb), *_strides_bhs(kb), *_strides_bhs(vb), *_strides_bhs(ob),
             *_strides_bhs(dob), *_strides_bhs(dqb), *_strides_bhs(dkb), *_strides_bhs(dvb),
-            float(scale), 1, int(window), _lib.stream()), "nx_flash_attn_bwd")
+            float(scale), 1, int(window), ctx.dropout[0], ctx.dropout[1], _lib.stream()), "nx_flash_attn_bwd")
         if rot > 0:
             _rope_launch(dq, dq, cos, sin, rot, pos0, True)
             _rope_launch(dk, dk, cos, sin, rot, pos0, True)
-        return (dqkv,) + (None,) * 10
+        return (dqkv,) + (None,) * 12
 
 
 def qkv_attention(qkv, *, num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int = 0,
                   cos=None, sin=None, pos0: int = 0, scale: float | None = None, window: int = -1,
-                  alibi=None):
+                  alibi=None, dropout_p: float = 0.0, seed: int | None = None):
     """Causal self-attention straight from the fused QKV projection output ``qkv`` [s, b, *]
     (heads are this rank's).  Returns the context [s, b, num_heads * head_dim]."""
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     window = -1 if window is None else int(window)
+    if dropout_p > 0 and seed is None:
+        from .attention import next_dropout_seed
+        seed = next_dropout_seed()
+    seed = seed or 0
     if qkv.is_cuda:
         if qkv.dtype not in _lib.H16 or head_dim % 8 or head_dim > 128:
             raise _lib.KernelError(f"qkv_attention: CUDA path needs bf16 and head dim % 8 == 0, <= 128 "
@@ -158,12 +163,12 @@ def qkv_attention(qkv, *, num_heads: int, num_kv_heads: int, head_dim: int, rota
         if alibi is not None:
             alibi = alibi.to(device=qkv.device, dtype=torch.float32).contiguous()
         return _QKVAttentionFn.apply(qkv, cos, sin, num_heads, num_kv_heads, head_dim, rotary_dim, pos0,
-                                     scale, window, alibi)
+                                     scale, window, alibi, float(dropout_p), seed)
     s, b = qkv.shape[0], qkv.shape[1]
     q, k, v = _qkv_views(qkv, num_heads, num_kv_heads, head_dim)
     if rotary_dim > 0:
         q = apply_rotary(q, cos, sin, rotary_dim, pos0)
         k = apply_rotary(k, cos, sin, rotary_dim, pos0)
     o, _ = attention_reference(q.permute(1, 0, 2, 3), k.permute(1, 0, 2, 3), v.permute(1, 0, 2, 3),
-                               scale=scale, causal=True, window=window, alibi=alibi)
+                               scale=scale, causal=True, window=window, alibi=alibi, dropout_p=dropout_p, seed=seed)
     return o.permute(1, 0, 2, 3).reshape(s, b, num_heads * head_dim)

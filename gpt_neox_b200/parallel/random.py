@@ -95,6 +95,16 @@ def model_parallel_cuda_manual_seed(seed: int):
     _TRACKER.add(_MODEL_PARALLEL_RNG, mp_seed)
 
 
+def _kernel_dropout_counters(new=None):
+    """The call counters from which the dropout kernels derive their seeds (attention dropout, bias-dropout-add);
+    returns the current pair and, if given, installs ``new``.  Part of the random state a recompute replays."""
+    from ..ops import attention, elementwise
+    old = (attention._DROPOUT_CALLS["n"], elementwise._DROPOUT_OFFSET["n"])
+    if new is not None:
+        attention._DROPOUT_CALLS["n"], elementwise._DROPOUT_OFFSET["n"] = new
+    return old
+
+
 class _CheckpointFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, run_function, n_tensor, *args):
@@ -103,6 +113,7 @@ class _CheckpointFunction(torch.autograd.Function):
         ctx.cpu_state = torch.get_rng_state()
         ctx.cuda_state = torch.cuda.get_rng_state() if ctx.cuda else None
         ctx.tracker_states = _TRACKER.get_states()
+        ctx.kernel_dropout = _kernel_dropout_counters()
         with torch.no_grad():
             outputs = run_function(*args)
         ctx.inputs = tuple(_stash(a) for a in args)
@@ -117,6 +128,7 @@ class _CheckpointFunction(torch.autograd.Function):
         if ctx.cuda:
             torch.cuda.set_rng_state(ctx.cuda_state)
         _TRACKER.set_states(ctx.tracker_states)
+        bwd_kernel_dropout = _kernel_dropout_counters(ctx.kernel_dropout)    # replay the kernels' own dropout masks
         detached = tuple(_unstash(a) for a in ctx.inputs)
         if _CKPT_CONFIG["synchronize"] and ctx.cuda:
             torch.cuda.synchronize()
@@ -126,6 +138,7 @@ class _CheckpointFunction(torch.autograd.Function):
         if ctx.cuda:
             torch.cuda.set_rng_state(bwd_cuda)
         _TRACKER.set_states(bwd_tracker)
+        _kernel_dropout_counters(bwd_kernel_dropout)
         if isinstance(outputs, torch.Tensor):
             outputs = (outputs,)
         pairs = [(o, g) for o, g in zip(outputs, grads) if isinstance(o, torch.Tensor) and o.requires_grad and g is not None]

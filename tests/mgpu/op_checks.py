@@ -1,0 +1,164 @@
+"""Op-level checks of the NVLink communication layer on the visible GPUs (launched by torchrun, one rank per GPU).
+
+Every fused GEMM + collective (all-gather -> GEMM, GEMM -> reduce-scatter, GEMM -> all-reduce), the stand-alone
+peer-memory collectives, the ZeRO workspace and the expert-parallel dispatch / combine are compared with a plain
+fp32 PyTorch product / reduction whose operands travel over NCCL.  Rank 0 prints ``CHECKS {json}``; any mismatch
+raises on the rank that sees it (the job then exits non-zero).
+"""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+
+def close(out, ref, what, max_tol=2e-2, mean_tol=8e-3):
+    """The tolerances of the single-GPU GEMM tests: maximum error relative to the largest value, mean relative error."""
+    out, ref = out.float(), ref.float()
+    err = (out - ref).abs().max().item() / (ref.abs().max().item() + 1e-6)
+    mean = ((out - ref).abs().mean() / (ref.abs().mean() + 1e-6)).item()
+    assert err < max_tol and mean < mean_tol, f"{what}: max err {err:.4g}, mean rel err {mean:.4g}"
+    return err
+
+
+def nccl_gather_rows(x, group):
+    parts = [torch.empty_like(x) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    return torch.cat(parts, dim=0)
+
+
+def main():
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16}[sys.argv[1] if len(sys.argv) > 1 else "bf16"]
+    rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    group = dist.group.WORLD
+    from gpt_neox_b200.comm import symm
+    from gpt_neox_b200.ops import _lib
+    be = symm.init_group(group)
+    done = {}
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    rnd = lambda *s, scale=1.0: (torch.randn(*s, device=dev, generator=g) * scale).to(dtype)   # noqa: E731
+
+    # ---- all-gather -> GEMM: several 256-row tiles per rank chunk, N not a multiple of the 256-wide tile, and a
+    #      row count whose chunks are 128-row tiles only (the single-CTA kernel)
+    for tag, m_shard, k, n, tb in (("pair", 512, 1088, 1000, False), ("pair_nn", 256, 512, 776, True),
+                                   ("single", 384, 320, 520, False)):
+        x = rnd(m_shard, k)
+        w = rnd(k, n, scale=0.05) if tb else rnd(n, k, scale=0.05)
+        dist.broadcast(w, 0)
+        bias = rnd(n)
+        dist.broadcast(bias, 0)
+        assert be.can_fuse(m_shard * ws, k, n)
+        y, gathered = be.ag_gemm(x, w, trans_b=tb, bias=bias)
+        xf = nccl_gather_rows(x, group)
+        ref = xf.float() @ (w.float() if tb else w.float().t()) + bias.float()
+        assert torch.equal(gathered, xf), f"ag_gemm[{tag}]: gathered operand differs from the NCCL all-gather"
+        done[f"ag_gemm_{tag}"] = close(y, ref, f"ag_gemm[{tag}]")
+
+    # ---- GEMM -> reduce-scatter (+ residual in the epilogue, + bias and a second residual on the owner)
+    for tag, m, k, n, tb in (("pair", 512 * ws, 576, 1000, False), ("pair_nn", 256 * ws, 1024, 520, True),
+                             ("single", 384 * ws, 320, 264, False)):
+        a = rnd(m, k)
+        w = rnd(k, n, scale=0.05) if tb else rnd(n, k, scale=0.05)
+        bias = rnd(n)
+        dist.broadcast(bias, 0)
+        res2 = rnd(m // ws, n)
+        out = be.gemm_rs(a, w, trans_b=tb, bias=bias, residual2=res2)
+        full = a.float() @ (w.float() if tb else w.float().t())
+        dist.all_reduce(full, group=group)
+        rows = m // ws
+        ref = full[rank * rows:(rank + 1) * rows] + bias.float() + res2.float()
+        done[f"gemm_rs_{tag}"] = close(out, ref, f"gemm_rs[{tag}]")
+
+    # ---- GEMM -> all-reduce (tensor parallelism without sequence parallelism)
+    m, k, n = 256 * ws * 2, 448, 1000
+    if be.can_fuse_ar(m, k, n):
+        a, w = rnd(m, k), rnd(n, k, scale=0.05)
+        bias = rnd(n)
+        dist.broadcast(bias, 0)
+        out = be.gemm_ar(a, w, bias=bias).clone()
+        full = a.float() @ w.float().t()
+        dist.all_reduce(full, group=group)
+        done["gemm_ar"] = close(out, full + bias.float(), "gemm_ar")
+
+    # ---- stand-alone collectives over peer memory (16-bit and fp32)
+    for dt, tag in ((dtype, "h16"), (torch.float32, "f32")):
+        x = (torch.randn(ws * 96, 1000, device=dev, generator=g)).to(dt)
+        ref = x.clone().float()
+        dist.all_reduce(ref, group=group)
+        got = be.all_reduce(x.clone())
+        done[f"all_reduce_{tag}"] = close(got, ref, f"all_reduce[{tag}]", 1e-2, 4e-3)
+        rs = be.reduce_scatter0(x.clone())
+        rows = x.shape[0] // ws
+        done[f"reduce_scatter_{tag}"] = close(rs, ref[rank * rows:(rank + 1) * rows], f"reduce_scatter0[{tag}]", 1e-2, 4e-3)
+        ag = be.all_gather0(x[:rows].contiguous())
+        assert torch.equal(ag, nccl_gather_rows(x[:rows].contiguous(), group)), f"all_gather0[{tag}]"
+        done[f"all_gather_{tag}"] = 0.0
+
+    # ---- ZeRO workspace: in-place gradient reduce-scatter and parameter all-gather
+    n_el = ws * 256 * 37
+    for gdt, tag in ((torch.float32, "f32"), (dtype, "h16")):
+        esz = torch.empty((), dtype=gdt).element_size()
+        zw = symm.ZeroWorkspace(group, n_el * esz, n_el * 2)
+        grads = zw.grad_buffer(gdt)
+        grads.copy_(torch.randn(n_el, device=dev, generator=g).to(gdt))
+        ref = grads.clone().float()
+        dist.all_reduce(ref, group=group)
+        dist.barrier(group)
+        zw.reduce_scatter_grads(gdt)
+        torch.cuda.synchronize()
+        shard = n_el // ws
+        done[f"zero_rs_{tag}"] = close(grads[rank * shard:(rank + 1) * shard], ref[rank * shard:(rank + 1) * shard],
+                                       f"zero reduce-scatter[{tag}]", 1e-2, 4e-3)
+        params = zw.param_buffer(dtype)
+        params.zero_()
+        mine = torch.randn(shard, device=dev, generator=g).to(dtype)
+        params[rank * shard:(rank + 1) * shard].copy_(mine)
+        dist.barrier(group)
+        zw.all_gather_params()
+        torch.cuda.synchronize()
+        dist.barrier(group)
+        assert torch.equal(params, nccl_gather_rows(mine, group)), f"zero all-gather[{tag}]"
+        done[f"zero_ag_{tag}"] = 0.0
+        del zw
+
+    # ---- expert parallelism: dispatch / combine as peer loads against the fp32 statement of the experts
+    from gpt_neox_b200.ops import moe_ep
+    T, topk, H, ffn, E = 512, 2, 256, 512, 2 * ws
+    e_local = E // ws
+    x = rnd(T, H)
+    logits = torch.randn(T, E, device=dev, generator=g)
+    wts, idx = torch.softmax(logits, -1).topk(topk, dim=-1)
+    wts = wts.to(dtype)
+    gw = torch.Generator(device="cuda").manual_seed(5)                      # the full expert weights, same on all ranks
+    w1_all = (torch.randn(E * ffn, H, device=dev, generator=gw) * 0.05).to(dtype)
+    w2_all = (torch.randn(E * ffn, H, device=dev, generator=gw) * 0.05).to(dtype)
+    w1 = w1_all[rank * e_local * ffn:(rank + 1) * e_local * ffn].contiguous()
+    w2 = w2_all[rank * e_local * ffn:(rank + 1) * e_local * ffn].contiguous()
+    out = moe_ep.experts_gelu_ep(x, wts, idx, w1, w2, E, group, "erf")
+    ref = torch.zeros(T, H, device=dev)
+    xf = x.float()
+    for e in range(E):
+        h = torch.nn.functional.gelu(xf @ w1_all[e * ffn:(e + 1) * ffn].float().t()).to(dtype).float()
+        ye = (h @ w2_all[e * ffn:(e + 1) * ffn].float()).to(dtype).float()
+        for j in range(topk):
+            sel = idx[:, j] == e
+            ref[sel] += wts[sel, j].float()[:, None] * ye[sel]
+    done["moe_ep"] = close(out, ref, "expert-parallel dispatch / combine", 3e-2, 1.5e-2)
+
+    torch.cuda.synchronize()
+    err = _lib.read_device_error()
+    assert err == 0, f"device error word 0x{err:x}"
+    dist.barrier()
+    if rank == 0:
+        print("CHECKS " + json.dumps({"ws": ws, "dtype": str(dtype), "checks": done}), flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -216,3 +216,50 @@ def test_eval_adapter_scores_are_layout_independent():
     tp2 = run_distributed(_loglikelihoods, 2, tiny_config(model_parallel_size=2, **base), reqs)[0]
     assert len(one) == 4 and all(l < 0 for l, _ in one)
     assert pp2 == one and tp2 == one
+
+
+def _run_local_eval(rank, world, cfg, task_dir):
+    import os
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    from gpt_neox_b200.eval_tasks import run_eval_harness
+    from gpt_neox_b200.initialize import initialize_megatron
+    from gpt_neox_b200.text_generation_utils import forward_model
+    torch.set_num_threads(1)
+    os.environ["NEOX_EVAL_TASK_DIR"] = task_dir
+    mpu.destroy_model_parallel()
+    a = NeoXArgs.from_dict(dict(cfg, global_num_gpus=world))
+    a.configure_distributed_args()
+    a.build_tokenizer()
+    initialize_megatron(a)
+    model, _, _, _ = training.setup_model_and_optimizer(neox_args=a, use_cache=False)
+    return run_eval_harness(model, forward_model, a, batch_size=2, eval_tasks=["choice", "lastword", "wiki"])
+
+
+def test_eval_harness_runs_end_to_end_on_local_task_files(tmp_path):
+    """``run_eval_harness`` (what ``eval.py`` and the in-training evaluation call) on three task files of the three
+    request types, without the lm_eval package: metrics of the harness's shape, identical on one rank and on two
+    pipeline stages, and a task with no local file asks for lm_eval by name."""
+    import json
+    from common import run_distributed
+    rows = [{"query": f"the number after {i} is", "choices": [f" {i + 1}", f" {i + 2}", " zero"], "gold": i % 3}
+            for i in range(6)]
+    (tmp_path / "choice.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    (tmp_path / "lastword.jsonl").write_text("\n".join(json.dumps({"text": f"row {i} ends with the word stop"})
+                                                       for i in range(4)))
+    (tmp_path / "wiki.jsonl").write_text(json.dumps({"document": "a short document of a few words " * 3}))
+    base = dict(use_cpu_initialization=True, make_vocab_size_divisible_by=64, attention_config=[[["global"], 2]],
+                optimizer=None, no_load_optim=True, tokenizer_type="CharLevelTokenizer", dataset_impl="gpt2")
+    one = run_distributed(_run_local_eval, 1, tiny_config(**base), str(tmp_path))[0]
+    res = one["results"]
+    assert set(res) == {"choice", "lastword", "wiki"}
+    assert 0.0 <= res["choice"]["acc"] <= 1.0 and 0.0 <= res["choice"]["acc_norm"] <= 1.0
+    assert res["lastword"]["ppl"] > 1.0 and 0.0 <= res["lastword"]["acc"] <= 1.0
+    assert res["wiki"]["byte_perplexity"] > 1.0 and res["wiki"]["bits_per_byte"] > 0.0
+    pp2 = run_distributed(_run_local_eval, 2, tiny_config(pipe_parallel_size=2, **base), str(tmp_path))[0]
+    for task in res:
+        for metric, v in res[task].items():
+            assert pp2["results"][task][metric] == pytest.approx(v, rel=1e-4), (task, metric)
+    from gpt_neox_b200.eval_tasks import local_tasks
+    assert local_tasks.resolve("hellaswag") is None

@@ -357,7 +357,12 @@ def test_qkv_attention_fused(np_, kvp, hn, rot):
     dict(b=2, sq=512, sk=512, h=4, hk=4, d=128), dict(b=1, sq=300, sk=300, h=4, hk=2, d=96),
     dict(b=1, sq=384, sk=384, h=2, hk=2, d=64), dict(b=1, sq=512, sk=512, h=2, hk=2, d=128, causal=False),
     dict(b=1, sq=512, sk=512, h=2, hk=2, d=128, window=100), dict(b=1, sq=512, sk=512, h=4, hk=4, d=128, alibi=True),
-    dict(b=2, sq=64, sk=320, h=2, hk=1, d=64)])
+    dict(b=2, sq=64, sk=320, h=2, hk=1, d=64),
+    # cached decoding: one new token (and a short chunk) against a long key sequence
+    dict(b=2, sq=1, sk=700, h=4, hk=2, d=128), dict(b=1, sq=5, sk=261, h=2, hk=2, d=64, alibi=True),
+    # dropout on the probabilities: the fp32 oracle applies the kernels' own mask
+    dict(b=2, sq=512, sk=512, h=4, hk=4, d=128, dropout=0.1), dict(b=1, sq=300, sk=300, h=4, hk=2, d=64, dropout=0.25),
+    dict(b=1, sq=384, sk=384, h=2, hk=2, d=128, dropout=0.5, alibi=True, window=200)])
 def test_flash_attention(cfg):
     from gpt_neox_b200.ops.attention import alibi_slopes, attention_reference, flash_attention
     torch.manual_seed(13)
@@ -365,14 +370,48 @@ def test_flash_attention(cfg):
     causal, window = cfg.get("causal", True), cfg.get("window", -1)
     al = alibi_slopes(h).to(DEV) if cfg.get("alibi") else None
     q, k, v = bf(b, sq, h, d, grad=True), bf(b, sk, hk, d, grad=True), bf(b, sk, hk, d, grad=True)
-    o = flash_attention(q, k, v, causal=causal, window=window, alibi=al)
+    drop, seed = cfg.get("dropout", 0.0), 0x1234ABCD5678EF01
+    o = flash_attention(q, k, v, causal=causal, window=window, alibi=al, dropout_p=drop, seed=seed)
     g = bf(b, sq, h, d)
     o.backward(g)
     qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
-    oref, _ = attention_reference(qr, kr, vr, causal=causal, window=window, alibi=al)
+    oref, _ = attention_reference(qr, kr, vr, causal=causal, window=window, alibi=al, dropout_p=drop, seed=seed)
     oref.backward(g.float())
     assert rel(o, oref) < 2e-2
     assert rel(q.grad, qr.grad) < 3e-2 and rel(k.grad, kr.grad) < 3e-2 and rel(v.grad, vr.grad) < 3e-2
+
+
+def test_attention_dropout_mask_statistics_and_seed_dependence():
+    """The mask is a pure function of (seed, batch, head, q, k): the keep rate matches 1 - p (p in steps of 1/256),
+    rows and columns are not correlated, and another seed gives another mask."""
+    from gpt_neox_b200.ops.attention import dropout_keep_mask, dropout_threshold
+    for p in (0.1, 0.5):
+        m = dropout_keep_mask(2, 3, 256, 384, p, 77, DEV).float()
+        want = 1.0 - dropout_threshold(p) / 256.0
+        assert abs(m.mean().item() - want) < 4e-3
+        assert (m.mean(dim=-1) - want).abs().max().item() < 0.15 and (m.mean(dim=-2) - want).abs().max().item() < 0.17
+        assert (m[0, 0] != m[0, 1]).float().mean().item() > 0.1            # heads differ
+        m2 = dropout_keep_mask(2, 3, 256, 384, p, 78, DEV).float()
+        assert (m != m2).float().mean().item() > 0.1                       # seeds differ
+
+
+def test_qkv_attention_dropout_matches_the_oracle_with_the_same_mask():
+    from gpt_neox_b200.ops.fused import qkv_attention
+    from gpt_neox_b200.ops.rope import rotary_tables
+    torch.manual_seed(21)
+    s, b, np_, hn, rot = 256, 2, 4, 64, 16
+    qkv = bf(s, b, 3 * np_ * hn, grad=True)
+    cos, sin = rotary_tables(rot, 512, device=DEV)
+    kw = dict(num_heads=np_, num_kv_heads=np_, head_dim=hn, rotary_dim=rot, dropout_p=0.2, seed=99)
+    x = qkv.clone()
+    out = qkv_attention(x, cos=cos, sin=sin, **kw)
+    qr = qkv.detach().float().cpu().requires_grad_(True)
+    ref = qkv_attention(qr, cos=cos.cpu(), sin=sin.cpu(), **kw)
+    assert rel(out.cpu(), ref) < 2e-2
+    g = bf(s, b, np_ * hn)
+    (gq,) = torch.autograd.grad(out, x, g)
+    ref.backward(g.float().cpu())
+    assert rel(gq.cpu(), qr.grad) < 3e-2
 
 
 def test_device_error_word_roundtrip():

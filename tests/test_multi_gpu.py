@@ -92,3 +92,27 @@ def test_expert_parallel_2_over_peer_memory_matches_nccl_all_to_all():
     assert p2p["moe_p2p"] is True and nccl["moe_p2p"] is False
     assert p2p["losses"] == pytest.approx(nccl["losses"], rel=2e-2)
     assert p2p["losses"][-1] < p2p["losses"][0]
+
+
+def _run_op_checks(nproc, dtype="bf16", timeout=600):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+           os.path.join(HERE, "mgpu", "op_checks.py"), dtype]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=dict(os.environ))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("CHECKS ")][-1]
+    return json.loads(line[len("CHECKS "):])
+
+
+@pytest.mark.parametrize("ws,dtype", [(2, "bf16"), (2, "fp16"), (4, "bf16"), (8, "bf16")])
+def test_communication_ops_match_fp32_references_over_nccl(ws, dtype):
+    """ag_gemm / gemm_rs / gemm_ar, the peer-memory all-reduce / reduce-scatter / all-gather, the ZeRO workspace and
+    the expert-parallel dispatch / combine, each against an fp32 PyTorch product or reduction gathered over NCCL
+    (tests/mgpu/op_checks.py), on 2, 4 and 8 GPUs."""
+    if torch.cuda.device_count() < ws:
+        pytest.skip(f"needs {ws} GPUs")
+    out = _run_op_checks(ws, dtype)
+    assert out["ws"] == ws
+    for name in ("ag_gemm_pair", "ag_gemm_single", "gemm_rs_pair", "gemm_rs_single", "all_reduce_h16", "all_reduce_f32",
+                 "reduce_scatter_h16", "zero_rs_f32", "zero_ag_h16", "moe_ep"):
+        assert name in out["checks"], (name, out)
