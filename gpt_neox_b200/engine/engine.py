@@ -485,9 +485,13 @@ class Engine(torch.nn.Module):
         self._sync_sequence_parallel_grads()
         if self.store_gradients:
             self.stored_gradients = [p.main_grad.detach().clone() for g in self.groups for p in g.params]
+        # 1-bit Adam past its warm-up averages compressed momenta itself: the gradients stay local
+        local_grads = bool(self.optimizer is not None and self.optimizer.generic is not None
+                           and getattr(self.optimizer.generic, "wants_local_gradients", lambda: False)())
         with self._span("grad_reduce"):
             for g in self.groups:
-                g.reduce_gradients()
+                if not local_grads:
+                    g.reduce_gradients()
         # global gradient norm: every element is owned (counted) by exactly one rank of the world
         self._acc.zero_()
         tp_rank0 = mpu.get_model_parallel_rank() == 0
@@ -505,6 +509,8 @@ class Engine(torch.nn.Module):
             dist.all_reduce(self._acc[1:2], op=dist.ReduceOp.MAX)
         dp_avg = 1.0 / max(g.dp_size for g in self.groups) if self.groups else 1.0
         dp_avg *= self._predivide                      # undo what reduce_gradients divided by beforehand
+        if local_grads:
+            dp_avg = 1.0                               # nothing was summed
         inv_scale = dp_avg / (self.loss_scaler.cur_scale if self.fp16_enabled else 1.0)
         optim_ops.clip_coef_(self._acc, self.gradient_clipping, inv_scale, self._scale, self._skip)
         self._last_grad_norm = self._scale[1]

@@ -422,8 +422,14 @@ def get_optimizer(model, neox_args, dummy=False):
     if ot in ("adam", "cpu_adam", "cpu_torch_adam"):
         cfg["adam_w_mode"] = True
     elif ot == "onebitadam":
-        raise NotImplementedError("OneBitAdam (compressed all-reduce over MPI/cupy) is not built: on one NVSwitch "
-                                  "box the uncompressed fused reduce-scatter is faster; use 'Adam'")
+        # the reference lets DeepSpeed build this one (megatron/training.py:1014-1017); here it is an in-tree
+        # optimizer on the engine's generic path (optimizers.py OnebitAdam)
+        from . import optimizers as opts
+        if (neox_args.zero_stage or 0) != 0:
+            raise ValueError("OneBitAdam keeps whole (unpartitioned) optimizer state: set zero_optimization.stage to 0")
+        kw = {k: params[k] for k in ("freeze_step", "eps") if k in params}
+        kw["betas"] = tuple(params.get("betas", (0.9, 0.999)))
+        generic = {"generic_cls": opts.OnebitAdam, "generic_kwargs": kw}
     else:
         from . import optimizers as opts
         table = {"sm3": (opts.SM3, {}), "madgrad_wd": (opts.madgrad_wd, {k: v for k, v in params.items()

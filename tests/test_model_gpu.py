@@ -65,8 +65,8 @@ def test_fused_model_matches_fp32_oracle(variant, precision):
 ])
 @pytest.mark.parametrize("precision", ["bfloat16", "fp16"])
 def test_other_model_families_match_fp32_oracle_loss(family, variant, precision):
-    """Mamba / RWKV-6 / gMLP / dMoE stacks: the bf16 CUDA-kernel model and the fp32 PyTorch statement of the
-    same model (same weights) agree on the loss, and the CUDA backward produces finite gradients everywhere."""
+    """Mamba / RWKV-6 / gMLP / dMoE stacks: the 16-bit CUDA-kernel model and the fp32 PyTorch statement of the
+    same model (same weights) agree on the loss and on the gradient of every parameter."""
     from gpt_neox_b200.models.gpt2_model import cross_entropy
     base = dict(num_layers=2, hidden_size=256, num_attention_heads=4, seq_length=256, max_position_embeddings=256,
                 synthetic_vocab_size=1000, attention_config=[[["flash"], 2]], distributed_backend="nccl")
@@ -86,10 +86,21 @@ def test_other_model_families_match_fp32_oracle_loss(family, variant, precision)
     out_g = m_gpu((x.cuda(), pos.cuda(), am.cuda() if am is not None else None))
     loss_g = cross_entropy(out_g, (y.cuda(), mask.cuda()))
     loss_g.backward()
-    with torch.no_grad():
-        loss_c = cross_entropy(m_cpu((x, pos, am)), (y, mask))
+    loss_c = cross_entropy(m_cpu((x, pos, am)), (y, mask))
+    loss_c.backward()
     assert abs(loss_g.item() - loss_c.item()) < 5e-2 * max(1.0, abs(loss_c.item())) * 0.5, (loss_g.item(), loss_c.item())
-    for n, p in m_gpu.named_parameters():
-        if p.grad is not None:
-            assert torch.isfinite(p.grad).all(), n
-    assert sum(p.grad is not None for p in m_gpu.parameters()) > 4
+    gg = {n: p.grad for n, p in m_gpu.named_parameters() if p.grad is not None}
+    assert len(gg) > 4
+    worst, where, compared = 0.0, None, 0
+    for n, p in m_cpu.named_parameters():
+        if n in gg:
+            assert torch.isfinite(gg[n]).all(), n
+            if p.grad is not None and p.grad.abs().max() > 1e-6:
+                r = ((gg[n].float().cpu() - p.grad).norm() / (p.grad.norm() + 1e-8)).item()
+                compared += 1
+                if r > worst:
+                    worst, where = r, n
+    assert compared > 4
+    # the router of a top-k MoE is discontinuous (a 16-bit rounding can move a token to another expert), so its
+    # stack gets a wider band than the smooth mixers
+    assert worst < (0.25 if family == "dmoe" else 0.12), f"worst relative gradient error {worst} at {where}"

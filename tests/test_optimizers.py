@@ -133,3 +133,68 @@ def test_8bit_adam_follows_32bit_adam_in_the_engine():
     assert got[0] == pytest.approx(ref[0], rel=1e-6)
     assert got == pytest.approx(ref, rel=3e-2)
     assert got[-1] < got[0]
+
+
+def _compressed_mean(rank, world, steps):
+    import torch
+    import torch.distributed as dist
+    from gpt_neox_b200.optimizers import CompressedAllreduce
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.manual_seed(100 + rank)
+    x = torch.randn(1000)                                   # this rank's (constant) vector
+    parts = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(parts, x)
+    mean = torch.stack(parts).mean(0)
+    car = CompressedAllreduce(x.numel(), dist.group.WORLD, x.device)
+    acc = torch.zeros_like(x)
+    first = None
+    for _ in range(steps):
+        out = car(x.clone())
+        first = out.clone() if first is None else first
+        acc += out
+    dist.destroy_process_group()
+    one = ((first - mean).norm() / mean.norm()).item()
+    avg = ((acc / steps - mean).norm() / mean.norm()).item()
+    return one, avg, first.tolist()[:8]
+
+
+def test_compressed_allreduce_is_unbiased_over_time_and_identical_on_all_ranks():
+    """One call gives a 1-bit approximation of the mean (large error); with error feedback on both stages the
+    time average of repeated calls converges to the true mean; every rank ends up with the same vector."""
+    from common import run_distributed
+    out = run_distributed(_compressed_mean, 2, 64)
+    (one0, avg0, head0), (one1, avg1, head1) = out
+    assert head0 == head1
+    assert one0 > 0.3 and avg0 < 0.1 and avg0 < one0 / 4, (one0, avg0)
+
+
+def _onebit_run(rank, world, cfg, steps):
+    import torch
+    from gpt_neox_b200 import parallel as mpu
+    from gpt_neox_b200 import training
+    from gpt_neox_b200.config import NeoXArgs
+    torch.set_num_threads(1)
+    mpu.destroy_model_parallel()
+    a = NeoXArgs.from_dict(dict(cfg, global_num_gpus=world, train_iters=steps, lr_decay_iters=steps))
+    a.configure_distributed_args()
+    a.build_tokenizer()
+    losses = []
+    training.collect_loss_for_unit_test = lambda l: losses.append(float(l))
+    model = training.pretrain(a)
+    opt = model.optimizer.generic
+    checksum = float(sum(p.double().sum() for p in model.module.parameters()))
+    return losses, opt.steps, opt.compression_steps, checksum
+
+
+def test_onebit_adam_trains_with_compressed_momentum_after_the_warmup():
+    """OneBitAdam on two data-parallel ranks (gloo): plain Adam on reduced gradients for ``freeze_step`` steps, then
+    local gradients + the 1-bit momentum all-reduce.  The loss keeps falling in the compressed phase and the
+    replicas stay bit-identical (same parameter checksum on both ranks)."""
+    from common import run_distributed, tiny_config
+    cfg = tiny_config(use_cpu_initialization=True, zero_optimization={"stage": 0}, num_layers=2, hidden_size=128,
+                      optimizer={"type": "OneBitAdam", "params": {"lr": 1e-3, "freeze_step": 6, "betas": [0.9, 0.95]}})
+    (l0, steps, comp, c0), (l1, _, _, c1) = run_distributed(_onebit_run, 2, cfg, 16)
+    assert (steps, comp) == (16, 10)
+    assert c0 == c1
+    assert min(l0[6:]) < l0[5] and l0[-1] < l0[0]
+    assert all(x == x for x in l0)
