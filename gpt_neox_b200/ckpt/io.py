@@ -63,8 +63,9 @@ def _expert_state_dict(module):
 
 
 def _module_state_dict(engine):
-    sd = engine.module.state_dict()
-    return {k: v.detach().cpu() for k, v in sd.items()}
+    with engine.gathered_parameters():             # ZeRO stage 3 keeps only slices between uses
+        sd = engine.module.state_dict()
+        return {k: v.detach().cpu() for k, v in sd.items()}
 
 
 def _pipe_layer_states(module):
@@ -98,9 +99,11 @@ def save_engine_checkpoint(engine, save_dir, tag=None, client_state=None):
         if dp_rank == 0:
             for idx, sd in _pipe_layer_states(engine.module).items():
                 torch.save(sd, os.path.join(tmp_dir, layer_file_name(idx, mp_rank)))
+    # collective under ZeRO stage 3 (the parameters are gathered): every rank takes part, rank 0 of the replicas writes
+    module_sd = None if is_pipe else _module_state_dict(engine)
     if dp_rank == 0 and (pp_rank == 0 or not is_pipe):
         state = {
-            "module": None if is_pipe else _module_state_dict(engine),
+            "module": None if is_pipe else module_sd,
             "optimizer": None,
             "lr_scheduler": engine.lr_scheduler.state_dict() if engine.lr_scheduler is not None else None,
             "dp_world_size": mpu.get_data_parallel_world_size(),
@@ -182,7 +185,8 @@ def load_engine_checkpoint(engine, load_dir, tag=None, load_optimizer_states=Tru
                             break
     else:
         sd = state["module"]
-        _load_into_flat(engine.module, sd, strict=load_module_strict)
+        with engine.gathered_parameters(write_back=True):
+            _load_into_flat(engine.module, sd, strict=load_module_strict)
     if mpu.get_expert_parallel_world_size() > 1 and _expert_param_names(engine.module):
         ef = os.path.join(ckpt_dir, expert_states_name(mpu.get_expert_parallel_rank(), mp_rank,
                                                        pp_rank if is_pipe else None))

@@ -41,7 +41,8 @@ def _is_replicated(p) -> bool:
 class FlatGroup:
     """One flat parameter space reduced over one data-parallel process group."""
 
-    def __init__(self, entries, dp_group, dp_size, dp_rank, zero_stage, grad_dtype, state_bits=32):
+    def __init__(self, entries, dp_group, dp_size, dp_rank, zero_stage, grad_dtype, state_bits=32,
+                 partition_params=False):
         # entries: list of (param, weight_decay)
         self.dp_group, self.dp_size, self.dp_rank = dp_group, dp_size, dp_rank
         self.zero_stage = zero_stage
@@ -60,7 +61,8 @@ class FlatGroup:
         unit = dp_size * 256
         self.total = (off + unit - 1) // unit * unit
         self.offsets = offs
-        self.zero_ws = self._try_symmetric_workspace(grad_dtype)
+        # (stage 3 allocates and frees the full buffers per module: they cannot live in one symmetric allocation)
+        self.zero_ws = None if partition_params else self._try_symmetric_workspace(grad_dtype)
         if self.zero_ws is not None:
             self.flat_lp = self.zero_ws.param_buffer(self.lp_dtype).zero_()
             self.main_grad = self.zero_ws.grad_buffer(grad_dtype).zero_()
@@ -103,6 +105,18 @@ class FlatGroup:
             lo, hi = max(a, s), min(b, e)
             if hi > lo:
                 self.segments.append((lo - s, hi - s, wd, rep, skip, lrm))
+        # ZeRO stage 3: between uses only this rank's slice of the parameters (and of the gradients) is kept
+        self.partition_params = bool(partition_params) and sharded
+        self.grad_dtype = grad_dtype
+        self.shapes = [tuple(p.shape) for p in self.params]
+        self.lp_shard = None
+        self.grad_acc = None
+        if self.partition_params:
+            self.lp_shard = self.flat_lp[s:e].clone()
+            if self.lp_dtype == torch.float32:
+                self.master = self.lp_shard          # fp32 parameters are their own master weights
+            self.grad_acc = torch.zeros(self.shard_size, dtype=grad_dtype, device=self.device)
+            self.release()
         self.q8_scales = None
         if state_bits == 8:
             self.q8_scales = [torch.zeros((2, optim_ops.q8_blocks(hi - lo)), dtype=torch.float32, device=self.device)
@@ -131,18 +145,85 @@ class FlatGroup:
         return ws if int(flag.item()) == 1 else None
 
     def numel(self):
-        return sum(p.numel() for p in self.params)
+        return sum(math.prod(sh) for sh in self.shapes)
+
+    # ------------------------------------------------------------------ ZeRO stage 3: gather / release
+    @property
+    def gathered(self):
+        return self.flat_lp is not None
+
+    def gather(self, with_grads=False):
+        """Materialise the whole flat parameter buffer from the ranks' slices (all-gather) and point the
+        parameters into it; ``with_grads`` also provides the full-size gradient buffer a backward pass writes."""
+        if not self.partition_params:
+            return
+        if self.flat_lp is None:
+            self.flat_lp = torch.empty(self.total, dtype=self.lp_dtype, device=self.device)
+            if self.flat_lp.is_cuda:
+                dist.all_gather_into_tensor(self.flat_lp, self.lp_shard, group=self.dp_group)
+            else:
+                parts = [torch.empty_like(self.lp_shard) for _ in range(self.dp_size)]
+                dist.all_gather(parts, self.lp_shard, group=self.dp_group)
+                self.flat_lp.copy_(torch.cat(parts))
+            for p, o, sh in zip(self.params, self.offsets, self.shapes):
+                p.data = self.flat_lp[o:o + math.prod(sh)].view(sh)
+        if with_grads and self.main_grad is None:
+            self.main_grad = torch.zeros(self.total, dtype=self.grad_dtype, device=self.device)
+            for p, o, sh in zip(self.params, self.offsets, self.shapes):
+                p.main_grad = self.main_grad[o:o + math.prod(sh)].view(sh)
+
+    def release(self):
+        """Drop the gathered buffers; the parameters keep their identity but hold no storage until the next gather."""
+        if not self.partition_params:
+            return
+        for p in self.params:
+            p.data = torch.empty(0, dtype=self.lp_dtype, device=self.device)
+            p.main_grad = None
+        self.flat_lp = None
+        self.main_grad = None
+
+    def finish_backward(self):
+        """After the backward pass of the modules that own these parameters: reduce-scatter the full gradient
+        buffer of this micro-batch into the rank's persistent gradient slice, then release everything."""
+        if not self.partition_params or self.main_grad is None:
+            return
+        self.fold_autograd_grads()
+        if self.predivide != 1.0:
+            self.main_grad.mul_(1.0 / self.predivide)
+        part = torch.empty(self.shard_size, dtype=self.grad_dtype, device=self.device)
+        if self.main_grad.is_cuda:
+            dist.reduce_scatter_tensor(part, self.main_grad, group=self.dp_group)
+        else:
+            dist.all_reduce(self.main_grad, group=self.dp_group)
+            part.copy_(self.main_grad[self.shard_start:self.shard_start + self.shard_size])
+        self.grad_acc.add_(part)
+        self.release()
+
+    def store_shard_from_gathered(self):
+        """Take this rank's slice of the (modified) gathered parameters as the new persistent slice."""
+        if self.partition_params and self.flat_lp is not None:
+            self.lp_shard.copy_(self.flat_lp[self.shard_start:self.shard_start + self.shard_size])
 
     def fold_autograd_grads(self):
         """Parameters whose gradient came through plain autograd (``.grad``) are added into
         ``main_grad``; GEMM weights were accumulated there directly by the wgrad epilogue."""
+        if self.main_grad is None:
+            return
         for p in self.params:
             if p.grad is not None:
                 p.main_grad.add_(p.grad.view_as(p.main_grad).to(p.main_grad.dtype))
                 p.grad = None
 
     def grad_shard(self):
+        if self.partition_params:
+            return self.grad_acc
         return self.main_grad[self.shard_start:self.shard_start + self.shard_size]
+
+    def lp_shard_view(self):
+        """This rank's slice of the low-precision parameters (what the optimizer step writes)."""
+        if self.partition_params:
+            return self.lp_shard
+        return self.flat_lp[self.shard_start:self.shard_start + self.shard_size]
 
     #: gradients are multiplied by 1 / predivide before the reduction (the engine folds the factor back into
     #: its post-reduction scale); comm_dtype, when set, is the dtype the reduction runs in
@@ -150,6 +231,8 @@ class FlatGroup:
     comm_dtype = None
 
     def reduce_gradients(self):
+        if self.partition_params:
+            return                # every micro-batch's gradients were reduce-scattered right after its backward
         if self.predivide != 1.0:
             self.main_grad.mul_(1.0 / self.predivide)
         if self.dp_size == 1:
@@ -174,6 +257,8 @@ class FlatGroup:
             dist.all_reduce(self.main_grad, group=self.dp_group)
 
     def gather_params(self):
+        if self.partition_params:
+            return                # parameters are gathered per module, when its forward / backward needs them
         if self.zero_ws is not None:
             self.zero_ws.all_gather_params()      # push the updated shard into every peer's parameter buffer
             return
@@ -187,7 +272,10 @@ class FlatGroup:
                 self.flat_lp.copy_(torch.cat(parts))
 
     def zero_grad(self):
-        self.main_grad.zero_()
+        if self.partition_params:
+            self.grad_acc.zero_()
+        if self.main_grad is not None:
+            self.main_grad.zero_()
         for p in self.params:
             p.grad = None
 
@@ -217,7 +305,9 @@ class FlatGroup:
 
     def refresh_master_from_lp(self):
         if self.lp_dtype != torch.float32:
-            self.master.copy_(self.flat_lp[self.shard_start:self.shard_start + self.shard_size].float())
+            self.master.copy_(self.lp_shard_view().float())
+        elif self.partition_params:
+            self.master = self.lp_shard
 
 
 class FlatAdam:
@@ -287,7 +377,7 @@ class FlatAdam:
             return
         for g in self.groups:
             gs = g.grad_shard()
-            lp_shard = g.flat_lp[g.shard_start:g.shard_start + g.shard_size] if g.lp_dtype != torch.float32 else None
+            lp_shard = g.lp_shard_view() if g.lp_dtype != torch.float32 else None
             for i, (lo, hi, wd, _rep, _skip, lrm) in enumerate(g.segments):
                 if g.state_bits == 8:
                     optim_ops.adamw8bit_step_(g.master[lo:hi], g.exp_avg[lo:hi], g.exp_avg_sq[lo:hi], g.q8_scales[i][0],
@@ -344,8 +434,9 @@ class Engine(torch.nn.Module):
         self.skipped_steps = 0
         self.global_samples = 0
         self.zero_stage = a.zero_stage if isinstance(a.zero_stage, int) else 0
-        if self.zero_stage >= 3:
-            raise NotImplementedError("ZeRO stage 3 (parameter partitioning) is not built; use stage 0, 1 or 2")
+        if self.zero_stage >= 3 and (mpu.get_model_parallel_world_size() > 1 or a.is_pipe_parallel):
+            raise ValueError("ZeRO stage 3 runs with tensor-parallel size 1 and without pipeline parallelism "
+                             "(as in the reference, megatron/training.py:878-893)")
         self.gradient_clipping = a.gradient_clipping or 0.0
         self.fp16_enabled = a.precision == "fp16"
         self.bfloat16_enabled = a.precision == "bfloat16"
@@ -369,6 +460,11 @@ class Engine(torch.nn.Module):
                 out.setdefault(e[0].dtype, []).append(e)
             return [out[k] for k in sorted(out, key=lambda d: (d != a.params_dtype, str(d)))]
 
+        self._z3_units = []
+        if self.zero_stage >= 3 and mpu.get_data_parallel_world_size() > 1:
+            # stage 3: one flat space per layer of the stack, so that a layer's parameters can be gathered for
+            # its forward / backward and dropped again; a parameter shared by two layers lives with the first
+            dense = self._build_stage3_groups(module, dense, by_dtype, grad_dtype, state_bits)
         for ents in by_dtype(dense):
             gd = torch.float32 if ents[0][0].dtype == torch.float32 else grad_dtype
             self.groups.append(FlatGroup(ents, mpu.get_data_parallel_group(), mpu.get_data_parallel_world_size(),
@@ -415,6 +511,97 @@ class Engine(torch.nn.Module):
         if a.dump_state:
             profiling.dump_state(self)
 
+    # ------------------------------------------------------------------ ZeRO stage 3
+    def _build_stage3_groups(self, module, dense, by_dtype, grad_dtype, state_bits):
+        """Creates the per-layer flat groups, installs the gather / release hooks and returns the entries that
+        belong to no layer (none in the shipped models; they would stay whole as under stage 1)."""
+        wd_of = {id(p): wd for p, wd in dense}
+        seq = getattr(module, "sequential", None)
+        units = list(seq) if seq is not None else [module]
+        owner = {}
+
+        def unit_params(u):
+            """Parameters a layer touches: its own and, for a function layer bound to another layer's module (the
+            tied read-out is ``Lambda(partial(fn, embedding))``), that module's."""
+            ps = list(u.parameters())
+            fn = getattr(u, "func", None)
+            for a_ in list(getattr(fn, "args", ())) + list((getattr(fn, "keywords", None) or {}).values()):
+                if isinstance(a_, torch.nn.Module):
+                    ps += [p for p in a_.parameters() if all(p is not q for q in ps)]
+            return ps
+
+        for u in units:
+            if not isinstance(u, torch.nn.Module):
+                continue
+            mine = [p for p in unit_params(u) if id(p) in wd_of and id(p) not in owner]
+            groups = []
+            for ents in by_dtype([(p, wd_of[id(p)]) for p in mine]):
+                gd = torch.float32 if ents[0][0].dtype == torch.float32 else grad_dtype
+                g = FlatGroup(ents, mpu.get_data_parallel_group(), mpu.get_data_parallel_world_size(),
+                              mpu.get_data_parallel_rank(), self.zero_stage, gd, state_bits, partition_params=True)
+                self.groups.append(g)
+                groups.append(g)
+                for p in g.params:
+                    owner[id(p)] = g
+            needs = []
+            for p in unit_params(u):
+                g = owner.get(id(p))
+                if g is not None and g not in needs:
+                    needs.append(g)
+            if needs:
+                self._z3_units.append((u, needs))
+                u.register_forward_pre_hook(lambda _m, _a, needs=needs: self._z3_before_forward(needs))
+                u.register_forward_hook(lambda _m, _a, _o, needs=needs: self._z3_after_forward(needs))
+                u.register_full_backward_pre_hook(lambda _m, _g, needs=needs: self._z3_before_backward(needs))
+        self._z3_pending = None
+        return [(p, wd) for p, wd in dense if id(p) not in owner]
+
+    def _z3_before_forward(self, needs):
+        for g in needs:
+            g.gather()
+
+    def _z3_after_forward(self, needs):
+        # inside a backward pass (activation recompute) the parameters are needed again at once
+        if self._z3_pending is not needs:
+            for g in needs:
+                if g.main_grad is None:
+                    g.release()
+
+    def _z3_before_backward(self, needs):
+        """A layer's backward is about to run: the layer whose backward ran before it is complete now (its gradients
+        are reduce-scattered and its buffers dropped), and this layer's parameters and gradient buffer are set up."""
+        if self._z3_pending is not None and self._z3_pending is not needs:
+            for g in self._z3_pending:
+                if g not in needs:
+                    g.finish_backward()
+        for g in needs:
+            g.gather(with_grads=True)
+        self._z3_pending = needs
+
+    def _z3_finish(self):
+        if self._z3_units and self._z3_pending is not None:
+            for g in self._z3_pending:
+                g.finish_backward()
+            self._z3_pending = None
+        for g in self.groups:          # parameters shared between layers may still hold a gradient buffer
+            if g.partition_params and g.main_grad is not None:
+                g.finish_backward()
+
+    @contextmanager
+    def gathered_parameters(self, write_back=False):
+        """All parameters materialised (state dicts, conversions, weight surgery).  ``write_back``: the ranks keep
+        their slices of whatever the block wrote into the parameters."""
+        parts = [g for g in self.groups if g.partition_params]
+        for g in parts:
+            g.gather()
+        try:
+            yield
+        finally:
+            for g in parts:
+                if write_back:
+                    g.store_shard_from_gathered()
+                g.release()
+
     # ------------------------------------------------------------------ reference-engine surface
     def train(self, mode=True):
         super().train(mode)
@@ -452,6 +639,7 @@ class Engine(torch.nn.Module):
             scaled = scaled * self.loss_scaler.cur_scale
         with self._span("backward"):
             scaled.backward(retain_graph=retain_graph)
+            self._z3_finish()
         return loss
 
     def _sync_sequence_parallel_grads(self):

@@ -501,7 +501,7 @@ def setup_model_and_optimizer(neox_args, use_cache=False, iteration=None):
             p.requires_grad = False
         reference_model = ref_engine
     mark_norms_for_sequence_parallel_grad_sync(engine.module, neox_args)
-    engine.total_params_count = sum(p.numel() for p in engine.module.parameters())
+    engine.total_params_count = engine.total_params if engine.groups else sum(p.numel() for p in engine.module.parameters())
     print_rank_0(f' > number of parameters on model parallel rank {mpu.get_model_parallel_rank()}: '
                  f'{engine.total_params_count}')
     curr_scheduler = None

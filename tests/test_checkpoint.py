@@ -77,8 +77,9 @@ def test_damaged_checkpoints(tmp_path):
     (1, dict(optimizer={"type": "sm3", "params": {"lr": 1e-3}})),
     (1, dict(gradient_accumulation_steps=2, hidden_dropout=0.1)),
     (2, dict(use_bnb_optimizer=True)),
+    (2, dict(zero_optimization={"stage": 3})),
     (1, dict(attention_dropout=0.1, attention_config=[[["flash"], 2]], checkpoint_activations=True)),
-], ids=["moe_expert_parallel_2", "sm3_state", "dropout_rng", "adam_8bit_state", "attention_dropout_recompute"])
+], ids=["moe_expert_parallel_2", "sm3_state", "dropout_rng", "adam_8bit_state", "zero_stage3", "attention_dropout_recompute"])
 def test_resume_is_exact_for_expert_parallel_generic_optimizer_and_dropout(tmp_path, world, over):
     """Things a resume has to carry beyond the dense weights and Adam moments: the experts of every expert-parallel
     rank (one state file per rank), the own state of SM3 / MADGRAD / Lion / SGD, and the random streams (re-applied

@@ -214,3 +214,41 @@ def test_qk_layernorm_is_not_summed_over_the_group_under_sequence_parallelism():
     a = run_distributed(_train, 2, cfg, 4)[0]
     b = run_distributed(_train, 2, dict(cfg, sequence_parallel=True), 4)[0]
     assert b == pytest.approx(a, rel=2e-6)
+
+
+def _train_stage3(rank, world, cfg, steps):
+    """As _train; also reports how many parameter elements each rank holds between steps and after a gather."""
+    from gpt_neox_b200 import training
+    held = {}
+    orig = training.train_step
+
+    def wrapped(*a, **kw):
+        out = orig(*a, **kw)
+        eng = kw["model"]
+        held["between_steps"] = sum(p.data.numel() for p in eng.module.parameters())
+        held["slices"] = sum(g.lp_shard.numel() for g in eng.groups if g.partition_params)
+        held["total"] = eng.total_params
+        held["groups"] = len(eng.groups)
+        return out
+    training.train_step = wrapped
+    try:
+        return _train(rank, world, cfg, steps), held
+    finally:
+        training.train_step = orig
+
+
+@pytest.mark.parametrize("over", [dict(), dict(checkpoint_activations=True, checkpoint_num_layers=1),
+                                  dict(no_weight_tying=False, gradient_accumulation_steps=2)],
+                         ids=["plain", "activation_checkpointing", "tied_embeddings_gas2"])
+def test_zero_stage3_partitions_parameters_and_matches_stage1(over):
+    """ZeRO stage 3 over two data-parallel ranks: each layer's parameters are gathered for its forward and backward
+    and dropped afterwards (between steps a rank holds no gathered parameter, only its slices: about half the
+    model), gradients are reduce-scattered per layer, and the loss curve is the stage-1 curve."""
+    cfg = tiny_config(use_cpu_initialization=True, num_layers=3, train_micro_batch_size_per_gpu=2, **over)
+    ref = run_distributed(_train, 2, cfg, 5)[0]
+    out = run_distributed(_train_stage3, 2, dict(cfg, zero_optimization={"stage": 3}), 5)
+    (losses, held), (losses1, _) = out
+    assert losses == pytest.approx(losses1, rel=1e-6)
+    assert losses == pytest.approx(ref, rel=2e-5)
+    assert held["between_steps"] == 0 and held["groups"] >= 5
+    assert held["total"] / 2 <= held["slices"] < held["total"] / 2 + 256 * 2 * held["groups"]
