@@ -5,6 +5,7 @@
   ``gpt_neox_b200.ops`` binds with ctypes.
 * ``lib/libneox_data.so`` – the CPU dataset-index builders (g++), the counterpart of the
   reference's ``megatron/data/helpers.cpp`` built by ``megatron/data/Makefile``.
+* ``lib/libneox_host.so`` – host AdamW for optimizer-state offload (g++, csrc/cpu_adam.cpp).
 
 Objects are cached under ``build/`` and rebuilt when a source or any header is newer.
 Run ``python -m gpt_neox_b200.build`` (``--force`` to rebuild everything).
@@ -99,6 +100,19 @@ def build_data_helpers(force: bool = False) -> Path:
     return out
 
 
+def build_host_ops(force: bool = False) -> Path:
+    """``lib/libneox_host.so``: host-side compute used by optimizer-state offload (csrc/cpu_adam.cpp)."""
+    LIB.mkdir(parents=True, exist_ok=True)
+    src = CSRC / "cpu_adam.cpp"
+    out = LIB / "libneox_host.so"
+    if src.exists() and (force or _stale(out, [src])):
+        cmd = [os.environ.get("CXX", "g++"), *CXX_FLAGS, "-fopenmp-simd", "-fvisibility=hidden", str(src), "-o", str(out)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"g++ failed:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
 def build_data_helpers_sanitized(out_dir, cxx=None) -> Path:
     """The dataset-index builders compiled with AddressSanitizer + UBSan (host code only; the GPU pool offers
     no compute-sanitizer).  The library must be loaded into a process that preloads the ASan runtime:
@@ -115,6 +129,7 @@ def build_data_helpers_sanitized(out_dir, cxx=None) -> Path:
 
 def build_all(force: bool = False, verbose: bool = False):
     a = build_data_helpers(force)
+    build_host_ops(force)
     b = build_cuda(force, verbose)
     return a, b
 

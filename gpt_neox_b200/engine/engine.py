@@ -42,7 +42,7 @@ class FlatGroup:
     """One flat parameter space reduced over one data-parallel process group."""
 
     def __init__(self, entries, dp_group, dp_size, dp_rank, zero_stage, grad_dtype, state_bits=32,
-                 partition_params=False):
+                 partition_params=False, offload=None):
         # entries: list of (param, weight_decay)
         self.dp_group, self.dp_size, self.dp_rank = dp_group, dp_size, dp_rank
         self.zero_stage = zero_stage
@@ -117,6 +117,16 @@ class FlatGroup:
                 self.master = self.lp_shard          # fp32 parameters are their own master weights
             self.grad_acc = torch.zeros(self.shard_size, dtype=grad_dtype, device=self.device)
             self.release()
+        # optimizer-state offload: master weights and moments of the shard in (pinned) host memory, plus staging
+        # buffers for the gradient shard on its way down and the new 16-bit weights on their way up
+        self.offload = offload if (offload and state_bits == 32) else None
+        if self.offload:
+            pin = self.device.type == "cuda"
+            host = lambda t: t.detach().to("cpu", copy=True).pin_memory() if pin else t.detach().to("cpu", copy=True)   # noqa: E731
+            self.master = host(self.master.float())
+            self.exp_avg, self.exp_avg_sq = host(self.exp_avg), host(self.exp_avg_sq)
+            self.host_grad = host(torch.zeros(self.shard_size, dtype=grad_dtype))
+            self.host_lp = host(torch.zeros(self.shard_size, dtype=self.lp_dtype))
         self.q8_scales = None
         if state_bits == 8:
             self.q8_scales = [torch.zeros((2, optim_ops.q8_blocks(hi - lo)), dtype=torch.float32, device=self.device)
@@ -298,12 +308,15 @@ class FlatGroup:
                     dst.copy_(src)
             self.exp_avg.copy_(sd["exp_avg"])
             self.exp_avg_sq.copy_(sd["exp_avg_sq"])
-            if self.lp_dtype != torch.float32:
+            if self.lp_dtype != torch.float32 or self.offload:
                 self.master.copy_(sd["master"])
             return True
         return False
 
     def refresh_master_from_lp(self):
+        if self.offload:
+            self.master.copy_(self.lp_shard_view().float())
+            return
         if self.lp_dtype != torch.float32:
             self.master.copy_(self.lp_shard_view().float())
         elif self.partition_params:
@@ -376,6 +389,9 @@ class FlatAdam:
                     g.flat_lp[g.shard_start:g.shard_start + g.shard_size].copy_(g.master)
             return
         for g in self.groups:
+            if g.offload:
+                self._offloaded_step(g, lr, b1, b2, eps, grad_scale, skip)
+                continue
             gs = g.grad_shard()
             lp_shard = g.lp_shard_view() if g.lp_dtype != torch.float32 else None
             for i, (lo, hi, wd, _rep, _skip, lrm) in enumerate(g.segments):
@@ -390,6 +406,26 @@ class FlatAdam:
                                       lp_shard[lo:hi] if lp_shard is not None else None,
                                       lr=lr * lrm, beta1=b1, beta2=b2, eps=eps, weight_decay=wd, step=self.step_count,
                                       adam_w_mode=self.adam_w_mode, grad_scale=grad_scale, skip=skip)
+
+    def _offloaded_step(self, g, lr, b1, b2, eps, grad_scale, skip):
+        """Optimizer-state offload: gradient shard to the host, AdamW there, new 16-bit weights back to the device."""
+        g.host_grad.copy_(g.grad_shard(), non_blocking=True)
+        if g.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        if skip is not None and int(skip[0]) != 0:
+            return
+        scale = float(grad_scale[0]) if grad_scale is not None else 1.0
+        for (lo, hi, wd, _rep, _skip, lrm) in g.segments:
+            if g.offload == "native":
+                optim_ops.cpu_adamw_step_(g.master[lo:hi], g.exp_avg[lo:hi], g.exp_avg_sq[lo:hi], g.host_grad[lo:hi],
+                                          g.host_lp[lo:hi], lr=lr * lrm, beta1=b1, beta2=b2, eps=eps, weight_decay=wd,
+                                          step=self.step_count, adam_w_mode=self.adam_w_mode, grad_scale=scale)
+            else:                       # "torch": the same update with PyTorch's CPU operators
+                optim_ops.adamw_step_(g.master[lo:hi], g.exp_avg[lo:hi], g.exp_avg_sq[lo:hi], g.host_grad[lo:hi],
+                                      g.host_lp[lo:hi], lr=lr * lrm, beta1=b1, beta2=b2, eps=eps, weight_decay=wd,
+                                      step=self.step_count, adam_w_mode=self.adam_w_mode,
+                                      grad_scale=torch.tensor([scale]), skip=None)
+        g.lp_shard_view().copy_(g.host_lp, non_blocking=True)
 
     def zero_grad(self, set_to_none=True):
         for g in self.groups:
@@ -444,6 +480,7 @@ class Engine(torch.nn.Module):
         grad_dtype = torch.float32 if (a.fp32_grad_accum or a.precision == "fp32") else a.params_dtype
         # 8-bit Adam moments when the optimizer configuration asks for them (and the fused Adam path is the optimizer)
         state_bits = int((optimizer_cfg or {}).get("state_bits", 32)) if not generic_optimizer else 32
+        offload = (optimizer_cfg or {}).get("offload") if not generic_optimizer else None      # None | "native" | "torch"
         dense, expert = [], []
         for pg in param_groups:
             wd = pg.get("weight_decay", a.weight_decay)
@@ -460,6 +497,7 @@ class Engine(torch.nn.Module):
                 out.setdefault(e[0].dtype, []).append(e)
             return [out[k] for k in sorted(out, key=lambda d: (d != a.params_dtype, str(d)))]
 
+        self._offload = offload
         self._z3_units = []
         if self.zero_stage >= 3 and mpu.get_data_parallel_world_size() > 1:
             # stage 3: one flat space per layer of the stack, so that a layer's parameters can be gathered for
@@ -468,16 +506,18 @@ class Engine(torch.nn.Module):
         for ents in by_dtype(dense):
             gd = torch.float32 if ents[0][0].dtype == torch.float32 else grad_dtype
             self.groups.append(FlatGroup(ents, mpu.get_data_parallel_group(), mpu.get_data_parallel_world_size(),
-                                         mpu.get_data_parallel_rank(), self.zero_stage, gd, state_bits))
+                                         mpu.get_data_parallel_rank(), self.zero_stage, gd, state_bits, offload=offload))
         for ents in by_dtype(expert):
             ep = mpu.get_expert_parallel_world_size()
             gd = torch.float32 if ents[0][0].dtype == torch.float32 else grad_dtype
             self.groups.append(FlatGroup(ents, mpu.get_expert_data_parallel_group(),
                                          mpu.get_data_parallel_world_size() // ep,
-                                         mpu.get_data_parallel_rank() // ep, self.zero_stage, gd, state_bits))
+                                         mpu.get_data_parallel_rank() // ep, self.zero_stage, gd, state_bits,
+                                         offload=offload))
         self.optimizer = None
         if optimizer_cfg is not None and self.groups:
-            self.optimizer = FlatAdam(self.groups, **optimizer_cfg, **(generic_optimizer or {}))
+            self.optimizer = FlatAdam(self.groups, **{k: v for k, v in optimizer_cfg.items() if k != "offload"},
+                                      **(generic_optimizer or {}))
             self.optimizer.cur_scale = self.loss_scaler.cur_scale
         self.lr_scheduler = lr_scheduler
         dev = self.groups[0].device if self.groups else torch.device("cpu")
@@ -538,7 +578,8 @@ class Engine(torch.nn.Module):
             for ents in by_dtype([(p, wd_of[id(p)]) for p in mine]):
                 gd = torch.float32 if ents[0][0].dtype == torch.float32 else grad_dtype
                 g = FlatGroup(ents, mpu.get_data_parallel_group(), mpu.get_data_parallel_world_size(),
-                              mpu.get_data_parallel_rank(), self.zero_stage, gd, state_bits, partition_params=True)
+                              mpu.get_data_parallel_rank(), self.zero_stage, gd, state_bits, partition_params=True,
+                              offload=self._offload)
                 self.groups.append(g)
                 groups.append(g)
                 for p in g.params:

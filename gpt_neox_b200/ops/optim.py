@@ -156,3 +156,47 @@ def adamw8bit_step_(p32, m8, v8, scale_m, scale_v, g, p_lp, *, lr, beta1, beta2,
     m8.copy_(a), v8.copy_(b), scale_m.copy_(c), scale_v.copy_(d)
     if p_lp is not None:
         p_lp.copy_(p32)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Host AdamW for optimizer-state offload (csrc/cpu_adam.cpp -> lib/libneox_host.so)
+# ---------------------------------------------------------------------------------------------------------------
+_HOST_LIB = [None]
+
+
+def _host_lib():
+    if _HOST_LIB[0] is None:
+        import ctypes as C
+        from pathlib import Path
+        path = Path(__file__).resolve().parent.parent / "lib" / "libneox_host.so"
+        if not path.exists():
+            from ..build import build_host_ops
+            build_host_ops()
+        L = C.CDLL(str(path))
+        F, I, P = C.c_float, C.c_int, C.c_void_p
+        L.nx_cpu_adamw.argtypes = [P, P, P, P, I, P, I, C.c_longlong, F, F, F, F, F, F, F, I, F, I]
+        L.nx_cpu_adamw.restype = I
+        _HOST_LIB[0] = L
+    return _HOST_LIB[0]
+
+
+_KIND = {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}
+
+
+def cpu_adamw_step_(p32, m, v, g, p_lp, *, lr, beta1, beta2, eps, weight_decay, step, adam_w_mode=True,
+                    grad_scale: float = 1.0, threads: int = 0):
+    """AdamW on host tensors with the native multi-threaded kernel: ``p32`` / ``m`` / ``v`` fp32, ``g`` bf16 / fp16 /
+    fp32, ``p_lp`` (optional) receives the new weights as bf16 / fp16.  All contiguous CPU tensors, updated in place."""
+    import ctypes as C
+    for t in (p32, m, v, g) + ((p_lp,) if p_lp is not None else ()):
+        assert t.device.type == "cpu" and t.is_contiguous()
+    assert p32.dtype == m.dtype == v.dtype == torch.float32 and g.dtype in _KIND and g.numel() == p32.numel()
+    lp16 = p_lp is not None and p_lp.dtype in (torch.bfloat16, torch.float16)
+    bc1, bc2 = 1.0 - beta1 ** step, 1.0 - beta2 ** step
+    _host_lib().nx_cpu_adamw(C.c_void_p(p32.data_ptr()), C.c_void_p(m.data_ptr()), C.c_void_p(v.data_ptr()),
+                             C.c_void_p(g.data_ptr()), _KIND[g.dtype], C.c_void_p(p_lp.data_ptr()) if lp16 else None,
+                             _KIND[p_lp.dtype] if lp16 else 0, p32.numel(), float(lr), float(beta1), float(beta2),
+                             float(eps), float(weight_decay), float(bc1), float(bc2), int(adam_w_mode),
+                             float(grad_scale), int(threads))
+    if p_lp is not None and not lp16:
+        p_lp.copy_(p32)

@@ -421,6 +421,15 @@ def get_optimizer(model, neox_args, dummy=False):
     generic = None
     if ot in ("adam", "cpu_adam", "cpu_torch_adam"):
         cfg["adam_w_mode"] = True
+        # optimizer-state offload: "cpu_adam" (the reference's DeepSpeedCPUAdam, megatron/training.py:1002-1012) runs
+        # this build's native host AdamW, "cpu_torch_adam" PyTorch's CPU operators; ZeRO's cpu_offload /
+        # offload_optimizer switch selects the native one for plain "adam" too
+        zo = neox_args.zero_optimization or {}
+        wants = bool(zo.get("cpu_offload")) or (zo.get("offload_optimizer") or {}).get("device") == "cpu"
+        if ot == "cpu_torch_adam":
+            cfg["offload"] = "torch"
+        elif ot == "cpu_adam" or wants:
+            cfg["offload"] = "native"
     elif ot == "onebitadam":
         # the reference lets DeepSpeed build this one (megatron/training.py:1014-1017); here it is an in-tree
         # optimizer on the engine's generic path (optimizers.py OnebitAdam)

@@ -198,3 +198,37 @@ def test_onebit_adam_trains_with_compressed_momentum_after_the_warmup():
     assert c0 == c1
     assert min(l0[6:]) < l0[5] and l0[-1] < l0[0]
     assert all(x == x for x in l0)
+
+
+@pytest.mark.parametrize("over", [dict(optimizer={"type": "cpu_adam", "params": {"lr": 6e-4, "betas": [0.9, 0.95], "eps": 1e-8}}),
+                                  dict(optimizer={"type": "cpu_torch_adam", "params": {"lr": 6e-4, "betas": [0.9, 0.95], "eps": 1e-8}}),
+                                  dict(zero_optimization={"stage": 3, "offload_optimizer": {"device": "cpu"}})],
+                         ids=["cpu_adam", "cpu_torch_adam", "zero3_offload_optimizer"])
+def test_optimizer_state_offload_matches_the_device_optimizer(over):
+    """Master weights and Adam moments held on the host (native multi-threaded AdamW, or PyTorch's CPU operators for
+    ``cpu_torch_adam``), two data-parallel ranks: the loss curve is that of the in-place optimizer."""
+    from common import run_distributed, tiny_config
+    cfg = tiny_config(use_cpu_initialization=True)
+    ref = run_distributed(_losses_with, 2, cfg, 6)[0]
+    got = run_distributed(_losses_with, 2, dict(cfg, **over), 6)[0]
+    assert got[0] == pytest.approx(ref[0], rel=2e-5)
+    assert got[1] == pytest.approx(ref[1], rel=1e-4)
+
+
+def test_native_host_adamw_matches_the_torch_statement_for_every_dtype_pair():
+    from gpt_neox_b200.ops.optim import adamw_step_, cpu_adamw_step_
+    torch.manual_seed(0)
+    for gd, lpd in ((torch.float32, torch.bfloat16), (torch.bfloat16, torch.bfloat16), (torch.float16, torch.float16),
+                    (torch.float32, torch.float32)):
+        n = 70001
+        p, m, v = torch.randn(n), torch.zeros(n), torch.zeros(n)
+        lp = torch.empty(n, dtype=lpd)
+        p2, m2, v2, lp2 = p.clone(), m.clone(), v.clone(), lp.clone()
+        for step in range(1, 4):
+            g = torch.randn(n).to(gd)
+            kw = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+            cpu_adamw_step_(p, m, v, g, lp, grad_scale=0.5, **kw)
+            adamw_step_(p2, m2, v2, g, lp2, grad_scale=torch.tensor([0.5]), **kw)
+        torch.testing.assert_close(p, p2, rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(v, v2, rtol=1e-5, atol=1e-7)
+        assert (lp.float() - lp2.float()).abs().max() <= 2.0 ** -7 * lp2.float().abs().max()
