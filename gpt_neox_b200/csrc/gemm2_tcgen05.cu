@@ -16,6 +16,8 @@
 // accumulate, fp32 output.  No loads with cluster multicast are used anywhere.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "common.h"
 #include "ptx.cuh"
 
@@ -58,6 +60,8 @@ struct Params {
   // ---- fused tensor-parallel collective (same protocol as csrc/gemm_tcgen05.cu, 256-row tiles)
   int comm, tp_rank, ws;
   int tiles_m_chunk;            // row tiles per rank chunk: (M / ws) / 256
+  int rs_lag;                   // reduce-scatter tile order: 0 = peers' chunks first, own chunk last; > 0 = interleaved (below)
+  int num_slots;                // length of the tile sequence the CTA pairs walk (== tiles unless interleaved)
   uint32_t epoch;
   h16* rs_stage[8];   // on rank q: staging [src rank][M / ws, N]
   uint32_t* rs_flags[8];        // on rank q: flags[tile in chunk][src rank][cta of pair][warp]
@@ -141,18 +145,42 @@ __device__ __forceinline__ void tile_coords2(int tile, int tiles_m, int tiles_n,
 
 // Tile order under a fused collective: whole rank chunks of rows at a time (reduce-scatter: peers' chunks
 // first, own last; all-gather: own chunk first, then the peers' as their shards arrive).
-__device__ __forceinline__ void tile_coords2_p(int tile, const Params& p, int& tm, int& tn, int& chunk) {
+// Interleaved reduce-scatter order (rs_lag > 0): the sequence is made of groups of ws slots; group q holds tile q
+// of every peer's chunk and, in its last slot, tile q - rs_lag of the own chunk.  Every rank walks the same
+// order, so the partial sums an own tile needs were produced by the peers about rs_lag groups (at least one
+// whole wave of CTA pairs) earlier, and the partial tiles cross NVLink evenly over the whole kernel instead of
+// all within its first (ws - 1) / ws.  Slots without a tile (the first rs_lag own slots, the last rs_lag peer
+// groups) return false and are skipped by every role alike.
+__device__ __forceinline__ bool tile_coords2_p(int tile, const Params& p, int& tm, int& tn, int& chunk) {
   if (p.comm == COMM_NONE) {
     tile_coords2(tile, p.tiles_m, p.tiles_n, tm, tn);
     chunk = 0;
-    return;
+    return true;
   }
   const int per_chunk = p.tiles_m_chunk * p.tiles_n;
+  if (p.rs_lag > 0) {
+    const int q = tile / p.ws, s = tile - q * p.ws;
+    int idx;
+    if (s < p.ws - 1) {
+      if (q >= per_chunk) return false;
+      chunk = (p.tp_rank + 1 + s) % p.ws;
+      idx = q;
+    } else {
+      if (q < p.rs_lag) return false;
+      chunk = p.tp_rank;
+      idx = q - p.rs_lag;
+    }
+    int tl;
+    tile_coords2(idx, p.tiles_m_chunk, p.tiles_n, tl, tn);
+    tm = chunk * p.tiles_m_chunk + tl;
+    return true;
+  }
   const int order = tile / per_chunk;
   chunk = p.comm != COMM_AG ? (p.tp_rank + 1 + order) % p.ws : (p.tp_rank + order) % p.ws;
   int tl;
   tile_coords2(tile - order * per_chunk, p.tiles_m_chunk, p.tiles_n, tl, tn);
   tm = chunk * p.tiles_m_chunk + tl;
+  return true;
 }
 
 template <bool A_MN, bool B_MN>
@@ -205,7 +233,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = p.num_slots;
   const int num_kb = (p.K + BK - 1) / BK;
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
   bool aborted = false;
@@ -218,7 +246,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       int ag_ready_chunk = -1;
       for (int tile = pair; tile < num_tiles && !aborted; tile += pairs) {
         int tm, tn, chunk;
-        tile_coords2_p(tile, p, tm, tn, chunk);
+        if (!tile_coords2_p(tile, p, tm, tn, chunk)) continue;
         int m0 = tm * (2 * BM) + rank * BM;
         const int n0 = tn * BN + rank * BNH;
         const CUtensorMap* mapA = &tmA;
@@ -276,6 +304,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       for (int tile = pair; tile < num_tiles && !aborted; tile += pairs) {
+        {
+          int tm_, tn_, chunk_;
+          if (!tile_coords2_p(tile, p, tm_, tn_, chunk_)) continue;
+        }
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1, p.err, 12)) {
           aborted = true;
           break;
@@ -320,7 +352,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     const long long chunk_rows = static_cast<long long>(p.tiles_m_chunk) * (2 * BM);
     for (int tile = pair; tile < num_tiles; tile += pairs) {
       int tm, tn, chunk;
-      tile_coords2_p(tile, p, tm, tn, chunk);
+      if (!tile_coords2_p(tile, p, tm, tn, chunk)) continue;
       const int m0 = tm * (2 * BM) + rank * BM, n0 = tn * BN;
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, p.err, 14)) {
         aborted = true;
@@ -679,6 +711,15 @@ struct Comm2Args {
   const unsigned long long* ar_count_ptrs = nullptr;   // and delivery counters
 };
 
+// NEOX_RS_ORDER=chunks selects the older order (all peers' chunks first); default: interleaved.
+static bool rs_interleave() {
+  static const bool on = [] {
+    const char* e = getenv("NEOX_RS_ORDER");
+    return !(e != nullptr && e[0] == 'c');
+  }();
+  return on;
+}
+
 static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                         long long ldc, int transA, int transB, const void* bias, const void* aux_in, void* aux_out,
                         const void* residual, long long ld_aux, int flags, float alpha, const Comm2Args& ca,
@@ -714,6 +755,8 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
   p.tiles_n = (N + BN - 1) / BN;
   p.err = device_error_word();
   p.comm = ca.mode;
+  p.num_slots = p.tiles_m * p.tiles_n;
+  p.rs_lag = 0;
   if (ca.mode != COMM_NONE) {
     NX_REQUIRE(ca.ws >= 2 && ca.ws <= 8 && ca.rank >= 0 && ca.rank < ca.ws, "gemm2_comm: bad rank/world %d/%d", ca.rank, ca.ws);
     NX_REQUIRE(!transA && M % (ca.ws * 2 * BM) == 0, "gemm2_comm: row-major A and M (%d) %% (ws * 256) == 0 required", M);
@@ -721,6 +764,13 @@ static int gemm2_common(const void* A, const void* B, void* C, int M, int N, int
     NX_REQUIRE(ca.data_ptrs != nullptr && ca.flag_ptrs != nullptr, "gemm2_comm: null peer tables");
     p.tp_rank = ca.rank; p.ws = ca.ws; p.epoch = ca.epoch;
     p.tiles_m_chunk = (M / ca.ws) / (2 * BM);
+    if ((ca.mode == COMM_RS || ca.mode == COMM_AR) && rs_interleave()) {
+      // own tiles trail the peers' by a little more than one wave of CTA pairs
+      const int tiles = p.tiles_m * p.tiles_n;
+      const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+      p.rs_lag = (pairs + ca.ws - 1) / ca.ws + 4;
+      p.num_slots = ca.ws * (p.tiles_m_chunk * p.tiles_n + p.rs_lag);
+    }
     for (int i = 0; i < ca.ws; ++i) {
       if (ca.mode == COMM_RS || ca.mode == COMM_AR) {
         p.rs_stage[i] = reinterpret_cast<h16*>(ca.data_ptrs[i]);

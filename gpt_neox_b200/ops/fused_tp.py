@@ -17,6 +17,7 @@ from __future__ import annotations
 import torch
 
 from ..comm import collectives, symm
+from . import _lib
 from .elementwise import colsum
 from .gemm import wgrad
 
