@@ -38,6 +38,11 @@ struct AttnBwdParams {
   // and the P^T that feeds dV is the dropped one
   uint32_t drop_thr, seed_lo, seed_hi;
   float drop_rp;
+  // block-sparse layout tables of the forward (null = dense): blk_rows[q * blk_nkt + kt] bit j = row q attends to
+  // key sub-block j of key tile kt; blk_any[qt * blk_nkt + kt] != 0 = tile (qt, kt) has any live block
+  const uint8_t* blk_rows;
+  const uint8_t* blk_any;
+  int blk_shift, blk_nkt;
 };
 
 // delta = rowsum(O * dO); one warp per (b, h, q) row.
@@ -172,6 +177,9 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
   if (p.window >= 0) kv_begin = max(0, q0 + off - p.window);
   const int jb = kv_begin / AB;
   const int nblk = max((kv_end + AB - 1) / AB - jb, 0);
+  // block-sparse layouts: key tiles without a live block for this query tile are skipped by every role; ring
+  // stages and barrier phases count the live tiles
+  auto tile_live = [&](int kt) { return p.blk_any == nullptr || p.blk_any[static_cast<long long>(qt) * p.blk_nkt + kt] != 0; };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUSED; ++i) {
@@ -196,10 +204,12 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       mbar_expect_tx(bar(QDO_FULL, 0), 2 * L::TILE);
       load_tile<DP>(tile(0), &tmQ, bar(QDO_FULL, 0), q0, head, batch);
       load_tile<DP>(tile(1), &tmDO, bar(QDO_FULL, 0), q0, head, batch);
-      for (int i = 0; i < nblk; ++i) {
+      for (int t = 0, n = 0; t < nblk; ++t) {
+        if (!tile_live(jb + t)) continue;
+        const int i = n++;
         const int st = i & 1;
         const uint32_t ph = (i >> 1) & 1;
-        const int k0 = (jb + i) * AB;
+        const int k0 = (jb + t) * AB;
         if (!mbar_wait(bar(K_EMPTY, st), ph ^ 1, p.err, 31)) { aborted = true; break; }
         mbar_expect_tx(bar(K_FULL, st), L::TILE);
         load_tile<DP>(tile(2 + st), &tmK, bar(K_FULL, st), k0, kv_head, batch);
@@ -220,7 +230,10 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
         return true;
       };
       if (!mbar_wait(bar(QDO_FULL, 0), 0, p.err, 34)) aborted = true;
-      for (int i = 0; i < nblk && !aborted; ++i) {
+      int n = 0;
+      for (int t = 0; t < nblk && !aborted; ++t) {
+        if (!tile_live(jb + t)) continue;
+        const int i = n++;
         const int st = i & 1;
         const uint32_t ph = (i >> 1) & 1;
         if (!mbar_wait(bar(K_FULL, st), ph, p.err, 35)) { aborted = true; break; }
@@ -233,7 +246,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
         umma_commit(bar(V_EMPTY, st));
         if (i > 0 && !issue_dq(i - 1)) { aborted = true; break; }
       }
-      if (!aborted && !issue_dq(nblk - 1)) aborted = true;
+      if (!aborted && n > 0 && !issue_dq(n - 1)) aborted = true;
     }
   } else {
     const int quad = warp & 3;
@@ -246,14 +259,22 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
     const float lse2 = p.lse[stat_idx];     // +inf for rows past Sq -> P = 0
     const float delta = p.delta[stat_idx];
     const float slope2 = p.alibi != nullptr ? p.alibi[head] * LOG2E : 0.f;
-    for (int i = 0; i < nblk; ++i) {
+    int nlive = 0;
+    for (int t = 0; t < nblk; ++t) {
+      if (!tile_live(jb + t)) continue;
+      const int i = nlive++;
       const int st = i & 1;
-      const int k0 = (jb + i) * AB;
+      const int k0 = (jb + t) * AB;
+      uint32_t bits = 0xffffffffu;
+      if (p.blk_rows != nullptr)
+        bits = row_ok ? p.blk_rows[static_cast<long long>(qi) * p.blk_nkt + (jb + t)] : 0u;
+      const uint32_t full_bits = (1u << (AB >> p.blk_shift)) - 1u;
+      const bool blk_partial = p.blk_rows != nullptr && !__all_sync(0xffffffffu, (bits & full_bits) == full_bits);
       if (!mbar_wait(bar(SDP_FULL, 0), i & 1, p.err, 38)) { aborted = true; break; }
       if (i >= 2 && !mbar_wait(bar(DQ_DONE, st), ((i - 2) >> 1) & 1, p.err, 39)) { aborted = true; break; }
       tc_fence_after_sync();
       const bool need_mask = (k0 + AB > p.Sk) || (p.causal && k0 + AB - 1 > q0 + quad * 32 + off) ||
-                             (p.window >= 0 && k0 < q0 + quad * 32 + 31 + off - p.window);
+                             (p.window >= 0 && k0 < q0 + quad * 32 + 31 + off - p.window) || blk_partial;
       const int rel0 = k0 - qpos;
       int hi = p.Sk - k0 - 1;
       if (p.causal) hi = min(hi, -rel0);
@@ -297,7 +318,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
               float x = fmaf(__uint_as_float(sv[j + e]), p.scale_log2,
                              fmaf(slope2, static_cast<float>(idx), bias0));
               float pr = exp2f(x);
-              if (idx < lo || idx > hi) pr = 0.f;
+              if (idx < lo || idx > hi || !((bits >> (idx >> p.blk_shift)) & 1u)) pr = 0.f;
               ds[e] = pr * (__uint_as_float(dv[j + e]) - delta);
             }
             pk[j >> 1] = pack_h16x2(ds[0], ds[1]);
@@ -313,8 +334,8 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
         mbar_arrive(bar(DS_FULL, st));
       }
     }
-    if (!aborted && nblk > 0) {
-      if (!mbar_wait(bar(DQ_DONE, (nblk - 1) & 1), ((nblk - 1) >> 1) & 1, p.err, 40)) aborted = true;
+    if (!aborted && nlive > 0) {
+      if (!mbar_wait(bar(DQ_DONE, (nlive - 1) & 1), ((nlive - 1) >> 1) & 1, p.err, 40)) aborted = true;
       tc_fence_after_sync();
     }
     if (!aborted) {
@@ -322,7 +343,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 #pragma unroll 1
       for (int c = 0; c < DP / 32; ++c) {
         uint32_t ov[32];
-        if (nblk > 0) {  // warp-uniform: every lane takes part in the collective TMEM load
+        if (nlive > 0) {  // warp-uniform: every lane takes part in the collective TMEM load
           tmem_ld_32x32b_x32(T_DQ + c * 32 + lane_off, ov);
           tmem_ld_wait();
         } else {
@@ -392,6 +413,10 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
   const int ib = q_begin / AB;
   const int nq = max((q_end + AB - 1) / AB - ib, 0);
   const int nsteps = nq * group;
+  // block-sparse layouts: query tiles without a live block for this key tile are skipped by every role
+  auto step_live = [&](int t) {
+    return p.blk_any == nullptr || p.blk_any[static_cast<long long>(ib + t % nq) * p.blk_nkt + kt] != 0;
+  };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUSED; ++i) mbar_init(bar0 + 8u * i, i == PT_FULL ? 4 : 1);
@@ -413,9 +438,11 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       mbar_expect_tx(bar(KV_FULL, 0), 2 * L::TILE);
       load_tile<DP>(tile(0), &tmK, bar(KV_FULL, 0), k0, kv_head, batch);
       load_tile<DP>(tile(1), &tmV, bar(KV_FULL, 0), k0, kv_head, batch);
-      for (int t = 0; t < nsteps; ++t) {
-        const int st = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
+      for (int t = 0, n = 0; t < nsteps; ++t) {
+        if (!step_live(t)) continue;
+        const int st = n & 1;
+        const uint32_t ph = (n >> 1) & 1;
+        ++n;
         const int head = kv_head * group + t / nq;
         const int q0 = (ib + t % nq) * AB;
         if (!mbar_wait(bar(Q_EMPTY, st), ph ^ 1, p.err, 51)) { aborted = true; break; }
@@ -431,7 +458,10 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
   } else if (warp == 1) {
     if (elect_one() && nsteps > 0) {
       if (!mbar_wait(bar(KV_FULL, 0), 0, p.err, 52)) aborted = true;
-      for (int t = 0; t < nsteps && !aborted; ++t) {
+      int n = 0;
+      for (int tt = 0; tt < nsteps && !aborted; ++tt) {
+        if (!step_live(tt)) continue;
+        const int t = n++;          // live steps: ring stages, barrier phases and the accumulate flags count these
         const int st = t & 1;
         if (!mbar_wait(bar(Q_FULL, st), (t >> 1) & 1, p.err, 53)) { aborted = true; break; }
         tc_fence_after_sync();
@@ -444,7 +474,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
         mma_ts<DP>(T_DK, T_DPT, tile(2 + st), t != 0);  // dK += dS^T Q
         umma_commit(bar(Q_EMPTY, st));
       }
-      if (!aborted) umma_commit(bar(ACC_DONE, 0));
+      if (!aborted && n > 0) umma_commit(bar(ACC_DONE, 0));
     }
   } else {
     const int quad = warp & 3;
@@ -452,9 +482,12 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const int kcol = k0 + r;
     const bool key_ok = kcol < p.Sk;
-    for (int t = 0; t < nsteps; ++t) {
-      const int head = kv_head * group + t / nq;
-      const int q0 = (ib + t % nq) * AB;
+    int nlive = 0;
+    for (int tt = 0; tt < nsteps; ++tt) {
+      if (!step_live(tt)) continue;
+      const int t = nlive++;
+      const int head = kv_head * group + tt / nq;
+      const int q0 = (ib + tt % nq) * AB;
       const float slope2 = p.alibi != nullptr ? p.alibi[head] * LOG2E : 0.f;
       const int st = t & 1;
       // lse / delta of this query block were bulk-copied next to the Q / dO tiles
@@ -468,8 +501,9 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       int lo = p.causal ? rel0 : -(1 << 30);
       int hi = p.window >= 0 ? rel0 + p.window : (1 << 30);
       if (!key_ok) hi = -(1 << 30);
-      const bool need_mask = __any_sync(0xffffffffu, lo > 0 || hi < AB - 1);
+      const bool need_mask = __any_sync(0xffffffffu, lo > 0 || hi < AB - 1) || p.blk_rows != nullptr;
       const float bias0 = slope2 * static_cast<float>(rel0);
+      const uint32_t kbit = 1u << (r >> p.blk_shift);      // this key row's sub-block within the key tile
       const bool plain = !need_mask && p.alibi == nullptr;   // warp-uniform: no per-element compares in the hot path
 #pragma unroll 1
       for (int c = 0; c < AB / 32; ++c) {
@@ -522,6 +556,10 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
               if (p.alibi != nullptr) x += fmaf(-slope2, static_cast<float>(idx), bias0);
               pr[e] = exp2f(x);
               if (idx < lo || idx > hi) pr[e] = 0.f;
+              if (p.blk_rows != nullptr) {   // the layout byte of query row q0 + idx (the same for the whole warp)
+                const int qq = min(q0 + idx, p.Sq - 1);
+                if (!(p.blk_rows[static_cast<long long>(qq) * p.blk_nkt + kt] & kbit)) pr[e] = 0.f;
+              }
               const float dpe = DROP ? __uint_as_float(dv[j + e]) * keepf[j + e] : __uint_as_float(dv[j + e]);
               ds[e] = pr[e] * (dpe - dq_[e]);
               if (DROP) pr[e] *= keepf[j + e];
@@ -540,7 +578,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(PT_FULL, 0));
     }
-    if (!aborted && nsteps > 0) {
+    if (!aborted && nlive > 0) {
       if (!mbar_wait(bar(ACC_DONE, 0), 0, p.err, 56)) aborted = true;
       tc_fence_after_sync();
     }
@@ -555,7 +593,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 #pragma unroll 1
         for (int c = 0; c < DP / 32; ++c) {
           uint32_t ov[32];
-          if (nsteps > 0) {
+          if (nlive > 0) {
             tmem_ld_32x32b_x32(T + c * 32 + lane_off, ov);
             tmem_ld_wait();
           } else {
@@ -624,7 +662,7 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 // Views as in nx_flash_attn_fwd (element strides batch, head, seq).  delta: fp32 scratch [B,H,Sq]
 // provided by the caller.  dq/dk/dv: 16-bit strided outputs, fully overwritten.  dropout_p / seed: the
-// values the forward was given.
+// values the forward was given; blk_rows / blk_any / blk_size: the forward's block-sparse layout tables.
 NX_API int NX_SYM(nx_flash_attn_bwd)(const void* q, const void* k, const void* v, const void* o, const void* dO,
                              const void* lse, void* delta, void* dq, void* dk, void* dv,
                              const void* alibi, int B, int H, int Hk, int Sq, int Sk, int D,
@@ -635,9 +673,13 @@ NX_API int NX_SYM(nx_flash_attn_bwd)(const void* q, const void* k, const void* v
                              long long dq_sh, long long dq_ss, long long dk_sb, long long dk_sh,
                              long long dk_ss, long long dv_sb, long long dv_sh, long long dv_ss,
                              float scale, int causal, int window, float dropout_p,
-                             unsigned long long seed, void* stream_) {
+                             unsigned long long seed, const void* blk_rows, const void* blk_any, int blk_size,
+                             void* stream_) {
   using namespace nx;
   if (B == 0 || H == 0 || Sq == 0 || Sk == 0) return NX_OK;
+  NX_REQUIRE((blk_rows == nullptr) == (blk_any == nullptr), "flash_attn_bwd: both block-layout tables or none");
+  NX_REQUIRE(blk_rows == nullptr || blk_size == 16 || blk_size == 32 || blk_size == 64 || blk_size == 128,
+             "flash_attn_bwd: block-sparse layouts need a block size of 16, 32, 64 or 128 (got %d)", blk_size);
   NX_REQUIRE(dropout_p >= 0.f && dropout_p < 1.f, "flash_attn_bwd: dropout probability %f outside [0, 1)", dropout_p);
   NX_REQUIRE(D % 8 == 0 && D <= 128 && D > 0, "flash_attn_bwd: head dim %d unsupported", D);
   NX_REQUIRE(Hk > 0 && H % Hk == 0, "flash_attn_bwd: H=%d not a multiple of Hk=%d", H, Hk);
@@ -694,6 +736,10 @@ NX_API int NX_SYM(nx_flash_attn_bwd)(const void* q, const void* k, const void* v
   p.drop_rp = 256.f / static_cast<float>(256u - p.drop_thr);
   p.seed_lo = static_cast<uint32_t>(seed);
   p.seed_hi = static_cast<uint32_t>(seed >> 32);
+  p.blk_rows = static_cast<const uint8_t*>(blk_rows);
+  p.blk_any = static_cast<const uint8_t*>(blk_any);
+  p.blk_nkt = (Sk + AB - 1) / AB;
+  p.blk_shift = blk_size == 16 ? 4 : blk_size == 32 ? 5 : blk_size == 64 ? 6 : 7;
   if (p.drop_thr > 0u) return D <= 64 ? launch_bwd<64, true>(tq, tk, tv, tdo, p, s) : launch_bwd<128, true>(tq, tk, tv, tdo, p, s);
   if (D <= 64) return launch_bwd<64, false>(tq, tk, tv, tdo, p, s);
   return launch_bwd<128, false>(tq, tk, tv, tdo, p, s);

@@ -44,6 +44,13 @@ struct AttnFwdParams {
   // values scaled by drop_rp = 256 / (256 - drop_thr)
   uint32_t drop_thr, seed_lo, seed_hi;
   float drop_rp;
+  // block-sparse layout (null = dense): key blocks of (1 << blk_shift) tokens, 16 <= block <= 128, one layout
+  // for all heads.  blk_rows[q * blk_nkt + kt]: bit j = query row q attends to sub-block j of key tile kt (128 keys);
+  // blk_any[qt * blk_nkt + kt] != 0: query tile qt (128 rows) has any live sub-block in key tile kt (else the tile
+  // is skipped by every role).
+  const uint8_t* blk_rows;
+  const uint8_t* blk_any;
+  int blk_shift, blk_nkt;
 };
 
 template <int DP>
@@ -80,9 +87,11 @@ __device__ __forceinline__ float row_max_plain(const uint32_t (&sv)[2][32]) {
 // Rewrites raw scores in place as base-2 logits: x = s * scale_log2 (+ slope2 * (col - qpos)),
 // -inf outside the live column range [lo, hi] of this block; returns the row maximum.
 // rel0 = (first column of the block) - (query position); col0 = first block column of this half row.
+// bits / shift: block-sparse layout of this row in this key tile (bit (idx >> shift) set = column idx is attended);
+// 0xffffffff with any shift for a dense layout.
 template <bool ALIBI>
 __device__ __forceinline__ float prep_scores(uint32_t (&sv)[2][32], float scale_log2, float slope2,
-                                             int rel0, int lo, int hi, int col0) {
+                                             int rel0, int lo, int hi, int col0, uint32_t bits, int shift) {
   float m0 = -INFINITY, m1 = -INFINITY;
   const float bias0 = ALIBI ? slope2 * static_cast<float>(rel0) : 0.f;
 #pragma unroll
@@ -92,7 +101,7 @@ __device__ __forceinline__ float prep_scores(uint32_t (&sv)[2][32], float scale_
       const int idx = col0 + c * 32 + j;
       float x = __uint_as_float(sv[c][j]) * scale_log2;
       if (ALIBI) x += fmaf(slope2, static_cast<float>(idx), bias0);
-      if (idx < lo || idx > hi) x = -INFINITY;
+      if (idx < lo || idx > hi || !((bits >> (idx >> shift)) & 1u)) x = -INFINITY;
       sv[c][j] = __float_as_uint(x);
       if (j & 1) m1 = fmaxf(m1, x); else m0 = fmaxf(m0, x);
     }
@@ -159,6 +168,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   const int jb = kv_begin / ATT_BN;
   const int je = (kv_end + ATT_BN - 1) / ATT_BN;  // exclusive
   const int nblk = max(je - jb, 0);
+  // block-sparse layouts: key tiles without a live block for this query tile are skipped by every role
+  auto tile_live = [&](int kt) { return p.blk_any == nullptr || p.blk_any[static_cast<long long>(qt) * p.blk_nkt + kt] != 0; };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 17; ++i) {
@@ -192,9 +203,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 #pragma unroll
       for (int c = 0; c < DP / 64; ++c)
         tma_load_4d(sbase + L::Q_OFF + c * (ATT_BM * 128), &tmQ, bar(Q_FULL, 0), c * 64, q0, head, batch);
-      for (int i = 0; i < nblk; ++i) {
-        const int st = i & 1;
-        const uint32_t ph = (i >> 1) & 1;
+      for (int i = 0, n = 0; i < nblk; ++i) {
+        if (!tile_live(jb + i)) continue;
+        const int st = n & 1;
+        const uint32_t ph = (n >> 1) & 1;
+        ++n;
         const int k0 = (jb + i) * ATT_BN;
         if (!mbar_wait(bar(K_EMPTY, st), ph ^ 1, p.err, 11)) { aborted = true; break; }
         mbar_expect_tx(bar(K_FULL, st), L::TILE);
@@ -233,7 +246,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         return true;
       };
       if (!mbar_wait(bar(Q_FULL, 0), 0, p.err, 15)) aborted = true;
-      for (int i = 0; i < nblk && !aborted; ++i) {
+      int n = 0;      // live key tiles so far: ring stages and barrier phases count these, not the tile index
+      for (int t = 0; t < nblk && !aborted; ++t) {
+        if (!tile_live(jb + t)) continue;
+        const int i = n++;
         const int st = i & 1;
         const uint32_t ph = (i >> 1) & 1;
         if (!mbar_wait(bar(K_FULL, st), ph, p.err, 16)) { aborted = true; break; }
@@ -250,7 +266,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         umma_commit(bar(K_EMPTY, st));
         if (i > 0 && !issue_pv(i - 1)) { aborted = true; break; }
       }
-      if (!aborted && !issue_pv(nblk - 1)) aborted = true;
+      if (!aborted && n > 0 && !issue_pv(n - 1)) aborted = true;
     }
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
@@ -280,10 +296,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     const int qpos = qi + off;
     float m_used = -INFINITY, l = 0.f;
     const float slope2 = p.alibi != nullptr ? p.alibi[head] * 1.4426950408889634f : 0.f;
-    for (int i = 0; i < nblk; ++i) {
+    int nlive = 0;
+    for (int t = 0; t < nblk; ++t) {
+      if (!tile_live(jb + t)) continue;
+      const int i = nlive++;
       const int st = i & 1;
       const uint32_t ph = (i >> 1) & 1;
-      const int k0 = (jb + i) * ATT_BN;
+      const int k0 = (jb + t) * ATT_BN;
+      // block-sparse: which 16..128-key sub-blocks of this key tile the row attends to
+      uint32_t bits = 0xffffffffu;
+      if (p.blk_rows != nullptr)
+        bits = qi < p.Sq ? p.blk_rows[static_cast<long long>(qi) * p.blk_nkt + (jb + t)] : 0u;
+      const uint32_t full_bits = (1u << (ATT_BN >> p.blk_shift)) - 1u;
+      const bool blk_partial = p.blk_rows != nullptr && !__all_sync(0xffffffffu, (bits & full_bits) == full_bits);
       if (!mbar_wait(bar(S_FULL, st), ph, p.err, 18)) { aborted = true; break; }
       tc_fence_after_sync();
       // One read of the whole score row into registers.
@@ -293,7 +318,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       tmem_ld_wait();
       // Does this block need per-element masking?  (warp-uniform decision)
       const bool need_mask = (k0 + ATT_BN > p.Sk) || (p.causal && k0 + ATT_BN - 1 > q0 + quad * 32 + off) ||
-                             (p.window >= 0 && k0 < q0 + quad * 32 + 31 + off - p.window);
+                             (p.window >= 0 && k0 < q0 + quad * 32 + 31 + off - p.window) || blk_partial;
       const bool plain = !need_mask && p.alibi == nullptr;
       float mx;
       if (plain) {
@@ -304,8 +329,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         int hi = p.Sk - k0 - 1;
         if (p.causal) hi = min(hi, -rel0);
         const int lo = p.window >= 0 ? -rel0 - p.window : -(1 << 30);
-        mx = p.alibi != nullptr ? prep_scores<true>(sv, p.scale_log2, slope2, rel0, lo, hi, col0)
-                                : prep_scores<false>(sv, p.scale_log2, slope2, rel0, lo, hi, col0);
+        mx = p.alibi != nullptr ? prep_scores<true>(sv, p.scale_log2, slope2, rel0, lo, hi, col0, bits, p.blk_shift)
+                                : prep_scores<false>(sv, p.scale_log2, slope2, rel0, lo, hi, col0, bits, p.blk_shift);
       }
       {
         // the row maximum over both column halves: both partners then take identical decisions
@@ -385,14 +410,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       }
     }
     // ---- epilogue: O / l -> global, lse
-    if (!aborted && nblk > 0) {
-      if (!mbar_wait(bar(PV_DONE, (nblk - 1) & 1), ((nblk - 1) >> 1) & 1, p.err, 21)) aborted = true;
+    const int nblk_live = nlive;      // (below, "nblk" means the key tiles that were really processed)
+    if (!aborted && nblk_live > 0) {
+      if (!mbar_wait(bar(PV_DONE, (nblk_live - 1) & 1), ((nblk_live - 1) >> 1) & 1, p.err, 21)) aborted = true;
       tc_fence_after_sync();
     }
     if (!aborted) {
       // total row sum = this half's + the partner's (same running max on both sides)
       float other = 0.f;
-      const bool ok = exchange(l, static_cast<uint32_t>(nblk + 1), other);
+      const bool ok = exchange(l, static_cast<uint32_t>(nblk_live + 1), other);
       if (!__all_sync(0xffffffffu, ok)) aborted = true;
       l += other;
     }
@@ -403,7 +429,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 #pragma unroll 1
       for (int c = half * (DP / 64); c < (half + 1) * (DP / 64); ++c) {
         uint32_t ov[32];
-        if (nblk > 0) {
+        if (nblk_live > 0) {
           tmem_ld_32x32b_x32(T_O + c * 32 + lane_off, ov);
           tmem_ld_wait();
         } else {
@@ -460,16 +486,22 @@ static bool attn_map(CUtensorMap* m, const void* base, int B, int Hh, int S, int
 // base-2 log-sum-exp of the scaled scores for rows < Sq (the caller pre-fills it with +inf).  alibi: fp32 [H] or null.
 // window < 0: no sliding window.  D % 8 == 0, D <= 128.  dropout_p > 0: dropout on the probabilities with
 // the mask of dropout_patch() under `seed` (the backward must be given the same p and seed).
+// blk_rows / blk_any (both or neither): block-sparse layout tables, uint8 [Sq, ceil(Sk / 128)] and
+// [ceil(Sq / 128), ceil(Sk / 128)] (see AttnFwdParams), blk_size the layout's block size in tokens.
 NX_API int NX_SYM(nx_flash_attn_fwd)(const void* q, const void* k, const void* v, void* o, void* lse,
                              const void* alibi, int B, int H, int Hk, int Sq, int Sk, int D,
                              long long q_sb, long long q_sh, long long q_ss, long long k_sb,
                              long long k_sh, long long k_ss, long long v_sb, long long v_sh,
                              long long v_ss, long long o_sb, long long o_sh, long long o_ss,
                              float scale, int causal, int window, float dropout_p,
-                             unsigned long long seed, void* stream_) {
+                             unsigned long long seed, const void* blk_rows, const void* blk_any, int blk_size,
+                             void* stream_) {
   using namespace nx;
   if (B == 0 || H == 0 || Sq == 0) return NX_OK;
   NX_REQUIRE(D % 8 == 0 && D <= 128 && D > 0, "flash_attn: head dim %d unsupported (need %%8, <=128)", D);
+  NX_REQUIRE((blk_rows == nullptr) == (blk_any == nullptr), "flash_attn: both block-layout tables or none");
+  NX_REQUIRE(blk_rows == nullptr || blk_size == 16 || blk_size == 32 || blk_size == 64 || blk_size == 128,
+             "flash_attn: block-sparse layouts need a block size of 16, 32, 64 or 128 (got %d)", blk_size);
   NX_REQUIRE(dropout_p >= 0.f && dropout_p < 1.f, "flash_attn: dropout probability %f outside [0, 1)", dropout_p);
   NX_REQUIRE(dropout_p == 0.f || (Sq <= 131072 && Sk <= 131072), "flash_attn: dropout needs sequences <= 131072");
   NX_REQUIRE(Hk > 0 && H % Hk == 0, "flash_attn: H=%d not a multiple of Hk=%d", H, Hk);
@@ -494,6 +526,10 @@ NX_API int NX_SYM(nx_flash_attn_fwd)(const void* q, const void* k, const void* v
   p.drop_rp = 256.f / static_cast<float>(256u - p.drop_thr);
   p.seed_lo = static_cast<uint32_t>(seed);
   p.seed_hi = static_cast<uint32_t>(seed >> 32);
+  p.blk_rows = static_cast<const uint8_t*>(blk_rows);
+  p.blk_any = static_cast<const uint8_t*>(blk_any);
+  p.blk_nkt = (Sk + ATT_BN - 1) / ATT_BN;
+  p.blk_shift = blk_size == 16 ? 4 : blk_size == 32 ? 5 : blk_size == 64 ? 6 : 7;
   const bool drop = p.drop_thr > 0u;
   dim3 grid((Sq + ATT_BM - 1) / ATT_BM, H, B);
   auto s = (cudaStream_t)stream_;

@@ -184,6 +184,9 @@ class ParallelSelfAttention(nn.Module):
         if neox_args.use_mup:
             self.norm_factor = self.hidden_size_per_attention_head
         self.coeff = coeff
+        # net softmax scale of the flash kernels: 1 / sqrt(d) (query-key layer scaling cancels out), 1 / d under muP
+        self.attn_scale = 1.0 / self.hidden_size_per_attention_head if neox_args.use_mup \
+            else 1.0 / math.sqrt(self.hidden_size_per_attention_head)
         self.rpe = rpe
         if self.pos_emb == "alibi":
             self.alibi_embed = AliBi(neox_args.num_attention_heads, ws, mpu.get_model_parallel_rank())
@@ -205,12 +208,19 @@ class ParallelSelfAttention(nn.Module):
         self.attention_type = neox_args.attention_config[layer_number]
         self.use_flash_attention = self.attention_type == "flash"
         self.sparse = self.attention_type not in ("global", "flash")
+        self.sparse_layout = None
         if self.sparse:
-            # block-sparse pattern as a token mask on the masked-softmax path (same function, dense FLOPs)
-            from .sparse_attention import token_mask
-            self.register_buffer("sparse_mask", token_mask(self.attention_type, neox_args.seq_length,
-                                                           neox_args.sparsity_config, seed=layer_number),
-                                 persistent=False)
+            # block-sparse pattern: on the GPU the flash kernels take the block layout (key tiles without a live
+            # block are skipped); the token mask serves the masked-softmax path (CPU, relative-position bias,
+            # block sizes the kernels do not take)
+            from ..ops.attention import BlockLayout
+            from .sparse_attention import block_layout, token_mask
+            cfg = neox_args.sparsity_config or {}
+            self.register_buffer("sparse_mask", token_mask(self.attention_type, neox_args.seq_length, cfg,
+                                                           seed=layer_number), persistent=False)
+            block = cfg.get("block", 16)
+            nb = (neox_args.seq_length + block - 1) // block
+            self.sparse_layout = BlockLayout(block_layout(self.attention_type, nb, cfg, seed=layer_number), block)
         self.dropout_p = neox_args.attention_dropout
         self.attention_dropout = nn.Dropout(self.dropout_p)
         self.dense = Row(neox_args=neox_args, input_size=neox_args.hidden_size,
@@ -298,6 +308,7 @@ class ParallelSelfAttention(nn.Module):
         if simple:
             ctx = fused_ops.qkv_attention(
                 mixed, num_heads=np_, num_kv_heads=kvp, head_dim=hn, rotary_dim=self.rotary_dim, cos=cos, sin=sin,
+                scale=self.attn_scale,
                 window=self.sliding_window_width if self.sliding_window_width is not None else -1,
                 alibi=self.alibi_embed.slopes if self.pos_emb == "alibi" else None, dropout_p=drop_p, seed=drop_seed)
             present = None
@@ -314,12 +325,15 @@ class ParallelSelfAttention(nn.Module):
                 k = torch.cat((layer_past[0].type_as(k), k), dim=0)
                 v = torch.cat((layer_past[1].type_as(v), v), dim=0)
             present = torch.stack((k, v)) if self.use_cache else None
-            if self.use_flash_attention and self.rpe is None:
+            sparse_kernel = (self.sparse and self.rpe is None and q.is_cuda and self.sparse_layout.kernel_ok
+                             and q.dtype in (torch.bfloat16, torch.float16) and hn % 8 == 0 and hn <= 128)
+            if (self.use_flash_attention and self.rpe is None) or sparse_kernel:
                 o = flash_attention(q.permute(1, 0, 2, 3), k.permute(1, 0, 2, 3), v.permute(1, 0, 2, 3),
-                                    causal=True,
+                                    causal=True, scale=self.attn_scale,
                                     window=self.sliding_window_width if self.sliding_window_width is not None else -1,
                                     alibi=self.alibi_embed.slopes if self.pos_emb == "alibi" else None,
-                                    dropout_p=drop_p, seed=drop_seed)
+                                    dropout_p=drop_p, seed=drop_seed,
+                                    block_layout=self.sparse_layout if sparse_kernel else None)
                 ctx = o.permute(1, 0, 2, 3).reshape(q.shape[0], q.shape[1], np_ * hn)
             else:
                 mask = attention_mask if not self.use_flash_attention else None

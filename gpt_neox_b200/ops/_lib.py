@@ -115,8 +115,8 @@ def _declare(lib):
     sig("nx_rope", [P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, I, I, P])
     sig("nx_embedding_fwd", [P, P, P, L, I, L, L, P])
     sig("nx_embedding_bwd", [P, P, P, L, I, L, L, P])
-    sig("nx_flash_attn_fwd", [P] * 6 + [I] * 6 + [L] * 12 + [F, I, I, F, U, P])
-    sig("nx_flash_attn_bwd", [P] * 11 + [I] * 6 + [L] * 24 + [F, I, I, F, U, P])
+    sig("nx_flash_attn_fwd", [P] * 6 + [I] * 6 + [L] * 12 + [F, I, I, F, U, P, P, I, P])
+    sig("nx_flash_attn_bwd", [P] * 11 + [I] * 6 + [L] * 24 + [F, I, I, F, U, P, P, I, P])
     return lib
 
 

@@ -109,7 +109,8 @@ class _QKVAttentionFn(torch.autograd.Function):
         _lib.check(_lib.lib(qkv).nx_flash_attn_fwd(
             _lib.ptr(qb), _lib.ptr(kb), _lib.ptr(vb), _lib.ptr(ob), _lib.ptr(lse), _lib.ptr(alibi),
             b, np_, kvp, s, s, hn, *_strides_bhs(qb), *_strides_bhs(kb), *_strides_bhs(vb), *_strides_bhs(ob),
-            float(scale), 1, int(window), float(dropout_p), int(seed), _lib.stream()), "nx_flash_attn_fwd")
+            float(scale), 1, int(window), float(dropout_p), int(seed), None, None, 0, _lib.stream()),
+            "nx_flash_attn_fwd")
         ctx.save_for_backward(qkv, out, lse, cos, sin, alibi)
         ctx.cfg = (np_, kvp, hn, rot, pos0, scale, window)
         ctx.dropout = (float(dropout_p), int(seed))
@@ -136,7 +137,8 @@ class _QKVAttentionFn(torch.autograd.Function):
             _lib.ptr(delta), _lib.ptr(dqb), _lib.ptr(dkb), _lib.ptr(dvb), _lib.ptr(alibi),
             b, np_, kvp, s, s, hn, *_strides_bhs(qb), *_strides_bhs(kb), *_strides_bhs(vb), *_strides_bhs(ob),
             *_strides_bhs(dob), *_strides_bhs(dqb), *_strides_bhs(dkb), *_strides_bhs(dvb),
-            float(scale), 1, int(window), ctx.dropout[0], ctx.dropout[1], _lib.stream()), "nx_flash_attn_bwd")
+            float(scale), 1, int(window), ctx.dropout[0], ctx.dropout[1], None, None, 0, _lib.stream()),
+            "nx_flash_attn_bwd")
         if rot > 0:
             _rope_launch(dq, dq, cos, sin, rot, pos0, True)
             _rope_launch(dk, dk, cos, sin, rot, pos0, True)

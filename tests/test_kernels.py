@@ -381,6 +381,56 @@ def test_flash_attention(cfg):
     assert rel(q.grad, qr.grad) < 3e-2 and rel(k.grad, kr.grad) < 3e-2 and rel(v.grad, vr.grad) < 3e-2
 
 
+@pytest.mark.parametrize("kind,cfg,block,sq,sk", [
+    ("sparse_fixed", {"num_local_blocks": 4, "num_global_blocks": 1}, 16, 640, 640),
+    ("bigbird", {"num_sliding_window_blocks": 3, "num_global_blocks": 1, "num_random_blocks": 1}, 32, 512, 512),
+    ("bslongformer", {"num_sliding_window_blocks": 3, "global_block_indices": [0]}, 64, 1024, 1024),
+    ("local", {"num_local_blocks": 2}, 128, 1024, 1024),
+    ("sparse_variable", {"local_window_blocks": [2, 4], "global_block_indices": [0]}, 16, 3, 500)])
+def test_block_sparse_flash_attention(kind, cfg, block, sq, sk):
+    """The five block-sparse layouts inside the flash kernels (key tiles without a live block are skipped, the rest
+    masked per sub-block), forward and backward, against the fp32 oracle with the same token mask; the last case is
+    cached decoding (3 new tokens against 500 keys)."""
+    from gpt_neox_b200.models.sparse_attention import block_layout
+    from gpt_neox_b200.ops.attention import BlockLayout, attention_reference, flash_attention
+    torch.manual_seed(17)
+    nb = (max(sq, sk) + block - 1) // block
+    lay = BlockLayout(block_layout(kind, nb, dict(cfg, block=block), seed=3), block)
+    rows, anyt = lay.tables(sq, sk, DEV)
+    if sq >= 512:
+        assert int((anyt == 0).sum()) > 0                     # some tiles really are skipped
+    b, h, hk, d = 2, 4, 2, 64
+    q, k, v = bf(b, sq, h, d, grad=True), bf(b, sk, hk, d, grad=True), bf(b, sk, hk, d, grad=True)
+    o = flash_attention(q, k, v, causal=True, block_layout=lay)
+    g = bf(b, sq, h, d)
+    o.backward(g)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    oref, _ = attention_reference(qr, kr, vr, causal=True, block_layout=lay)
+    oref.backward(g.float())
+    assert rel(o, oref) < 2e-2
+    assert rel(q.grad, qr.grad) < 3e-2 and rel(k.grad, kr.grad) < 3e-2 and rel(v.grad, vr.grad) < 3e-2
+
+
+def test_flash_attention_varlen_matches_per_sequence_oracle():
+    """Packed sequences of unequal length (and unequal query / key lengths: cached decoding): each attends to itself only."""
+    from gpt_neox_b200.ops.attention import attention_reference, flash_attention_varlen
+    torch.manual_seed(31)
+    lq, lk, h, hk, d = [130, 1, 257, 64], [130, 300, 257, 200], 4, 2, 64
+    cq = [0] + torch.tensor(lq).cumsum(0).tolist()
+    ck = [0] + torch.tensor(lk).cumsum(0).tolist()
+    q, k, v = bf(cq[-1], h, d, grad=True), bf(ck[-1], hk, d, grad=True), bf(ck[-1], hk, d, grad=True)
+    o = flash_attention_varlen(q, k, v, cq, torch.tensor(ck))
+    g = bf(cq[-1], h, d)
+    o.backward(g)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    refs = [attention_reference(qr[cq[i]:cq[i + 1]][None], kr[ck[i]:ck[i + 1]][None], vr[ck[i]:ck[i + 1]][None])[0][0]
+            for i in range(4)]
+    oref = torch.cat(refs, 0)
+    oref.backward(g.float())
+    assert rel(o, oref) < 2e-2
+    assert rel(q.grad, qr.grad) < 3e-2 and rel(k.grad, kr.grad) < 3e-2 and rel(v.grad, vr.grad) < 3e-2
+
+
 def test_attention_dropout_mask_statistics_and_seed_dependence():
     """The mask is a pure function of (seed, batch, head, q, k): the keep rate matches 1 - p (p in steps of 1/256),
     rows and columns are not correlated, and another seed gives another mask."""
