@@ -54,12 +54,13 @@ def _stale(target: Path, deps) -> bool:
 SINGLE_BUILD = {"common.cu", "colsum_noalloc.cu"}
 
 
-def _compile_one(src: Path, headers, force: bool, verbose: bool, half: bool = False):
-    stem = src.stem + ("_f16" if half else "")
+def _compile_one(src: Path, headers, force: bool, verbose: bool, half: bool = False, debug_bounds: bool = False):
+    stem = src.stem + ("_f16" if half else "") + ("_dbg" if debug_bounds else "")
     obj = OBJ / (stem + ".o")
     if not force and not _stale(obj, [src, *headers]):
         return obj, ""
-    cmd = [_nvcc(), *NVCC_FLAGS, *(["-DNX_HALF"] if half else []), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *NVCC_FLAGS, *(["-DNX_HALF"] if half else []), *(["-DNEOX_DEBUG_BOUNDS"] if debug_bounds else []),
+           "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
@@ -70,15 +71,17 @@ def _compile_one(src: Path, headers, force: bool, verbose: bool, half: bool = Fa
     return obj, log
 
 
-def build_cuda(force: bool = False, verbose: bool = False) -> Path:
+def build_cuda(force: bool = False, verbose: bool = False, debug_bounds: bool = False) -> Path:
+    """``debug_bounds``: a second library, ``lib/libneox_b200_dbg.so``, whose communication kernels range-check every
+    access into a symmetric workspace (``-DNEOX_DEBUG_BOUNDS``); ``NEOX_KERNEL_LIB=debug`` makes the ops load it."""
     OBJ.mkdir(parents=True, exist_ok=True)
     LIB.mkdir(parents=True, exist_ok=True)
     srcs = sorted(CSRC.glob("*.cu"))
     headers = sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")))
     jobs = [(s, False) for s in srcs] + [(s, True) for s in srcs if s.name not in SINGLE_BUILD]
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
-        objs = [o for o, _ in ex.map(lambda j: _compile_one(j[0], headers, force, verbose, j[1]), jobs)]
-    out = LIB / "libneox_b200.so"
+        objs = [o for o, _ in ex.map(lambda j: _compile_one(j[0], headers, force, verbose, j[1], debug_bounds), jobs)]
+    out = LIB / ("libneox_b200_dbg.so" if debug_bounds else "libneox_b200.so")
     if force or _stale(out, objs):
         cmd = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
                "-Xcompiler", "-fPIC", "-o", str(out), *map(str, objs), "-lcudart"]
@@ -149,3 +152,5 @@ if __name__ == "__main__":
     a, b = build_all(force, verbose)
     print("built", a)
     print("built", b)
+    if "--debug-bounds" in sys.argv:
+        print("built", build_cuda(force, verbose, debug_bounds=True))

@@ -20,6 +20,7 @@ from ..ops import _lib
 from ..ops.gemm import LAUNCHES
 
 _BACKENDS: dict = {}
+GUARD, GUARD_BYTE = 4096, 0xA5        # guard bands between the regions of a symmetric workspace
 DEFAULT_BYTES = int(os.environ.get("NEOX_SYMM_BYTES", 768 * 1024 * 1024))
 
 
@@ -70,23 +71,37 @@ class SymmBackend:
             mc = 0
         self.mc = mc
         self.epoch = 1
-        # regions: [barrier flags 64K][RS flags 1M][AG flags 16K][collective payload][gather x2][stage x2]
+        # regions: [barrier flags 64K][RS flags 1M][AG flags 16K][collective payload][gather x2][stage x2]; every
+        # data region is followed by a guard band of GUARD bytes holding a fixed pattern (check_guards)
         self.rs_flag_off = self.flag_bytes
         self.ag_flag_off = self.rs_flag_off + (1 << 20)
         data0 = self.ag_flag_off + (16 << 10)
-        unit = ((nbytes - data0) // 5) // 4096 * 4096
+        pitch = ((nbytes - data0) // 5) // 4096 * 4096
+        unit = pitch - GUARD
         self.unit = unit
         self.payload_bytes = unit
         self.payload = self.buf[self.flag_bytes:]          # collectives address their payload from here
         self.coll_off = data0
-        self.gather_off = [data0 + unit, data0 + 2 * unit]
-        self.stage_off = [data0 + 3 * unit, data0 + 4 * unit]
+        self.gather_off = [data0 + pitch, data0 + 2 * pitch]
+        self.stage_off = [data0 + 3 * pitch, data0 + 4 * pitch]
+        self.guard_offs = [data0 + i * pitch + unit for i in range(5)]
+        for o in self.guard_offs:
+            self.buf[o:o + GUARD].fill_(GUARD_BYTE)
+        _lib.register_workspace(int(self.hdl.buffer_ptrs[self.me]), nbytes)
+        jitter = int(os.environ.get("NEOX_COMM_JITTER_NS", "0"))
+        if jitter > 0:
+            _lib.set_comm_jitter_ns(jitter)
         self.ag_calls = 0
         self.rs_calls = 0
         self.ar_calls = 0
         self.ar_count_off = self.ag_flag_off + (8 << 10)      # upper half of the all-gather flag area
         self.ar_target = 0
         dist.barrier(group)
+
+    def check_guards(self) -> bool:
+        """True if no kernel wrote past the end of a data region (synchronises)."""
+        torch.cuda.synchronize()
+        return all(bool((self.buf[o:o + GUARD] == GUARD_BYTE).all()) for o in self.guard_offs)
 
     def _table(self, off):
         return (C.c_ulonglong * 8)(*([int(p) + off for p in self.hdl.buffer_ptrs] + [0] * (8 - self.ws)))
@@ -283,7 +298,7 @@ class ZeroWorkspace:
         PP = C.POINTER(C.c_ulonglong)
         self.group, self.ws, self.me = group, dist.get_world_size(group), dist.get_rank(group)
         self.flag_bytes = L.nx_comm_flag_bytes()
-        al = lambda n: (n + 4095) // 4096 * 4096
+        al = lambda n: (n + 4095) // 4096 * 4096 + GUARD       # each buffer is followed by a guard band
         self.grad_off = self.flag_bytes
         self.param_off = self.grad_off + al(grad_bytes)
         total = self.param_off + al(param_bytes)
@@ -294,9 +309,17 @@ class ZeroWorkspace:
         self.hdl = symm_mem.rendezvous(self.buf, group)
         self.ptrs = (C.c_ulonglong * 8)(*([int(p) for p in self.hdl.buffer_ptrs] + [0] * (8 - self.ws)))
         self.grad_bytes, self.param_bytes = grad_bytes, param_bytes
+        self.guard_offs = [self.param_off - GUARD, total - GUARD]
+        for o in self.guard_offs:
+            self.buf[o:o + GUARD].fill_(GUARD_BYTE)
+        _lib.register_workspace(int(self.hdl.buffer_ptrs[self.me]), total)
         self.epoch = 1
         self.grid = min(2 * torch.cuda.get_device_properties(dev).multi_processor_count, 1024)
         dist.barrier(group)
+
+    def check_guards(self) -> bool:
+        torch.cuda.synchronize()
+        return all(bool((self.buf[o:o + GUARD] == GUARD_BYTE).all()) for o in self.guard_offs)
 
     def grad_buffer(self, dtype):
         return self.buf[self.grad_off:self.grad_off + self.grad_bytes].view(dtype)

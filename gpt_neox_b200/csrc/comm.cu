@@ -21,6 +21,7 @@ constexpr int COMM_FLAG_BYTES = 64 * 1024;
 
 struct PeerTable {
   void* ptr[COMM_MAX_RANKS];  // base of every rank's symmetric workspace, as mapped on this rank
+  long long limit;            // size of one workspace in bytes if the host registered it (debug range checks), else 0
 };
 
 // Block-level barrier across ranks.  phase distinguishes the barriers of one launch.
@@ -32,6 +33,7 @@ __device__ __forceinline__ bool rank_barrier(const PeerTable& t, int me, int ws,
     const int peer = threadIdx.x;
     uint32_t* remote = reinterpret_cast<uint32_t*>(t.ptr[peer]) + blockIdx.x * COMM_MAX_RANKS + me;
     __threadfence_system();
+    comm_jitter(err, epoch + peer);
     st_release_sys(remote, epoch);
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(t.ptr[me]) + blockIdx.x * COMM_MAX_RANKS + peer;
     ok = wait_flag_ge(mine, epoch, err, where);
@@ -87,6 +89,7 @@ __global__ void __launch_bounds__(COMM_THREADS) allreduce_kernel(PeerTable t, co
   const long long v0 = me * per, v1 = min(nvec, v0 + per);
   for (long long v = v0 + blockIdx.x * (long long)blockDim.x + threadIdx.x; v < v1;
        v += (long long)gridDim.x * blockDim.x) {
+    if (!NX_IN_RANGE(pay + v * 16, 16, t.limit, err, 111)) continue;
     const uint4 s = reduce_vec<BF16>(t, ws, mc, pay, v * 16);
     if (mc != nullptr) {
       multimem_st_b128(reinterpret_cast<char*>(const_cast<void*>(mc)) + pay + v * 16, s);
@@ -109,6 +112,7 @@ __global__ void __launch_bounds__(COMM_THREADS) reduce_scatter_kernel(PeerTable 
   const long long base = me * shard_bytes;
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec;
        v += (long long)gridDim.x * blockDim.x) {
+    if (!NX_IN_RANGE(pay + base + v * 16, 16, t.limit, err, 112)) continue;
     reinterpret_cast<uint4*>(out)[v] = reduce_vec<BF16>(t, ws, mc, pay, base + v * 16);
   }
   rank_barrier(t, me, ws, epoch + 1, err, 104);  // peers may overwrite their payload only after all reads
@@ -125,6 +129,7 @@ __global__ void __launch_bounds__(COMM_THREADS) allgather_kernel(PeerTable t, co
   const long long base = pay + me * shard_bytes;
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec;
        v += (long long)gridDim.x * blockDim.x) {
+    if (!NX_IN_RANGE(base + v * 16, 16, t.limit, err, 113)) continue;
     const uint4 x = reinterpret_cast<const uint4*>(in)[v];
     if (mc != nullptr) {
       multimem_st_b128(reinterpret_cast<char*>(const_cast<void*>(mc)) + base + v * 16, x);
@@ -149,8 +154,9 @@ __global__ void __launch_bounds__(COMM_THREADS) zero_reduce_scatter_kernel(PeerT
                                                                            long long shard_bytes, uint32_t epoch,
                                                                            int* err) {
   if (!rank_barrier(t, me, ws, epoch, err, 107)) return;
-  const long long nvec = shard_bytes / 16;
+  long long nvec = shard_bytes / 16;
   const long long base = pay + me * shard_bytes;
+  if (!NX_IN_RANGE(base, shard_bytes, t.limit, err, 114)) nvec = 0;       // nothing is touched; the barriers still run
   const long long stride = (long long)gridDim.x * blockDim.x;
   char* mine = reinterpret_cast<char*>(t.ptr[me]) + base;
   constexpr int U = 4;
@@ -194,8 +200,9 @@ __global__ void __launch_bounds__(COMM_THREADS) zero_all_gather_kernel(PeerTable
                                                                        long long shard_bytes, uint32_t epoch,
                                                                        int* err) {
   if (!rank_barrier(t, me, ws, epoch, err, 109)) return;
-  const long long nvec = shard_bytes / 16;
+  long long nvec = shard_bytes / 16;
   const long long base = pay + me * shard_bytes;
+  if (!NX_IN_RANGE(base, shard_bytes, t.limit, err, 115)) nvec = 0;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const char* mine = reinterpret_cast<const char*>(t.ptr[me]) + base;
   constexpr int U = 4;
@@ -219,15 +226,45 @@ __global__ void __launch_bounds__(COMM_THREADS) zero_all_gather_kernel(PeerTable
   rank_barrier(t, me, ws, epoch + 1, err, 110);
 }
 
-static bool fill_table(PeerTable& t, const unsigned long long* ptrs, int ws) {
+// Workspace sizes registered by the host (base address as seen by this rank -> bytes), for the debug range checks.
+static unsigned long long g_ws_base[32];
+static long long g_ws_bytes[32];
+static int g_ws_n = 0;
+
+static bool fill_table(PeerTable& t, const unsigned long long* ptrs, int ws, int me = -1) {
   if (ws < 1 || ws > COMM_MAX_RANKS) return false;
   for (int i = 0; i < COMM_MAX_RANKS; ++i) t.ptr[i] = i < ws ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+  t.limit = 0;
+  if (me >= 0 && me < ws)
+    for (int i = 0; i < g_ws_n; ++i)
+      if (g_ws_base[i] == ptrs[me]) t.limit = g_ws_bytes[i];
   return true;
 }
 
 }  // namespace nx
 
 NX_API int NX_SYM(nx_comm_flag_bytes)() { return nx::COMM_FLAG_BYTES; }
+// Tells the library how large the symmetric workspace that starts at `base` (this rank's own buffer) is.  Only the
+// NEOX_DEBUG_BOUNDS build acts on it (range checks inside the kernels); the table holds the last 32 workspaces.
+NX_API int NX_SYM(nx_comm_register_workspace)(unsigned long long base, long long bytes) {
+  using namespace nx;
+  for (int i = 0; i < g_ws_n; ++i)
+    if (g_ws_base[i] == base) {
+      g_ws_bytes[i] = bytes;
+      return NX_OK;
+    }
+  const int slot = g_ws_n < 32 ? g_ws_n++ : 31;
+  g_ws_base[slot] = base;
+  g_ws_bytes[slot] = bytes;
+  return NX_OK;
+}
+NX_API int NX_SYM(nx_comm_debug_bounds)() {
+#ifdef NEOX_DEBUG_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
 NX_API int NX_SYM(nx_comm_epochs_per_call)() { return 2; }
 
 // dtype: 0 = bf16, 1 = fp32.  peer_ptrs: host array of ws workspace base addresses (as mapped here).
@@ -237,7 +274,7 @@ NX_API int NX_SYM(nx_comm_allreduce)(const unsigned long long* peer_ptrs, unsign
                              long long payload_off, long long bytes, int dtype, unsigned int epoch, void* stream_) {
   using namespace nx;
   PeerTable t;
-  NX_REQUIRE(fill_table(t, peer_ptrs, ws), "comm: world size %d out of range", ws);
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws, me), "comm: world size %d out of range", ws);
   NX_REQUIRE(bytes % 16 == 0, "comm: payload must be a multiple of 16 bytes");
   auto s = (cudaStream_t)stream_;
   if (dtype == 0)
@@ -253,7 +290,7 @@ NX_API int NX_SYM(nx_comm_reduce_scatter)(const unsigned long long* peer_ptrs, u
                                   long long payload_off, long long shard_bytes, void* out, int dtype, unsigned int epoch, void* stream_) {
   using namespace nx;
   PeerTable t;
-  NX_REQUIRE(fill_table(t, peer_ptrs, ws), "comm: world size %d out of range", ws);
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws, me), "comm: world size %d out of range", ws);
   NX_REQUIRE(shard_bytes % 16 == 0, "comm: shard must be a multiple of 16 bytes");
   auto s = (cudaStream_t)stream_;
   if (dtype == 0)
@@ -269,7 +306,7 @@ NX_API int NX_SYM(nx_comm_allgather)(const unsigned long long* peer_ptrs, unsign
                              long long payload_off, long long shard_bytes, const void* in, unsigned int epoch, void* stream_) {
   using namespace nx;
   PeerTable t;
-  NX_REQUIRE(fill_table(t, peer_ptrs, ws), "comm: world size %d out of range", ws);
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws, me), "comm: world size %d out of range", ws);
   NX_REQUIRE(shard_bytes % 16 == 0, "comm: shard must be a multiple of 16 bytes");
   allgather_kernel<<<COMM_BLOCKS, COMM_THREADS, 0, (cudaStream_t)stream_>>>(
       t, (const void*)mc_ptr, me, ws, payload_off, shard_bytes, in, epoch, device_error_word());
@@ -283,7 +320,7 @@ NX_API int NX_SYM(nx_comm_zero_reduce_scatter)(const unsigned long long* peer_pt
                                        long long shard_bytes, int dtype, int grid, unsigned int epoch, void* stream_) {
   using namespace nx;
   PeerTable t;
-  NX_REQUIRE(fill_table(t, peer_ptrs, ws), "comm: world size %d out of range", ws);
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws, me), "comm: world size %d out of range", ws);
   NX_REQUIRE(shard_bytes % 16 == 0 && payload_off % 16 == 0, "comm: shard / offset must be multiples of 16 bytes");
   NX_REQUIRE(grid >= 1 && grid * COMM_MAX_RANKS * 4 <= COMM_FLAG_BYTES, "comm: grid %d does not fit the flag area", grid);
   auto s = (cudaStream_t)stream_;
@@ -300,7 +337,7 @@ NX_API int NX_SYM(nx_comm_zero_all_gather)(const unsigned long long* peer_ptrs, 
                                    long long shard_bytes, int grid, unsigned int epoch, void* stream_) {
   using namespace nx;
   PeerTable t;
-  NX_REQUIRE(fill_table(t, peer_ptrs, ws), "comm: world size %d out of range", ws);
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws, me), "comm: world size %d out of range", ws);
   NX_REQUIRE(shard_bytes % 16 == 0 && payload_off % 16 == 0, "comm: shard / offset must be multiples of 16 bytes");
   NX_REQUIRE(grid >= 1 && grid * COMM_MAX_RANKS * 4 <= COMM_FLAG_BYTES, "comm: grid %d does not fit the flag area", grid);
   zero_all_gather_kernel<<<grid, COMM_THREADS, 0, (cudaStream_t)stream_>>>(t, me, ws, payload_off, shard_bytes, epoch,

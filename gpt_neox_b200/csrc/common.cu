@@ -19,7 +19,7 @@ void set_last_error(const char* fmt, ...) {
   va_end(ap);
 }
 
-// [0] error word, [1] unused, [2..3] run-time wait budget in cycles as one 64-bit value (0 = default)
+// [0] error word, [1] communication jitter in ns (0 = off), [2..3] run-time wait budget in cycles as one 64-bit value (0 = default)
 __device__ __align__(16) int g_error_word[4] = {0, 0, 0, 0};
 
 static int* g_err_ptr[64] = {nullptr};
@@ -213,6 +213,17 @@ NX_API int nx_set_wait_budget_cycles(long long cycles) {
   NX_REQUIRE(cycles >= 0, "wait budget must be >= 0");
   NX_CUDA_CHECK(cudaDeviceSynchronize());
   NX_CUDA_CHECK(cudaMemcpy(p + 2, &cycles, sizeof(long long), cudaMemcpyHostToDevice));
+  return NX_OK;
+}
+
+// Upper bound (nanoseconds) of the pseudo-random sleep in front of every cross-rank signal of the communication
+// kernels (debug aid against timing-dependent protocol errors); 0 = off.  Synchronises the device.
+NX_API int nx_set_comm_jitter_ns(int max_ns) {
+  int* p = nx::device_error_word();
+  if (p == nullptr) return NX_ERR_CUDA;
+  NX_REQUIRE(max_ns >= 0 && max_ns <= 1000000, "jitter must be within [0, 1 ms]");
+  NX_CUDA_CHECK(cudaDeviceSynchronize());
+  NX_CUDA_CHECK(cudaMemcpy(p + 1, &max_ns, sizeof(int), cudaMemcpyHostToDevice));
   return NX_OK;
 }
 

@@ -607,9 +607,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
       if (rs_like && chunk != p.tp_rank) {
         __threadfence_system();
         __syncwarp();
-        if (lane == 0)
+        if (lane == 0) {
+          comm_jitter(p.err, static_cast<uint32_t>(tile_in_chunk));
           st_release_sys(p.rs_flags[chunk] + (static_cast<long long>(tile_in_chunk) * p.ws + p.tp_rank) * 8 + warp_slot,
                          p.epoch);
+        }
       }
       // this warp is done with the accumulator: tell the leader's MMA thread
       tc_fence_before_sync();
@@ -652,7 +654,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     }
     __threadfence_system();
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (pt < p.ws && pt != p.tp_rank) st_release_sys(p.ag_flags[pt] + p.tp_rank * 256 + blockIdx.x, p.epoch);
+    if (pt < p.ws && pt != p.tp_rank) {
+      comm_jitter(p.err, static_cast<uint32_t>(pt));
+      st_release_sys(p.ag_flags[pt] + p.tp_rank * 256 + blockIdx.x, p.epoch);
+    }
     for (int order = 1; order < p.ws; ++order) {
       const int chunk = (p.tp_rank + order) % p.ws;
       bool ok = true;

@@ -49,6 +49,37 @@ __device__ __forceinline__ void report_error(int* err_word, int code, int where)
   }
 }
 
+// ---------------------------------------------------------------------------
+// debug aids for the communication kernels
+//   * NEOX_DEBUG_BOUNDS build (python -m gpt_neox_b200.build --debug-bounds): every access into a symmetric
+//     workspace is range-checked against the workspace size the host registered; a violation records
+//     {ERR_BOUNDS, site} and the access is skipped (nothing traps).  In the normal build the check is no code.
+//   * jitter: when the host sets a non-zero jitter (nx_set_comm_jitter_ns; int 1 of the error block), every
+//     cross-rank signal is preceded by a pseudo-random sleep below that many nanoseconds, which reorders the
+//     arrivals of flags and data between runs and shakes out protocol errors that need unlucky timing.
+// ---------------------------------------------------------------------------
+#ifdef NEOX_DEBUG_BOUNDS
+__device__ __forceinline__ bool in_range(long long off, long long nbytes, long long limit, int* err_word, int where) {
+  if (limit <= 0 || (off >= 0 && off + nbytes <= limit)) return true;
+  report_error(err_word, ERR_BOUNDS, where);
+  return false;
+}
+#define NX_IN_RANGE(off, nbytes, limit, err, where) in_range((off), (nbytes), (limit), (err), (where))
+#else
+#define NX_IN_RANGE(off, nbytes, limit, err, where) true
+#endif
+
+__device__ __forceinline__ void comm_jitter(const int* err_word, uint32_t salt) {
+  if (err_word == nullptr) return;
+  const int max_ns = *reinterpret_cast<const volatile int*>(err_word + 1);
+  if (max_ns <= 0) return;
+  uint32_t x = salt * 0x9e3779b9u + blockIdx.x * 0x85ebca6bu + static_cast<uint32_t>(clock64());
+  x ^= x >> 15;
+  x *= 0x2c1b3c6du;
+  x ^= x >> 12;
+  __nanosleep(x % static_cast<uint32_t>(max_ns));
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

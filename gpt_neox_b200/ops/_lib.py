@@ -14,7 +14,9 @@ import torch
 
 _LIB = None
 _HALF = None
-_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libneox_b200.so"
+# NEOX_KERNEL_LIB=debug loads the range-checking build (python -m gpt_neox_b200.build --debug-bounds)
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / (
+    "libneox_b200_dbg.so" if os.environ.get("NEOX_KERNEL_LIB") == "debug" else "libneox_b200.so")
 
 c_void_p, c_int, c_ll, c_float = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 
@@ -67,6 +69,9 @@ def _declare(lib):
     sig("nx_poison_device_error", [I])
     sig("nx_sm_count", [])
     sig("nx_set_wait_budget_cycles", [L])
+    sig("nx_set_comm_jitter_ns", [I])
+    sig("nx_comm_register_workspace", [U, L])
+    sig("nx_comm_debug_bounds", [])
     sig("nx_mbar_timeout_probe", [P, P])
     sig("nx_wait_counter", [P, C.c_uint, P])
     sig("nx_abi_version", [])
@@ -171,6 +176,18 @@ def set_wait_budget_cycles(cycles: int):
     """Cycle budget of every bounded wait (mbarrier / flag) in kernels launched afterwards on the current
     device; 0 restores the built-in default (4e9 cycles, about two seconds)."""
     check(lib().nx_set_wait_budget_cycles(int(cycles)), "nx_set_wait_budget_cycles")
+
+
+def set_comm_jitter_ns(max_ns: int):
+    """Debug aid: a pseudo-random sleep below ``max_ns`` nanoseconds in front of every cross-rank signal of the
+    communication kernels launched afterwards on the current device (0 = off)."""
+    check(lib().nx_set_comm_jitter_ns(int(max_ns)), "nx_set_comm_jitter_ns")
+
+
+def register_workspace(base_ptr: int, nbytes: int):
+    """Tell both kernel builds the size of a symmetric workspace (acted on by the range-checking debug build)."""
+    lib().nx_comm_register_workspace(int(base_ptr), int(nbytes))
+    lib(torch.float16).nx_comm_register_workspace(int(base_ptr), int(nbytes))
 
 
 def raise_on_device_error():

@@ -125,6 +125,7 @@ def main():
         dist.barrier(group)
         assert torch.equal(params, nccl_gather_rows(mine, group)), f"zero all-gather[{tag}]"
         done[f"zero_ag_{tag}"] = 0.0
+        assert zw.check_guards(), "a ZeRO kernel wrote into a guard band"
         del zw
 
     # ---- expert parallelism: dispatch / combine as peer loads against the fp32 statement of the experts
@@ -152,6 +153,9 @@ def main():
     done["moe_ep"] = close(out, ref, "expert-parallel dispatch / combine", 3e-2, 1.5e-2)
 
     torch.cuda.synchronize()
+    assert be.check_guards(), "a kernel wrote into a guard band of the symmetric workspace"
+    done["guards_intact"] = 0.0
+    done["debug_bounds_build"] = float(_lib.lib().nx_comm_debug_bounds())
     err = _lib.read_device_error()
     assert err == 0, f"device error word 0x{err:x}"
     dist.barrier()

@@ -142,3 +142,46 @@ def test_bounded_waits_run_out_return_and_leave_the_context_usable():
     ref = x.float() @ w.float().t()
     assert ((y.float() - ref).abs().max() / ref.abs().max()).item() < 1e-2
     assert _lib.read_device_error() == 0
+
+
+@pytest.mark.gpu
+def test_range_checking_build_records_an_out_of_range_access_and_skips_it():
+    """The NEOX_DEBUG_BOUNDS build of the communication kernels: an all-gather whose shard would end beyond the
+    registered size of the workspace records {ERR_BOUNDS, site 113} and touches nothing (one rank, its own buffer:
+    nothing is out of range in reality, only the registered size is made too small)."""
+    import ctypes as C
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import ctypes as C, torch
+from gpt_neox_b200.ops import _lib
+L = _lib.lib()
+assert L.nx_comm_debug_bounds() == 1
+flag = L.nx_comm_flag_bytes()
+buf = torch.zeros(flag + 65536, dtype=torch.uint8, device="cuda")
+x = torch.full((4096,), 7, dtype=torch.uint8, device="cuda")
+ptrs = (C.c_ulonglong * 8)(buf.data_ptr(), *([0] * 7))
+L.nx_comm_allgather.argtypes = [C.POINTER(C.c_ulonglong), C.c_ulonglong, C.c_int, C.c_int, C.c_longlong, C.c_longlong,
+                                C.c_void_p, C.c_uint, C.c_void_p]
+_lib.register_workspace(buf.data_ptr(), flag + 65536)
+_lib.check(L.nx_comm_allgather(ptrs, 0, 0, 1, flag, 4096, _lib.ptr(x), 1, _lib.stream()))
+torch.cuda.synchronize()
+assert _lib.read_device_error() == 0 and int(buf[flag:flag + 4096].sum()) == 7 * 4096
+_lib.register_workspace(buf.data_ptr(), flag + 2048)          # pretend the workspace ends in the middle of the shard
+buf.zero_()
+_lib.check(L.nx_comm_allgather(ptrs, 0, 0, 1, flag, 4096, _lib.ptr(x), 3, _lib.stream()))
+torch.cuda.synchronize()
+v = _lib.read_device_error()
+assert (v & 0xff, v >> 8) == (2, 113), hex(v)
+assert int(buf[flag:flag + 2048].sum()) == 7 * 2048 and int(buf[flag + 2048:].sum()) == 0
+print("RANGE_CHECK_OK")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    dbg = os.path.join(root, "gpt_neox_b200", "lib", "libneox_b200_dbg.so")
+    if not os.path.exists(dbg):
+        from gpt_neox_b200.build import build_cuda
+        build_cuda(debug_bounds=True)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, cwd=root,
+                       env=dict(os.environ, NEOX_KERNEL_LIB="debug", PYTHONPATH=root))
+    assert "RANGE_CHECK_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

@@ -94,11 +94,11 @@ def test_expert_parallel_2_over_peer_memory_matches_nccl_all_to_all():
     assert p2p["losses"][-1] < p2p["losses"][0]
 
 
-def _run_op_checks(nproc, dtype="bf16", timeout=600):
+def _run_op_checks(nproc, dtype="bf16", timeout=600, env=None):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
            os.path.join(HERE, "mgpu", "op_checks.py"), dtype]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=dict(os.environ))
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=dict(os.environ, **(env or {})))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     line = [l for l in r.stdout.splitlines() if l.startswith("CHECKS ")][-1]
     return json.loads(line[len("CHECKS "):])
@@ -116,3 +116,18 @@ def test_communication_ops_match_fp32_references_over_nccl(ws, dtype):
     for name in ("ag_gemm_pair", "ag_gemm_single", "gemm_rs_pair", "gemm_rs_single", "all_reduce_h16", "all_reduce_f32",
                  "reduce_scatter_h16", "zero_rs_f32", "zero_ag_h16", "moe_ep"):
         assert name in out["checks"], (name, out)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_communication_ops_under_jitter_and_range_checks():
+    """The same op-level checks with (a) a pseudo-random sleep of up to 20 us in front of every cross-rank signal,
+    which permutes the arrival order of flags and data, and (b) the build whose communication kernels range-check
+    every access into a symmetric workspace.  Results stay right, guard bands stay intact, no error is recorded."""
+    out = _run_op_checks(2, "bf16", env={"NEOX_COMM_JITTER_NS": "20000"})
+    assert "moe_ep" in out["checks"] and "guards_intact" in out["checks"]
+    dbg = os.path.join(os.path.dirname(HERE), "gpt_neox_b200", "lib", "libneox_b200_dbg.so")
+    if not os.path.exists(dbg):
+        from gpt_neox_b200.build import build_cuda
+        build_cuda(debug_bounds=True)
+    out = _run_op_checks(2, "bf16", env={"NEOX_KERNEL_LIB": "debug", "NEOX_COMM_JITTER_NS": "5000"})
+    assert out["checks"]["debug_bounds_build"] == 1.0 and "guards_intact" in out["checks"]
