@@ -21,7 +21,9 @@
 namespace nx {
 
 constexpr int AB = 128;  // rows per tile in every role
-constexpr int AB_THREADS = 192;
+constexpr int AB_THREADS = 320;  // producer warp, MMA warp, eight element-wise warps (two per TMEM lane quadrant,
+                                 // each taking half of the 128 columns: one warp per scheduler left the
+                                 // exponential / convert pipes idle during the serial S -> P -> dS chain)
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnBwdParams {
@@ -104,6 +106,22 @@ __global__ void attn_delta_vec8_kernel(const h16* __restrict__ o, const h16* __r
   if (live && (lane % LPR) == 0) delta[(static_cast<long long>(b) * H + h) * Sq_pad + q] = s;
 }
 
+// AND of a predicate over the 64 threads (two warps) that meet at named barrier `id`.
+__device__ __forceinline__ bool pair_all(bool ok, int id) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred pi, po;\n"
+      "setp.ne.u32 pi, %1, 0;\n"
+      "bar.red.and.pred po, %2, 64, pi;\n"
+      "selp.u32 %0, 1, 0, po;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(ok ? 1u : 0u), "r"(id)
+      : "memory");
+  return out != 0;
+}
+
 template <int DP>
 struct BwdSmem {
   static constexpr int TILE = AB * DP * 2;
@@ -184,7 +202,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUSED; ++i) {
       const bool by_softmax = (i == SDP_EMPTY) || (i >= DS_FULL && i < DS_FULL + 2);
-      mbar_init(bar0 + 8u * i, by_softmax ? 4 : 1);
+      mbar_init(bar0 + 8u * i, by_softmax ? 8 : 1);
     }
     fence_barrier_init();
   }
@@ -250,6 +268,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;    // which 64 of the 128 key columns of a block (and which half of dQ's columns)
     const int r = quad * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const int qi = q0 + r;
@@ -281,7 +300,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       const int lo = p.window >= 0 ? -rel0 - p.window : -(1 << 30);
       const float bias0 = slope2 * static_cast<float>(rel0) - lse2;  // folded into the exponent
 #pragma unroll 1
-      for (int c = 0; c < AB / 32; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32b_x32(T_S + c * 32 + lane_off, sv);
         tmem_ld_32x32b_x32(T_DP + c * 32 + lane_off, dv);
@@ -341,7 +360,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
     if (!aborted) {
       h16* orow = p.dq + batch * p.dq_sb + head * p.dq_sh + static_cast<long long>(qi) * p.dq_ss;
 #pragma unroll 1
-      for (int c = 0; c < DP / 32; ++c) {
+      for (int c = half * (DP / 64); c < (half + 1) * (DP / 64); ++c) {   // this half's dQ columns
         uint32_t ov[32];
         if (nlive > 0) {  // warp-uniform: every lane takes part in the collective TMEM load
           tmem_ld_32x32b_x32(T_DQ + c * 32 + lane_off, ov);
@@ -419,7 +438,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUSED; ++i) mbar_init(bar0 + 8u * i, i == PT_FULL ? 4 : 1);
+    for (int i = 0; i < NUSED; ++i) mbar_init(bar0 + 8u * i, i == PT_FULL ? 8 : 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -478,6 +497,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;   // which 64 of the 128 query columns of a step (and which half of dK / dV)
     const int r = quad * 32 + lane;  // key row in tile
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const int kcol = k0 + r;
@@ -491,10 +511,13 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       const float slope2 = p.alibi != nullptr ? p.alibi[head] * LOG2E : 0.f;
       const int st = t & 1;
       // lse / delta of this query block were bulk-copied next to the Q / dO tiles
-      if (!mbar_wait(bar(Q_FULL, st), (t >> 1) & 1, p.err, 57)) { aborted = true; break; }
+      bool ok = mbar_wait(bar(Q_FULL, st), (t >> 1) & 1, p.err, 57);
       const float4* v_lse = reinterpret_cast<const float4*>(sgen + L::VEC_OFF + st * (2 * AB * 4));
       const float4* v_del = v_lse + AB / 4;
-      if (!mbar_wait(bar(ST_FULL, 0), t & 1, p.err, 55)) { aborted = true; break; }
+      if (ok) ok = mbar_wait(bar(ST_FULL, 0), t & 1, p.err, 55);
+      // the two warps of a quadrant meet at a named barrier further down: they must take the same decision here
+      // (a wait that ran out on one of them ends the loop for both)
+      if (!pair_all(ok, 5 + quad)) { aborted = true; break; }
       tc_fence_after_sync();
       // query columns qq (0..127) of this block are alive for lo <= qq <= hi
       const int rel0 = kcol - q0 - off;  // key position minus position of query column 0
@@ -505,13 +528,19 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       const float bias0 = slope2 * static_cast<float>(rel0);
       const uint32_t kbit = 1u << (r >> p.blk_shift);      // this key row's sub-block within the key tile
       const bool plain = !need_mask && p.alibi == nullptr;   // warp-uniform: no per-element compares in the hot path
-#pragma unroll 1
-      for (int c = 0; c < AB / 32; ++c) {
+      // P^T and dS^T (16 bit) go over the columns S^T and dP^T were read from, and the partner warp of this
+      // quadrant reads the other half of those columns: both chunks of this warp are kept in registers until the
+      // two warps have finished reading (named barrier of the quadrant's 64 threads), then everything is stored.
+      uint32_t pp_all[2][16], pd_all[2][16];
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
+        uint32_t (&pp)[16] = pp_all[cc];
+        uint32_t (&pd)[16] = pd_all[cc];
         uint32_t sv[32], dv[32];
         tmem_ld_32x32b_x32(T_ST + c * 32 + lane_off, sv);
         tmem_ld_32x32b_x32(T_DPT + c * 32 + lane_off, dv);
         tmem_ld_wait();
-        uint32_t pp[16], pd[16];
         float keepf[32];      // DROP: 0 or 1 / (1 - p) per query column of this chunk (unused otherwise)
         if (DROP) {
 #pragma unroll
@@ -570,8 +599,13 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
             pd[(j >> 1) + 1] = pack_h16x2(ds[2], ds[3]);
           }
         }
-        tmem_st_32x32b_x16(T_ST + c * 16 + lane_off, pp);
-        tmem_st_32x32b_x16(T_DPT + c * 16 + lane_off, pd);
+      }
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
+        tmem_st_32x32b_x16(T_ST + c * 16 + lane_off, pp_all[cc]);
+        tmem_st_32x32b_x16(T_DPT + c * 16 + lane_off, pd_all[cc]);
       }
       tmem_st_wait();
       tc_fence_before_sync();
@@ -591,7 +625,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
                         ss = which == 0 ? p.dk_ss : p.dv_ss;
         h16* orow = base + batch * sb + kv_head * sh + static_cast<long long>(kcol) * ss;
 #pragma unroll 1
-        for (int c = 0; c < DP / 32; ++c) {
+        for (int c = half * (DP / 64); c < (half + 1) * (DP / 64); ++c) {   // this half's columns
           uint32_t ov[32];
           if (nlive > 0) {
             tmem_ld_32x32b_x32(T + c * 32 + lane_off, ov);

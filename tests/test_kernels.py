@@ -273,7 +273,6 @@ def test_adamw_sumsq_clip():
     assert torch.equal(before, p)
 
 
-@pytest.mark.parametrize("hn,rot", [(128, 32), (96, 24), (64, 64)])
 def test_adamw_8bit_state_kernel_matches_the_pytorch_statement():
     """csrc/optim.cu adam8_kernel against ops/optim.py's PyTorch statement of the same update and the same 8-bit
     block-wise codes: the master weights agree to fp32 rounding, the codes agree except where a value sits on a
@@ -308,6 +307,7 @@ def test_adamw_8bit_state_kernel_matches_the_pytorch_statement():
     assert torch.equal(before, p)
 
 
+@pytest.mark.parametrize("hn,rot", [(128, 32), (96, 24), (64, 64)])
 def test_rope_strided(hn, rot):
     from gpt_neox_b200.ops.rope import apply_rotary, rotary_tables
     torch.manual_seed(9)
