@@ -14,6 +14,8 @@
 // Recomputing S and dP in both kernels costs 7 tile GEMMs instead of 5 but keeps every
 // accumulator in TMEM from first to last block.  Counterpart of the flash-attn 2 backward the
 // reference calls through autograd (megatron/model/transformer.py:573-690).
+#include <cstdlib>
+
 #include "common.h"
 #include "ptx.cuh"
 #include "reduce.cuh"
@@ -21,9 +23,11 @@
 namespace nx {
 
 constexpr int AB = 128;  // rows per tile in every role
-constexpr int AB_THREADS = 320;  // producer warp, MMA warp, eight element-wise warps (two per TMEM lane quadrant,
-                                 // each taking half of the 128 columns: one warp per scheduler left the
-                                 // exponential / convert pipes idle during the serial S -> P -> dS chain)
+// Threads per CTA: producer warp, MMA warp and 4 * HALVES element-wise warps.  HALVES = 2 (default) puts two warps
+// on every TMEM lane quadrant, each taking half of the 128 columns of a block (one warp per scheduler leaves the
+// exponential / convert pipes idle during the serial S -> P -> dS chain); HALVES = 1 is the four-warp form
+// (NEOX_ATTN_BWD_WARPS=4 selects it).
+constexpr int ab_threads(int halves) { return 64 + 128 * halves; }
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnBwdParams {
@@ -166,8 +170,8 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_
 // dQ kernel.  smem tiles: 0 = Q, 1 = dO, 2..3 = K ring, 4..5 = V ring.
 // TMEM: S [0,128) dP [128,256) dQ [256,256+DP) dS0 [384,448) dS1 [448,512)
 // ------------------------------------------------------------------------------------------------
-template <int DP, bool DROP>
-__global__ void __launch_bounds__(AB_THREADS, 1)
+template <int DP, bool DROP, int HALVES>
+__global__ void __launch_bounds__(ab_threads(HALVES), 1)
     attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                        const AttnBwdParams p) {
@@ -202,7 +206,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
   if (threadIdx.x == 0) {
     for (int i = 0; i < NUSED; ++i) {
       const bool by_softmax = (i == SDP_EMPTY) || (i >= DS_FULL && i < DS_FULL + 2);
-      mbar_init(bar0 + 8u * i, by_softmax ? 8 : 1);
+      mbar_init(bar0 + 8u * i, by_softmax ? 4 * HALVES : 1);
     }
     fence_barrier_init();
   }
@@ -268,7 +272,8 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
     }
   } else {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;    // which 64 of the 128 key columns of a block (and which half of dQ's columns)
+    const int half = (warp - 2) >> 2;    // HALVES = 2: which 64 of the 128 key columns of a block (and half of dQ's columns)
+    constexpr int CPW = (AB / 32) / HALVES;   // 32-column chunks per warp and block
     const int r = quad * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const int qi = q0 + r;
@@ -300,7 +305,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       const int lo = p.window >= 0 ? -rel0 - p.window : -(1 << 30);
       const float bias0 = slope2 * static_cast<float>(rel0) - lse2;  // folded into the exponent
 #pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; ++c) {
+      for (int c = half * CPW; c < (half + 1) * CPW; ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32b_x32(T_S + c * 32 + lane_off, sv);
         tmem_ld_32x32b_x32(T_DP + c * 32 + lane_off, dv);
@@ -360,7 +365,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
     if (!aborted) {
       h16* orow = p.dq + batch * p.dq_sb + head * p.dq_sh + static_cast<long long>(qi) * p.dq_ss;
 #pragma unroll 1
-      for (int c = half * (DP / 64); c < (half + 1) * (DP / 64); ++c) {   // this half's dQ columns
+      for (int c = half * (DP / 32 / HALVES); c < (half + 1) * (DP / 32 / HALVES); ++c) {   // this warp's dQ columns
         uint32_t ov[32];
         if (nlive > 0) {  // warp-uniform: every lane takes part in the collective TMEM load
           tmem_ld_32x32b_x32(T_DQ + c * 32 + lane_off, ov);
@@ -403,8 +408,8 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 // TMEM: S^T [0,128) (P^T bf16 overwrites cols [0,64)), dP^T [128,256) (dS^T bf16 over [128,192)),
 //       dK [256,256+DP), dV [384,384+DP)
 // ------------------------------------------------------------------------------------------------
-template <int DP, bool DROP>
-__global__ void __launch_bounds__(AB_THREADS, 1)
+template <int DP, bool DROP, int HALVES>
+__global__ void __launch_bounds__(ab_threads(HALVES), 1)
     attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                         const AttnBwdParams p) {
@@ -438,7 +443,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUSED; ++i) mbar_init(bar0 + 8u * i, i == PT_FULL ? 8 : 1);
+    for (int i = 0; i < NUSED; ++i) mbar_init(bar0 + 8u * i, i == PT_FULL ? 4 * HALVES : 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -517,7 +522,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       if (ok) ok = mbar_wait(bar(ST_FULL, 0), t & 1, p.err, 55);
       // the two warps of a quadrant meet at a named barrier further down: they must take the same decision here
       // (a wait that ran out on one of them ends the loop for both)
-      if (!pair_all(ok, 5 + quad)) { aborted = true; break; }
+      if (HALVES == 2 ? !pair_all(ok, 5 + quad) : !ok) { aborted = true; break; }
       tc_fence_after_sync();
       // query columns qq (0..127) of this block are alive for lo <= qq <= hi
       const int rel0 = kcol - q0 - off;  // key position minus position of query column 0
@@ -531,10 +536,15 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
       // P^T and dS^T (16 bit) go over the columns S^T and dP^T were read from, and the partner warp of this
       // quadrant reads the other half of those columns: both chunks of this warp are kept in registers until the
       // two warps have finished reading (named barrier of the quadrant's 64 threads), then everything is stored.
+      // (With four warps a thread takes all four chunks, two at a time; its own earlier stores never reach columns
+      //  it has yet to read.)
+#pragma unroll 1
+      for (int grp = 0; grp < 2 / HALVES; ++grp) {
+      const int cbase = (half * (2 / HALVES) + grp) * 2;
       uint32_t pp_all[2][16], pd_all[2][16];
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;
+        const int c = cbase + cc;
         uint32_t (&pp)[16] = pp_all[cc];
         uint32_t (&pd)[16] = pd_all[cc];
         uint32_t sv[32], dv[32];
@@ -600,12 +610,13 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
           }
         }
       }
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+      if (HALVES == 2) asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;
+        const int c = cbase + cc;
         tmem_st_32x32b_x16(T_ST + c * 16 + lane_off, pp_all[cc]);
         tmem_st_32x32b_x16(T_DPT + c * 16 + lane_off, pd_all[cc]);
+      }
       }
       tmem_st_wait();
       tc_fence_before_sync();
@@ -625,7 +636,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
                         ss = which == 0 ? p.dk_ss : p.dv_ss;
         h16* orow = base + batch * sb + kv_head * sh + static_cast<long long>(kcol) * ss;
 #pragma unroll 1
-        for (int c = half * (DP / 64); c < (half + 1) * (DP / 64); ++c) {   // this half's columns
+        for (int c = half * (DP / 32 / HALVES); c < (half + 1) * (DP / 32 / HALVES); ++c) {   // this warp's columns
           uint32_t ov[32];
           if (nlive > 0) {
             tmem_ld_32x32b_x32(T + c * 32 + lane_off, ov);
@@ -672,24 +683,34 @@ static bool bwd_map(CUtensorMap* m, const void* base, int B, int Hh, int S, int 
   return make_tma_4d(m, base, dims, strides, box, 2, true);
 }
 
-template <int DP, bool DROP>
-static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+template <int DP, bool DROP, int HALVES>
+static int launch_bwd_h(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                       const CUtensorMap& tdo, const AttnBwdParams& p, cudaStream_t s) {
   static bool cfg = false;
   if (!cfg) {
-    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel<DP, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel<DP, DROP, HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        BwdSmem<DP>::DYN));
-    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<DP, DROP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<DP, DROP, HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        BwdSmem<DP>::DYN));
     cfg = true;
   }
   dim3 gq((p.Sq + AB - 1) / AB, p.H, p.B);
-  attn_bwd_dq_kernel<DP, DROP><<<gq, AB_THREADS, BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
+  attn_bwd_dq_kernel<DP, DROP, HALVES><<<gq, ab_threads(HALVES), BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
   NX_LAUNCH_CHECK();
   dim3 gk((p.Sk + AB - 1) / AB, p.Hk, p.B);
-  attn_bwd_dkv_kernel<DP, DROP><<<gk, AB_THREADS, BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
+  attn_bwd_dkv_kernel<DP, DROP, HALVES><<<gk, ab_threads(HALVES), BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
   NX_LAUNCH_CHECK();
   return NX_OK;
+}
+
+template <int DP, bool DROP>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                      const CUtensorMap& tdo, const AttnBwdParams& p, cudaStream_t s) {
+  static const bool four = [] {
+    const char* e = getenv("NEOX_ATTN_BWD_WARPS");
+    return e != nullptr && atoi(e) == 4;
+  }();
+  return four ? launch_bwd_h<DP, DROP, 1>(tq, tk, tv, tdo, p, s) : launch_bwd_h<DP, DROP, 2>(tq, tk, tv, tdo, p, s);
 }
 
 }  // namespace nx

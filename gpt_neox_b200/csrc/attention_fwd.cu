@@ -19,6 +19,13 @@
 //               stores its half of O.
 // TMEM columns: S0 [0,128) S1 [128,256) O [256,256+DP) P0 [384,448) P1 [448,512).
 // Head dims up to 128 are zero-padded to DP in {64,128} by TMA out-of-bounds fill.
+//
+// Second shape of the same kernel (template parameters BN = 64, HALVES = 1; the default): 64-key blocks, four
+// softmax warps (a thread owns a whole row of the block: no max exchange), P_j written over the columns of S_j,
+// so a CTA needs 256 TMEM columns, 96 KB of shared memory and 192 threads, and TWO CTAs share an SM: while one
+// waits in its S -> softmax -> P -> PV chain the other one's MMAs run, which is what a single CTA per SM could
+// not do (tensor pipe 23 - 28 % active in the first shape).  TMEM columns: S0 [0,64) S1 [64,128) O [128,128+DP),
+// P_j = the first 32 columns of S_j.  NEOX_ATTN_FWD_SHAPE=1 selects the first shape.
 #include <cstdlib>
 
 #include "common.h"
@@ -27,8 +34,7 @@
 namespace nx {
 
 constexpr int ATT_BM = 128;  // query rows per CTA
-constexpr int ATT_BN = 128;  // keys per block
-constexpr int ATT_THREADS = 320;
+constexpr int att_threads(int halves) { return 64 + 128 * halves; }
 
 struct AttnFwdParams {
   h16* o;
@@ -53,13 +59,14 @@ struct AttnFwdParams {
   int blk_shift, blk_nkt;
 };
 
-template <int DP>
+template <int DP, int BN>
 struct AttnSmem {
-  static constexpr int TILE = ATT_BN * DP * 2;  // one Q / K / V tile
+  static constexpr int TILE = ATT_BM * DP * 2;  // the Q tile
+  static constexpr int KV_TILE = BN * DP * 2;   // one K / V tile
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = TILE;
-  static constexpr int V_OFF = 3 * TILE;
-  static constexpr int BAR_OFF = 5 * TILE;
+  static constexpr int V_OFF = TILE + 2 * KV_TILE;
+  static constexpr int BAR_OFF = TILE + 4 * KV_TILE;
   // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2],
   // pv_done[2]  = 17 barriers, then the TMEM base word in slot 17
   static constexpr int NBAR = 18;
@@ -138,11 +145,15 @@ __device__ __forceinline__ uint32_t pack_h16x2_alu(float lo, float hi) {
 // save); 1 = MUFU + integer packing; 2 = every second exp2 as the polynomial + integer packing
 // (NEOX_ATTN_EXP selects).
 // DROP: dropout on the probabilities (the row sum stays that of the undropped softmax).
-template <int DP, int EXPV, bool DROP = false>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+template <int DP, int EXPV, bool DROP, int BN, int HALVES>
+__global__ void __launch_bounds__(att_threads(HALVES), HALVES == 1 ? 2 : 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
-  using L = AttnSmem<DP>;
+  static_assert((BN == 128 && HALVES == 2) || (BN == 64 && HALVES == 1), "a softmax thread owns 64 columns");
+  constexpr int ATT_BN = BN;
+  constexpr int ATT_THREADS = att_threads(HALVES);
+  constexpr uint32_t TMEM_COLS = HALVES == 2 ? 512 : 256;
+  using L = AttnSmem<DP, BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
@@ -169,12 +180,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   const int je = (kv_end + ATT_BN - 1) / ATT_BN;  // exclusive
   const int nblk = max(je - jb, 0);
   // block-sparse layouts: key tiles without a live block for this query tile are skipped by every role
-  auto tile_live = [&](int kt) { return p.blk_any == nullptr || p.blk_any[static_cast<long long>(qt) * p.blk_nkt + kt] != 0; };
+  // (the layout tables are kept per 128-key tile; a 64-key block looks up the tile it lies in)
+  constexpr int KT_SHIFT = BN == 64 ? 1 : 0;
+  auto tile_live = [&](int kt) {
+    return p.blk_any == nullptr || p.blk_any[static_cast<long long>(qt) * p.blk_nkt + (kt >> KT_SHIFT)] != 0;
+  };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 17; ++i) {
       const bool softmax_arrives = (i >= S_EMPTY && i < S_EMPTY + 2) || (i >= P_FULL && i < P_FULL + 2);
-      mbar_init(bar0 + 8u * i, softmax_arrives ? 8 : 1);
+      mbar_init(bar0 + 8u * i, softmax_arrives ? 4 * HALVES : 1);
     }
     fence_barrier_init();
   }
@@ -186,14 +201,17 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     tma_prefetch_desc(&tmV);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot_gen;
-  const uint32_t T_S = tmem, T_O = tmem + 256, T_P = tmem + 384;
+  // S_j at T_S + j * BN; P_j (16 bit: BN / 2 columns) in its own columns (first shape) or over the first columns of
+  // S_j (second shape: the thread that writes a row of P_j has read that row of S_j into registers before)
+  const uint32_t T_S = tmem, T_O = tmem + 2 * BN, T_P = HALVES == 2 ? tmem + 384 : tmem;
+  constexpr uint32_t P_STRIDE = HALVES == 2 ? BN / 2 : BN;
   bool aborted = false;
 
   if (warp == 0) {
@@ -210,16 +228,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         ++n;
         const int k0 = (jb + i) * ATT_BN;
         if (!mbar_wait(bar(K_EMPTY, st), ph ^ 1, p.err, 11)) { aborted = true; break; }
-        mbar_expect_tx(bar(K_FULL, st), L::TILE);
+        mbar_expect_tx(bar(K_FULL, st), L::KV_TILE);
 #pragma unroll
         for (int c = 0; c < DP / 64; ++c)
-          tma_load_4d(sbase + L::K_OFF + st * L::TILE + c * (ATT_BN * 128), &tmK, bar(K_FULL, st),
+          tma_load_4d(sbase + L::K_OFF + st * L::KV_TILE + c * (ATT_BN * 128), &tmK, bar(K_FULL, st),
                       c * 64, k0, kv_head, batch);
         if (!mbar_wait(bar(V_EMPTY, st), ph ^ 1, p.err, 12)) { aborted = true; break; }
-        mbar_expect_tx(bar(V_FULL, st), L::TILE);
+        mbar_expect_tx(bar(V_FULL, st), L::KV_TILE);
 #pragma unroll
         for (int c = 0; c < DP / 64; ++c)
-          tma_load_4d(sbase + L::V_OFF + st * L::TILE + c * (ATT_BN * 128), &tmV, bar(V_FULL, st),
+          tma_load_4d(sbase + L::V_OFF + st * L::KV_TILE + c * (ATT_BN * 128), &tmV, bar(V_FULL, st),
                       c * 64, k0, kv_head, batch);
       }
     }
@@ -234,12 +252,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         if (!mbar_wait(bar(P_FULL, st), ph, p.err, 13)) return false;
         if (!mbar_wait(bar(V_FULL, st), ph, p.err, 14)) return false;
         tc_fence_after_sync();
-        const uint32_t vb = sbase + L::V_OFF + st * L::TILE;
+        const uint32_t vb = sbase + L::V_OFF + st * L::KV_TILE;
 #pragma unroll
         for (int k = 0; k < ATT_BN / 16; ++k) {
-          // V tile is [128 keys][DP] with the head dim contiguous: MN-major B operand.
+          // V tile is [BN keys][DP] with the head dim contiguous: MN-major B operand.
           const uint64_t bdesc = umma_smem_desc_sw128(vb + k * 2048, ATT_BN * 128, 1024);
-          umma_bf16_ts(T_O, T_P + st * 64 + k * 8, bdesc, idesc_o, (i | k) != 0 ? 1u : 0u);
+          umma_bf16_ts(T_O, T_P + st * P_STRIDE + k * 8, bdesc, idesc_o, (i | k) != 0 ? 1u : 0u);
         }
         umma_commit(bar(PV_DONE, st));
         umma_commit(bar(V_EMPTY, st));
@@ -255,12 +273,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         if (!mbar_wait(bar(K_FULL, st), ph, p.err, 16)) { aborted = true; break; }
         if (!mbar_wait(bar(S_EMPTY, st), ph ^ 1, p.err, 17)) { aborted = true; break; }
         tc_fence_after_sync();
-        const uint32_t qb = sbase + L::Q_OFF, kb = sbase + L::K_OFF + st * L::TILE;
+        const uint32_t qb = sbase + L::Q_OFF, kb = sbase + L::K_OFF + st * L::KV_TILE;
 #pragma unroll
         for (int k = 0; k < DP / 16; ++k) {
-          const uint32_t o = (k >> 2) * (ATT_BM * 128) + (k & 3) * 32;
-          umma_bf16_ss(T_S + st * 128, umma_smem_desc_sw128(qb + o, 0, 1024),
-                       umma_smem_desc_sw128(kb + o, 0, 1024), idesc_s, k != 0 ? 1u : 0u);
+          const uint32_t oq = (k >> 2) * (ATT_BM * 128) + (k & 3) * 32;
+          const uint32_t ok = (k >> 2) * (ATT_BN * 128) + (k & 3) * 32;
+          umma_bf16_ss(T_S + st * BN, umma_smem_desc_sw128(qb + oq, 0, 1024),
+                       umma_smem_desc_sw128(kb + ok, 0, 1024), idesc_s, k != 0 ? 1u : 0u);
         }
         umma_commit(bar(S_FULL, st));
         umma_commit(bar(K_EMPTY, st));
@@ -271,7 +290,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;  // which 64 of the block's 128 key columns (and which half of O)
+    const int half = HALVES == 2 ? (warp - 2) >> 2 : 0;  // first shape: which 64 of the block's 128 key columns (and half of O)
     const int col0 = half * 64;
     const int r = quad * 32 + lane;  // row in tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
@@ -305,16 +324,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       const int k0 = (jb + t) * ATT_BN;
       // block-sparse: which 16..128-key sub-blocks of this key tile the row attends to
       uint32_t bits = 0xffffffffu;
-      if (p.blk_rows != nullptr)
-        bits = qi < p.Sq ? p.blk_rows[static_cast<long long>(qi) * p.blk_nkt + (jb + t)] : 0u;
-      const uint32_t full_bits = (1u << (ATT_BN >> p.blk_shift)) - 1u;
+      if (p.blk_rows != nullptr) {
+        bits = qi < p.Sq ? p.blk_rows[static_cast<long long>(qi) * p.blk_nkt + ((jb + t) >> KT_SHIFT)] : 0u;
+        if (BN == 64) bits >>= ((jb + t) & 1) * (64 >> p.blk_shift);      // the 64-key half of the 128-key tile
+      }
+      const uint32_t full_bits = (1u << max(1, ATT_BN >> p.blk_shift)) - 1u;
       const bool blk_partial = p.blk_rows != nullptr && !__all_sync(0xffffffffu, (bits & full_bits) == full_bits);
       if (!mbar_wait(bar(S_FULL, st), ph, p.err, 18)) { aborted = true; break; }
       tc_fence_after_sync();
       // One read of the whole score row into registers.
       uint32_t sv[2][32];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) tmem_ld_32x32b_x32(T_S + st * 128 + col0 + c * 32 + lane_off, sv[c]);
+      for (int c = 0; c < 2; ++c) tmem_ld_32x32b_x32(T_S + st * BN + col0 + c * 32 + lane_off, sv[c]);
       tmem_ld_wait();
       // Does this block need per-element masking?  (warp-uniform decision)
       const bool need_mask = (k0 + ATT_BN > p.Sk) || (p.causal && k0 + ATT_BN - 1 > q0 + quad * 32 + off) ||
@@ -332,7 +353,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         mx = p.alibi != nullptr ? prep_scores<true>(sv, p.scale_log2, slope2, rel0, lo, hi, col0, bits, p.blk_shift)
                                 : prep_scores<false>(sv, p.scale_log2, slope2, rel0, lo, hi, col0, bits, p.blk_shift);
       }
-      {
+      if (HALVES == 2) {
         // the row maximum over both column halves: both partners then take identical decisions
         float other;
         bool ok = exchange(mx, static_cast<uint32_t>(i + 1), other);
@@ -355,7 +376,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         if (!mbar_wait(bar(PV_DONE, (i - 1) & 1), ((i - 1) >> 1) & 1, p.err, 19)) { aborted = true; break; }
         tc_fence_after_sync();
 #pragma unroll 1
-        for (int c = half * (DP / 64); c < (half + 1) * (DP / 64); ++c) {   // this half's O columns
+        for (int c = half * (DP / 32 / HALVES); c < (half + 1) * (DP / 32 / HALVES); ++c) {   // this warp's O columns
           uint32_t ov[32];
           tmem_ld_32x32b_x32(T_O + c * 32 + lane_off, ov);
           tmem_ld_wait();
@@ -397,7 +418,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
           }
           pk[j >> 1] = EXPV == 0 ? pack_h16x2(p0, p1) : pack_h16x2_alu(p0, p1);
         }
-        tmem_st_32x32b_x16(T_P + st * 64 + half * 32 + c * 16 + lane_off, pk);
+        tmem_st_32x32b_x16(T_P + st * P_STRIDE + half * 32 + c * 16 + lane_off, pk);
       }
       const float rowsum = (rs[0] + rs[1]) + (rs[2] + rs[3]);
       l += rowsum;
@@ -415,7 +436,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       if (!mbar_wait(bar(PV_DONE, (nblk_live - 1) & 1), ((nblk_live - 1) >> 1) & 1, p.err, 21)) aborted = true;
       tc_fence_after_sync();
     }
-    if (!aborted) {
+    if (HALVES == 2 && !aborted) {
       // total row sum = this half's + the partner's (same running max on both sides)
       float other = 0.f;
       const bool ok = exchange(l, static_cast<uint32_t>(nblk_live + 1), other);
@@ -427,7 +448,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       const bool row_ok = qi < p.Sq;
       h16* orow = p.o + batch * p.o_sb + head * p.o_sh + static_cast<long long>(qi) * p.o_ss;
 #pragma unroll 1
-      for (int c = half * (DP / 64); c < (half + 1) * (DP / 64); ++c) {
+      for (int c = half * (DP / 32 / HALVES); c < (half + 1) * (DP / 32 / HALVES); ++c) {
         uint32_t ov[32];
         if (nblk_live > 0) {
           tmem_ld_32x32b_x32(T_O + c * 32 + lane_off, ov);
@@ -466,7 +487,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem, 512);
+    tmem_dealloc(tmem, TMEM_COLS);
   }
 }
 
@@ -510,9 +531,14 @@ NX_API int NX_SYM(nx_flash_attn_fwd)(const void* q, const void* k, const void* v
                  (reinterpret_cast<uintptr_t>(o) & 15) == 0,
              "flash_attn: output view must be 16-byte aligned");
   CUtensorMap tq, tk, tv;
+  static const int shape = [] {          // 2 (default): 64-key blocks, two CTAs per SM; 1: 128-key blocks, one CTA per SM
+    const char* e = getenv("NEOX_ATTN_FWD_SHAPE");
+    return e != nullptr && atoi(e) == 1 ? 1 : 2;
+  }();
+  const int bn = shape == 1 ? 128 : 64;
   if (!attn_map(&tq, q, B, H, Sq, D, q_sb, q_sh, q_ss, ATT_BM)) return NX_ERR_ARG;
-  if (!attn_map(&tk, k, B, Hk, Sk, D, k_sb, k_sh, k_ss, ATT_BN)) return NX_ERR_ARG;
-  if (!attn_map(&tv, v, B, Hk, Sk, D, v_sb, v_sh, v_ss, ATT_BN)) return NX_ERR_ARG;
+  if (!attn_map(&tk, k, B, Hk, Sk, D, k_sb, k_sh, k_ss, bn)) return NX_ERR_ARG;
+  if (!attn_map(&tv, v, B, Hk, Sk, D, v_sb, v_sh, v_ss, bn)) return NX_ERR_ARG;
   AttnFwdParams p;
   p.o = (h16*)o; p.lse = (float*)lse; p.alibi = (const float*)alibi;
   p.B = B; p.H = H; p.Hk = Hk; p.Sq = Sq; p.Sk = Sk; p.D = D;
@@ -528,7 +554,7 @@ NX_API int NX_SYM(nx_flash_attn_fwd)(const void* q, const void* k, const void* v
   p.seed_hi = static_cast<uint32_t>(seed >> 32);
   p.blk_rows = static_cast<const uint8_t*>(blk_rows);
   p.blk_any = static_cast<const uint8_t*>(blk_any);
-  p.blk_nkt = (Sk + ATT_BN - 1) / ATT_BN;
+  p.blk_nkt = (Sk + 127) / 128;
   p.blk_shift = blk_size == 16 ? 4 : blk_size == 32 ? 5 : blk_size == 64 ? 6 : 7;
   const bool drop = p.drop_thr > 0u;
   dim3 grid((Sq + ATT_BM - 1) / ATT_BM, H, B);
@@ -538,27 +564,37 @@ NX_API int NX_SYM(nx_flash_attn_fwd)(const void* q, const void* k, const void* v
     const int v = e ? atoi(e) : 0;
     return v < 0 || v > 2 ? 0 : v;
   }();
-#define NX_ATTN_LAUNCH(DPV, EV, ...)                                                                         \
+#define NX_ATTN_LAUNCH(DPV, EV, DR, BNV, HV)                                                                 \
   do {                                                                                                       \
     static bool cfg = false;                                                                                 \
-    auto kern = attn_fwd_kernel<DPV, EV, ##__VA_ARGS__>;                                                     \
+    auto kern = attn_fwd_kernel<DPV, EV, DR, BNV, HV>;                                                       \
     if (!cfg) {                                                                                              \
-      NX_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<DPV>::DYN)); \
+      NX_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
+                                         AttnSmem<DPV, BNV>::DYN));                                          \
       cfg = true;                                                                                            \
     }                                                                                                        \
-    kern<<<grid, ATT_THREADS, AttnSmem<DPV>::DYN, s>>>(tq, tk, tv, p);                                       \
+    kern<<<grid, att_threads(HV), AttnSmem<DPV, BNV>::DYN, s>>>(tq, tk, tv, p);                              \
   } while (0)
-  if (drop) {
-    if (D <= 64) NX_ATTN_LAUNCH(64, 0, true);
-    else NX_ATTN_LAUNCH(128, 0, true);
+  if (shape == 2) {
+    if (drop) {
+      if (D <= 64) NX_ATTN_LAUNCH(64, 0, true, 64, 1);
+      else NX_ATTN_LAUNCH(128, 0, true, 64, 1);
+    } else if (D <= 64) {
+      NX_ATTN_LAUNCH(64, 0, false, 64, 1);
+    } else {
+      NX_ATTN_LAUNCH(128, 0, false, 64, 1);
+    }
+  } else if (drop) {
+    if (D <= 64) NX_ATTN_LAUNCH(64, 0, true, 128, 2);
+    else NX_ATTN_LAUNCH(128, 0, true, 128, 2);
   } else if (D <= 64) {
-    if (expv == 0) NX_ATTN_LAUNCH(64, 0);
-    else if (expv == 1) NX_ATTN_LAUNCH(64, 1);
-    else NX_ATTN_LAUNCH(64, 2);
+    if (expv == 0) NX_ATTN_LAUNCH(64, 0, false, 128, 2);
+    else if (expv == 1) NX_ATTN_LAUNCH(64, 1, false, 128, 2);
+    else NX_ATTN_LAUNCH(64, 2, false, 128, 2);
   } else {
-    if (expv == 0) NX_ATTN_LAUNCH(128, 0);
-    else if (expv == 1) NX_ATTN_LAUNCH(128, 1);
-    else NX_ATTN_LAUNCH(128, 2);
+    if (expv == 0) NX_ATTN_LAUNCH(128, 0, false, 128, 2);
+    else if (expv == 1) NX_ATTN_LAUNCH(128, 1, false, 128, 2);
+    else NX_ATTN_LAUNCH(128, 2, false, 128, 2);
   }
 #undef NX_ATTN_LAUNCH
   NX_LAUNCH_CHECK();
