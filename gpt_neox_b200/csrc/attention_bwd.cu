@@ -143,10 +143,10 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* m, ui
 #pragma unroll
   for (int c = 0; c < DP / 64; ++c) tma_load_4d(dst + c * (AB * 128), m, bar, c * 64, row0, head, batch);
 }
-// D[128 x 128] = A[128 x DP] * B[128 x DP]^T, both K-major (head dim contiguous).
-template <int DP>
+// D[128 x N] = A[128 x DP] * B[N x DP]^T, both K-major (head dim contiguous); b points at the first of the N rows.
+template <int DP, int N = AB>
 __device__ __forceinline__ void mma_nt(uint32_t d_tmem, uint32_t a, uint32_t b) {
-  constexpr uint32_t idesc = umma_idesc_bf16(AB, AB, 0, 0);
+  constexpr uint32_t idesc = umma_idesc_bf16(AB, N, 0, 0);
 #pragma unroll
   for (int k = 0; k < DP / 16; ++k) {
     const uint32_t o = (k >> 2) * (AB * 128) + (k & 3) * 32;
@@ -156,11 +156,12 @@ __device__ __forceinline__ void mma_nt(uint32_t d_tmem, uint32_t a, uint32_t b) 
 }
 // D[128 x DP] (+)= A_tmem[128 x 128 (bf16, 64 columns)] * B[128 x DP] with B's head dim contiguous
 // (MN-major B operand).
-template <int DP>
+// KR: rows of B (the contraction length), 128 or 64; b points at the first of them.
+template <int DP, int KR = AB>
 __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b, bool accumulate) {
   constexpr uint32_t idesc = umma_idesc_bf16(AB, DP, 0, 1);
 #pragma unroll
-  for (int k = 0; k < AB / 16; ++k) {
+  for (int k = 0; k < KR / 16; ++k) {
     umma_bf16_ts(d_tmem, a_tmem + k * 8, umma_smem_desc_sw128(b + k * 2048, AB * 128, 1024), idesc,
                  (accumulate || k != 0) ? 1u : 0u);
   }
@@ -169,8 +170,13 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_
 // ------------------------------------------------------------------------------------------------
 // dQ kernel.  smem tiles: 0 = Q, 1 = dO, 2..3 = K ring, 4..5 = V ring.
 // TMEM: S [0,128) dP [128,256) dQ [256,256+DP) dS0 [384,448) dS1 [448,512)
+// PIPE (default, eight element-wise warps): the 128 keys of a block are handled as two halves of 64 with their own
+// S / dP columns (S_h at [64 h, ...), dP_h at [128 + 64 h, ...)), dS_h at [384 + 32 h, ...) and their own barriers.
+// The MMA warp issues S / dP of half u + 1 before it waits for dS of half u, so the tensor core computes the next
+// half (and dQ += dS K of the previous one) while the element-wise warps work on the current one; without PIPE
+// the tensor core and the element-wise warps take turns.
 // ------------------------------------------------------------------------------------------------
-template <int DP, bool DROP, int HALVES>
+template <int DP, bool DROP, int HALVES, bool PIPE>
 __global__ void __launch_bounds__(ab_threads(HALVES), 1)
     attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -180,8 +186,9 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t bar0 = sbase + L::BAR_OFF;
-  enum { QDO_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, SDP_FULL = 9, SDP_EMPTY = 10,
-         DS_FULL = 11, DQ_DONE = 13, NUSED = 15 };
+  static_assert(!PIPE || HALVES == 2, "the pipelined form gives each of a half's 64 columns' halves to one warp");
+  enum { QDO_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, SDP_FULL = 9, DS_FULL = 11, DQ_DONE = 13,
+         SDP_EMPTY = 15, NUSED = 16 };
   auto bar = [&](int which, int idx) { return bar0 + 8u * (which + idx); };
   const uint32_t tmem_slot = bar0 + 8u * 23;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(sgen + L::BAR_OFF + 8 * 23);
@@ -253,7 +260,37 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
       };
       if (!mbar_wait(bar(QDO_FULL, 0), 0, p.err, 34)) aborted = true;
       int n = 0;
-      for (int t = 0; t < nblk && !aborted; ++t) {
+      if (PIPE) {
+        // sub-step u = 2 i + h of live block i: S_h = Q K_h^T, dP_h = dO V_h^T (64 keys), later dQ += dS_h K_h
+        int nl = 0;
+        for (int t = 0; t < nblk; ++t) nl += tile_live(jb + t) ? 1 : 0;
+        auto issue_m1 = [&](int u) -> bool {
+          const int i = u >> 1, h = u & 1, st = i & 1;
+          if (h == 0) {
+            if (!mbar_wait(bar(K_FULL, st), (i >> 1) & 1, p.err, 35)) return false;
+            if (!mbar_wait(bar(V_FULL, st), (i >> 1) & 1, p.err, 36)) return false;
+          }
+          tc_fence_after_sync();
+          mma_nt<DP, 64>(T_S + h * 64, tile(0), tile(2 + st) + h * (64 * 128));
+          mma_nt<DP, 64>(T_DP + h * 64, tile(1), tile(4 + st) + h * (64 * 128));
+          umma_commit(bar(SDP_FULL, h));
+          if (h == 1) umma_commit(bar(V_EMPTY, st));
+          return true;
+        };
+        const int nsub = 2 * nl;
+        if (!aborted && nsub > 0 && !issue_m1(0)) aborted = true;
+        for (int u = 0; u < nsub && !aborted; ++u) {
+          const int i = u >> 1, h = u & 1, st = i & 1;
+          if (u + 1 < nsub && !issue_m1(u + 1)) { aborted = true; break; }
+          if (!mbar_wait(bar(DS_FULL, h), i & 1, p.err, 33)) { aborted = true; break; }
+          tc_fence_after_sync();
+          mma_ts<DP, 64>(T_DQ, T_DS + h * 32, tile(2 + st) + h * (64 * 128), u != 0);    // dQ += dS_h K_h
+          if (h == 1) umma_commit(bar(K_EMPTY, st));
+        }
+        if (!aborted && nsub > 0) umma_commit(bar(DQ_DONE, 0));
+        n = 0;      // (the loop below is the unpipelined form)
+      }
+      for (int t = 0; !PIPE && t < nblk && !aborted; ++t) {
         if (!tile_live(jb + t)) continue;
         const int i = n++;
         const int st = i & 1;
@@ -268,7 +305,7 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
         umma_commit(bar(V_EMPTY, st));
         if (i > 0 && !issue_dq(i - 1)) { aborted = true; break; }
       }
-      if (!aborted && n > 0 && !issue_dq(n - 1)) aborted = true;
+      if (!PIPE && !aborted && n > 0 && !issue_dq(n - 1)) aborted = true;
     }
   } else {
     const int quad = warp & 3;
@@ -294,9 +331,11 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
         bits = row_ok ? p.blk_rows[static_cast<long long>(qi) * p.blk_nkt + (jb + t)] : 0u;
       const uint32_t full_bits = (1u << (AB >> p.blk_shift)) - 1u;
       const bool blk_partial = p.blk_rows != nullptr && !__all_sync(0xffffffffu, (bits & full_bits) == full_bits);
-      if (!mbar_wait(bar(SDP_FULL, 0), i & 1, p.err, 38)) { aborted = true; break; }
-      if (i >= 2 && !mbar_wait(bar(DQ_DONE, st), ((i - 2) >> 1) & 1, p.err, 39)) { aborted = true; break; }
-      tc_fence_after_sync();
+      if (!PIPE) {
+        if (!mbar_wait(bar(SDP_FULL, 0), i & 1, p.err, 38)) { aborted = true; break; }
+        if (i >= 2 && !mbar_wait(bar(DQ_DONE, st), ((i - 2) >> 1) & 1, p.err, 39)) { aborted = true; break; }
+        tc_fence_after_sync();
+      }
       const bool need_mask = (k0 + AB > p.Sk) || (p.causal && k0 + AB - 1 > q0 + quad * 32 + off) ||
                              (p.window >= 0 && k0 < q0 + quad * 32 + 31 + off - p.window) || blk_partial;
       const int rel0 = k0 - qpos;
@@ -304,8 +343,15 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
       if (p.causal) hi = min(hi, -rel0);
       const int lo = p.window >= 0 ? -rel0 - p.window : -(1 << 30);
       const float bias0 = slope2 * static_cast<float>(rel0) - lse2;  // folded into the exponent
+      // PIPE: pass h = 0, 1 over the block's halves, this warp's chunk in each is c = 2 h + half (block columns
+      // 32 c ..), read from the half's own S / dP columns after its own barrier; otherwise CPW chunks of the one buffer.
 #pragma unroll 1
-      for (int c = half * CPW; c < (half + 1) * CPW; ++c) {
+      for (int cc = 0; cc < (PIPE ? 2 : CPW); ++cc) {
+        const int c = PIPE ? cc * 2 + half : half * CPW + cc;
+        if (PIPE) {
+          if (!mbar_wait(bar(SDP_FULL, cc), i & 1, p.err, 38)) { aborted = true; break; }
+          tc_fence_after_sync();
+        }
         uint32_t sv[32], dv[32];
         tmem_ld_32x32b_x32(T_S + c * 32 + lane_off, sv);
         tmem_ld_32x32b_x32(T_DP + c * 32 + lane_off, dv);
@@ -348,18 +394,31 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
             pk[j >> 1] = pack_h16x2(ds[0], ds[1]);
           }
         }
-        tmem_st_32x32b_x16(T_DS + st * 64 + c * 16 + lane_off, pk);
+        if (PIPE) {
+          // dS_h sits at [384 + 32 h, ...): the chunk's 16 columns at 16 c (c = 2 h + half)
+          tmem_st_32x32b_x16(T_DS + c * 16 + lane_off, pk);
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(DS_FULL, cc));
+        } else {
+          tmem_st_32x32b_x16(T_DS + st * 64 + c * 16 + lane_off, pk);
+        }
       }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(SDP_EMPTY, 0));
-        mbar_arrive(bar(DS_FULL, st));
+      if (aborted) break;
+      if (!PIPE) {
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar(SDP_EMPTY, 0));
+          mbar_arrive(bar(DS_FULL, st));
+        }
       }
     }
     if (!aborted && nlive > 0) {
-      if (!mbar_wait(bar(DQ_DONE, (nlive - 1) & 1), ((nlive - 1) >> 1) & 1, p.err, 40)) aborted = true;
+      if (PIPE ? !mbar_wait(bar(DQ_DONE, 0), 0, p.err, 40)
+               : !mbar_wait(bar(DQ_DONE, (nlive - 1) & 1), ((nlive - 1) >> 1) & 1, p.err, 40)) aborted = true;
       tc_fence_after_sync();
     }
     if (!aborted) {
@@ -407,8 +466,13 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
 // dK / dV kernel.  smem tiles: 0 = K, 1 = V, 2..3 = Q ring, 4..5 = dO ring.
 // TMEM: S^T [0,128) (P^T bf16 overwrites cols [0,64)), dP^T [128,256) (dS^T bf16 over [128,192)),
 //       dK [256,256+DP), dV [384,384+DP)
+// PIPE (default, eight element-wise warps): a step's 128 query columns are handled as two halves of 64 with their
+// own S^T / dP^T buffers (S^T_h at [64 h, 64 h + 64), dP^T_h at [128 + 64 h, ...)) and their own barriers.  The MMA
+// warp issues S^T / dP^T of half u + 1 before it waits for P^T / dS^T of half u, so the tensor core works on the
+// next half (and on dV / dK of the previous one) while the element-wise warps are busy with the current one;
+// without PIPE the four phases of a step run one after the other.
 // ------------------------------------------------------------------------------------------------
-template <int DP, bool DROP, int HALVES>
+template <int DP, bool DROP, int HALVES, bool PIPE>
 __global__ void __launch_bounds__(ab_threads(HALVES), 1)
     attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -418,7 +482,8 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
   const uint32_t bar0 = sbase + L::BAR_OFF;
-  enum { KV_FULL = 0, Q_FULL = 1, Q_EMPTY = 3, ST_FULL = 5, PT_FULL = 6, ACC_DONE = 7, NUSED = 8 };
+  static_assert(!PIPE || HALVES == 2, "the pipelined form splits a half's 64 columns over two warps per quadrant");
+  enum { KV_FULL = 0, Q_FULL = 1, Q_EMPTY = 3, ST_FULL = 5, PT_FULL = 7, ACC_DONE = 9, NUSED = 10 };
   auto bar = [&](int which, int idx) { return bar0 + 8u * (which + idx); };
   const uint32_t tmem_slot = bar0 + 8u * 23;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(sgen + L::BAR_OFF + 8 * 23);
@@ -443,7 +508,7 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NUSED; ++i) mbar_init(bar0 + 8u * i, i == PT_FULL ? 4 * HALVES : 1);
+    for (int i = 0; i < NUSED; ++i) mbar_init(bar0 + 8u * i, (i == PT_FULL || i == PT_FULL + 1) ? 4 * HALVES : 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -483,7 +548,34 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
     if (elect_one() && nsteps > 0) {
       if (!mbar_wait(bar(KV_FULL, 0), 0, p.err, 52)) aborted = true;
       int n = 0;
-      for (int tt = 0; tt < nsteps && !aborted; ++tt) {
+      if (PIPE) {
+        // sub-step u = 2 t + h of live step t: S^T_h = K Q_h^T, dP^T_h = V dO_h^T (64 query rows), later
+        // dV += P^T_h dO_h, dK += dS^T_h Q_h
+        int nl = 0;
+        for (int tt = 0; tt < nsteps; ++tt) nl += step_live(tt) ? 1 : 0;
+        auto issue_m1 = [&](int u) -> bool {
+          const int t = u >> 1, h = u & 1, st = t & 1;
+          if (h == 0 && !mbar_wait(bar(Q_FULL, st), (t >> 1) & 1, p.err, 53)) return false;
+          tc_fence_after_sync();
+          mma_nt<DP, 64>(T_ST + h * 64, tile(0), tile(2 + st) + h * (64 * 128));
+          mma_nt<DP, 64>(T_DPT + h * 64, tile(1), tile(4 + st) + h * (64 * 128));
+          umma_commit(bar(ST_FULL, h));
+          return true;
+        };
+        const int nsub = 2 * nl;
+        if (!aborted && nsub > 0 && !issue_m1(0)) aborted = true;
+        for (int u = 0; u < nsub && !aborted; ++u) {
+          const int t = u >> 1, h = u & 1, st = t & 1;
+          if (u + 1 < nsub && !issue_m1(u + 1)) { aborted = true; break; }
+          if (!mbar_wait(bar(PT_FULL, h), t & 1, p.err, 54)) { aborted = true; break; }
+          tc_fence_after_sync();
+          mma_ts<DP, 64>(T_DV, T_ST + h * 64, tile(4 + st) + h * (64 * 128), u != 0);    // dV += P^T_h dO_h
+          mma_ts<DP, 64>(T_DK, T_DPT + h * 64, tile(2 + st) + h * (64 * 128), u != 0);   // dK += dS^T_h Q_h
+          if (h == 1) umma_commit(bar(Q_EMPTY, st));
+        }
+        n = nl;
+      }
+      for (int tt = 0; !PIPE && tt < nsteps && !aborted; ++tt) {
         if (!step_live(tt)) continue;
         const int t = n++;          // live steps: ring stages, barrier phases and the accumulate flags count these
         const int st = t & 1;
@@ -519,11 +611,13 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
       bool ok = mbar_wait(bar(Q_FULL, st), (t >> 1) & 1, p.err, 57);
       const float4* v_lse = reinterpret_cast<const float4*>(sgen + L::VEC_OFF + st * (2 * AB * 4));
       const float4* v_del = v_lse + AB / 4;
-      if (ok) ok = mbar_wait(bar(ST_FULL, 0), t & 1, p.err, 55);
-      // the two warps of a quadrant meet at a named barrier further down: they must take the same decision here
-      // (a wait that ran out on one of them ends the loop for both)
-      if (HALVES == 2 ? !pair_all(ok, 5 + quad) : !ok) { aborted = true; break; }
-      tc_fence_after_sync();
+      if (!PIPE) {
+        if (ok) ok = mbar_wait(bar(ST_FULL, 0), t & 1, p.err, 55);
+        // the two warps of a quadrant meet at a named barrier further down: they must take the same decision here
+        // (a wait that ran out on one of them ends the loop for both)
+        if (HALVES == 2 ? !pair_all(ok, 5 + quad) : !ok) { aborted = true; break; }
+        tc_fence_after_sync();
+      }
       // query columns qq (0..127) of this block are alive for lo <= qq <= hi
       const int rel0 = kcol - q0 - off;  // key position minus position of query column 0
       int lo = p.causal ? rel0 : -(1 << 30);
@@ -538,18 +632,30 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
       // two warps have finished reading (named barrier of the quadrant's 64 threads), then everything is stored.
       // (With four warps a thread takes all four chunks, two at a time; its own earlier stores never reach columns
       //  it has yet to read.)
+      // PIPE: two passes (the halves of the step), one 32-column chunk per warp and pass, each pass with its own
+      // S^T / dP^T buffer and barriers; otherwise 2 / HALVES passes over two chunks each in the one buffer.
+      constexpr int NGRP = PIPE ? 2 : 2 / HALVES;
+      constexpr int NCC = PIPE ? 1 : 2;
 #pragma unroll 1
-      for (int grp = 0; grp < 2 / HALVES; ++grp) {
-      const int cbase = (half * (2 / HALVES) + grp) * 2;
-      uint32_t pp_all[2][16], pd_all[2][16];
+      for (int grp = 0; grp < NGRP; ++grp) {
+      const int cbase = PIPE ? grp * 2 + half : (half * (2 / HALVES) + grp) * 2;
+      // where this pass's chunks sit in TMEM: columns of the S^T buffer read / of the 16-bit result written
+      const uint32_t rd0 = PIPE ? grp * 64 + half * 32 : cbase * 32;
+      const uint32_t wr0 = PIPE ? grp * 64 + half * 16 : cbase * 16;
+      if (PIPE) {
+        if (ok) ok = mbar_wait(bar(ST_FULL, grp), t & 1, p.err, 55);
+        if (!pair_all(ok, 5 + quad)) { aborted = true; break; }
+        tc_fence_after_sync();
+      }
+      uint32_t pp_all[NCC][16], pd_all[NCC][16];
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
+      for (int cc = 0; cc < NCC; ++cc) {
         const int c = cbase + cc;
         uint32_t (&pp)[16] = pp_all[cc];
         uint32_t (&pd)[16] = pd_all[cc];
         uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(T_ST + c * 32 + lane_off, sv);
-        tmem_ld_32x32b_x32(T_DPT + c * 32 + lane_off, dv);
+        tmem_ld_32x32b_x32(T_ST + rd0 + cc * 32 + lane_off, sv);
+        tmem_ld_32x32b_x32(T_DPT + rd0 + cc * 32 + lane_off, dv);
         tmem_ld_wait();
         float keepf[32];      // DROP: 0 or 1 / (1 - p) per query column of this chunk (unused otherwise)
         if (DROP) {
@@ -612,16 +718,24 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
       }
       if (HALVES == 2) asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = cbase + cc;
-        tmem_st_32x32b_x16(T_ST + c * 16 + lane_off, pp_all[cc]);
-        tmem_st_32x32b_x16(T_DPT + c * 16 + lane_off, pd_all[cc]);
+      for (int cc = 0; cc < NCC; ++cc) {
+        tmem_st_32x32b_x16(T_ST + wr0 + cc * 16 + lane_off, pp_all[cc]);
+        tmem_st_32x32b_x16(T_DPT + wr0 + cc * 16 + lane_off, pd_all[cc]);
+      }
+      if (PIPE) {
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(PT_FULL, grp));
       }
       }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(PT_FULL, 0));
+      if (aborted) break;
+      if (!PIPE) {
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(PT_FULL, 0));
+      }
     }
     if (!aborted && nlive > 0) {
       if (!mbar_wait(bar(ACC_DONE, 0), 0, p.err, 56)) aborted = true;
@@ -688,17 +802,35 @@ static int launch_bwd_h(const CUtensorMap& tq, const CUtensorMap& tk, const CUte
                       const CUtensorMap& tdo, const AttnBwdParams& p, cudaStream_t s) {
   static bool cfg = false;
   if (!cfg) {
-    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel<DP, DROP, HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       BwdSmem<DP>::DYN));
-    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<DP, DROP, HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       BwdSmem<DP>::DYN));
+    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel<DP, DROP, HALVES, false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<DP>::DYN));
+    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel<DP, DROP, HALVES, HALVES == 2>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<DP>::DYN));
+    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<DP, DROP, HALVES, false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<DP>::DYN));
+    NX_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel<DP, DROP, HALVES, HALVES == 2>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<DP>::DYN));
     cfg = true;
   }
   dim3 gq((p.Sq + AB - 1) / AB, p.H, p.B);
-  attn_bwd_dq_kernel<DP, DROP, HALVES><<<gq, ab_threads(HALVES), BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
+  static const bool serial_q = [] {        // NEOX_ATTN_DQ_PIPE=0: the unpipelined form
+    const char* e = getenv("NEOX_ATTN_DQ_PIPE");
+    return e != nullptr && atoi(e) == 0;
+  }();
+  if (HALVES == 2 && !serial_q)
+    attn_bwd_dq_kernel<DP, DROP, HALVES, HALVES == 2><<<gq, ab_threads(HALVES), BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
+  else
+    attn_bwd_dq_kernel<DP, DROP, HALVES, false><<<gq, ab_threads(HALVES), BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
   NX_LAUNCH_CHECK();
   dim3 gk((p.Sk + AB - 1) / AB, p.Hk, p.B);
-  attn_bwd_dkv_kernel<DP, DROP, HALVES><<<gk, ab_threads(HALVES), BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
+  static const bool serial = [] {        // NEOX_ATTN_DKV_PIPE=0: the unpipelined form
+    const char* e = getenv("NEOX_ATTN_DKV_PIPE");
+    return e != nullptr && atoi(e) == 0;
+  }();
+  if (HALVES == 2 && !serial)
+    attn_bwd_dkv_kernel<DP, DROP, HALVES, HALVES == 2><<<gk, ab_threads(HALVES), BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
+  else
+    attn_bwd_dkv_kernel<DP, DROP, HALVES, false><<<gk, ab_threads(HALVES), BwdSmem<DP>::DYN, s>>>(tq, tk, tv, tdo, p);
   NX_LAUNCH_CHECK();
   return NX_OK;
 }
