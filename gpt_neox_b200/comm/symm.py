@@ -38,6 +38,7 @@ def _declare():
             "nx_gemm2_bf16_allreduce": [P, P, I, I, I, LL, LL, I, P, P, LL, I, I, I, U, PP, PP, PP, PP, U, P],
             "nx_gemm_grid": [I, I],
             "nx_comm_zero_reduce_scatter": [PP, I, I, LL, LL, I, I, U, P],
+            "nx_comm_zero_reduce_range": [PP, I, I, LL, LL, LL, LL, I, I, I, U, P],
             "nx_comm_zero_all_gather": [PP, I, I, LL, LL, I, U, P]}
     for name, argtypes in sigs.items():
         for nm in (name, name + "_f16"):            # the bf16 build and the fp16 build of every entry point
@@ -339,6 +340,21 @@ class ZeroWorkspace:
                                                           self.grad_bytes // self.ws,
                                                           1 if dtype == torch.float32 else 0, self.grid, self._next(),
                                                           _lib.stream()), "nx_comm_zero_reduce_scatter")
+
+    #: launch shape of one overlapped bucket reduction: 128-thread blocks need about 10K registers, which is what the
+    #: persistent GEMM CTAs of the backward pass leave free on an SM, so the reduction runs beside them; one block per
+    #: SM x 4 vectors in flight per thread (1.2 MB) covers the NVLink latency
+    RANGE_GRID, RANGE_THREADS = 148, 128
+
+    def reduce_grad_range(self, dtype, lo_bytes: int, hi_bytes: int, stream=None):
+        """Sum bytes [lo, hi) of the gradient buffers of all ranks; every part of the range ends up, reduced, in the
+        buffer of the rank whose chunk it belongs to.  Every rank calls this with the same ranges in the same order."""
+        LAUNCHES["n"] += 1
+        _lib.check(_lib.lib(dtype).nx_comm_zero_reduce_range(self.ptrs, self.me, self.ws, self.grad_off,
+                                                             self.grad_bytes // self.ws, lo_bytes, hi_bytes,
+                                                             1 if dtype == torch.float32 else 0, self.RANGE_GRID,
+                                                             self.RANGE_THREADS, self._next(), stream if stream is not None else _lib.stream()),
+                   "nx_comm_zero_reduce_range")
 
     def all_gather_params(self):
         """Push this rank's chunk of the parameter buffer into every peer's buffer (in place)."""

@@ -196,6 +196,65 @@ __global__ void __launch_bounds__(COMM_THREADS) zero_reduce_scatter_kernel(PeerT
   rank_barrier(t, me, ws, epoch + 1, err, 108);
 }
 
+// Overlapped ZeRO gradient reduction of ONE bucket: the byte range [lo, hi) of the gradient buffer (a layer's
+// gradients, complete while the backward pass of the layers below is still running).  The range's 16-byte
+// vectors are dealt to the ranks in equal contiguous slices; a rank sums its slice over all ranks' buffers and
+// writes the result into the buffer of the rank that owns that part of the flat space (owner = offset / shard
+// bytes), so every bucket loads all ranks and all links evenly whichever shard it falls into.  Nobody else reads
+// or writes a vector between the two barriers, so the result can go over the operand in place.
+template <bool BF16>
+__global__ void __launch_bounds__(COMM_THREADS) zero_reduce_range_kernel(PeerTable t, int me, int ws, long long pay,
+                                                                         long long shard_bytes, long long lo,
+                                                                         long long hi, uint32_t epoch, int* err) {
+  if (!rank_barrier(t, me, ws, epoch, err, 116)) return;
+  const long long nvec = (hi - lo) / 16;
+  const long long per = (nvec + ws - 1) / ws;
+  const long long v0 = me * per;
+  long long v1 = min(nvec, v0 + per);
+  if (!NX_IN_RANGE(pay + lo, hi - lo, t.limit, err, 117)) v1 = v0;        // nothing is touched; the barriers still run
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  constexpr int U = 4;
+  long long v = v0 + blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (; v + (U - 1) * stride < v1; v += U * stride) {
+    float acc[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+    for (int r = 0; r < ws; ++r) {
+      const char* src = reinterpret_cast<const char*>(t.ptr[r]) + pay + lo;
+      uint4 x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) x[u] = *reinterpret_cast<const uint4*>(src + (v + u * stride) * 16);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (BF16) {
+          acc_bf16x8(acc[u], x[u]);
+        } else {
+          acc[u][0] += __uint_as_float(x[u].x); acc[u][1] += __uint_as_float(x[u].y);
+          acc[u][2] += __uint_as_float(x[u].z); acc[u][3] += __uint_as_float(x[u].w);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      uint4 o;
+      if (BF16) o = pack_acc(acc[u]);
+      else o = make_uint4(__float_as_uint(acc[u][0]), __float_as_uint(acc[u][1]), __float_as_uint(acc[u][2]),
+                          __float_as_uint(acc[u][3]));
+      const long long off = lo + (v + u * stride) * 16;
+      const int owner = static_cast<int>(min(off / shard_bytes, (long long)(ws - 1)));
+      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.ptr[owner]) + pay + off) = o;
+    }
+  }
+  for (; v < v1; v += stride) {
+    const long long off = lo + v * 16;
+    const int owner = static_cast<int>(min(off / shard_bytes, (long long)(ws - 1)));
+    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.ptr[owner]) + pay + off) = reduce_vec<BF16>(t, ws, nullptr, pay, off);
+  }
+  rank_barrier(t, me, ws, epoch + 1, err, 118);
+}
+
 __global__ void __launch_bounds__(COMM_THREADS) zero_all_gather_kernel(PeerTable t, int me, int ws, long long pay,
                                                                        long long shard_bytes, uint32_t epoch,
                                                                        int* err) {
@@ -330,6 +389,31 @@ NX_API int NX_SYM(nx_comm_zero_reduce_scatter)(const unsigned long long* peer_pt
   else
     zero_reduce_scatter_kernel<false><<<grid, COMM_THREADS, 0, s>>>(t, me, ws, payload_off, shard_bytes, epoch,
                                                                     device_error_word());
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+// One bucket of the overlapped ZeRO gradient reduction: bytes [lo, hi) of the gradient buffer at payload_off
+// (see zero_reduce_range_kernel).  Every rank passes the same range, grid and epoch.  Small blocks (128 threads)
+// fit into the registers the persistent GEMM CTAs of the backward pass leave free on an SM.
+NX_API int NX_SYM(nx_comm_zero_reduce_range)(const unsigned long long* peer_ptrs, int me, int ws, long long payload_off,
+                                     long long shard_bytes, long long lo, long long hi, int dtype, int grid,
+                                     int threads, unsigned int epoch, void* stream_) {
+  using namespace nx;
+  PeerTable t;
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws, me), "comm: world size %d out of range", ws);
+  NX_REQUIRE(shard_bytes > 0 && shard_bytes % 16 == 0 && payload_off % 16 == 0,
+             "comm: shard / offset must be multiples of 16 bytes");
+  NX_REQUIRE(lo >= 0 && hi >= lo && hi <= shard_bytes * ws && lo % 16 == 0 && hi % 16 == 0,
+             "comm: range [%lld, %lld) must be 16-byte aligned and inside the buffer", lo, hi);
+  NX_REQUIRE(grid >= 1 && grid * COMM_MAX_RANKS * 4 <= COMM_FLAG_BYTES, "comm: grid %d does not fit the flag area", grid);
+  NX_REQUIRE(threads >= 32 && threads <= COMM_THREADS && threads % 32 == 0, "comm: %d threads per block", threads);
+  auto s = (cudaStream_t)stream_;
+  if (dtype == 0)
+    zero_reduce_range_kernel<true><<<grid, threads, 0, s>>>(t, me, ws, payload_off, shard_bytes, lo, hi, epoch,
+                                                            device_error_word());
+  else
+    zero_reduce_range_kernel<false><<<grid, threads, 0, s>>>(t, me, ws, payload_off, shard_bytes, lo, hi, epoch,
+                                                             device_error_word());
   NX_LAUNCH_CHECK();
   return NX_OK;
 }

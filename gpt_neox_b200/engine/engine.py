@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import contextlib
 import math
+import os
 from contextlib import contextmanager
 
 import torch
@@ -36,6 +37,17 @@ def _lr_mult(p) -> float:
 def _is_replicated(p) -> bool:
     """True for parameters that hold the same values on every tensor-parallel rank."""
     return not getattr(p, "model_parallel", False)
+
+
+def _unit_params(u):
+    """Parameters a layer of the stack touches: its own and, for a function layer bound to another layer's module
+    (the tied read-out is ``Lambda(partial(fn, embedding))``), that module's."""
+    ps = list(u.parameters())
+    fn = getattr(u, "func", None)
+    for a_ in list(getattr(fn, "args", ())) + list((getattr(fn, "keywords", None) or {}).values()):
+        if isinstance(a_, torch.nn.Module):
+            ps += [p for p in a_.parameters() if all(p is not q for q in ps)]
+    return ps
 
 
 class FlatGroup:
@@ -127,6 +139,9 @@ class FlatGroup:
             self.exp_avg, self.exp_avg_sq = host(self.exp_avg), host(self.exp_avg_sq)
             self.host_grad = host(torch.zeros(self.shard_size, dtype=grad_dtype))
             self.host_lp = host(torch.zeros(self.shard_size, dtype=self.lp_dtype))
+        # bucketed gradient reduction overlapped with the backward pass (Engine._ov_*): element ranges already
+        # reduced (or in flight) this step, outstanding collective handles, the stream the peer-memory kernels run on
+        self._reduced, self._works, self._side = [], [], None
         self.q8_scales = None
         if state_bits == 8:
             self.q8_scales = [torch.zeros((2, optim_ops.q8_blocks(hi - lo)), dtype=torch.float32, device=self.device)
@@ -219,10 +234,60 @@ class FlatGroup:
         ``main_grad``; GEMM weights were accumulated there directly by the wgrad epilogue."""
         if self.main_grad is None:
             return
-        for p in self.params:
+        for p, o in zip(self.params, self.offsets):
             if p.grad is not None:
+                if any(lo <= o < hi for lo, hi in self._reduced):
+                    raise RuntimeError("a gradient arrived after its bucket was reduced (overlap_comm): a parameter is "
+                                       "used by a layer that runs its backward after the layer that owns it")
                 p.main_grad.add_(p.grad.view_as(p.main_grad).to(p.main_grad.dtype))
                 p.grad = None
+
+    # ------------------------------------------------------------------ bucketed reduction, overlapped with backward
+    def param_ranges(self, params):
+        """Element ranges [lo, hi) of the flat space that hold ``params`` (padding included), adjacent ones merged."""
+        at = {id(p): o for p, o in zip(self.params, self.offsets)}
+        spans = sorted((at[id(p)], at[id(p)] + (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN) for p in params if id(p) in at)
+        out = []
+        for lo, hi in spans:
+            if out and out[-1][1] == lo:
+                out[-1] = (out[-1][0], hi)
+            else:
+                out.append((lo, hi))
+        return out
+
+    def reduce_range_async(self, lo, hi):
+        """Start the data-parallel sum of main_grad[lo:hi] (complete on every rank) without waiting for it: over
+        peer memory on a side stream when the buffers are symmetric (each part lands in its owner's buffer), else
+        as an asynchronous all-reduce of the range.  ``reduce_gradients`` covers what is left and waits."""
+        if hi <= lo:
+            return
+        self._reduced.append((lo, hi))
+        if self.predivide != 1.0:
+            self.main_grad[lo:hi].mul_(1.0 / self.predivide)
+        if self.dp_size == 1:
+            return
+        if self.zero_ws is not None:
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.device)
+            self._side.wait_stream(torch.cuda.current_stream())
+            esz = self.main_grad.element_size()
+            with torch.cuda.stream(self._side):
+                self.zero_ws.reduce_grad_range(self.main_grad.dtype, lo * esz, hi * esz)
+        else:
+            self._works.append(dist.all_reduce(self.main_grad[lo:hi], group=self.dp_group, async_op=True))
+
+    def _finish_bucketed(self):
+        """Reduce whatever no bucket covered, then wait for every bucket."""
+        covered, at = sorted(self._reduced), 0
+        for lo, hi in covered + [(self.total, self.total)]:
+            if lo > at:
+                self.reduce_range_async(at, lo)
+            at = max(at, hi)
+        if self._side is not None:
+            torch.cuda.current_stream().wait_stream(self._side)
+        for w in self._works:
+            w.wait()
+        self._reduced, self._works = [], []
 
     def grad_shard(self):
         if self.partition_params:
@@ -243,6 +308,9 @@ class FlatGroup:
     def reduce_gradients(self):
         if self.partition_params:
             return                # every micro-batch's gradients were reduce-scattered right after its backward
+        if self._reduced:
+            self._finish_bucketed()   # the layers' buckets were started from the backward pass
+            return
         if self.predivide != 1.0:
             self.main_grad.mul_(1.0 / self.predivide)
         if self.dp_size == 1:
@@ -541,6 +609,14 @@ class Engine(torch.nn.Module):
                 "bfp16": torch.bfloat16}[a.communication_data_type]
         for g in self.groups:
             g.predivide, g.comm_dtype = self._predivide, comm
+        # zero_optimization.overlap_comm: reduce each layer's gradients as soon as its backward is done
+        self._ov_pending = None
+        self._ov_buckets = 0
+        zo = a.zero_optimization or {}
+        local = hasattr((generic_optimizer or {}).get("generic_cls"), "wants_local_gradients")   # 1-bit Adam
+        if (zo.get("overlap_comm") and os.environ.get("NEOX_ZERO_OVERLAP", "1") != "0" and self.zero_stage < 3
+                and not a.is_pipe_parallel and comm is None and not local and any(g.dp_size > 1 for g in self.groups)):
+            self._install_overlap_hooks(module)
         # engine-side observability switches (all off by default)
         from ..obs import profiling
         self.breakdown = profiling.StepBreakdown(a.steps_per_print, dev) if a.wall_clock_breakdown else None
@@ -560,15 +636,7 @@ class Engine(torch.nn.Module):
         units = list(seq) if seq is not None else [module]
         owner = {}
 
-        def unit_params(u):
-            """Parameters a layer touches: its own and, for a function layer bound to another layer's module (the
-            tied read-out is ``Lambda(partial(fn, embedding))``), that module's."""
-            ps = list(u.parameters())
-            fn = getattr(u, "func", None)
-            for a_ in list(getattr(fn, "args", ())) + list((getattr(fn, "keywords", None) or {}).values()):
-                if isinstance(a_, torch.nn.Module):
-                    ps += [p for p in a_.parameters() if all(p is not q for q in ps)]
-            return ps
+        unit_params = _unit_params
 
         for u in units:
             if not isinstance(u, torch.nn.Module):
@@ -628,6 +696,55 @@ class Engine(torch.nn.Module):
             if g.partition_params and g.main_grad is not None:
                 g.finish_backward()
 
+    # ------------------------------------------------------------------ gradient reduction overlapped with backward
+    def _install_overlap_hooks(self, module):
+        """One bucket per layer of the stack: the ranges of the flat gradient buffers that hold the parameters the
+        layer is the first (in forward order) to use.  On the last micro-batch of a step a layer's bucket is
+        reduced when the backward of the next layer down begins: by then every node of its own backward has run
+        (autograd runs nodes latest-created first), and a parameter shared with a later layer is complete too,
+        since that layer's backward ran earlier.  What DeepSpeed's ``overlap_comm`` does with per-parameter hooks
+        and ``reduce_bucket_size`` buckets (reference configs/pythia/1-4B.yml:33), here one launch per layer."""
+        seq = getattr(module, "sequential", None)
+        where = {id(p): g for g in self.groups for p in g.params if g.dp_size > 1 and not g.partition_params}
+        seen = set()
+        for u in (list(seq) if seq is not None else []):
+            if not isinstance(u, torch.nn.Module):
+                continue
+            mine = [p for p in _unit_params(u) if id(p) in where and id(p) not in seen]
+            seen.update(id(p) for p in mine)
+            bucket = []
+            for g in self.groups:
+                ps = [p for p in mine if where[id(p)] is g]
+                if ps:
+                    bucket.append((g, ps, g.param_ranges(ps)))
+            if bucket:
+                self._ov_buckets += 1
+                u.register_full_backward_pre_hook(lambda _m, _g, b=bucket: self._ov_before_backward(b))
+
+    def _ov_active(self):
+        return self._ov_buckets > 0 and self.is_gradient_accumulation_boundary() and not self.store_gradients
+
+    def _ov_before_backward(self, bucket):
+        if not self._ov_active():
+            return
+        if self._ov_pending is not None and self._ov_pending is not bucket:
+            self._ov_launch(self._ov_pending)
+        self._ov_pending = bucket
+
+    def _ov_launch(self, bucket):
+        for g, params, ranges in bucket:
+            for p in params:
+                if p.grad is not None:
+                    p.main_grad.add_(p.grad.view_as(p.main_grad).to(p.main_grad.dtype))
+                    p.grad = None
+            for lo, hi in ranges:
+                g.reduce_range_async(lo, hi)
+
+    def _ov_finish(self):
+        if self._ov_pending is not None:
+            self._ov_launch(self._ov_pending)
+            self._ov_pending = None
+
     @contextmanager
     def gathered_parameters(self, write_back=False):
         """All parameters materialised (state dicts, conversions, weight surgery).  ``write_back``: the ranks keep
@@ -681,6 +798,7 @@ class Engine(torch.nn.Module):
         with self._span("backward"):
             scaled.backward(retain_graph=retain_graph)
             self._z3_finish()
+            self._ov_finish()
         return loss
 
     def _sync_sequence_parallel_grads(self):

@@ -115,6 +115,24 @@ def main():
         shard = n_el // ws
         done[f"zero_rs_{tag}"] = close(grads[rank * shard:(rank + 1) * shard], ref[rank * shard:(rank + 1) * shard],
                                        f"zero reduce-scatter[{tag}]", 1e-2, 4e-3)
+        # bucket-wise reduction (overlap_comm): odd ranges that straddle chunk borders, on a side stream, in place
+        fresh = torch.randn(n_el, device=dev, generator=g).to(gdt)
+        dist.barrier(group)
+        grads.copy_(fresh)
+        ref = fresh.clone().float()
+        dist.all_reduce(ref, group=group)
+        torch.cuda.synchronize()
+        dist.barrier(group)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        cuts = [0, 64 * 5, shard - 64, shard + 64 * 3, n_el - 64 * 7, n_el]
+        with torch.cuda.stream(side):
+            for lo, hi in zip(cuts[:-1], cuts[1:]):
+                zw.reduce_grad_range(gdt, lo * esz, hi * esz)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        done[f"zero_range_{tag}"] = close(grads[rank * shard:(rank + 1) * shard], ref[rank * shard:(rank + 1) * shard],
+                                          f"zero bucket reduction[{tag}]", 1e-2, 4e-3)
         params = zw.param_buffer(dtype)
         params.zero_()
         mine = torch.randn(shard, device=dev, generator=g).to(dtype)

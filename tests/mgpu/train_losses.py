@@ -55,7 +55,9 @@ def main():
         tp_be = symm.backend_for(mpu.get_model_parallel_group())
         calls = {k: getattr(tp_be, k, 0) for k in ("ag_calls", "rs_calls", "ar_calls")} if tp_be is not None else {}
         from gpt_neox_b200.ops import moe_ep
+        buckets = int(getattr(model, "_ov_buckets", 0))
         print("LOSSES " + json.dumps({"losses": losses, "device_error": err, "zero_symm": zs, "fused_calls": calls,
+                                      "overlap_buckets": buckets,
                                       "moe_p2p": bool(moe_ep._WORKSPACES)}),
               flush=True)
     if torch.distributed.is_initialized():

@@ -252,3 +252,46 @@ def test_zero_stage3_partitions_parameters_and_matches_stage1(over):
     assert losses == pytest.approx(ref, rel=2e-5)
     assert held["between_steps"] == 0 and held["groups"] >= 5
     assert held["total"] / 2 <= held["slices"] < held["total"] / 2 + 256 * 2 * held["groups"]
+
+
+def _train_overlap(rank, world, cfg, steps):
+    """As _train; also counts the ranges started from inside the backward pass (before the step's own reduction)."""
+    from gpt_neox_b200.engine import engine as eng
+    started = {"in_backward": 0, "at_step": 0, "in_step": False}
+    orig_async, orig_finish = eng.FlatGroup.reduce_range_async, eng.FlatGroup._finish_bucketed
+
+    def counting(self, lo, hi):
+        started["at_step" if started["in_step"] else "in_backward"] += 1
+        return orig_async(self, lo, hi)
+
+    def finishing(self):
+        started["in_step"] = True
+        try:
+            return orig_finish(self)
+        finally:
+            started["in_step"] = False
+    eng.FlatGroup.reduce_range_async, eng.FlatGroup._finish_bucketed = counting, finishing
+    try:
+        return _train(rank, world, cfg, steps), started
+    finally:
+        eng.FlatGroup.reduce_range_async, eng.FlatGroup._finish_bucketed = orig_async, orig_finish
+
+
+@pytest.mark.parametrize("over", [dict(), dict(checkpoint_activations=True, checkpoint_num_layers=1),
+                                  dict(no_weight_tying=False, gradient_accumulation_steps=2, gradient_clipping=0.05),
+                                  dict(zero_optimization={"stage": 0, "overlap_comm": True}, prescale_gradients=True)],
+                         ids=["plain", "activation_checkpointing", "tied_embeddings_gas2_clip", "stage0_prescale"])
+def test_gradient_reduction_overlapped_with_backward_matches_the_single_reduction(over):
+    """``overlap_comm``: every layer's gradients are reduced from inside the backward pass of the last micro-batch
+    (one bucket per layer, nothing but leftovers at the step) and the loss curve is that of the single reduction."""
+    cfg = tiny_config(use_cpu_initialization=True, num_layers=3, train_micro_batch_size_per_gpu=2,
+                      zero_optimization={"stage": 1, "overlap_comm": False})
+    cfg.update(over)
+    zo = dict(cfg["zero_optimization"])
+    ref = run_distributed(_train, 2, dict(cfg, zero_optimization=dict(zo, overlap_comm=False)), 5)[0]
+    out = run_distributed(_train_overlap, 2, dict(cfg, zero_optimization=dict(zo, overlap_comm=True)), 5)
+    (losses, started), (losses1, _) = out
+    assert losses == pytest.approx(losses1, rel=1e-6)
+    assert losses == pytest.approx(ref, rel=1e-6)
+    assert started["in_backward"] >= 5 * 5              # embedding, three layers, final norm (+ read-out) per step
+    assert started["at_step"] <= 5 * 2                  # alignment tails only

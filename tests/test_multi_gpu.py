@@ -54,6 +54,22 @@ def test_zero_over_peer_memory_matches_nccl_zero():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("symm", ["1", "0"], ids=["peer_memory", "nccl"])
+def test_gradient_reduction_overlapped_with_backward_matches_single_reduction(symm):
+    """``overlap_comm``: one bucket per layer, reduced from a side stream (peer-memory kernel) or as an asynchronous
+    NCCL all-reduce while the backward pass of the layers below runs; same loss curve as the one reduction at the
+    step, no device error."""
+    opt = {"optimizer": {"type": "Adam", "params": {"lr": 3e-4, "betas": [0.9, 0.95], "eps": 1e-8}},
+           "gradient_clipping": 0.5}
+    env = {"NEOX_ZERO_SYMM": symm}
+    once = _run(2, "fused", 1, 0, 8, json.dumps(dict(opt, zero_optimization={"stage": 1, "overlap_comm": False})), env=env)
+    over = _run(2, "fused", 1, 0, 8, json.dumps(dict(opt, zero_optimization={"stage": 1, "overlap_comm": True})), env=env)
+    assert over["device_error"] == 0 and once["overlap_buckets"] == 0 and over["overlap_buckets"] >= 5
+    assert over["zero_symm"] is (symm == "1")
+    assert over["losses"] == pytest.approx(once["losses"], rel=2e-3)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_pipeline_parallel_2_matches_single_stage():
     """1F1B over two pipeline stages (NCCL p2p) follows the loss curve of the unpipelined model."""
     opt = {"optimizer": {"type": "Adam", "params": {"lr": 3e-4, "betas": [0.9, 0.95], "eps": 1e-8}},
