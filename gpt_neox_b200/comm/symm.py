@@ -38,6 +38,7 @@ def _declare():
             "nx_gemm2_bf16_allreduce": [P, P, I, I, I, LL, LL, I, P, P, LL, I, I, I, U, PP, PP, PP, PP, U, P],
             "nx_gemm_grid": [I, I],
             "nx_comm_zero_reduce_scatter": [PP, I, I, LL, LL, I, I, U, P],
+            "nx_comm_embed_push": [PP, I, I, LL, P, P, I, I, I, LL, LL, I, I, U, P],
             "nx_comm_zero_reduce_range": [PP, I, I, LL, LL, LL, LL, I, I, I, U, P],
             "nx_comm_zero_all_gather": [PP, I, I, LL, LL, I, U, P]}
     for name, argtypes in sigs.items():
@@ -242,6 +243,27 @@ class SymmBackend:
                                                 _lib.stream()), "nx_comm_allreduce")
         x.copy_(stage)
         return x
+
+    def can_embed_push(self, ids: torch.Tensor, table: torch.Tensor, sp: bool) -> bool:
+        b, s = ids.shape
+        rows = b * (s // self.ws if sp else s)
+        return (ids.dim() == 2 and ids.dtype == torch.int64 and table.dtype in _lib.H16 and table.shape[1] % 8 == 0
+                and (not sp or s % self.ws == 0) and rows * table.shape[1] * 2 <= self.payload_bytes)
+
+    def embed_push(self, ids: torch.Tensor, table: torch.Tensor, vocab_lo: int, sp: bool) -> torch.Tensor:
+        """Vocabulary-parallel embedding of ``ids`` [B, S] without a reduction: every rank stores the rows of the ids
+        it owns straight into the output of the ranks that need them.  Returns [B, S, H], or this rank's
+        [B, S / ws, H] slice along the sequence with ``sp``."""
+        b, s = ids.shape
+        h = table.shape[1]
+        s_loc = s // self.ws if sp else s
+        LAUNCHES["n"] += 1
+        grid = min(2 * torch.cuda.get_device_properties(ids.device).multi_processor_count, 1024)
+        _lib.check(_lib.lib(table).nx_comm_embed_push(self.ptrs, self.me, self.ws, self.coll_off,
+                                                      _lib.ptr(ids.contiguous()), _lib.ptr(table), b, s, h, int(vocab_lo),
+                                                      table.shape[0], 1 if sp else 0, grid, self._next_epoch(),
+                                                      _lib.stream()), "nx_comm_embed_push")
+        return self._view(b * s_loc * h * 2, table.dtype, (b, s_loc, h)).clone()
 
     def reduce_scatter0(self, x: torch.Tensor) -> torch.Tensor:
         nb = x.numel() * x.element_size()

@@ -82,14 +82,14 @@ __device__ __forceinline__ float row_max_plain(const uint32_t (&sv)[2][32]) {
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      m0 = fmaxf(m0, __uint_as_float(sv[c][j]));
-      m1 = fmaxf(m1, __uint_as_float(sv[c][j + 1]));
-      m2 = fmaxf(m2, __uint_as_float(sv[c][j + 2]));
-      m3 = fmaxf(m3, __uint_as_float(sv[c][j + 3]));
+    for (int j = 0; j < 32; j += 8) {
+      m0 = fmax3(m0, __uint_as_float(sv[c][j]), __uint_as_float(sv[c][j + 1]));
+      m1 = fmax3(m1, __uint_as_float(sv[c][j + 2]), __uint_as_float(sv[c][j + 3]));
+      m2 = fmax3(m2, __uint_as_float(sv[c][j + 4]), __uint_as_float(sv[c][j + 5]));
+      m3 = fmax3(m3, __uint_as_float(sv[c][j + 6]), __uint_as_float(sv[c][j + 7]));
     }
   }
-  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+  return fmaxf(fmax3(m0, m1, m2), m3);
 }
 // Rewrites raw scores in place as base-2 logits: x = s * scale_log2 (+ slope2 * (col - qpos)),
 // -inf outside the live column range [lo, hi] of this block; returns the row maximum.
@@ -381,7 +381,11 @@ __global__ void __launch_bounds__(att_threads(HALVES), HALVES == 1 ? 2 : 1)
           tmem_ld_32x32b_x32(T_O + c * 32 + lane_off, ov);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha);
+          for (int j = 0; j < 32; j += 2) {
+            const float2 o2 = fmul2(u2f2(ov[j], ov[j + 1]), make_float2(alpha, alpha));
+            ov[j] = __float_as_uint(o2.x);
+            ov[j + 1] = __float_as_uint(o2.y);
+          }
           tmem_st_32x32b_x32(T_O + c * 32 + lane_off, ov);
         }
         tmem_st_wait();
@@ -392,23 +396,19 @@ __global__ void __launch_bounds__(att_threads(HALVES), HALVES == 1 ? 2 : 1)
       }
       // probabilities (base 2), packed to bf16 and written to TMEM as the A operand of P V
       const float msub = m_used == -INFINITY ? 0.f : m_used;
-      float rs[4] = {0.f, 0.f, 0.f, 0.f};
+      // (packed fp32 pairs: one FFMA2 scales and shifts two scores, one FADD2 adds two probabilities to the row sums)
+      float2 rs[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+      const float2 sc2 = make_float2(plain ? p.scale_log2 : 1.f, plain ? p.scale_log2 : 1.f);
+      const float2 nm2 = make_float2(-msub, -msub);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          float x0, x1;
-          if (plain) {
-            x0 = fmaf(__uint_as_float(sv[c][j]), p.scale_log2, -msub);
-            x1 = fmaf(__uint_as_float(sv[c][j + 1]), p.scale_log2, -msub);
-          } else {
-            x0 = __uint_as_float(sv[c][j]) - msub;
-            x1 = __uint_as_float(sv[c][j + 1]) - msub;
-          }
-          float p0 = exp2f(x0);
-          float p1 = EXPV == 2 ? exp2_poly(x1) : exp2f(x1);
-          rs[(j >> 1) & 3] += p0 + p1;
+          const float2 x = ffma2(u2f2(sv[c][j], sv[c][j + 1]), sc2, nm2);
+          float p0 = exp2f(x.x);
+          float p1 = EXPV == 2 ? exp2_poly(x.y) : exp2f(x.y);
+          rs[(j >> 1) & 3] = fadd2(rs[(j >> 1) & 3], make_float2(p0, p1));
           if (DROP) {
             const int kk = k0 + col0 + c * 32 + j;        // even: (kk, kk + 1) share one patch
             const uint32_t patch = dropout_patch(p.seed_lo, p.seed_hi, static_cast<uint32_t>(batch * p.H + head),
@@ -420,7 +420,8 @@ __global__ void __launch_bounds__(att_threads(HALVES), HALVES == 1 ? 2 : 1)
         }
         tmem_st_32x32b_x16(T_P + st * P_STRIDE + half * 32 + c * 16 + lane_off, pk);
       }
-      const float rowsum = (rs[0] + rs[1]) + (rs[2] + rs[3]);
+      const float2 rs01 = fadd2(fadd2(rs[0], rs[1]), fadd2(rs[2], rs[3]));
+      const float rowsum = rs01.x + rs01.y;
       l += rowsum;
       tmem_st_wait();
       tc_fence_before_sync();

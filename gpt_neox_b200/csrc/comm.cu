@@ -285,6 +285,44 @@ __global__ void __launch_bounds__(COMM_THREADS) zero_all_gather_kernel(PeerTable
   rank_barrier(t, me, ws, epoch + 1, err, 110);
 }
 
+// Vocabulary-parallel embedding with the tensor-parallel reduction folded away (the reference looks the ids up
+// against the local part of the table, zeroes the rows of foreign ids and all-reduces the result,
+// megatron/mpu/layers.py:186-212; under sequence parallelism it then keeps one slice).  A token's row exists on
+// exactly one rank, the owner of that part of the vocabulary: that rank stores the row straight into the output
+// buffer (payload offset `pay` of the workspace) of every rank that needs it, which under sequence parallelism
+// is the single rank that owns the token's part of the sequence.  Nothing is summed, and a row crosses NVLink once
+// per destination.  ids: [B, S] row-major; output per rank: [B, S, H], or [B, S / ws, H] with sp != 0.
+// One warp per token.  An id outside every rank's range leaves its output row unwritten.
+__global__ void __launch_bounds__(COMM_THREADS) embed_push_kernel(PeerTable t, int me, int ws, long long pay,
+                                                                  const long long* __restrict__ ids,
+                                                                  const h16* __restrict__ table, int B, int S, int H,
+                                                                  long long vocab_lo, long long vocab_n, int sp,
+                                                                  uint32_t epoch, int* err) {
+  if (!rank_barrier(t, me, ws, epoch, err, 119)) return;       // the previous readers of the buffers are done
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long T = static_cast<long long>(B) * S;
+  const int s_loc = sp ? S / ws : S;
+  const int nvec = H >> 3;
+  const long long row_bytes = static_cast<long long>(H) * 2;
+  for (long long tok = warp; tok < T; tok += nwarps) {
+    const long long id = ids[tok] - vocab_lo;
+    if (id < 0 || id >= vocab_n) continue;                     // another rank owns this part of the vocabulary
+    const uint4* src = reinterpret_cast<const uint4*>(table + id * H);
+    const int b = static_cast<int>(tok / S), sq = static_cast<int>(tok % S);
+    const long long slot = sp ? static_cast<long long>(b) * s_loc + (sq % s_loc) : tok;
+    const long long off = pay + slot * row_bytes;
+    if (!NX_IN_RANGE(off, row_bytes, t.limit, err, 120)) continue;
+    const int r0 = sp ? sq / s_loc : 0, r1 = sp ? r0 + 1 : ws;
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 x = src[v];
+      for (int r = r0; r < r1; ++r) reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.ptr[r]) + off)[v] = x;
+    }
+  }
+  rank_barrier(t, me, ws, epoch + 1, err, 121);                // every row of every rank's output has landed
+}
+
 // Workspace sizes registered by the host (base address as seen by this rank -> bytes), for the debug range checks.
 static unsigned long long g_ws_base[32];
 static long long g_ws_bytes[32];
@@ -369,6 +407,25 @@ NX_API int NX_SYM(nx_comm_allgather)(const unsigned long long* peer_ptrs, unsign
   NX_REQUIRE(shard_bytes % 16 == 0, "comm: shard must be a multiple of 16 bytes");
   allgather_kernel<<<COMM_BLOCKS, COMM_THREADS, 0, (cudaStream_t)stream_>>>(
       t, (const void*)mc_ptr, me, ws, payload_off, shard_bytes, in, epoch, device_error_word());
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+
+// Vocabulary-parallel embedding lookup whose rows are stored straight into the consumers' buffers (see
+// embed_push_kernel).  table: this rank's [vocab_n, H] part (first id vocab_lo).  Output: payload_off of every
+// rank's workspace.  Every rank passes the same ids, shapes, grid and epoch.
+NX_API int NX_SYM(nx_comm_embed_push)(const unsigned long long* peer_ptrs, int me, int ws, long long payload_off,
+                              const void* ids, const void* table, int B, int S, int H, long long vocab_lo,
+                              long long vocab_n, int sp, int grid, unsigned int epoch, void* stream_) {
+  using namespace nx;
+  PeerTable t;
+  NX_REQUIRE(fill_table(t, peer_ptrs, ws, me), "comm: world size %d out of range", ws);
+  NX_REQUIRE(H % 8 == 0 && payload_off % 16 == 0, "embed_push: H=%d must be a multiple of 8", H);
+  NX_REQUIRE(!sp || S % ws == 0, "embed_push: sequence length %d does not divide into %d ranks", S, ws);
+  NX_REQUIRE(grid >= 1 && grid * COMM_MAX_RANKS * 4 <= COMM_FLAG_BYTES, "comm: grid %d does not fit the flag area", grid);
+  embed_push_kernel<<<grid, COMM_THREADS, 0, (cudaStream_t)stream_>>>(
+      t, me, ws, payload_off, (const long long*)ids, (const h16*)table, B, S, H, vocab_lo, vocab_n, sp, epoch,
+      device_error_word());
   NX_LAUNCH_CHECK();
   return NX_OK;
 }

@@ -450,6 +450,19 @@ __device__ __forceinline__ void gelu_tanh_both(float x, float& g, float& dg) {
 // the same mask whatever their thread-to-element mapping.  One 32-bit hash serves the 2 x 2 patch
 // (q & ~1, k & ~1): byte (q & 1) * 2 + (k & 1) is compared with the threshold.  p is quantised to 1/256.
 // ---------------------------------------------------------------------------
+// ---- packed fp32 pairs (sm_100 FFMA2 / FADD2 / FMUL2: one issue slot for two lanes of work) and the three-input
+//      maximum; the element-wise halves of the attention kernels are issue-bound, so these halve their FMA-pipe
+//      instruction count.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 u2f2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
+
 __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   x ^= x >> 16;
   x *= 0x7feb352du;

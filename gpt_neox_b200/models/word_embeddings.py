@@ -62,7 +62,13 @@ class Embedding(nn.Module):
         self.init_method(self.tokentype_embeddings.weight)
 
     def forward(self, input_ids, position_ids, tokentype_ids=None):
-        embeddings = self.word_embeddings(input_ids)
+        # sequence parallelism: when nothing between the lookup and the scatter needs the whole sequence, the lookup
+        # itself delivers this rank's slice (over peer memory each row goes only to the rank that owns its position)
+        pos_table = self.use_pos_emb and self.embedding_type in ("learned", "sinusoidal")
+        early = (self.sequence_parallel and not pos_table and tokentype_ids is None
+                 and not (self.training and self.embedding_dropout.p > 0))
+        embeddings = self.word_embeddings(input_ids, to_sequence_parallel=True) if early else \
+            self.word_embeddings(input_ids)
         if self.use_pos_emb and self.embedding_type in ("learned", "sinusoidal"):
             if self.embedding_type == "learned" and self.opt_pos_emb_offset:
                 position_ids = position_ids + self.opt_pos_emb_offset
@@ -76,7 +82,7 @@ class Embedding(nn.Module):
         if self.use_mup:
             with torch.no_grad():
                 embeddings.mul_(self.mup_embedding_mult)
-        if self.sequence_parallel:
+        if self.sequence_parallel and not early:
             embeddings = scatter_to_sequence_parallel_region(embeddings, seq_dim=1)
         return embeddings
 

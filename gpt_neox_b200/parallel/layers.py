@@ -20,7 +20,8 @@ from ..ops.gemm import linear as linear_op
 from . import state as mpu
 from .mappings import (copy_to_model_parallel_region, gather_from_model_parallel_region,
                        gather_from_sequence_parallel_region, reduce_from_model_parallel_region,
-                       reduce_scatter_to_sequence_parallel_region, scatter_to_model_parallel_region)
+                       reduce_scatter_to_sequence_parallel_region, scatter_to_model_parallel_region,
+                       scatter_to_sequence_parallel_region)
 from .random import get_cuda_rng_tracker
 from .utils import VocabUtility, divide
 
@@ -92,13 +93,55 @@ class VocabParallelEmbedding(nn.Module):
                                             device=_device(neox_args), dtype=neox_args.params_dtype))
         _init_partitioned(self.weight, (num_embeddings, embedding_dim), 0, init_method, neox_args)
 
-    def forward(self, input_):
+    def forward(self, input_, to_sequence_parallel=False):
+        """``to_sequence_parallel``: return this rank's slice along the sequence (dim 1) instead of the whole
+        [batch, seq, hidden] result."""
+        if self.model_parallel_size > 1 and input_.is_cuda and input_.dim() == 2:
+            # over peer memory the owner of a vocabulary entry stores its row straight into the output of the
+            # rank(s) that need it: no all-reduce over rows of zeros, no separate scatter
+            from ..ops import fused_tp
+            be = fused_tp.backend(self.weight, mpu.get_model_parallel_group())
+            if be is not None and be.can_embed_push(input_, self.weight, to_sequence_parallel):
+                out = _EmbedPushFn.apply(input_, self.weight, self.vocab_start_index, be, bool(to_sequence_parallel))
+                return out * self.mup_embedding_mult if self.use_mup else out
         out = embedding_op(input_, self.weight, self.vocab_start_index)
         if self.use_mup:
             out = out * self.mup_embedding_mult
         if self.model_parallel_size > 1:
             out = reduce_from_model_parallel_region(out)
+            if to_sequence_parallel:
+                out = scatter_to_sequence_parallel_region(out, seq_dim=1)
         return out
+
+
+class _EmbedPushFn(torch.autograd.Function):
+    """Vocabulary-parallel lookup whose rows travel straight to their consumers (comm/symm.py embed_push).  Backward:
+    the gradient rows of all tokens (gathered along the sequence if the output was a slice) are scattered into this
+    rank's part of the table by the kernel the unfused path uses."""
+
+    @staticmethod
+    def forward(ctx, ids, table, vocab_start, be, sp):
+        ctx.save_for_backward(ids)
+        ctx.table, ctx.vocab_start, ctx.sp = table, int(vocab_start), sp
+        return be.embed_push(ids, table, vocab_start, sp)
+
+    @staticmethod
+    def backward(ctx, gy):
+        from ..ops import _lib
+        from ..ops.gemm import LAUNCHES
+        from .mappings import _gather_along_seq_dim
+        (ids,) = ctx.saved_tensors
+        table = ctx.table
+        V, H = table.shape
+        g = _gather_along_seq_dim(gy.contiguous(), 1) if ctx.sp else gy
+        g2 = g.reshape(-1, H).contiguous()
+        flat = ids.reshape(-1).contiguous()
+        mg = getattr(table, "main_grad", None)
+        target = mg if mg is not None else torch.zeros((V, H), device=table.device, dtype=torch.float32)
+        LAUNCHES["n"] += 1
+        _lib.check(_lib.lib(g2).nx_embedding_bwd(_lib.ptr(flat), _lib.ptr(g2), _lib.ptr(target), flat.numel(), H,
+                                                 ctx.vocab_start, V, _lib.stream()), "nx_embedding_bwd")
+        return None, (None if mg is not None else target.to(table.dtype)), None, None, None
 
 
 class ParallelRelativePositionBias(nn.Module):

@@ -146,6 +146,25 @@ def main():
         assert zw.check_guards(), "a ZeRO kernel wrote into a guard band"
         del zw
 
+    # ---- vocabulary-parallel embedding whose rows are stored straight into their consumers' buffers
+    V, H, B, S = 64 * ws + 24, 264, 3, 16 * ws
+    gt = torch.Generator(device="cuda").manual_seed(11)                     # table and ids: the same on all ranks
+    table = torch.randn(V, H, device=dev, generator=gt).to(dtype)
+    ids = torch.randint(0, V, (B, S), device=dev, generator=gt)
+    per = (V + ws - 1) // ws
+    lo, hi = rank * per, min(V, (rank + 1) * per)
+    local = table[lo:hi].contiguous()
+    want = torch.nn.functional.embedding(ids, table)
+    for _ in range(2):                                                       # twice: the buffer is reused
+        assert be.can_embed_push(ids, local, False) and be.can_embed_push(ids, local, True)
+        assert torch.equal(be.embed_push(ids, local, lo, False), want), "embed_push: full output"
+        s_loc = S // ws
+        assert torch.equal(be.embed_push(ids, local, lo, True), want[:, rank * s_loc:(rank + 1) * s_loc]), \
+            "embed_push: sequence-parallel slice"
+        ids = ids.flip(1).contiguous()
+        want = torch.nn.functional.embedding(ids, table)
+    done["embed_push"] = 0.0
+
     # ---- expert parallelism: dispatch / combine as peer loads against the fp32 statement of the experts
     from gpt_neox_b200.ops import moe_ep
     T, topk, H, ffn, E = 512, 2, 256, 512, 2 * ws

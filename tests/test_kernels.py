@@ -29,7 +29,7 @@ def bf(*shape, scale=1.0, grad=False):
 
 
 @pytest.mark.parametrize("rows,H", [(7, 64), (300, 512), (1024, 2048), (33, 4096), (5, 6144), (700, 8192),
-                                     (40, 16384)])
+                                     (40, 16384), (20000, 1024), (5001, 6144)])   # the last two wrap the stage ring
 def test_layernorm_fwd_bwd(rows, H):
     from gpt_neox_b200.ops.norm import layer_norm
     torch.manual_seed(0)
@@ -71,7 +71,7 @@ def test_dual_layernorm_matches_two_norms():
         assert rel(bs[i].grad, br[i].grad) < 2e-2
 
 
-@pytest.mark.parametrize("rows,H", [(1000, 4096), (77, 6144), (300, 8192), (9, 16384), (5, 32768)])
+@pytest.mark.parametrize("rows,H", [(1000, 4096), (77, 6144), (300, 8192), (9, 16384), (5, 32768), (9000, 4096)])
 def test_dual_layernorm_with_residual_carry_one_backward_pass(rows, H):
     """(x, y1, y2) = dual norm with the residual stream carried through the node: dx = g_res + both
     norm gradients from ONE backward kernel launch."""
@@ -112,7 +112,7 @@ def test_rmsnorm_carry_adds_residual_gradient():
     assert rel(w.grad, wr.grad) < 2e-2
 
 
-@pytest.mark.parametrize("rows,H", [(64, 256), (513, 4096)])
+@pytest.mark.parametrize("rows,H", [(64, 256), (513, 4096), (12000, 2048)])
 def test_rmsnorm_fwd_bwd(rows, H):
     from gpt_neox_b200.ops.norm import rms_norm
     torch.manual_seed(2)
