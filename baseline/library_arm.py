@@ -264,7 +264,7 @@ class Zero1AdamW:
 def build(model_name, n_gpus, rank, dev, seq):
     """Returns (model, optimizer, tp, dp, dp_rank)."""
     c = SHAPES[model_name]
-    tp = 1 if n_gpus == 1 else 2
+    tp = 1 if (n_gpus == 1 or "1-4B" in model_name) else 2      # Pythia-1.4B: pure data parallel, as in bench.py
     dp = n_gpus // tp
     tp_group = dp_group = None
     tp_rank, dp_rank = 0, 0

@@ -303,7 +303,8 @@ def main():
         gas = args.gas or 1
         global_batch = micro * gas * dp
     else:
-        tp = 1 if n == 1 else 2
+        # Pythia-6.9B: the named layout is TP 2 (+ sequence parallelism) x DP N/2; Pythia-1.4B: pure data parallel
+        tp = 1 if (n == 1 or "1-4B" in args.model) else 2
         dp = n // tp
         micro = args.micro_batch or (4 if "6-9B" in args.model else 16)
         per_gpu_seqs = 64 if "6-9B" in args.model else 128         # sequences per GPU per optimizer step

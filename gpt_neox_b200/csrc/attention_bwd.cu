@@ -372,12 +372,11 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
         if (!need_mask && p.alibi == nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
-            // the softmax scale of dS is applied once, to dQ, in the epilogue; fp32 pairs share one issue slot
-            const float2 x = ffma2(u2f2(sv[j], sv[j + 1]), make_float2(p.scale_log2, p.scale_log2),
-                                   make_float2(-lse2, -lse2));
-            const float2 dd = fadd2(u2f2(dv[j], dv[j + 1]), make_float2(-delta, -delta));
-            const float2 ds = fmul2(make_float2(exp2f(x.x), exp2f(x.y)), dd);
-            pk[j >> 1] = pack_h16x2(ds.x, ds.y);
+            // the softmax scale of dS is applied once, to dQ, in the epilogue
+            const float p0 = exp2f(fmaf(__uint_as_float(sv[j]), p.scale_log2, -lse2));
+            const float p1 = exp2f(fmaf(__uint_as_float(sv[j + 1]), p.scale_log2, -lse2));
+            pk[j >> 1] = pack_h16x2(p0 * (__uint_as_float(dv[j]) - delta),
+                                     p1 * (__uint_as_float(dv[j + 1]) - delta));
           }
         } else {
 #pragma unroll
@@ -677,16 +676,11 @@ __global__ void __launch_bounds__(ab_threads(HALVES), 1)
             const float lq[4] = {l4.x, l4.y, l4.z, l4.w}, dq_[4] = {d4.x, d4.y, d4.z, d4.w};
             float pr[4], ds[4];
 #pragma unroll
-            for (int e = 0; e < 4; e += 2) {     // fp32 pairs share one issue slot (FFMA2 / FADD2 / FMUL2)
-              const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
-              const float2 x = ffma2(u2f2(sv[j + e], sv[j + e + 1]), sc2, make_float2(-lq[e], -lq[e + 1]));
-              float2 pr2 = make_float2(exp2f(x.x), exp2f(x.y));
-              float2 dp2 = u2f2(dv[j + e], dv[j + e + 1]);
-              if (DROP) dp2 = fmul2(dp2, make_float2(keepf[j + e], keepf[j + e + 1]));
-              const float2 ds2 = fmul2(pr2, fadd2(dp2, make_float2(-dq_[e], -dq_[e + 1])));   // softmax scale: once,
-              if (DROP) pr2 = fmul2(pr2, make_float2(keepf[j + e], keepf[j + e + 1]));       // on dK, in the epilogue;
-              pr[e] = pr2.x; pr[e + 1] = pr2.y;                                                // dV takes the dropped
-              ds[e] = ds2.x; ds[e + 1] = ds2.y;                                                // probabilities
+            for (int e = 0; e < 4; ++e) {
+              pr[e] = exp2f(fmaf(__uint_as_float(sv[j + e]), p.scale_log2, -lq[e]));
+              const float dpe = DROP ? __uint_as_float(dv[j + e]) * keepf[j + e] : __uint_as_float(dv[j + e]);
+              ds[e] = pr[e] * (dpe - dq_[e]);     // softmax scale: once, on dK, in the epilogue
+              if (DROP) pr[e] *= keepf[j + e];    // dV takes the dropped probabilities
             }
             pp[j >> 1] = pack_h16x2(pr[0], pr[1]);
             pp[(j >> 1) + 1] = pack_h16x2(pr[2], pr[3]);

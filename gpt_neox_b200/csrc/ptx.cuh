@@ -134,13 +134,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same test, but the thread may be suspended by the hardware for up to `hint_ns` nanoseconds while the phase
+// is incomplete (it is woken when the phase completes).  A waiting warp then stops competing for issue slots with
+// the warps that share its scheduler: with the plain form a waiting control warp re-polled every few dozen cycles
+// and its loop took as many issue slots as a working warp.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+#ifndef NX_MBAR_SUSPEND_NS
+#define NX_MBAR_SUSPEND_NS 4000u
+#endif
 // Bounded wait. Returns false (and records ERR_WAIT_TIMEOUT) if the budget ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err_word, int where) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3ff) == 0) {
+  while (!mbar_try_wait_suspend(bar, parity, NX_MBAR_SUSPEND_NS)) {
+    if ((++spins & 0x3f) == 0) {
       if (clock64() - t0 > wait_budget(err_word)) {
         report_error(err_word, ERR_WAIT_TIMEOUT, where);
         return false;
