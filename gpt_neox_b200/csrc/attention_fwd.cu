@@ -77,10 +77,11 @@ struct AttnSmem {
 };
 
 // Row maximum of raw scores (no mask, no ALiBi), four independent chains for ILP.
-__device__ __forceinline__ float row_max_plain(const uint32_t (&sv)[2][32]) {
+template <int NC>
+__device__ __forceinline__ float row_max_plain(const uint32_t (&sv)[NC][32]) {
   float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-  for (int c = 0; c < 2; ++c) {
+  for (int c = 0; c < NC; ++c) {
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
       m0 = fmax3(m0, __uint_as_float(sv[c][j]), __uint_as_float(sv[c][j + 1]));
@@ -96,13 +97,13 @@ __device__ __forceinline__ float row_max_plain(const uint32_t (&sv)[2][32]) {
 // rel0 = (first column of the block) - (query position); col0 = first block column of this half row.
 // bits / shift: block-sparse layout of this row in this key tile (bit (idx >> shift) set = column idx is attended);
 // 0xffffffff with any shift for a dense layout.
-template <bool ALIBI>
-__device__ __forceinline__ float prep_scores(uint32_t (&sv)[2][32], float scale_log2, float slope2,
+template <bool ALIBI, int NC>
+__device__ __forceinline__ float prep_scores(uint32_t (&sv)[NC][32], float scale_log2, float slope2,
                                              int rel0, int lo, int hi, int col0, uint32_t bits, int shift) {
   float m0 = -INFINITY, m1 = -INFINITY;
   const float bias0 = ALIBI ? slope2 * static_cast<float>(rel0) : 0.f;
 #pragma unroll
-  for (int c = 0; c < 2; ++c) {
+  for (int c = 0; c < NC; ++c) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const int idx = col0 + c * 32 + j;
@@ -146,13 +147,15 @@ __device__ __forceinline__ uint32_t pack_h16x2_alu(float lo, float hi) {
 // (NEOX_ATTN_EXP selects).
 // DROP: dropout on the probabilities (the row sum stays that of the undropped softmax).
 template <int DP, int EXPV, bool DROP, int BN, int HALVES>
-__global__ void __launch_bounds__(att_threads(HALVES), HALVES == 1 ? 2 : 1)
+__global__ void __launch_bounds__(att_threads(HALVES), BN == 64 ? 2 : 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
-  static_assert((BN == 128 && HALVES == 2) || (BN == 64 && HALVES == 1), "a softmax thread owns 64 columns");
+  static_assert((BN == 128 && HALVES == 2) || BN == 64, "a softmax thread owns 64 columns, or 32 in the third shape");
+  constexpr int CPT = BN / HALVES;      // key columns of a block per softmax thread
+  constexpr int NC = CPT / 32;          // ... in 32-column TMEM loads
   constexpr int ATT_BN = BN;
   constexpr int ATT_THREADS = att_threads(HALVES);
-  constexpr uint32_t TMEM_COLS = HALVES == 2 ? 512 : 256;
+  constexpr uint32_t TMEM_COLS = BN == 128 ? 512 : 256;
   using L = AttnSmem<DP, BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -210,8 +213,10 @@ __global__ void __launch_bounds__(att_threads(HALVES), HALVES == 1 ? 2 : 1)
   const uint32_t tmem = *tmem_slot_gen;
   // S_j at T_S + j * BN; P_j (16 bit: BN / 2 columns) in its own columns (first shape) or over the first columns of
   // S_j (second shape: the thread that writes a row of P_j has read that row of S_j into registers before)
-  const uint32_t T_S = tmem, T_O = tmem + 2 * BN, T_P = HALVES == 2 ? tmem + 384 : tmem;
-  constexpr uint32_t P_STRIDE = HALVES == 2 ? BN / 2 : BN;
+  // (third shape, BN = 64 with two warps per lane quadrant: the second half row's P lands on columns the FIRST half
+  // row's thread reads; that thread has them in registers before it publishes its maximum, which the partner waits for)
+  const uint32_t T_S = tmem, T_O = tmem + 2 * BN, T_P = BN == 128 ? tmem + 384 : tmem;
+  constexpr uint32_t P_STRIDE = BN == 128 ? BN / 2 : BN;
   bool aborted = false;
 
   if (warp == 0) {
@@ -291,7 +296,7 @@ __global__ void __launch_bounds__(att_threads(HALVES), HALVES == 1 ? 2 : 1)
     // ------------------------------------------------------------------ softmax / epilogue
     const int quad = warp & 3;
     const int half = HALVES == 2 ? (warp - 2) >> 2 : 0;  // first shape: which 64 of the block's 128 key columns (and half of O)
-    const int col0 = half * 64;
+    const int col0 = half * CPT;
     const int r = quad * 32 + lane;  // row in tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     volatile unsigned long long* xch = reinterpret_cast<volatile unsigned long long*>(sgen + L::XCH_OFF);
@@ -333,9 +338,9 @@ __global__ void __launch_bounds__(att_threads(HALVES), HALVES == 1 ? 2 : 1)
       if (!mbar_wait(bar(S_FULL, st), ph, p.err, 18)) { aborted = true; break; }
       tc_fence_after_sync();
       // One read of the whole score row into registers.
-      uint32_t sv[2][32];
+      uint32_t sv[NC][32];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) tmem_ld_32x32b_x32(T_S + st * BN + col0 + c * 32 + lane_off, sv[c]);
+      for (int c = 0; c < NC; ++c) tmem_ld_32x32b_x32(T_S + st * BN + col0 + c * 32 + lane_off, sv[c]);
       tmem_ld_wait();
       // Does this block need per-element masking?  (warp-uniform decision)
       const bool need_mask = (k0 + ATT_BN > p.Sk) || (p.causal && k0 + ATT_BN - 1 > q0 + quad * 32 + off) ||
@@ -343,15 +348,15 @@ __global__ void __launch_bounds__(att_threads(HALVES), HALVES == 1 ? 2 : 1)
       const bool plain = !need_mask && p.alibi == nullptr;
       float mx;
       if (plain) {
-        mx = row_max_plain(sv) * p.scale_log2;
+        mx = row_max_plain<NC>(sv) * p.scale_log2;
       } else {
         // columns idx (0..127) of this block are alive for lo <= idx <= hi
         const int rel0 = k0 - qpos;
         int hi = p.Sk - k0 - 1;
         if (p.causal) hi = min(hi, -rel0);
         const int lo = p.window >= 0 ? -rel0 - p.window : -(1 << 30);
-        mx = p.alibi != nullptr ? prep_scores<true>(sv, p.scale_log2, slope2, rel0, lo, hi, col0, bits, p.blk_shift)
-                                : prep_scores<false>(sv, p.scale_log2, slope2, rel0, lo, hi, col0, bits, p.blk_shift);
+        mx = p.alibi != nullptr ? prep_scores<true, NC>(sv, p.scale_log2, slope2, rel0, lo, hi, col0, bits, p.blk_shift)
+                                : prep_scores<false, NC>(sv, p.scale_log2, slope2, rel0, lo, hi, col0, bits, p.blk_shift);
       }
       if (HALVES == 2) {
         // the row maximum over both column halves: both partners then take identical decisions
@@ -401,7 +406,7 @@ __global__ void __launch_bounds__(att_threads(HALVES), HALVES == 1 ? 2 : 1)
       const float2 sc2 = make_float2(plain ? p.scale_log2 : 1.f, plain ? p.scale_log2 : 1.f);
       const float2 nm2 = make_float2(-msub, -msub);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < NC; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
@@ -418,7 +423,7 @@ __global__ void __launch_bounds__(att_threads(HALVES), HALVES == 1 ? 2 : 1)
           }
           pk[j >> 1] = EXPV == 0 ? pack_h16x2(p0, p1) : pack_h16x2_alu(p0, p1);
         }
-        tmem_st_32x32b_x16(T_P + st * P_STRIDE + half * 32 + c * 16 + lane_off, pk);
+        tmem_st_32x32b_x16(T_P + st * P_STRIDE + half * (CPT / 2) + c * 16 + lane_off, pk);
       }
       const float2 rs01 = fadd2(fadd2(rs[0], rs[1]), fadd2(rs[2], rs[3]));
       const float rowsum = rs01.x + rs01.y;
@@ -532,9 +537,12 @@ NX_API int NX_SYM(nx_flash_attn_fwd)(const void* q, const void* k, const void* v
                  (reinterpret_cast<uintptr_t>(o) & 15) == 0,
              "flash_attn: output view must be 16-byte aligned");
   CUtensorMap tq, tk, tv;
-  static const int shape = [] {          // 2 (default): 64-key blocks, two CTAs per SM; 1: 128-key blocks, one CTA per SM
+  // 2 (default): 64-key blocks, four softmax warps, two CTAs per SM; 1: 128-key blocks, eight softmax warps, one CTA per
+  // SM; 3: 64-key blocks, eight softmax warps on 32-column half rows, two CTAs per SM
+  static const int shape = [] {
     const char* e = getenv("NEOX_ATTN_FWD_SHAPE");
-    return e != nullptr && atoi(e) == 1 ? 1 : 2;
+    const int v = e != nullptr ? atoi(e) : 2;
+    return v == 1 || v == 3 ? v : 2;
   }();
   const int bn = shape == 1 ? 128 : 64;
   if (!attn_map(&tq, q, B, H, Sq, D, q_sb, q_sh, q_ss, ATT_BM)) return NX_ERR_ARG;
@@ -576,7 +584,16 @@ NX_API int NX_SYM(nx_flash_attn_fwd)(const void* q, const void* k, const void* v
     }                                                                                                        \
     kern<<<grid, att_threads(HV), AttnSmem<DPV, BNV>::DYN, s>>>(tq, tk, tv, p);                              \
   } while (0)
-  if (shape == 2) {
+  if (shape == 3) {
+    if (drop) {
+      if (D <= 64) NX_ATTN_LAUNCH(64, 0, true, 64, 2);
+      else NX_ATTN_LAUNCH(128, 0, true, 64, 2);
+    } else if (D <= 64) {
+      NX_ATTN_LAUNCH(64, 0, false, 64, 2);
+    } else {
+      NX_ATTN_LAUNCH(128, 0, false, 64, 2);
+    }
+  } else if (shape == 2) {
     if (drop) {
       if (D <= 64) NX_ATTN_LAUNCH(64, 0, true, 64, 1);
       else NX_ATTN_LAUNCH(128, 0, true, 64, 1);

@@ -415,6 +415,24 @@ def test_flash_attention(cfg):
     assert rel(q.grad, qr.grad) < 3e-2 and rel(k.grad, kr.grad) < 3e-2 and rel(v.grad, vr.grad) < 3e-2
 
 
+@pytest.mark.parametrize("env", [{"NEOX_ATTN_FWD_SHAPE": "1"}, {"NEOX_ATTN_FWD_SHAPE": "3"},
+                                 {"NEOX_ATTN_BWD_WARPS": "4"}, {"NEOX_ATTN_DKV_PIPE": "0", "NEOX_ATTN_DQ_PIPE": "0"}],
+                         ids=["fwd_shape1", "fwd_shape3", "bwd_4warps", "bwd_unpipelined"])
+def test_flash_attention_selectable_kernel_shapes(env):
+    """The kernel shapes that an environment variable selects instead of the defaults (read once per process, hence a
+    child process): the dense, dropout and block-sparse cases of this file under each of them."""
+    import os
+    import subprocess
+    import sys
+    if "_dtype" in globals() and DT != torch.bfloat16:
+        pytest.skip("one operand type is enough for the shape selection")
+    cmd = [sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", os.path.abspath(__file__), "-k",
+           "(test_flash_attention or test_block_sparse_flash_attention) and not selectable and not varlen"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=dict(os.environ, **env))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout
+
+
 @pytest.mark.parametrize("kind,cfg,block,sq,sk", [
     ("sparse_fixed", {"num_local_blocks": 4, "num_global_blocks": 1}, 16, 640, 640),
     ("bigbird", {"num_sliding_window_blocks": 3, "num_global_blocks": 1, "num_random_blocks": 1}, 32, 512, 512),
