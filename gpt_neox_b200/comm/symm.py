@@ -11,6 +11,7 @@ address is passed to the kernels, which then use ``multimem`` reductions / store
 from __future__ import annotations
 
 import ctypes as C
+import heapq
 import os
 
 import torch
@@ -96,6 +97,7 @@ class SymmBackend:
         self.ag_calls = 0
         self.rs_calls = 0
         self.ar_calls = 0
+        self.pool = None                                      # gather-buffer pool: created by the first keep=True gather
         self.ar_count_off = self.ag_flag_off + (8 << 10)      # upper half of the all-gather flag area
         self.ar_target = 0
         dist.barrier(group)
@@ -115,18 +117,75 @@ class SymmBackend:
                 and m_full * n * 2 <= self.unit and (m_full // self.ws // 128) * ((n + 255) // 256) * self.ws * 16
                 <= (1 << 20))
 
+    # ------------------------------------------------------------------ pool of gather buffers that outlive a call
+    def _pool_create(self, slot_bytes: int):
+        """A second symmetric allocation, cut into equal slots: a gathered activation that the backward pass needs
+        again (the weight-gradient GEMM) stays where the peers pushed it instead of being copied out of the
+        two-deep gather ring.  Collective over the group (first ``ag_gemm(keep=True)``); every rank takes the same
+        decision.  NEOX_AG_POOL_GB sizes it (default 8, 0 = off)."""
+        import torch.distributed._symmetric_memory as symm_mem
+        self.pool = False
+        budget = int(float(os.environ.get("NEOX_AG_POOL_GB", "8")) * (1 << 30))
+        slot = (slot_bytes + 4095) // 4096 * 4096
+        n = min(budget // slot, 4096) if slot > 0 else 0
+        ok, buf, hdl = 1, None, None
+        if n < 2:
+            ok = 0
+        else:
+            try:
+                buf = symm_mem.empty(n * slot, dtype=torch.uint8, device=self.buf.device)
+                hdl = symm_mem.rendezvous(buf, self.group)
+            except Exception as e:  # noqa: BLE001 - any failure means "keep copying", decided collectively
+                print(f"gather-buffer pool unavailable ({type(e).__name__}: {e}); gathered activations are copied", flush=True)
+                ok = 0
+        flag = torch.tensor([ok], device=self.buf.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 1:
+            self.pool = {"buf": buf, "hdl": hdl, "slot": slot, "n": n, "free": list(range(n)),
+                         "ptrs": [int(p) for p in hdl.buffer_ptrs]}
+            heapq.heapify(self.pool["free"])
+
+    def pool_alloc(self, nbytes: int):
+        """Lowest free slot that holds ``nbytes``, or None (pool off, exhausted, or slots too small).  Every rank of the
+        group calls alloc / release / reset at the same points of the program, so all pick the same slot."""
+        if self.pool is None:
+            self._pool_create(nbytes)
+        if not self.pool or nbytes > self.pool["slot"] or not self.pool["free"]:
+            return None
+        return heapq.heappop(self.pool["free"])
+
+    def pool_release(self, slot):
+        if slot is not None and self.pool:
+            heapq.heappush(self.pool["free"], slot)
+
+    def pool_reset(self):
+        """Every slot free again (between optimizer steps no gathered activation is alive)."""
+        if self.pool:
+            self.pool["free"] = list(range(self.pool["n"]))
+
     def ag_gemm(self, x_shard, w, *, trans_b=False, bias=None, gelu=None, aux_out=None, dgelu_aux=None,
-                dgelu=None, aux_deriv=False):
+                dgelu=None, aux_deriv=False, keep=False):
         """``y = all_gather_rows(x_shard) @ op(w) (+ epilogue)``. Returns (y [M, N], gathered x [M, K]): the
-        gathered matrix is a view of the symmetric gather buffer, valid until the second next call."""
+        gathered matrix is a view of the symmetric gather buffer, valid until the second next call.  With
+        ``keep`` a third value is returned: a pool slot (or None if none was to be had); the gathered matrix then
+        lives in that slot until ``pool_release(slot)``.  A peer may push the next gather into a released slot as soon
+        as it has finished the fused call that follows the release in program order, so every read of the slot must be
+        enqueued BEFORE the first fused call after the release."""
         from ..ops import gemm as G
         ms, k = x_shard.shape
         m = ms * self.ws
         n = w.shape[1] if trans_b else w.shape[0]
-        par = self.ag_calls & 1
-        self.ag_calls += 1
-        goff = self.gather_off[par]
-        gathered = self.buf[goff:goff + m * k * 2].view(x_shard.dtype).view(m, k)
+        slot = self.pool_alloc(m * k * 2) if keep else None
+        if slot is not None:
+            so = slot * self.pool["slot"]
+            gathered = self.pool["buf"][so:so + m * k * 2].view(x_shard.dtype).view(m, k)
+            dst_table = (C.c_ulonglong * 8)(*([p + so for p in self.pool["ptrs"]] + [0] * (8 - self.ws)))
+        else:
+            par = self.ag_calls & 1
+            self.ag_calls += 1
+            goff = self.gather_off[par]
+            gathered = self.buf[goff:goff + m * k * 2].view(x_shard.dtype).view(m, k)
+            dst_table = self._table(goff)
         out = torch.empty((m, n), device=x_shard.device, dtype=x_shard.dtype)
         flags = 0
         ld_aux = 0
@@ -144,9 +203,9 @@ class SymmBackend:
         _lib.check(self._comm_gemm(m, x_shard)(
             _lib.ptr(gathered), _lib.ptr(w), _lib.ptr(out), m, n, k, k, w.stride(0), out.stride(0), int(trans_b),
             _lib.ptr(bias), _lib.ptr(dgelu_aux), _lib.ptr(aux_out), None, ld_aux, flags, 2, self.me, self.ws, epoch,
-            self._table(goff), self._table(self.ag_flag_off), None, 0, _lib.ptr(x_shard), x_shard.stride(0),
+            dst_table, self._table(self.ag_flag_off), None, 0, _lib.ptr(x_shard), x_shard.stride(0),
             _lib.stream()), "nx_gemm_bf16_comm(all-gather)")
-        return out, gathered
+        return (out, gathered, slot) if keep else (out, gathered)
 
     def gemm_rs(self, a, w, *, trans_b=False, residual=None, bias=None, residual2=None, dgelu_aux=None, dgelu=None):
         """``out = reduce_scatter_rows(a @ op(w) + residual) + bias + residual2`` -> [M / ws, N]."""
@@ -307,6 +366,12 @@ def backend_for(group):
 
 def reset():
     _BACKENDS.clear()
+
+
+def pool_reset_all():
+    """Free every slot of every group's gather-buffer pool (the engine calls this between optimizer steps)."""
+    for be in _BACKENDS.values():
+        be.pool_reset()
 
 
 class ZeroWorkspace:

@@ -874,6 +874,9 @@ class Engine(torch.nn.Module):
             for g in self.groups:
                 g.gather_params()
                 g.zero_grad()
+        if self.groups and self.groups[0].device.type == "cuda":
+            from ..comm import symm
+            symm.pool_reset_all()           # no gathered activation outlives the step: every gather-pool slot is free
         for m in self._fp8_modules():
             m.fp8_meta.roll()               # delayed scaling: this step's amax feeds the next steps' scales
         if overflow:

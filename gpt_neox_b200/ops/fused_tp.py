@@ -29,6 +29,20 @@ def backend(x, group):
     return symm.backend_for(group)
 
 
+def _keeps(ctx) -> bool:
+    """Ask for a pool slot only when a backward pass will come for it (the input gradient's fused reduce-scatter is
+    what makes the release safe, the weight gradient is what reads the slot)."""
+    return bool(ctx.needs_input_grad[0] and ctx.needs_input_grad[1])
+
+
+def _release(ctx):
+    """Give the gather slot of this node back.  A second backward pass over the same graph (``retain_graph``) would
+    read a slot that has been reused: the pooled form is for the single backward pass of training."""
+    slot, ctx.slot = getattr(ctx, "slot", None), None
+    if slot is not None:
+        ctx.be.pool_release(slot)
+
+
 def _rows(x):
     x2 = x.reshape(-1, x.shape[-1])
     return x2 if x2.is_contiguous() else x2.contiguous()
@@ -38,17 +52,20 @@ class _AGLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, w, b, be):
         x2 = _rows(x_shard)
-        y, gathered = be.ag_gemm(x2, w, bias=b)
-        ctx.save_for_backward(gathered.clone(), w)
-        ctx.be, ctx.has_bias, ctx.in_shape = be, b is not None, x_shard.shape
+        # the gathered operand is needed again by the weight-gradient GEMM: it stays in a pool slot of the symmetric
+        # workspace when one is free, else it is copied out of the two-deep gather ring
+        y, gathered, slot = be.ag_gemm(x2, w, bias=b, keep=_keeps(ctx))
+        ctx.save_for_backward(gathered if (slot is not None or not any(ctx.needs_input_grad)) else gathered.clone(), w)
+        ctx.be, ctx.has_bias, ctx.in_shape, ctx.slot = be, b is not None, x_shard.shape, slot
         return y.view(x_shard.shape[0] * be.ws, *x_shard.shape[1:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, gy):
         xf, w = ctx.saved_tensors
         gy2 = _rows(gy)
-        dx = ctx.be.gemm_rs(gy2, w, trans_b=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
         dw = wgrad(gy2, xf, w) if ctx.needs_input_grad[1] else None
+        _release(ctx)                  # after the last read of the slot, before the fused call below
+        dx = ctx.be.gemm_rs(gy2, w, trans_b=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
         db = colsum(gy2) if ctx.has_bias else None
         return dx, dw, db, None
 
@@ -80,8 +97,10 @@ class _MLPGeluSPFn(torch.autograd.Function):
         x2 = _rows(x_shard)
         m = x2.shape[0] * be.ws
         pre = torch.empty((m, w1.shape[0]), device=x2.device, dtype=x2.dtype)
-        h, gathered = be.ag_gemm(x2, w1, bias=b1, gelu=kind, aux_out=pre, aux_deriv=True)     # pre = gelu'(.)
-        xf = gathered.clone()
+        h, gathered, slot = be.ag_gemm(x2, w1, bias=b1, gelu=kind, aux_out=pre, aux_deriv=True,     # pre = gelu'(.)
+                                       keep=_keeps(ctx))
+        xf = gathered if (slot is not None or not any(ctx.needs_input_grad)) else gathered.clone()
+        ctx.slot = slot
         pf = _rows(partial_full) if partial_full is not None else None
         rs = _rows(res_shard) if res_shard is not None else None
         out = be.gemm_rs(h, w2, residual=pf, bias=bias_total, residual2=rs)
@@ -105,8 +124,9 @@ class _MLPGeluSPFn(torch.autograd.Function):
         # every rank adds bias_total to its own rows only; its gradient over ALL rows, divided by the
         # number of ranks that will each report it, keeps the sum over ranks exact
         d_bt = (colsum(g_full, torch.float32) / be.ws).to(g.dtype) if has_bt else None
-        dx = be.gemm_rs(dpre, w1, trans_b=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
         dw1 = wgrad(dpre, xf, w1) if ctx.needs_input_grad[1] else None
+        _release(ctx)                  # after the last read of the slot, before the fused call below
+        dx = be.gemm_rs(dpre, w1, trans_b=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
         db1 = colsum(dpre) if has_b1 else None
         return dx, dw1, db1, dw2, d_pf, d_bt, (g if has_rs else None), None, None
 

@@ -56,8 +56,9 @@ def main():
         calls = {k: getattr(tp_be, k, 0) for k in ("ag_calls", "rs_calls", "ar_calls")} if tp_be is not None else {}
         from gpt_neox_b200.ops import moe_ep
         buckets = int(getattr(model, "_ov_buckets", 0))
+        pool = getattr(tp_be, "pool", None) if tp_be is not None else None
         print("LOSSES " + json.dumps({"losses": losses, "device_error": err, "zero_symm": zs, "fused_calls": calls,
-                                      "overlap_buckets": buckets,
+                                      "overlap_buckets": buckets, "gather_pool_slots": pool["n"] if pool else 0,
                                       "moe_p2p": bool(moe_ep._WORKSPACES)}),
               flush=True)
     if torch.distributed.is_initialized():

@@ -31,6 +31,14 @@ def test_fused_tp2_sp_matches_nccl_baseline():
     assert base["device_error"] == 0 and fused["device_error"] == 0
     assert fused["losses"] == pytest.approx(base["losses"], rel=2e-2)
     assert fused["losses"][-1] < fused["losses"][0]
+    assert fused["gather_pool_slots"] > 0            # gathered activations stayed in pool slots (no copies)
+    # the same run with every flag signal delayed by a pseudo-random time, and with the gather pool switched off:
+    # neither the order in which peers arrive nor where the gathered operand is kept may change the numbers
+    jit = _run(2, "fused", 2, 1, 6, env={"NEOX_COMM_JITTER_NS": "30000"})
+    nopool = _run(2, "fused", 2, 1, 6, env={"NEOX_AG_POOL_GB": "0"})
+    assert jit["device_error"] == 0 and nopool["gather_pool_slots"] == 0
+    assert jit["losses"] == pytest.approx(fused["losses"], rel=2e-3)       # (fp32 atomics in the embedding backward
+    assert nopool["losses"] == pytest.approx(fused["losses"], rel=2e-3)    # make runs differ in the last bits)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
