@@ -201,7 +201,8 @@ class _FlashAttnFn(torch.autograd.Function):
         dq = torch.empty((b, sq, h, d), device=q.device, dtype=q.dtype)
         dk = torch.empty((b, sk, hk, d), device=q.device, dtype=q.dtype)
         dv = torch.empty((b, sk, hk, d), device=q.device, dtype=q.dtype)
-        delta = torch.zeros(lse.shape, device=q.device, dtype=torch.float32)
+        # (rows beyond the sequence exist only when it is not a multiple of the 128-row tile: only then a fill)
+        delta = (torch.empty if lse.shape[-1] == sq else torch.zeros)(lse.shape, device=q.device, dtype=torch.float32)
         LAUNCHES["n"] += 3
         rows, anyt, blk, _keep = _layout_args(ctx.layout, sq, sk, q.device)
         _lib.check(_lib.lib(q).nx_flash_attn_bwd(

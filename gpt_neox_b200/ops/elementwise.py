@@ -44,22 +44,40 @@ def _cuda_ok(x):
     return x.is_cuda and x.dtype in _lib.H16 and x.shape[-1] % 8 == 0
 
 
-def colsum(x2: torch.Tensor, out_dtype=None) -> torch.Tensor:
-    """Sum over rows of a 2-D bf16 tensor (bias gradient); fp32 accumulation."""
+def colsum(x2: torch.Tensor, out_dtype=None, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """Sum over rows of a 2-D bf16 tensor (bias gradient); fp32 accumulation.  ``out`` (fp32 or the input's dtype, N
+    contiguous elements) receives the sums, added to its contents with ``accumulate``."""
     if not x2.is_cuda:
-        return x2.float().sum(0).to(out_dtype or x2.dtype)
+        r = x2.float().sum(0)
+        if out is not None:
+            out.copy_(out.float() + r if accumulate else r)
+            return out
+        return r.to(out_dtype or x2.dtype)
     rows, N = x2.shape
     L = _lib.lib(x2)
     slabs = L.nx_colsum_slabs(rows)
     ws = torch.empty(slabs * N, device=x2.device, dtype=torch.float32)
-    out_dtype = out_dtype or x2.dtype
-    out = torch.empty(N, device=x2.device, dtype=out_dtype)
+    out_dtype = out.dtype if out is not None else (out_dtype or x2.dtype)
+    if out is None:
+        out = torch.empty(N, device=x2.device, dtype=out_dtype)
     LAUNCHES["n"] += 2
     _lib.check(L.nx_colsum_bf16(
         _lib.ptr(x2), _lib.ptr(out) if out_dtype == torch.float32 else None,
         _lib.ptr(out) if out_dtype == x2.dtype else None, _lib.ptr(ws), rows, N, x2.stride(0),
-        0, _lib.stream()), "nx_colsum_bf16")
+        1 if accumulate else 0, _lib.stream()), "nx_colsum_bf16")
     return out
+
+
+def bias_grad(x2: torch.Tensor, bias) -> torch.Tensor | None:
+    """Gradient of a bias that was added to every row: the column sum of ``x2``.  When the engine gave the bias a
+    fp32 ``main_grad`` the sum is added straight into it by the reduction kernel (returns None: nothing is left for
+    autograd to accumulate, convert and fold in later)."""
+    mg = getattr(bias, "main_grad", None)
+    if (mg is not None and x2.is_cuda and mg.dtype == torch.float32 and mg.is_contiguous()
+            and mg.numel() == x2.shape[1]):
+        colsum(x2, out=mg.view(-1), accumulate=True)
+        return None
+    return colsum(x2)
 
 
 class _BiasActFn(torch.autograd.Function):

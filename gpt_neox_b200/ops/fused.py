@@ -21,7 +21,7 @@ import torch.nn.functional as F
 from . import _lib
 from .attention import _fwd as _attn_fwd_launch
 from .attention import _strides_bhs, attention_reference
-from .elementwise import colsum
+from .elementwise import bias_grad, colsum
 from .gemm import LAUNCHES, gemm, wgrad
 from .rope import _launch as _rope_launch
 from .rope import apply_rotary
@@ -45,6 +45,7 @@ class _MLPGeluFn(torch.autograd.Function):
         ctx.kind, ctx.recompute_act = kind, recompute_act
         ctx.has_b1, ctx.has_b2, ctx.has_res = b1 is not None, b2 is not None, residual is not None
         ctx.x_shape = x.shape
+        ctx.biases = (b1, b2)           # the parameters themselves: their main_grad takes the bias gradients
         ctx.save_for_backward(x2, w1, b1, w2, pre, None if recompute_act else h)
         return y.view(*x.shape[:-1], w2.shape[0])
 
@@ -60,10 +61,10 @@ class _MLPGeluFn(torch.autograd.Function):
         # d(pre) = (gy @ W2) * gelu'(pre)   -- derivative applied in the GEMM epilogue
         dpre = gemm(gy2, w2, trans_b=True, dgelu_aux=pre, dgelu=ctx.kind if ctx.recompute_act else "mul")
         gw2 = wgrad(gy2, h, w2) if ctx.needs_input_grad[3] else None
-        gb2 = colsum(gy2) if (ctx.has_b2 and ctx.needs_input_grad[4]) else None
+        gb2 = bias_grad(gy2, ctx.biases[1]) if (ctx.has_b2 and ctx.needs_input_grad[4]) else None
         gx = gemm(dpre, w1, trans_b=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
         gw1 = wgrad(dpre, x2, w1) if ctx.needs_input_grad[1] else None
-        gb1 = colsum(dpre) if (ctx.has_b1 and ctx.needs_input_grad[2]) else None
+        gb1 = bias_grad(dpre, ctx.biases[0]) if (ctx.has_b1 and ctx.needs_input_grad[2]) else None
         gres = gy2.view(gy.shape) if ctx.has_res else None     # contiguous from here on down the stack
         return gx, gw1, gb1, gw2, gb2, gres, None, None
 
@@ -130,7 +131,8 @@ class _QKVAttentionFn(torch.autograd.Function):
         qb, kb, vb, dqb, dkb, dvb = map(perm, (q, k, v, dq, dk, dv))
         ob = perm(out)
         dob = perm(gout.view(s, b, np_, hn))
-        delta = torch.zeros(lse.shape, device=qkv.device, dtype=torch.float32)
+        # (rows beyond the sequence exist only when it is not a multiple of the 128-row tile: only then a fill)
+        delta = (torch.empty if lse.shape[-1] == s else torch.zeros)(lse.shape, device=qkv.device, dtype=torch.float32)
         LAUNCHES["n"] += 3
         _lib.check(_lib.lib(qkv).nx_flash_attn_bwd(
             _lib.ptr(qb), _lib.ptr(kb), _lib.ptr(vb), _lib.ptr(ob), _lib.ptr(dob), _lib.ptr(lse),

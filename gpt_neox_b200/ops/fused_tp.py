@@ -18,7 +18,7 @@ import torch
 
 from ..comm import collectives, symm
 from . import _lib
-from .elementwise import colsum
+from .elementwise import bias_grad, colsum
 from .gemm import wgrad
 
 
@@ -56,7 +56,7 @@ class _AGLinearFn(torch.autograd.Function):
         # workspace when one is free, else it is copied out of the two-deep gather ring
         y, gathered, slot = be.ag_gemm(x2, w, bias=b, keep=_keeps(ctx))
         ctx.save_for_backward(gathered if (slot is not None or not any(ctx.needs_input_grad)) else gathered.clone(), w)
-        ctx.be, ctx.has_bias, ctx.in_shape, ctx.slot = be, b is not None, x_shard.shape, slot
+        ctx.be, ctx.has_bias, ctx.in_shape, ctx.slot, ctx.bias = be, b is not None, x_shard.shape, slot, b
         return y.view(x_shard.shape[0] * be.ws, *x_shard.shape[1:-1], w.shape[0])
 
     @staticmethod
@@ -66,7 +66,7 @@ class _AGLinearFn(torch.autograd.Function):
         dw = wgrad(gy2, xf, w) if ctx.needs_input_grad[1] else None
         _release(ctx)                  # after the last read of the slot, before the fused call below
         dx = ctx.be.gemm_rs(gy2, w, trans_b=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
-        db = colsum(gy2) if ctx.has_bias else None
+        db = bias_grad(gy2, ctx.bias) if ctx.has_bias else None
         return dx, dw, db, None
 
 
@@ -77,7 +77,7 @@ class _LinearRSFn(torch.autograd.Function):
         r2 = _rows(res_shard) if res_shard is not None else None
         y = be.gemm_rs(x2, w, bias=b, residual2=r2)
         ctx.save_for_backward(x2, w)
-        ctx.be, ctx.has_bias, ctx.has_res = be, b is not None, res_shard is not None
+        ctx.be, ctx.has_bias, ctx.has_res, ctx.bias = be, b is not None, res_shard is not None, b
         ctx.x_shape = x.shape
         return y.view(x.shape[0] // be.ws, *x.shape[1:-1], w.shape[0])
 
@@ -87,7 +87,7 @@ class _LinearRSFn(torch.autograd.Function):
         g2 = _rows(gy)
         dx, g_full = ctx.be.ag_gemm(g2, w, trans_b=True)          # dX = all_gather(g) @ W
         dw = wgrad(g_full, x2, w) if ctx.needs_input_grad[1] else None
-        db = colsum(g2) if ctx.has_bias else None                 # partial over this rank's rows: the
+        db = bias_grad(g2, ctx.bias) if ctx.has_bias else None    # partial over this rank's rows: the
         return dx.view(ctx.x_shape), dw, db, (gy if ctx.has_res else None), None  # engine sums it over TP
 
 
@@ -107,6 +107,7 @@ class _MLPGeluSPFn(torch.autograd.Function):
         ctx.save_for_backward(xf, w1, w2, pre, h)
         ctx.be, ctx.kind = be, kind
         ctx.flags = (b1 is not None, partial_full is not None, bias_total is not None, res_shard is not None)
+        ctx.bias1 = b1
         ctx.in_shape = x_shard.shape
         ctx.pf_shape = partial_full.shape if partial_full is not None else None
         return out.view(x_shard.shape[:-1] + (w2.shape[0],))
@@ -127,7 +128,7 @@ class _MLPGeluSPFn(torch.autograd.Function):
         dw1 = wgrad(dpre, xf, w1) if ctx.needs_input_grad[1] else None
         _release(ctx)                  # after the last read of the slot, before the fused call below
         dx = be.gemm_rs(dpre, w1, trans_b=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
-        db1 = colsum(dpre) if has_b1 else None
+        db1 = bias_grad(dpre, ctx.bias1) if has_b1 else None
         return dx, dw1, db1, dw2, d_pf, d_bt, (g if has_rs else None), None, None
 
 
@@ -141,7 +142,7 @@ class _LinearARFn(torch.autograd.Function):
         x2 = _rows(x)
         y = be.gemm_ar(x2, w, bias=b).clone()
         ctx.save_for_backward(x2, w)
-        ctx.has_bias, ctx.x_shape = b is not None, x.shape
+        ctx.has_bias, ctx.x_shape, ctx.bias = b is not None, x.shape, b
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -151,7 +152,7 @@ class _LinearARFn(torch.autograd.Function):
         g2 = _rows(gy)
         dx = gemm(g2, w, trans_b=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
         dw = wgrad(g2, x2, w) if ctx.needs_input_grad[1] else None
-        db = colsum(g2) if ctx.has_bias else None
+        db = bias_grad(g2, ctx.bias) if ctx.has_bias else None
         return dx, dw, db, None
 
 

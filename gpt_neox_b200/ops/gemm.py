@@ -136,7 +136,7 @@ class _LinearFn(torch.autograd.Function):
         x2 = _as_2d(x)
         y = gemm(x2, weight, bias=bias)
         ctx.save_for_backward(x2, weight)
-        ctx.has_bias = bias is not None
+        ctx.has_bias, ctx.bias = bias is not None, bias
         ctx.x_shape = x.shape
         return y.view(*x.shape[:-1], weight.shape[0])
 
@@ -150,8 +150,8 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             gw = wgrad(gy2, x2, weight)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            from .elementwise import colsum
-            gb = colsum(gy2)
+            from .elementwise import bias_grad
+            gb = bias_grad(gy2, ctx.bias)
         return gx, gw, gb
 
 

@@ -53,6 +53,7 @@ class _NormFn(torch.autograd.Function):
         ctx.kind, ctx.dual, ctx.shape, ctx.carry = kind, dual, x.shape, carry
         ctx.has_beta = beta is not None
         ctx.has_beta2 = beta2 is not None
+        ctx.params = tuple(getattr(t, "_nx_param", None) for t in (gamma, beta, gamma2, beta2))
         ctx.save_for_backward(x2, gamma, gamma2, mean, rstd)
         outs = (y1.view(x.shape),) + ((y2.view(x.shape),) if dual else ())
         if carry:
@@ -85,16 +86,30 @@ class _NormFn(torch.autograd.Function):
             blocks = L.nx_norm_bwd_blocks(rows)
             ws = torch.empty(blocks * (4 if gb is not None else 2) * H, device=x2.device, dtype=torch.float32)
             dx = torch.empty_like(x2)
-            dga, dba = new(), (new() if hba else None)
-            dgb, dbb = (new() if gb is not None else None), (new() if hbb else None)
+            # parameter gradients: straight into the fp32 main_grad buffers (added by the partial-sum reduction
+            # kernel) when every parameter of this call has one, else into fresh buffers that autograd routes
+            owners = {id(gamma): ctx.params[0:2], id(gamma2): ctx.params[2:4]} if ctx.dual else {id(gamma): ctx.params[0:2]}
+            want = [owners[id(gma)][0]] + ([owners[id(gma)][1]] if hba else [])
+            if gb is not None:
+                want += [owners[id(gmb)][0]] + ([owners[id(gmb)][1]] if hbb else [])
+            mgs = [getattr(p_, "main_grad", None) if p_ is not None else None for p_ in want]
+            direct = all(m is not None and m.dtype == torch.float32 and m.is_contiguous() and m.numel() == H for m in mgs)
+            if direct:
+                it = iter(mgs)
+                dga, dba = next(it), (next(it) if hba else None)
+                dgb, dbb = (next(it) if gb is not None else None), (next(it) if (gb is not None and hbb) else None)
+            else:
+                dga, dba = new(), (new() if hba else None)
+                dgb, dbb = (new() if gb is not None else None), (new() if hbb else None)
             LAUNCHES["n"] += 2
             _lib.check(L.nx_norm_bwd(
                 ctx.kind, _lib.ptr(ga), _lib.ptr(gb), _lib.ptr(x2), _lib.ptr(mean), _lib.ptr(rstd),
                 _lib.ptr(gma), _lib.ptr(gmb), _lib.ptr(gres), _lib.ptr(dx), _lib.ptr(dga), _lib.ptr(dba),
-                _lib.ptr(dgb), _lib.ptr(dbb), _lib.ptr(ws), rows, H, 0, _lib.stream()), "nx_norm_bwd")
-            grads[id(gma)] = (dga, dba)
-            if gb is not None:
-                grads[id(gmb)] = (dgb, dbb)
+                _lib.ptr(dgb), _lib.ptr(dbb), _lib.ptr(ws), rows, H, 1 if direct else 0, _lib.stream()), "nx_norm_bwd")
+            if not direct:
+                grads[id(gma)] = (dga, dba)
+                if gb is not None:
+                    grads[id(gmb)] = (dgb, dbb)
         d1 = grads.get(id(gamma), (None, None))
         d2 = grads.get(id(gamma2), (None, None)) if ctx.dual else (None, None)
         return (None, dx.view(ctx.shape) if dx is not None else None, d1[0], d1[1], None, d2[0], d2[1], None)
@@ -107,15 +122,20 @@ class _ParamGrad(torch.autograd.Function):
     @staticmethod
     def forward(ctx, p):
         ctx.p = p
+        ctx.set_materialize_grads(False)      # no gradient arrives when the norm kernel wrote into main_grad itself
         return p.detach()
 
     @staticmethod
     def backward(ctx, g):
-        return _accum_param_grad(ctx.p, g)
+        return None if g is None else _accum_param_grad(ctx.p, g)
 
 
 def _wrap(p):
-    return None if p is None else (_ParamGrad.apply(p) if p.requires_grad else p)
+    if p is None or not p.requires_grad:
+        return p
+    w = _ParamGrad.apply(p)
+    w._nx_param = p          # the norm's backward adds into p.main_grad itself when it can (see _NormFn.backward)
+    return w
 
 
 def layer_norm(x, weight, bias=None, eps: float = 1e-5, carry: bool = False):

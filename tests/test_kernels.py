@@ -525,3 +525,33 @@ def test_device_error_word_roundtrip():
     with pytest.raises(_lib.DeviceWaitTimeout):
         _lib.raise_on_device_error()
     assert _lib.read_device_error(clear=False) == 0
+
+
+def test_bias_and_norm_gradients_accumulate_straight_into_main_grad():
+    """With an fp32 ``main_grad`` on the parameters (what the engine installs) the norm and bias-gradient kernels add
+    into it themselves: nothing reaches ``.grad``, and two backward passes leave twice the fp32 reference there."""
+    from gpt_neox_b200.ops.gemm import linear
+    from gpt_neox_b200.ops.norm import dual_layer_norm
+    torch.manual_seed(21)
+    rows, H, N = 640, 1024, 768
+    x = bf(rows, H, grad=True)
+    params = {"g1": (1 + 0.1 * torch.randn(H, device=DEV)).to(DT), "b1": bf(H, scale=0.1), "g2": (1 + 0.1 * torch.randn(H, device=DEV)).to(DT),
+              "b2": bf(H, scale=0.1), "w": bf(N, H, scale=0.05), "b": bf(N, scale=0.1)}
+    for p in params.values():
+        p.requires_grad_(True)
+        p.main_grad = torch.zeros(p.shape, device=DEV, dtype=torch.float32)
+    g = bf(rows, N)
+    g2 = bf(rows, H)
+    for _ in range(2):
+        y1, y2 = dual_layer_norm(x, params["g1"], params["b1"], params["g2"], params["b2"], 1e-5)
+        out = linear(y1, params["w"], params["b"])
+        torch.autograd.backward([out, y2], [g, g2])
+    ref = {k: v.detach().float().requires_grad_(True) for k, v in params.items()}
+    xr = x.detach().float().requires_grad_(True)
+    r1 = F.layer_norm(xr, (H,), ref["g1"], ref["b1"], 1e-5)
+    r2 = F.layer_norm(xr, (H,), ref["g2"], ref["b2"], 1e-5)
+    ro = F.linear(r1.to(DT).float(), ref["w"], ref["b"])
+    torch.autograd.backward([ro, r2], [g.float(), g2.float()])
+    for k, p in params.items():
+        assert p.grad is None, k
+        assert rel(p.main_grad, 2 * ref[k].grad) < 2e-2, k
