@@ -141,3 +141,125 @@ def dequantize_reference(q8, scale, e5m2=False):
     """uint8 fp8 bit patterns -> fp32 values / scale (test helper)."""
     dt = torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn
     return q8.view(dt).float() / scale
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Block-scaled fp8 (MXFP8): one power-of-two scale per 32 consecutive elements of a row, applied by the tensor core
+# (csrc/gemm_mxfp8_tcgen05.cu).  No amax history and no per-tensor scale: every tensor is quantised from its own
+# values when it is used.  Scale layout: uint32 words [ceil(cols / 128)][rows padded to 128], word = the ue8m0 bytes of
+# four consecutive 32-element groups of one row.
+# ---------------------------------------------------------------------------------------------------------------
+def _pad128(n: int) -> int:
+    return (n + 127) // 128 * 128
+
+
+def mxfp8_quantize(x2: torch.Tensor, e5m2: bool = False):
+    """16-bit [rows, cols] (cols % 32 == 0) -> (fp8 bytes [rows, cols] uint8, scale words [ceil(cols/128), pad128(rows)]
+    int32)."""
+    rows, cols = x2.shape
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    out = torch.empty((rows, cols), device=x2.device, dtype=torch.uint8)
+    sf = torch.full(((cols + 127) // 128, _pad128(rows)), 0x7F7F7F7F, device=x2.device, dtype=torch.int32)
+    LAUNCHES["n"] += 1
+    _lib.check(_lib.lib(x2).nx_mxfp8_quantize(_lib.ptr(x2), x2.stride(0), _lib.ptr(out), cols, _lib.ptr(sf), sf.stride(0),
+                                              rows, cols, int(e5m2), _lib.stream()), "nx_mxfp8_quantize")
+    return out, sf
+
+
+def mxfp8_quantize_reference(x2: torch.Tensor, e5m2: bool = False):
+    """The quantiser in plain PyTorch (any device): same bytes and scale words as the kernel."""
+    rows, cols = x2.shape
+    fmax = E5M2_MAX if e5m2 else E4M3_MAX
+    g = x2.float().reshape(rows, cols // 32, 32)
+    amax = g.abs().amax(-1)
+    mant, ex = torch.frexp(amax / fmax)                                   # amax / fmax = mant * 2^ex, mant in [0.5, 1)
+    e = torch.where(mant == 0.5, ex - 1, ex).clamp(-127, 127)             # ceil(log2(.))
+    e = torch.where(amax > 0, e, torch.zeros_like(e))
+    q = (g * torch.exp2(-e.float()).unsqueeze(-1)).clamp(-fmax, fmax)
+    q8 = q.to(torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn).view(torch.uint8).reshape(rows, cols)
+    nkb = (cols + 127) // 128
+    by = torch.full((nkb, _pad128(rows), 4), 127, dtype=torch.int32, device=x2.device)
+    eb = (e + 127).to(torch.int32)                                        # [rows, groups]
+    ngr = cols // 32
+    padded = torch.full((rows, nkb * 4), 127, dtype=torch.int32, device=x2.device)
+    padded[:, :ngr] = eb
+    by[:, :rows, :] = padded.reshape(rows, nkb, 4).permute(1, 0, 2)
+    words = by[..., 0] | (by[..., 1] << 8) | (by[..., 2] << 16) | (by[..., 3] << 24)
+    return q8, words.to(torch.int32)
+
+
+def mxfp8_dequantize_reference(q8: torch.Tensor, sf: torch.Tensor, e5m2: bool = False) -> torch.Tensor:
+    """fp8 bytes + scale words -> fp32 values (test helper)."""
+    rows, cols = q8.shape
+    vals = q8.view(torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn).float()
+    nkb = sf.shape[0]
+    w = sf[:, :rows].to(torch.int64) & 0xFFFFFFFF                         # [nkb, rows]
+    by = torch.stack([(w >> (8 * i)) & 0xFF for i in range(4)], dim=-1)   # [nkb, rows, 4]
+    e = (by.permute(1, 0, 2).reshape(rows, nkb * 4)[:, :cols // 32] - 127).float()
+    return (vals.reshape(rows, cols // 32, 32) * torch.exp2(e).unsqueeze(-1)).reshape(rows, cols)
+
+
+def gemm_mxfp8(a8, sfa, b8, sfb, *, a_e5m2=False, b_e5m2=False, bias=None, out=None, accumulate=False, alpha=None,
+               out_dtype=torch.bfloat16, sf_layout: int = 0):
+    """C[M,N] = (a8 with its block scales)[M,K] @ (b8 with its block scales)[N,K]^T (+ bias); 16-bit result, or fp32 into
+    ``out`` (optionally +=)."""
+    M, K = a8.shape
+    N = b8.shape[0]
+    out_f32 = out is not None and out.dtype == torch.float32
+    if out is None:
+        out = torch.empty((M, N), device=a8.device, dtype=out_dtype)
+    like = out if not out_f32 else (bias if bias is not None else torch.empty(0, dtype=out_dtype))
+    LAUNCHES["n"] += 1
+    _lib.check(_lib.lib(like).nx_gemm_mxfp8(_lib.ptr(a8), _lib.ptr(b8), _lib.ptr(out), M, N, K, a8.stride(0), b8.stride(0),
+                                            out.stride(0), _lib.ptr(sfa), _lib.ptr(sfb), sfa.stride(0), sfb.stride(0),
+                                            int(a_e5m2), int(b_e5m2), _lib.ptr(alpha), _lib.ptr(bias), int(out_f32),
+                                            int(accumulate), int(sf_layout), _lib.stream()), "nx_gemm_mxfp8")
+    return out
+
+
+class _MxFp8LinearFn(torch.autograd.Function):
+    """y = x W^T (+ b) with all three GEMMs block-scaled.  Every GEMM contracts over the dimension its operands were
+    quantised along: forward x [M,K] and W [N,K] along K; input gradient dY [M,N] and W^T [K,N] along N; weight
+    gradient dY^T [N,M] and x^T [K,M] along M (the transposed copies are made before quantising, since the scale
+    blocks run along the contracted dimension)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, hybrid):
+        x2 = x.reshape(-1, x.shape[-1])
+        x8, sx = mxfp8_quantize(x2)
+        w8, sw = mxfp8_quantize(weight)
+        y = gemm_mxfp8(x8, sx, w8, sw, bias=bias, out_dtype=x.dtype)
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias, ctx.x_shape, ctx.hybrid = bias is not None, x.shape, hybrid
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, weight = ctx.saved_tensors
+        g2 = gy.reshape(-1, gy.shape[-1])
+        e5 = bool(ctx.hybrid)
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            g8, sg = mxfp8_quantize(g2, e5m2=e5)
+            wt8, swt = mxfp8_quantize(weight.t().contiguous())
+            gx = gemm_mxfp8(g8, sg, wt8, swt, a_e5m2=e5, out_dtype=gy.dtype).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            gt8, sgt = mxfp8_quantize(g2.t().contiguous(), e5m2=e5)
+            xt8, sxt = mxfp8_quantize(x2.t().contiguous())
+            mg = getattr(weight, "main_grad", None)
+            if mg is not None and mg.dtype == torch.float32:
+                gemm_mxfp8(gt8, sgt, xt8, sxt, a_e5m2=e5, out=mg, accumulate=True, out_dtype=gy.dtype)
+            else:
+                gw = gemm_mxfp8(gt8, sgt, xt8, sxt, a_e5m2=e5, out_dtype=gy.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            from .elementwise import colsum
+            gb = colsum(g2.contiguous())
+        return gx, gw, gb, None
+
+
+def mxfp8_linear(x, weight, bias=None, hybrid: bool = True):
+    """``F.linear`` on block-scaled fp8 tensor-core GEMMs (tokens, in and out features multiples of 32)."""
+    if not (x.is_cuda and x.dtype in _lib.H16):
+        raise _lib.KernelError("mxfp8_linear needs CUDA bf16 / fp16 activations")
+    return _MxFp8LinearFn.apply(x, weight, bias, hybrid)

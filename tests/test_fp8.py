@@ -97,3 +97,107 @@ def test_fp8_model_loss_tracks_bf16_model():
     g1 = dict(models[1].named_parameters())["sequential.2.mlp.linear1.weight"].grad.float()
     assert ((g0 - g1).norm() / g0.norm()).item() < 0.2
     assert any(getattr(m, "fp8_meta", None) is not None for m in models[1].modules())
+
+
+# ------------------------------------------------------------------------------------------------ block-scaled (MXFP8)
+@pytest.mark.parametrize("rows,cols,e5m2", [(300, 416, False), (128, 128, True), (5, 32, False), (1000, 4096, False)])
+def test_mxfp8_quantiser_matches_the_pytorch_statement(rows, cols, e5m2):
+    """One power-of-two scale per 32 elements of a row (the smallest that brings the group into range), values
+    converted with saturation, scale bytes packed four to a word per 128-column block: bytes and words equal the
+    PyTorch statement bit for bit."""
+    from gpt_neox_b200.ops import fp8
+    torch.manual_seed(0)
+    x = (torch.randn(rows, cols, device="cuda") * (torch.rand(rows, 1, device="cuda") * 40)).bfloat16()
+    x[0, :32] = 0                                              # an all-zero group keeps scale 1
+    x[-1, -32:] = 448.0 if not e5m2 else 57344.0               # exactly the format maximum: scale 1, no saturation
+    q, sf = fp8.mxfp8_quantize(x, e5m2=e5m2)
+    qr, sfr = fp8.mxfp8_quantize_reference(x, e5m2=e5m2)
+    assert torch.equal(sf, sfr)
+    assert torch.equal(q, qr)
+    back = fp8.mxfp8_dequantize_reference(q, sf, e5m2=e5m2)
+    tol = 2.0 ** -3 if e5m2 else 2.0 ** -4                      # half a unit of the last mantissa bit, relative
+    assert ((back - x.float()).abs() <= tol * x.float().abs().reshape(rows, -1, 32).amax(-1, keepdim=True)
+            .expand(rows, cols // 32, 32).reshape(rows, cols) + 1e-30).all()
+
+
+def _sf_words(e):
+    """exponents [rows, groups] -> scale words in the kernels' layout."""
+    from gpt_neox_b200.ops import fp8
+    rows, ngr = e.shape
+    nkb = (ngr + 3) // 4
+    pad = torch.full((rows, nkb * 4), 127, dtype=torch.int32, device=e.device)
+    pad[:, :ngr] = e + 127
+    by = torch.full((nkb, fp8._pad128(rows), 4), 127, dtype=torch.int32, device=e.device)
+    by[:, :rows, :] = pad.reshape(rows, nkb, 4).permute(1, 0, 2)
+    return (by[..., 0] | (by[..., 1] << 8) | (by[..., 2] << 16) | (by[..., 3] << 24)).to(torch.int32)
+
+
+@pytest.mark.parametrize("pattern", ["unit", "a_rows", "a_kgroups", "b_rows", "b_kgroups", "random"])
+def test_mxfp8_gemm_applies_every_scale_where_it_belongs(pattern):
+    """Scale factors that vary only along one axis of one operand pin down the tensor-memory layout the kernel
+    stages them in: each pattern must reproduce the fp32 product of the de-scaled operands."""
+    from gpt_neox_b200.ops import _lib, fp8
+    torch.manual_seed(2)
+    M, N, K = 384, 256, 512
+    a = torch.randn(M, K, device="cuda").clamp(-3, 3).to(torch.float8_e4m3fn)
+    b = torch.randn(N, K, device="cuda").clamp(-3, 3).to(torch.float8_e4m3fn)
+    g = K // 32
+    ea = torch.zeros(M, g, dtype=torch.int32, device="cuda")
+    eb = torch.zeros(N, g, dtype=torch.int32, device="cuda")
+    rows = lambda n: (torch.arange(n, device="cuda", dtype=torch.int32) % 7 - 3).unsqueeze(1).expand(n, g).contiguous()   # noqa: E731
+    kgr = lambda n: (torch.arange(g, device="cuda", dtype=torch.int32) % 5 - 2).unsqueeze(0).expand(n, g).contiguous()   # noqa: E731
+    if pattern == "a_rows":
+        ea = rows(M)
+    elif pattern == "a_kgroups":
+        ea = kgr(M)
+    elif pattern == "b_rows":
+        eb = rows(N)
+    elif pattern == "b_kgroups":
+        eb = kgr(N)
+    elif pattern == "random":
+        ea = torch.randint(-4, 5, (M, g), device="cuda", dtype=torch.int32)
+        eb = torch.randint(-4, 5, (N, g), device="cuda", dtype=torch.int32)
+    ref = (a.float().reshape(M, g, 32) * torch.exp2(ea.float()).unsqueeze(-1)).reshape(M, K) @ \
+          (b.float().reshape(N, g, 32) * torch.exp2(eb.float()).unsqueeze(-1)).reshape(N, K).t()
+    out = fp8.gemm_mxfp8(a.view(torch.uint8), _sf_words(ea), b.view(torch.uint8), _sf_words(eb))
+    torch.cuda.synchronize()
+    assert _lib.read_device_error() == 0
+    torch.testing.assert_close(out.float(), ref, rtol=1e-2, atol=ref.abs().max().item() * 4e-3)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (200, 136, 160), (1024, 768, 2048), (130, 8, 32)])
+def test_mxfp8_gemm_matches_dequantised_matmul(M, N, K):
+    from gpt_neox_b200.ops import fp8
+    torch.manual_seed(3)
+    a = (torch.randn(M, K, device="cuda") * (1 + 10 * torch.rand(M, 1, device="cuda"))).bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    a8, sa = fp8.mxfp8_quantize(a)
+    b8, sb = fp8.mxfp8_quantize(b, e5m2=True)
+    bias = torch.randn(N, device="cuda").bfloat16()
+    got = fp8.gemm_mxfp8(a8, sa, b8, sb, b_e5m2=True, bias=bias)
+    want = fp8.mxfp8_dequantize_reference(a8, sa) @ fp8.mxfp8_dequantize_reference(b8, sb, True).t() + bias.float()
+    torch.testing.assert_close(got.float(), want, rtol=1e-2, atol=want.abs().max().item() * 4e-3)
+    acc = torch.ones(M, N, device="cuda")
+    fp8.gemm_mxfp8(a8, sa, b8, sb, b_e5m2=True, out=acc, accumulate=True)
+    torch.testing.assert_close(acc, want - bias.float() + 1.0, rtol=1e-3, atol=want.abs().max().item() * 1e-4)
+    # against the unquantised product: the error of block-scaled e4m3 x e5m2 operands
+    exact = a.float() @ b.float().t()
+    assert ((got.float() - bias.float() - exact).norm() / exact.norm()).item() < 0.08
+
+
+def test_mxfp8_linear_tracks_16_bit_linear():
+    """Forward, input gradient and weight gradient of the block-scaled linear against the fp32 statement."""
+    from gpt_neox_b200.ops import fp8
+    torch.manual_seed(4)
+    x = torch.randn(4, 96, 512, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(768, 512, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    b = torch.randn(768, device="cuda").bfloat16().requires_grad_(True)
+    y = fp8.mxfp8_linear(x, w, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    nerr = lambda u, v: ((u.float() - v).norm() / v.norm()).item()   # noqa: E731
+    assert nerr(y, yr) < 0.06 and nerr(x.grad, xr.grad) < 0.12 and nerr(w.grad, wr.grad) < 0.12
+    assert nerr(b.grad, br.grad) < 1e-2
