@@ -49,6 +49,8 @@ def parse():
     p.add_argument("--fp8", action="store_true",
                    help="run the linear layers' GEMMs (forward, dgrad, wgrad) on the fp8 tensor cores with delayed "
                         "scaling; reported under dtype 'fp8' and never as the bf16 headline")
+    p.add_argument("--fp8-recipe", type=str, default="delayed", choices=("delayed", "mxfp8"),
+                   help="with --fp8: per-tensor delayed scaling, or block scaling (one power-of-two scale per 32 elements)")
     p.add_argument("--kernel-table", type=str, default=None,
                    help="after the timed regions, run one more (untimed) step under torch.profiler and write the "
                         "per-kernel device-time table of rank 0 to this file")
@@ -321,7 +323,7 @@ def main():
         over["moe_expert_parallel_size"] = n
     if args.fp8:
         over.update(te_columnparallel=True, te_rowparallel=True, te_fp8_amax_history_len=16,
-                    te_fp8_amax_compute_algo="max")
+                    te_fp8_amax_compute_algo="max", te_fp8_recipe=args.fp8_recipe)
         if tp > 1:
             over["comm_mode"] = "nccl_baseline"      # the fused AG/RS GEMM kernels are bf16
     neox_args = NeoXArgs.from_ymls([os.path.join(REPO, "configs", "bench", args.model + ".yml")], overwrite_values=over)
@@ -429,7 +431,7 @@ def main():
             tflops += extra / (dev_ms / 1000.0) / n / 1e12
         out = {"metric": "tokens_per_sec", "value": tps, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
                "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak",
-               "vs_baseline": None, "dtype": "fp8" if args.fp8 else "bf16", "data": "synthetic tokens, random-init weights",
+               "vs_baseline": None, "dtype": ("fp8" if args.fp8_recipe == "delayed" else "mxfp8") if args.fp8 else "bf16", "data": "synthetic tokens, random-init weights",
                "tflops_per_gpu": tflops, "impl": "ours", "mode": args.mode,
                "config": {"model": args.model, "global_batch": global_batch, "seq_len": seq, "micro_batch": micro,
                           "grad_accum": gas,

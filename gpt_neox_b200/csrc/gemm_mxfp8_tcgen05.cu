@@ -15,9 +15,11 @@
 // Four warps bring the words of a K block to tensor memory (tcgen05.st, each warp its own lane quarter) one ring
 // stage ahead of the MMA warp.
 //
-// Pipeline: one persistent CTA per SM, 128 x 128 tiles; warp 0 issues TMA loads into a 6-stage shared-memory ring
-// (128-byte swizzle: a row of a tile is 128 fp8 values), warp 1 issues the MMAs, warps 2-5 drain the two TMEM
-// accumulators, warps 6-9 stage the scale factors.  TMEM: accumulators [0,256), scale stages [256, 256 + 8 * 6).
+// Pipeline: one persistent CTA per SM, 128 x BN tiles; warp 0 issues TMA loads into a shared-memory ring
+// (128-byte swizzle: a row of a tile is 128 fp8 values), warp 1 issues the MMAs, warps 2-5 drain the TMEM
+// accumulators, warps 6-9 stage the scale factors.  TMEM: accumulator stages [0, NACC * BN), then 16 columns per ring
+// stage for the scale cells.  The accumulators cannot be 2 x 256 columns as in the per-tensor kernel (the scale cells
+// need room), so the tile is 128 x 256 with one accumulator stage (the default: fastest as measured) or narrower with two.
 //
 // Plus the quantiser: 16-bit -> fp8 with one scale per 32 elements of a row, emitted in the layout above.
 #include <cuda_fp8.h>
@@ -28,13 +30,23 @@
 namespace nx {
 
 namespace mx {
-constexpr int BM = 128, BN = 128, BK = 128, UK = 32, STAGES = 6, THREADS = 320;
-constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-constexpr int NBAR = 3 * STAGES + 4;
-constexpr int DYN_BYTES = BAR_OFFSET + NBAR * 8 + 16 + 1024;
-constexpr uint32_t SF_COL0 = 2 * BN;      // first scale-factor column
+constexpr int BM = 128, BK = 128, UK = 32, THREADS = 320;
 constexpr uint32_t TMEM_COLS = 512;
+constexpr int SF_STRIDE = 16;             // TMEM columns per scale stage: A in 0..3, B in 4..4 + BN / 32
+// Tile shapes.  BN columns per tile, NACC accumulator stages, ring stages such that the TMEM columns
+// (NACC * BN + 16 per stage) fit 512 and the operand ring fits shared memory.
+template <int BN_, int NACC_, int STAGES_>
+struct Cfg {
+  static constexpr int BN = BN_, NACC = NACC_, STAGES = STAGES_;
+  static constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int NBAR = 3 * STAGES + 4;
+  static constexpr int DYN_BYTES = BAR_OFFSET + NBAR * 8 + 16 + 1024;
+  static constexpr uint32_t SF_COL0 = NACC * BN;      // first scale-factor column
+  static_assert(NACC * BN + STAGES * SF_STRIDE <= 512, "tensor memory");
+  static_assert(DYN_BYTES <= 227 * 1024, "shared memory");
+  static_assert(BN % 32 == 0 && BN <= 256 && 4 + BN / 32 <= SF_STRIDE, "tile width");
+};
 }  // namespace mx
 
 struct MxGemmParams {
@@ -49,8 +61,6 @@ struct MxGemmParams {
   int out_f32, accumulate;
   int tiles_m, tiles_n;
   uint32_t idesc;
-  int sf_layout;                    // 0: the layout described above; 1: cell (lane l) = the word of tile row l in
-                                    // every column (kept for bring-up comparisons)
   int* err;
 };
 
@@ -66,24 +76,22 @@ __device__ __forceinline__ void umma_mxf8_ss(uint32_t tmem_d, uint64_t adesc, ui
       : "memory");
 }
 
-__device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t (&r)[8]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
-               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-               : "memory");
-}
-
 // Block-scaled instruction descriptor: scale-factor id of B at bits [4,6), a / b format at bits 7 / 10 (0 = e4m3,
 // 1 = e5m2), both K-major, N >> 3 at bit 17, scale type at bit 23 (1 = ue8m0), M >> 4 at bit 24, scale-factor id of
 // A at bits [29,31).  The ids (which of the four bytes of a scale cell a K step uses) are or-ed in per instruction.
-static uint32_t idesc_mxf8(int a_e5m2, int b_e5m2) {
+static uint32_t idesc_mxf8(int a_e5m2, int b_e5m2, int bn) {
   return (static_cast<uint32_t>(a_e5m2) << 7) | (static_cast<uint32_t>(b_e5m2) << 10) |
-         (static_cast<uint32_t>(mx::BN >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(mx::BM >> 4) << 24);
+         (static_cast<uint32_t>(bn >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(mx::BM >> 4) << 24);
 }
 
+template <class C>
 __global__ void __launch_bounds__(mx::THREADS, 1)
     gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const MxGemmParams p) {
   using namespace mx;
+  constexpr int BN = C::BN, NACC = C::NACC, STAGES = C::STAGES, A_BYTES = C::A_BYTES, STAGE_BYTES = C::STAGE_BYTES,
+                BAR_OFFSET = C::BAR_OFFSET, NBAR = C::NBAR;
+  constexpr uint32_t SF_COL0 = C::SF_COL0;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -103,7 +111,7 @@ __global__ void __launch_bounds__(mx::THREADS, 1)
       mbar_init(empty_bar(s), 1);
       mbar_init(sf_full_bar(s), 4);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < NACC; ++a) {
       mbar_init(tmem_full_bar(a), 1);
       mbar_init(tmem_empty_bar(a), 4);
     }
@@ -168,7 +176,7 @@ __global__ void __launch_bounds__(mx::THREADS, 1)
           tc_fence_after_sync();
           const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
           const uint32_t b_addr = a_addr + A_BYTES;
-          const uint32_t t_sfa = tmem_base + SF_COL0 + stage * 8, t_sfb = t_sfa + 4;
+          const uint32_t t_sfa = tmem_base + SF_COL0 + stage * SF_STRIDE, t_sfb = t_sfa + 4;
 #pragma unroll
           for (int k = 0; k < BK / UK; ++k) {
             // K-major, 128-byte swizzle: 8-row groups 1024 B apart; 32 fp8 K-elements advance 32 B; K step k uses
@@ -186,7 +194,7 @@ __global__ void __launch_bounds__(mx::THREADS, 1)
         }
         if (aborted) break;
         umma_commit(tmem_full_bar(acc));
-        if (++acc == 2) {
+        if (++acc == NACC) {
           acc = 0;
           acc_phase ^= 1;
         }
@@ -201,30 +209,24 @@ __global__ void __launch_bounds__(mx::THREADS, 1)
       const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
       const long long m0 = static_cast<long long>(tm) * BM, n0 = static_cast<long long>(tn) * BN;
       for (int kb = 0; kb < num_kb; ++kb) {
-        uint32_t w[8];
-        const uint32_t* ra = p.sfa + kb * p.ld_sfa + m0;
-        const uint32_t* rb = p.sfb + kb * p.ld_sfb + n0;
-        if (p.sf_layout == 0) {
+        // cell (lane l, column c) = the scale word of tile row 32 c + l: A in columns 0..3, B in 4..4 + BN / 32; rows past
+        // the padded end of the scale array (a tile width that is not a multiple of 128) re-read its last word: the
+        // operand rows there are zero-filled by TMA and their outputs are never stored
+        uint32_t w[16];
+        const uint32_t* ra = p.sfa + kb * p.ld_sfa;
+        const uint32_t* rb = p.sfb + kb * p.ld_sfb;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            w[c] = __ldg(ra + 32 * c + lane);
-            w[4 + c] = __ldg(rb + 32 * c + lane);
-          }
-        } else {
-          const uint32_t wa = __ldg(ra + quad * 32 + lane), wb = __ldg(rb + quad * 32 + lane);
+        for (int c = 0; c < 4; ++c) w[c] = __ldg(ra + min(m0 + 32 * c + lane, p.ld_sfa - 1));
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            w[c] = wa;
-            w[4 + c] = wb;
-          }
-        }
+        for (int c = 0; c < 12; ++c)
+          w[4 + c] = c < BN / 32 ? __ldg(rb + min(n0 + 32 * c + lane, p.ld_sfb - 1)) : 0x7f7f7f7fu;
         bool ok = mbar_wait(empty_bar(stage), phase ^ 1, p.err, 75);
         if (!__all_sync(0xffffffffu, ok)) {
           aborted = true;
           break;
         }
         tc_fence_after_sync();
-        tmem_st_32x32b_x8(tmem_base + SF_COL0 + stage * 8 + (static_cast<uint32_t>(quad * 32) << 16), w);
+        tmem_st_32x32b_x16(tmem_base + SF_COL0 + stage * SF_STRIDE + (static_cast<uint32_t>(quad * 32) << 16), w);
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
@@ -307,7 +309,7 @@ __global__ void __launch_bounds__(mx::THREADS, 1)
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
-      if (++acc == 2) {
+      if (++acc == NACC) {
         acc = 0;
         acc_phase ^= 1;
       }
@@ -325,13 +327,37 @@ __global__ void __launch_bounds__(mx::THREADS, 1)
   }
 }
 
+namespace mx {
+template <class C>
+static int launch(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, MxGemmParams p,
+                  int a_e5m2, int b_e5m2, cudaStream_t stream) {
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + C::BN - 1) / C::BN;
+  p.idesc = idesc_mxf8(a_e5m2, b_e5m2, C::BN);
+  CUtensorMap tmA, tmB;
+  if (!make_tma_2d(&tmA, A, M, K, lda, BM, BK, 1)) return NX_ERR_ARG;
+  if (!make_tma_2d(&tmB, B, N, K, ldb, C::BN, BK, 1)) return NX_ERR_ARG;
+  static bool configured = false;
+  if (!configured) {
+    NX_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::DYN_BYTES));
+    configured = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_mxfp8_kernel<C><<<grid, THREADS, C::DYN_BYTES, stream>>>(tmA, tmB, p);
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+}  // namespace mx
+
 // A [M, K] and B [N, K]: fp8 bytes, leading dimensions in elements (multiples of 16); sfa / sfb: scale words
 // [ceil(K / 128)][ld_sf*] with ld_sfa >= round_up(M, 128), ld_sfb >= round_up(N, 128) (padding rows hold 0x7f7f7f7f);
 // a_e5m2 / b_e5m2 select the operand formats.  C: 16-bit [M, N] or fp32 (out_f32; accumulate adds into it).
+// tile: 0 = chosen here; 128 / 192 / 224 / 256 = that tile width (256: one accumulator stage).
 NX_API int NX_SYM(nx_gemm_mxfp8)(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                                  long long ldb, long long ldc, const void* sfa, const void* sfb, long long ld_sfa,
                                  long long ld_sfb, int a_e5m2, int b_e5m2, const void* alpha, const void* bias,
-                                 int out_f32, int accumulate, int sf_layout, cudaStream_t stream) {
+                                 int out_f32, int accumulate, int tile, cudaStream_t stream) {
   using namespace mx;
   NX_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_mxfp8: empty problem");
   NX_REQUIRE(lda % 16 == 0 && ldb % 16 == 0 && K % 32 == 0, "gemm_mxfp8: K must be a multiple of 32, leading dimensions of 16");
@@ -339,12 +365,8 @@ NX_API int NX_SYM(nx_gemm_mxfp8)(const void* A, const void* B, void* C, int M, i
   NX_REQUIRE((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) % 16 == 0,
              "gemm_mxfp8: operands must be 16-byte aligned");
   NX_REQUIRE(sfa != nullptr && sfb != nullptr, "gemm_mxfp8: scale factors are required");
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  NX_REQUIRE(ld_sfa >= static_cast<long long>(tiles_m) * BM && ld_sfb >= static_cast<long long>(tiles_n) * BN,
+  NX_REQUIRE(ld_sfa >= (M + 127) / 128 * 128 && ld_sfb >= (N + 127) / 128 * 128,
              "gemm_mxfp8: scale rows must be padded to multiples of 128 (ld_sfa %lld, ld_sfb %lld)", ld_sfa, ld_sfb);
-  CUtensorMap tmA, tmB;
-  if (!make_tma_2d(&tmA, A, M, K, lda, BM, BK, 1)) return NX_ERR_ARG;
-  if (!make_tma_2d(&tmB, B, N, K, ldb, BN, BK, 1)) return NX_ERR_ARG;
   MxGemmParams p{};
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc;
   p.alpha = static_cast<const float*>(alpha);
@@ -352,20 +374,18 @@ NX_API int NX_SYM(nx_gemm_mxfp8)(const void* A, const void* B, void* C, int M, i
   p.sfa = static_cast<const uint32_t*>(sfa); p.sfb = static_cast<const uint32_t*>(sfb);
   p.ld_sfa = ld_sfa; p.ld_sfb = ld_sfb;
   p.out_f32 = out_f32; p.accumulate = accumulate;
-  p.tiles_m = tiles_m; p.tiles_n = tiles_n;
-  p.idesc = idesc_mxf8(a_e5m2, b_e5m2);
-  p.sf_layout = sf_layout;
   p.err = device_error_word();
-  static bool configured = false;
-  if (!configured) {
-    NX_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_BYTES));
-    configured = true;
+  // measured (8192 x 12288 x 4096 / 8192 x 4096 x 16384): 128: 1287 / 1050, 192: 1724 / 1390, 224: 1909 / 1530,
+  // 256 with one accumulator stage: 2056 / 1899 TFLOP/s -- the wide tile outweighs the unhidden epilogue
+  if (tile == 0) tile = N <= 128 ? 128 : 256;
+  switch (tile) {
+    case 128: return launch<Cfg<128, 2, 6>>(A, B, M, N, K, lda, ldb, p, a_e5m2, b_e5m2, stream);
+    case 192: return launch<Cfg<192, 2, 5>>(A, B, M, N, K, lda, ldb, p, a_e5m2, b_e5m2, stream);
+    case 224: return launch<Cfg<224, 2, 4>>(A, B, M, N, K, lda, ldb, p, a_e5m2, b_e5m2, stream);
+    case 256: return launch<Cfg<256, 1, 4>>(A, B, M, N, K, lda, ldb, p, a_e5m2, b_e5m2, stream);
+    default: NX_REQUIRE(false, "gemm_mxfp8: tile width %d (128, 192, 224 or 256)", tile);
   }
-  const int tiles = tiles_m * tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_mxfp8_kernel<<<grid, THREADS, DYN_BYTES, stream>>>(tmA, tmB, p);
-  NX_LAUNCH_CHECK();
-  return NX_OK;
+  return NX_ERR_ARG;
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -35,8 +35,9 @@ from .positional_embeddings import AliBi, RotaryEmbedding
 
 
 def get_parallel_linear(neox_args):
-    """(column, row) linear classes. The ``te_columnparallel`` / ``te_rowparallel`` switches select
-    the block-scaled fp8 GEMM variants when they are built; otherwise the bf16 layers."""
+    """(column, row) linear classes.  The ``te_columnparallel`` / ``te_rowparallel`` / ``te_layernorm_mlp`` switches do
+    not change the class: the parallel linears themselves run their GEMMs in fp8 then (per-tensor delayed scaling, or
+    block scaling with ``te_fp8_recipe: mxfp8``; parallel/layers.py ``_fp8_or_bf16_linear``)."""
     return mpu.ColumnParallelLinear, mpu.RowParallelLinear
 
 

@@ -201,9 +201,9 @@ def mxfp8_dequantize_reference(q8: torch.Tensor, sf: torch.Tensor, e5m2: bool = 
 
 
 def gemm_mxfp8(a8, sfa, b8, sfb, *, a_e5m2=False, b_e5m2=False, bias=None, out=None, accumulate=False, alpha=None,
-               out_dtype=torch.bfloat16, sf_layout: int = 0):
+               out_dtype=torch.bfloat16, tile: int = 0):
     """C[M,N] = (a8 with its block scales)[M,K] @ (b8 with its block scales)[N,K]^T (+ bias); 16-bit result, or fp32 into
-    ``out`` (optionally +=)."""
+    ``out`` (optionally +=).  ``tile``: tile width of the kernel (0 = its own choice; 128 / 192 / 224 / 256)."""
     M, K = a8.shape
     N = b8.shape[0]
     out_f32 = out is not None and out.dtype == torch.float32
@@ -214,7 +214,7 @@ def gemm_mxfp8(a8, sfa, b8, sfb, *, a_e5m2=False, b_e5m2=False, bias=None, out=N
     _lib.check(_lib.lib(like).nx_gemm_mxfp8(_lib.ptr(a8), _lib.ptr(b8), _lib.ptr(out), M, N, K, a8.stride(0), b8.stride(0),
                                             out.stride(0), _lib.ptr(sfa), _lib.ptr(sfb), sfa.stride(0), sfb.stride(0),
                                             int(a_e5m2), int(b_e5m2), _lib.ptr(alpha), _lib.ptr(bias), int(out_f32),
-                                            int(accumulate), int(sf_layout), _lib.stream()), "nx_gemm_mxfp8")
+                                            int(accumulate), int(tile), _lib.stream()), "nx_gemm_mxfp8")
     return out
 
 

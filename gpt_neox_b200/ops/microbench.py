@@ -8,7 +8,7 @@ timing: the form to put under a profiler.  ``--graph`` captures the operator's l
 first and times replays of it, which takes the Python and launch overhead of a many-launch operator
 out of a microsecond-scale measurement.
 
-ops: gemm, gemm_fp8, gemm_wgrad, attn_fwd, attn_bwd, layernorm, dual_norm_bwd, scan_fwd, scan_bwd, conv1d, moe_fwd, moe_fwdbwd,
+ops: gemm, gemm_fp8, gemm_mxfp8, mxfp8_quantize, gemm_wgrad, attn_fwd, attn_bwd, layernorm, dual_norm_bwd, scan_fwd, scan_bwd, conv1d, moe_fwd, moe_fwdbwd,
      wkv_fwd, wkv_fwdbwd, adamw, ce   (moe: tokens = batch*seq, hidden --n, ffn --k, experts --heads, top-2)
 """
 from __future__ import annotations
@@ -73,6 +73,17 @@ def build(op, a):
         w8, _ = fp8.quantize(rn(N, K), mb)
         alpha = torch.ones(1, device=dev)
         fn = lambda: fp8.gemm_fp8(x8, w8, alpha)
+        return fn, 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N
+    if op in ("gemm_mxfp8", "mxfp8_quantize"):
+        from . import fp8
+        M, N, K = a.m, a.n, a.k
+        if op == "mxfp8_quantize":
+            x = rn(M, N)
+            fn = lambda: fp8.mxfp8_quantize(x)
+            return fn, 0.0, 3.0 * M * N + 4.0 * M * N / 32
+        x8, sx = fp8.mxfp8_quantize(rn(M, K))
+        w8, sw = fp8.mxfp8_quantize(rn(N, K))
+        fn = lambda: fp8.gemm_mxfp8(x8, sx, w8, sw)
         return fn, 2.0 * M * N * K, 1.0 * (M * K + N * K) + 2.0 * M * N
     if op in ("attn_fwd", "attn_bwd"):
         from .attention import flash_attention

@@ -42,6 +42,11 @@ def _device(neox_args):
 def _fp8_or_bf16_linear(mod, x, weight, bias):
     """The module's GEMM: fp8 tensor cores when the module was built with fp8 enabled (``te_columnparallel`` /
     ``te_rowparallel`` / ``te_layernorm_mlp``), the bf16 kernel otherwise."""
+    if getattr(mod, "use_fp8", False) and x.is_cuda and getattr(mod._fp8_args, "te_fp8_recipe", "delayed") == "mxfp8" \
+            and (x.numel() // x.shape[-1]) % 32 == 0 and weight.shape[0] % 32 == 0 and weight.shape[1] % 32 == 0:
+        # block-scaled recipe: one power-of-two scale per 32 elements, no amax history (ops/fp8.py mxfp8_linear)
+        from ..ops.fp8 import mxfp8_linear
+        return mxfp8_linear(x, weight, bias, hybrid=getattr(mod._fp8_args, "te_fp8_format", "hybrid") == "hybrid")
     if getattr(mod, "use_fp8", False) and x.is_cuda and x.dtype == torch.bfloat16 and \
             (x.numel() // x.shape[-1]) % 8 == 0 and weight.shape[0] % 16 == 0 and weight.shape[1] % 16 == 0:
         from ..ops.fp8 import Fp8LinearMeta, fp8_linear

@@ -165,8 +165,9 @@ def test_mxfp8_gemm_applies_every_scale_where_it_belongs(pattern):
     torch.testing.assert_close(out.float(), ref, rtol=1e-2, atol=ref.abs().max().item() * 4e-3)
 
 
+@pytest.mark.parametrize("tile", [0, 128, 192, 224, 256])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 256), (200, 136, 160), (1024, 768, 2048), (130, 8, 32)])
-def test_mxfp8_gemm_matches_dequantised_matmul(M, N, K):
+def test_mxfp8_gemm_matches_dequantised_matmul(M, N, K, tile):
     from gpt_neox_b200.ops import fp8
     torch.manual_seed(3)
     a = (torch.randn(M, K, device="cuda") * (1 + 10 * torch.rand(M, 1, device="cuda"))).bfloat16()
@@ -174,11 +175,11 @@ def test_mxfp8_gemm_matches_dequantised_matmul(M, N, K):
     a8, sa = fp8.mxfp8_quantize(a)
     b8, sb = fp8.mxfp8_quantize(b, e5m2=True)
     bias = torch.randn(N, device="cuda").bfloat16()
-    got = fp8.gemm_mxfp8(a8, sa, b8, sb, b_e5m2=True, bias=bias)
+    got = fp8.gemm_mxfp8(a8, sa, b8, sb, b_e5m2=True, bias=bias, tile=tile)
     want = fp8.mxfp8_dequantize_reference(a8, sa) @ fp8.mxfp8_dequantize_reference(b8, sb, True).t() + bias.float()
     torch.testing.assert_close(got.float(), want, rtol=1e-2, atol=want.abs().max().item() * 4e-3)
     acc = torch.ones(M, N, device="cuda")
-    fp8.gemm_mxfp8(a8, sa, b8, sb, b_e5m2=True, out=acc, accumulate=True)
+    fp8.gemm_mxfp8(a8, sa, b8, sb, b_e5m2=True, out=acc, accumulate=True, tile=tile)
     torch.testing.assert_close(acc, want - bias.float() + 1.0, rtol=1e-3, atol=want.abs().max().item() * 1e-4)
     # against the unquantised product: the error of block-scaled e4m3 x e5m2 operands
     exact = a.float() @ b.float().t()
