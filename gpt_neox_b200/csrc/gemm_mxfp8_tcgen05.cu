@@ -439,6 +439,113 @@ mxfp8_quantize_kernel(const h16* __restrict__ x, long long ldx, uint8_t* __restr
   sf[(static_cast<long long>(g >> 2) * ld_sf + row) * 4 + (g & 3)] = static_cast<uint8_t>(e + 127);
 }
 
+// Both forms from one read: the row-wise form above (scale blocks along the columns: the operand of a GEMM that
+// contracts over the columns) and the column-wise form (out_t [cols, rows] with scale blocks along the ROWS of x: the
+// operand of a GEMM that contracts over the rows, which both backward GEMMs of a linear layer need).  A block takes
+// a 32-row x 256-column tile: thread (row t / 8, group t mod 8) quantises its 32 row elements and leaves the 16-bit
+// values in shared memory, then thread t quantises column t of the tile (32 values down the rows).
+template <bool E5M2>
+__device__ __forceinline__ uint8_t mx_scale_and_quantize(const float (&v)[32], float amax, uint32_t (&q)[8]) {
+  constexpr float FP8_MAX = E5M2 ? 57344.f : 448.f;
+  int e = 0;
+  if (amax > 0.f && amax < INFINITY) {
+    const uint32_t bits = __float_as_uint(amax / FP8_MAX);
+    e = static_cast<int>((bits >> 23) & 0xffu) - 127 + ((bits & 0x7fffffu) != 0u ? 1 : 0);
+    e = max(-127, min(127, e));
+  }
+  const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t wq = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      wq |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i * 4 + j] * inv, __NV_SATFINITE, E5M2 ? __NV_E5M2 : __NV_E4M3))
+            << (8 * j);
+    q[i] = wq;
+  }
+  return static_cast<uint8_t>(e + 127);
+}
+
+template <bool E5M2>
+__global__ void __launch_bounds__(256)
+mxfp8_quantize_dual_kernel(const h16* __restrict__ x, long long ldx, uint8_t* __restrict__ out, long long ldo,
+                           uint8_t* __restrict__ sf, long long ld_sf, uint8_t* __restrict__ out_t, long long ldt,
+                           uint8_t* __restrict__ sf_t, long long ld_sft, int rows, int cols) {
+  __shared__ __align__(16) h16 tile[32][256 + 8];
+  const int r0 = blockIdx.y * 32, c0 = blockIdx.x * 256;
+  const int t = threadIdx.x;
+  {
+    const int r = t >> 3, g = t & 7;
+    const int row = r0 + r, col = c0 + g * 32;
+    if (row < rows && col < cols) {
+      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * ldx + col);
+      float v[32];
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 u = src[i];
+        *reinterpret_cast<uint4*>(&tile[r][g * 32 + i * 8]) = u;
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_h16x2(w[j]);
+          v[i * 8 + 2 * j] = f.x;
+          v[i * 8 + 2 * j + 1] = f.y;
+          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+      }
+      uint32_t q[8];
+      const uint8_t sb = mx_scale_and_quantize<E5M2>(v, amax, q);
+      uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(row) * ldo + col);
+      dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+      dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+      const int gg = col >> 5;
+      sf[(static_cast<long long>(gg >> 2) * ld_sf + row) * 4 + (gg & 3)] = sb;
+    }
+  }
+  __syncthreads();
+  const int col = c0 + t;
+  if (col < cols && r0 + 32 <= rows) {
+    float v[32];
+    float amax = 0.f;
+#pragma unroll
+    for (int r = 0; r < 32; ++r) {
+      v[r] = h16_to_float(tile[r][t]);
+      amax = fmaxf(amax, fabsf(v[r]));
+    }
+    uint32_t q[8];
+    const uint8_t sb = mx_scale_and_quantize<E5M2>(v, amax, q);
+    uint4* dst = reinterpret_cast<uint4*>(out_t + static_cast<long long>(col) * ldt + r0);
+    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+    const int gg = r0 >> 5;
+    sf_t[(static_cast<long long>(gg >> 2) * ld_sft + col) * 4 + (gg & 3)] = sb;
+  }
+}
+
+// x 16-bit [rows, cols] (rows and cols multiples of 32): out [rows, cols] + sf as nx_mxfp8_quantize, and out_t
+// [cols, rows] + sf_t = the same for x transposed (scale blocks along the rows of x).  Both scale arrays pre-filled
+// with 0x7f7f7f7f by the caller.
+NX_API int NX_SYM(nx_mxfp8_quantize_dual)(const void* x, long long ldx, void* out, long long ldo, void* sf,
+                                          long long ld_sf, void* out_t, long long ldt, void* sf_t, long long ld_sft,
+                                          int rows, int cols, int e5m2, cudaStream_t stream) {
+  NX_REQUIRE(rows % 32 == 0 && cols % 32 == 0 && ldx % 8 == 0 && ldo % 16 == 0 && ldt % 16 == 0,
+             "mxfp8_quantize_dual: rows and columns must be multiples of 32");
+  NX_REQUIRE(ld_sf >= rows && ld_sft >= cols, "mxfp8_quantize_dual: scale rows");
+  NX_REQUIRE((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out_t)) % 16 == 0,
+             "mxfp8_quantize_dual: alignment");
+  if (rows <= 0 || cols <= 0) return NX_OK;
+  dim3 grid((cols + 255) / 256, rows / 32);
+  if (e5m2)
+    mxfp8_quantize_dual_kernel<true><<<grid, 256, 0, stream>>>((const h16*)x, ldx, (uint8_t*)out, ldo, (uint8_t*)sf, ld_sf,
+                                                               (uint8_t*)out_t, ldt, (uint8_t*)sf_t, ld_sft, rows, cols);
+  else
+    mxfp8_quantize_dual_kernel<false><<<grid, 256, 0, stream>>>((const h16*)x, ldx, (uint8_t*)out, ldo, (uint8_t*)sf, ld_sf,
+                                                                (uint8_t*)out_t, ldt, (uint8_t*)sf_t, ld_sft, rows, cols);
+  NX_LAUNCH_CHECK();
+  return NX_OK;
+}
+
 // x 16-bit [rows, cols] (cols % 32 == 0); out fp8 [rows, cols]; sf: scale words [ceil(cols / 128)][ld_sf], which the
 // caller has filled with 0x7f7f7f7f (the kernel writes only the bytes of real rows and groups).
 NX_API int NX_SYM(nx_mxfp8_quantize)(const void* x, long long ldx, void* out, long long ldo, void* sf, long long ld_sf,

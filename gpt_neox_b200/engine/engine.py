@@ -879,6 +879,9 @@ class Engine(torch.nn.Module):
             symm.pool_reset_all()           # no gathered activation outlives the step: every gather-pool slot is free
         for m in self._fp8_modules():
             m.fp8_meta.roll()               # delayed scaling: this step's amax feeds the next steps' scales
+        if getattr(self.neox_args, "te_fp8_recipe", "delayed") == "mxfp8":
+            from ..ops import fp8
+            fp8.mxfp8_new_step()            # block scaling: the weights changed, their quantised copies are stale
         if overflow:
             self.skipped_steps += 1
         elif self.lr_scheduler is not None:

@@ -112,6 +112,7 @@ def _declare(lib):
     sig("nx_fp8_quantize", [P, L, P, P, L, P, L, P, I, I, I, P])
     sig("nx_gemm_mxfp8", [P, P, P, I, I, I, L, L, L, P, P, L, L, I, I, P, P, I, I, I, P])
     sig("nx_mxfp8_quantize", [P, L, P, L, P, L, I, I, I, P])
+    sig("nx_mxfp8_quantize_dual", [P, L, P, L, P, L, P, L, P, L, I, I, I, P])
     sig("nx_moe_blocks", [I])
     sig("nx_moe_max_rows", [I, I])
     sig("nx_moe_plan", [P, I, I, P, P, P, P, P, P, P, P])

@@ -218,43 +218,92 @@ def gemm_mxfp8(a8, sfa, b8, sfb, *, a_e5m2=False, b_e5m2=False, bias=None, out=N
     return out
 
 
+def mxfp8_quantize_dual(x2: torch.Tensor, e5m2: bool = False):
+    """One read of x [rows, cols] (both multiples of 32), both quantised forms: (q [rows, cols], sf) with the scale
+    blocks along the columns, and (q_t [cols, rows], sf_t) = the same for x transposed (blocks along the rows of x)."""
+    rows, cols = x2.shape
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    dev = x2.device
+    out = torch.empty((rows, cols), device=dev, dtype=torch.uint8)
+    out_t = torch.empty((cols, rows), device=dev, dtype=torch.uint8)
+    sf = torch.full(((cols + 127) // 128, _pad128(rows)), 0x7F7F7F7F, device=dev, dtype=torch.int32)
+    sf_t = torch.full(((rows + 127) // 128, _pad128(cols)), 0x7F7F7F7F, device=dev, dtype=torch.int32)
+    LAUNCHES["n"] += 1
+    _lib.check(_lib.lib(x2).nx_mxfp8_quantize_dual(_lib.ptr(x2), x2.stride(0), _lib.ptr(out), cols, _lib.ptr(sf),
+                                                   sf.stride(0), _lib.ptr(out_t), rows, _lib.ptr(sf_t), sf_t.stride(0),
+                                                   rows, cols, int(e5m2), _lib.stream()), "nx_mxfp8_quantize_dual")
+    return out, sf, out_t, sf_t
+
+
+#: quantised weights are reused by every micro-batch of an optimizer step: id(weight) -> (step generation, data pointer,
+#: tensor version, the four tensors of mxfp8_quantize_dual).  The engine bumps the generation after every optimizer step
+#: (its fused update writes the weights through raw pointers, which no tensor version records).
+_MX_WEIGHTS: dict = {}
+_MX_GENERATION = {"n": 0}
+
+
+def mxfp8_new_step():
+    _MX_GENERATION["n"] += 1
+    if len(_MX_WEIGHTS) > 4096:
+        _MX_WEIGHTS.clear()
+
+
+def _mx_weight(weight):
+    key = (_MX_GENERATION["n"], weight.data_ptr(), weight._version)
+    hit = _MX_WEIGHTS.get(id(weight))
+    if hit is None or hit[0] != key:
+        hit = (key, mxfp8_quantize_dual(weight.detach()))
+        _MX_WEIGHTS[id(weight)] = hit
+    return hit[1]
+
+
 class _MxFp8LinearFn(torch.autograd.Function):
     """y = x W^T (+ b) with all three GEMMs block-scaled.  Every GEMM contracts over the dimension its operands were
     quantised along: forward x [M,K] and W [N,K] along K; input gradient dY [M,N] and W^T [K,N] along N; weight
-    gradient dY^T [N,M] and x^T [K,M] along M (the transposed copies are made before quantising, since the scale
-    blocks run along the contracted dimension)."""
+    gradient dY^T [N,M] and x^T [K,M] along M.  The transposed forms come out of the same quantiser pass as the
+    straight ones (one read of x, of dY and -- once per optimizer step -- of W)."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, hybrid):
         x2 = x.reshape(-1, x.shape[-1])
-        x8, sx = mxfp8_quantize(x2)
-        w8, sw = mxfp8_quantize(weight)
+        need_wgrad = ctx.needs_input_grad[1]
+        w8, sw, wt8, swt = _mx_weight(weight)
+        if need_wgrad and x2.shape[0] % 32 == 0:
+            x8, sx, xt8, sxt = mxfp8_quantize_dual(x2)
+        else:
+            (x8, sx), xt8, sxt = mxfp8_quantize(x2), None, None
         y = gemm_mxfp8(x8, sx, w8, sw, bias=bias, out_dtype=x.dtype)
-        ctx.save_for_backward(x2, weight)
-        ctx.has_bias, ctx.x_shape, ctx.hybrid = bias is not None, x.shape, hybrid
+        ctx.save_for_backward(xt8, sxt, wt8, swt, x2 if (need_wgrad and xt8 is None) else None)
+        ctx.weight, ctx.bias, ctx.has_bias, ctx.x_shape, ctx.hybrid = weight, bias, bias is not None, x.shape, hybrid
         return y.view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, gy):
-        x2, weight = ctx.saved_tensors
+        xt8, sxt, wt8, swt, x2 = ctx.saved_tensors
+        weight = ctx.weight
         g2 = gy.reshape(-1, gy.shape[-1])
         e5 = bool(ctx.hybrid)
         gx = gw = gb = None
-        if ctx.needs_input_grad[0]:
+        need_gw = ctx.needs_input_grad[1]
+        if need_gw and g2.shape[0] % 32 == 0:
+            g8, sg, gt8, sgt = mxfp8_quantize_dual(g2, e5m2=e5)
+        else:
             g8, sg = mxfp8_quantize(g2, e5m2=e5)
-            wt8, swt = mxfp8_quantize(weight.t().contiguous())
+            gt8, sgt = mxfp8_quantize(g2.t().contiguous(), e5m2=e5) if need_gw else (None, None)
+        if ctx.needs_input_grad[0]:
             gx = gemm_mxfp8(g8, sg, wt8, swt, a_e5m2=e5, out_dtype=gy.dtype).view(ctx.x_shape)
-        if ctx.needs_input_grad[1]:
-            gt8, sgt = mxfp8_quantize(g2.t().contiguous(), e5m2=e5)
-            xt8, sxt = mxfp8_quantize(x2.t().contiguous())
+        if need_gw:
+            if xt8 is None:
+                xt8, sxt = mxfp8_quantize(x2.t().contiguous())
             mg = getattr(weight, "main_grad", None)
             if mg is not None and mg.dtype == torch.float32:
                 gemm_mxfp8(gt8, sgt, xt8, sxt, a_e5m2=e5, out=mg, accumulate=True, out_dtype=gy.dtype)
             else:
                 gw = gemm_mxfp8(gt8, sgt, xt8, sxt, a_e5m2=e5, out_dtype=gy.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            from .elementwise import colsum
-            gb = colsum(g2.contiguous())
+            from .elementwise import bias_grad
+            gb = bias_grad(g2.contiguous(), ctx.bias)
         return gx, gw, gb, None
 
 

@@ -202,3 +202,39 @@ def test_mxfp8_linear_tracks_16_bit_linear():
     nerr = lambda u, v: ((u.float() - v).norm() / v.norm()).item()   # noqa: E731
     assert nerr(y, yr) < 0.06 and nerr(x.grad, xr.grad) < 0.12 and nerr(w.grad, wr.grad) < 0.12
     assert nerr(b.grad, br.grad) < 1e-2
+
+
+@pytest.mark.parametrize("rows,cols,e5m2", [(64, 96, False), (320, 1024, True), (8192, 512, False)])
+def test_mxfp8_dual_quantiser_gives_both_forms_from_one_read(rows, cols, e5m2):
+    """The row-wise form equals the single quantiser's, the column-wise form equals quantising the transposed tensor."""
+    from gpt_neox_b200.ops import fp8
+    torch.manual_seed(5)
+    x = (torch.randn(rows, cols, device="cuda") * (torch.rand(rows, 1, device="cuda") * 30)).bfloat16()
+    q, sf, qt, sft = fp8.mxfp8_quantize_dual(x, e5m2=e5m2)
+    q1, sf1 = fp8.mxfp8_quantize_reference(x, e5m2=e5m2)
+    q2, sf2 = fp8.mxfp8_quantize_reference(x.t().contiguous(), e5m2=e5m2)
+    assert torch.equal(q, q1) and torch.equal(sf, sf1)
+    assert torch.equal(qt, q2) and torch.equal(sft, sf2)
+
+
+def test_mxfp8_weights_are_quantised_once_per_step():
+    """The quantised forms of a weight are reused until the weight changes (a tensor version bump) or a new optimizer
+    step is announced (the engine's fused update writes through raw pointers)."""
+    from gpt_neox_b200.ops import fp8
+    torch.manual_seed(6)
+    x = torch.randn(64, 256, device="cuda").bfloat16()
+    w = (torch.randn(128, 256, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    fp8.mxfp8_linear(x, w)
+    first = fp8._MX_WEIGHTS[id(w)][1][0]
+    fp8.mxfp8_linear(x, w)
+    assert fp8._MX_WEIGHTS[id(w)][1][0] is first
+    with torch.no_grad():
+        w.mul_(2.0)
+    y = fp8.mxfp8_linear(x, w)
+    assert fp8._MX_WEIGHTS[id(w)][1][0] is not first
+    second = fp8._MX_WEIGHTS[id(w)][1][0]
+    fp8.mxfp8_new_step()
+    fp8.mxfp8_linear(x, w)
+    assert fp8._MX_WEIGHTS[id(w)][1][0] is not second
+    ref = x.float() @ w.detach().float().t()
+    assert ((y.float() - ref).norm() / ref.norm()).item() < 0.06
