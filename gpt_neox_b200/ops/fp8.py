@@ -56,6 +56,7 @@ class Fp8LinearMeta:
 
     def roll(self):
         self.x.roll(), self.w.roll(), self.g.roll()
+        self._w_cache = None              # new scale, new weights: the quantised weight copies are stale
 
 
 def quantize(x2, meta: Fp8TensorMeta, transpose=False):
@@ -84,6 +85,18 @@ def gemm_fp8(a8, b8, alpha, *, a_e5m2=False, b_e5m2=False, bias=None, out=None, 
     return out
 
 
+def _delayed_weight(weight, meta: "Fp8LinearMeta", transpose: bool):
+    """The quantised weight (and its transpose) of this optimizer step.  Under delayed scaling the weight's scale
+    changes only when the history rolls (once per step) and the weight itself only in the optimizer step, so every
+    micro-batch of a step reuses the first one's copies.  ``Fp8LinearMeta.roll`` drops them."""
+    key = (weight.data_ptr(), weight._version, bool(transpose))
+    hit = getattr(meta, "_w_cache", None)
+    if hit is None or hit[0] != key:
+        hit = (key, quantize(weight, meta.w, transpose=transpose))
+        meta._w_cache = hit
+    return hit[1]
+
+
 class _Fp8LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, meta: Fp8LinearMeta):
@@ -92,7 +105,7 @@ class _Fp8LinearFn(torch.autograd.Function):
             x2 = x2.contiguous()
         need_wgrad = weight.requires_grad
         x8, x8t = quantize(x2, meta.x, transpose=need_wgrad and meta.fp8_wgrad)
-        w8, w8t = quantize(weight, meta.w, transpose=x.requires_grad)
+        w8, w8t = _delayed_weight(weight, meta, transpose=x.requires_grad)
         alpha = 1.0 / (meta.x.scale * meta.w.scale)
         y = gemm_fp8(x8, w8, alpha, bias=bias)
         ctx.save_for_backward(x8t, w8t, meta.x.scale.clone(), meta.w.scale.clone(),
