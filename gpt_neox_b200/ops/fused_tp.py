@@ -31,8 +31,11 @@ def backend(x, group):
 
 def _keeps(ctx) -> bool:
     """Ask for a pool slot only when a backward pass will come for it (the input gradient's fused reduce-scatter is
-    what makes the release safe, the weight gradient is what reads the slot)."""
-    return bool(ctx.needs_input_grad[0] and ctx.needs_input_grad[1])
+    what makes the release safe, the weight gradient is what reads the slot).  Under pipeline parallelism, where the
+    forward passes of later micro-batches run between the backward passes of earlier ones, the gathered operand is
+    copied as before: the pooled form has only been run with one micro-batch in flight."""
+    from .. import parallel as mpu
+    return bool(ctx.needs_input_grad[0] and ctx.needs_input_grad[1] and mpu.get_pipe_parallel_world_size() == 1)
 
 
 def _release(ctx):
