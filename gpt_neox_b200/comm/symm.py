@@ -50,6 +50,28 @@ def _declare():
     return L
 
 
+class SlotPool:
+    """Which of ``n`` equal slots are free.  Every rank of a group makes the same alloc / release / reset calls in the
+    same order, so all ranks pick the same slot without talking to each other: ``alloc`` always takes the lowest free
+    index."""
+
+    def __init__(self, n: int):
+        self.n = int(n)
+        self.free = list(range(self.n))
+        heapq.heapify(self.free)
+
+    def alloc(self):
+        return heapq.heappop(self.free) if self.free else None
+
+    def release(self, slot: int):
+        if not 0 <= slot < self.n or slot in self.free:
+            raise ValueError(f"slot {slot} is not an allocated slot of this pool")
+        heapq.heappush(self.free, slot)
+
+    def reset(self):
+        self.free = list(range(self.n))
+
+
 class SymmBackend:
     def __init__(self, group, nbytes: int = DEFAULT_BYTES):
         import torch.distributed._symmetric_memory as symm_mem
@@ -141,27 +163,26 @@ class SymmBackend:
         flag = torch.tensor([ok], device=self.buf.device, dtype=torch.int32)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
         if int(flag.item()) == 1:
-            self.pool = {"buf": buf, "hdl": hdl, "slot": slot, "n": n, "free": list(range(n)),
+            self.pool = {"buf": buf, "hdl": hdl, "slot": slot, "n": n, "slots": SlotPool(n),
                          "ptrs": [int(p) for p in hdl.buffer_ptrs]}
-            heapq.heapify(self.pool["free"])
 
     def pool_alloc(self, nbytes: int):
         """Lowest free slot that holds ``nbytes``, or None (pool off, exhausted, or slots too small).  Every rank of the
         group calls alloc / release / reset at the same points of the program, so all pick the same slot."""
         if self.pool is None:
             self._pool_create(nbytes)
-        if not self.pool or nbytes > self.pool["slot"] or not self.pool["free"]:
+        if not self.pool or nbytes > self.pool["slot"]:
             return None
-        return heapq.heappop(self.pool["free"])
+        return self.pool["slots"].alloc()
 
     def pool_release(self, slot):
-        if slot is not None and self.pool:
-            heapq.heappush(self.pool["free"], slot)
+        if slot is not None and self.pool and slot not in self.pool["slots"].free:    # (a reset may have freed it already)
+            self.pool["slots"].release(slot)
 
     def pool_reset(self):
         """Every slot free again (between optimizer steps no gathered activation is alive)."""
         if self.pool:
-            self.pool["free"] = list(range(self.pool["n"]))
+            self.pool["slots"].reset()
 
     def ag_gemm(self, x_shard, w, *, trans_b=False, bias=None, gelu=None, aux_out=None, dgelu_aux=None,
                 dgelu=None, aux_deriv=False, keep=False):

@@ -248,3 +248,27 @@ def test_comet_experiment_gets_name_tags_and_parameters(monkeypatch):
     assert calls["init"] == dict(workspace="ws", project_name="proj")
     assert calls["name"] == "run-7" and calls["tags"] == ["a", "b"] and calls["others"] == {"k": 1}
     assert calls["params"]["hidden_size"] == 64
+
+
+def test_gather_slot_pool_is_deterministic():
+    """Ranks agree on gather-buffer slots without communicating: the same call sequence gives the same slots, the lowest
+    free index first; a reset frees everything; releasing a slot twice is an error."""
+    pytest.importorskip("torch")
+    from gpt_neox_b200.comm.symm import SlotPool
+    a, b = SlotPool(4), SlotPool(4)
+    seq = []
+    for pool in (a, b):
+        got = [pool.alloc(), pool.alloc(), pool.alloc()]
+        pool.release(got[1])
+        got.append(pool.alloc())            # the released slot comes back first
+        got.append(pool.alloc())
+        got.append(pool.alloc())            # exhausted
+        seq.append(got)
+    assert seq[0] == seq[1] == [0, 1, 2, 1, 3, None]
+    with pytest.raises(ValueError):
+        a.release(7)
+    a.release(2)
+    with pytest.raises(ValueError):
+        a.release(2)
+    a.reset()
+    assert [a.alloc() for _ in range(5)] == [0, 1, 2, 3, None]
