@@ -62,8 +62,10 @@ def test_fp8_linear_tracks_bf16_linear():
     assert meta.x.scale.item() > 1.0
 
 
-def test_fp8_model_loss_tracks_bf16_model():
-    """Same weights, linear layers on fp8 tensor cores vs bf16: first losses agree, and the fp8 model trains."""
+@pytest.mark.parametrize("recipe", ["delayed", "mxfp8"])
+def test_fp8_model_loss_tracks_bf16_model(recipe):
+    """Same weights, linear layers on fp8 tensor cores (per-tensor delayed scaling, or block scaling) vs bf16: first
+    losses agree, and so do the weight gradients."""
     from common import tiny_config
     from gpt_neox_b200 import parallel as mpu
     from gpt_neox_b200 import training
@@ -75,7 +77,8 @@ def test_fp8_model_loss_tracks_bf16_model():
                 precision="bfloat16")
     models = []
     for fp8_on in (False, True):
-        a = NeoXArgs.from_dict(tiny_config(**base, te_columnparallel=fp8_on, te_rowparallel=fp8_on))
+        a = NeoXArgs.from_dict(tiny_config(**base, te_columnparallel=fp8_on, te_rowparallel=fp8_on,
+                                           te_fp8_recipe=recipe))
         a.configure_distributed_args()
         a.build_tokenizer()
         mpu.destroy_model_parallel()
@@ -96,7 +99,12 @@ def test_fp8_model_loss_tracks_bf16_model():
     g0 = dict(models[0].named_parameters())["sequential.2.mlp.linear1.weight"].grad.float()
     g1 = dict(models[1].named_parameters())["sequential.2.mlp.linear1.weight"].grad.float()
     assert ((g0 - g1).norm() / g0.norm()).item() < 0.2
-    assert any(getattr(m, "fp8_meta", None) is not None for m in models[1].modules())
+    if recipe == "delayed":
+        assert any(getattr(m, "fp8_meta", None) is not None for m in models[1].modules())
+    else:
+        from gpt_neox_b200.ops import fp8
+        w = dict(models[1].named_parameters())["sequential.2.mlp.linear1.weight"]
+        assert id(w) in fp8._MX_WEIGHTS                   # the block-scaled path ran (and cached its quantised weights)
 
 
 # ------------------------------------------------------------------------------------------------ block-scaled (MXFP8)
