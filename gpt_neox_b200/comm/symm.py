@@ -149,7 +149,7 @@ class SymmBackend:
         self.pool = False
         budget = int(float(os.environ.get("NEOX_AG_POOL_GB", "8")) * (1 << 30))
         slot = (slot_bytes + 4095) // 4096 * 4096
-        n = min(budget // slot, 4096) if slot > 0 else 0
+        n = min(budget // slot, 512) if slot > 0 else 0          # (small models: do not turn the whole budget into slots)
         ok, buf, hdl = 1, None, None
         if n < 2:
             ok = 0
