@@ -185,11 +185,11 @@ class SymmBackend:
             self.pool["slots"].reset()
 
     def ag_gemm(self, x_shard, w, *, trans_b=False, bias=None, gelu=None, aux_out=None, dgelu_aux=None,
-                dgelu=None, aux_deriv=False, keep=False):
+                dgelu=None, aux_deriv=False, keep=None):
         """``y = all_gather_rows(x_shard) @ op(w) (+ epilogue)``. Returns (y [M, N], gathered x [M, K]): the
         gathered matrix is a view of the symmetric gather buffer, valid until the second next call.  With
-        ``keep`` a third value is returned: a pool slot (or None if none was to be had); the gathered matrix then
-        lives in that slot until ``pool_release(slot)``.  A peer may push the next gather into a released slot as soon
+        ``keep`` given (True or False) a third value is returned: a pool slot, or None if none was asked for (False) or
+        to be had; with a slot the gathered matrix lives in it until ``pool_release(slot)``.  A peer may push the next gather into a released slot as soon
         as it has finished the fused call that follows the release in program order, so every read of the slot must be
         enqueued BEFORE the first fused call after the release."""
         from ..ops import gemm as G
@@ -226,7 +226,7 @@ class SymmBackend:
             _lib.ptr(bias), _lib.ptr(dgelu_aux), _lib.ptr(aux_out), None, ld_aux, flags, 2, self.me, self.ws, epoch,
             dst_table, self._table(self.ag_flag_off), None, 0, _lib.ptr(x_shard), x_shard.stride(0),
             _lib.stream()), "nx_gemm_bf16_comm(all-gather)")
-        return (out, gathered, slot) if keep else (out, gathered)
+        return (out, gathered, slot) if keep is not None else (out, gathered)
 
     def gemm_rs(self, a, w, *, trans_b=False, residual=None, bias=None, residual2=None, dgelu_aux=None, dgelu=None):
         """``out = reduce_scatter_rows(a @ op(w) + residual) + bias + residual2`` -> [M / ws, N]."""

@@ -86,6 +86,41 @@ def main():
         dist.all_reduce(full, group=group)
         done["gemm_ar"] = close(out, full + bias.float(), "gemm_ar")
 
+    # ---- the autograd functions of the fused linears: without grad (no pool slot is asked for), with an input that
+    #      needs no gradient (none either), and the training case (gathered operand kept in a pool slot)
+    from gpt_neox_b200.ops import fused_tp
+    m_shard, k, n = 256, 512, 384
+    w0 = rnd(n, k, scale=0.05)
+    dist.broadcast(w0, 0)
+    b0 = rnd(n)
+    dist.broadcast(b0, 0)
+    x0 = rnd(m_shard, k)
+    xf = nccl_gather_rows(x0, group).float()
+    ref = xf @ w0.float().t() + b0.float()
+    with torch.no_grad():
+        done["ag_linear_no_grad"] = close(fused_tp.ag_linear(x0, w0, b0, be), ref, "ag_linear under no_grad")
+    wp, bp = w0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+    y = fused_tp.ag_linear(x0, wp, bp, be)                                   # x needs no gradient
+    gy = rnd(m_shard * ws, n)
+    dist.broadcast(gy, 0)
+    y.backward(gy)
+    done["ag_linear_weight_only"] = close(wp.grad, gy.float().t() @ xf, "ag_linear dW (input without grad)")
+    xp, wp, bp = x0.clone().requires_grad_(True), w0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+    be.pool_release(be.pool_alloc(m_shard * ws * k * 2))                     # (creates the pool on first use)
+    slots_before = len(be.pool["slots"].free) if be.pool else -1
+    y = fused_tp.ag_linear(xp, wp, bp, be)
+    in_use = (slots_before - len(be.pool["slots"].free)) if be.pool else 0
+    y.backward(gy)
+    done["ag_linear_train"] = close(y, ref, "ag_linear forward")
+    close(wp.grad, gy.float().t() @ xf, "ag_linear dW")
+    dx_full = gy.float() @ w0.float()
+    dist.all_reduce(dx_full, group=group)                                    # every rank holds the same dY: sum = ws x
+    close(xp.grad, dx_full[rank * m_shard:(rank + 1) * m_shard], "ag_linear dX (reduce-scattered)")
+    close(bp.grad, gy.float().sum(0), "ag_linear db", 2e-2, 1e-2)
+    if be.pool:
+        assert in_use == 1 and len(be.pool["slots"].free) == slots_before, "pool slot not taken / not given back"
+    done["gather_pool_slots"] = float(be.pool["n"]) if be.pool else 0.0
+
     # ---- stand-alone collectives over peer memory (16-bit and fp32)
     for dt, tag in ((dtype, "h16"), (torch.float32, "f32")):
         x = (torch.randn(ws * 96, 1000, device=dev, generator=g)).to(dt)
