@@ -120,3 +120,42 @@ def test_mlp_gelu_sp_glue(pooled):
     assert be.log.count("release") == (1 if pooled else 0)
     if pooled:
         assert be.log.index("release") < len(be.log) - 1 - be.log[::-1].index("gemm_rs")   # before the last fused call
+
+
+@pytest.mark.parametrize("with_bias,with_res", [(True, True), (False, False)])
+def test_linear_rs_glue(with_bias, with_res):
+    x, _, _, w2 = _tensors()
+    x = torch.randn(12, 24)
+    b = torch.randn(16) * 0.1 if with_bias else None
+    res = torch.randn(12, 16) * 0.1 if with_res else None
+    be = FakeBackend(0)
+    leaves = [t.clone().requires_grad_(True) if t is not None else None for t in (x, w2, b, res)]
+    y = fused_tp.linear_rs(leaves[0], leaves[1], leaves[2], leaves[3], be)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref = [t.clone().requires_grad_(True) if t is not None else None for t in (x, w2, b, res)]
+    yr = ref[0] @ ref[1].t()
+    if with_bias:
+        yr = yr + ref[2]
+    if with_res:
+        yr = yr + ref[3]
+    yr.backward(g)
+    for a, r in zip(leaves, ref):
+        if a is not None:
+            assert torch.allclose(a.grad, r.grad, atol=2e-4)
+
+
+def test_bias_gradient_goes_straight_into_main_grad_when_present():
+    """With an fp32 ``main_grad`` on the bias (what the engine installs) the glue returns no gradient for it and the sum
+    lands in ``main_grad``; on CPU the reduction kernel's stand-in adds it."""
+    x, w, b, _ = _tensors()
+    be = FakeBackend(1)
+    xp, wp, bp = x.clone().requires_grad_(True), w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    bp.main_grad = torch.ones(b.shape, dtype=torch.float32)
+    y = fused_tp.ag_linear(xp, wp, bp, be)
+    g = torch.randn_like(y)
+    y.backward(g)
+    if bp.grad is None:                   # CUDA-only fast path is not taken on CPU tensors: the plain column sum is used
+        assert torch.allclose(bp.main_grad, torch.ones_like(bp.main_grad) + g.sum(0), atol=1e-4)
+    else:
+        assert torch.allclose(bp.grad, g.sum(0), atol=1e-4)
