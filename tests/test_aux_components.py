@@ -272,3 +272,28 @@ def test_gather_slot_pool_is_deterministic():
         a.release(2)
     a.reset()
     assert [a.alloc() for _ in range(5)] == [0, 1, 2, 3, None]
+
+
+def test_bucketed_reduction_covers_every_element_exactly_once():
+    """The ranges reduced from inside the backward pass plus the leftovers reduced at the step tile the flat gradient
+    buffer without overlap: with a pre-division factor every element ends up divided exactly once."""
+    torch = pytest.importorskip("torch")
+    from gpt_neox_b200.engine.engine import FlatGroup
+    ps = [torch.nn.Parameter(torch.randn(n)) for n in (100, 64, 7, 300)]
+    g = FlatGroup([(p, 0.1 if i % 2 == 0 else 0.0) for i, p in enumerate(ps)], None, 1, 0, 1, torch.float32)
+    g.predivide = 4.0
+    g.main_grad.fill_(8.0)
+    ranges = g.param_ranges([ps[1], ps[3]])
+    assert all(lo % 64 == 0 and hi % 64 == 0 for lo, hi in ranges)
+    assert sum(hi - lo for lo, hi in ranges) == 64 + 320            # alignment padding included
+    for lo, hi in ranges:
+        g.reduce_range_async(lo, hi)
+    inside = torch.zeros(g.total, dtype=torch.bool)
+    for lo, hi in ranges:
+        inside[lo:hi] = True
+    assert (g.main_grad[inside] == 2.0).all() and (g.main_grad[~inside] == 8.0).all()
+    g.reduce_gradients()                                             # the leftovers, then the wait
+    assert (g.main_grad == 2.0).all() and g._reduced == []
+    g.main_grad.fill_(8.0)
+    g.reduce_gradients()                                             # nothing bucketed this time: the single reduction
+    assert (g.main_grad == 2.0).all()
